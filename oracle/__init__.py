@@ -1,0 +1,431 @@
+"""CPU checkers for the moty quantized-matmul path.  TEST INFRASTRUCTURE ONLY.
+
+Two shared libraries are wrapped here with ctypes + numpy:
+
+* ``Oracle``  -- ``libmoty_oracle.so``, the plain-C restatement (moty_oracle.c);
+* ``Ref``     -- ``_ref/libmoty_ref_<tier>.so``, the unmodified reference sources
+  compiled by ``oracle/Makefile`` (present only where they were built or shipped
+  prebuilt).
+
+Nothing in the shipped package may import this module; it exists for the tests,
+the smoke check and the benchmark's CPU-baseline arm.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+WF_F32, WF_I8, WF_I4, WF_I2, WF_I4G, WF_Q4K, WF_Q6K, WF_Q4R4, WF_Q8R4 = range(9)
+
+
+def _p(a, t=None):
+    if a is None:
+        return None
+    assert a.flags["C_CONTIGUOUS"], "array must be contiguous"
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def build(ref_src: str = "/root/reference/c") -> None:
+    """Compile the restatement (always) and the reference (when its sources exist)."""
+    subprocess.check_call(["make", "-s", "-C", HERE, "all", f"REF={ref_src}"])
+
+
+def _cpu_has(flag: str) -> bool:
+    try:
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    return flag in line.split()
+    except OSError:
+        pass
+    return False
+
+
+class _ExpertsI8(C.Structure):
+    _fields_ = [("E", C.c_int), ("K", C.c_int), ("I", C.c_int), ("D", C.c_int),
+                ("g", C.c_void_p), ("u", C.c_void_p), ("d", C.c_void_p),
+                ("gs", C.c_void_p), ("us", C.c_void_p), ("ds", C.c_void_p)]
+
+
+class Experts:
+    """Expert-major arrays of one MoE layer (int8 per-row or Q4R4)."""
+
+    def __init__(self, E, K, I, D, g, u, d, gs, us, ds):
+        self.E, self.K, self.I, self.D = E, K, I, D
+        self.g, self.u, self.d, self.gs, self.us, self.ds = (np.ascontiguousarray(a) for a in (g, u, d, gs, us, ds))
+        self.c = _ExpertsI8(E, K, I, D, *(a.ctypes.data for a in (self.g, self.u, self.d, self.gs, self.us, self.ds)))
+
+
+class Oracle:
+    """The C restatement.  Shapes follow the reference: x [S][I], y [S][O]."""
+
+    def __init__(self):
+        path = os.path.join(HERE, "libmoty_oracle.so")
+        if not os.path.exists(path):
+            build()
+        self.lib = C.CDLL(path)
+        L = self.lib
+        L.oracle_qrow_i8.restype = C.c_float
+        L.oracle_f16_to_f32.restype = C.c_float
+        L.oracle_f16_to_f32.argtypes = [C.c_uint16]
+        L.oracle_f32_to_f16.restype = C.c_uint16
+        L.oracle_f32_to_f16.argtypes = [C.c_float]
+        L.oracle_dot_i8i8.restype = C.c_int32
+        L.oracle_dot_i4i8.restype = C.c_int32
+        L.oracle_argmax.restype = C.c_int
+
+    # -- scalars -------------------------------------------------------
+    def f16_to_f32(self, h):
+        return self.lib.oracle_f16_to_f32(int(h))
+
+    def f32_to_f16(self, f):
+        return self.lib.oracle_f32_to_f16(float(np.float32(f)))
+
+    # -- quantizers ----------------------------------------------------
+    def qrow_i8(self, x):
+        x = _f32(x)
+        q = np.empty(x.shape, np.int8)
+        s = self.lib.oracle_qrow_i8(_p(x), _p(q), C.c_int(x.size))
+        return q, np.float32(s)
+
+    def qrows_i8(self, x):
+        x = _f32(x)
+        q = np.empty(x.shape, np.int8)
+        s = np.empty(x.shape[0], np.float32)
+        for r in range(x.shape[0]):
+            s[r] = self.lib.oracle_qrow_i8(_p(x[r]), _p(q[r]), C.c_int(x.shape[1]))
+        return q, s
+
+    def quant_g32(self, x):
+        x = _f32(x)
+        I = x.shape[-1]
+        rows = x.reshape(-1, I)
+        xq = np.empty(rows.shape, np.int8)
+        xs = np.empty((rows.shape[0], I // 32), np.float32)
+        xsum = np.empty((rows.shape[0], I // 32), np.int32)
+        for r in range(rows.shape[0]):
+            self.lib.oracle_quant_g32(_p(rows[r]), C.c_int(I), _p(xq[r]), _p(xs[r]), _p(xsum[r]))
+        return xq, xs, xsum
+
+    # -- dots and drivers ----------------------------------------------
+    def dot_i8i8(self, w, x):
+        w = np.ascontiguousarray(w, np.int8); x = np.ascontiguousarray(x, np.int8)
+        return int(self.lib.oracle_dot_i8i8(_p(w), _p(x), C.c_int(w.size)))
+
+    def dot_i4i8(self, w4, x):
+        w4 = np.ascontiguousarray(w4, np.uint8); x = np.ascontiguousarray(x, np.int8)
+        return int(self.lib.oracle_dot_i4i8(_p(w4), _p(x), C.c_int(x.size)))
+
+    def matmul_q_s(self, x, q, scale, want_acc=False):
+        x = _f32(x); q = np.ascontiguousarray(q, np.int8); scale = _f32(scale)
+        S, I = x.shape; O = q.shape[0]
+        y = np.empty((S, O), np.float32)
+        acc = np.empty((S, O), np.int32) if want_acc else None
+        self.lib.oracle_matmul_q_s(_p(y), _p(x), _p(q), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O),
+                                   _p(acc), None, None)
+        return (y, acc) if want_acc else y
+
+    def matmul_i4_idot_s(self, x, q4, scale, I):
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); scale = _f32(scale)
+        S = x.shape[0]; O = scale.size
+        y = np.empty((S, O), np.float32)
+        self.lib.oracle_matmul_i4_idot_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
+    def matmul_q4r4_s(self, x, q4, s16, O):
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); s16 = np.ascontiguousarray(s16, np.uint16)
+        S, I = x.shape
+        y = np.empty((S, O), np.float32)
+        self.lib.oracle_matmul_q4r4_s(_p(y), _p(x), _p(q4), _p(s16), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
+    def q4r4_gemm(self, w, d, xq, xs, xsum, nb, ns):
+        """One 4-row block; returns (y [ns][4], int32 group sums [ns][4][nb])."""
+        y = np.empty((ns, 4), np.float32)
+        isum = np.empty((ns, 4, nb), np.int32)
+        self.lib.oracle_q4r4_gemm(_p(np.ascontiguousarray(w)), _p(np.ascontiguousarray(d)), _p(np.ascontiguousarray(xq)),
+                                  _p(np.ascontiguousarray(xs)), _p(np.ascontiguousarray(xsum)),
+                                  C.c_int(nb), C.c_int(ns), _p(y), C.c_int(4), _p(isum))
+        return y, isum
+
+    # -- load-time quantizers ------------------------------------------
+    def quantize_rows(self, w, bits=8):
+        w = _f32(w); O, I = w.shape
+        q = np.empty((O, I), np.int8); s = np.empty(O, np.float32)
+        self.lib.oracle_quantize_rows(_p(w), _p(q), _p(s), C.c_int(O), C.c_int(I), C.c_int(bits))
+        return q, s
+
+    def pack_int4(self, w):
+        w = _f32(w); O, I = w.shape
+        q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty(O, np.float32)
+        self.lib.oracle_pack_int4(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I))
+        return q4, s
+
+    def pack_q4r4(self, w):
+        w = _f32(w); O, I = w.shape
+        nblk, nb = (O + 3) // 4, I // 32
+        q4 = np.empty(nblk * nb * 64, np.uint8); s16 = np.empty(nblk * nb * 4, np.uint16)
+        self.lib.oracle_pack_q4r4(_p(w), C.c_int(O), C.c_int(I), _p(q4), _p(s16))
+        return q4, s16
+
+    # -- router ---------------------------------------------------------
+    def softmax(self, x):
+        x = _f32(x).copy()
+        rows = x.reshape(-1, x.shape[-1])
+        for r in range(rows.shape[0]):
+            self.lib.oracle_softmax(_p(rows[r]), C.c_int(rows.shape[1]))
+        return x
+
+    def moe_topk(self, p, K, norm):
+        p = _f32(p); rows = p.reshape(-1, p.shape[-1])
+        idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+        for r in range(rows.shape[0]):
+            self.lib.oracle_moe_topk(_p(rows[r]), C.c_int(rows.shape[1]), C.c_int(K), _p(idx[r]), _p(w[r]), C.c_int(norm))
+        return idx, w
+
+    def route_topk(self, logits, K):
+        lg = _f32(logits).copy(); rows = lg.reshape(-1, lg.shape[-1])
+        idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+        for r in range(rows.shape[0]):
+            self.lib.oracle_route_topk(_p(rows[r]), C.c_int(rows.shape[1]), C.c_int(K), _p(idx[r]), _p(w[r]))
+        return idx, w, lg
+
+    def argmax(self, v):
+        v = _f32(v)
+        return int(self.lib.oracle_argmax(_p(v), C.c_int(v.size)))
+
+    # -- blocks ---------------------------------------------------------
+    def silu_mul(self, g, u):
+        g = _f32(g).copy(); u = _f32(u)
+        self.lib.oracle_silu_mul(_p(g), _p(u), C.c_int64(g.size))
+        return g
+
+    def gelu_mul(self, g, u):
+        g = _f32(g).copy(); u = _f32(u)
+        self.lib.oracle_gelu_mul(_p(g), _p(u), C.c_int64(g.size))
+        return g
+
+    def ffn_q8(self, x, gq, gs, uq, us, dq, ds, act=0, want_h=False):
+        x = _f32(x); S, D = x.shape; I = gq.shape[0]
+        out = np.empty((S, D), np.float32)
+        h = np.empty((S, I), np.float32) if want_h else None
+        self.lib.oracle_ffn_q8(_p(out), _p(x), C.c_int(S), C.c_int(D), C.c_int(I), C.c_int(act),
+                               _p(gq), _p(_f32(gs)), _p(uq), _p(_f32(us)), _p(dq), _p(_f32(ds)), _p(h))
+        return (out, h) if want_h else out
+
+    def ffn_q4r4(self, x, I, gq, gs, uq, us, dq, ds, act=0):
+        x = _f32(x); S, D = x.shape
+        out = np.empty((S, D), np.float32)
+        self.lib.oracle_ffn_q4r4(_p(out), _p(x), C.c_int(S), C.c_int(D), C.c_int(I), C.c_int(act),
+                                 _p(gq), _p(gs), _p(uq), _p(us), _p(dq), _p(ds))
+        return out
+
+    def _moe(self, fn, ex, x, logits, *extra):
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        fn(C.byref(ex.c), _p(x), *extra[:1], _p(lg), _p(out), *extra[1:], _p(idx), _p(w))
+        return out, idx, w
+
+    def moe_d1(self, ex, x, logits):
+        x = _f32(x).reshape(1, ex.D); lg = _f32(logits).reshape(1, ex.E).copy()
+        out = np.empty((1, ex.D), np.float32)
+        idx = np.empty((1, ex.K), np.int32); w = np.empty((1, ex.K), np.float32)
+        self.lib.oracle_moe_d1(C.byref(ex.c), _p(x), _p(lg), _p(out), _p(idx), _p(w))
+        return out, idx, w
+
+    def moe_batch(self, ex, x, logits):
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        self.lib.oracle_moe_batch(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(out), _p(idx), _p(w))
+        return out, idx, w
+
+    def olmoe_moe(self, ex, x, logits, norm_topk):
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        self.lib.oracle_olmoe_moe(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(out), C.c_int(norm_topk), _p(idx), _p(w))
+        return out, idx, w
+
+    def moe_q4r4(self, ex, x, logits):
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        self.lib.oracle_moe_q4r4(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(out), _p(idx), _p(w))
+        return out, idx, w
+
+
+class Ref:
+    """The unmodified reference, compiled by oracle/Makefile.  ``Ref.available()``
+    is False where neither the sources nor a prebuilt library exist."""
+
+    @staticmethod
+    def path():
+        d = os.path.join(HERE, "_ref")
+        native = os.path.join(d, "libmoty_ref_native.so")
+        v3 = os.path.join(d, "libmoty_ref_v3.so")
+        need = os.path.join(d, "native_needs_avx512vnni")
+        if os.path.exists(native):
+            needs512 = os.path.exists(need) and open(need).read().strip() not in ("", "0")
+            if not needs512 or (_cpu_has("avx512_vnni") and _cpu_has("avx512bw")):
+                return native
+        return v3 if os.path.exists(v3) else None
+
+    @staticmethod
+    def available():
+        return Ref.path() is not None
+
+    def __init__(self, threads: int | None = None):
+        p = Ref.path()
+        if p is None:
+            raise RuntimeError("reference library not built (oracle/_ref is empty)")
+        self.tier = "native" if p.endswith("native.so") else "x86-64-v3"
+        os.environ.setdefault("MOTY_NO_OMP_TUNE", "1")
+        self.lib = C.CDLL(p)
+        L = self.lib
+        L.moty_hw_qrow_i8.restype = C.c_float
+        L.moty_hw_dot_i8i8.restype = C.c_int32
+        L.moty_hw_dot_i4i8.restype = C.c_int32
+        L.moty_hw_f16_to_f32.restype = C.c_float
+        L.moty_hw_f16_to_f32.argtypes = [C.c_uint16]
+        L.moty_f32_to_f16.restype = C.c_uint16
+        L.moty_f32_to_f16.argtypes = [C.c_float]
+        L.moty_argmax_v.restype = C.c_int
+        L.refshim_threads.restype = C.c_int
+        if threads:
+            L.refshim_set_threads(C.c_int(threads))
+
+    def threads(self):
+        return int(self.lib.refshim_threads())
+
+    def set_threads(self, n):
+        self.lib.refshim_set_threads(C.c_int(n))
+
+    def f16_to_f32(self, h):
+        return self.lib.moty_hw_f16_to_f32(int(h))
+
+    def f32_to_f16(self, f):
+        return self.lib.moty_f32_to_f16(float(np.float32(f)))
+
+    def qrow_i8(self, x):
+        x = _f32(x); q = np.empty(x.shape, np.int8)
+        s = self.lib.moty_hw_qrow_i8(_p(x), _p(q), C.c_int(x.size))
+        return q, np.float32(s)
+
+    def quant_g32(self, x):
+        x = _f32(x); I = x.shape[-1]; rows = x.reshape(-1, I)
+        xq = np.empty(rows.shape, np.int8)
+        xs = np.empty((rows.shape[0], I // 32), np.float32); xsum = np.empty((rows.shape[0], I // 32), np.int32)
+        for r in range(rows.shape[0]):
+            self.lib.moty_hw_quant_g32(_p(rows[r]), C.c_int(I), _p(xq[r]), _p(xs[r]), _p(xsum[r]))
+        return xq, xs, xsum
+
+    def dot_i8i8(self, w, x):
+        w = np.ascontiguousarray(w, np.int8); x = np.ascontiguousarray(x, np.int8)
+        return int(self.lib.moty_hw_dot_i8i8(_p(w), _p(x), C.c_int(w.size)))
+
+    def dot_i4i8(self, w4, x):
+        w4 = np.ascontiguousarray(w4, np.uint8); x = np.ascontiguousarray(x, np.int8)
+        return int(self.lib.moty_hw_dot_i4i8(_p(w4), _p(x), C.c_int(x.size)))
+
+    def matmul_q_s(self, x, q, scale):
+        x = _f32(x); q = np.ascontiguousarray(q, np.int8); scale = _f32(scale)
+        S, I = x.shape; O = q.shape[0]
+        y = np.empty((S, O), np.float32)
+        self.lib.moty_matmul_q_s(_p(y), _p(x), _p(q), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
+    def matmul_q4r4_s(self, x, q4, s16, O):
+        x = _f32(x); S, I = x.shape
+        y = np.empty((S, O), np.float32)
+        self.lib.moty_matmul_q4r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q4, np.uint8)),
+                                    _p(np.ascontiguousarray(s16, np.uint16)), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
+    def quantize_rows(self, w, bits=8):
+        w = _f32(w); O, I = w.shape
+        q = np.empty((O, I), np.int8); s = np.empty(O, np.float32)
+        self.lib.moty_quantize_rows(_p(w), _p(q), _p(s), C.c_int(O), C.c_int(I), C.c_int(bits))
+        return q, s
+
+    def pack_int4(self, w):
+        w = _f32(w); O, I = w.shape
+        q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty(O, np.float32)
+        self.lib.moty_pack_int4(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I))
+        return q4, s
+
+    def pack_q4r4(self, w):
+        w = _f32(w); O, I = w.shape
+        nblk, nb = (O + 3) // 4, I // 32
+        q4 = np.empty(nblk * nb * 64, np.uint8); s16 = np.empty(nblk * nb * 4, np.uint16)
+        self.lib.refshim_pack_q4r4(_p(w), C.c_int(O), C.c_int(I), _p(q4), _p(s16))
+        return q4, s16
+
+    def softmax(self, x):
+        x = _f32(x).copy(); rows = x.reshape(-1, x.shape[-1])
+        for r in range(rows.shape[0]):
+            self.lib.moty_softmax_row(_p(rows[r]), C.c_int(rows.shape[1]))
+        return x
+
+    def moe_topk(self, p, K, norm):
+        p = _f32(p); rows = p.reshape(-1, p.shape[-1])
+        idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+        for r in range(rows.shape[0]):
+            self.lib.moty_moe_topk(_p(rows[r]), C.c_int(rows.shape[1]), C.c_int(K), _p(idx[r]), _p(w[r]), C.c_int(norm))
+        return idx, w
+
+    def route_topk(self, logits, K):
+        lg = _f32(logits).copy(); rows = lg.reshape(-1, lg.shape[-1])
+        idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+        for r in range(rows.shape[0]):
+            self.lib.refshim_route_topk(_p(rows[r]), C.c_int(rows.shape[1]), C.c_int(K), _p(idx[r]), _p(w[r]))
+        return idx, w, lg
+
+    def argmax(self, v):
+        v = _f32(v)
+        return int(self.lib.moty_argmax_v(_p(v), C.c_int(v.size)))
+
+    def silu_mul(self, g, u):
+        g = _f32(g).copy(); u = _f32(u)
+        self.lib.moty_hw_silu_mul(_p(g), _p(u), C.c_int64(g.size))
+        return g
+
+    def moe_topk_block(self, ex, x, router_f=None, router_q=None, router_qs=None):
+        """nn/moe.c block (S=1: decode path, S>1: batch path); router f32 or int8."""
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        out = np.empty((S, ex.D), np.float32)
+        fmt = WF_F32 if router_f is not None else WF_I8
+        self.lib.refshim_moe_topk(C.byref(ex.c), C.c_int(fmt), _p(_f32(router_f)) if router_f is not None else None,
+                                  _p(router_q) if router_q is not None else None,
+                                  _p(_f32(router_qs)) if router_qs is not None else None,
+                                  _p(x), C.c_int(S), _p(out))
+        return out
+
+    def olmoe_moe(self, ex, x, logits, norm_topk):
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        self.lib.refshim_olmoe_moe(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(out), C.c_int(norm_topk), _p(idx), _p(w))
+        return out, idx, w
+
+    def dense_ffn(self, fmt, x, I, gq, gs, uq, us, dq, ds):
+        x = _f32(x); S, D = x.shape
+        out = np.empty((S, D), np.float32)
+        self.lib.refshim_dense_ffn(C.c_int(fmt), _p(gq), _p(gs), _p(uq), _p(us), _p(dq), _p(ds),
+                                   C.c_int(D), C.c_int(I), _p(x), C.c_int(S), _p(out))
+        return out

@@ -1,0 +1,632 @@
+/* moty_oracle.c -- CPU restatement of moty's quantized-matmul hot path.
+ *
+ * TEST INFRASTRUCTURE ONLY.  This file is the checker the CUDA library is
+ * compared against; it is never linked into, imported by or called from the
+ * shipped library.  Only the test-suite, the smoke check and the benchmark's
+ * CPU-baseline leg may load it.
+ *
+ * Every function restates, in plain scalar C, what the named reference
+ * function computes (file:line refer to the moty source tree, directory c/).
+ * The restatement is pinned two ways: against the committed golden vectors
+ * (tests/golden, produced by the reference's own compiled code) and, where the
+ * reference build is present, bit-for-bit against that build.
+ *
+ * Floating-point contract: the reference is built by gcc in GNU mode for a
+ * machine with FMA, so `acc += a * b` in its sources is one fused
+ * multiply-add.  This file is compiled with -ffp-contract=off and spells every
+ * such step as fmaf(), so its results do not depend on compiler flags.
+ */
+#include <math.h>
+#include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
+
+#define ORACLE_API __attribute__((visibility("default")))
+
+/* ------------------------------------------------------------------ */
+/* f16 <-> f32                                                          */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_q4r4.h:22-33 -- IEEE half to float, subnormals normalised. */
+ORACLE_API float oracle_f16_to_f32(uint16_t h) {
+    uint32_t sign = ((uint32_t)h >> 15) << 31;
+    int exp = (h >> 10) & 31;
+    uint32_t man = h & 1023u;
+    uint32_t bits;
+    if (exp == 31) {
+        bits = sign | 0x7f800000u | (man << 13);
+    } else if (exp != 0) {
+        bits = sign | ((uint32_t)(exp + 112) << 23) | (man << 13);
+    } else if (man == 0) {
+        bits = sign;
+    } else {
+        int e = 113;                         /* value = man * 2^-24 */
+        while (!(man & 1024u)) { man <<= 1; e--; }
+        bits = sign | ((uint32_t)e << 23) | ((man & 1023u) << 13);
+    }
+    float f; memcpy(&f, &bits, 4); return f;
+}
+
+/* nn/quant.c:110-126 -- float to IEEE half, round to nearest even. */
+ORACLE_API uint16_t oracle_f32_to_f16(float f) {
+    uint32_t u; memcpy(&u, &f, 4);
+    uint16_t sign = (uint16_t)((u >> 16) & 0x8000u);
+    uint32_t e8 = (u >> 23) & 255u, man = u & 0x7fffffu;
+    if (e8 == 255u) return (uint16_t)(sign | 0x7c00u | (man ? 0x200u : 0u));
+    int e = (int)e8 - 112;                   /* re-biased half exponent */
+    if (e >= 31) return (uint16_t)(sign | 0x7c00u);
+    if (e <= 0) {
+        if (e < -10) return sign;
+        uint32_t full = man | 0x800000u;
+        int drop = 14 - e;
+        uint32_t q = full >> drop, rest = full & ((1u << drop) - 1u), mid = 1u << (drop - 1);
+        if (rest > mid || (rest == mid && (q & 1u))) q++;
+        return (uint16_t)(sign | q);
+    }
+    uint32_t q = ((uint32_t)e << 10) | (man >> 13), rest = man & 0x1fffu;
+    if (rest > 0x1000u || (rest == 0x1000u && (q & 1u))) q++;
+    return (uint16_t)(sign | q);
+}
+
+/* ------------------------------------------------------------------ */
+/* activation quantizers                                               */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_quant.h:9-16 -- per-row symmetric int8; returns the scale.
+ * No clamp: |q| <= 127 follows from s >= amax/127. */
+ORACLE_API float oracle_qrow_i8(const float *x, int8_t *q, int n) {
+    float amax = 0.f;
+    for (int i = 0; i < n; i++) { float a = fabsf(x[i]); if (a > amax) amax = a; }
+    float s = amax / 127.f;
+    if (s < 1e-12f) s = 1e-12f;
+    float inv = 1.f / s;
+    for (int i = 0; i < n; i++) q[i] = (int8_t)lrintf(x[i] * inv);
+    return s;
+}
+
+/* hw/hw_q4r4.h:36-45 -- per group of 32: int8 codes, f32 scale, int32 code sum. */
+ORACLE_API void oracle_quant_g32(const float *x, int I, int8_t *xq, float *xs, int32_t *xsum) {
+    for (int g = 0; g < I / 32; g++) {
+        const float *p = x + 32 * g;
+        float amax = 0.f;
+        for (int j = 0; j < 32; j++) { float a = fabsf(p[j]); if (a > amax) amax = a; }
+        float s = amax / 127.f;
+        if (s < 1e-30f) s = 1e-30f;
+        float inv = 1.f / s;
+        int32_t total = 0;
+        for (int j = 0; j < 32; j++) {
+            int v = (int)lrintf(p[j] * inv);
+            xq[32 * g + j] = (int8_t)v;
+            total += v;
+        }
+        xs[g] = s; xsum[g] = total;
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* integer dots                                                        */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_scalar.h:8-12 -- the contract every SIMD tier must match exactly. */
+ORACLE_API int32_t oracle_dot_i8i8(const int8_t *w, const int8_t *x, int n) {
+    int32_t acc = 0;
+    for (int i = 0; i < n; i++) acc += (int32_t)w[i] * (int32_t)x[i];
+    return acc;
+}
+
+/* hw/hw_scalar.h:14-22 -- per-row int4: element 2k in the low nibble, 2k+1 in
+ * the high nibble, stored code = value + 8. */
+ORACLE_API int32_t oracle_dot_i4i8(const uint8_t *w4, const int8_t *x, int n) {
+    int32_t acc = 0;
+    for (int i = 0; i < n; i++) {
+        int nib = (i & 1) ? (w4[i >> 1] >> 4) : (w4[i >> 1] & 15);
+        acc += (nib - 8) * (int32_t)x[i];
+    }
+    return acc;
+}
+
+/* ------------------------------------------------------------------ */
+/* Q8_0 driver                                                         */
+/* ------------------------------------------------------------------ */
+
+/* nn/matmul.c:29-36,51-66 (IDOT=1 path): quantize each activation row, then
+ * y[s][o] = (scale[o] * sx[s]) * (float)dot.  acc32 (optional) receives the
+ * int32 accumulators [S][O]; xi_out/sx_out (optional) the quantized rows. */
+ORACLE_API void oracle_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale,
+                                  int S, int I, int O, int32_t *acc32, int8_t *xi_out, float *sx_out) {
+    int8_t *xi = xi_out ? xi_out : (int8_t *)malloc((size_t)S * I + 1);
+    float *sx = sx_out ? sx_out : (float *)malloc(sizeof(float) * (S ? S : 1));
+    for (int s = 0; s < S; s++) sx[s] = oracle_qrow_i8(x + (size_t)s * I, xi + (size_t)s * I, I);
+    #pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++) {
+        const int8_t *w = q + (size_t)o * I;
+        for (int s = 0; s < S; s++) {
+            int32_t d = oracle_dot_i8i8(w, xi + (size_t)s * I, I);
+            if (acc32) acc32[(size_t)s * O + o] = d;
+            y[(size_t)s * O + o] = scale[o] * sx[s] * (float)d;
+        }
+    }
+    if (!xi_out) free(xi);
+    if (!sx_out) free(sx);
+}
+
+/* nn/matmul.c:75-96,98-106 with IDOT4=1: per-row int4 weights, int8 activations. */
+ORACLE_API void oracle_matmul_i4_idot_s(float *y, const float *x, const uint8_t *q4, const float *scale,
+                                        int S, int I, int O) {
+    int8_t *xi = (int8_t *)malloc((size_t)S * I + 1);
+    float *sx = (float *)malloc(sizeof(float) * (S ? S : 1));
+    int rb = (I + 1) / 2;
+    for (int s = 0; s < S; s++) sx[s] = oracle_qrow_i8(x + (size_t)s * I, xi + (size_t)s * I, I);
+    #pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++)
+        for (int s = 0; s < S; s++)
+            y[(size_t)s * O + o] = scale[o] * sx[s] *
+                (float)oracle_dot_i4i8(q4 + (size_t)o * rb, xi + (size_t)s * I, I);
+    free(xi); free(sx);
+}
+
+/* ------------------------------------------------------------------ */
+/* Q4R4: 4-row blocks, groups of 32, f16 scale stream                  */
+/* ------------------------------------------------------------------ */
+
+/* Integer part shared by both kernels below: for block row r and group g,
+ * sum over j<16 of low_nibble(byte j) * x[j] + high_nibble(byte j) * x[j+16]
+ * (hw/hw_q4r4.h:56-57).  The codes are unsigned 0..15. */
+static int32_t q4r4_group_dot(const uint8_t *row16, const int8_t *xg) {
+    int32_t acc = 0;
+    for (int j = 0; j < 16; j++)
+        acc += (int32_t)(row16[j] & 15) * xg[j] + (int32_t)(row16[j] >> 4) * xg[j + 16];
+    return acc;
+}
+
+/* hw/hw_q4r4.h:47-63 -- one 4-row block against ns token rows; the offset -8
+ * is removed in the integer domain, then one fused multiply-add per group in
+ * ascending group order.  isum (optional) gets the offset-corrected int32 group
+ * sums laid out [t][r][g]. */
+ORACLE_API void oracle_q4r4_gemm(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs,
+                                 const int32_t *xsum, int nb, int ns, float *y, int ys, int32_t *isum) {
+    int I = nb * 32;
+    for (int t = 0; t < ns; t++)
+        for (int r = 0; r < 4; r++) {
+            float acc = 0.f;
+            for (int g = 0; g < nb; g++) {
+                int32_t s = q4r4_group_dot(w + (size_t)g * 64 + r * 16, xq + (size_t)t * I + g * 32)
+                            - 8 * xsum[(size_t)t * nb + g];
+                if (isum) isum[((size_t)t * 4 + r) * nb + g] = s;
+                float c = oracle_f16_to_f32(d[(size_t)g * 4 + r]) * xs[(size_t)t * nb + g];
+                acc = fmaf((float)s, c, acc);
+            }
+            y[(size_t)t * ys + r] = acc;
+        }
+}
+
+/* hw/hw_q4r4.h:86-93 -- scales of four token rows re-laid per group:
+ * xst[g*4+t] = xs[t][g], xct[g*4+t] = 8 * xsum[t][g] * xs[t][g] (left to right). */
+ORACLE_API void oracle_q4r4_tile_scales(const float *xs, const int32_t *xsum, int nb, float *xst, float *xct) {
+    for (int g = 0; g < nb; g++)
+        for (int t = 0; t < 4; t++) {
+            float s = xs[(size_t)t * nb + g];
+            xst[g * 4 + t] = s;
+            xct[g * 4 + t] = 8.f * (float)xsum[(size_t)t * nb + g] * s;
+        }
+}
+
+/* hw/hw_q4r4.h:69-84 -- the 4-token prefill tile: the raw (uncorrected) int
+ * sum is scaled first, then the offset term is subtracted in float. */
+ORACLE_API void oracle_q4r4_gemm4t(const uint8_t *w, const uint16_t *d, const int8_t *xq, int64_t ldx,
+                                   const float *xst, const float *xct, int nb, float *y, int ys) {
+    for (int t = 0; t < 4; t++)
+        for (int r = 0; r < 4; r++) {
+            float acc = 0.f;
+            for (int g = 0; g < nb; g++) {
+                int32_t s = q4r4_group_dot(w + (size_t)g * 64 + r * 16, xq + t * ldx + g * 32);
+                float dd = oracle_f16_to_f32(d[(size_t)g * 4 + r]);
+                acc = fmaf((float)s, dd * xst[g * 4 + t], acc);
+                acc = fmaf(-dd, xct[g * 4 + t], acc);
+            }
+            y[(size_t)t * ys + r] = acc;
+        }
+}
+
+/* nn/matmul.c:371-433 -- the driver: group-quantize the S rows; tokens are cut
+ * into tiles of 32; inside a tile every complete group of 4 tokens goes through
+ * the 4-token kernel and the remaining (tile size % 4) tokens through the
+ * token-by-token kernel.  Which kernel a token meets decides how the -8 offset
+ * is folded, so the split must be reproduced to match bit for bit. */
+ORACLE_API void oracle_matmul_q4r4_s(float *y, const float *x, const uint8_t *q4, const uint16_t *s16,
+                                     int S, int I, int O) {
+    int nb = I / 32, nblk = (O + 3) / 4, full = O / 4;
+    size_t SI = (size_t)S * I + 1, SN = (size_t)S * nb + 1;
+    int8_t *xq = (int8_t *)malloc(SI);
+    float *xs = (float *)malloc(SN * 4), *xst = (float *)malloc(SN * 4), *xct = (float *)malloc(SN * 4);
+    int32_t *xsum = (int32_t *)malloc(SN * 4);
+    for (int s = 0; s < S; s++)
+        oracle_quant_g32(x + (size_t)s * I, I, xq + (size_t)s * I, xs + (size_t)s * nb, xsum + (size_t)s * nb);
+    for (int k = 0; k < S / 4; k++)
+        oracle_q4r4_tile_scales(xs + (size_t)k * 4 * nb, xsum + (size_t)k * 4 * nb, nb,
+                                xst + (size_t)k * nb * 4, xct + (size_t)k * nb * 4);
+    for (int t0 = 0; t0 < S; t0 += 32) {
+        int ns = S - t0 < 32 ? S - t0 : 32, n4 = ns / 4 * 4;
+        #pragma omp parallel for schedule(dynamic, 8)
+        for (int ob = 0; ob < nblk; ob++) {
+            float tmp[4 * 32];
+            int ragged = (ob == full);
+            float *yo = ragged ? tmp : y + (size_t)t0 * O + ob * 4;
+            int ys = ragged ? 4 : O;
+            const uint8_t *wb = q4 + (size_t)ob * nb * 64;
+            const uint16_t *db = s16 + (size_t)ob * nb * 4;
+            for (int t = 0; t < n4; t += 4)
+                oracle_q4r4_gemm4t(wb, db, xq + (size_t)(t0 + t) * I, I,
+                                   xst + (size_t)((t0 + t) / 4) * nb * 4, xct + (size_t)((t0 + t) / 4) * nb * 4,
+                                   nb, yo + (size_t)t * ys, ys);
+            if (n4 < ns)
+                oracle_q4r4_gemm(wb, db, xq + (size_t)(t0 + n4) * I, xs + (size_t)(t0 + n4) * nb,
+                                 xsum + (size_t)(t0 + n4) * nb, nb, ns - n4, yo + (size_t)n4 * ys, ys, NULL);
+            if (ragged)
+                for (int t = 0; t < ns; t++)
+                    for (int r = 0; r < O - full * 4; r++)
+                        y[(size_t)(t0 + t) * O + full * 4 + r] = tmp[t * 4 + r];
+        }
+    }
+    free(xq); free(xs); free(xst); free(xct); free(xsum);
+}
+
+/* ------------------------------------------------------------------ */
+/* load-time weight quantizers                                         */
+/* ------------------------------------------------------------------ */
+
+/* nn/quant.c:12-33 -- per-row int8 (bits=8) with a true division per element. */
+ORACLE_API void oracle_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I, int bits) {
+    int qmax = (1 << (bits - 1)) - 1;
+    #pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++) {
+        const float *row = w + (size_t)o * I;
+        float amax = 0.f;
+        for (int i = 0; i < I; i++) { float a = fabsf(row[i]); if (a > amax) amax = a; }
+        float s = amax / (float)qmax;
+        if (s < 1e-8f) s = 1e-8f;
+        scale[o] = s;
+        for (int i = 0; i < I; i++) {
+            int v = (int)lrintf(row[i] / s);
+            if (v > qmax) v = qmax;
+            if (v < -qmax - 1) v = -qmax - 1;
+            q[(size_t)o * I + i] = (int8_t)v;
+        }
+    }
+}
+
+/* nn/quant.c:35-55 -- per-row int4, scale amax/7, code = clamp(round(w/s),-8,7)+8. */
+ORACLE_API void oracle_pack_int4(const float *w, uint8_t *q4, float *scale, int O, int I) {
+    int rb = (I + 1) / 2;
+    for (int o = 0; o < O; o++) {
+        const float *row = w + (size_t)o * I;
+        float amax = 0.f;
+        for (int i = 0; i < I; i++) { float a = fabsf(row[i]); if (a > amax) amax = a; }
+        float s = amax / 7.f;
+        if (s < 1e-8f) s = 1e-8f;
+        scale[o] = s;
+        for (int b = 0; b < rb; b++) {
+            int code[2] = { 8, 8 };
+            for (int h = 0; h < 2; h++) {
+                int i = 2 * b + h;
+                if (i >= I) break;
+                int v = (int)lrintf(row[i] / s);
+                if (v > 7) v = 7;
+                if (v < -8) v = -8;
+                code[h] = v + 8;
+            }
+            q4[(size_t)o * rb + b] = (uint8_t)(code[0] | (code[1] << 4));
+        }
+    }
+}
+
+/* nn/quant.c:157-179 -- one 4-row Q4R4 block.  Group scale: the largest-
+ * magnitude weight maps to code -8 unless that step would clip the largest
+ * weight of the other sign; the scale is stored signed in f16 and the codes are
+ * computed from the ROUNDED scale.  Byte j of a row = code[j] | code[j+16] << 4.
+ * Rows past nr: bytes 0x88 (code 8 = value 0), scale bits 0. */
+ORACLE_API void oracle_pack_q4r4_block(const float *w, int nr, int I, uint8_t *blk, uint16_t *d) {
+    int nb = I / 32;
+    for (int g = 0; g < nb; g++)
+        for (int r = 0; r < 4; r++) {
+            uint8_t *out = blk + (size_t)g * 64 + r * 16;
+            if (r >= nr) { memset(out, 0x88, 16); d[(size_t)g * 4 + r] = 0; continue; }
+            const float *p = w + (size_t)r * I + g * 32;
+            float big = 0.f;
+            for (int j = 0; j < 32; j++) if (fabsf(p[j]) > fabsf(big)) big = p[j];
+            float other = 0.f;
+            for (int j = 0; j < 32; j++)
+                if ((p[j] > 0) != (big > 0) && fabsf(p[j]) > other) other = fabsf(p[j]);
+            float step = fmaxf(fabsf(big) / 8.f, other / 7.f);
+            uint16_t h = oracle_f32_to_f16(big > 0 ? -step : step);
+            float dd = oracle_f16_to_f32(h);
+            float inv = dd != 0.f ? 1.f / dd : 0.f;
+            uint8_t code[32];
+            for (int j = 0; j < 32; j++) {
+                int v = (int)lrintf(p[j] * inv);
+                if (v < -8) v = -8;
+                if (v > 7) v = 7;
+                code[j] = (uint8_t)(v + 8);
+            }
+            d[(size_t)g * 4 + r] = h;
+            for (int j = 0; j < 16; j++) out[j] = (uint8_t)(code[j] | (code[j + 16] << 4));
+        }
+}
+
+/* runtime/rt_model_load.h:85-121 (r4_pack_part) -- a whole [O][I] matrix in
+ * blocks of 4 rows; the last block may hold fewer than 4 rows. */
+ORACLE_API void oracle_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16) {
+    int nb = I / 32, nblk = (O + 3) / 4;
+    #pragma omp parallel for schedule(static)
+    for (int b = 0; b < nblk; b++) {
+        int nr = O - 4 * b < 4 ? O - 4 * b : 4;
+        oracle_pack_q4r4_block(w + (size_t)b * 4 * I, nr, I, q4 + (size_t)b * nb * 64, s16 + (size_t)b * nb * 4);
+    }
+}
+
+/* ------------------------------------------------------------------ */
+/* router                                                              */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_ops.h:22-26 -- in-place softmax: max from -1e30, libm expf, sequential
+ * f32 sum, one division per element. */
+ORACLE_API void oracle_softmax(float *x, int n) {
+    float m = -1e30f;
+    for (int i = 0; i < n; i++) if (x[i] > m) m = x[i];
+    float total = 0.f;
+    for (int i = 0; i < n; i++) { x[i] = expf(x[i] - m); total += x[i]; }
+    for (int i = 0; i < n; i++) x[i] /= total;
+}
+
+/* runtime/moecache.c:97-111 -- K rounds of "largest not yet taken", strict >
+ * from a floor of -1e30 so ties resolve to the lowest index; optional
+ * renormalisation by the sequential sum of the K picked values. */
+ORACLE_API void oracle_moe_topk(const float *p, int E, int K, int *idx, float *w, int norm_topk) {
+    for (int k = 0; k < K; k++) {
+        int best = -1; float bv = -1e30f;
+        for (int e = 0; e < E; e++) {
+            int used = 0;
+            for (int j = 0; j < k; j++) if (idx[j] == e) { used = 1; break; }
+            if (!used && p[e] > bv) { bv = p[e]; best = e; }
+        }
+        idx[k] = best; w[k] = bv;
+    }
+    if (norm_topk) {
+        float total = 0.f;
+        for (int k = 0; k < K; k++) total += w[k];
+        if (total > 0) for (int k = 0; k < K; k++) w[k] /= total;
+    }
+}
+
+/* nn/moe.c:27-30 -- softmax in place, then top-K with renormalisation on. */
+ORACLE_API void oracle_route_topk(float *logits, int E, int K, int *idx, float *w) {
+    oracle_softmax(logits, E);
+    oracle_moe_topk(logits, E, K, idx, w, 1);
+}
+
+/* nn/sample.c:9-13 -- greedy token: first index of the maximum. */
+ORACLE_API int oracle_argmax(const float *v, int n) {
+    int best = 0; float bv = v[0];
+    for (int i = 1; i < n; i++) if (v[i] > bv) { bv = v[i]; best = i; }
+    return best;
+}
+
+/* ------------------------------------------------------------------ */
+/* activations and FFN / MoE blocks                                    */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_ops.h:19-21 -- g = silu(g) * u, silu(v) = v / (1 + expf(-v)). */
+ORACLE_API void oracle_silu_mul(float *g, const float *u, int64_t n) {
+    for (int64_t i = 0; i < n; i++) { float v = g[i]; g[i] = (v / (1.f + expf(-v))) * u[i]; }
+}
+
+/* engines/gemma.c:389-391,398 -- g = gelu_tanh(g) * u. */
+ORACLE_API void oracle_gelu_mul(float *g, const float *u, int64_t n) {
+    for (int64_t i = 0; i < n; i++) {
+        float v = g[i];
+        float t = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        g[i] = t * u[i];
+    }
+}
+
+/* nn/ffn.c:26-55, engines/qwen.c:654-679, engines/gemma.c:392-401 with Q8_0
+ * matrices: gate and up GEMV/GEMM, activation * up, down GEMV/GEMM.
+ * act: 0 = SiLU (qwen), 1 = tanh-GeLU (gemma).  h_out (optional) gets the
+ * [S][I] activation fed to the down projection. */
+ORACLE_API void oracle_ffn_q8(float *out, const float *x, int S, int D, int I, int act,
+                              const int8_t *gq, const float *gs, const int8_t *uq, const float *us,
+                              const int8_t *dq, const float *ds, float *h_out) {
+    size_t n = (size_t)S * I + 1;
+    float *g = h_out ? h_out : (float *)malloc(n * 4), *u = (float *)malloc(n * 4);
+    oracle_matmul_q_s(g, x, gq, gs, S, D, I, NULL, NULL, NULL);
+    oracle_matmul_q_s(u, x, uq, us, S, D, I, NULL, NULL, NULL);
+    if (act == 0) oracle_silu_mul(g, u, (int64_t)S * I); else oracle_gelu_mul(g, u, (int64_t)S * I);
+    oracle_matmul_q_s(out, g, dq, ds, S, I, D, NULL, NULL, NULL);
+    if (!h_out) free(g);
+    free(u);
+}
+
+/* Same block with Q4R4 matrices (what QBITS=4 Q4FMT=r4 loads). */
+ORACLE_API void oracle_ffn_q4r4(float *out, const float *x, int S, int D, int I, int act,
+                                const uint8_t *gq, const uint16_t *gs, const uint8_t *uq, const uint16_t *us,
+                                const uint8_t *dq, const uint16_t *ds) {
+    size_t n = (size_t)S * I + 1;
+    float *g = (float *)malloc(n * 4), *u = (float *)malloc(n * 4);
+    oracle_matmul_q4r4_s(g, x, gq, gs, S, D, I);
+    oracle_matmul_q4r4_s(u, x, uq, us, S, D, I);
+    if (act == 0) oracle_silu_mul(g, u, (int64_t)S * I); else oracle_gelu_mul(g, u, (int64_t)S * I);
+    oracle_matmul_q4r4_s(out, g, dq, ds, S, I, D);
+    free(g); free(u);
+}
+
+/* Experts of one MoE layer, all resident, per-row int8 (the layout of
+ * runtime/moe.h:35-39 ExpertSlot, one slot per expert id):
+ *   g,u: [E][I][D] int8, gs,us: [E][I] f32;  d: [E][D][I] int8, ds: [E][D] f32. */
+typedef struct {
+    int E, K, I, D;
+    const int8_t *g, *u, *d;
+    const float *gs, *us, *ds;
+} OracleExperts;
+
+/* nn/moe.c:33-153 (softmax/top-k variant, int8 experts, no shared expert),
+ * given the router logits of the one token: route, quantize x once, all gate
+ * and up rows, SiLU*up then per-expert re-quantization, all down rows, and the
+ * weighted sum accumulated in selection order k = 0..K-1 (one fused
+ * multiply-add per element).  idx_out/w_out (optional) return the routing. */
+ORACLE_API void oracle_moe_d1(const OracleExperts *ex, const float *x, float *logits, float *out,
+                              int *idx_out, float *w_out) {
+    int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
+    int idx[64]; float w[64];
+    oracle_route_topk(logits, E, K, idx, w);
+    int8_t *xi = (int8_t *)malloc(D), *hi = (int8_t *)malloc(I);
+    float *gb = (float *)malloc((size_t)I * 4), *ub = (float *)malloc((size_t)I * 4), *hb = (float *)malloc((size_t)D * 4);
+    float sx = oracle_qrow_i8(x, xi, D);
+    memset(out, 0, (size_t)D * 4);
+    /* the reference computes all experts' rows first and sums afterwards; the
+     * per-expert values and the k-ordered accumulation are what matter */
+    float *hall = (float *)malloc((size_t)K * D * 4);
+    for (int k = 0; k < K; k++) {
+        size_t e = (size_t)idx[k];
+        #pragma omp parallel for schedule(static)
+        for (int i = 0; i < I; i++) {
+            gb[i] = ex->gs[e * I + i] * sx * (float)oracle_dot_i8i8(ex->g + (e * I + i) * D, xi, D);
+            ub[i] = ex->us[e * I + i] * sx * (float)oracle_dot_i8i8(ex->u + (e * I + i) * D, xi, D);
+        }
+        oracle_silu_mul(gb, ub, I);
+        float sh = oracle_qrow_i8(gb, hi, I);
+        #pragma omp parallel for schedule(static)
+        for (int dd = 0; dd < D; dd++)
+            hall[(size_t)k * D + dd] = ex->ds[e * D + dd] * sh * (float)oracle_dot_i8i8(ex->d + (e * D + dd) * I, hi, I);
+    }
+    for (int k = 0; k < K; k++)
+        for (int dd = 0; dd < D; dd++) out[dd] = fmaf(w[k], hall[(size_t)k * D + dd], out[dd]);
+    if (idx_out) memcpy(idx_out, idx, sizeof(int) * K);
+    if (w_out) memcpy(w_out, w, sizeof(float) * K);
+    (void)hb;
+    free(xi); free(hi); free(gb); free(ub); free(hb); free(hall);
+}
+
+/* nn/moe.c:159-205 (softmax/top-k, int8 experts, no shared expert), given the
+ * router logits [S][E]: per-token routing, then experts in ascending id; each
+ * expert gathers its tokens in ascending token order, runs the three Q8_0
+ * matmuls on the gathered rows and scatter-adds weight * h.  A token's output
+ * is therefore accumulated in ascending EXPERT order, unlike the S=1 path. */
+ORACLE_API void oracle_moe_batch(const OracleExperts *ex, const float *x, int S, float *logits, float *out,
+                                 int *idx_out, float *w_out) {
+    int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
+    int *idx = (int *)malloc(sizeof(int) * (size_t)S * K);
+    float *rw = (float *)malloc(sizeof(float) * (size_t)S * K);
+    for (int s = 0; s < S; s++) oracle_route_topk(logits + (size_t)s * E, E, K, idx + (size_t)s * K, rw + (size_t)s * K);
+    memset(out, 0, (size_t)S * D * 4);
+    int *tl = (int *)malloc(sizeof(int) * (S ? S : 1));
+    float *xsub = (float *)malloc((size_t)S * D * 4 + 4), *g = (float *)malloc((size_t)S * I * 4 + 4);
+    float *u = (float *)malloc((size_t)S * I * 4 + 4), *h = (float *)malloc((size_t)S * D * 4 + 4);
+    for (int e = 0; e < E; e++) {
+        int nt = 0;
+        for (int s = 0; s < S; s++)
+            for (int k = 0; k < K; k++) if (idx[(size_t)s * K + k] == e) { tl[nt++] = s; break; }
+        if (!nt) continue;
+        for (int t = 0; t < nt; t++) memcpy(xsub + (size_t)t * D, x + (size_t)tl[t] * D, (size_t)D * 4);
+        oracle_matmul_q_s(g, xsub, ex->g + (size_t)e * I * D, ex->gs + (size_t)e * I, nt, D, I, NULL, NULL, NULL);
+        oracle_matmul_q_s(u, xsub, ex->u + (size_t)e * I * D, ex->us + (size_t)e * I, nt, D, I, NULL, NULL, NULL);
+        oracle_silu_mul(g, u, (int64_t)nt * I);
+        oracle_matmul_q_s(h, g, ex->d + (size_t)e * D * I, ex->ds + (size_t)e * D, nt, I, D, NULL, NULL, NULL);
+        for (int t = 0; t < nt; t++)
+            for (int k = 0; k < K; k++)
+                if (idx[(size_t)tl[t] * K + k] == e) {
+                    float wk = rw[(size_t)tl[t] * K + k];
+                    float *o = out + (size_t)tl[t] * D;
+                    for (int dd = 0; dd < D; dd++) o[dd] = fmaf(wk, h[(size_t)t * D + dd], o[dd]);
+                }
+    }
+    if (idx_out) memcpy(idx_out, idx, sizeof(int) * (size_t)S * K);
+    if (w_out) memcpy(w_out, rw, sizeof(float) * (size_t)S * K);
+    free(idx); free(rw); free(tl); free(xsub); free(g); free(u); free(h);
+}
+
+/* engines/olmoe.c:219-244 -- OLMoE's own block: for every token, softmax +
+ * top-K (renormalisation per config), then for each selected expert in
+ * selection order three S=1 Q8_0 GEMVs and out += weight * h. */
+ORACLE_API void oracle_olmoe_moe(const OracleExperts *ex, const float *x, int S, float *logits, float *out,
+                                 int norm_topk, int *idx_out, float *w_out) {
+    int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
+    float *g = (float *)malloc((size_t)I * 4), *u = (float *)malloc((size_t)I * 4), *h = (float *)malloc((size_t)D * 4);
+    memset(out, 0, (size_t)S * D * 4);
+    for (int s = 0; s < S; s++) {
+        int idx[64]; float w[64];
+        float *p = logits + (size_t)s * E;
+        oracle_softmax(p, E);
+        oracle_moe_topk(p, E, K, idx, w, norm_topk);
+        const float *xs = x + (size_t)s * D;
+        for (int k = 0; k < K; k++) {
+            size_t e = (size_t)idx[k];
+            oracle_matmul_q_s(g, xs, ex->g + e * I * D, ex->gs + e * I, 1, D, I, NULL, NULL, NULL);
+            oracle_matmul_q_s(u, xs, ex->u + e * I * D, ex->us + e * I, 1, D, I, NULL, NULL, NULL);
+            oracle_silu_mul(g, u, I);
+            oracle_matmul_q_s(h, g, ex->d + e * D * I, ex->ds + e * D, 1, I, D, NULL, NULL, NULL);
+            float *o = out + (size_t)s * D;
+            for (int dd = 0; dd < D; dd++) o[dd] = fmaf(w[k], h[dd], o[dd]);
+        }
+        if (idx_out) memcpy(idx_out + (size_t)s * K, idx, sizeof(int) * K);
+        if (w_out) memcpy(w_out + (size_t)s * K, w, sizeof(float) * K);
+    }
+    free(g); free(u); free(h);
+}
+
+/* Q4R4 experts (no reference engine stores experts this way; this is the
+ * composition of reference functions the Qwen3-30B-A3B-shaped configuration
+ * is checked against): routing as nn/moe.c:27-30, each expert's three
+ * projections through the Q4R4 driver (nn/matmul.c:371-433) on its gathered
+ * rows, accumulation order as nn/moe.c:200-202 (S>1) or :146-149 (S=1).
+ *   g,u: [E] Q4R4 matrices of O=I rows, width D;  d: [E] Q4R4 of O=D, width I. */
+typedef struct {
+    int E, K, I, D;
+    const uint8_t *g, *u, *d;        /* codes, expert-major */
+    const uint16_t *gs, *us, *ds;    /* f16 scale streams, expert-major */
+} OracleExpertsQ4;
+
+ORACLE_API void oracle_moe_q4r4(const OracleExpertsQ4 *ex, const float *x, int S, float *logits, float *out,
+                                int *idx_out, float *w_out) {
+    int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
+    size_t gq = (size_t)((I + 3) / 4) * (D / 32) * 64, gsn = (size_t)((I + 3) / 4) * (D / 32) * 4;
+    size_t dq = (size_t)((D + 3) / 4) * (I / 32) * 64, dsn = (size_t)((D + 3) / 4) * (I / 32) * 4;
+    int *idx = (int *)malloc(sizeof(int) * (size_t)S * K);
+    float *rw = (float *)malloc(sizeof(float) * (size_t)S * K);
+    for (int s = 0; s < S; s++) oracle_route_topk(logits + (size_t)s * E, E, K, idx + (size_t)s * K, rw + (size_t)s * K);
+    memset(out, 0, (size_t)S * D * 4);
+    float *xsub = (float *)malloc((size_t)S * D * 4 + 4), *g = (float *)malloc((size_t)S * I * 4 + 4);
+    float *u = (float *)malloc((size_t)S * I * 4 + 4), *h = (float *)malloc((size_t)S * D * 4 + 4);
+    int *tl = (int *)malloc(sizeof(int) * (S ? S : 1));
+    if (S == 1) {
+        for (int k = 0; k < K; k++) {
+            size_t e = (size_t)idx[k];
+            oracle_matmul_q4r4_s(g, x, ex->g + e * gq, ex->gs + e * gsn, 1, D, I);
+            oracle_matmul_q4r4_s(u, x, ex->u + e * gq, ex->us + e * gsn, 1, D, I);
+            oracle_silu_mul(g, u, I);
+            oracle_matmul_q4r4_s(h, g, ex->d + e * dq, ex->ds + e * dsn, 1, I, D);
+            for (int dd = 0; dd < D; dd++) out[dd] = fmaf(rw[k], h[dd], out[dd]);
+        }
+    } else {
+        for (int e = 0; e < E; e++) {
+            int nt = 0;
+            for (int s = 0; s < S; s++)
+                for (int k = 0; k < K; k++) if (idx[(size_t)s * K + k] == e) { tl[nt++] = s; break; }
+            if (!nt) continue;
+            for (int t = 0; t < nt; t++) memcpy(xsub + (size_t)t * D, x + (size_t)tl[t] * D, (size_t)D * 4);
+            oracle_matmul_q4r4_s(g, xsub, ex->g + (size_t)e * gq, ex->gs + (size_t)e * gsn, nt, D, I);
+            oracle_matmul_q4r4_s(u, xsub, ex->u + (size_t)e * gq, ex->us + (size_t)e * gsn, nt, D, I);
+            oracle_silu_mul(g, u, (int64_t)nt * I);
+            oracle_matmul_q4r4_s(h, g, ex->d + (size_t)e * dq, ex->ds + (size_t)e * dsn, nt, I, D);
+            for (int t = 0; t < nt; t++)
+                for (int k = 0; k < K; k++)
+                    if (idx[(size_t)tl[t] * K + k] == e) {
+                        float wk = rw[(size_t)tl[t] * K + k];
+                        float *o = out + (size_t)tl[t] * D;
+                        for (int dd = 0; dd < D; dd++) o[dd] = fmaf(wk, h[(size_t)t * D + dd], o[dd]);
+                    }
+        }
+    }
+    if (idx_out) memcpy(idx_out, idx, sizeof(int) * (size_t)S * K);
+    if (w_out) memcpy(w_out, rw, sizeof(float) * (size_t)S * K);
+    free(idx); free(rw); free(tl); free(xsub); free(g); free(u); free(h);
+}
