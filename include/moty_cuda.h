@@ -1,0 +1,192 @@
+/* moty_cuda.h -- C ABI of the B200 (sm_100a) backend for moty's quantized-matmul path.
+ *
+ * One shared library, libmoty_cuda.so.  Plain C types only: pointers, ints,
+ * opaque handles.  Every function returns 0 on success and a negative
+ * MOTY_CUDA_E* code on failure (moty_cuda_last_error() holds the message); the
+ * library never falls back to the CPU and never longjmps.  Calls are serial per
+ * process, like the reference drivers they replace (those keep function-level
+ * static scratch: nn/matmul.c:55-58, 370).
+ *
+ * Naming follows the call sites of moty's absent CUDA backend
+ * (engines/glm.c:244, 797-809, 5709: moty_cuda_init / _tensor_upload / _matmul).
+ * "Replaces" below names the reference function (moty source tree, directory
+ * c/) whose results each entry reproduces.
+ *
+ * Pointer suffix convention: plain entries take HOST pointers for activations
+ * and results (they copy in and out on the library's stream and return after
+ * the result is in host memory); *_dev entries take DEVICE pointers, enqueue on
+ * `stream` (a cudaStream_t passed as void*, NULL = the library's own stream) and
+ * return without synchronising.
+ */
+#ifndef MOTY_CUDA_H
+#define MOTY_CUDA_H
+#include <stdint.h>
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* weight formats: the values of the WF_* enum in hw/hw.h:53 */
+enum { MOTY_WF_F32 = 0, MOTY_WF_I8 = 1, MOTY_WF_I4 = 2, MOTY_WF_Q4R4 = 7 };
+/* activations between the two halves of an FFN (hw/hw_ops.h:19-21, engines/gemma.c:389-391) */
+enum { MOTY_ACT_SILU = 0, MOTY_ACT_GELU_TANH = 1 };
+
+enum {
+    MOTY_CUDA_OK = 0,
+    MOTY_CUDA_EINIT = -1,      /* library not initialised / device not in the set */
+    MOTY_CUDA_EARG = -2,       /* bad argument (shape, format, NULL) */
+    MOTY_CUDA_ECUDA = -3,      /* a CUDA call failed */
+    MOTY_CUDA_ENOMEM = -4,     /* device allocation failed */
+    MOTY_CUDA_ELIMIT = -5,     /* size beyond what the entry point supports */
+    MOTY_CUDA_EKERNEL = -6     /* a kernel reported an internal error (bounded wait expired) */
+};
+
+typedef struct MotyCudaMat MotyCudaMat;   /* one weight matrix resident on one GPU */
+typedef struct MotyCudaMoe MotyCudaMoe;   /* one MoE layer: router + resident experts */
+
+/* ---- lifecycle -------------------------------------------------------- */
+
+/* Select the GPUs (ndev >= 1 device ordinals; NULL/0 = device 0), create one
+ * stream and the scratch arenas per device.  Precedent: moty_cuda_init(devices,
+ * ndev) at engines/glm.c:5701-5709. */
+int moty_cuda_init(const int *devices, int ndev);
+void moty_cuda_shutdown(void);
+const char *moty_cuda_last_error(void);
+/* SM count of an initialised device, <0 on error */
+int moty_cuda_sm_count(int device);
+/* block until everything enqueued on the library's stream of `device` is done */
+int moty_cuda_sync(int device);
+
+/* pinned host memory for callers that want asynchronous copies on the plain
+ * (host-pointer) entries; ordinary malloc'd memory works too, only slower */
+int moty_cuda_host_alloc(void **p, size_t bytes);
+int moty_cuda_host_free(void *p);
+
+/* ---- weights ----------------------------------------------------------
+ * Replaces the host-side Mat descriptor (nn/nn_mat.h:18-25).  Layouts are the
+ * reference's own, copied byte for byte:
+ *   MOTY_WF_I8   codes int8 [O][I] row-major, scales f32 [O]            (nn/quant.c:12-33)
+ *   MOTY_WF_Q4R4 codes uint8 [ceil(O/4)][I/32][64], scales f16 [ceil(O/4)][I/32][4]
+ *                                                                         (hw/hw_q4r4.h:3-11)
+ *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55)
+ *   MOTY_WF_F32  codes float [O][I], scales NULL (router matrices only)
+ * The hook point in the loader is right after load_mat_bits / load_mat_r4 /
+ * load_embed_q8 (runtime/rt_model_load.h:85-177, 209-226). */
+int moty_cuda_upload_mat(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
+                         int O, int I, int device);
+/* rows [o0, o1) of the same host matrix: the row shard of one GPU.  For
+ * MOTY_WF_Q4R4 o0 must be a multiple of 4. */
+int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
+                              int O, int I, int o0, int o1, int device);
+int moty_cuda_free_mat(MotyCudaMat *m);
+int64_t moty_cuda_mat_bytes(const MotyCudaMat *m);
+int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *device);
+
+/* ---- the operator boundary --------------------------------------------
+ * Replaces moty_mat_apply(y, x, w, S) (nn/mat.c:70-83) for the formats above:
+ *   WF_I8   -> moty_matmul_q_s      (nn/matmul.c:51-66, IDOT=1 path)
+ *   WF_Q4R4 -> moty_matmul_q4r4_s   (nn/matmul.c:405-433)
+ *   WF_I4   -> moty_matmul_i4_s with IDOT4=1 (nn/matmul.c:75-96)
+ * x is [S][I] f32, y is [S][O] f32.  Like the reference, I <= 16384 for the
+ * integer paths (NN_QROW_MAX, nn/nn_matmul.h:35); larger I is MOTY_CUDA_ELIMIT. */
+int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
+int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
+/* same, also returning the int32 accumulators [S][O] of the Q8_0 path (the
+ * values moty_hw_dot_i8i8 returns, hw/hw_scalar.h:8-12) for exact checks */
+int moty_cuda_mat_apply_acc(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S);
+
+/* HwBackend.matmul_i8 (hw/hw_backend.h:56-57) / moty_matmul_q_s with host
+ * weights: uploads, runs, frees.  A correctness convenience, not a fast path. */
+int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale, int S, int I, int O);
+/* moty_matmul_q4r4_s (nn/matmul.c:405) with host weights */
+int moty_cuda_matmul_q4r4_s(float *y, const float *x, const uint8_t *q4, const uint16_t *s16, int S, int I, int O);
+
+/* ---- kernels of the hw.h contract, host-callable ----------------------- */
+
+/* moty_hw_qrow_i8 (hw/hw_quant.h:9-16) over `rows` rows of n floats:
+ * q [rows][n] int8, scale [rows] f32. */
+int moty_cuda_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n);
+int moty_cuda_qrow_i8_dev(const float *x_dev, int8_t *q_dev, float *scale_dev, int rows, int n, void *stream);
+/* moty_hw_quant_g32 (hw/hw_q4r4.h:36-45) over `rows` rows of I floats (I % 32 == 0) */
+int moty_cuda_quant_g32(const float *x, int rows, int I, int8_t *xq, float *xs, int32_t *xsum);
+int moty_cuda_quant_g32_dev(const float *x_dev, int rows, int I, int8_t *xq_dev, float *xs_dev,
+                            int32_t *xsum_dev, void *stream);
+/* moty_hw_dot_i8i8 (hw/hw_scalar.h:8-12): nrows dots of length n, w [nrows][n]
+ * against one x [n]; out [nrows] int32.  A test entry: per-row host calls are
+ * meaningless for speed, the GEMV/GEMM kernels use the same device code. */
+int moty_cuda_dot_i8i8(const int8_t *w, const int8_t *x, int nrows, int n, int32_t *out);
+/* moty_hw_dot_i4i8 (hw/hw_scalar.h:14-22), same calling shape; w4 [nrows][(n+1)/2] */
+int moty_cuda_dot_i4i8(const uint8_t *w4, const int8_t *x, int nrows, int n, int32_t *out);
+
+/* ---- router ------------------------------------------------------------
+ * moty_moe_topk (runtime/moecache.c:97-111) on `rows` rows of E already
+ * soft-maxed values: idx [rows][K] int32, w [rows][K] f32. */
+int moty_cuda_moe_topk(const float *probs, int rows, int E, int K, int *idx, float *w, int norm_topk);
+/* route_topk (nn/moe.c:27-30): softmax (hw/hw_ops.h:22-26) then top-K with
+ * renormalisation.  probs_out (optional) receives the softmax [rows][E]. */
+int moty_cuda_route_topk(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs_out);
+int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E, int K, int *idx_dev, float *w_dev,
+                             float *probs_dev, int norm_topk, void *stream);
+
+/* ---- dense FFN -----------------------------------------------------------
+ * Replaces moty_nn_dense_ffn (nn/ffn.c:26-55) and the engines' mlp()
+ * (engines/qwen.c:654-679 SiLU, engines/gemma.c:392-401 tanh-GeLU):
+ * out = down( act(gate x) * up x ), x [S][D], out [S][D].  The intermediate
+ * [S][I] never leaves the GPU. */
+int moty_cuda_ffn(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
+                  float *out, const float *x, int S);
+int moty_cuda_ffn_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
+                      float *out_dev, const float *x_dev, int S, void *stream);
+
+/* ---- MoE layer -------------------------------------------------------------
+ * Replaces the MotyMoeView + ExpertCache pair (nn/moe.h:20-33, runtime/moe.h:35-54)
+ * with all experts resident on the GPU, keyed by expert id (never by slot
+ * pointer: the reference reuses slots on eviction, runtime/moecache.c:51-89).
+ * efmt: MOTY_WF_I8 (ExpertSlot layout: g,u [I][D] int8 + f32 row scales,
+ * d [D][I]) or MOTY_WF_Q4R4 (each projection in the Q4R4 block layout).
+ * Experts [e_lo, e_hi) live on this GPU (expert-parallel shard); others are
+ * skipped by the block entries and must be served by another rank. */
+int moty_cuda_moe_create(MotyCudaMoe **out, int E, int K, int I, int D, int efmt,
+                         int e_lo, int e_hi, int device);
+int moty_cuda_moe_free(MotyCudaMoe *m);
+/* what LoadExpertFn (runtime/moe.h:56, engines/olmoe.c:141-151) fills for one expert */
+int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *g, const void *gs,
+                                const void *u, const void *us, const void *d, const void *ds);
+/* optional router matrix [E][D]; without one the block entries need `logits` */
+int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router);
+
+/* moty_nn_moe_topk_d1 (nn/moe.c:33-153): one token.  logits (optional, [E]) are
+ * the router outputs; NULL = compute them with the router set above.  The K
+ * weighted expert outputs are summed in selection order k = 0..K-1. */
+int moty_cuda_moe_d1(MotyCudaMoe *m, float *out, const float *x, const float *logits);
+/* moty_nn_moe_topk_batch (nn/moe.c:159-205): S tokens; a token's expert outputs
+ * are summed in ascending expert id. */
+int moty_cuda_moe_batch(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits);
+/* engines/olmoe.c:219-244: S tokens, each summed in selection order, with the
+ * config's norm_topk flag. */
+int moty_cuda_olmoe_moe(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits, int norm_topk);
+/* device-pointer form of the three above.  order: 0 = selection order (d1 /
+ * olmoe), 1 = ascending expert id (batch).  idx_dev/w_dev (optional) return the
+ * routing [S][K].  partial != 0: only this GPU's experts contribute and the
+ * result is a partial sum to be combined across ranks. */
+int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, int S,
+                            const float *logits_dev, int order, int norm_topk,
+                            int *idx_dev, float *w_dev, void *stream);
+
+/* ---- greedy token ----------------------------------------------------------
+ * moty_argmax_v (nn/sample.c:9-13): first index of the maximum of v [n]. */
+int moty_cuda_argmax(const float *v, int n, int *out);
+int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream);
+
+/* ---- load-time quantizers (weights) -----------------------------------------
+ * moty_quantize_rows (nn/quant.c:12-33) with bits = 8: w [O][I] f32 host ->
+ * q [O][I] int8, scale [O] f32 host, computed on the GPU. */
+int moty_cuda_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I);
+/* moty_pack_q4r4_block over a whole matrix (nn/quant.c:157-179,
+ * runtime/rt_model_load.h:85-121): q4 [ceil(O/4)][I/32][64], s16 [..][4]. */
+int moty_cuda_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOTY_CUDA_H */

@@ -1,0 +1,354 @@
+"""moty_b200 -- host-side mirror of moty's quantized-matmul operators over the
+sm_100a library ``libmoty_cuda.so`` (C ABI in ``include/moty_cuda.h``).
+
+Names follow the reference's operator layer (moty source tree, directory c/):
+``Mat`` + ``mat_apply`` (nn/nn_mat.h:18-30, nn/mat.c:70-83), ``dense_ffn``
+(nn/ffn.h:14), the MoE block (nn/moe.h:35-38), the hw.h kernels (hw/hw.h:58-124).
+Arrays are numpy; shapes follow the reference: x ``[S][I]``, y ``[S][O]``.
+
+There is no CPU fallback: if the library is missing or a call fails, an
+exception is raised.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libmoty_cuda.so")
+
+WF_F32, WF_I8, WF_I4, WF_Q4R4 = 0, 1, 2, 7
+ACT_SILU, ACT_GELU_TANH = 0, 1
+QROW_MAX = 16384
+
+_lib = None
+
+
+class MotyCudaError(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """The loaded C-ABI library.  Raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise MotyCudaError(f"{LIB_PATH} is missing: build it with `python -m moty_b200.build` "
+                                "(there is no CPU fallback)")
+        _lib = C.CDLL(LIB_PATH)
+        _lib.moty_cuda_last_error.restype = C.c_char_p
+        _lib.moty_cuda_mat_bytes.restype = C.c_int64
+    return _lib
+
+
+def _ck(rc: int) -> None:
+    if rc != 0:
+        raise MotyCudaError(f"libmoty_cuda error {rc}: {lib().moty_cuda_last_error().decode()}")
+
+
+def _p(a):
+    if a is None:
+        return None
+    if not a.flags["C_CONTIGUOUS"]:
+        raise ValueError("array must be C-contiguous")
+    return C.c_void_p(a.ctypes.data)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def init(devices=None) -> None:
+    """moty_cuda_init: select GPUs (default: device 0)."""
+    if devices is None:
+        _ck(lib().moty_cuda_init(None, 0))
+    else:
+        arr = (C.c_int * len(devices))(*devices)
+        _ck(lib().moty_cuda_init(arr, len(devices)))
+
+
+def shutdown() -> None:
+    lib().moty_cuda_shutdown()
+
+
+def sync(device: int = 0) -> None:
+    _ck(lib().moty_cuda_sync(device))
+
+
+def sm_count(device: int = 0) -> int:
+    n = lib().moty_cuda_sm_count(device)
+    if n < 0:
+        _ck(n)
+    return n
+
+
+def pinned_empty(shape, dtype) -> np.ndarray:
+    """A numpy array in page-locked host memory (freed when the array dies)."""
+    dtype = np.dtype(dtype)
+    n = int(np.prod(shape)) * dtype.itemsize
+    ptr = C.c_void_p()
+    _ck(lib().moty_cuda_host_alloc(C.byref(ptr), C.c_size_t(max(n, 1))))
+    buf = (C.c_char * max(n, 1)).from_address(ptr.value)
+    arr = np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape))).reshape(shape)
+    _PINNED[arr.ctypes.data] = ptr.value
+    return arr
+
+
+_PINNED: dict[int, int] = {}
+
+
+def pinned_free(arr: np.ndarray) -> None:
+    p = _PINNED.pop(arr.ctypes.data, None)
+    if p:
+        _ck(lib().moty_cuda_host_free(C.c_void_p(p)))
+
+
+# ---------------------------------------------------------------------------
+# weights and mat_apply
+# ---------------------------------------------------------------------------
+class Mat:
+    """A weight matrix resident on one GPU (the device-side ``Mat``)."""
+
+    def __init__(self, fmt: int, codes: np.ndarray, scales, O: int, I: int, device: int = 0, rows=None):
+        self.fmt, self.O, self.I, self.device = fmt, O, I, device
+        codes = np.ascontiguousarray(codes)
+        scales = None if scales is None else np.ascontiguousarray(scales)
+        h = C.c_void_p()
+        if rows is None:
+            _ck(lib().moty_cuda_upload_mat(C.byref(h), fmt, _p(codes), _p(scales), O, I, device))
+        else:
+            _ck(lib().moty_cuda_upload_mat_rows(C.byref(h), fmt, _p(codes), _p(scales), O, I, rows[0], rows[1], device))
+            self.O = rows[1] - rows[0]
+        self.h = h
+
+    @classmethod
+    def i8(cls, q, scale, device=0, rows=None):
+        q = np.ascontiguousarray(q, np.int8)
+        return cls(WF_I8, q, _f32(scale), q.shape[0], q.shape[1], device, rows)
+
+    @classmethod
+    def q4r4(cls, q4, s16, O, I, device=0, rows=None):
+        return cls(WF_Q4R4, np.ascontiguousarray(q4, np.uint8), np.ascontiguousarray(s16, np.uint16), O, I, device, rows)
+
+    @classmethod
+    def i4(cls, q4, scale, O, I, device=0):
+        return cls(WF_I4, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device)
+
+    @classmethod
+    def f32(cls, w, device=0):
+        w = _f32(w)
+        return cls(WF_F32, w, None, w.shape[0], w.shape[1], device)
+
+    def nbytes(self) -> int:
+        return int(lib().moty_cuda_mat_bytes(self.h))
+
+    def free(self) -> None:
+        if self.h:
+            lib().moty_cuda_free_mat(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass
+
+
+def mat_apply(w: Mat, x, y: np.ndarray | None = None, want_acc: bool = False):
+    """moty_mat_apply (nn/mat.c:70-83) with host arrays: returns y ``[S][O]``
+    (and the int32 accumulators for WF_I8 when ``want_acc``)."""
+    x = _f32(x)
+    if x.ndim == 1:
+        x = x[None, :]
+    S = x.shape[0]
+    if x.shape[1] != w.I:
+        raise ValueError(f"x has width {x.shape[1]}, matrix expects {w.I}")
+    if y is None:
+        y = np.empty((S, w.O), np.float32)
+    if want_acc:
+        acc = np.empty((S, w.O), np.int32)
+        _ck(lib().moty_cuda_mat_apply_acc(w.h, _p(y), _p(acc), _p(x), S))
+        return y, acc
+    _ck(lib().moty_cuda_mat_apply(w.h, _p(y), _p(x), S))
+    return y
+
+
+def mat_apply_dev(w: Mat, y_ptr: int, x_ptr: int, S: int, stream: int = 0) -> None:
+    """Device-pointer form: enqueue only (no synchronisation)."""
+    _ck(lib().moty_cuda_mat_apply_dev(w.h, C.c_void_p(y_ptr), C.c_void_p(x_ptr), S, C.c_void_p(stream)))
+
+
+def matmul_q_s(x, q, scale):
+    """moty_matmul_q_s (nn/matmul.c:51-66) with host weights."""
+    x = _f32(x); q = np.ascontiguousarray(q, np.int8); scale = _f32(scale)
+    S, I = x.shape; O = q.shape[0]
+    y = np.empty((S, O), np.float32)
+    _ck(lib().moty_cuda_matmul_q_s(_p(y), _p(x), _p(q), _p(scale), S, I, O))
+    return y
+
+
+def matmul_q4r4_s(x, q4, s16, O):
+    """moty_matmul_q4r4_s (nn/matmul.c:405-433) with host weights."""
+    x = _f32(x); S, I = x.shape
+    y = np.empty((S, O), np.float32)
+    _ck(lib().moty_cuda_matmul_q4r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q4, np.uint8)),
+                                      _p(np.ascontiguousarray(s16, np.uint16)), S, I, O))
+    return y
+
+
+# ---------------------------------------------------------------------------
+# hw.h kernels
+# ---------------------------------------------------------------------------
+def qrow_i8(x):
+    """moty_hw_qrow_i8 per row: returns (q int8 [rows][n], scale f32 [rows])."""
+    x = _f32(x)
+    rows = x.reshape(-1, x.shape[-1]) if x.ndim > 1 else x[None, :]
+    q = np.empty(rows.shape, np.int8); s = np.empty(rows.shape[0], np.float32)
+    _ck(lib().moty_cuda_qrow_i8(_p(rows), _p(q), _p(s), rows.shape[0], rows.shape[1]))
+    return q.reshape(x.shape), s
+
+
+def quant_g32(x):
+    """moty_hw_quant_g32 per row: (xq, xs [rows][I/32], xsum [rows][I/32])."""
+    x = _f32(x)
+    rows = x.reshape(-1, x.shape[-1])
+    I = rows.shape[1]
+    xq = np.empty(rows.shape, np.int8)
+    xs = np.empty((rows.shape[0], I // 32), np.float32); xsum = np.empty((rows.shape[0], I // 32), np.int32)
+    _ck(lib().moty_cuda_quant_g32(_p(rows), rows.shape[0], I, _p(xq), _p(xs), _p(xsum)))
+    return xq, xs, xsum
+
+
+def dot_i8i8(w, x):
+    """moty_hw_dot_i8i8 for every row of w [nrows][n] against x [n]."""
+    w = np.ascontiguousarray(w, np.int8); x = np.ascontiguousarray(x, np.int8)
+    w2 = w.reshape(-1, x.size) if x.size else w.reshape(w.shape[0] if w.ndim > 1 else 1, 0)
+    out = np.empty(w2.shape[0], np.int32)
+    _ck(lib().moty_cuda_dot_i8i8(_p(w2), _p(x), w2.shape[0], x.size, _p(out)))
+    return out
+
+
+def dot_i4i8(w4, x, nrows):
+    w4 = np.ascontiguousarray(w4, np.uint8); x = np.ascontiguousarray(x, np.int8)
+    out = np.empty(nrows, np.int32)
+    _ck(lib().moty_cuda_dot_i4i8(_p(w4), _p(x), nrows, x.size, _p(out)))
+    return out
+
+
+def moe_topk(probs, K, norm_topk):
+    """moty_moe_topk per row of already soft-maxed values."""
+    p = _f32(probs); rows = p.reshape(-1, p.shape[-1])
+    idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+    _ck(lib().moty_cuda_moe_topk(_p(rows), rows.shape[0], rows.shape[1], K, _p(idx), _p(w), int(norm_topk)))
+    return idx, w
+
+
+def route_topk(logits, K, want_probs=False):
+    """route_topk (nn/moe.c:27-30): softmax + top-K with renormalisation."""
+    lg = _f32(logits); rows = lg.reshape(-1, lg.shape[-1])
+    idx = np.empty((rows.shape[0], K), np.int32); w = np.empty((rows.shape[0], K), np.float32)
+    probs = np.empty(rows.shape, np.float32) if want_probs else None
+    _ck(lib().moty_cuda_route_topk(_p(rows), rows.shape[0], rows.shape[1], K, _p(idx), _p(w), _p(probs)))
+    return (idx, w, probs) if want_probs else (idx, w)
+
+
+def argmax(v) -> int:
+    """moty_argmax_v: first index of the maximum."""
+    v = _f32(v).ravel()
+    out = C.c_int(0)
+    _ck(lib().moty_cuda_argmax(_p(v), v.size, C.byref(out)))
+    return out.value
+
+
+def quantize_rows(w):
+    """moty_quantize_rows (bits=8) computed on the GPU."""
+    w = _f32(w); O, I = w.shape
+    q = np.empty((O, I), np.int8); s = np.empty(O, np.float32)
+    _ck(lib().moty_cuda_quantize_rows(_p(w), _p(q), _p(s), O, I))
+    return q, s
+
+
+def pack_q4r4(w):
+    """moty_pack_q4r4_block over a whole matrix, computed on the GPU."""
+    w = _f32(w); O, I = w.shape
+    nblk, nb = (O + 3) // 4, I // 32
+    q4 = np.empty(nblk * nb * 64, np.uint8); s16 = np.empty(nblk * nb * 4, np.uint16)
+    _ck(lib().moty_cuda_pack_q4r4(_p(w), O, I, _p(q4), _p(s16)))
+    return q4, s16
+
+
+# ---------------------------------------------------------------------------
+# blocks
+# ---------------------------------------------------------------------------
+def dense_ffn(gate: Mat, up: Mat, down: Mat, x, act: int = ACT_SILU):
+    """moty_nn_dense_ffn / the engines' mlp(): down(act(gate x) * up x)."""
+    x = _f32(x)
+    if x.ndim == 1:
+        x = x[None, :]
+    out = np.empty((x.shape[0], down.O), np.float32)
+    _ck(lib().moty_cuda_ffn(gate.h, up.h, down.h, act, _p(out), _p(x), x.shape[0]))
+    return out
+
+
+def dense_ffn_dev(gate: Mat, up: Mat, down: Mat, out_ptr: int, x_ptr: int, S: int, act: int = ACT_SILU, stream: int = 0):
+    _ck(lib().moty_cuda_ffn_dev(gate.h, up.h, down.h, act, C.c_void_p(out_ptr), C.c_void_p(x_ptr), S, C.c_void_p(stream)))
+
+
+class Moe:
+    """One MoE layer with its experts resident on a GPU (the device-side
+    MotyMoeView + ExpertCache).  ``e_lo:e_hi`` is this GPU's expert shard."""
+
+    def __init__(self, E, K, I, D, efmt=WF_I8, e_lo=0, e_hi=None, device=0):
+        self.E, self.K, self.I, self.D, self.efmt, self.device = E, K, I, D, efmt, device
+        self.e_lo, self.e_hi = e_lo, E if e_hi is None else e_hi
+        h = C.c_void_p()
+        _ck(lib().moty_cuda_moe_create(C.byref(h), E, K, I, D, efmt, self.e_lo, self.e_hi, device))
+        self.h = h
+        self.router = None
+
+    def upload_expert(self, eid, g, gs, u, us, d, ds):
+        arrs = [np.ascontiguousarray(a) for a in (g, gs, u, us, d, ds)]
+        _ck(lib().moty_cuda_moe_upload_expert(self.h, eid, *(_p(a) for a in arrs)))
+
+    def set_router(self, router: Mat | None):
+        self.router = router
+        _ck(lib().moty_cuda_moe_set_router(self.h, router.h if router else None))
+
+    def d1(self, x, logits=None):
+        """moty_nn_moe_topk_d1: one token."""
+        x = _f32(x).reshape(1, self.D); out = np.empty((1, self.D), np.float32)
+        lg = None if logits is None else _f32(logits).reshape(1, self.E)
+        _ck(lib().moty_cuda_moe_d1(self.h, _p(out), _p(x), _p(lg)))
+        return out
+
+    def batch(self, x, logits=None):
+        """moty_nn_moe_topk_batch: S tokens, experts in ascending id."""
+        x = _f32(x).reshape(-1, self.D); S = x.shape[0]; out = np.empty((S, self.D), np.float32)
+        lg = None if logits is None else _f32(logits).reshape(S, self.E)
+        _ck(lib().moty_cuda_moe_batch(self.h, _p(out), _p(x), S, _p(lg)))
+        return out
+
+    def olmoe(self, x, logits=None, norm_topk=0):
+        """engines/olmoe.c moe(): per token, selection order."""
+        x = _f32(x).reshape(-1, self.D); S = x.shape[0]; out = np.empty((S, self.D), np.float32)
+        lg = None if logits is None else _f32(logits).reshape(S, self.E)
+        _ck(lib().moty_cuda_olmoe_moe(self.h, _p(out), _p(x), S, _p(lg), int(norm_topk)))
+        return out
+
+    def apply_dev(self, out_ptr, x_ptr, S, logits_ptr=0, order=0, norm_topk=1, idx_ptr=0, w_ptr=0, stream=0):
+        _ck(lib().moty_cuda_moe_apply_dev(self.h, C.c_void_p(out_ptr), C.c_void_p(x_ptr), S,
+                                          C.c_void_p(logits_ptr), order, norm_topk,
+                                          C.c_void_p(idx_ptr), C.c_void_p(w_ptr), C.c_void_p(stream)))
+
+    def free(self):
+        if self.h:
+            lib().moty_cuda_moe_free(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.free()
+        except Exception:
+            pass

@@ -1,0 +1,797 @@
+// api.cu -- the C ABI of libmoty_cuda (include/moty_cuda.h): contexts, weight
+// upload, the mat_apply / FFN / MoE drivers.  Host logic only; kernels live in
+// the other translation units.  No CPU fallback anywhere: a failure is returned.
+#include "kernels.cuh"
+#include "moe.cuh"
+#include <string.h>
+#include <stdlib.h>
+#include <new>
+
+// ---------------------------------------------------------------------------
+// errors
+// ---------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+int moty_set_error(int code, const char *fmt, ...) {
+    va_list ap; va_start(ap, fmt);
+    vsnprintf(g_err, sizeof g_err, fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+extern "C" const char *moty_cuda_last_error(void) { return g_err; }
+
+// ---------------------------------------------------------------------------
+// contexts
+// ---------------------------------------------------------------------------
+static DevCtx g_ctx[MOTY_MAX_DEV];
+static int g_nctx = 0;
+
+DevCtx *moty_ctx(int device) {
+    for (int i = 0; i < g_nctx; i++)
+        if (g_ctx[i].ready && g_ctx[i].dev == device) return &g_ctx[i];
+    return nullptr;
+}
+
+int moty_grow(DevCtx *c, Buf *b, size_t bytes) {
+    if (bytes <= b->cap) return 0;
+    CK(cudaSetDevice(c->dev));
+    if (b->p) { CK(cudaStreamSynchronize(c->stream)); CK(cudaFree(b->p)); b->p = nullptr; b->cap = 0; }
+    size_t want = bytes + bytes / 4 + 256;
+    CK(cudaMalloc(&b->p, want));
+    b->cap = want;
+    return 0;
+}
+
+int moty_grow_pinned(DevCtx *c, Buf *b, size_t bytes) {
+    if (bytes <= b->cap) return 0;
+    CK(cudaSetDevice(c->dev));
+    if (b->p) { CK(cudaStreamSynchronize(c->stream)); CK(cudaFreeHost(b->p)); b->p = nullptr; b->cap = 0; }
+    size_t want = bytes + bytes / 4 + 256;
+    CK(cudaMallocHost(&b->p, want));
+    b->cap = want;
+    return 0;
+}
+
+static void free_buf(Buf *b) { if (b->p) cudaFree(b->p); b->p = nullptr; b->cap = 0; }
+static void free_pinned(Buf *b) { if (b->p) cudaFreeHost(b->p); b->p = nullptr; b->cap = 0; }
+
+extern "C" int moty_cuda_init(const int *devices, int ndev) {
+    int zero = 0;
+    if (!devices || ndev <= 0) { devices = &zero; ndev = 1; }
+    if (ndev > MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "init: %d devices (max %d)", ndev, MOTY_MAX_DEV);
+    int have = 0;
+    CK(cudaGetDeviceCount(&have));
+    for (int i = 0; i < ndev; i++) {
+        int d = devices[i];
+        if (d < 0 || d >= have) return moty_set_error(MOTY_CUDA_EARG, "init: device %d of %d", d, have);
+        if (moty_ctx(d)) continue;
+        if (g_nctx >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "init: context table full");
+        CK(cudaSetDevice(d));
+        cudaDeviceProp prop;
+        CK(cudaGetDeviceProperties(&prop, d));
+        if (prop.major != 10)
+            return moty_set_error(MOTY_CUDA_EINIT, "device %d is sm_%d%d; this library is built for sm_100a only",
+                                  d, prop.major, prop.minor);
+        DevCtx *c = &g_ctx[g_nctx];
+        *c = DevCtx();
+        c->dev = d; c->sms = prop.multiProcessorCount;
+        CK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
+        CK(cudaMalloc(&c->err_dev, 64));
+        CK(cudaMemset(c->err_dev, 0, 64));
+        CKR(gemv_q8_init_device());
+        CKR(q4r4_init_device());
+        c->ready = true;
+        g_nctx++;
+    }
+    return 0;
+}
+
+extern "C" void moty_cuda_shutdown(void) {
+    for (int i = 0; i < g_nctx; i++) {
+        DevCtx *c = &g_ctx[i];
+        if (!c->ready) continue;
+        cudaSetDevice(c->dev);
+        cudaStreamSynchronize(c->stream);
+        Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc};
+        for (Buf *b : bs) free_buf(b);
+        free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
+        if (c->err_dev) cudaFree(c->err_dev);
+        cudaStreamDestroy(c->stream);
+        c->ready = false;
+    }
+    g_nctx = 0;
+}
+
+extern "C" int moty_cuda_sm_count(int device) {
+    DevCtx *c = moty_ctx(device);
+    return c ? c->sms : moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+}
+
+extern "C" int moty_cuda_sync(int device) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    CK(cudaSetDevice(device));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_host_alloc(void **p, size_t bytes) {
+    if (!p) return moty_set_error(MOTY_CUDA_EARG, "host_alloc: null");
+    CK(cudaMallocHost(p, bytes ? bytes : 1));
+    return 0;
+}
+
+extern "C" int moty_cuda_host_free(void *p) {
+    if (p) CK(cudaFreeHost(p));
+    return 0;
+}
+
+static cudaStream_t pick_stream(DevCtx *c, void *stream) { return stream ? (cudaStream_t)stream : c->stream; }
+
+// ---------------------------------------------------------------------------
+// weights
+// ---------------------------------------------------------------------------
+static int mat_sizes(int fmt, int O, int I, size_t *cb, size_t *sb) {
+    if (O <= 0 || I <= 0) return moty_set_error(MOTY_CUDA_EARG, "matrix %dx%d", O, I);
+    switch (fmt) {
+        case MOTY_WF_I8: *cb = (size_t)O * I; *sb = (size_t)O * 4; return 0;
+        case MOTY_WF_I4: *cb = (size_t)O * ((I + 1) / 2); *sb = (size_t)O * 4; return 0;
+        case MOTY_WF_F32: *cb = (size_t)O * I * 4; *sb = 0; return 0;
+        case MOTY_WF_Q4R4:
+            if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "Q4R4 needs I %% 32 == 0 (I=%d)", I);
+            *cb = (size_t)((O + 3) / 4) * (I / 32) * 64; *sb = (size_t)((O + 3) / 4) * (I / 32) * 8; return 0;
+        default: return moty_set_error(MOTY_CUDA_EARG, "unsupported weight format %d", fmt);
+    }
+}
+
+extern "C" int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
+                                         int O, int I, int o0, int o1, int device) {
+    if (!out || !codes) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: null argument");
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    if (o0 < 0 || o1 > O || o0 >= o1) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: rows [%d,%d) of %d", o0, o1, O);
+    if (fmt != MOTY_WF_F32 && !scales) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: scales missing");
+    if (fmt == MOTY_WF_Q4R4 && (o0 % 4)) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: Q4R4 shard must start on a block (o0=%d)", o0);
+    size_t cb, sb, cb0, sb0;
+    int rows = o1 - o0;
+    CKR(mat_sizes(fmt, rows, I, &cb, &sb));
+    // byte offset of row o0 in the host arrays
+    size_t dummy;
+    if (o0 > 0) { CKR(mat_sizes(fmt, o0, I, &cb0, &sb0)); } else { cb0 = sb0 = 0; }
+    (void)dummy;
+    CK(cudaSetDevice(device));
+    MotyCudaMat *m = new (std::nothrow) MotyCudaMat();
+    if (!m) return moty_set_error(MOTY_CUDA_ENOMEM, "upload_mat: host allocation");
+    memset(m, 0, sizeof *m);
+    m->fmt = fmt; m->O = rows; m->I = I; m->device = device; m->code_bytes = cb; m->scale_bytes = sb;
+    cudaError_t e = cudaMalloc(&m->codes, cb + 256);
+    if (e == cudaSuccess && sb) e = cudaMalloc(&m->scales, sb + 256);
+    if (e != cudaSuccess) {
+        if (m->codes) cudaFree(m->codes);
+        delete m;
+        return moty_set_error(MOTY_CUDA_ENOMEM, "upload_mat: %s", cudaGetErrorString(e));
+    }
+    e = cudaMemcpyAsync(m->codes, (const char *)codes + cb0, cb, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess && sb) e = cudaMemcpyAsync(m->scales, (const char *)scales + sb0, sb, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        cudaFree(m->codes); if (m->scales) cudaFree(m->scales); delete m;
+        return moty_set_error(MOTY_CUDA_ECUDA, "upload_mat copy: %s", cudaGetErrorString(e));
+    }
+    if (fmt == MOTY_WF_I8) q8_tc_make_tmap(m);      // optional: absent descriptor = no tensor-core path
+    *out = m;
+    return 0;
+}
+
+extern "C" int moty_cuda_upload_mat(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
+                                    int O, int I, int device) {
+    return moty_cuda_upload_mat_rows(out, fmt, codes, scales, O, I, 0, O, device);
+}
+
+extern "C" int moty_cuda_free_mat(MotyCudaMat *m) {
+    if (!m) return 0;
+    DevCtx *c = moty_ctx(m->device);
+    if (c) { cudaSetDevice(m->device); cudaStreamSynchronize(c->stream); }
+    if (m->codes) cudaFree(m->codes);
+    if (m->scales) cudaFree(m->scales);
+    delete m;
+    return 0;
+}
+
+extern "C" int64_t moty_cuda_mat_bytes(const MotyCudaMat *m) { return m ? (int64_t)(m->code_bytes + m->scale_bytes) : 0; }
+
+extern "C" int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *device) {
+    if (!m) return moty_set_error(MOTY_CUDA_EARG, "mat_shape: null");
+    if (fmt) *fmt = m->fmt;
+    if (O) *O = m->O;
+    if (I) *I = m->I;
+    if (device) *device = m->device;
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// mat_apply
+// ---------------------------------------------------------------------------
+static const int Q8_TC_MIN_S = 16;
+
+static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int S, int32_t *acc, cudaStream_t st) {
+    if (S <= 0) return 0;
+    const int I = w->I, O = w->O;
+    if (w->fmt == MOTY_WF_F32) return launch_f32_rows((const float *)w->codes, x, y, S, I, O, st);
+    if (I > MOTY_QROW_MAX)
+        return moty_set_error(MOTY_CUDA_ELIMIT, "mat_apply: I=%d exceeds %d (the reference switches to an f32 path there)", I, MOTY_QROW_MAX);
+    if (w->fmt == MOTY_WF_I8) {
+        if (S == 1 && I % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+            return launch_q8_gemv_fused(x, (const int8_t *)w->codes, (const float *)w->scales, y, acc, I, O, c->sms, st);
+        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
+        CKR(moty_grow(c, &c->sx, (size_t)S * 4));
+        CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
+        if (I % 16 != 0)
+            return launch_q8_any((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                                 (const float *)c->sx.p, y, acc, S, I, O, st);
+        if (S >= Q8_TC_MIN_S && w->has_tmap && q8_tc_supported(S, I, O))
+            return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
+        Q8Args a; memset(&a, 0, sizeof a);
+        a.w = (const int8_t *)w->codes; a.scale = (const float *)w->scales;
+        a.xi = (const int8_t *)c->xi.p; a.sx = (const float *)c->sx.p;
+        a.y = y; a.ldy = O; a.acc = acc; a.S = S; a.I = I; a.O = O;
+        return launch_q8_small(a, c->sms, st);
+    }
+    if (acc) return moty_set_error(MOTY_CUDA_EARG, "int32 accumulators exist for MOTY_WF_I8 only");
+    if (w->fmt == MOTY_WF_Q4R4) {
+        int nb = I / 32;
+        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
+        CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
+        CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
+        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+        CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
+        CKR(launch_q4r4_forms((uint8_t *)c->misc.p, S, st));
+        Q4Args a; memset(&a, 0, sizeof a);
+        a.w = (const uint8_t *)w->codes; a.d = (const uint16_t *)w->scales;
+        a.xq = (const int8_t *)c->xi.p; a.xs = (const float *)c->xs.p; a.xsum = (const int32_t *)c->xsum.p;
+        a.form = (const uint8_t *)c->misc.p;
+        a.y = y; a.ldy = O; a.S = S; a.I = I; a.O = O;
+        return launch_q4r4_small(a, c->sms, st);
+    }
+    if (w->fmt == MOTY_WF_I4) {
+        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
+        CKR(moty_grow(c, &c->sx, (size_t)S * 4));
+        CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
+        return launch_i4_rows((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                              (const float *)c->sx.p, y, S, I, O, st);
+    }
+    return moty_set_error(MOTY_CUDA_EARG, "mat_apply: format %d", w->fmt);
+}
+
+extern "C" int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream) {
+    if (!w || !y_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_dev: null argument");
+    DevCtx *c = moty_ctx(w->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
+    CK(cudaSetDevice(w->device));
+    return mat_apply_on(c, w, y_dev, x_dev, S, nullptr, pick_stream(c, stream));
+}
+
+// host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
+static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
+    if (!w || !y || !x) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: null argument");
+    if (S <= 0) return 0;
+    DevCtx *c = moty_ctx(w->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
+    CK(cudaSetDevice(w->device));
+    size_t xb = (size_t)S * w->I * 4, yb = (size_t)S * w->O * 4;
+    CKR(moty_grow(c, &c->dx, xb));
+    CKR(moty_grow(c, &c->dy, yb));
+    if (acc) CKR(moty_grow(c, &c->acc32, yb));
+    CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
+    CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, acc ? (int32_t *)c->acc32.p : nullptr, c->stream));
+    CK(cudaMemcpyAsync(y, c->dy.p, yb, cudaMemcpyDeviceToHost, c->stream));
+    if (acc) CK(cudaMemcpyAsync(acc, c->acc32.p, yb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S) {
+    return mat_apply_host(w, y, nullptr, x, S);
+}
+
+extern "C" int moty_cuda_mat_apply_acc(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
+    if (w && w->fmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_acc: MOTY_WF_I8 only");
+    return mat_apply_host(w, y, acc, x, S);
+}
+
+static int first_device() {
+    for (int i = 0; i < g_nctx; i++) if (g_ctx[i].ready) return g_ctx[i].dev;
+    return -1;
+}
+
+extern "C" int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale, int S, int I, int O) {
+    int dev = first_device();
+    if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
+    MotyCudaMat *m = nullptr;
+    CKR(moty_cuda_upload_mat(&m, MOTY_WF_I8, q, scale, O, I, dev));
+    int r = moty_cuda_mat_apply(m, y, x, S);
+    moty_cuda_free_mat(m);
+    return r;
+}
+
+extern "C" int moty_cuda_matmul_q4r4_s(float *y, const float *x, const uint8_t *q4, const uint16_t *s16, int S, int I, int O) {
+    int dev = first_device();
+    if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
+    MotyCudaMat *m = nullptr;
+    CKR(moty_cuda_upload_mat(&m, MOTY_WF_Q4R4, q4, s16, O, I, dev));
+    int r = moty_cuda_mat_apply(m, y, x, S);
+    moty_cuda_free_mat(m);
+    return r;
+}
+
+// ---------------------------------------------------------------------------
+// kernels of the hw.h contract
+// ---------------------------------------------------------------------------
+static int ctx0(DevCtx **c) {
+    int dev = first_device();
+    if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
+    *c = moty_ctx(dev);
+    CK(cudaSetDevice(dev));
+    return 0;
+}
+
+extern "C" int moty_cuda_qrow_i8_dev(const float *x_dev, int8_t *q_dev, float *scale_dev, int rows, int n, void *stream) {
+    DevCtx *c; CKR(ctx0(&c));
+    return launch_qrow_i8(x_dev, q_dev, scale_dev, rows, n, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (rows <= 0 || n <= 0) return 0;
+    size_t nb = (size_t)rows * n;
+    CKR(moty_grow(c, &c->dx, nb * 4));
+    CKR(moty_grow(c, &c->xi, nb + 16));
+    CKR(moty_grow(c, &c->sx, (size_t)rows * 4));
+    CK(cudaMemcpyAsync(c->dx.p, x, nb * 4, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_qrow_i8((const float *)c->dx.p, (int8_t *)c->xi.p, (float *)c->sx.p, rows, n, c->stream));
+    CK(cudaMemcpyAsync(q, c->xi.p, nb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(scale, c->sx.p, (size_t)rows * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_quant_g32_dev(const float *x_dev, int rows, int I, int8_t *xq_dev, float *xs_dev,
+                                       int32_t *xsum_dev, void *stream) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "quant_g32: I=%d", I);
+    return launch_quant_g32(x_dev, rows, I, xq_dev, xs_dev, xsum_dev, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_quant_g32(const float *x, int rows, int I, int8_t *xq, float *xs, int32_t *xsum) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (I % 32 || I <= 0) return moty_set_error(MOTY_CUDA_EARG, "quant_g32: I=%d", I);
+    if (rows <= 0) return 0;
+    size_t n = (size_t)rows * I, ng = (size_t)rows * (I / 32);
+    CKR(moty_grow(c, &c->dx, n * 4));
+    CKR(moty_grow(c, &c->xi, n + 16));
+    CKR(moty_grow(c, &c->xs, ng * 4));
+    CKR(moty_grow(c, &c->xsum, ng * 4));
+    CK(cudaMemcpyAsync(c->dx.p, x, n * 4, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_quant_g32((const float *)c->dx.p, rows, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, c->stream));
+    CK(cudaMemcpyAsync(xq, c->xi.p, n, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(xs, c->xs.p, ng * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(xsum, c->xsum.p, ng * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+static int dot_rows_host(const void *w, size_t wbytes, const int8_t *x, int nrows, int n, int32_t *out, int i4) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (nrows <= 0) return 0;
+    if (n < 0) return moty_set_error(MOTY_CUDA_EARG, "dot: n=%d", n);
+    CKR(moty_grow(c, &c->dx, wbytes + 16));
+    CKR(moty_grow(c, &c->xi, (size_t)n + 16));
+    CKR(moty_grow(c, &c->acc32, (size_t)nrows * 4));
+    if (wbytes) CK(cudaMemcpyAsync(c->dx.p, w, wbytes, cudaMemcpyHostToDevice, c->stream));
+    if (n) CK(cudaMemcpyAsync(c->xi.p, x, n, cudaMemcpyHostToDevice, c->stream));
+    if (i4) CKR(launch_dot_i4i8_rows((const uint8_t *)c->dx.p, (const int8_t *)c->xi.p, nrows, n, (int32_t *)c->acc32.p, c->stream));
+    else CKR(launch_dot_i8i8_rows((const int8_t *)c->dx.p, (const int8_t *)c->xi.p, nrows, n, (int32_t *)c->acc32.p, c->stream));
+    CK(cudaMemcpyAsync(out, c->acc32.p, (size_t)nrows * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_dot_i8i8(const int8_t *w, const int8_t *x, int nrows, int n, int32_t *out) {
+    return dot_rows_host(w, (size_t)nrows * n, x, nrows, n, out, 0);
+}
+
+extern "C" int moty_cuda_dot_i4i8(const uint8_t *w4, const int8_t *x, int nrows, int n, int32_t *out) {
+    return dot_rows_host(w4, (size_t)nrows * ((n + 1) / 2), x, nrows, n, out, 1);
+}
+
+// ---------------------------------------------------------------------------
+// router
+// ---------------------------------------------------------------------------
+static int route_host(const float *in, int rows, int E, int K, int *idx, float *w, float *probs_out, int softmax, int norm) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (rows <= 0) return 0;
+    size_t lb = (size_t)rows * E * 4, kb = (size_t)rows * K * 4;
+    CKR(moty_grow(c, &c->dlogits, lb));
+    CKR(moty_grow(c, &c->daux, lb + 2 * kb));
+    float *probs = (float *)c->daux.p;
+    int *didx = (int *)((char *)c->daux.p + lb);
+    float *dw = (float *)((char *)c->daux.p + lb + kb);
+    CK(cudaMemcpyAsync(c->dlogits.p, in, lb, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_route((const float *)c->dlogits.p, rows, E, K, didx, dw, probs_out ? probs : nullptr, softmax, norm, c->stream));
+    CK(cudaMemcpyAsync(idx, didx, kb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(w, dw, kb, cudaMemcpyDeviceToHost, c->stream));
+    if (probs_out) CK(cudaMemcpyAsync(probs_out, probs, lb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_topk(const float *probs, int rows, int E, int K, int *idx, float *w, int norm_topk) {
+    return route_host(probs, rows, E, K, idx, w, nullptr, 0, norm_topk);
+}
+
+extern "C" int moty_cuda_route_topk(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs_out) {
+    return route_host(logits, rows, E, K, idx, w, probs_out, 1, 1);
+}
+
+extern "C" int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E, int K, int *idx_dev, float *w_dev,
+                                        float *probs_dev, int norm_topk, void *stream) {
+    DevCtx *c; CKR(ctx0(&c));
+    return launch_route(logits_dev, rows, E, K, idx_dev, w_dev, probs_dev, 1, norm_topk, pick_stream(c, stream));
+}
+
+// ---------------------------------------------------------------------------
+// greedy token
+// ---------------------------------------------------------------------------
+extern "C" int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream) {
+    DevCtx *c; CKR(ctx0(&c));
+    CKR(moty_grow(c, &c->daux, 4096));
+    return launch_argmax_scratch(v_dev, n, out_dev, (float *)c->daux.p, (int *)((char *)c->daux.p + 1024),
+                                 pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_argmax(const float *v, int n, int *out) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (n <= 0 || !v || !out) return moty_set_error(MOTY_CUDA_EARG, "argmax: n=%d", n);
+    CKR(moty_grow(c, &c->dx, (size_t)n * 4));
+    CKR(moty_grow(c, &c->daux, 4096));
+    CK(cudaMemcpyAsync(c->dx.p, v, (size_t)n * 4, cudaMemcpyHostToDevice, c->stream));
+    int *dout = (int *)((char *)c->daux.p + 2048);
+    CKR(launch_argmax_scratch((const float *)c->dx.p, n, dout, (float *)c->daux.p, (int *)((char *)c->daux.p + 1024), c->stream));
+    CK(cudaMemcpyAsync(out, dout, 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// load-time quantizers
+// ---------------------------------------------------------------------------
+extern "C" int moty_cuda_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (O <= 0 || I <= 0) return moty_set_error(MOTY_CUDA_EARG, "quantize_rows: %dx%d", O, I);
+    size_t n = (size_t)O * I;
+    CKR(moty_grow(c, &c->dx, n * 4));
+    CKR(moty_grow(c, &c->dy, n + 16));
+    CKR(moty_grow(c, &c->sx, (size_t)O * 4));
+    CK(cudaMemcpyAsync(c->dx.p, w, n * 4, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_quantize_rows((const float *)c->dx.p, (int8_t *)c->dy.p, (float *)c->sx.p, O, I, c->stream));
+    CK(cudaMemcpyAsync(q, c->dy.p, n, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(scale, c->sx.p, (size_t)O * 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16) {
+    DevCtx *c; CKR(ctx0(&c));
+    if (O <= 0 || I <= 0 || I % 32) return moty_set_error(MOTY_CUDA_EARG, "pack_q4r4: %dx%d", O, I);
+    size_t n = (size_t)O * I, cb, sb;
+    CKR(mat_sizes(MOTY_WF_Q4R4, O, I, &cb, &sb));
+    CKR(moty_grow(c, &c->dx, n * 4));
+    CKR(moty_grow(c, &c->dy, cb + 16));
+    CKR(moty_grow(c, &c->daux, sb + 16));
+    CK(cudaMemcpyAsync(c->dx.p, w, n * 4, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_pack_q4r4((const float *)c->dx.p, O, I, (uint8_t *)c->dy.p, (uint16_t *)c->daux.p, c->stream));
+    CK(cudaMemcpyAsync(q4, c->dy.p, cb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaMemcpyAsync(s16, c->daux.p, sb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// dense FFN
+// ---------------------------------------------------------------------------
+static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
+                  float *out, const float *x, int S, cudaStream_t st) {
+    int I = gate->O, D = gate->I;
+    if (up->O != I || up->I != D || down->O != D || down->I != I)
+        return moty_set_error(MOTY_CUDA_EARG, "ffn: shapes gate %dx%d up %dx%d down %dx%d", gate->O, gate->I, up->O, up->I, down->O, down->I);
+    if (gate->device != up->device || gate->device != down->device) return moty_set_error(MOTY_CUDA_EARG, "ffn: matrices on different devices");
+    if (act != MOTY_ACT_SILU && act != MOTY_ACT_GELU_TANH) return moty_set_error(MOTY_CUDA_EARG, "ffn: activation %d", act);
+    size_t hb = (size_t)S * I * 4;
+    CKR(moty_grow(c, &c->g, hb));
+    CKR(moty_grow(c, &c->u, hb));
+    CKR(mat_apply_on(c, gate, (float *)c->g.p, x, S, nullptr, st));
+    CKR(mat_apply_on(c, up, (float *)c->u.p, x, S, nullptr, st));
+    CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)S * I, act, st));
+    return mat_apply_on(c, down, out, (const float *)c->g.p, S, nullptr, st);
+}
+
+extern "C" int moty_cuda_ffn_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
+                                 float *out_dev, const float *x_dev, int S, void *stream) {
+    if (!gate || !up || !down || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "ffn_dev: null argument");
+    DevCtx *c = moty_ctx(gate->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", gate->device);
+    CK(cudaSetDevice(gate->device));
+    if (S <= 0) return 0;
+    return ffn_on(c, gate, up, down, act, out_dev, x_dev, S, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_ffn(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
+                             float *out, const float *x, int S) {
+    if (!gate || !up || !down || !out || !x) return moty_set_error(MOTY_CUDA_EARG, "ffn: null argument");
+    DevCtx *c = moty_ctx(gate->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", gate->device);
+    CK(cudaSetDevice(gate->device));
+    if (S <= 0) return 0;
+    size_t xb = (size_t)S * gate->I * 4;
+    CKR(moty_grow(c, &c->dx, xb));
+    CKR(moty_grow(c, &c->dy, xb));
+    CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
+    CKR(ffn_on(c, gate, up, down, act, (float *)c->dy.p, (const float *)c->dx.p, S, c->stream));
+    CK(cudaMemcpyAsync(out, c->dy.p, xb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// MoE layer
+// ---------------------------------------------------------------------------
+struct MotyCudaMoe {
+    int E, K, I, D, efmt, e_lo, e_hi, device;
+    void *g, *u, *d;             // code slabs [e_hi - e_lo][...]
+    void *gs, *us, *ds;          // scale slabs
+    size_t gcb, gsb, dcb, dsb;   // bytes per expert: gate/up codes, gate/up scales, down codes, down scales
+    MotyCudaMat *router;
+    // plan buffers (device), sized for capS tokens
+    int capS;
+    int *idx, *pair_tok, *pos_of, *ord, *counters;
+    float *w;
+    uint8_t *form;
+    void *t_gate, *t_up, *t_down;
+    float *logits;
+};
+
+extern "C" int moty_cuda_moe_create(MotyCudaMoe **out, int E, int K, int I, int D, int efmt,
+                                    int e_lo, int e_hi, int device) {
+    if (!out) return moty_set_error(MOTY_CUDA_EARG, "moe_create: null");
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    if (E <= 0 || E > 4096 || K <= 0 || K > 64 || K > E || I <= 0 || D <= 0 || e_lo < 0 || e_hi > E || e_lo >= e_hi)
+        return moty_set_error(MOTY_CUDA_EARG, "moe_create: E=%d K=%d I=%d D=%d experts [%d,%d)", E, K, I, D, e_lo, e_hi);
+    if (efmt != MOTY_WF_I8 && efmt != MOTY_WF_Q4R4) return moty_set_error(MOTY_CUDA_EARG, "moe_create: expert format %d", efmt);
+    if (efmt == MOTY_WF_I8 && (I % 16 || D % 16)) return moty_set_error(MOTY_CUDA_EARG, "moe_create: int8 experts need I, D %% 16 == 0");
+    if (efmt == MOTY_WF_Q4R4 && (I % 32 || D % 32)) return moty_set_error(MOTY_CUDA_EARG, "moe_create: Q4R4 experts need I, D %% 32 == 0");
+    if (I > MOTY_QROW_MAX || D > MOTY_QROW_MAX) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_create: width above %d", MOTY_QROW_MAX);
+    CK(cudaSetDevice(device));
+    MotyCudaMoe *m = new (std::nothrow) MotyCudaMoe();
+    if (!m) return moty_set_error(MOTY_CUDA_ENOMEM, "moe_create: host allocation");
+    memset(m, 0, sizeof *m);
+    m->E = E; m->K = K; m->I = I; m->D = D; m->efmt = efmt; m->e_lo = e_lo; m->e_hi = e_hi; m->device = device;
+    CKR(mat_sizes(efmt, I, D, &m->gcb, &m->gsb));
+    CKR(mat_sizes(efmt, D, I, &m->dcb, &m->dsb));
+    size_t n = (size_t)(e_hi - e_lo);
+    cudaError_t e = cudaMalloc(&m->g, n * m->gcb + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&m->u, n * m->gcb + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&m->d, n * m->dcb + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&m->gs, n * m->gsb + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&m->us, n * m->gsb + 256);
+    if (e == cudaSuccess) e = cudaMalloc(&m->ds, n * m->dsb + 256);
+    if (e != cudaSuccess) { moty_cuda_moe_free(m); return moty_set_error(MOTY_CUDA_ENOMEM, "moe_create: %s", cudaGetErrorString(e)); }
+    *out = m;
+    return 0;
+}
+
+static void moe_free_plan(MotyCudaMoe *m) {
+    void *ps[] = {m->idx, m->pair_tok, m->pos_of, m->ord, m->counters, m->w, m->form, m->t_gate, m->t_up, m->t_down, m->logits};
+    for (void *p : ps) if (p) cudaFree(p);
+    m->idx = m->pair_tok = m->pos_of = m->ord = m->counters = nullptr; m->w = nullptr; m->form = nullptr;
+    m->t_gate = m->t_up = m->t_down = nullptr; m->logits = nullptr; m->capS = 0;
+}
+
+extern "C" int moty_cuda_moe_free(MotyCudaMoe *m) {
+    if (!m) return 0;
+    DevCtx *c = moty_ctx(m->device);
+    if (c) { cudaSetDevice(m->device); cudaStreamSynchronize(c->stream); }
+    void *ps[] = {m->g, m->u, m->d, m->gs, m->us, m->ds};
+    for (void *p : ps) if (p) cudaFree(p);
+    moe_free_plan(m);
+    delete m;
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *g, const void *gs,
+                                           const void *u, const void *us, const void *d, const void *ds) {
+    if (!m || !g || !gs || !u || !us || !d || !ds) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert: null argument");
+    if (eid < m->e_lo || eid >= m->e_hi) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert: expert %d outside [%d,%d)", eid, m->e_lo, m->e_hi);
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    CK(cudaSetDevice(m->device));
+    size_t le = (size_t)(eid - m->e_lo);
+    CK(cudaMemcpyAsync((char *)m->g + le * m->gcb, g, m->gcb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->u + le * m->gcb, u, m->gcb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->d + le * m->dcb, d, m->dcb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->gs + le * m->gsb, gs, m->gsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->us + le * m->gsb, us, m->gsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->ds + le * m->dsb, ds, m->dsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router) {
+    if (!m) return moty_set_error(MOTY_CUDA_EARG, "moe_set_router: null");
+    if (router && (router->O != m->E || router->I != m->D || router->device != m->device))
+        return moty_set_error(MOTY_CUDA_EARG, "moe_set_router: router %dx%d on device %d", router->O, router->I, router->device);
+    m->router = router;
+    return 0;
+}
+
+static int moe_ensure_plan(MotyCudaMoe *m, int S) {
+    if (S <= m->capS) return 0;
+    DevCtx *c = moty_ctx(m->device);
+    CK(cudaStreamSynchronize(c->stream));
+    moe_free_plan(m);
+    int cap = S + S / 4 + 8;
+    size_t SK = (size_t)cap * m->K;
+    size_t ntile = SK + (size_t)(m->e_hi - m->e_lo);      // loose bound: one row per tile
+    size_t tsz = m->efmt == MOTY_WF_I8 ? sizeof(Q8Tile) : sizeof(Q4Tile);
+    CK(cudaMalloc(&m->idx, SK * 4)); CK(cudaMalloc(&m->pair_tok, SK * 4)); CK(cudaMalloc(&m->pos_of, SK * 4));
+    CK(cudaMalloc(&m->ord, SK * 4)); CK(cudaMalloc(&m->counters, 64)); CK(cudaMalloc(&m->w, SK * 4));
+    CK(cudaMalloc(&m->form, SK + 16));
+    CK(cudaMalloc(&m->t_gate, ntile * tsz)); CK(cudaMalloc(&m->t_up, ntile * tsz)); CK(cudaMalloc(&m->t_down, ntile * tsz));
+    CK(cudaMalloc(&m->logits, (size_t)cap * m->E * 4));
+    m->capS = cap;
+    return 0;
+}
+
+static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, int S, const float *logits,
+                        int order, int norm_topk, int *idx_out, float *w_out, cudaStream_t st) {
+    const int E = m->E, K = m->K, I = m->I, D = m->D;
+    const bool q8 = m->efmt == MOTY_WF_I8;
+    const int T = q8 ? 8 : 4;
+    CKR(moe_ensure_plan(m, S));
+    if (!logits) {
+        if (!m->router) return moty_set_error(MOTY_CUDA_EARG, "moe: neither logits nor a router matrix");
+        CKR(mat_apply_on(c, m->router, m->logits, x, S, nullptr, st));
+        logits = m->logits;
+    }
+    CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
+    size_t P = (size_t)S * K;                                 // upper bound on local (token, expert) pairs
+    int ntiles_max = (int)((P + T - 1) / T) + (m->e_hi - m->e_lo);
+    if ((size_t)ntiles_max > P + (size_t)(m->e_hi - m->e_lo)) ntiles_max = (int)(P + (size_t)(m->e_hi - m->e_lo));
+    if (ntiles_max > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "moe: %d tiles in one call; split the batch", ntiles_max);
+    MoePlanArgs pa; memset(&pa, 0, sizeof pa);
+    pa.idx = m->idx; pa.S = S; pa.K = K; pa.E = E; pa.e_lo = m->e_lo; pa.e_hi = m->e_hi; pa.T = T; pa.order = order; pa.q8 = q8;
+    if (q8) {
+        pa.g8 = (const int8_t *)m->g; pa.u8 = (const int8_t *)m->u; pa.d8 = (const int8_t *)m->d;
+        pa.gs = (const float *)m->gs; pa.us = (const float *)m->us; pa.ds = (const float *)m->ds;
+        pa.gstride = m->gcb; pa.gsstride = m->gsb / 4; pa.dstride = m->dcb; pa.dsstride = m->dsb / 4;
+        pa.t8_gate = (Q8Tile *)m->t_gate; pa.t8_up = (Q8Tile *)m->t_up; pa.t8_down = (Q8Tile *)m->t_down;
+    } else {
+        pa.g4 = (const uint8_t *)m->g; pa.u4 = (const uint8_t *)m->u; pa.d4 = (const uint8_t *)m->d;
+        pa.gs16 = (const uint16_t *)m->gs; pa.us16 = (const uint16_t *)m->us; pa.ds16 = (const uint16_t *)m->ds;
+        pa.gstride = m->gcb; pa.gsstride = m->gsb / 2; pa.dstride = m->dcb; pa.dsstride = m->dsb / 2;
+        pa.t4_gate = (Q4Tile *)m->t_gate; pa.t4_up = (Q4Tile *)m->t_up; pa.t4_down = (Q4Tile *)m->t_down;
+        pa.form = m->form;
+    }
+    pa.pair_tok = m->pair_tok; pa.pos_of = m->pos_of; pa.ord = m->ord;
+    pa.ntiles = m->counters; pa.npairs = m->counters + 1;
+    CKR(launch_moe_plan(pa, st));
+
+    // activations of the two halves: [P][I] each, then the down outputs [P][D]
+    CKR(moty_grow(c, &c->g, P * I * 4));
+    CKR(moty_grow(c, &c->u, P * I * 4));
+    CKR(moty_grow(c, &c->h, P * D * 4));
+    // rows the plan leaves unused (non-local experts) must not feed NaNs to the quantizers
+    CK(cudaMemsetAsync(c->g.p, 0, P * I * 4, st));
+    CK(cudaMemsetAsync(c->u.p, 0, P * I * 4, st));
+    if (q8) {
+        CKR(moty_grow(c, &c->xi, (size_t)S * D + 16));
+        CKR(moty_grow(c, &c->sx, (size_t)S * 4));
+        CKR(moty_grow(c, &c->hq, P * I + 16));
+        CKR(moty_grow(c, &c->hs, P * 4));
+        CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, D, st));
+        Q8Args a; memset(&a, 0, sizeof a);
+        a.ntiles_dev = m->counters; a.ntiles_max = ntiles_max;
+        a.xi = (const int8_t *)c->xi.p; a.sx = (const float *)c->sx.p; a.xmap = m->pair_tok;
+        a.ldy = I; a.S = (int)P; a.I = D; a.O = I;
+        a.tiles = (const Q8Tile *)m->t_gate; a.y = (float *)c->g.p;
+        CKR(launch_q8_small(a, c->sms, st));
+        a.tiles = (const Q8Tile *)m->t_up; a.y = (float *)c->u.p;
+        CKR(launch_q8_small(a, c->sms, st));
+        CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
+        CKR(launch_qrow_i8((const float *)c->g.p, (int8_t *)c->hq.p, (float *)c->hs.p, (int)P, I, st));
+        Q8Args b; memset(&b, 0, sizeof b);
+        b.ntiles_dev = m->counters; b.ntiles_max = ntiles_max;
+        b.xi = (const int8_t *)c->hq.p; b.sx = (const float *)c->hs.p;
+        b.ldy = D; b.S = (int)P; b.I = I; b.O = D;
+        b.tiles = (const Q8Tile *)m->t_down; b.y = (float *)c->h.p;
+        CKR(launch_q8_small(b, c->sms, st));
+    } else {
+        int nbD = D / 32, nbI = I / 32;
+        CKR(moty_grow(c, &c->xi, (size_t)S * D + 16));
+        CKR(moty_grow(c, &c->xs, (size_t)S * nbD * 4));
+        CKR(moty_grow(c, &c->xsum, (size_t)S * nbD * 4));
+        CKR(moty_grow(c, &c->hq, P * I + 16));
+        CKR(moty_grow(c, &c->hxs, P * nbI * 4));
+        CKR(moty_grow(c, &c->hxsum, P * nbI * 4));
+        CKR(launch_quant_g32(x, S, D, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
+        Q4Args a; memset(&a, 0, sizeof a);
+        a.ntiles_dev = m->counters; a.ntiles_max = ntiles_max;
+        a.xq = (const int8_t *)c->xi.p; a.xs = (const float *)c->xs.p; a.xsum = (const int32_t *)c->xsum.p;
+        a.xmap = m->pair_tok; a.form = m->form;
+        a.ldy = I; a.S = (int)P; a.I = D; a.O = I;
+        a.tiles = (const Q4Tile *)m->t_gate; a.y = (float *)c->g.p;
+        CKR(launch_q4r4_small(a, c->sms, st));
+        a.tiles = (const Q4Tile *)m->t_up; a.y = (float *)c->u.p;
+        CKR(launch_q4r4_small(a, c->sms, st));
+        CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
+        CKR(launch_quant_g32((const float *)c->g.p, (int)P, I, (int8_t *)c->hq.p, (float *)c->hxs.p, (int32_t *)c->hxsum.p, st));
+        Q4Args b; memset(&b, 0, sizeof b);
+        b.ntiles_dev = m->counters; b.ntiles_max = ntiles_max;
+        b.xq = (const int8_t *)c->hq.p; b.xs = (const float *)c->hxs.p; b.xsum = (const int32_t *)c->hxsum.p;
+        b.form = m->form;
+        b.ldy = D; b.S = (int)P; b.I = I; b.O = D;
+        b.tiles = (const Q4Tile *)m->t_down; b.y = (float *)c->h.p;
+        CKR(launch_q4r4_small(b, c->sms, st));
+    }
+    CKR(launch_moe_combine(out, (const float *)c->h.p, m->w, m->pos_of, m->ord, S, K, D, st));
+    if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, P * 4, cudaMemcpyDeviceToDevice, st));
+    if (w_out) CK(cudaMemcpyAsync(w_out, m->w, P * 4, cudaMemcpyDeviceToDevice, st));
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, int S,
+                                       const float *logits_dev, int order, int norm_topk,
+                                       int *idx_dev, float *w_dev, void *stream) {
+    if (!m || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_apply_dev: null argument");
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    CK(cudaSetDevice(m->device));
+    if (S <= 0) return 0;
+    return moe_apply_on(c, m, out_dev, x_dev, S, logits_dev, order, norm_topk, idx_dev, w_dev, pick_stream(c, stream));
+}
+
+static int moe_host(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits, int order, int norm) {
+    if (!m || !out || !x) return moty_set_error(MOTY_CUDA_EARG, "moe: null argument");
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    CK(cudaSetDevice(m->device));
+    if (S <= 0) return 0;
+    size_t xb = (size_t)S * m->D * 4, lb = (size_t)S * m->E * 4;
+    CKR(moty_grow(c, &c->dx, xb));
+    CKR(moty_grow(c, &c->dy, xb));
+    CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
+    const float *dl = nullptr;
+    if (logits) {
+        CKR(moty_grow(c, &c->dlogits, lb));
+        CK(cudaMemcpyAsync(c->dlogits.p, logits, lb, cudaMemcpyHostToDevice, c->stream));
+        dl = (const float *)c->dlogits.p;
+    }
+    CKR(moe_apply_on(c, m, (float *)c->dy.p, (const float *)c->dx.p, S, dl, order, norm, nullptr, nullptr, c->stream));
+    CK(cudaMemcpyAsync(out, c->dy.p, xb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_d1(MotyCudaMoe *m, float *out, const float *x, const float *logits) {
+    return moe_host(m, out, x, 1, logits, 0, 1);
+}
+
+extern "C" int moty_cuda_moe_batch(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits) {
+    return moe_host(m, out, x, S, logits, 1, 1);
+}
+
+extern "C" int moty_cuda_olmoe_moe(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits, int norm_topk) {
+    return moe_host(m, out, x, S, logits, 0, norm_topk);
+}

@@ -1,0 +1,77 @@
+// kernels.cuh -- launchers of the device kernels (all enqueue on `st`, none synchronise).
+#pragma once
+#include "common.cuh"
+
+// ---- quant.cu ---------------------------------------------------------------
+int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cudaStream_t st);
+int launch_quant_g32(const float *x, int rows, int I, int8_t *xq, float *xs, int32_t *xsum, cudaStream_t st);
+int launch_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I, cudaStream_t st);
+int launch_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16, cudaStream_t st);
+
+// ---- gemv_q8.cu ---------------------------------------------------------------
+// One Q8_0 product over pre-quantized activation rows:
+//   y[yrow(t)][o] = (scale[o] * sx[xrow(t)]) * (float)dot(W[o], xi[xrow(t)])
+// A "tile" is up to 8 activation rows that share one weight matrix.  The dense
+// drivers use identity row maps and a single matrix; the MoE block passes a tile
+// table so that every tile can point at another expert's matrix.
+struct Q8Tile {
+    const int8_t *w;        // [O][I]
+    const float *scale;     // [O]
+    int row0;               // first entry of xmap/ymap (or first row when maps are null)
+    int nrows;              // 1..8
+};
+struct Q8Args {
+    const int8_t *w; const float *scale;        // dense: the one matrix
+    const Q8Tile *tiles; const int *ntiles_dev;  // grouped: tile table (+ device count), else null
+    int ntiles_max;
+    const int8_t *xi; const float *sx;          // quantized activation rows [..][I], scales
+    const int *xmap, *ymap;                     // optional gather / scatter row maps
+    float *y; int ldy;                          // output rows, leading dimension
+    int32_t *acc;                               // optional int32 accumulators, same indexing as y
+    int S, I, O;
+};
+int launch_q8_small(const Q8Args &a, int sms, cudaStream_t st);
+// S = 1 with the activation quantizer fused in (x is f32; xi/sx unused)
+int launch_q8_gemv_fused(const float *x, const int8_t *w, const float *scale, float *y, int32_t *acc,
+                         int I, int O, int sms, cudaStream_t st);
+int launch_dot_i8i8_rows(const int8_t *w, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
+int launch_dot_i4i8_rows(const uint8_t *w4, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
+// per-row int4 weights (WF_I4) against int8 rows, same epilogue as Q8_0
+int launch_i4_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx,
+                   float *y, int S, int I, int O, cudaStream_t st);
+
+int launch_q8_any(const int8_t *W, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
+                  int S, int I, int O, cudaStream_t st);
+int gemv_q8_init_device();
+int q4r4_init_device();
+
+// ---- gemm_q8_tc.cu --------------------------------------------------------------
+// tcgen05 int8 GEMM for S >= 16: weights through a TMA descriptor, int32
+// accumulators in TMEM, epilogue (scale[o]*sx[s])*(float)acc.
+bool q8_tc_supported(int S, int I, int O);
+int q8_tc_make_tmap(MotyCudaMat *m);
+int launch_q8_tc(const MotyCudaMat *w, const int8_t *xi, const float *sx, float *y, int32_t *acc,
+                 int S, DevCtx *c, cudaStream_t st);
+
+// ---- q4r4.cu ----------------------------------------------------------------------
+struct Q4Tile { const uint8_t *w; const uint16_t *d; int row0; int nrows; };
+struct Q4Args {
+    const uint8_t *w; const uint16_t *d;
+    const Q4Tile *tiles; const int *ntiles_dev; int ntiles_max;
+    const int8_t *xq; const float *xs; const int32_t *xsum;   // group-quantized rows
+    const int *xmap, *ymap;
+    const uint8_t *form;     // per activation row: 1 = 4-token-tile formula, 0 = token-by-token
+    float *y; int ldy;
+    int S, I, O;
+};
+int launch_q4r4_small(const Q4Args &a, int sms, cudaStream_t st);
+// which of the reference's two kernels each of S tokens goes through
+int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
+
+// ---- router.cu ----------------------------------------------------------------------
+int launch_route(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs,
+                 int do_softmax, int norm_topk, cudaStream_t st);
+int launch_argmax_scratch(const float *v, int n, int *out, float *pv, int *pi, cudaStream_t st);
+
+// ---- moe.cu / ffn -------------------------------------------------------------------
+int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st);

@@ -1,0 +1,184 @@
+// moe.cu -- device-side pieces of the FFN and MoE blocks: activation*up, the
+// routing plan (token lists per expert and tile tables for the grouped
+// products), the ordered weighted combine, and the f32 router GEMV.
+#include "kernels.cuh"
+#include "moe.cuh"
+
+// ---------------------------------------------------------------------------
+// g = act(g) * u.  SiLU: v / (1 + exp(-v)) (hw/hw_ops.h:19-21); tanh-GeLU:
+// 0.5 v (1 + tanh(0.79788456 (v + 0.044715 v^3))) (engines/gemma.c:389-391).
+// exp/tanh are evaluated in f64 and rounded once; the surrounding f32 steps are
+// spelled out so that nothing is fused or reassociated.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) act_mul_kernel(float *__restrict__ g, const float *__restrict__ u, long long n, int act) {
+    long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    float v = g[i], t;
+    if (act == MOTY_ACT_SILU) {
+        float e = (float)exp((double)(-v));
+        t = __fdiv_rn(v, __fadd_rn(1.f, e));
+    } else {
+        // v + 0.044715 v v v: the CPU build fuses the last multiply with the add
+        float inner = __fmul_rn(0.7978845608028654f, fmaf(__fmul_rn(__fmul_rn(0.044715f, v), v), v, v));
+        float th = (float)tanh((double)inner);
+        t = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, th));
+    }
+    g[i] = __fmul_rn(t, u[i]);
+}
+
+int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st) {
+    if (n <= 0) return 0;
+    act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, n, act);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Routing plan.  Input: idx [S][K] (expert of every selection).  One CTA.
+//   cnt/off per local expert, pairs sorted by (expert, token):
+//     pair_tok[p]  token of position p          (gather map of the gate/up product)
+//     pos_of[s*K+k] position of selection (s,k), -1 when its expert is not local
+//   tile tables for the grouped products (tile = up to T positions of one expert)
+//   ord[s*K + j]: the token's selections in combine order
+//   form[p]: which of the two Q4R4 kernels the reference would use for that row
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
+    extern __shared__ int sh[];
+    int *cnt = sh, *off = sh + a.E;                      // [E] each
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int SK = a.S * a.K;
+    for (int e = tid; e < a.E; e += 1024) cnt[e] = 0;
+    __syncthreads();
+    // pass 1: counts (a token never selects the same expert twice)
+    for (int e = a.e_lo + warp; e < a.e_hi; e += 32) {
+        int c = 0;
+        for (int i = lane; i < SK; i += 32) c += (a.idx[i] == e);
+        c = warp_sum_i32(c);
+        if (lane == 0) cnt[e] = c;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int run = 0, nt = 0;
+        for (int e = 0; e < a.E; e++) {
+            off[e] = run;
+            int c = cnt[e];
+            for (int r0 = 0; r0 < c; r0 += a.T) {
+                int nr = c - r0 < a.T ? c - r0 : a.T;
+                int le = e - a.e_lo;
+                if (a.q8) {
+                    a.t8_gate[nt] = Q8Tile{a.g8 + (size_t)le * a.gstride, a.gs + (size_t)le * a.gsstride, run + r0, nr};
+                    a.t8_up[nt]   = Q8Tile{a.u8 + (size_t)le * a.gstride, a.us + (size_t)le * a.gsstride, run + r0, nr};
+                    a.t8_down[nt] = Q8Tile{a.d8 + (size_t)le * a.dstride, a.ds + (size_t)le * a.dsstride, run + r0, nr};
+                } else {
+                    a.t4_gate[nt] = Q4Tile{a.g4 + (size_t)le * a.gstride, a.gs16 + (size_t)le * a.gsstride, run + r0, nr};
+                    a.t4_up[nt]   = Q4Tile{a.u4 + (size_t)le * a.gstride, a.us16 + (size_t)le * a.gsstride, run + r0, nr};
+                    a.t4_down[nt] = Q4Tile{a.d4 + (size_t)le * a.dstride, a.ds16 + (size_t)le * a.dsstride, run + r0, nr};
+                }
+                nt++;
+            }
+            run += c;
+        }
+        *a.ntiles = nt;
+        *a.npairs = run;
+    }
+    __syncthreads();
+    // pass 2: positions, tokens ascending inside an expert
+    for (int e = a.e_lo + warp; e < a.e_hi; e += 32) {
+        int base = off[e], c = cnt[e];
+        for (int i0 = 0; i0 < SK; i0 += 32) {
+            int i = i0 + lane;
+            bool hit = i < SK && a.idx[i] == e;
+            unsigned m = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                int p = base + __popc(m & ((1u << lane) - 1u));
+                a.pair_tok[p] = i / a.K;
+                a.pos_of[i] = p;
+                if (a.form) {
+                    int t = p - off[e];                  // row inside this expert's gathered batch
+                    int t0 = t / 32 * 32, ns = c - t0 < 32 ? c - t0 : 32;
+                    a.form[p] = (t - t0) < ns / 4 * 4 ? 1 : 0;
+                }
+            }
+            base += __popc(m);
+        }
+    }
+    // selections of non-local experts
+    for (int i = tid; i < SK; i += 1024) {
+        int e = a.idx[i];
+        if (e < a.e_lo || e >= a.e_hi) a.pos_of[i] = -1;
+    }
+    // combine order per token
+    for (int s = tid; s < a.S; s += 1024) {
+        int *o = a.ord + (size_t)s * a.K;
+        for (int k = 0; k < a.K; k++) o[k] = k;
+        if (a.order == 1) {                              // ascending expert id: insertion sort of <= 64 entries
+            const int *ix = a.idx + (size_t)s * a.K;
+            for (int k = 1; k < a.K; k++) {
+                int v = o[k], j = k - 1;
+                while (j >= 0 && ix[o[j]] > ix[v]) { o[j + 1] = o[j]; j--; }
+                o[j + 1] = v;
+            }
+        }
+    }
+}
+
+int launch_moe_plan(const MoePlanArgs &a, cudaStream_t st) {
+    size_t smem = (size_t)2 * a.E * sizeof(int);
+    moe_plan_kernel<<<1, 1024, smem, st>>>(a);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// out[s][d] = sum over the token's selections, IN ORDER, of w * h[pos][d], each
+// step one fused multiply-add starting from 0 (nn/moe.c:146-149, 200-202,
+// engines/olmoe.c:240).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_combine_kernel(float *__restrict__ out, const float *__restrict__ h,
+                                                          const float *__restrict__ w, const int *__restrict__ pos_of,
+                                                          const int *__restrict__ ord, int S, int K, int D) {
+    int s = blockIdx.y;
+    int d = blockIdx.x * 256 + threadIdx.x;
+    if (d >= D) return;
+    float acc = 0.f;
+    for (int j = 0; j < K; j++) {
+        int k = ord[(size_t)s * K + j];
+        int p = pos_of[(size_t)s * K + k];
+        if (p >= 0) acc = fmaf(w[(size_t)s * K + k], h[(size_t)p * D + d], acc);
+    }
+    out[(size_t)s * D + d] = acc;
+}
+
+int launch_moe_combine(float *out, const float *h, const float *w, const int *pos_of, const int *ord,
+                       int S, int K, int D, cudaStream_t st) {
+    if (S <= 0) return 0;
+    dim3 grid((D + 255) / 256, S);
+    moe_combine_kernel<<<grid, 256, 0, st>>>(out, h, w, pos_of, ord, S, K, D);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
+// f32 matrix (router of an engine that keeps it unquantized): one warp per
+// output row, f32 accumulation.  Outside the quantized path; the summation
+// order differs from a CPU SIMD dot, so it is close, not bit-equal.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__ W, const float *__restrict__ x,
+                                                       float *__restrict__ y, int S, int I, int O) {
+    int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (o >= O) return;
+    for (int s = 0; s < S; s++) {
+        float acc = 0.f;
+        for (int i = lane; i < I; i += 32) acc = fmaf(W[(size_t)o * I + i], x[(size_t)s * I + i], acc);
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+        if (lane == 0) y[(size_t)s * O + o] = acc;
+    }
+}
+
+int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st) {
+    if (O <= 0 || S <= 0) return 0;
+    f32_rows_kernel<<<(O + 7) / 8, 256, 0, st>>>(W, x, y, S, I, O);
+    CK(cudaGetLastError());
+    return 0;
+}

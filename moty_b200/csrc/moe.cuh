@@ -1,0 +1,25 @@
+// moe.cuh -- argument blocks shared by moe.cu and the C-ABI layer.
+#pragma once
+#include "kernels.cuh"
+
+struct MoePlanArgs {
+    const int *idx;            // [S][K] routed expert ids
+    int S, K, E, e_lo, e_hi;
+    int T;                     // rows per tile (8 for int8 experts, 4 for Q4R4)
+    int order;                 // 0 selection order, 1 ascending expert id
+    int q8;                    // 1 int8 experts, 0 Q4R4 experts
+    // expert slabs: expert e (local index e - e_lo) starts at base + local * stride
+    const int8_t *g8, *u8, *d8; const float *gs, *us, *ds;
+    const uint8_t *g4, *u4, *d4; const uint16_t *gs16, *us16, *ds16;
+    size_t gstride, gsstride, dstride, dsstride;   // in elements of the respective arrays
+    // outputs
+    int *pair_tok, *pos_of, *ord, *ntiles, *npairs;
+    uint8_t *form;             // Q4R4 only, else null
+    Q8Tile *t8_gate, *t8_up, *t8_down;
+    Q4Tile *t4_gate, *t4_up, *t4_down;
+};
+
+int launch_moe_plan(const MoePlanArgs &a, cudaStream_t st);
+int launch_moe_combine(float *out, const float *h, const float *w, const int *pos_of, const int *ord,
+                       int S, int K, int D, cudaStream_t st);
+int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st);

@@ -1,0 +1,109 @@
+"""GPU parity of the FFN and MoE blocks through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import golden, same_bits
+
+pytestmark = pytest.mark.gpu
+
+# The blocks pass through exp()/tanh(): the GPU rounds them correctly, libm is
+# within one ulp of that.  A one-ulp change before a re-quantization can move an
+# int8 code by one, so blocks are compared at 1e-5 of the output magnitude, and
+# additionally bit for bit whenever the intermediate codes agree.
+TOL = 1e-5
+
+
+def close(a, b, tol=TOL):
+    scale = max(float(np.abs(b).max()), 1e-30)
+    return float(np.abs(a - b).max()) <= tol * scale
+
+
+def test_ffn_q8_and_q4r4(gpu, oracle):
+    g = golden("blocks")
+    G = gpu.Mat.i8(g["gq"], g["gs"]); U = gpu.Mat.i8(g["uq"], g["us"]); Dn = gpu.Mat.i8(g["dq"], g["ds"])
+    G4 = gpu.Mat.q4r4(g["g4"], g["g4s"], 256, 128); U4 = gpu.Mat.q4r4(g["u4"], g["u4s"], 256, 128)
+    D4 = gpu.Mat.q4r4(g["d4"], g["d4s"], 128, 256)
+    for S in (1, 5):
+        x = g[f"ffn_x{S}"]
+        assert close(gpu.dense_ffn(G, U, Dn, x), g[f"ffn8_{S}"], 2e-3)      # one flipped code = 1/127 of one term
+        assert close(gpu.dense_ffn(G4, U4, D4, x), g[f"ffn4_{S}"], 2e-3)
+        y = gpu.dense_ffn(G, U, Dn, x, act=gpu.ACT_GELU_TANH)
+        h = oracle.gelu_mul(oracle.matmul_q_s(x, g["gq"], g["gs"]), oracle.matmul_q_s(x, g["uq"], g["us"]))
+        assert close(y, oracle.matmul_q_s(h, g["dq"], g["ds"]), 2e-3)
+
+
+def _moe_from_golden(gpu, g):
+    E, K, I, D = (int(v) for v in g["moe_dims"])
+    m = gpu.Moe(E, K, I, D)
+    for e in range(E):
+        m.upload_expert(e, g["moe_g"][e], g["moe_gs"][e], g["moe_u"][e], g["moe_us"][e], g["moe_d"][e], g["moe_ds"][e])
+    return m
+
+
+def test_moe_blocks_golden(gpu):
+    g = golden("blocks")
+    m = _moe_from_golden(gpu, g)
+    assert close(m.d1(g["moe_x1"], g["moe_logits1"]), g["moe_out1"], 2e-3)
+    assert close(m.batch(g["moe_x9"], g["moe_logits9"]), g["moe_out9"], 2e-3)
+    for S in (1, 9):
+        assert close(m.olmoe(g[f"moe_x{S}"], g[f"moe_logits{S}"], 0), g[f"olmoe_out{S}"], 2e-3)
+    # with the router on the GPU as an int8 matrix: same logits bit for bit -> same routing
+    m.set_router(gpu.Mat.i8(g["moe_rq"], g["moe_rs"]))
+    assert close(m.d1(g["moe_x1"]), g["moe_out1"], 2e-3)
+    assert close(m.batch(g["moe_x9"]), g["moe_out9"], 2e-3)
+
+
+@pytest.mark.parametrize("E,K,I,D,S", [(64, 8, 128, 256, 1), (64, 8, 128, 256, 40), (16, 4, 96, 160, 7)])
+def test_moe_q8_vs_oracle(gpu, oracle, E, K, I, D, S):
+    from oracle import Experts
+    rng = np.random.default_rng(E + K + S)
+    g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
+    d = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
+    gs, us = (rng.uniform(0.001, 0.02, (E, I)).astype(np.float32) for _ in range(2))
+    ds = rng.uniform(0.001, 0.02, (E, D)).astype(np.float32)
+    ex = Experts(E, K, I, D, g, u, d, gs, us, ds)
+    m = gpu.Moe(E, K, I, D)
+    for e in range(E):
+        m.upload_expert(e, g[e], gs[e], u[e], us[e], d[e], ds[e])
+    x = rng.standard_normal((S, D)).astype(np.float32)
+    logits = (rng.standard_normal((S, E)) * 0.5).astype(np.float32)
+    want = (oracle.moe_d1 if S == 1 else oracle.moe_batch)(ex, x, logits)[0]
+    got = m.d1(x, logits) if S == 1 else m.batch(x, logits)
+    assert close(got, want, 2e-3)
+    want, idx, w = oracle.olmoe_moe(ex, x, logits, 0)
+    assert close(m.olmoe(x, logits, 0), want, 2e-3)
+
+
+@pytest.mark.parametrize("S", [1, 3, 21])
+def test_moe_q4r4_vs_oracle(gpu, oracle, S):
+    from oracle import Experts
+    E, K, I, D = 16, 4, 96, 128
+    rng = np.random.default_rng(S)
+    packs = {k: [oracle.pack_q4r4((rng.standard_normal(shape) * 0.05).astype(np.float32)) for _ in range(E)]
+             for k, shape in (("g", (I, D)), ("u", (I, D)), ("d", (D, I)))}
+    cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
+    ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
+    m = gpu.Moe(E, K, I, D, efmt=gpu.WF_Q4R4)
+    for e in range(E):
+        m.upload_expert(e, packs["g"][e][0], packs["g"][e][1], packs["u"][e][0], packs["u"][e][1],
+                        packs["d"][e][0], packs["d"][e][1])
+    x = rng.standard_normal((S, D)).astype(np.float32)
+    logits = (rng.standard_normal((S, E)) * 0.5).astype(np.float32)
+    want = oracle.moe_q4r4(ex, x, logits)[0]
+    got = m.d1(x, logits) if S == 1 else m.batch(x, logits)
+    assert close(got, want, 2e-3)
+
+
+def test_expert_shards_sum_to_the_whole(gpu, oracle):
+    """Two expert-parallel shards: their partial outputs add up to the unsharded
+    block (f32 sums in another order: compared at 1e-5 of magnitude)."""
+    g = golden("blocks")
+    E, K, I, D = (int(v) for v in g["moe_dims"])
+    whole = _moe_from_golden(gpu, g).batch(g["moe_x9"], g["moe_logits9"])
+    total = np.zeros_like(whole)
+    for lo, hi in ((0, 4), (4, 8)):
+        m = gpu.Moe(E, K, I, D, e_lo=lo, e_hi=hi)
+        for e in range(lo, hi):
+            m.upload_expert(e, g["moe_g"][e], g["moe_gs"][e], g["moe_u"][e], g["moe_us"][e], g["moe_d"][e], g["moe_ds"][e])
+        total += m.batch(g["moe_x9"], g["moe_logits9"])
+    assert close(total, whole)

@@ -1,0 +1,110 @@
+"""GPU parity of mat_apply (Q8_0, Q4R4, per-row int4) through the C ABI."""
+import numpy as np
+import pytest
+
+from conftest import golden, same_bits
+
+pytestmark = pytest.mark.gpu
+
+S_ALL = (1, 2, 3, 4, 5, 7, 16, 37)
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_q8_golden_bit_exact(gpu, oracle, tag):
+    g = golden("matmul_" + tag)
+    W = gpu.Mat.i8(g["W8"], g["sc"])
+    for S in S_ALL:
+        y, acc = gpu.mat_apply(W, g[f"x{S}"], want_acc=True)
+        _, acc_o = oracle.matmul_q_s(g[f"x{S}"], g["W8"], g["sc"], want_acc=True)
+        assert np.array_equal(acc, acc_o), f"int32 accumulators differ at S={S}"
+        assert same_bits(y, g[f"y8_{S}"]), f"f32 outputs differ at S={S}"
+        assert same_bits(gpu.mat_apply(W, g[f"x{S}"]), g[f"y8_{S}"])
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_q4r4_golden_bit_exact(gpu, tag):
+    g = golden("matmul_" + tag)
+    O, I = int(g["O"]), int(g["I"])
+    W = gpu.Mat.q4r4(g["q4"], g["s16"], O, I)
+    for S in S_ALL:
+        y = gpu.mat_apply(W, g[f"x{S}"])
+        assert same_bits(y, g[f"y4_{S}"]), f"S={S}: max diff {np.abs(y - g[f'y4_{S}']).max()}"
+
+
+@pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1024, 3072), (515, 3840), (260, 15360), (77, 16384), (9, 16), (5, 100)])
+@pytest.mark.parametrize("S", [1, 2, 4, 8, 16, 33])
+def test_q8_vs_oracle(gpu, oracle, O, I, S):
+    """Config-2 recipe: int8 U[-127,127], scales U(0.001,0.02), x ~ N(0,1)."""
+    rng = np.random.default_rng(O * 7 + I + S)
+    Wq = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    W = gpu.Mat.i8(Wq, sc)
+    y, acc = gpu.mat_apply(W, x, want_acc=True)
+    yo, acco = oracle.matmul_q_s(x, Wq, sc, want_acc=True)
+    assert np.array_equal(acc, acco)
+    assert same_bits(y, yo)
+
+
+@pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1022, 3072), (515, 3840), (258, 15360), (768, 2048), (4, 32), (7, 64)])
+@pytest.mark.parametrize("S", [1, 2, 3, 4, 7, 12, 37])
+def test_q4r4_vs_oracle(gpu, oracle, O, I, S):
+    rng = np.random.default_rng(O * 3 + I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, s16 = oracle.pack_q4r4(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    W = gpu.Mat.q4r4(q4, s16, O, I)
+    y = gpu.mat_apply(W, x)
+    yo = oracle.matmul_q4r4_s(x, q4, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
+def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
+    """tests/q4r4_tests.c:88-172: extreme codes and activations, long rows."""
+    O, I = 8, 16384
+    q4 = np.full(2 * (I // 32) * 64, 0xFF, np.uint8)            # every code 15
+    s16 = np.full(2 * (I // 32) * 4, 0x3C00, np.uint16)          # scale 1.0
+    x = np.full((2, I), 127.0, np.float32); x[1] = -127.0
+    W = gpu.Mat.q4r4(q4, s16, O, I)
+    assert same_bits(gpu.mat_apply(W, x), oracle.matmul_q4r4_s(x, q4, s16, O))
+
+
+def test_i4_rows(gpu, oracle):
+    rng = np.random.default_rng(9)
+    for (O, I, S) in ((64, 128, 1), (33, 101, 3)):
+        Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+        q4, sc = oracle.pack_int4(Wf)
+        x = rng.standard_normal((S, I)).astype(np.float32)
+        W = gpu.Mat.i4(q4, sc, O, I)
+        assert same_bits(gpu.mat_apply(W, x), oracle.matmul_i4_idot_s(x, q4, sc, I))
+
+
+def test_host_weight_entries(gpu, oracle):
+    g = golden("matmul_a")
+    assert same_bits(gpu.matmul_q_s(g["x5"], g["W8"], g["sc"]), g["y8_5"])
+    assert same_bits(gpu.matmul_q4r4_s(g["x5"], g["q4"], g["s16"], int(g["O"])), g["y4_5"])
+
+
+def test_row_shards_concatenate_to_the_whole(gpu, oracle):
+    """A matrix cut into row shards gives, concatenated, the unsharded result bit for bit."""
+    rng = np.random.default_rng(10)
+    O, I = 1000, 1024
+    Wq = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    x = rng.standard_normal((3, I)).astype(np.float32)
+    whole = gpu.mat_apply(gpu.Mat.i8(Wq, sc), x)
+    parts = [gpu.mat_apply(gpu.Mat.i8(Wq, sc, rows=(a, b)), x) for a, b in ((0, 252), (252, 500), (500, 1000))]
+    assert same_bits(np.concatenate(parts, axis=1), whole)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, s16 = oracle.pack_q4r4(Wf)
+    whole = gpu.mat_apply(gpu.Mat.q4r4(q4, s16, O, I), x)
+    parts = [gpu.mat_apply(gpu.Mat.q4r4(q4, s16, O, I, rows=(a, b)), x) for a, b in ((0, 252), (252, 500), (500, 1000))]
+    assert same_bits(np.concatenate(parts, axis=1), whole)
+
+
+def test_errors_are_loud(gpu):
+    with pytest.raises(gpu.MotyCudaError):
+        gpu.Mat.q4r4(np.zeros(64, np.uint8), np.zeros(4, np.uint16), 4, 40)          # I % 32 != 0
+    W = gpu.Mat.i8(np.zeros((4, 32), np.int8), np.ones(4, np.float32))
+    with pytest.raises(ValueError):
+        gpu.mat_apply(W, np.zeros((1, 16), np.float32))
+    with pytest.raises(gpu.MotyCudaError):
+        gpu.Mat.i8(np.zeros((4, 32), np.int8), np.ones(4, np.float32), device=7)     # not initialised

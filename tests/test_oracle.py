@@ -1,0 +1,130 @@
+"""CPU: the C restatement against the golden vectors (made by the reference's own
+compiled code) and, where the reference library exists, bit for bit against it."""
+import numpy as np
+import pytest
+
+from conftest import golden, same_bits
+
+
+def test_f16_tables(oracle):
+    g = golden("f16")
+    got = np.array([oracle.f16_to_f32(h) for h in range(65536)], np.float32).view(np.uint32)
+    assert same_bits(got, g["f16_to_f32_bits"])
+    h = np.array([oracle.f32_to_f16(v) for v in g["probe"]], np.uint16)
+    assert same_bits(h, g["probe_f16"])
+
+
+def test_dots_exact(oracle):
+    g = golden("dots")
+    for n in g["ns"]:
+        assert oracle.dot_i8i8(g[f"w{n}"], g[f"x{n}"]) == int(g[f"d{n}"])
+        assert oracle.dot_i4i8(g[f"w4_{n}"], g[f"x{n}"]) == int(g[f"d4_{n}"])
+    assert oracle.dot_i8i8(g["wmax"], g["xmax"]) == int(g["dmax"]) == 128 * 127 * 16384
+
+
+def test_quantizers(oracle):
+    g = golden("quant")
+    for n in list(g["ns"]) + ["zero", "ties"]:
+        q, s = oracle.qrow_i8(g[f"x{n}"])
+        assert same_bits(q, g[f"q{n}"]) and np.float32(s) == g[f"s{n}"]
+    xq, xs, xsum = oracle.quant_g32(g["g32_x"])
+    assert same_bits(xq, g["g32_q"]) and same_bits(xs, g["g32_s"]) and same_bits(xsum, g["g32_sum"])
+    # reconstruction bound of the reference's own test (tests/simd_tests.c:127-145)
+    x = g["x1024"]; q, s = oracle.qrow_i8(x)
+    assert np.all(np.abs(x - s * q.astype(np.float32)) <= s / 2 * 1.0001)
+
+
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
+def test_drivers(oracle, tag):
+    g = golden("matmul_" + tag)
+    O, I = int(g["O"]), int(g["I"])
+    q8, s8 = oracle.quantize_rows(g["Wf"])
+    assert same_bits(q8, g["q8"]) and same_bits(s8, g["s8"])
+    q4, s16 = oracle.pack_q4r4(g["Wf"])
+    assert same_bits(q4, g["q4"]) and same_bits(s16, g["s16"])
+    qi4, si4 = oracle.pack_int4(g["Wf"])
+    assert same_bits(qi4, g["qi4"]) and same_bits(si4, g["si4"])
+    for S in (1, 2, 3, 4, 5, 7, 16, 37):
+        x = g[f"x{S}"]
+        y, acc = oracle.matmul_q_s(x, g["W8"], g["sc"], want_acc=True)
+        assert same_bits(y, g[f"y8_{S}"])
+        xi, sx = oracle.qrows_i8(x)
+        assert np.array_equal(acc, xi.astype(np.int32) @ g["W8"].astype(np.int32).T)
+        assert same_bits(oracle.matmul_q4r4_s(x, g["q4"], g["s16"], O), g[f"y4_{S}"])
+
+
+def test_q4r4_batch_is_not_row_invariant(oracle):
+    """The reference folds the -8 offset differently for tokens inside a complete
+    group of 4 (nn/matmul.c:397-402): a batch is NOT always bitwise equal to its
+    rows run one by one.  The restatement must keep that, so pin it."""
+    g = golden("matmul_a")
+    O = int(g["O"]); x = g["x5"]
+    yb = oracle.matmul_q4r4_s(x, g["q4"], g["s16"], O)
+    y1 = np.concatenate([oracle.matmul_q4r4_s(x[i:i + 1], g["q4"], g["s16"], O) for i in range(5)])
+    assert same_bits(yb[4], y1[4])                      # the tail token takes the one-token kernel
+    np.testing.assert_allclose(yb, y1, rtol=0, atol=1e-5 * np.abs(y1).max())
+
+
+def test_q8_batch_is_row_invariant(oracle):
+    """tests/qwen_tests.c:82-109: an S=4 batch equals four S=1 calls bit for bit."""
+    g = golden("matmul_c"); x = g["x4"]
+    yb = oracle.matmul_q_s(x, g["W8"], g["sc"])
+    y1 = np.concatenate([oracle.matmul_q_s(x[i:i + 1], g["W8"], g["sc"]) for i in range(4)])
+    assert same_bits(yb, y1)
+
+
+def test_router(oracle):
+    g = golden("router")
+    for tag in "abcd":
+        K = int(g[f"K_{tag}"])
+        idx, w, probs = oracle.route_topk(g[f"lg_{tag}"], K)
+        assert same_bits(idx, g[f"idx_{tag}"]) and same_bits(w, g[f"w_{tag}"]) and same_bits(probs, g[f"p_{tag}"])
+        idx0, w0 = oracle.moe_topk(g[f"p_{tag}"], K, 0)
+        assert same_bits(idx0, g[f"idx0_{tag}"]) and same_bits(w0, g[f"w0_{tag}"])
+        assert list(g[f"idx_{tag}"][0]) == list(range(K))         # all-equal row: lowest indices
+    assert oracle.argmax(g["argmax_v"]) == int(g["argmax_i"]) == 77
+
+
+def test_topk_is_naive_greedy(oracle):
+    """tests/moe_tests.c:15-39: identical to a naive greedy pick over random (E, K)."""
+    rng = np.random.default_rng(5)
+    for _ in range(200):
+        E = int(rng.integers(2, 300)); K = int(rng.integers(1, min(E, 16) + 1))
+        p = rng.random(E).astype(np.float32)
+        idx, w = oracle.moe_topk(p, K, 0)
+        order = sorted(range(E), key=lambda e: (-p[e], e))[:K]
+        assert list(idx[0]) == order and np.array_equal(w[0], p[order])
+
+
+def test_blocks(oracle):
+    from oracle import Experts
+    g = golden("blocks")
+    for S in (1, 5):
+        x = g[f"ffn_x{S}"]
+        assert same_bits(oracle.ffn_q8(x, g["gq"], g["gs"], g["uq"], g["us"], g["dq"], g["ds"]), g[f"ffn8_{S}"])
+        assert same_bits(oracle.ffn_q4r4(x, 256, g["g4"], g["g4s"], g["u4"], g["u4s"], g["d4"], g["d4s"]), g[f"ffn4_{S}"])
+    E, K, I, D = (int(v) for v in g["moe_dims"])
+    ex = Experts(E, K, I, D, g["moe_g"], g["moe_u"], g["moe_d"], g["moe_gs"], g["moe_us"], g["moe_ds"])
+    out, _, _ = oracle.moe_d1(ex, g["moe_x1"], g["moe_logits1"])
+    assert same_bits(out, g["moe_out1"])
+    out, _, _ = oracle.moe_batch(ex, g["moe_x9"], g["moe_logits9"])
+    assert same_bits(out, g["moe_out9"])
+    for S in (1, 9):
+        out, idx, w = oracle.olmoe_moe(ex, g[f"moe_x{S}"], g[f"moe_logits{S}"], 0)
+        assert same_bits(out, g[f"olmoe_out{S}"]) and same_bits(idx, g[f"olmoe_idx{S}"]) and same_bits(w, g[f"olmoe_w{S}"])
+
+
+def test_oracle_equals_reference_build(oracle, ref):
+    """Fresh random inputs, both libraries, bit for bit (skipped without the reference)."""
+    rng = np.random.default_rng(11)
+    for (O, I, S) in ((33, 64, 3), (257, 1024, 9), (64, 3072, 33)):
+        W = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+        x = rng.standard_normal((S, I)).astype(np.float32)
+        assert same_bits(oracle.matmul_q_s(x, W, sc), ref.matmul_q_s(x, W, sc))
+        Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+        a, b = oracle.pack_q4r4(Wf), ref.pack_q4r4(Wf)
+        assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
+        assert same_bits(oracle.matmul_q4r4_s(x, a[0], a[1], O), ref.matmul_q4r4_s(x, a[0], a[1], O))
+    lg = (rng.standard_normal((500, 128)) * 0.05).astype(np.float32)
+    a, b = oracle.route_topk(lg, 8), ref.route_topk(lg, 8)
+    assert all(same_bits(u, v) for u, v in zip(a, b))
