@@ -1,0 +1,326 @@
+#!/usr/bin/env python
+"""Benchmark of the Q8_0 decode GEMV path (the op-level sweep of the baseline).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+One step = one pass of the S=1 Q8_0 GEMV over the six sweep shapes (O x I:
+1024x1024, 3072x1024, 1024x3072, 151936x1024, 15360x3840, 3840x15360; int8
+weights U[-127,127], f32 row scales U(0.001,0.02), activations N(0,1), seed 0).
+The weights of one pass total 280 MB, more than the 126 MB L2, so every pass
+streams from HBM.
+
+value      algorithmic GB/s with activations and results resident on the GPU
+           (moty_cuda_mat_apply_dev), CUDA events on the launch stream, max over ranks
+e2e        the same passes through the host-pointer entry moty_cuda_mat_apply
+           (pinned host buffers; H2D of x and D2H of y inside the timed region)
+roofline   the dominant kernel (the 151936x1024 GEMV): bytes / its own average
+           launch time, measured with events inside the timed region
+cpu_baseline / --impl reference
+           the reference's own OpenMP code (oracle/_ref, else the C restatement)
+           on the host cores, same passes
+
+N > 1: one process per GPU (torchrun), independent replicas of the sweep, no
+data-path collective (the op sweep does not shard); value = N passes / max time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import re
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SHAPES = [(1024, 1024), (3072, 1024), (1024, 3072), (151936, 1024), (15360, 3840), (3840, 15360)]
+DOMINANT = 3                                   # index of the 151936x1024 matrix
+METRIC = "Q8_0 GEMV HBM GB/s (op-level sweep, S=1 decode)"
+WORKLOAD = "configs[1]: op-level Q8_0 sweep, six shapes, S=1, seed 0"
+
+
+def algo_bytes(O, I, S=1):
+    """Q8_0 bytes per call: weights + row scales + activations in + results out."""
+    return O * I + 4 * O + 4 * S * I + 4 * S * O
+
+
+def make_inputs(seed=0):
+    rng = np.random.default_rng(seed)
+    mats = []
+    for (O, I) in SHAPES:
+        W = rng.integers(-127, 128, size=(O, I), dtype=np.int8)
+        sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+        x = rng.standard_normal((1, I)).astype(np.float32)
+        mats.append((W, sc, x))
+    return mats
+
+
+def measured_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def profile_traffic():
+    """DRAM bytes per launch of the dominant kernel, from the committed ncu summary."""
+    p = os.path.join(ROOT, "profiles", "q8_gemv_fused_151936x1024.md")
+    if os.path.exists(p):
+        m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)", open(p).read())
+        if m:
+            return float(m.group(1))
+    return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._t = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                 "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                 "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                 "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for k, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def start(self):
+        if self.nv:
+            self._t = threading.Thread(target=self._run, daemon=True)
+            self._t.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._t:
+            self._t.join()
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the reference's own code on the host cores
+# ---------------------------------------------------------------------------
+def cpu_arm(mats, steps, warmup, budget_s=None):
+    """Time passes of the sweep with moty_matmul_q_s.  Returns (GB/s, cores, kind, passes, seconds)."""
+    from oracle import Oracle, Ref
+    if Ref.available():
+        r = Ref(); kind = "reference"; cores = r.threads()
+        call = r.matmul_q_s
+    else:
+        r = Oracle(); kind = "port"; cores = os.cpu_count() or 1
+        call = r.matmul_q_s
+    for _ in range(max(warmup, 1)):
+        for (W, sc, x) in mats:
+            call(x, W, sc)
+    total = sum(algo_bytes(*s) for s in SHAPES)
+    t0 = time.perf_counter(); done = 0
+    while done < steps:
+        for (W, sc, x) in mats:
+            call(x, W, sc)
+        done += 1
+        if budget_s is not None and time.perf_counter() - t0 > budget_s and done >= 3:
+            break
+    dt = time.perf_counter() - t0
+    return total * done / dt / 1e9, cores, kind, done, dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    mats = make_inputs()
+    gbs, cores, kind, done, dt = cpu_arm(mats, args.steps, args.warmup, budget_s=120.0)
+    line = {"impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": done, "warmup": args.warmup, "ms_per_step": round(dt / done * 1e3, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xint8->int32",
+            "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs_larger_than_l2"},
+            "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+                             "sample": f"{done} passes of the sweep, {dt:.1f} s"},
+            "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+def run_gpu(args):
+    import torch
+    import moty_b200 as mb
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    mb.init([local])
+    dev = torch.device("cuda", local)
+
+    mats = make_inputs()
+    W = [mb.Mat.i8(w, sc, device=local) for (w, sc, _) in mats]
+    xs = [torch.from_numpy(x).to(dev) for (_, _, x) in mats]
+    ys = [torch.empty((1, O), dtype=torch.float32, device=dev) for (O, _) in SHAPES]
+    stream = torch.cuda.Stream(device=dev)
+    sp = stream.cuda_stream
+    total_bytes = sum(algo_bytes(*s) for s in SHAPES)
+
+    def one_pass():
+        for w, x, y in zip(W, xs, ys):
+            mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), 1, sp)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            one_pass()
+        barrier()
+        sampler.start()
+        # ---- device-resident passes ----
+        K = args.steps
+        dom_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record(stream)
+        for k in range(K):
+            for i, (w, x, y) in enumerate(zip(W, xs, ys)):
+                if i == DOMINANT:
+                    dom_ev[k][0].record(stream)
+                    mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), 1, sp)
+                    dom_ev[k][1].record(stream)
+                else:
+                    mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), 1, sp)
+        e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        dom_ms = statistics.mean(a.elapsed_time(b) for a, b in dom_ev)
+
+    # ---- end to end through the host-pointer entry, pinned host buffers ----
+    hx = [mb.pinned_empty((1, I), np.float32) for (_, I) in SHAPES]
+    hy = [mb.pinned_empty((1, O), np.float32) for (O, _) in SHAPES]
+    for h, (_, _, x) in zip(hx, mats):
+        h[...] = x
+    for _ in range(3):
+        for w, h_in, h_out in zip(W, hx, hy):
+            mb.mat_apply(w, h_in, h_out)
+    barrier()
+    Ke = max(3, min(K, 200))
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        for w, h_in, h_out in zip(W, hx, hy):
+            mb.mat_apply(w, h_in, h_out)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    barrier()
+    clocks = sampler.stop()
+
+    # parity guard: the numbers above are only worth printing if the results are right
+    if rank == 0:
+        from oracle import Oracle
+        o = Oracle()
+        for i in range(min(3, len(mats))):
+            w, sc, x = mats[i]
+            if w.shape[0] > 20000:
+                continue
+            assert ys[i].cpu().numpy().tobytes() == o.matmul_q_s(x, w, sc).tobytes(), "GPU result differs from the oracle"
+            assert hy[i].tobytes() == ys[i].cpu().numpy().tobytes()
+
+    if dist is not None:
+        t = torch.tensor([ms, dom_ms, e2e_s], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, dom_ms, e2e_s = (float(v) for v in t.tolist())
+    if rank != 0:
+        if dist is not None:
+            dist.destroy_process_group()
+        return
+
+    value = world * total_bytes * K / (ms * 1e-3) / 1e9
+    e2e = world * total_bytes * Ke / e2e_s / 1e9
+    peak, peak_kind = measured_peak()
+    O, I = SHAPES[DOMINANT]
+    achieved = algo_bytes(O, I) / (dom_ms * 1e-3) / 1e9
+    cpu = None
+    if world == 1 and not args.no_cpu:
+        gbs, cores, kind, done, dt = cpu_arm(mats, 10 ** 9, 1, budget_s=12.0)
+        cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
+               "sample": f"{done} passes of the same sweep with moty_matmul_q_s, {dt:.1f} s"}
+    line = {"metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": K,
+            "warmup": max(args.warmup, 3), "ms_per_step": round(ms / K, 6), "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "int8xint8->int32", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "l2": "inputs_larger_than_l2 (280 MB of weights per pass, L2 126 MB)",
+                       "parallelism": "replicas" if world > 1 else "single", "bytes_per_step": total_bytes},
+            "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
+            "roofline": {"bound": "hbm", "kernel": "q8_gemv_fused 151936x1024 S=1", "achieved": round(achieved, 1),
+                         "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
+                         "traffic": profile_traffic(), "algorithmic_bytes": algo_bytes(O, I),
+                         "avg_launch_us": round(dom_ms * 1e3, 3)},
+            "cpu_baseline": cpu,
+            "e2e": {"value": round(e2e, 2), "unit": "GB/s", "steps": Ke,
+                    "h2d_bytes_per_step": sum(4 * I for (_, I) in SHAPES), "d2h_bytes_per_step": sum(4 * O for (O, _) in SHAPES)},
+            "gpu_launches": K * len(SHAPES), "clocks": clocks}
+    print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
+    args = ap.parse_args()
+    if args.shapes:
+        global SHAPES, DOMINANT, WORKLOAD
+        keep = [int(v) for v in args.shapes.split(",")]
+        dom = SHAPES[DOMINANT]
+        SHAPES = [SHAPES[i] for i in keep]
+        DOMINANT = SHAPES.index(dom) if dom in SHAPES else 0
+        WORKLOAD += f" (subset {keep})"
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
