@@ -53,6 +53,14 @@ int moty_grow_pinned(DevCtx *c, Buf *b, size_t bytes) {
     return 0;
 }
 
+int moty_grow_zero(DevCtx *c, Buf *b, size_t bytes) {
+    if (bytes <= b->cap) return 0;
+    CKR(moty_grow(c, b, bytes));
+    CK(cudaMemsetAsync(b->p, 0, b->cap, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
 static void free_buf(Buf *b) { if (b->p) cudaFree(b->p); b->p = nullptr; b->cap = 0; }
 static void free_pinned(Buf *b) { if (b->p) cudaFreeHost(b->p); b->p = nullptr; b->cap = 0; }
 
@@ -79,6 +87,8 @@ extern "C" int moty_cuda_init(const int *devices, int ndev) {
         CK(cudaStreamCreateWithFlags(&c->stream, cudaStreamNonBlocking));
         CK(cudaMalloc(&c->err_dev, 64));
         CK(cudaMemset(c->err_dev, 0, 64));
+        CK(cudaMalloc(&c->ctr, 64));
+        CK(cudaMemset(c->ctr, 0, 64));
         CKR(gemv_q8_init_device());
         CKR(q4r4_init_device());
         c->ready = true;
@@ -94,10 +104,11 @@ extern "C" void moty_cuda_shutdown(void) {
         cudaSetDevice(c->dev);
         cudaStreamSynchronize(c->stream);
         Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
-                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc};
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell};
         for (Buf *b : bs) free_buf(b);
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
+        if (c->ctr) cudaFree(c->ctr);
         cudaStreamDestroy(c->stream);
         c->ready = false;
     }
@@ -223,11 +234,17 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (I > MOTY_QROW_MAX)
         return moty_set_error(MOTY_CUDA_ELIMIT, "mat_apply: I=%d exceeds %d (the reference switches to an f32 path there)", I, MOTY_QROW_MAX);
     if (w->fmt == MOTY_WF_I8) {
-        if (S == 1 && I % 16 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
-            return launch_q8_gemv_fused(x, (const int8_t *)w->codes, (const float *)w->scales, y, acc, I, O, c->sms, st);
+        const bool stream_ok = I % 16 == 0 && S <= 8;
+        if (stream_ok && I > 4096) CKR(moty_grow_zero(c, &c->kcell, (size_t)8 * O * 8));
+        if (stream_ok && S == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
+            return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, x, nullptr, nullptr, y, acc,
+                                    1, I, O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, st);
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
+        if (stream_ok)
+            return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, nullptr, (const int8_t *)c->xi.p,
+                                    (const float *)c->sx.p, y, acc, S, I, O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, st);
         if (I % 16 != 0)
             return launch_q8_any((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
                                  (const float *)c->sx.p, y, acc, S, I, O, st);

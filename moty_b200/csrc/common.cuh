@@ -48,6 +48,9 @@ struct DevCtx {
     Buf hpin_in, hpin_out;           // pinned host
     // FFN / MoE intermediates
     Buf g, u, h, hq, hs, hxs, hxsum, pair, misc;
+    // streaming GEMV: ticket/exit counters and K-split cells, all zero between launches
+    int *ctr = nullptr;
+    Buf kcell;
     // device error word written by kernels whose bounded waits expire
     int *err_dev = nullptr;
 };
@@ -55,6 +58,7 @@ struct DevCtx {
 DevCtx *moty_ctx(int device);                       // nullptr when not initialised
 int moty_grow(DevCtx *c, Buf *b, size_t bytes);     // device buffer, grow-only
 int moty_grow_pinned(DevCtx *c, Buf *b, size_t bytes);
+int moty_grow_zero(DevCtx *c, Buf *b, size_t bytes);   // device buffer, zero-filled when (re)allocated
 
 struct MotyCudaMat {
     int fmt, O, I, device;

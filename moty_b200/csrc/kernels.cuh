@@ -43,6 +43,12 @@ int launch_i4_rows(const uint8_t *w4, const float *scale, const int8_t *xi, cons
 int launch_q8_any(const int8_t *W, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
                   int S, int I, int O, cudaStream_t st);
 int gemv_q8_init_device();
+
+// ---- gemv_q8_stream.cu -------------------------------------------------------
+// persistent streaming GEMV for 1..8 rows; S == 1 quantizes x (f32) in the kernel
+int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const int8_t *xi, const float *sx,
+                     float *y, int32_t *acc, int S, int I, int O, int *counters, unsigned long long *cell,
+                     int sms, cudaStream_t st);
 int q4r4_init_device();
 
 // ---- gemm_q8_tc.cu --------------------------------------------------------------
