@@ -305,7 +305,13 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, acc ? (int32_t *)c->acc32.p : nullptr, c->stream));
     CK(cudaMemcpyAsync(y, c->dy.p, yb, cudaMemcpyDeviceToHost, c->stream));
     if (acc) CK(cudaMemcpyAsync(acc, c->acc32.p, yb, cudaMemcpyDeviceToHost, c->stream));
+    int kerr = 0;
+    if (S >= Q8_TC_MIN_S) CK(cudaMemcpyAsync(&kerr, c->err_dev, 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
+    if (kerr) {
+        cudaMemsetAsync(c->err_dev, 0, 4, c->stream);
+        return moty_set_error(MOTY_CUDA_EKERNEL, "tensor-core GEMM gave up on a bounded wait (no result written)");
+    }
     return 0;
 }
 

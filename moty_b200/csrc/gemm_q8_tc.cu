@@ -1,9 +1,274 @@
-// gemm_q8_tc.cu -- tcgen05 int8 GEMM (placeholder until the kernel lands: reports
-// "not supported" so that the drivers keep using the dp4a kernels).
+// gemm_q8_tc.cu -- Q8_0 prefill GEMM on the 5th-generation tensor cores.
+//
+//   acc[o][s] = sum_i W[o][i] * xi[s][i]       int8 x int8 -> int32, exact
+//   y[s][o]   = (scale[o] * sx[s]) * (float)acc (nn/matmul.c:29-36)
+//
+// One CTA computes a 128 (output rows) x BN (tokens) tile:
+//   warp 0   producer: TMA loads of the W tile [128 x 128 B] and the activation
+//            tile [BN x 128 B] into a STAGES-deep shared-memory ring, 128-byte swizzle,
+//            completion on mbarriers (per-CTA loads only, no multicast);
+//   warp 1   issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BN, K=32; four per
+//            128-byte K block) accumulating int32 in TMEM, tcgen05.commit frees the
+//            ring slots and finally signals the epilogue;
+//   warps 2-5 epilogue: tcgen05.ld of their 32-lane TMEM quarter, scale, coalesced
+//            stores of y (32 consecutive output rows per instruction).
+// W is the A operand so that M = 128 weight rows fill the tensor-core datapath even
+// when only 16 tokens are present; the kernel is then HBM-bound on the weights.
+//
+// Every mbarrier wait is bounded: on expiry the waiter raises a CTA-wide abort
+// flag and a device error word, all roles fall through to the common exit, the
+// TMEM columns are freed, and the host reports MOTY_CUDA_EKERNEL.
 #include "kernels.cuh"
+#include <cuda.h>
 
-bool q8_tc_supported(int, int, int) { return false; }
-int q8_tc_make_tmap(MotyCudaMat *m) { m->has_tmap = false; return 0; }
-int launch_q8_tc(const MotyCudaMat *, const int8_t *, const float *, float *, int32_t *, int, DevCtx *, cudaStream_t) {
-    return moty_set_error(MOTY_CUDA_EARG, "tensor-core path not built");
+namespace {
+
+constexpr int BM = 128;          // weight rows per CTA tile
+constexpr int BKB = 128;         // K bytes per stage (= one 128-byte swizzle row)
+constexpr uint32_t WAIT_LIMIT = 1u << 24;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait; returns false (and raises the abort flag) when the limit is hit or another role aborted
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+    for (uint32_t it = 0; it < WAIT_LIMIT; it++) {
+        if (mbar_try(bar, parity)) return true;
+        if ((it & 255u) == 255u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, rows 128 B apart,
+// 8-row groups 1024 B apart, descriptor version 1 (sm_100)
+__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused for swizzled K-major)
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct TcArgs {
+    const float *scale; const float *sx; float *y; int32_t *acc;
+    int S, I, O;
+    int *err;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+                                                       const __grid_constant__ CUtensorMap mapB, TcArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    // 1024-byte alignment for the swizzled tiles
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
+    const int nkb = (a.I + BKB - 1) / BKB;
+    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int i = 0; i < STAGES; i++) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
+        mbar_init(&tmem_full_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_s;
+    volatile int *abort_flag = &abort_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                int st = kb % STAGES;
+                uint32_t ph = (kb / STAGES) & 1;
+                if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag)) break;
+                mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+                uint8_t *sa = smem + (size_t)st * STAGE_BYTES;
+                tma_load_2d(sa, &mapA, kb * BKB, m0, &full_bar[st]);
+                tma_load_2d(sa + A_BYTES, &mapB, kb * BKB, n0, &full_bar[st]);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = BN, M = 128
+            const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; kb++) {
+                int st = kb % STAGES;
+                uint32_t ph = (kb / STAGES) & 1;
+                ok = mbar_wait(&full_bar[st], ph, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint32_t sa = smem_u32(smem + (size_t)st * STAGE_BYTES);
+                uint32_t sb = sa + A_BYTES;
+#pragma unroll
+                for (int k4 = 0; k4 < BKB / 32; k4++) {
+                    if (kb * BKB + k4 * 32 >= a.I) break;                  // nothing but zero fill beyond I
+                    umma_i8(tmem_base, umma_desc(sa + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
+                }
+                umma_commit(&empty_bar[st]);                               // slot reusable when these MMAs retire
+            }
+            if (ok) umma_commit(&tmem_full_bar);                           // accumulator complete
+        }
+    } else {
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
+        const int q = warp & 3;
+        // one lane waits, the warp follows its verdict (tcgen05.ld is warp-collective)
+        int ok = lane == 0 ? (int)mbar_wait(&tmem_full_bar, 0, abort_flag) : 1;
+        ok = __shfl_sync(0xffffffffu, ok, 0);
+        if (ok) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int o = m0 + q * 32 + lane;
+            const float sc = o < a.O ? __ldg(a.scale + o) : 0.f;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(taddr));
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (n0 + c0 >= a.S) break;
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    int s = n0 + c0 + j;
+                    if (s < a.S && o < a.O) {
+                        int v = (int)r[j];
+                        a.y[(size_t)s * a.O + o] = __fmul_rn(__fmul_rn(sc, __ldg(a.sx + s)), (float)v);
+                        if (a.acc) a.acc[(size_t)s * a.O + o] = v;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (abort_s) {
+        // give bulk copies that may still be in flight time to land before the CTA's memory is released
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_s) atomicExch(a.err, 1);
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeFn)p;
+    }
+    return fn;
+}
+
+// rows x cols int8 matrix, row-major; box = box_rows x 128 bytes, 128-byte swizzle, zero fill out of bounds
+int make_map(CUtensorMap *m, const void *base, int rows, int cols, int box_rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return moty_set_error(MOTY_CUDA_ECUDA, "cuTensorMapEncodeTiled not available");
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols};
+    cuuint32_t box[2] = {(cuuint32_t)BKB, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void *>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return moty_set_error(MOTY_CUDA_ECUDA, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return 0;
+}
+
+template <int BN, int STAGES>
+int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi, const float *sx, float *y, int32_t *acc,
+                int S, DevCtx *c, cudaStream_t st) {
+    CUtensorMap mapB;
+    CKR(make_map(&mapB, xi, S, w->I, BN));
+    size_t smem = (size_t)STAGES * (BM * BKB + BN * BKB) + 1024;
+    auto k = q8_tc_kernel<BN, STAGES>;
+    CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    TcArgs a;
+    a.scale = (const float *)w->scales; a.sx = sx; a.y = y; a.acc = acc; a.S = S; a.I = w->I; a.O = w->O; a.err = c->err_dev;
+    dim3 grid((w->O + BM - 1) / BM, (S + BN - 1) / BN);
+    k<<<grid, 192, smem, st>>>(mapA, mapB, a);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+}  // namespace
+
+// the tensor map wants 16-byte row strides; rows shorter than one K block gain nothing
+bool q8_tc_supported(int S, int I, int O) { return S >= 16 && I % 16 == 0 && I >= 128 && O >= 1; }
+
+int q8_tc_make_tmap(MotyCudaMat *m) {
+    m->has_tmap = false;
+    if (m->fmt != MOTY_WF_I8 || m->I % 16 != 0 || m->I < 128) return 0;
+    static_assert(sizeof(CUtensorMap) <= sizeof(m->tmap), "tensor map storage");
+    if (make_map(reinterpret_cast<CUtensorMap *>(m->tmap), m->codes, m->O, m->I, BM) != 0) return 0;
+    m->has_tmap = true;
+    return 0;
+}
+
+int launch_q8_tc(const MotyCudaMat *w, const int8_t *xi, const float *sx, float *y, int32_t *acc,
+                 int S, DevCtx *c, cudaStream_t st) {
+    const CUtensorMap &mapA = *reinterpret_cast<const CUtensorMap *>(w->tmap);
+    if (S <= 16) return launch_tc_t<16, 8>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 32) return launch_tc_t<32, 8>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 64) return launch_tc_t<64, 6>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 128) return launch_tc_t<128, 6>(mapA, w, xi, sx, y, acc, S, c, st);
+    return launch_tc_t<256, 4>(mapA, w, xi, sx, y, acc, S, c, st);
 }
