@@ -171,6 +171,57 @@ def run_reference(args):
 
 
 # ---------------------------------------------------------------------------
+# extras: the other rows of the op-level sweep, timed per shape (reported beside the
+# headline, not part of it): Q8_0 at S=16 and S=512, Q4R4 at S=1 and S=16, and one
+# library int8 GEMM as the calibration point for the int8 tensor peak
+# ---------------------------------------------------------------------------
+def q4r4_bytes(O, I, S=1):
+    return (O + 3) // 4 * (I // 32) * 72 + 4 * S * I + 4 * S * O
+
+
+def run_extras(torch, mb, dev, stream, W8, local):
+    sp = stream.cuda_stream
+    out = {"rows": []}
+    a = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=dev)
+    b = torch.randint(-127, 128, (8192, 8192), dtype=torch.int8, device=dev)
+    best = 1e9
+    for _ in range(8):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(); torch._int_mm(a, b); e1.record(); torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1))
+    out["int8_library_gemm_8192_tops"] = round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+    del a, b
+    rng = np.random.default_rng(1)
+    W4 = []
+    for (O, I) in SHAPES:
+        nblk, nb = (O + 3) // 4, I // 32
+        q4 = rng.integers(0, 256, nblk * nb * 64, dtype=np.uint8)
+        s16 = np.full(nblk * nb * 4, 0x1A00, np.uint16)               # f16 0.00293
+        W4.append(mb.Mat.q4r4(q4, s16, O, I, device=local))
+    with torch.cuda.stream(stream):
+        for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4)):
+            xs = [torch.randn((S, I), device=dev) for (_, I) in SHAPES]
+            ys = [torch.empty((S, O), device=dev) for (O, _) in SHAPES]
+            ev = [[] for _ in SHAPES]
+            for p in range(passes + 1):
+                for i, (w, x, y) in enumerate(zip(mats, xs, ys)):
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), S, sp)
+                    e1.record(stream)
+                    if p > 0:
+                        ev[i].append((e0, e1))
+            torch.cuda.synchronize()
+            for i, (O, I) in enumerate(SHAPES):
+                us = statistics.mean(a.elapsed_time(b) for a, b in ev[i]) * 1e3
+                nbytes = algo_bytes(O, I, S) if fmt == "q8_0" else q4r4_bytes(O, I, S)
+                out["rows"].append({"fmt": fmt, "S": S, "O": O, "I": I, "us": round(us, 2),
+                                    "GBs": round(nbytes / us / 1e3, 1), "TOPS": round(2.0 * S * O * I / us / 1e6, 2)})
+            del xs, ys
+    return out
+
+
+# ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu(args):
@@ -281,6 +332,9 @@ def run_gpu(args):
         gbs, cores, kind, done, dt = cpu_arm(mats, 10 ** 9, 1, budget_s=12.0)
         cpu = {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": kind,
                "sample": f"{done} passes of the same sweep with moty_matmul_q_s, {dt:.1f} s"}
+    extras = None
+    if world == 1 and not args.no_extras and len(SHAPES) == 6:
+        extras = run_extras(torch, mb, dev, stream, W, local)
     line = {"metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms / K, 6), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8xint8->int32", "data": "synthetic",
@@ -294,7 +348,7 @@ def run_gpu(args):
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "steps": Ke,
                     "h2d_bytes_per_step": sum(4 * I for (_, I) in SHAPES), "d2h_bytes_per_step": sum(4 * O for (O, _) in SHAPES)},
-            "gpu_launches": K * len(SHAPES), "clocks": clocks}
+            "gpu_launches": K * len(SHAPES), "clocks": clocks, "extras": extras}
     print(json.dumps(line), flush=True)
     if dist is not None:
         dist.destroy_process_group()
@@ -308,6 +362,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     args = ap.parse_args()
     if args.shapes:
         global SHAPES, DOMINANT, WORKLOAD
