@@ -95,6 +95,24 @@ int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, in
  * values moty_hw_dot_i8i8 returns, hw/hw_scalar.h:8-12) for exact checks */
 int moty_cuda_mat_apply_acc(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S);
 
+/* The Q8_0 product for hosts that must not allocate (no counterpart in the
+ * reference: its drivers grow static scratch with malloc).  Meant for callers
+ * that own all device memory themselves, or that cannot take the device-wide
+ * stall of cudaMalloc/cudaFree inside a decode loop.  All four arrays are DEVICE
+ * pointers supplied by the caller: q [O][I] int8, scale [O], x [S][I], y [S][O].
+ * The quantized activation rows live in a fixed array inside the library
+ * (8 x 16384 bytes of codes + 8 scales per GPU, held until the process exits), so
+ *   1 <= S <= 8, I a multiple of 16, 16 <= I <= 16384; anything else is
+ *   MOTY_CUDA_ELIMIT.
+ * The call needs no moty_cuda_init and calls no allocating routine.  Its FIRST
+ * call on a device looks up the array's device address and sets kernel
+ * attributes; make that first call before any stream capture.  All calls share
+ * the one array: two calls that overlap on the GPU (different streams) race;
+ * calls on one stream are ordered and safe.  Results equal moty_cuda_mat_apply_dev
+ * bit for bit.  `stream` NULL = the default stream. */
+int moty_cuda_q8_apply_noalloc(float *y_dev, const float *x_dev, const int8_t *q_dev, const float *scale_dev,
+                               int S, int I, int O, int device, void *stream);
+
 /* HwBackend.matmul_i8 (hw/hw_backend.h:56-57) / moty_matmul_q_s with host
  * weights: uploads, runs, frees.  A correctness convenience, not a fast path. */
 int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale, int S, int I, int O);

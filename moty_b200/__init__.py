@@ -352,3 +352,11 @@ class Moe:
             self.free()
         except Exception:
             pass
+
+
+def q8_apply_noalloc(y_ptr: int, x_ptr: int, q_ptr: int, scale_ptr: int, S: int, I: int, O: int,
+                     device: int = 0, stream: int = 0) -> None:
+    """The Q8_0 product for hosts that must not allocate: device pointers in and
+    out, scratch in a fixed array inside the library (S <= 8, I <= 16384)."""
+    _ck(lib().moty_cuda_q8_apply_noalloc(C.c_void_p(y_ptr), C.c_void_p(x_ptr), C.c_void_p(q_ptr), C.c_void_p(scale_ptr),
+                                         S, I, O, device, C.c_void_p(stream)))
