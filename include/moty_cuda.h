@@ -191,6 +191,20 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
                             const float *logits_dev, int order, int norm_topk,
                             int *idx_dev, float *w_dev, void *stream);
 
+/* Expert-parallel building blocks (no reference counterpart: the reference is one
+ * process).  Arithmetic is that of the block entries above, cut at the exchange.
+ * moe_experts_dev: P activation rows x_rows [P][D], each with ONE expert id
+ * eid [P] (the rows a peer routed here); h [P][D] receives that expert's output
+ * down(silu(gate x) * up x) per row, zeros for experts not resident on this GPU.
+ * Per-row results equal what nn/moe.c:195-199 computes for that row. */
+int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_dev, const int *eid_dev,
+                              int P, void *stream);
+/* moe_combine_dev: out[s] = sum over the token's K selections of w[s][k] * h[s*K+k],
+ * one fused multiply-add per step from 0, in selection order (order 0,
+ * nn/moe.c:146-149) or ascending expert id (order 1, nn/moe.c:200-202). */
+int moty_cuda_moe_combine_dev(float *out_dev, const float *h_dev, const float *w_dev, const int *idx_dev,
+                              int S, int K, int D, int order, void *stream);
+
 /* ---- greedy token ----------------------------------------------------------
  * moty_argmax_v (nn/sample.c:9-13): first index of the maximum of v [n]. */
 int moty_cuda_argmax(const float *v, int n, int *out);

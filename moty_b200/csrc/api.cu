@@ -579,7 +579,7 @@ struct MotyCudaMoe {
     // plan buffers (device), sized for capS tokens
     int capS;
     int *idx, *pair_tok, *pos_of, *ord, *counters;
-    float *w;
+    float *w, *ones;
     uint8_t *form;
     void *t_gate, *t_up, *t_down;
     float *logits;
@@ -616,9 +616,9 @@ extern "C" int moty_cuda_moe_create(MotyCudaMoe **out, int E, int K, int I, int 
 }
 
 static void moe_free_plan(MotyCudaMoe *m) {
-    void *ps[] = {m->idx, m->pair_tok, m->pos_of, m->ord, m->counters, m->w, m->form, m->t_gate, m->t_up, m->t_down, m->logits};
+    void *ps[] = {m->idx, m->pair_tok, m->pos_of, m->ord, m->counters, m->w, m->ones, m->form, m->t_gate, m->t_up, m->t_down, m->logits};
     for (void *p : ps) if (p) cudaFree(p);
-    m->idx = m->pair_tok = m->pos_of = m->ord = m->counters = nullptr; m->w = nullptr; m->form = nullptr;
+    m->idx = m->pair_tok = m->pos_of = m->ord = m->counters = nullptr; m->w = nullptr; m->ones = nullptr; m->form = nullptr;
     m->t_gate = m->t_up = m->t_down = nullptr; m->logits = nullptr; m->capS = 0;
 }
 
@@ -671,30 +671,48 @@ static int moe_ensure_plan(MotyCudaMoe *m, int S) {
     CK(cudaMalloc(&m->idx, SK * 4)); CK(cudaMalloc(&m->pair_tok, SK * 4)); CK(cudaMalloc(&m->pos_of, SK * 4));
     CK(cudaMalloc(&m->ord, SK * 4)); CK(cudaMalloc(&m->counters, 64)); CK(cudaMalloc(&m->w, SK * 4));
     CK(cudaMalloc(&m->form, SK + 16));
+    CK(cudaMalloc(&m->ones, SK * 4));
+    {
+        float *tmp = (float *)malloc(SK * 4);
+        if (!tmp) return moty_set_error(MOTY_CUDA_ENOMEM, "moe plan: host allocation");
+        for (size_t i = 0; i < SK; i++) tmp[i] = 1.f;
+        cudaError_t e = cudaMemcpy(m->ones, tmp, SK * 4, cudaMemcpyHostToDevice);
+        free(tmp);
+        CK(e);
+    }
     CK(cudaMalloc(&m->t_gate, ntile * tsz)); CK(cudaMalloc(&m->t_up, ntile * tsz)); CK(cudaMalloc(&m->t_down, ntile * tsz));
     CK(cudaMalloc(&m->logits, (size_t)cap * m->E * 4));
     m->capS = cap;
     return 0;
 }
 
+// eid_given == null: route the S tokens (softmax + top-K of the logits) and combine their K
+// expert outputs in `order`.  eid_given != null: S rows with ONE given expert each (the rows an
+// expert-parallel peer sent here); out[i] is that expert's output for row i, zero when the
+// expert is not resident on this GPU.
 static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, int S, const float *logits,
-                        int order, int norm_topk, int *idx_out, float *w_out, cudaStream_t st) {
-    const int E = m->E, K = m->K, I = m->I, D = m->D;
+                        int order, int norm_topk, int *idx_out, float *w_out, const int *eid_given, cudaStream_t st) {
+    const int E = m->E, K = eid_given ? 1 : m->K, I = m->I, D = m->D;
     const bool q8 = m->efmt == MOTY_WF_I8;
     const int T = q8 ? 8 : 4;
-    CKR(moe_ensure_plan(m, S));
-    if (!logits) {
-        if (!m->router) return moty_set_error(MOTY_CUDA_EARG, "moe: neither logits nor a router matrix");
-        CKR(mat_apply_on(c, m->router, m->logits, x, S, nullptr, st));
-        logits = m->logits;
+    CKR(moe_ensure_plan(m, eid_given ? (S + m->K - 1) / m->K : S));
+    const int *idxp = m->idx; const float *wp = m->w;
+    if (eid_given) {
+        idxp = eid_given; wp = m->ones;
+    } else {
+        if (!logits) {
+            if (!m->router) return moty_set_error(MOTY_CUDA_EARG, "moe: neither logits nor a router matrix");
+            CKR(mat_apply_on(c, m->router, m->logits, x, S, nullptr, st));
+            logits = m->logits;
+        }
+        CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
     }
-    CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
     size_t P = (size_t)S * K;                                 // upper bound on local (token, expert) pairs
     int ntiles_max = (int)((P + T - 1) / T) + (m->e_hi - m->e_lo);
     if ((size_t)ntiles_max > P + (size_t)(m->e_hi - m->e_lo)) ntiles_max = (int)(P + (size_t)(m->e_hi - m->e_lo));
     if (ntiles_max > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "moe: %d tiles in one call; split the batch", ntiles_max);
     MoePlanArgs pa; memset(&pa, 0, sizeof pa);
-    pa.idx = m->idx; pa.S = S; pa.K = K; pa.E = E; pa.e_lo = m->e_lo; pa.e_hi = m->e_hi; pa.T = T; pa.order = order; pa.q8 = q8;
+    pa.idx = idxp; pa.S = S; pa.K = K; pa.E = E; pa.e_lo = m->e_lo; pa.e_hi = m->e_hi; pa.T = T; pa.order = order; pa.q8 = q8;
     if (q8) {
         pa.g8 = (const int8_t *)m->g; pa.u8 = (const int8_t *)m->u; pa.d8 = (const int8_t *)m->d;
         pa.gs = (const float *)m->gs; pa.us = (const float *)m->us; pa.ds = (const float *)m->ds;
@@ -768,7 +786,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         b.tiles = (const Q4Tile *)m->t_down; b.y = (float *)c->h.p;
         CKR(launch_q4r4_small(b, c->sms, st));
     }
-    CKR(launch_moe_combine(out, (const float *)c->h.p, m->w, m->pos_of, m->ord, S, K, D, st));
+    CKR(launch_moe_combine(out, (const float *)c->h.p, wp, m->pos_of, m->ord, S, K, D, st));
     if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, P * 4, cudaMemcpyDeviceToDevice, st));
     if (w_out) CK(cudaMemcpyAsync(w_out, m->w, P * 4, cudaMemcpyDeviceToDevice, st));
     return 0;
@@ -782,7 +800,7 @@ extern "C" int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const flo
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
     CK(cudaSetDevice(m->device));
     if (S <= 0) return 0;
-    return moe_apply_on(c, m, out_dev, x_dev, S, logits_dev, order, norm_topk, idx_dev, w_dev, pick_stream(c, stream));
+    return moe_apply_on(c, m, out_dev, x_dev, S, logits_dev, order, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream));
 }
 
 static int moe_host(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits, int order, int norm) {
@@ -801,7 +819,7 @@ static int moe_host(MotyCudaMoe *m, float *out, const float *x, int S, const flo
         CK(cudaMemcpyAsync(c->dlogits.p, logits, lb, cudaMemcpyHostToDevice, c->stream));
         dl = (const float *)c->dlogits.p;
     }
-    CKR(moe_apply_on(c, m, (float *)c->dy.p, (const float *)c->dx.p, S, dl, order, norm, nullptr, nullptr, c->stream));
+    CKR(moe_apply_on(c, m, (float *)c->dy.p, (const float *)c->dx.p, S, dl, order, norm, nullptr, nullptr, nullptr, c->stream));
     CK(cudaMemcpyAsync(out, c->dy.p, xb, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     return 0;
@@ -817,4 +835,26 @@ extern "C" int moty_cuda_moe_batch(MotyCudaMoe *m, float *out, const float *x, i
 
 extern "C" int moty_cuda_olmoe_moe(MotyCudaMoe *m, float *out, const float *x, int S, const float *logits, int norm_topk) {
     return moe_host(m, out, x, S, logits, 0, norm_topk);
+}
+
+// ---------------------------------------------------------------------------
+// expert-parallel building blocks (device pointers)
+// ---------------------------------------------------------------------------
+extern "C" int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_dev, const int *eid_dev,
+                                         int P, void *stream) {
+    if (!m || !h_dev || !x_rows_dev || !eid_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_experts_dev: null argument");
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    CK(cudaSetDevice(m->device));
+    if (P <= 0) return 0;
+    return moe_apply_on(c, m, h_dev, x_rows_dev, P, nullptr, 0, 0, nullptr, nullptr, eid_dev, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_moe_combine_dev(float *out_dev, const float *h_dev, const float *w_dev, const int *idx_dev,
+                                         int S, int K, int D, int order, void *stream) {
+    if (!out_dev || !h_dev || !w_dev || !idx_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: null argument");
+    if (S <= 0) return 0;
+    if (K < 1 || K > 64 || D < 1) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: K=%d D=%d", K, D);
+    DevCtx *c; CKR(ctx0(&c));
+    return launch_moe_combine_sk(out_dev, h_dev, w_dev, idx_dev, S, K, D, order, pick_stream(c, stream));
 }

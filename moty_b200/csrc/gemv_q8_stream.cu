@@ -177,9 +177,19 @@ template <int NS, int R, int LPR, bool FUSED>
 static int launch_t(const StreamArgs &a, int sms, cudaStream_t st) {
     size_t smem = FUSED ? (a.I <= 4096 ? (size_t)a.I * 5 : (size_t)a.I) : (size_t)NS * a.I;
     auto k = q8_stream_kernel<NS, R, LPR, FUSED>;
-    if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    int per_sm = 0;
-    CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, k, 256, smem));
+    // the occupancy query costs a few microseconds of host time: remember the last answer
+    // (all GPUs a process drives are the same model)
+    static size_t cached_smem[MOTY_MAX_DEV];
+    static int cached_per_sm[MOTY_MAX_DEV];
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q8_stream: device %d", dev);
+    if (smem + 1 != cached_smem[dev]) {                         // stored +1 so that zero-init means "nothing cached"
+        if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached_per_sm[dev], k, 256, smem));
+        cached_smem[dev] = smem + 1;
+    }
+    int per_sm = cached_per_sm[dev];
     if (per_sm < 1) return moty_set_error(MOTY_CUDA_ELIMIT, "q8_stream: kernel does not fit (smem %zu)", smem);
     int nunits = ((a.O + R - 1) / R) * a.KS;
     int ctas = sms * per_sm;

@@ -158,6 +158,46 @@ int launch_moe_combine(float *out, const float *h, const float *w, const int *po
     return 0;
 }
 
+// The same ordered combine for expert outputs laid out per selection, h[(s*K + k)][D]
+// (what comes back from an expert-parallel exchange): one CTA per token; order 0 =
+// selection order, 1 = ascending expert id.
+__global__ void __launch_bounds__(256) moe_combine_sk_kernel(float *__restrict__ out, const float *__restrict__ h,
+                                                             const float *__restrict__ w, const int *__restrict__ idx,
+                                                             int K, int D, int order) {
+    __shared__ int ord[64];
+    __shared__ float ws[64];
+    const int s = blockIdx.x;
+    if (threadIdx.x == 0) {
+        for (int k = 0; k < K; k++) ord[k] = k;
+        if (order == 1) {
+            const int *ix = idx + (size_t)s * K;
+            for (int k = 1; k < K; k++) {
+                int v = ord[k], j = k - 1;
+                while (j >= 0 && ix[ord[j]] > ix[v]) { ord[j + 1] = ord[j]; j--; }
+                ord[j + 1] = v;
+            }
+        }
+        for (int k = 0; k < K; k++) ws[k] = w[(size_t)s * K + k];
+    }
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float acc = 0.f;
+        for (int j = 0; j < K; j++) {
+            int k = ord[j];
+            acc = fmaf(ws[k], h[((size_t)s * K + k) * D + d], acc);
+        }
+        out[(size_t)s * D + d] = acc;
+    }
+}
+
+int launch_moe_combine_sk(float *out, const float *h, const float *w, const int *idx,
+                          int S, int K, int D, int order, cudaStream_t st) {
+    if (S <= 0) return 0;
+    moe_combine_sk_kernel<<<S, 256, 0, st>>>(out, h, w, idx, K, D, order);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 // ---------------------------------------------------------------------------
 // f32 matrix (router of an engine that keeps it unquantized): one warp per
 // output row, f32 accumulation.  Outside the quantized path; the summation

@@ -22,4 +22,6 @@ struct MoePlanArgs {
 int launch_moe_plan(const MoePlanArgs &a, cudaStream_t st);
 int launch_moe_combine(float *out, const float *h, const float *w, const int *pos_of, const int *ord,
                        int S, int K, int D, cudaStream_t st);
+int launch_moe_combine_sk(float *out, const float *h, const float *w, const int *idx,
+                          int S, int K, int D, int order, cudaStream_t st);
 int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st);
