@@ -225,7 +225,7 @@ extern "C" int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *
 // ---------------------------------------------------------------------------
 // mat_apply
 // ---------------------------------------------------------------------------
-static const int Q8_TC_MIN_S = 16;
+static const int Q8_TC_MIN_S = 9;
 
 static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int S, int32_t *acc, cudaStream_t st) {
     if (S <= 0) return 0;
@@ -234,7 +234,11 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (I > MOTY_QROW_MAX)
         return moty_set_error(MOTY_CUDA_ELIMIT, "mat_apply: I=%d exceeds %d (the reference switches to an f32 path there)", I, MOTY_QROW_MAX);
     if (w->fmt == MOTY_WF_I8) {
-        const bool stream_ok = I % 16 == 0 && S <= 8;
+        // more than 8 rows go to the tensor cores (a 16-token tile, rows past S are zero fill);
+        // up to 8 rows stream through the dp4a GEMV
+        const bool vec = I % 16 == 0;
+        const bool tc = vec && S >= Q8_TC_MIN_S && w->has_tmap && q8_tc_supported(S, I, O);
+        const bool stream_ok = vec && !tc && S <= 64;
         if (stream_ok && I > 4096) CKR(moty_grow_zero(c, &c->kcell, (size_t)8 * O * 8));
         if (stream_ok && S == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)
             return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, x, nullptr, nullptr, y, acc,
@@ -242,14 +246,20 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
-        if (stream_ok)
-            return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, nullptr, (const int8_t *)c->xi.p,
-                                    (const float *)c->sx.p, y, acc, S, I, O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, st);
-        if (I % 16 != 0)
+        if (tc) return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
+        if (stream_ok) {
+            for (int s0 = 0; s0 < S; s0 += 8) {
+                int ns = S - s0 < 8 ? S - s0 : 8;
+                CKR(launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, nullptr,
+                                     (const int8_t *)c->xi.p + (size_t)s0 * I, (const float *)c->sx.p + s0,
+                                     y + (size_t)s0 * O, acc ? acc + (size_t)s0 * O : nullptr, ns, I, O, c->ctr,
+                                     (unsigned long long *)c->kcell.p, c->sms, st));
+            }
+            return 0;
+        }
+        if (!vec)
             return launch_q8_any((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
                                  (const float *)c->sx.p, y, acc, S, I, O, st);
-        if (S >= Q8_TC_MIN_S && w->has_tmap && q8_tc_supported(S, I, O))
-            return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
         Q8Args a; memset(&a, 0, sizeof a);
         a.w = (const int8_t *)w->codes; a.scale = (const float *)w->scales;
         a.xi = (const int8_t *)c->xi.p; a.sx = (const float *)c->sx.p;
@@ -259,12 +269,26 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (acc) return moty_set_error(MOTY_CUDA_EARG, "int32 accumulators exist for MOTY_WF_I8 only");
     if (w->fmt == MOTY_WF_Q4R4) {
         int nb = I / 32;
+        if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q4R4 needs I %% 32 == 0");
+        if (S == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)   // decode: one launch, the row is group-quantized in the kernel
+            return launch_q4r4_stream((const uint8_t *)w->codes, (const uint16_t *)w->scales, x, nullptr, nullptr, nullptr,
+                                      nullptr, y, 1, I, O, c->sms, st);
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
         CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
         CKR(moty_grow(c, &c->misc, (size_t)S + 16));
         CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
         CKR(launch_q4r4_forms((uint8_t *)c->misc.p, S, st));
+        if (S <= 32) {                                // small batches: the streaming kernel once per 4 rows
+            for (int s0 = 0; s0 < S; s0 += 4) {
+                int ns = S - s0 < 4 ? S - s0 : 4;
+                CKR(launch_q4r4_stream((const uint8_t *)w->codes, (const uint16_t *)w->scales, nullptr,
+                                       (const int8_t *)c->xi.p + (size_t)s0 * I, (const float *)c->xs.p + (size_t)s0 * nb,
+                                       (const int32_t *)c->xsum.p + (size_t)s0 * nb, (const uint8_t *)c->misc.p + s0,
+                                       y + (size_t)s0 * O, ns, I, O, c->sms, st));
+            }
+            return 0;
+        }
         Q4Args a; memset(&a, 0, sizeof a);
         a.w = (const uint8_t *)w->codes; a.d = (const uint16_t *)w->scales;
         a.xq = (const int8_t *)c->xi.p; a.xs = (const float *)c->xs.p; a.xsum = (const int32_t *)c->xsum.p;

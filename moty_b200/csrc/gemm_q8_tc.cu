@@ -3,15 +3,16 @@
 //   acc[o][s] = sum_i W[o][i] * xi[s][i]       int8 x int8 -> int32, exact
 //   y[s][o]   = (scale[o] * sx[s]) * (float)acc (nn/matmul.c:29-36)
 //
-// One CTA computes a 128 (output rows) x BN (tokens) tile:
+// Persistent CTAs (one per SM) walk over 128 (output rows) x BN (tokens) tiles:
 //   warp 0   producer: TMA loads of the W tile [128 x 128 B] and the activation
 //            tile [BN x 128 B] into a STAGES-deep shared-memory ring, 128-byte swizzle,
 //            completion on mbarriers (per-CTA loads only, no multicast);
 //   warp 1   issues tcgen05.mma.cta_group::1.kind::i8 (M=128, N=BN, K=32; four per
-//            128-byte K block) accumulating int32 in TMEM, tcgen05.commit frees the
-//            ring slots and finally signals the epilogue;
+//            128-byte K block) accumulating int32 in one of two TMEM accumulators,
+//            tcgen05.commit frees the ring slots and finally signals the epilogue;
 //   warps 2-5 epilogue: tcgen05.ld of their 32-lane TMEM quarter, scale, coalesced
-//            stores of y (32 consecutive output rows per instruction).
+//            stores of y (32 consecutive output rows per instruction), overlapped with
+//            the MMAs of the next tile through the second accumulator.
 // W is the A operand so that M = 128 weight rows fill the tensor-core datapath even
 // when only 16 tokens are present; the kernel is then HBM-bound on the weights.
 //
@@ -86,26 +87,32 @@ struct TcArgs {
     int *err;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                        const __grid_constant__ CUtensorMap mapB, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-    constexpr int A_BYTES = BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
-    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar;
+    // MT = 2: two 128-row weight sub-tiles share one activation tile (half the activation bytes per
+    // MAC through shared memory); their two accumulators fill TMEM, so no double buffering then
+    constexpr int A_BYTES = MT * BM * BKB, B_BYTES = BN * BKB, STAGE_BYTES = A_BYTES + B_BYTES;
+    constexpr int NBUF = (2 * MT * BN <= 512) ? 2 : 1;
+    __shared__ uint64_t full_bar[STAGES], empty_bar[STAGES], tmem_full_bar[2], tmem_empty_bar[2];
     __shared__ uint32_t tmem_base_s;
     __shared__ int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * BM, n0 = blockIdx.y * BN;
     const int nkb = (a.I + BKB - 1) / BKB;
-    constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;
+    const int ntn = (a.S + BN - 1) / BN, ntm = (a.O + MT * BM - 1) / (MT * BM);
+    const int ntiles = ntm * ntn;
+    const int krot = (int)((blockIdx.x * 5u) % (unsigned)nkb);
+    // two accumulators of BN columns: the epilogue of one tile overlaps the MMAs of the next
+    constexpr uint32_t TMEM_COLS = NBUF * MT * BN < 32 ? 32 : NBUF * MT * BN;
 
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int i = 0; i < STAGES; i++) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-        mbar_init(&tmem_full_bar, 1);
+        for (int i = 0; i < 2; i++) { mbar_init(&tmem_full_bar[i], 1); mbar_init(&tmem_empty_bar[i], 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -119,61 +126,90 @@ __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ C
     const uint32_t tmem_base = tmem_base_s;
     volatile int *abort_flag = &abort_s;
 
+    // Persistent over output tiles.  Consecutive tile numbers share the weight rows (same m,
+    // next n), so CTAs running side by side fetch the same W tile and the second fetch hits L2.
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < nkb; kb++) {
-                int st = kb % STAGES;
-                uint32_t ph = (kb / STAGES) & 1;
-                if (!mbar_wait(&empty_bar[st], ph ^ 1, abort_flag)) break;
-                mbar_expect_tx(&full_bar[st], STAGE_BYTES);
-                uint8_t *sa = smem + (size_t)st * STAGE_BYTES;
-                tma_load_2d(sa, &mapA, kb * BKB, m0, &full_bar[st]);
-                tma_load_2d(sa + A_BYTES, &mapB, kb * BKB, n0, &full_bar[st]);
+            uint32_t it = 0;                                         // ring position, continuous across tiles
+            for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
+                const int m0 = (t / ntn) * MT * BM, n0 = (t % ntn) * BN;
+                bool ok = true;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int st = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    ok = mbar_wait(&empty_bar[st], ph ^ 1, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(&full_bar[st], STAGE_BYTES);
+                    uint8_t *sa = smem + (size_t)st * STAGE_BYTES;
+                    // every CTA starts its K loop at another block: integer accumulation is order
+                    // independent, and the CTAs stop hammering the same activation tile in L2 together
+                    const int kr = (kb + krot) % nkb;
+                    tma_load_2d(sa, &mapA, kr * BKB, m0, &full_bar[st]);
+                    if (MT == 2) tma_load_2d(sa + BM * BKB, &mapA, kr * BKB, m0 + BM, &full_bar[st]);
+                    tma_load_2d(sa + A_BYTES, &mapB, kr * BKB, n0, &full_bar[st]);
+                }
+                if (!ok) break;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             // instruction descriptor: D = s32, A = B = signed int8, both K-major, N = BN, M = 128
             const uint32_t idesc = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t it = 0, tl = 0;
             bool ok = true;
-            for (int kb = 0; kb < nkb && ok; kb++) {
-                int st = kb % STAGES;
-                uint32_t ph = (kb / STAGES) & 1;
-                ok = mbar_wait(&full_bar[st], ph, abort_flag);
+            for (int t = blockIdx.x; t < ntiles && ok; t += gridDim.x, tl++) {
+                const uint32_t buf = tl % NBUF, use = tl / NBUF;
+                ok = mbar_wait(&tmem_empty_bar[buf], (use & 1) ^ 1, abort_flag);   // epilogue has drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                uint32_t sa = smem_u32(smem + (size_t)st * STAGE_BYTES);
-                uint32_t sb = sa + A_BYTES;
+                const uint32_t tacc = tmem_base + buf * MT * BN;
+                for (int kb = 0; kb < nkb; kb++, it++) {
+                    const int st = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    ok = mbar_wait(&full_bar[st], ph, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_u32(smem + (size_t)st * STAGE_BYTES);
+                    const uint32_t sb = sa + A_BYTES;
 #pragma unroll
-                for (int k4 = 0; k4 < BKB / 32; k4++) {
-                    if (kb * BKB + k4 * 32 >= a.I) break;                  // nothing but zero fill beyond I
-                    umma_i8(tmem_base, umma_desc(sa + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
+                    for (int k4 = 0; k4 < BKB / 32; k4++) {
+                        if (((kb + krot) % nkb) * BKB + k4 * 32 >= a.I) break;   // nothing but zero fill beyond I
+                        umma_i8(tacc, umma_desc(sa + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
+                        if (MT == 2)
+                            umma_i8(tacc + BN, umma_desc(sa + BM * BKB + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
+                    }
+                    umma_commit(&empty_bar[st]);                           // slot reusable when these MMAs retire
                 }
-                umma_commit(&empty_bar[st]);                               // slot reusable when these MMAs retire
+                if (ok) umma_commit(&tmem_full_bar[buf]);                  // accumulator complete
             }
-            if (ok) umma_commit(&tmem_full_bar);                           // accumulator complete
         }
     } else {
         // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
         const int q = warp & 3;
-        // one lane waits, the warp follows its verdict (tcgen05.ld is warp-collective)
-        int ok = lane == 0 ? (int)mbar_wait(&tmem_full_bar, 0, abort_flag) : 1;
-        ok = __shfl_sync(0xffffffffu, ok, 0);
-        if (ok) {
+        uint32_t tl = 0;
+        for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
+            const int m0 = (t / ntn) * MT * BM, n0 = (t % ntn) * BN;
+            const uint32_t buf = tl % NBUF, use = tl / NBUF;
+            // one lane waits, the warp follows its verdict (tcgen05.ld is warp-collective)
+            int ok = lane == 0 ? (int)mbar_wait(&tmem_full_bar[buf], use & 1, abort_flag) : 1;
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int o = m0 + q * 32 + lane;
+#pragma unroll 1
+            for (int mt = 0; mt < MT; mt++) {
+            const int o = m0 + mt * BM + q * 32 + lane;
             const float sc = o < a.O ? __ldg(a.scale + o) : 0.f;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (n0 + c0 >= a.S) break;                                 // warp-uniform
                 uint32_t r[16];
-                uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt) * BN + (uint32_t)c0;
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                       "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                     : "r"(taddr));
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (n0 + c0 >= a.S) break;
 #pragma unroll
                 for (int j = 0; j < 16; j++) {
                     int s = n0 + c0 + j;
@@ -184,6 +220,12 @@ __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ C
                     }
                 }
             }
+            }
+            // this warp is done reading the accumulator: hand it back to the MMA warp
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&tmem_empty_bar[buf])) : "memory");
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -233,17 +275,18 @@ int make_map(CUtensorMap *m, const void *base, int rows, int cols, int box_rows)
     return 0;
 }
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, int MT>
 int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi, const float *sx, float *y, int32_t *acc,
                 int S, DevCtx *c, cudaStream_t st) {
     CUtensorMap mapB;
     CKR(make_map(&mapB, xi, S, w->I, BN));
-    size_t smem = (size_t)STAGES * (BM * BKB + BN * BKB) + 1024;
-    auto k = q8_tc_kernel<BN, STAGES>;
+    size_t smem = (size_t)STAGES * (MT * BM * BKB + BN * BKB) + 1024;
+    auto k = q8_tc_kernel<BN, STAGES, MT>;
     CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     TcArgs a;
     a.scale = (const float *)w->scales; a.sx = sx; a.y = y; a.acc = acc; a.S = S; a.I = w->I; a.O = w->O; a.err = c->err_dev;
-    dim3 grid((w->O + BM - 1) / BM, (S + BN - 1) / BN);
+    int ntiles = ((w->O + MT * BM - 1) / (MT * BM)) * ((S + BN - 1) / BN);
+    int grid = ntiles < c->sms ? ntiles : c->sms;             // persistent: one CTA per SM
     k<<<grid, 192, smem, st>>>(mapA, mapB, a);
     CK(cudaGetLastError());
     return 0;
@@ -252,7 +295,7 @@ int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi,
 }  // namespace
 
 // the tensor map wants 16-byte row strides; rows shorter than one K block gain nothing
-bool q8_tc_supported(int S, int I, int O) { return S >= 16 && I % 16 == 0 && I >= 128 && O >= 1; }
+bool q8_tc_supported(int S, int I, int O) { return S >= 9 && I % 16 == 0 && I >= 128 && O >= 1; }
 
 int q8_tc_make_tmap(MotyCudaMat *m) {
     m->has_tmap = false;
@@ -266,9 +309,16 @@ int q8_tc_make_tmap(MotyCudaMat *m) {
 int launch_q8_tc(const MotyCudaMat *w, const int8_t *xi, const float *sx, float *y, int32_t *acc,
                  int S, DevCtx *c, cudaStream_t st) {
     const CUtensorMap &mapA = *reinterpret_cast<const CUtensorMap *>(w->tmap);
-    if (S <= 16) return launch_tc_t<16, 8>(mapA, w, xi, sx, y, acc, S, c, st);
-    if (S <= 32) return launch_tc_t<32, 8>(mapA, w, xi, sx, y, acc, S, c, st);
-    if (S <= 64) return launch_tc_t<64, 6>(mapA, w, xi, sx, y, acc, S, c, st);
-    if (S <= 128) return launch_tc_t<128, 6>(mapA, w, xi, sx, y, acc, S, c, st);
-    return launch_tc_t<256, 4>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 16) return launch_tc_t<16, 8, 1>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 32) return launch_tc_t<32, 8, 1>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 64) return launch_tc_t<64, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (S <= 128) return launch_tc_t<128, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
+    // Large batches are bound by the bytes that reach shared memory per MAC.  256 x 256 tiles (two
+    // accumulators, no epilogue overlap) pay off when K is long and there are enough tiles for every
+    // SM; with few 128 x 256 tiles the batch is cut into 128-token tiles so that more SMs take part.
+    const long long t256 = (long long)((w->O + 127) / 128) * ((S + 255) / 256);
+    if (w->I >= 2048 && (long long)((w->O + 255) / 256) * ((S + 255) / 256) >= c->sms)
+        return launch_tc_t<256, 3, 2>(mapA, w, xi, sx, y, acc, S, c, st);
+    if (t256 * 10 < (long long)c->sms * 6) return launch_tc_t<128, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
+    return launch_tc_t<256, 4, 1>(mapA, w, xi, sx, y, acc, S, c, st);
 }

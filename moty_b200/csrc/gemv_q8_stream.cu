@@ -223,7 +223,8 @@ int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const 
     a.seg = (I16 + a.KS - 1) / a.KS;
     if (a.KS > 1 && !cell) return moty_set_error(MOTY_CUDA_EARG, "q8_stream: K-split cells missing");
     int lpr = (a.seg + 31) / 32;                     // 128-bit loads per lane and row
-    if (S == 1) return launch_ns<1, true>(a, lpr, sms, st);
+    if (S == 1 && x) return launch_ns<1, true>(a, lpr, sms, st);     // f32 row: quantized inside the kernel
+    if (S == 1) return launch_ns<1, false>(a, lpr, sms, st);         // already quantized (tail of a chunked batch)
     if (S == 2) return launch_ns<2, false>(a, lpr, sms, st);
     if (S <= 4) return launch_ns<4, false>(a, lpr, sms, st);
     return launch_ns<8, false>(a, lpr, sms, st);

@@ -81,3 +81,8 @@ int launch_argmax_scratch(const float *v, int n, int *out, float *pv, int *pi, c
 
 // ---- moe.cu / ffn -------------------------------------------------------------------
 int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st);
+
+// ---- q4r4_stream.cu -------------------------------------------------------------------
+// persistent Q4R4 GEMV for 1..4 rows; S == 1 with x != null quantizes the row in the kernel
+int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, const int8_t *xq, const float *xs,
+                       const int32_t *xsum, const uint8_t *form, float *y, int S, int I, int O, int sms, cudaStream_t st);

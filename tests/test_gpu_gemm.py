@@ -9,7 +9,7 @@ from conftest import same_bits
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("O,I", [(128, 128), (256, 1024), (1000, 1024), (130, 3072), (515, 3840), (64, 15360), (300, 144), (77, 2064)])
+@pytest.mark.parametrize("O,I", [(128, 128), (256, 1024), (1000, 1024), (130, 3072), (515, 3840), (64, 15360), (300, 144), (77, 2064), (9600, 256)])
 @pytest.mark.parametrize("S", [16, 17, 32, 48, 64, 100, 128, 200, 256, 300, 512])
 def test_q8_gemm_vs_oracle(gpu, oracle, O, I, S):
     rng = np.random.default_rng(O + 31 * I + S)
@@ -45,3 +45,15 @@ def test_batch_equals_rows_at_full_size(gpu):
     # linearity of the integer part: doubling an activation row keeps its codes (the scale doubles)
     y2 = gpu.mat_apply(W, 2 * x[:16])
     assert same_bits(y2, 2 * yb[:16])
+
+
+@pytest.mark.parametrize("O,I,S", [(19000, 2048, 300), (19100, 384, 300)])
+def test_q8_gemm_256_row_tiles_vs_oracle(gpu, oracle, O, I, S):
+    """Shapes with enough 256 x 256 tiles to take the two-accumulator variant, ragged in O and S."""
+    rng = np.random.default_rng(O + I + S)
+    Wq = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    y, acc = gpu.mat_apply(gpu.Mat.i8(Wq, sc), x, want_acc=True)
+    yo, acco = oracle.matmul_q_s(x, Wq, sc, want_acc=True)
+    assert np.array_equal(acc, acco), f"{(acc != acco).sum()} accumulators differ"
+    assert same_bits(y, yo)
