@@ -218,7 +218,59 @@ def run_extras(torch, mb, dev, stream, W8, local):
                 out["rows"].append({"fmt": fmt, "S": S, "O": O, "I": I, "us": round(us, 2),
                                     "GBs": round(nbytes / us / 1e3, 1), "TOPS": round(2.0 * S * O * I / us / 1e6, 2)})
             del xs, ys
+    del W4
+    out["moe"] = run_moe_extras(torch, mb, dev, stream, local)
     return out
+
+
+def run_moe_extras(torch, mb, dev, stream, local):
+    """One routed MoE layer, decode (S=1) and a small prefill batch, on the two MoE shapes of the
+    baseline: OLMoE-1B-7B (E=64, K=8, expert FFN 1024, hidden 2048, int8 experts) and
+    Qwen3-30B-A3B (E=128, K=8, expert FFN 768, hidden 2048, Q4R4 experts).  Four layers with
+    different weights are cycled so that a layer's experts are not L2-resident when it runs.
+    Bytes = the K selected experts' gate+up+down (codes and scales)."""
+    sp = stream.cuda_stream
+    rng = np.random.default_rng(2)
+    rows = []
+    for name, E, K, I, D, fmt in (("olmoe", 64, 8, 1024, 2048, mb.WF_I8), ("qwen3-30b-a3b", 128, 8, 768, 2048, mb.WF_Q4R4)):
+        layers = []
+        for _ in range(4):
+            m = mb.Moe(E, K, I, D, efmt=fmt, device=local)
+            for e in range(E):
+                if fmt == mb.WF_I8:
+                    g = rng.integers(-127, 128, (I, D), dtype=np.int8); u = rng.integers(-127, 128, (I, D), dtype=np.int8)
+                    d = rng.integers(-127, 128, (D, I), dtype=np.int8)
+                    gs = rng.uniform(0.001, 0.02, I).astype(np.float32); us = rng.uniform(0.001, 0.02, I).astype(np.float32)
+                    ds = rng.uniform(0.001, 0.02, D).astype(np.float32)
+                else:
+                    ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
+                    g = rng.integers(0, 256, ng * 64, dtype=np.uint8); u = rng.integers(0, 256, ng * 64, dtype=np.uint8)
+                    d = rng.integers(0, 256, nd * 64, dtype=np.uint8)
+                    gs = np.full(ng * 4, 0x1A00, np.uint16); us = np.full(ng * 4, 0x1A00, np.uint16); ds = np.full(nd * 4, 0x1A00, np.uint16)
+                m.upload_expert(e, g, gs, u, us, d, ds)
+            layers.append(m)
+        per_expert = (3 * I * D + 4 * (2 * I + D)) if fmt == mb.WF_I8 else (2 * (I // 4) * (D // 32) * 72 + (D // 4) * (I // 32) * 72)
+        with torch.cuda.stream(stream):
+            for S in (1, 64):
+                x = torch.randn((S, D), device=dev)
+                logits = [torch.randn((S, E), device=dev) for _ in range(8)]
+                outp = torch.empty((S, D), device=dev)
+                ev = []
+                for it in range(12):
+                    m = layers[it % 4]
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    m.apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
+                    e1.record(stream)
+                    if it >= 4:
+                        ev.append((e0, e1))
+                torch.cuda.synchronize()
+                us = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3
+                touched = K * per_expert if S == 1 else min(E, S * K) * per_expert
+                rows.append({"layer": name, "S": S, "us": round(us, 1), "expert_GBs": round(touched / us / 1e3, 1)})
+        for m in layers:
+            m.free()
+    return rows
 
 
 # ---------------------------------------------------------------------------

@@ -191,6 +191,12 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
                             const float *logits_dev, int order, int norm_topk,
                             int *idx_dev, float *w_dev, void *stream);
 
+/* One token through int8 experts normally takes a two-kernel streaming path (same
+ * arithmetic, same results as the general grouped path that batches use).  This
+ * switch (1 = on, the default; returns the previous value) lets a test run both
+ * and compare them bit for bit; it has no reference counterpart. */
+int moty_cuda_set_moe_fast_path(int on);
+
 /* Expert-parallel building blocks (no reference counterpart: the reference is one
  * process).  Arithmetic is that of the block entries above, cut at the exchange.
  * moe_experts_dev: P activation rows x_rows [P][D], each with ONE expert id

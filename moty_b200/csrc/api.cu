@@ -710,6 +710,14 @@ static int moe_ensure_plan(MotyCudaMoe *m, int S) {
     return 0;
 }
 
+static int g_moe_fast = 1;
+
+extern "C" int moty_cuda_set_moe_fast_path(int on) {
+    int prev = g_moe_fast;
+    g_moe_fast = on ? 1 : 0;
+    return prev;
+}
+
 // eid_given == null: route the S tokens (softmax + top-K of the logits) and combine their K
 // expert outputs in `order`.  eid_given != null: S rows with ONE given expert each (the rows an
 // expert-parallel peer sent here); out[i] is that expert's output for row i, zero when the
@@ -730,6 +738,18 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             logits = m->logits;
         }
         CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
+    }
+    // decode fast path: one token, int8 experts, selection-order combine -> two streaming kernels
+    if (S == 1 && q8 && !eid_given && order == 0 && g_moe_fast && moe_decode_q8_supported(K, I, D) &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
+        CKR(launch_moe_decode_q8(m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u, (const int8_t *)m->d,
+                                 (const float *)m->gs, (const float *)m->us, (const float *)m->ds,
+                                 m->gcb, m->gsb / 4, m->dcb, m->dsb / 4, x, (float *)c->g.p, out,
+                                 K, I, D, m->e_lo, m->e_hi, c->sms, st));
+        if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+        if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+        return 0;
     }
     size_t P = (size_t)S * K;                                 // upper bound on local (token, expert) pairs
     int ntiles_max = (int)((P + T - 1) / T) + (m->e_hi - m->e_lo);

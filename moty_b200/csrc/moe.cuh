@@ -25,3 +25,10 @@ int launch_moe_combine(float *out, const float *h, const float *w, const int *po
 int launch_moe_combine_sk(float *out, const float *h, const float *w, const int *idx,
                           int S, int K, int D, int order, cudaStream_t st);
 int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st);
+
+// ---- moe_decode.cu: one routed token through int8 experts in two streaming kernels ----
+bool moe_decode_q8_supported(int K, int I, int D);
+int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const int8_t *u, const int8_t *d,
+                         const float *gs, const float *us, const float *ds, size_t gstride, size_t gsstride,
+                         size_t dstride, size_t dsstride, const float *x, float *h, float *out,
+                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st);

@@ -18,6 +18,13 @@
 // runs inside the kernel: it needs no row-wide reduction.
 #include "kernels.cuh"
 
+// unsigned bytes of a times signed bytes of b, accumulated: dp4a.u32.s32
+__device__ __forceinline__ int dp4a_us(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 struct Q4StreamArgs {
     const uint8_t *w; const uint16_t *d;
     const float *x;                                            // FUSED: the f32 row
@@ -42,21 +49,27 @@ __global__ void __launch_bounds__(256) q4r4_stream_kernel(Q4StreamArgs a) {
     const int nblk = (O + 3) / 4, nunits = (nblk + BPW - 1) / BPW, nit = (nb + GS - 1) / GS;
     const int nwarps = gridDim.x * 8, gw = blockIdx.x * 8 + warp;
     const int my_units = gw < nunits ? (nunits - gw + nwarps - 1) / nwarps : 0;
-    const long long total = (long long)my_units * nit;
+    const int total = my_units * nit;                          // steps of this warp (fits an int: < 2^31 / 512 bytes)
 
+    // Loads walk two pointers (codes, scales) that advance by one step; a new unit re-bases them.
     int4 wv[PF]; uint16_t dv[PF];
-    int ld_unit = gw, ld_it = 0; long long ld_j = 0;
+    int ld_unit = gw, ld_it = 0, ld_j = 0;
+    const size_t lane_code = (size_t)gl * 64 + r * 16, lane_scale = (size_t)gl * 4 + r;
+    const uint8_t *lp = a.w + ((size_t)(gw * BPW + blk_in) * nb) * 64 + lane_code;
+    const uint16_t *dp = a.d + ((size_t)(gw * BPW + blk_in) * nb) * 4 + lane_scale;
     auto load_next = [&](int slot) {
         wv[slot] = make_int4(0, 0, 0, 0); dv[slot] = 0;
         if (ld_j < total) {
-            const int g = ld_it * GS + gl, blk = ld_unit * BPW + blk_in;
-            if (g < nb && blk < nblk) {
-                const size_t bg = (size_t)blk * nb + g;
-                wv[slot] = ldg_stream16(a.w + bg * 64 + r * 16);
-                dv[slot] = __ldg(a.d + bg * 4 + r);
+            if (ld_it * GS + gl < nb && ld_unit * BPW + blk_in < nblk) {
+                wv[slot] = ldg_stream16(lp);
+                dv[slot] = __ldg(dp);
             }
-            ld_j++;
-            if (++ld_it == nit) { ld_it = 0; ld_unit += nwarps; }
+            ld_j++; lp += GS * 64; dp += GS * 4;
+            if (++ld_it == nit) {
+                ld_it = 0; ld_unit += nwarps;
+                lp = a.w + ((size_t)(ld_unit * BPW + blk_in) * nb) * 64 + lane_code;
+                dp = a.d + ((size_t)(ld_unit * BPW + blk_in) * nb) * 4 + lane_scale;
+            }
         }
     };
 #pragma unroll
@@ -108,7 +121,7 @@ __global__ void __launch_bounds__(256) q4r4_stream_kernel(Q4StreamArgs a) {
 #pragma unroll
     for (int s = 0; s < NS; s++) acc[s] = 0.f;
     int cur_unit = gw, cur_it = 0;
-    for (long long j0 = 0; j0 < total; j0 += PF) {
+    for (int j0 = 0; j0 < total; j0 += PF) {
 #pragma unroll
         for (int u = 0; u < PF; u++) {
             if (j0 + u >= total) break;                        // warp-uniform
@@ -118,17 +131,24 @@ __global__ void __launch_bounds__(256) q4r4_stream_kernel(Q4StreamArgs a) {
             const int4 w4 = wv[u];
             const float dd = f16bits_to_f32(dv[u]);
             load_next(u);                                      // refill the slot: PF steps stay in flight
-            int4 lo, hi;
-            lo.x = w4.x & 0x0f0f0f0f; hi.x = (w4.x >> 4) & 0x0f0f0f0f;
-            lo.y = w4.y & 0x0f0f0f0f; hi.y = (w4.y >> 4) & 0x0f0f0f0f;
-            lo.z = w4.z & 0x0f0f0f0f; hi.z = (w4.z >> 4) & 0x0f0f0f0f;
-            lo.w = w4.w & 0x0f0f0f0f; hi.w = (w4.w >> 4) & 0x0f0f0f0f;
+            // low nibbles as they are; high nibbles stay in place (16 x their value) and are read as
+            // UNSIGNED bytes by dp4a, the exact factor 16 is shifted out of the sum afterwards
+            int4 lo; uint4 hi;
+            lo.x = w4.x & 0x0f0f0f0f; hi.x = (unsigned)w4.x & 0xf0f0f0f0u;
+            lo.y = w4.y & 0x0f0f0f0f; hi.y = (unsigned)w4.y & 0xf0f0f0f0u;
+            lo.z = w4.z & 0x0f0f0f0f; hi.z = (unsigned)w4.z & 0xf0f0f0f0u;
+            lo.w = w4.w & 0x0f0f0f0f; hi.w = (unsigned)w4.w & 0xf0f0f0f0u;
             float fs[NS], c0[NS], c1[NS];
 #pragma unroll
             for (int s = 0; s < NS; s++) {
                 const int4 *xg = reinterpret_cast<const int4 *>(xq_s + (size_t)s * I + gc * 32);
-                int sraw = dp4a4(lo, xg[0], 0);
-                sraw = dp4a4(hi, xg[1], sraw);
+                const int4 x0 = xg[0], x1 = xg[1];
+                int sraw = dp4a4(lo, x0, 0);
+                int s16 = dp4a_us(hi.x, x1.x, 0);
+                s16 = dp4a_us(hi.y, x1.y, s16);
+                s16 = dp4a_us(hi.z, x1.z, s16);
+                s16 = dp4a_us(hi.w, x1.w, s16);
+                sraw += s16 >> 4;
                 const float xsc = xs_s[s * nb + gc];
                 const int xsm = xsum_s[s * nb + gc];
                 c0[s] = __fmul_rn(dd, xsc);

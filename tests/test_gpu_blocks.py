@@ -107,3 +107,30 @@ def test_expert_shards_sum_to_the_whole(gpu, oracle):
             m.upload_expert(e, g["moe_g"][e], g["moe_gs"][e], g["moe_u"][e], g["moe_us"][e], g["moe_d"][e], g["moe_ds"][e])
         total += m.batch(g["moe_x9"], g["moe_logits9"])
     assert close(total, whole)
+
+
+@pytest.mark.parametrize("E,K,I,D,lo,hi", [(64, 8, 1024, 2048, 0, 64), (16, 4, 96, 160, 0, 16), (16, 4, 96, 160, 4, 12), (8, 8, 48, 2048, 0, 8)])
+def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, hi):
+    """The two-kernel decode path and the grouped path are the same arithmetic: bit-identical,
+    also on an expert shard (non-resident experts contribute nothing)."""
+    from oracle import Experts
+    rng = np.random.default_rng(E * K + I + lo)
+    g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
+    d = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
+    gs, us = (rng.uniform(0.001, 0.02, (E, I)).astype(np.float32) for _ in range(2))
+    ds = rng.uniform(0.001, 0.02, (E, D)).astype(np.float32)
+    m = gpu.Moe(E, K, I, D, e_lo=lo, e_hi=hi)
+    for e in range(lo, hi):
+        m.upload_expert(e, g[e], gs[e], u[e], us[e], d[e], ds[e])
+    for trial in range(3):
+        x = rng.standard_normal((1, D)).astype(np.float32)
+        logits = (rng.standard_normal((1, E)) * 0.5).astype(np.float32)
+        prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
+        fast = m.d1(x, logits); fast_ol = m.olmoe(x, logits, 0)
+        gpu.lib().moty_cuda_set_moe_fast_path(0)
+        slow = m.d1(x, logits); slow_ol = m.olmoe(x, logits, 0)
+        gpu.lib().moty_cuda_set_moe_fast_path(prev)
+        assert same_bits(fast, slow) and same_bits(fast_ol, slow_ol)
+    if (lo, hi) == (0, E):
+        want = oracle.moe_d1(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0]
+        assert close(fast, want, 2e-3)
