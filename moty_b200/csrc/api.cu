@@ -751,6 +751,17 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
         return 0;
     }
+    if (S == 1 && !q8 && !eid_given && order == 0 && g_moe_fast && moe_decode_q4_supported(K, I, D) &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
+        CKR(launch_moe_decode_q4(m->idx, m->w, (const uint8_t *)m->g, (const uint8_t *)m->u, (const uint8_t *)m->d,
+                                 (const uint16_t *)m->gs, (const uint16_t *)m->us, (const uint16_t *)m->ds,
+                                 m->gcb, m->gsb / 2, m->dcb, m->dsb / 2, x, (float *)c->g.p, out,
+                                 K, I, D, m->e_lo, m->e_hi, c->sms, st));
+        if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+        if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+        return 0;
+    }
     size_t P = (size_t)S * K;                                 // upper bound on local (token, expert) pairs
     int ntiles_max = (int)((P + T - 1) / T) + (m->e_hi - m->e_lo);
     if ((size_t)ntiles_max > P + (size_t)(m->e_hi - m->e_lo)) ntiles_max = (int)(P + (size_t)(m->e_hi - m->e_lo));

@@ -32,3 +32,10 @@ int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const 
                          const float *gs, const float *us, const float *ds, size_t gstride, size_t gsstride,
                          size_t dstride, size_t dsstride, const float *x, float *h, float *out,
                          int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st);
+
+// ---- moe_decode_q4.cu: the same for Q4R4 experts ----
+bool moe_decode_q4_supported(int K, int I, int D);
+int launch_moe_decode_q4(const int *idx, const float *w, const uint8_t *g, const uint8_t *u, const uint8_t *d,
+                         const uint16_t *gs, const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
+                         size_t dstride, size_t dsstride, const float *x, float *h, float *out,
+                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st);

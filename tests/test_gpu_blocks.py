@@ -134,3 +134,35 @@ def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, h
     if (lo, hi) == (0, E):
         want = oracle.moe_d1(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0]
         assert close(fast, want, 2e-3)
+
+
+@pytest.mark.parametrize("E,K,I,D,lo,hi", [(16, 4, 96, 128, 0, 16), (128, 8, 768, 2048, 0, 128), (16, 4, 96, 128, 8, 16)])
+def test_moe_q4r4_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, hi):
+    from oracle import Experts
+    rng = np.random.default_rng(E + I + lo)
+    small = E <= 16
+    if small:
+        packs = {k: [oracle.pack_q4r4((rng.standard_normal(shape) * 0.05).astype(np.float32)) for _ in range(E)]
+                 for k, shape in (("g", (I, D)), ("u", (I, D)), ("d", (D, I)))}
+    else:                                      # random codes and f16 scales: packing 128 experts on the CPU is slow
+        ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
+        mk = lambda n: (rng.integers(0, 256, n * 64, dtype=np.uint8),
+                        rng.uniform(0.001, 0.01, n * 4).astype(np.float16).view(np.uint16))
+        packs = {"g": [mk(ng) for _ in range(E)], "u": [mk(ng) for _ in range(E)], "d": [mk(nd) for _ in range(E)]}
+    m = gpu.Moe(E, K, I, D, efmt=gpu.WF_Q4R4, e_lo=lo, e_hi=hi)
+    for e in range(lo, hi):
+        m.upload_expert(e, packs["g"][e][0], packs["g"][e][1], packs["u"][e][0], packs["u"][e][1],
+                        packs["d"][e][0], packs["d"][e][1])
+    for trial in range(3):
+        x = rng.standard_normal((1, D)).astype(np.float32)
+        logits = (rng.standard_normal((1, E)) * 0.5).astype(np.float32)
+        prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
+        fast = m.d1(x, logits)
+        gpu.lib().moty_cuda_set_moe_fast_path(0)
+        slow = m.d1(x, logits)
+        gpu.lib().moty_cuda_set_moe_fast_path(prev)
+        assert same_bits(fast, slow)
+    if small and (lo, hi) == (0, E):
+        cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
+        ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
+        assert close(fast, oracle.moe_q4r4(ex, x, logits)[0], 2e-3)
