@@ -72,7 +72,7 @@ def measured_peak():
 
 def profile_traffic():
     """DRAM bytes per launch of the dominant kernel, from the committed ncu summary."""
-    p = os.path.join(ROOT, "profiles", "q8_gemv_fused_151936x1024.md")
+    p = os.path.join(ROOT, "profiles", "q8_stream_gemv_151936x1024.md")
     if os.path.exists(p):
         m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)", open(p).read())
         if m:
@@ -414,7 +414,7 @@ def run_gpu(args):
                        "parallelism": "replicas" if world > 1 else "single", "bytes_per_step": total_bytes,
                        "launch": "direct" if args.no_graph else "cuda_graph_replay"},
             "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
-            "roofline": {"bound": "hbm", "kernel": "q8_gemv_fused 151936x1024 S=1", "achieved": round(achieved, 1),
+            "roofline": {"bound": "hbm", "kernel": "q8_stream_kernel<1,4,2,fused> 151936x1024 S=1", "achieved": round(achieved, 1),
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                          "traffic": profile_traffic(), "algorithmic_bytes": algo_bytes(O, I),
                          "avg_launch_us": round(dom_ms * 1e3, 3)},

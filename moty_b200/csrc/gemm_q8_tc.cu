@@ -313,12 +313,12 @@ int launch_q8_tc(const MotyCudaMat *w, const int8_t *xi, const float *sx, float 
     if (S <= 32) return launch_tc_t<32, 8, 1>(mapA, w, xi, sx, y, acc, S, c, st);
     if (S <= 64) return launch_tc_t<64, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
     if (S <= 128) return launch_tc_t<128, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
-    // Large batches are bound by the bytes that reach shared memory per MAC.  256 x 256 tiles (two
-    // accumulators, no epilogue overlap) pay off when K is long and there are enough tiles for every
-    // SM; with few 128 x 256 tiles the batch is cut into 128-token tiles so that more SMs take part.
+    // Large batches are bound by the bytes that reach shared memory per MAC, so the widest token
+    // tile wins (measured on 15360x3840, S=4096: 256-token tiles 1.8-1.96 POP/s, 128-token tiles
+    // 1.3); with few 128 x 256 tiles the batch is cut into 128-token tiles so that more SMs take
+    // part.  The 256-row variant (MT = 2) halves the activation bytes per MAC but has no second
+    // accumulator to overlap its epilogue and measured slower everywhere (1.3 POP/s): not selected.
     const long long t256 = (long long)((w->O + 127) / 128) * ((S + 255) / 256);
-    if (w->I >= 2048 && (long long)((w->O + 255) / 256) * ((S + 255) / 256) >= c->sms)
-        return launch_tc_t<256, 3, 2>(mapA, w, xi, sx, y, acc, S, c, st);
     if (t256 * 10 < (long long)c->sms * 6) return launch_tc_t<128, 6, 1>(mapA, w, xi, sx, y, acc, S, c, st);
     return launch_tc_t<256, 4, 1>(mapA, w, xi, sx, y, acc, S, c, st);
 }
