@@ -255,17 +255,20 @@ def run_moe_extras(torch, mb, dev, stream, local):
                 x = torch.randn((S, D), device=dev)
                 logits = [torch.randn((S, E), device=dev) for _ in range(8)]
                 outp = torch.empty((S, D), device=dev)
+                # a decode step runs its layers back to back: time runs of 16 consecutive layer calls
+                # (the four weight sets cycled, 50-200 MB each: not L2-resident) and divide
+                for it in range(8):
+                    layers[it % 4].apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
                 ev = []
-                for it in range(12):
-                    m = layers[it % 4]
+                for rep in range(5):
                     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     e0.record(stream)
-                    m.apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
+                    for it in range(16):
+                        layers[it % 4].apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
                     e1.record(stream)
-                    if it >= 4:
-                        ev.append((e0, e1))
+                    ev.append((e0, e1))
                 torch.cuda.synchronize()
-                us = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3
+                us = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3 / 16
                 touched = K * per_expert if S == 1 else min(E, S * K) * per_expert
                 rows.append({"layer": name, "S": S, "us": round(us, 1), "expert_GBs": round(touched / us / 1e3, 1)})
         for m in layers:

@@ -191,10 +191,15 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
                             const float *logits_dev, int order, int norm_topk,
                             int *idx_dev, float *w_dev, void *stream);
 
-/* One token through int8 experts normally takes a two-kernel streaming path (same
- * arithmetic, same results as the general grouped path that batches use).  This
- * switch (1 = on, the default; returns the previous value) lets a test run both
- * and compare them bit for bit; it has no reference counterpart. */
+/* One token through a routed layer normally takes a decode path that streams the
+ * selected experts once: for int8 experts ONE cooperative launch (router, gate/up,
+ * a bounded grid barrier, down); for Q4R4 experts a router launch and two streaming
+ * launches.  Same arithmetic, same bits as the general grouped path that batches use.
+ * This switch lets a test run them all and compare: 1 = best decode path (default),
+ * 2 = the split decode path (separate router / gate-up / down launches, both
+ * formats), 0 = the grouped path.  Returns the previous value; no reference
+ * counterpart.  If the fused kernel's barrier wait ever expires (a fraction of a
+ * second), the host-pointer entries return MOTY_CUDA_EKERNEL. */
 int moty_cuda_set_moe_fast_path(int on);
 
 /* Expert-parallel building blocks (no reference counterpart: the reference is one

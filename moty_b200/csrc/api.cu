@@ -21,6 +21,16 @@ int moty_set_error(int code, const char *fmt, ...) {
 
 extern "C" const char *moty_cuda_last_error(void) { return g_err; }
 
+// Programmatic dependent launch is on unless the environment says MOTY_CUDA_PDL=0 (read once).
+bool moty_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("MOTY_CUDA_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on == 1;
+}
+
 // ---------------------------------------------------------------------------
 // contexts
 // ---------------------------------------------------------------------------
@@ -710,11 +720,13 @@ static int moe_ensure_plan(MotyCudaMoe *m, int S) {
     return 0;
 }
 
+// 0: generic tile path; 1: best decode path (one fused launch where supported); 2: the split
+// decode path (router, gate/up and down as separate launches)
 static int g_moe_fast = 1;
 
 extern "C" int moty_cuda_set_moe_fast_path(int on) {
     int prev = g_moe_fast;
-    g_moe_fast = on ? 1 : 0;
+    g_moe_fast = on < 0 ? 0 : (on > 2 ? 1 : on);
     return prev;
 }
 
@@ -736,6 +748,34 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             if (!m->router) return moty_set_error(MOTY_CUDA_EARG, "moe: neither logits nor a router matrix");
             CKR(mat_apply_on(c, m->router, m->logits, x, S, nullptr, st));
             logits = m->logits;
+        }
+        // decode, int8 experts: router + gate/up + down in one cooperative launch
+        if (S == 1 && q8 && order == 0 && g_moe_fast == 1 && moe_decode_fused_q8_supported(E, K, I, D) &&
+            (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
+            CKR(launch_moe_decode_fused_q8(logits, E, norm_topk, m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u,
+                                           (const int8_t *)m->d, (const float *)m->gs, (const float *)m->us,
+                                           (const float *)m->ds, m->gcb, m->gsb / 4, m->dcb, m->dsb / 4, x,
+                                           (float *)c->g.p, out, K, I, D, m->e_lo, m->e_hi,
+                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st));
+            if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            return 0;
+        }
+        if (S == 1 && !q8 && order == 0 && g_moe_fast == 1 && moe_decode_fused_q4_supported(E, K, I, D) &&
+            (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            CKR(moty_grow(c, &c->hq, (size_t)K * I + 16));
+            CKR(moty_grow(c, &c->hxs, (size_t)K * (I / 32) * 4));
+            CKR(moty_grow(c, &c->hxsum, (size_t)K * (I / 32) * 4));
+            CKR(launch_moe_decode_fused_q4(logits, E, norm_topk, m->idx, m->w, (const uint8_t *)m->g, (const uint8_t *)m->u,
+                                           (const uint8_t *)m->d, (const uint16_t *)m->gs, (const uint16_t *)m->us,
+                                           (const uint16_t *)m->ds, m->gcb, m->gsb / 2, m->dcb, m->dsb / 2, x,
+                                           (int8_t *)c->hq.p, (float *)c->hxs.p, (int *)c->hxsum.p, out, K, I, D,
+                                           m->e_lo, m->e_hi, reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1,
+                                           c->sms, st));
+            if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            return 0;
         }
         CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
     }
@@ -876,7 +916,15 @@ static int moe_host(MotyCudaMoe *m, float *out, const float *x, int S, const flo
     }
     CKR(moe_apply_on(c, m, (float *)c->dy.p, (const float *)c->dx.p, S, dl, order, norm, nullptr, nullptr, nullptr, c->stream));
     CK(cudaMemcpyAsync(out, c->dy.p, xb, cudaMemcpyDeviceToHost, c->stream));
+    int kerr = 0;
+    CK(cudaMemcpyAsync(&kerr, c->err_dev + 1, 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
+    if (kerr) {
+        // the grid barrier of the fused decode kernel expired: its counters are no longer consistent
+        cudaMemsetAsync(c->err_dev + 1, 0, 4, c->stream);
+        cudaMemsetAsync(c->ctr + 4, 0, 8, c->stream);
+        return moty_set_error(MOTY_CUDA_EKERNEL, "fused MoE decode gave up on its grid barrier (result incomplete)");
+    }
     return 0;
 }
 

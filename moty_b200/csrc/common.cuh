@@ -75,6 +75,30 @@ struct MotyCudaMat {
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
 
+// Programmatic dependent launch.  A kernel launched through moty_launch_pdl may start while the
+// kernel before it on the stream is still draining; everything it does before pdl_wait() must
+// touch only memory that no kernel writes (uploaded weights, its own shared memory), and every
+// read of an activation and every global write comes after pdl_wait(), which returns once the
+// earlier kernels have finished and their writes are visible.  pdl_trigger() lets the kernel
+// after this one be scheduled into SMs as this one's CTAs leave.  Both are no-ops in a launch
+// without the attribute.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+bool moty_pdl_enabled();             // false when the environment has MOTY_CUDA_PDL=0
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t moty_launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                   Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = moty_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
+}
+
 __device__ __forceinline__ int4 ldg_stream16(const void *p) {
     // weights are read exactly once: keep them out of L1
     int4 v;

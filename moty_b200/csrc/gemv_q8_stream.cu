@@ -79,7 +79,9 @@ __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(Strea
     // tens of thousands of atomics on one address serialise in L2)
     const int nwarps = gridDim.x * 8;
     int t0 = blockIdx.x * 8 + warp;
-    if (t0 < nunits) issue(t0);
+    pdl_trigger();
+    if (t0 < nunits) issue(t0);          // weights only: may run before the previous kernel has finished
+    pdl_wait();                          // activations and outputs from here on
 
     // ---- activation rows into shared memory (int8 codes) ----
     int8_t *xq_s = reinterpret_cast<int8_t *>(smem4);
@@ -194,8 +196,7 @@ static int launch_t(const StreamArgs &a, int sms, cudaStream_t st) {
     int nunits = ((a.O + R - 1) / R) * a.KS;
     int ctas = sms * per_sm;
     if (ctas > (nunits + 7) / 8) ctas = (nunits + 7) / 8;        // never more warps than units
-    k<<<ctas, 256, smem, st>>>(a);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(k, dim3(ctas), dim3(256), smem, st, a));
     return 0;
 }
 

@@ -18,9 +18,6 @@
 
 namespace {
 
-template <int N> struct LgD { static constexpr int v = 1 + LgD<N / 2>::v; };
-template <> struct LgD<1> { static constexpr int v = 0; };
-
 template <int N>
 __device__ __forceinline__ void reduce_multi_d(int (&v)[N], int lane) {
     int off = 16;
@@ -86,6 +83,8 @@ __global__ void __launch_bounds__(256, (LPR <= 2 ? 4 : 2)) moe_dec_gateup_kernel
         sc_u = __ldg(a.us + le * a.gsstride + i);
     };
     int t0 = blockIdx.x * 8 + warp;
+    pdl_trigger();
+    pdl_wait();                                   // the routing and x come from earlier kernels
     if (t0 < nunits) issue(t0);
 
     // x -> int8 codes in shared memory (moty_hw_qrow_i8, hw/hw_quant.h:9-16)
@@ -162,6 +161,8 @@ __global__ void __launch_bounds__(256, 2) moe_dec_down_kernel(MoeDecArgs a) {
     constexpr int R = 2;
     const int nunits = (D + R - 1) / R, nwarps = gridDim.x * 8;
 
+    pdl_trigger();
+    pdl_wait();                                   // h comes from the kernel before this one
     // every warp quantizes the hidden rows of some experts: amax over the row, then the codes
     for (int k = warp; k < K; k += 8) {
         const int e = a.idx[k];
@@ -268,9 +269,8 @@ int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const 
         int ctas = sms * 4; if (ctas > (units + 7) / 8) ctas = (units + 7) / 8;
         int lpr = (D / 16 + 31) / 32;
         size_t smem = (size_t)D;
-        if (lpr <= 2) moe_dec_gateup_kernel<2><<<ctas, 256, smem, st>>>(a);
-        else moe_dec_gateup_kernel<4><<<ctas, 256, smem, st>>>(a);
-        CK(cudaGetLastError());
+        if (lpr <= 2) CK(moty_launch_pdl(moe_dec_gateup_kernel<2>, dim3(ctas), dim3(256), smem, st, a));
+        else CK(moty_launch_pdl(moe_dec_gateup_kernel<4>, dim3(ctas), dim3(256), smem, st, a));
     }
     {
         int units = (D + 1) / 2;
@@ -280,17 +280,16 @@ int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const 
         if (lpr <= 2) {
             auto k = moe_dec_down_kernel<2, 4>;
             if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k<<<ctas, 256, smem, st>>>(a);
+            CK(moty_launch_pdl(k, dim3(ctas), dim3(256), smem, st, a));
         } else if (lpr <= 4) {
             auto k = moe_dec_down_kernel<4, 2>;
             if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k<<<ctas, 256, smem, st>>>(a);
+            CK(moty_launch_pdl(k, dim3(ctas), dim3(256), smem, st, a));
         } else {
             auto k = moe_dec_down_kernel<8, 1>;
             if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            k<<<ctas, 256, smem, st>>>(a);
+            CK(moty_launch_pdl(k, dim3(ctas), dim3(256), smem, st, a));
         }
-        CK(cudaGetLastError());
     }
     return 0;
 }

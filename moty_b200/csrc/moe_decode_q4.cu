@@ -8,12 +8,10 @@
 // re-quantization of the hidden row (hw/hw_q4r4.h:36-45), and the weighted sum in
 // selection order (nn/moe.c:146-149).  Operation for operation it is the generic path
 // (q4r4_small_kernel tiles + act + combine), so results are bit-identical to it.
-//
-// Layout of a step: a warp owns one 4-row block, lane = (group-in-step << 2) | row,
-// 512 contiguous bytes of codes per step, the running sum of a row hops from the lane of
-// group g to the lane of group g+1 by shuffle.
+// The step layout and its helpers are in q4_decode.cuh.
 #include "kernels.cuh"
 #include "moe.cuh"
+#include "q4_decode.cuh"
 
 namespace {
 
@@ -25,58 +23,6 @@ struct MoeDec4Args {
     int K, I, D, e_lo, e_hi;
 };
 
-// group-of-32 quantizer, one thread per group (moty_hw_quant_g32): n floats at src -> codes, scale, sum
-__device__ __forceinline__ void quant_groups(const float *src, int ngroups, int8_t *xq, float *xs, int *xsum,
-                                             int tid, int nthreads) {
-    for (int g = tid; g < ngroups; g += nthreads) {
-        const float4 *p = reinterpret_cast<const float4 *>(src + (size_t)g * 32);
-        float4 v[8];
-#pragma unroll
-        for (int k = 0; k < 8; k++) v[k] = p[k];
-        float amax = 0.f;
-#pragma unroll
-        for (int k = 0; k < 8; k++)
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[k].x), fabsf(v[k].y)), fmaxf(fabsf(v[k].z), fabsf(v[k].w))));
-        const float s = quant_scale(amax, 1e-30f);
-        const float inv = __fdiv_rn(1.f, s);
-        int tot = 0;
-        int *dst = reinterpret_cast<int *>(xq + (size_t)g * 32);
-#pragma unroll
-        for (int k = 0; k < 8; k++) {
-            int c0 = quant_code(v[k].x, inv), c1 = quant_code(v[k].y, inv);
-            int c2 = quant_code(v[k].z, inv), c3 = quant_code(v[k].w, inv);
-            tot += c0 + c1 + c2 + c3;
-            dst[k] = (c0 & 255) | ((c1 & 255) << 8) | ((c2 & 255) << 16) | ((c3 & 255) << 24);
-        }
-        xs[g] = s; xsum[g] = tot;
-    }
-}
-
-// one 512-byte step of one block: the lane's (row, group) integer sum and its chain factor
-__device__ __forceinline__ void q4_step_terms(const int4 &w4, uint16_t dbits, const int8_t *xq_s, const float *xs_s,
-                                              const int *xsum_s, int gc, float &fs, float &c0) {
-    int4 lo, hi;
-    lo.x = w4.x & 0x0f0f0f0f; hi.x = (w4.x >> 4) & 0x0f0f0f0f;
-    lo.y = w4.y & 0x0f0f0f0f; hi.y = (w4.y >> 4) & 0x0f0f0f0f;
-    lo.z = w4.z & 0x0f0f0f0f; hi.z = (w4.z >> 4) & 0x0f0f0f0f;
-    lo.w = w4.w & 0x0f0f0f0f; hi.w = (w4.w >> 4) & 0x0f0f0f0f;
-    const int4 *xg = reinterpret_cast<const int4 *>(xq_s + (size_t)gc * 32);
-    int sraw = dp4a4(lo, xg[0], 0);
-    sraw = dp4a4(hi, xg[1], sraw);
-    fs = (float)(sraw - 8 * xsum_s[gc]);
-    c0 = __fmul_rn(f16bits_to_f32(dbits), xs_s[gc]);
-}
-
-// the chain hop of one step: 8 groups side by side, ascending
-__device__ __forceinline__ float q4_chain(float acc, float fs, float c0, bool valid, int gl, int prev) {
-#pragma unroll
-    for (int jj = 0; jj < 8; jj++) {
-        float in = __shfl_sync(0xffffffffu, acc, prev);
-        if (gl == jj) acc = valid ? fmaf(fs, c0, in) : in;
-    }
-    return acc;
-}
-
 // ---- kernel A: gate and up blocks of the K selected experts, activation fused ----
 __global__ void __launch_bounds__(256) moe_dec4_gateup_kernel(MoeDec4Args a) {
     extern __shared__ int4 sm4[];
@@ -87,6 +33,8 @@ __global__ void __launch_bounds__(256) moe_dec4_gateup_kernel(MoeDec4Args a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gl = lane >> 2, r = lane & 3;
     const int prev = (lane + 28) & 31;
     const int nblk = (I + 3) / 4, nit = (nb + 7) / 8, nunits = a.K * nblk, nwarps = gridDim.x * 8;
+    pdl_trigger();
+    pdl_wait();                                                // the routing and x come from earlier kernels
     quant_groups(a.x, nb, xq_s, xs_s, xsum_s, threadIdx.x, 256);
     __syncthreads();
     for (int t = blockIdx.x * 8 + warp; t < nunits; t += nwarps) {
@@ -142,6 +90,8 @@ __global__ void __launch_bounds__(256) moe_dec4_down_kernel(MoeDec4Args a) {
     __shared__ int loc_s[64];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gl = lane >> 2, r = lane & 3;
     const int prev = (lane + 28) & 31;
+    pdl_trigger();
+    pdl_wait();                                                            // h comes from the kernel before this one
     if (threadIdx.x < K) { int e = a.idx[threadIdx.x]; loc_s[threadIdx.x] = e >= a.e_lo && e < a.e_hi; }
     __syncthreads();
     // hidden rows of the resident experts -> group-quantized codes (rows of absent experts are never read)
@@ -208,16 +158,14 @@ int launch_moe_decode_q4(const int *idx, const float *w, const uint8_t *g, const
         int units = K * ((I + 3) / 4);
         int ctas = sms * 4; if (ctas > (units + 7) / 8) ctas = (units + 7) / 8;
         size_t smem = (size_t)D + (size_t)(D / 32) * 8;
-        moe_dec4_gateup_kernel<<<ctas, 256, smem, st>>>(a);
-        CK(cudaGetLastError());
+        CK(moty_launch_pdl(moe_dec4_gateup_kernel, dim3(ctas), dim3(256), smem, st, a));
     }
     {
         int units = (D + 3) / 4;
         int ctas = sms * 4; if (ctas > (units + 7) / 8) ctas = (units + 7) / 8;
         size_t smem = (size_t)K * I + (size_t)K * (I / 32) * 8;
         if (smem > 48 * 1024) CK(cudaFuncSetAttribute(moe_dec4_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        moe_dec4_down_kernel<<<ctas, 256, smem, st>>>(a);
-        CK(cudaGetLastError());
+        CK(moty_launch_pdl(moe_dec4_down_kernel, dim3(ctas), dim3(256), smem, st, a));
     }
     return 0;
 }

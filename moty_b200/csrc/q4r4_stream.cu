@@ -72,8 +72,10 @@ __global__ void __launch_bounds__(256) q4r4_stream_kernel(Q4StreamArgs a) {
             }
         }
     };
+    pdl_trigger();
 #pragma unroll
-    for (int u = 0; u < PF; u++) load_next(u);
+    for (int u = 0; u < PF; u++) load_next(u);                 // weights only: may overlap the previous kernel
+    pdl_wait();
 
     // ---- activation rows into shared memory ----
     if (FUSED) {
@@ -223,8 +225,7 @@ static int launch_q4s_t(const Q4StreamArgs &a, int sms, cudaStream_t st) {
     int nunits = ((a.O + 3) / 4 + (8 / GS) - 1) / (8 / GS);
     int ctas = sms * per_sm;
     if (ctas > (nunits + 7) / 8) ctas = (nunits + 7) / 8;
-    k<<<ctas, 256, smem, st>>>(a);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(k, dim3(ctas), dim3(256), smem, st, a));
     return 0;
 }
 

@@ -109,10 +109,12 @@ def test_expert_shards_sum_to_the_whole(gpu, oracle):
     assert close(total, whole)
 
 
-@pytest.mark.parametrize("E,K,I,D,lo,hi", [(64, 8, 1024, 2048, 0, 64), (16, 4, 96, 160, 0, 16), (16, 4, 96, 160, 4, 12), (8, 8, 48, 2048, 0, 8)])
+@pytest.mark.parametrize("E,K,I,D,lo,hi", [(64, 8, 1024, 2048, 0, 64), (16, 4, 96, 160, 0, 16), (16, 4, 96, 160, 4, 12),
+                                           (8, 8, 48, 2048, 0, 8), (32, 6, 2064, 512, 0, 32), (12, 10, 4096, 64, 0, 12)])
 def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, hi):
-    """The two-kernel decode path and the grouped path are the same arithmetic: bit-identical,
-    also on an expert shard (non-resident experts contribute nothing)."""
+    """The fused one-launch decode path (1), the split decode path (2) and the grouped path (0) are
+    the same arithmetic: bit-identical, also on an expert shard (non-resident experts contribute
+    nothing), and repeated calls keep the fused kernel's grid barrier consistent."""
     from oracle import Experts
     rng = np.random.default_rng(E * K + I + lo)
     g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
@@ -127,16 +129,20 @@ def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, h
         logits = (rng.standard_normal((1, E)) * 0.5).astype(np.float32)
         prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
         fast = m.d1(x, logits); fast_ol = m.olmoe(x, logits, 0)
+        gpu.lib().moty_cuda_set_moe_fast_path(2)
+        split = m.d1(x, logits); split_ol = m.olmoe(x, logits, 0)
         gpu.lib().moty_cuda_set_moe_fast_path(0)
         slow = m.d1(x, logits); slow_ol = m.olmoe(x, logits, 0)
         gpu.lib().moty_cuda_set_moe_fast_path(prev)
         assert same_bits(fast, slow) and same_bits(fast_ol, slow_ol)
+        assert same_bits(split, slow) and same_bits(split_ol, slow_ol)
     if (lo, hi) == (0, E):
         want = oracle.moe_d1(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0]
         assert close(fast, want, 2e-3)
 
 
-@pytest.mark.parametrize("E,K,I,D,lo,hi", [(16, 4, 96, 128, 0, 16), (128, 8, 768, 2048, 0, 128), (16, 4, 96, 128, 8, 16)])
+@pytest.mark.parametrize("E,K,I,D,lo,hi", [(16, 4, 96, 128, 0, 16), (128, 8, 768, 2048, 0, 128), (16, 4, 96, 128, 8, 16),
+                                           (16, 6, 1312, 416, 0, 16), (16, 4, 96, 128, 15, 16)])
 def test_moe_q4r4_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, hi):
     from oracle import Experts
     rng = np.random.default_rng(E + I + lo)
@@ -157,11 +163,13 @@ def test_moe_q4r4_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, 
         x = rng.standard_normal((1, D)).astype(np.float32)
         logits = (rng.standard_normal((1, E)) * 0.5).astype(np.float32)
         prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
-        fast = m.d1(x, logits)
+        fast = m.d1(x, logits); fast2 = m.d1(x, logits)        # twice: the fused kernel's counters must come back to zero
+        gpu.lib().moty_cuda_set_moe_fast_path(2)
+        split = m.d1(x, logits)
         gpu.lib().moty_cuda_set_moe_fast_path(0)
         slow = m.d1(x, logits)
         gpu.lib().moty_cuda_set_moe_fast_path(prev)
-        assert same_bits(fast, slow)
+        assert same_bits(fast, slow) and same_bits(fast2, slow) and same_bits(split, slow)
     if small and (lo, hi) == (0, E):
         cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
         ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
