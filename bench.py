@@ -133,7 +133,12 @@ def cpu_arm(mats, steps, warmup, budget_s=None):
     """Time passes of the sweep with moty_matmul_q_s.  Returns (GB/s, cores, kind, passes, seconds)."""
     from oracle import Oracle, Ref
     if Ref.available():
-        r = Ref(); kind = "reference"; cores = r.threads()
+        r = Ref(); kind = "reference"
+        # all the host threads this process may use (a launcher may have put OMP_NUM_THREADS=1 in
+        # the environment for its ranks; rank 0 alone runs this arm)
+        avail = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+        r.set_threads(avail)
+        cores = r.threads()
         call = r.matmul_q_s
     else:
         r = Oracle(); kind = "port"; cores = os.cpu_count() or 1
