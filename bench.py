@@ -177,7 +177,7 @@ def run_reference(args):
 
 # ---------------------------------------------------------------------------
 # extras: the other rows of the op-level sweep, timed per shape (reported beside the
-# headline, not part of it): Q8_0 at S=16 and S=512, Q4R4 at S=1 and S=16, and one
+# headline, not part of it): Q8_0 at S=16 and S=512, Q4R4 at S=1, 16 and 512, and one
 # library int8 GEMM as the calibration point for the int8 tensor peak
 # ---------------------------------------------------------------------------
 def q4r4_bytes(O, I, S=1):
@@ -204,7 +204,7 @@ def run_extras(torch, mb, dev, stream, W8, local):
         s16 = np.full(nblk * nb * 4, 0x1A00, np.uint16)               # f16 0.00293
         W4.append(mb.Mat.q4r4(q4, s16, O, I, device=local))
     with torch.cuda.stream(stream):
-        for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4)):
+        for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4), ("q4r4", W4, 512, 2)):
             xs = [torch.randn((S, I), device=dev) for (_, I) in SHAPES]
             ys = [torch.empty((S, O), device=dev) for (O, _) in SHAPES]
             ev = [[] for _ in SHAPES]
@@ -435,6 +435,39 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_case(args):
+    """One matrix product, launched --warmup + --steps times on one stream (a small, self-ending
+    workload for ncu captures of a single kernel)."""
+    import torch
+    import moty_b200 as mb
+    fmt, S, O, I = args.case.split(":")
+    S, O, I = int(S), int(O), int(I)
+    mb.init([0])
+    dev = torch.device("cuda:0")
+    rng = np.random.default_rng(3)
+    if fmt == "q8_0":
+        w = mb.Mat.i8(rng.integers(-127, 128, (O, I), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
+        nbytes = algo_bytes(O, I, S)
+    else:
+        nblk, nb = (O + 3) // 4, I // 32
+        w = mb.Mat.q4r4(rng.integers(0, 256, nblk * nb * 64, dtype=np.uint8), np.full(nblk * nb * 4, 0x1A00, np.uint16), O, I, device=0)
+        nbytes = q4r4_bytes(O, I, S)
+    stream = torch.cuda.Stream(device=dev)
+    with torch.cuda.stream(stream):
+        x = torch.randn((S, I), device=dev); y = torch.empty((S, O), device=dev)
+        for _ in range(max(args.warmup, 1)):
+            mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), S, stream.cuda_stream)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(args.steps):
+            mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), S, stream.cuda_stream)
+        e1.record(stream)
+        torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1e3 / args.steps
+    print(json.dumps({"case": args.case, "us": round(us, 2), "GBs": round(nbytes / us / 1e3, 1),
+                      "TOPS": round(2.0 * S * O * I / us / 1e6, 2), "steps": args.steps}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -445,7 +478,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
+    ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0 or q4r4): time only that product, "
+                                                "--steps launches after --warmup, print one row and exit")
     args = ap.parse_args()
+    if args.case:
+        run_case(args)
+        return
     if args.shapes:
         global SHAPES, DOMINANT, WORKLOAD
         keep = [int(v) for v in args.shapes.split(",")]

@@ -114,7 +114,7 @@ extern "C" void moty_cuda_shutdown(void) {
         cudaSetDevice(c->dev);
         cudaStreamSynchronize(c->stream);
         Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
-                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell};
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec};
         for (Buf *b : bs) free_buf(b);
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
@@ -286,25 +286,21 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
         CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
-        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
         CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
-        CKR(launch_q4r4_forms((uint8_t *)c->misc.p, S, st));
-        if (S <= 32) {                                // small batches: the streaming kernel once per 4 rows
-            for (int s0 = 0; s0 < S; s0 += 4) {
-                int ns = S - s0 < 4 ? S - s0 : 4;
-                CKR(launch_q4r4_stream((const uint8_t *)w->codes, (const uint16_t *)w->scales, nullptr,
-                                       (const int8_t *)c->xi.p + (size_t)s0 * I, (const float *)c->xs.p + (size_t)s0 * nb,
-                                       (const int32_t *)c->xsum.p + (size_t)s0 * nb, (const uint8_t *)c->misc.p + s0,
-                                       y + (size_t)s0 * O, ns, I, O, c->sms, st));
-            }
-            return 0;
+        if (S <= 4) {                                 // the streaming kernel, all rows in one pass
+            CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+            CKR(launch_q4r4_forms((uint8_t *)c->misc.p, S, st));
+            return launch_q4r4_stream((const uint8_t *)w->codes, (const uint16_t *)w->scales, nullptr,
+                                      (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
+                                      (const uint8_t *)c->misc.p, y, S, I, O, c->sms, st);
         }
-        Q4Args a; memset(&a, 0, sizeof a);
-        a.w = (const uint8_t *)w->codes; a.d = (const uint16_t *)w->scales;
-        a.xq = (const int8_t *)c->xi.p; a.xs = (const float *)c->xs.p; a.xsum = (const int32_t *)c->xsum.p;
-        a.form = (const uint8_t *)c->misc.p;
-        a.y = y; a.ldy = O; a.S = S; a.I = I; a.O = O;
-        return launch_q4r4_small(a, c->sms, st);
+        // batches: integer MMA per group, sequential f32 chain in registers
+        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 8));
+        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+        return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
+                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
+                               (uint8_t *)c->misc.p, y, O, S, I, O,
+                               c->sms, st);
     }
     if (w->fmt == MOTY_WF_I4) {
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));

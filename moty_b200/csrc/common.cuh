@@ -48,6 +48,7 @@ struct DevCtx {
     Buf hpin_in, hpin_out;           // pinned host
     // FFN / MoE intermediates
     Buf g, u, h, hq, hs, hxs, hxsum, pair, misc;
+    Buf rec;                         // per (token, group) records of the Q4R4 batch kernel
     // streaming GEMV: ticket/exit counters and K-split cells, all zero between launches
     int *ctr = nullptr;
     Buf kcell;

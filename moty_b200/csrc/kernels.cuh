@@ -74,6 +74,10 @@ int launch_q4r4_small(const Q4Args &a, int sms, cudaStream_t st);
 // which of the reference's two kernels each of S tokens goes through
 int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 
+// ---- q4r4_mma.cu: Q4R4 x a batch of rows, integer MMA per group + the sequential f32 chain ----
+int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
+                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int sms, cudaStream_t st);
+
 // ---- router.cu ----------------------------------------------------------------------
 int launch_route(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs,
                  int do_softmax, int norm_topk, cudaStream_t st);

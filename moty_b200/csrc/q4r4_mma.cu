@@ -1,0 +1,253 @@
+// q4r4_mma.cu -- Q4R4 weights x a batch of group-quantized activation rows (S >= 5).
+//
+// Replaces moty_matmul_q4r4_s (nn/matmul.c:405-433) with its two kernels
+// moty_hw_q4r4_gemm_ref / _gemm4t_ref (hw/hw_q4r4.h:47-84) for batches.
+//
+// The arithmetic has two layers.  Inside one group of 32 weights the reference sums
+// integers: exact in any order.  Across groups it adds ONE f32 term per group to a
+// running sum, in ascending group order: that chain has to be reproduced step by step.
+// So the integer layer goes to the tensor cores one group at a time -- a K = 32 integer
+// MMA is exactly one group -- and its int32 result is consumed in registers by the f32
+// chain before the next group: mma.sync.m16n8k32 (u8 nibble codes x s8 activation codes ->
+// s32), 16 weight rows x 8 tokens per instruction, accumulator fragments in registers.
+// (tcgen05 keeps accumulators in TMEM; reading a whole tile back after every K = 32 step
+// costs more than the MMA saves, and the chain, 4 instructions per output and group, is
+// the bound either way.)
+//
+// Fragment fit: the 16 rows of an M tile are four Q4R4 blocks.  A block stores, per row and
+// group, 16 bytes with byte j = code[j] | code[j+16] << 4; the A fragment wants from thread
+// (gid, tid) the codes k = 4 tid .. 4 tid + 3 (a0/a1) and k = 16 + 4 tid .. (a2/a3) of rows
+// gid and gid + 8: that is ONE 32-bit word per row, low nibbles -> a0/a1, high -> a2/a3.
+// Weights, activation codes and the chain records all reach the warps through a three-stage
+// shared-memory ring filled by cp.async (eight groups per stage), so no load sits in the chain.
+//
+// Per (group, token) an 8-byte record {xs, v} prepared by q4r4_rec_kernel carries what the
+// chain step needs in either of the reference's formulas (which one is a per-token flag):
+//   token-by-token (hw/hw_q4r4.h:58-59), v = 8*xsum:        acc = fma((float)(sum - v), d*xs, acc)
+//   4-token tile   (hw/hw_q4r4.h:78-81), v = (8*xsum)*xs:   acc = fma((float)sum, d*xs, acc); acc = fma(-d, v, acc)
+#include "kernels.cuh"
+
+struct Q4MmaArgs {
+    const uint8_t *w; const uint16_t *d;
+    const int8_t *xq;                         // codes [S][I]
+    const int2 *rec;                          // records [I/32][S8], S8 = S rounded up to 8
+    const uint8_t *form;                      // per token: 1 = 4-token-tile formula
+    float *y; int ldy;
+    int S, S8, I, O;
+};
+
+// D = A (16x32 u8, row) * B (32x8 s8, col), accumulator input zero
+__device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                               unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// int -> float for |i| < 2^22 without the conversion unit (a quarter-rate pipe that the chain would
+// saturate): 0x4B400000 is 1.5 * 2^23 as a float; adding i to its bit pattern gives the float
+// 1.5 * 2^23 + i exactly, and the subtraction is exact.  Group sums are below 2^17 in magnitude.
+__device__ __forceinline__ float small_int_to_float(int i_plus_magic) {
+    return __fsub_rn(__int_as_float(i_plus_magic), 12582912.0f);
+}
+
+// one step of the chain; voff = 8*xsum for a token-form token, 0 for a tile-form token
+__device__ __forceinline__ float q4_chain_step(float acc, int sum, float d, int xs_bits, int voff, int v, bool tile_form) {
+    const float fs = small_int_to_float(sum - voff + 0x4B400000);
+    acc = fmaf(fs, __fmul_rn(d, __int_as_float(xs_bits)), acc);
+    if (tile_form) acc = fmaf(-d, __int_as_float(v), acc);
+    return acc;
+}
+
+// 16-byte and 8-byte asynchronous copies global -> shared (.cg: around L1, for data read once)
+__device__ __forceinline__ void cp_async16(void *smem, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *smem, const void *g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// A CTA takes 8 M tiles (128 weight rows, one M tile per warp) x NT N tiles (8 NT tokens) and walks
+// the groups in stages of GCH = 8.  One stage in shared memory:
+//   W  per warp: its four blocks' codes, 4 x 512 bytes, each block padded by 64 bytes so that the two
+//      blocks a fragment load touches sit in different banks
+//   D  per warp: 4 x 64 bytes of f16 scales
+//   B  the tokens' codes, 256 bytes per token, token stride 272 bytes (eight tokens -> eight bank groups)
+//   R  the records, [group][token pair] 16 bytes
+constexpr int GCH = 8, NSTG = 3;
+constexpr int WBLK = 512 + 64, STG_W1 = 4 * WBLK, STG_D1 = 4 * 64, BTOK = 272;
+template <int NT> struct Q4Stage {
+    static constexpr int W = 0, D = 8 * STG_W1, B = D + 8 * STG_D1, R = B + NT * 8 * BTOK, BYTES = R + NT * GCH * 64;
+};
+
+template <int NT>
+__global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
+    using L = Q4Stage<NT>;
+    extern __shared__ int4 smem_q4mma[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>(smem_q4mma);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tid = lane & 3;
+    const int I = a.I, nb = I / 32, O = a.O, S = a.S;
+    const int nblk = (O + 3) / 4, nstage = (nb + GCH - 1) / GCH;
+    const int mt = blockIdx.x * 8 + warp;                      // this warp's M tile (may lie past the end: it still copies and syncs)
+    const int n00 = blockIdx.y * NT * 8;                       // first token of the CTA
+    const int row_a = mt * 16 + gid, row_b = row_a + 8;
+    // where this thread's fragment words and scales sit inside a stage
+    const int ba_l = gid >> 2, bb_l = ba_l + 2, rr = gid & 3;
+    const int offA = L::W + warp * STG_W1 + ba_l * WBLK + rr * 16 + tid * 4, offB = L::W + warp * STG_W1 + bb_l * WBLK + rr * 16 + tid * 4;
+    const int offdA = L::D + warp * STG_D1 + ba_l * 64 + rr * 2, offdB = L::D + warp * STG_D1 + bb_l * 64 + rr * 2;
+    // first group held by stage s: a partial last stage is shifted back so that it never runs past the row
+    auto stage_g0 = [&](int s) { const int g0 = s * GCH; return g0 + GCH <= nb ? g0 : (nb >= GCH ? nb - GCH : 0); };
+    auto fill_w = [&](int s) {                                 // weights: lane l copies int4 number l of each block, and 8 bytes of scales
+        if (s >= nstage) return;
+        unsigned char *dst = smem + (size_t)(s % NSTG) * L::BYTES;
+        const int gs = stage_g0(s);
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
+            if (nb >= GCH || lane * 16 < nb * 64)
+                cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + lane * 16, a.w + ((size_t)blk * nb + gs) * 64 + lane * 16);
+        }
+        const int q = lane >> 3, part = lane & 7;
+        int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
+        if (nb >= GCH || part < nb)
+            cp_async8(dst + L::D + warp * STG_D1 + q * 64 + part * 8, a.d + ((size_t)blk * nb + gs) * 4 + part * 4);
+    };
+    auto fill_x = [&](int s) {                                 // activation side: codes and records of the CTA's tokens
+        if (s >= nstage) return;
+        unsigned char *dst = smem + (size_t)(s % NSTG) * L::BYTES;
+        const int gs = stage_g0(s);
+        for (int t = threadIdx.x; t < NT * 128; t += 256) {    // 16 chunks of 16 bytes per token
+            const int tok = t >> 4, ch = t & 15;
+            int n = n00 + tok; n = n < S ? n : S - 1;
+            if (nb >= GCH || ch * 16 < nb * 32)
+                cp_async16(dst + L::B + tok * BTOK + ch * 16, a.xq + (size_t)n * I + (size_t)gs * 32 + ch * 16);
+        }
+        for (int t = threadIdx.x; t < NT * GCH * 4; t += 256) {   // per N tile and group: four token pairs of 16 bytes
+            const int j = t / (GCH * 4), u = (t >> 2) % GCH, pr = t & 3;
+            if (gs + u < nb && n00 + j * 8 + pr * 2 < a.S8)        // token pairs past the padded batch: nothing to copy, nothing stored
+                cp_async16(dst + L::R + j * GCH * 64 + u * 64 + pr * 16, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + pr * 2);
+        }
+    };
+    pdl_trigger();
+    fill_w(0); fill_w(1);                                      // weights only: may overlap the previous kernel
+    pdl_wait();                                                // codes and records come from the kernels before this one
+    fill_x(0); cp_async_commit();
+    fill_x(1); cp_async_commit();
+
+    bool f0[NT], f1[NT];
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        int t0 = n00 + j * 8 + tid * 2, t1 = t0 + 1;
+        f0[j] = t0 < S && a.form[t0] != 0; f1[j] = t1 < S && a.form[t1] != 0;
+        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    }
+    for (int s = 0; s < nstage; s++) {
+        cp_async_wait<1>();                                    // this thread's copies of stage s have landed
+        __syncthreads();                                       // everyone's have, and everyone is done with stage s - 1
+        fill_w(s + 2); fill_x(s + 2); cp_async_commit();       // into the slot stage s - 1 used
+        const unsigned char *st = smem + (size_t)(s % NSTG) * L::BYTES;
+        const int g0 = s * GCH, gs = stage_g0(s);
+        auto group_step = [&](int ul) {                        // ul: position of the group inside the stage
+            const unsigned wA = *reinterpret_cast<const unsigned *>(st + offA + ul * 64);
+            const unsigned wB = *reinterpret_cast<const unsigned *>(st + offB + ul * 64);
+            const float dA = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdA + ul * 8));
+            const float dB = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdB + ul * 8));
+            const unsigned a0 = wA & 0x0f0f0f0fu, a2 = (wA >> 4) & 0x0f0f0f0fu;
+            const unsigned a1 = wB & 0x0f0f0f0fu, a3 = (wB >> 4) & 0x0f0f0f0fu;
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                const unsigned char *bp = st + L::B + (j * 8 + gid) * BTOK + ul * 32 + tid * 4;
+                const unsigned b0 = *reinterpret_cast<const unsigned *>(bp), b1 = *reinterpret_cast<const unsigned *>(bp + 16);
+                int c[4];
+                mma_u8s8_16832(c, a0, a1, a2, a3, b0, b1);
+                const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1
+                const int v0 = f0[j] ? 0 : q.y, v1 = f1[j] ? 0 : q.w;
+                acc[j][0] = q4_chain_step(acc[j][0], c[0], dA, q.x, v0, q.y, f0[j]);   // (row_a, t0)
+                acc[j][1] = q4_chain_step(acc[j][1], c[1], dA, q.z, v1, q.w, f1[j]);   // (row_a, t1)
+                acc[j][2] = q4_chain_step(acc[j][2], c[2], dB, q.x, v0, q.y, f0[j]);   // (row_b, t0)
+                acc[j][3] = q4_chain_step(acc[j][3], c[3], dB, q.z, v1, q.w, f1[j]);   // (row_b, t1)
+            }
+        };
+        if (g0 + GCH <= nb) {
+#pragma unroll
+            for (int u = 0; u < GCH; u++) group_step(u);
+        } else {
+            for (int g = g0; g < nb; g++) group_step(g - gs);
+        }
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int j = 0; j < NT; j++) {
+        const int t0 = n00 + j * 8 + tid * 2, t1 = t0 + 1;
+        if (t0 < S) {
+            if (row_a < O) a.y[(size_t)t0 * a.ldy + row_a] = acc[j][0];
+            if (row_b < O) a.y[(size_t)t0 * a.ldy + row_b] = acc[j][2];
+        }
+        if (t1 < S) {
+            if (row_a < O) a.y[(size_t)t1 * a.ldy + row_a] = acc[j][1];
+            if (row_b < O) a.y[(size_t)t1 * a.ldy + row_b] = acc[j][3];
+        }
+    }
+}
+
+// records of the chain step, [group][token] (token count padded to 8, padding zeroed), and the
+// per-token formula flag: moty_matmul_q4r4_s cuts the batch into tiles of 32 tokens and sends the
+// first (size / 4 * 4) tokens of a tile through the 4-token kernel, the rest through the
+// token-by-token kernel (nn/matmul.c:424-432)
+__global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
+                                                       int2 *__restrict__ rec, uint8_t *__restrict__ form, int S, int S8, int nb) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)S8 * nb) return;
+    const int g = (int)(i / S8), t = (int)(i - (long long)g * S8);
+    int2 r = make_int2(0, 0);
+    if (t < S) {
+        const int t0 = t / 32 * 32;
+        const int ns = S - t0 < 32 ? S - t0 : 32;
+        const int f = (t - t0) < ns / 4 * 4 ? 1 : 0;
+        const float sc = xs[(size_t)t * nb + g]; const int sm = xsum[(size_t)t * nb + g];
+        r.x = __float_as_int(sc);
+        r.y = f ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm;
+        if (g == 0) form[t] = (uint8_t)f;
+    }
+    rec[i] = r;
+}
+
+template <int NT>
+static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st) {
+    constexpr int SMEM = NSTG * Q4Stage<NT>::BYTES;
+    static bool attr_done[MOTY_MAX_DEV];
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: device %d", dev);
+    if (!attr_done[dev]) {
+        CK(cudaFuncSetAttribute(q4r4_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        attr_done[dev] = true;
+    }
+    const int nmt = (a.O + 15) / 16;
+    dim3 grid((nmt + 7) / 8, (a.S + 8 * NT - 1) / (8 * NT));
+    if (grid.y > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q4r4_mma: S=%d in one call", a.S);
+    CK(moty_launch_pdl(q4r4_mma_kernel<NT>, grid, dim3(256), (size_t)SMEM, st, a));
+    return 0;
+}
+
+// xq/xs/xsum: the group-quantized batch; rec: scratch for (I/32) * ceil8(S) records of 8 bytes;
+// form: scratch for S bytes
+int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
+                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int sms, cudaStream_t st) {
+    if (I % 32 != 0 || I <= 0 || S <= 0) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: S=%d I=%d", S, I);
+    if (O <= 0) return 0;
+    const int nb = I / 32, S8 = (S + 7) / 8 * 8;
+    const long long nrec = (long long)S8 * nb;
+    q4r4_rec_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, rec, form, S, S8, nb);
+    CK(cudaGetLastError());
+    Q4MmaArgs a;
+    a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
+    // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
+    const long long mct = ((O + 15) / 16 + 7) / 8, want = (long long)sms * 2;
+    if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4>(a, st);
+    if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2>(a, st);
+    return launch_mma_t<1>(a, st);
+}
