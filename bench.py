@@ -228,52 +228,72 @@ def run_extras(torch, mb, dev, stream, W8, local):
     return out
 
 
+MOE_SHAPES = {"olmoe": (64, 8, 1024, 2048, "i8"), "qwen3-30b-a3b": (128, 8, 768, 2048, "q4r4")}
+
+
+def make_moe_layers(mb, name, nlayers, local, rng):
+    """nlayers routed layers of the named shape with different random experts, GPU-resident."""
+    E, K, I, D, f = MOE_SHAPES[name]
+    fmt = mb.WF_I8 if f == "i8" else mb.WF_Q4R4
+    layers = []
+    for _ in range(nlayers):
+        m = mb.Moe(E, K, I, D, efmt=fmt, device=local)
+        for e in range(E):
+            if fmt == mb.WF_I8:
+                g = rng.integers(-127, 128, (I, D), dtype=np.int8); u = rng.integers(-127, 128, (I, D), dtype=np.int8)
+                d = rng.integers(-127, 128, (D, I), dtype=np.int8)
+                gs = rng.uniform(0.001, 0.02, I).astype(np.float32); us = rng.uniform(0.001, 0.02, I).astype(np.float32)
+                ds = rng.uniform(0.001, 0.02, D).astype(np.float32)
+            else:
+                ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
+                g = rng.integers(0, 256, ng * 64, dtype=np.uint8); u = rng.integers(0, 256, ng * 64, dtype=np.uint8)
+                d = rng.integers(0, 256, nd * 64, dtype=np.uint8)
+                gs = np.full(ng * 4, 0x1A00, np.uint16); us = np.full(ng * 4, 0x1A00, np.uint16); ds = np.full(nd * 4, 0x1A00, np.uint16)
+            m.upload_expert(e, g, gs, u, us, d, ds)
+        layers.append(m)
+    per_expert = (3 * I * D + 4 * (2 * I + D)) if fmt == mb.WF_I8 else (2 * (I // 4) * (D // 32) * 72 + (D // 4) * (I // 32) * 72)
+    return layers, per_expert
+
+
+def time_moe(torch, layers, name, S, dev, stream, reps=5, run=16):
+    """Microseconds per layer call: runs of `run` consecutive calls (a decode step runs its layers back
+    to back), the weight sets cycled so that a layer's experts are not L2-resident when it runs."""
+    E, K, I, D, _ = MOE_SHAPES[name]
+    sp = stream.cuda_stream
+    x = torch.randn((S, D), device=dev)
+    logits = [torch.randn((S, E), device=dev) for _ in range(8)]
+    outp = torch.empty((S, D), device=dev)
+    order = 0 if S == 1 else 1
+
+    def call(it):
+        layers[it % len(layers)].apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), order, 1, 0, 0, sp)
+    for it in range(8):
+        call(it)
+    ev = []
+    for _ in range(reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for it in range(run):
+            call(it)
+        e1.record(stream)
+        ev.append((e0, e1))
+    torch.cuda.synchronize()
+    return statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3 / run
+
+
 def run_moe_extras(torch, mb, dev, stream, local):
     """One routed MoE layer, decode (S=1) and a small prefill batch, on the two MoE shapes of the
     baseline: OLMoE-1B-7B (E=64, K=8, expert FFN 1024, hidden 2048, int8 experts) and
-    Qwen3-30B-A3B (E=128, K=8, expert FFN 768, hidden 2048, Q4R4 experts).  Four layers with
-    different weights are cycled so that a layer's experts are not L2-resident when it runs.
-    Bytes = the K selected experts' gate+up+down (codes and scales)."""
-    sp = stream.cuda_stream
+    Qwen3-30B-A3B (E=128, K=8, expert FFN 768, hidden 2048, Q4R4 experts).
+    Bytes = the touched experts' gate+up+down (codes and scales)."""
     rng = np.random.default_rng(2)
     rows = []
-    for name, E, K, I, D, fmt in (("olmoe", 64, 8, 1024, 2048, mb.WF_I8), ("qwen3-30b-a3b", 128, 8, 768, 2048, mb.WF_Q4R4)):
-        layers = []
-        for _ in range(4):
-            m = mb.Moe(E, K, I, D, efmt=fmt, device=local)
-            for e in range(E):
-                if fmt == mb.WF_I8:
-                    g = rng.integers(-127, 128, (I, D), dtype=np.int8); u = rng.integers(-127, 128, (I, D), dtype=np.int8)
-                    d = rng.integers(-127, 128, (D, I), dtype=np.int8)
-                    gs = rng.uniform(0.001, 0.02, I).astype(np.float32); us = rng.uniform(0.001, 0.02, I).astype(np.float32)
-                    ds = rng.uniform(0.001, 0.02, D).astype(np.float32)
-                else:
-                    ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
-                    g = rng.integers(0, 256, ng * 64, dtype=np.uint8); u = rng.integers(0, 256, ng * 64, dtype=np.uint8)
-                    d = rng.integers(0, 256, nd * 64, dtype=np.uint8)
-                    gs = np.full(ng * 4, 0x1A00, np.uint16); us = np.full(ng * 4, 0x1A00, np.uint16); ds = np.full(nd * 4, 0x1A00, np.uint16)
-                m.upload_expert(e, g, gs, u, us, d, ds)
-            layers.append(m)
-        per_expert = (3 * I * D + 4 * (2 * I + D)) if fmt == mb.WF_I8 else (2 * (I // 4) * (D // 32) * 72 + (D // 4) * (I // 32) * 72)
+    for name in MOE_SHAPES:
+        E, K = MOE_SHAPES[name][:2]
+        layers, per_expert = make_moe_layers(mb, name, 4, local, rng)
         with torch.cuda.stream(stream):
             for S in (1, 64):
-                x = torch.randn((S, D), device=dev)
-                logits = [torch.randn((S, E), device=dev) for _ in range(8)]
-                outp = torch.empty((S, D), device=dev)
-                # a decode step runs its layers back to back: time runs of 16 consecutive layer calls
-                # (the four weight sets cycled, 50-200 MB each: not L2-resident) and divide
-                for it in range(8):
-                    layers[it % 4].apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
-                ev = []
-                for rep in range(5):
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record(stream)
-                    for it in range(16):
-                        layers[it % 4].apply_dev(outp.data_ptr(), x.data_ptr(), S, logits[it % 8].data_ptr(), 0 if S == 1 else 1, 1, 0, 0, sp)
-                    e1.record(stream)
-                    ev.append((e0, e1))
-                torch.cuda.synchronize()
-                us = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3 / 16
+                us = time_moe(torch, layers, name, S, dev, stream)
                 touched = K * per_expert if S == 1 else min(E, S * K) * per_expert
                 rows.append({"layer": name, "S": S, "us": round(us, 1), "expert_GBs": round(touched / us / 1e3, 1)})
         for m in layers:
@@ -440,11 +460,20 @@ def run_case(args):
     workload for ncu captures of a single kernel)."""
     import torch
     import moty_b200 as mb
-    fmt, S, O, I = args.case.split(":")
-    S, O, I = int(S), int(O), int(I)
+    parts = args.case.split(":")
     mb.init([0])
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(3)
+    if parts[0] == "moe":                                      # moe:NAME:S -- layer calls of a routed layer, two weight sets
+        name, S = parts[1], int(parts[2])
+        layers, per_expert = make_moe_layers(mb, name, 2, 0, rng)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            us = time_moe(torch, layers, name, S, dev, stream, reps=max(1, args.steps // 16), run=16)
+        print(json.dumps({"case": args.case, "us_per_layer": round(us, 2)}), flush=True)
+        return
+    fmt, S, O, I = parts
+    S, O, I = int(S), int(O), int(I)
     if fmt == "q8_0":
         w = mb.Mat.i8(rng.integers(-127, 128, (O, I), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
         nbytes = algo_bytes(O, I, S)
@@ -478,8 +507,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
-    ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0 or q4r4): time only that product, "
-                                                "--steps launches after --warmup, print one row and exit")
+    ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0 or q4r4) times only that product, "
+                                                "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
+                                                "times calls of one routed layer; prints one row and exits")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -58,6 +58,20 @@ def test_q4r4_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I,S", [(4096, 256, 320), (4096, 352, 157), (4100, 96, 163), (2052, 3840, 33), (4096, 64, 321)])
+def test_q4r4_batches_vs_oracle(gpu, oracle, O, I, S):
+    """Batches large enough for the 16- and 32-token CTA tiles of the MMA kernel, ragged in every
+    dimension: rows not a multiple of 128, tokens not a multiple of 8 (mixed 4-token / single-token
+    formulas in the last tile), group counts that are not a multiple of the 8-group stage."""
+    rng = np.random.default_rng(O + I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, s16 = oracle.pack_q4r4(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.q4r4(q4, s16, O, I), x)
+    yo = oracle.matmul_q4r4_s(x, q4, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
 def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
     """tests/q4r4_tests.c:88-172: extreme codes and activations, long rows."""
     O, I = 8, 16384
