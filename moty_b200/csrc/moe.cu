@@ -42,70 +42,82 @@ int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st
 //   ord[s*K + j]: the token's selections in combine order
 //   form[p]: which of the two Q4R4 kernels the reference would use for that row
 // ---------------------------------------------------------------------------
+//
+// The selections are cut into 32 contiguous segments, one per warp.  Pass A counts every
+// segment's selections per expert (warp-private rows of a [32][E] table, lanes with the same
+// expert found by match_any); a prefix over the warps turns the rows into each segment's first
+// position inside the expert's list; pass B walks the segments again and hands out positions in
+// ascending selection order, which keeps tokens ascending inside an expert (the order of the
+// reference's gathered batches, nn/moe.c:172-186).
 __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
     extern __shared__ int sh[];
-    int *cnt = sh, *off = sh + a.E;                      // [E] each
+    int *cnt = sh, *off = sh + a.E, *toff = sh + 2 * a.E, *wcnt = sh + 3 * a.E;      // [E], [E], [E], [32][E]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int SK = a.S * a.K;
-    for (int e = tid; e < a.E; e += 1024) cnt[e] = 0;
+    const int SK = a.S * a.K, E = a.E;
+    const int seg = ((SK + 31) / 32 + 31) / 32 * 32;                                 // selections per warp, a multiple of 32
+    const int i_lo = warp * seg, i_hi = i_lo + seg < SK ? i_lo + seg : SK;
+    pdl_trigger();
+    pdl_wait();                                                                      // idx comes from the router launch
+    for (int j = tid; j < 32 * E; j += 1024) wcnt[j] = 0;
     __syncthreads();
-    // pass 1: counts (a token never selects the same expert twice)
-    for (int e = a.e_lo + warp; e < a.e_hi; e += 32) {
-        int c = 0;
-        for (int i = lane; i < SK; i += 32) c += (a.idx[i] == e);
-        c = warp_sum_i32(c);
-        if (lane == 0) cnt[e] = c;
+    for (int i0 = i_lo; i0 < i_hi; i0 += 32) {                                       // pass A
+        const int i = i0 + lane;
+        const int e = i < i_hi ? a.idx[i] : -1;
+        const bool hit = e >= a.e_lo && e < a.e_hi;
+        const unsigned m = __match_any_sync(0xffffffffu, hit ? e : -1 - lane);      // misses match nobody
+        if (hit && (m & ((1u << lane) - 1u)) == 0) wcnt[warp * E + e] += __popc(m);  // lowest lane of each expert's set
+        __syncwarp();
+    }
+    __syncthreads();
+    for (int e = tid; e < E; e += 1024) {                                            // exclusive prefix over the warps
+        int run = 0;
+        for (int w = 0; w < 32; w++) { int t = wcnt[w * E + e]; wcnt[w * E + e] = run; run += t; }
+        cnt[e] = run;
     }
     __syncthreads();
     if (tid == 0) {
         int run = 0, nt = 0;
-        for (int e = 0; e < a.E; e++) {
-            off[e] = run;
-            int c = cnt[e];
-            for (int r0 = 0; r0 < c; r0 += a.T) {
-                int nr = c - r0 < a.T ? c - r0 : a.T;
-                int le = e - a.e_lo;
-                if (a.q8) {
-                    a.t8_gate[nt] = Q8Tile{a.g8 + (size_t)le * a.gstride, a.gs + (size_t)le * a.gsstride, run + r0, nr};
-                    a.t8_up[nt]   = Q8Tile{a.u8 + (size_t)le * a.gstride, a.us + (size_t)le * a.gsstride, run + r0, nr};
-                    a.t8_down[nt] = Q8Tile{a.d8 + (size_t)le * a.dstride, a.ds + (size_t)le * a.dsstride, run + r0, nr};
-                } else {
-                    a.t4_gate[nt] = Q4Tile{a.g4 + (size_t)le * a.gstride, a.gs16 + (size_t)le * a.gsstride, run + r0, nr};
-                    a.t4_up[nt]   = Q4Tile{a.u4 + (size_t)le * a.gstride, a.us16 + (size_t)le * a.gsstride, run + r0, nr};
-                    a.t4_down[nt] = Q4Tile{a.d4 + (size_t)le * a.dstride, a.ds16 + (size_t)le * a.dsstride, run + r0, nr};
-                }
-                nt++;
-            }
-            run += c;
-        }
+        for (int e = 0; e < E; e++) { off[e] = run; toff[e] = nt; run += cnt[e]; nt += (cnt[e] + a.T - 1) / a.T; }
         *a.ntiles = nt;
         *a.npairs = run;
     }
     __syncthreads();
-    // pass 2: positions, tokens ascending inside an expert
-    for (int e = a.e_lo + warp; e < a.e_hi; e += 32) {
-        int base = off[e], c = cnt[e];
-        for (int i0 = 0; i0 < SK; i0 += 32) {
-            int i = i0 + lane;
-            bool hit = i < SK && a.idx[i] == e;
-            unsigned m = __ballot_sync(0xffffffffu, hit);
-            if (hit) {
-                int p = base + __popc(m & ((1u << lane) - 1u));
-                a.pair_tok[p] = i / a.K;
-                a.pos_of[i] = p;
-                if (a.form) {
-                    int t = p - off[e];                  // row inside this expert's gathered batch
-                    int t0 = t / 32 * 32, ns = c - t0 < 32 ? c - t0 : 32;
-                    a.form[p] = (t - t0) < ns / 4 * 4 ? 1 : 0;
-                }
+    for (int e = tid; e < E; e += 1024) {                                            // tile tables: up to T positions of one expert
+        const int c = cnt[e], le = e - a.e_lo;
+        int nt = toff[e];
+        for (int r0 = 0; r0 < c; r0 += a.T, nt++) {
+            const int nr = c - r0 < a.T ? c - r0 : a.T, row0 = off[e] + r0;
+            if (a.q8) {
+                a.t8_gate[nt] = Q8Tile{a.g8 + (size_t)le * a.gstride, a.gs + (size_t)le * a.gsstride, row0, nr};
+                a.t8_up[nt]   = Q8Tile{a.u8 + (size_t)le * a.gstride, a.us + (size_t)le * a.gsstride, row0, nr};
+                a.t8_down[nt] = Q8Tile{a.d8 + (size_t)le * a.dstride, a.ds + (size_t)le * a.dsstride, row0, nr};
+            } else {
+                a.t4_gate[nt] = Q4Tile{a.g4 + (size_t)le * a.gstride, a.gs16 + (size_t)le * a.gsstride, row0, nr};
+                a.t4_up[nt]   = Q4Tile{a.u4 + (size_t)le * a.gstride, a.us16 + (size_t)le * a.gsstride, row0, nr};
+                a.t4_down[nt] = Q4Tile{a.d4 + (size_t)le * a.dstride, a.ds16 + (size_t)le * a.dsstride, row0, nr};
             }
-            base += __popc(m);
         }
     }
-    // selections of non-local experts
-    for (int i = tid; i < SK; i += 1024) {
-        int e = a.idx[i];
-        if (e < a.e_lo || e >= a.e_hi) a.pos_of[i] = -1;
+    for (int i0 = i_lo; i0 < i_hi; i0 += 32) {                                       // pass B
+        const int i = i0 + lane;
+        const int e = i < i_hi ? a.idx[i] : -1;
+        const bool hit = e >= a.e_lo && e < a.e_hi;
+        const unsigned m = __match_any_sync(0xffffffffu, hit ? e : -1 - lane);
+        if (hit) {
+            const int t = wcnt[warp * E + e] + __popc(m & ((1u << lane) - 1u));      // row inside this expert's gathered batch
+            const int p = off[e] + t;
+            a.pair_tok[p] = i / a.K;
+            a.pos_of[i] = p;
+            if (a.form) {
+                const int c = cnt[e], t0 = t / 32 * 32, ns = c - t0 < 32 ? c - t0 : 32;
+                a.form[p] = (t - t0) < ns / 4 * 4 ? 1 : 0;
+            }
+        } else if (i < i_hi) {
+            a.pos_of[i] = -1;                                                        // selections of non-local experts
+        }
+        __syncwarp();
+        if (hit && (m & ((1u << lane) - 1u)) == 0) wcnt[warp * E + e] += __popc(m);
+        __syncwarp();
     }
     // combine order per token
     for (int s = tid; s < a.S; s += 1024) {
@@ -123,9 +135,10 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
 }
 
 int launch_moe_plan(const MoePlanArgs &a, cudaStream_t st) {
-    size_t smem = (size_t)2 * a.E * sizeof(int);
-    moe_plan_kernel<<<1, 1024, smem, st>>>(a);
-    CK(cudaGetLastError());
+    size_t smem = (size_t)(3 + 32) * a.E * sizeof(int);
+    if (smem > 200 * 1024) return moty_set_error(MOTY_CUDA_ELIMIT, "moe plan: E=%d", a.E);
+    if (smem > 48 * 1024) CK(cudaFuncSetAttribute(moe_plan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    CK(moty_launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), smem, st, a));
     return 0;
 }
 
