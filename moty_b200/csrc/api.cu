@@ -734,7 +734,10 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
                         int order, int norm_topk, int *idx_out, float *w_out, const int *eid_given, cudaStream_t st) {
     const int E = m->E, K = eid_given ? 1 : m->K, I = m->I, D = m->D;
     const bool q8 = m->efmt == MOTY_WF_I8;
-    const int T = q8 ? 8 : 4;
+    // rows per tile of the grouped products: 8 for the int8 tile kernel; 8, 16 or 32 for the Q4R4 MMA kernel
+    // (more when experts see more rows each)
+    int T = 8;
+    if (!q8) { long long per = (long long)S * K / (m->e_hi - m->e_lo > 0 ? m->e_hi - m->e_lo : 1); T = per >= 24 ? 32 : (per >= 12 ? 16 : 8); }
     CKR(moe_ensure_plan(m, eid_given ? (S + m->K - 1) / m->K : S));
     const int *idxp = m->idx; const float *wp = m->w;
     if (eid_given) {
@@ -858,24 +861,19 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         CKR(moty_grow(c, &c->hxs, P * nbI * 4));
         CKR(moty_grow(c, &c->hxsum, P * nbI * 4));
         CKR(launch_quant_g32(x, S, D, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
-        Q4Args a; memset(&a, 0, sizeof a);
-        a.ntiles_dev = m->counters; a.ntiles_max = ntiles_max;
-        a.xq = (const int8_t *)c->xi.p; a.xs = (const float *)c->xs.p; a.xsum = (const int32_t *)c->xsum.p;
-        a.xmap = m->pair_tok; a.form = m->form;
-        a.ldy = I; a.S = (int)P; a.I = D; a.O = I;
-        a.tiles = (const Q4Tile *)m->t_gate; a.y = (float *)c->g.p;
-        CKR(launch_q4r4_small(a, c->sms, st));
-        a.tiles = (const Q4Tile *)m->t_up; a.y = (float *)c->u.p;
-        CKR(launch_q4r4_small(a, c->sms, st));
+        const size_t P8 = (P + 7) / 8 * 8;
+        CKR(moty_grow(c, &c->rec, P8 * (size_t)(nbD > nbI ? nbD : nbI) * 8));
+        CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_gate, m->counters, ntiles_max, T, m->counters + 1,
+                                    (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
+                                    m->pair_tok, m->form, (int2 *)c->rec.p, 1, (float *)c->g.p, I, (int)P, D, I, st));
+        CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_up, m->counters, ntiles_max, T, m->counters + 1,
+                                    (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
+                                    m->pair_tok, m->form, (int2 *)c->rec.p, 0, (float *)c->u.p, I, (int)P, D, I, st));
         CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
         CKR(launch_quant_g32((const float *)c->g.p, (int)P, I, (int8_t *)c->hq.p, (float *)c->hxs.p, (int32_t *)c->hxsum.p, st));
-        Q4Args b; memset(&b, 0, sizeof b);
-        b.ntiles_dev = m->counters; b.ntiles_max = ntiles_max;
-        b.xq = (const int8_t *)c->hq.p; b.xs = (const float *)c->hxs.p; b.xsum = (const int32_t *)c->hxsum.p;
-        b.form = m->form;
-        b.ldy = D; b.S = (int)P; b.I = I; b.O = D;
-        b.tiles = (const Q4Tile *)m->t_down; b.y = (float *)c->h.p;
-        CKR(launch_q4r4_small(b, c->sms, st));
+        CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_down, m->counters, ntiles_max, T, m->counters + 1,
+                                    (const int8_t *)c->hq.p, (const float *)c->hxs.p, (const int32_t *)c->hxsum.p,
+                                    nullptr, m->form, (int2 *)c->rec.p, 1, (float *)c->h.p, D, (int)P, I, D, st));
     }
     CKR(launch_moe_combine(out, (const float *)c->h.p, wp, m->pos_of, m->ord, S, K, D, st));
     if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, P * 4, cudaMemcpyDeviceToDevice, st));

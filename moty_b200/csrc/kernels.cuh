@@ -78,6 +78,11 @@ int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
                     int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int sms, cudaStream_t st);
 
+int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
+                            const int *npairs_dev, const int8_t *xq, const float *xs, const int32_t *xsum,
+                            const int *xmap, const uint8_t *form, int2 *rec, int build_rec, float *y, int ldy, int P,
+                            int I, int O, cudaStream_t st);
+
 // ---- router.cu ----------------------------------------------------------------------
 int launch_route(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs,
                  int do_softmax, int norm_topk, cudaStream_t st);

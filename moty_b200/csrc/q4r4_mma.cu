@@ -26,6 +26,7 @@
 //   token-by-token (hw/hw_q4r4.h:58-59), v = 8*xsum:        acc = fma((float)(sum - v), d*xs, acc)
 //   4-token tile   (hw/hw_q4r4.h:78-81), v = (8*xsum)*xs:   acc = fma((float)sum, d*xs, acc); acc = fma(-d, v, acc)
 #include "kernels.cuh"
+#include <string.h>
 
 struct Q4MmaArgs {
     const uint8_t *w; const uint16_t *d;
@@ -34,6 +35,9 @@ struct Q4MmaArgs {
     const uint8_t *form;                      // per token: 1 = 4-token-tile formula
     float *y; int ldy;
     int S, S8, I, O;
+    // grouped mode (MoE batches): CTA row y of the grid is a tile = up to 8 NT consecutive rows of the
+    // gathered batch that share one expert's matrix; xq rows are found through xmap (null: identity)
+    const Q4Tile *tiles; const int *ntiles_dev; const int *xmap;
 };
 
 // D = A (16x32 u8, row) * B (32x8 s8, col), accumulator input zero
@@ -88,10 +92,18 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
     extern __shared__ int4 smem_q4mma[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(smem_q4mma);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tid = lane & 3;
-    const int I = a.I, nb = I / 32, O = a.O, S = a.S;
+    const int I = a.I, nb = I / 32, O = a.O;
+    const uint8_t *Wp = a.w; const uint16_t *Dp = a.d;
+    int n00 = blockIdx.y * NT * 8, S = a.S;                    // first token of the CTA, end of its token range
+    pdl_trigger();
+    if (a.tiles) {
+        pdl_wait();                                            // the tile table comes from the plan kernel
+        if ((int)blockIdx.y >= *a.ntiles_dev) return;          // CTA-uniform
+        const Q4Tile t = a.tiles[blockIdx.y];
+        Wp = t.w; Dp = t.d; n00 = t.row0; S = t.row0 + t.nrows;
+    }
     const int nblk = (O + 3) / 4, nstage = (nb + GCH - 1) / GCH;
     const int mt = blockIdx.x * 8 + warp;                      // this warp's M tile (may lie past the end: it still copies and syncs)
-    const int n00 = blockIdx.y * NT * 8;                       // first token of the CTA
     const int row_a = mt * 16 + gid, row_b = row_a + 8;
     // where this thread's fragment words and scales sit inside a stage
     const int ba_l = gid >> 2, bb_l = ba_l + 2, rr = gid & 3;
@@ -107,12 +119,12 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
         for (int q = 0; q < 4; q++) {
             int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
             if (nb >= GCH || lane * 16 < nb * 64)
-                cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + lane * 16, a.w + ((size_t)blk * nb + gs) * 64 + lane * 16);
+                cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + lane * 16, Wp + ((size_t)blk * nb + gs) * 64 + lane * 16);
         }
         const int q = lane >> 3, part = lane & 7;
         int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
         if (nb >= GCH || part < nb)
-            cp_async8(dst + L::D + warp * STG_D1 + q * 64 + part * 8, a.d + ((size_t)blk * nb + gs) * 4 + part * 4);
+            cp_async8(dst + L::D + warp * STG_D1 + q * 64 + part * 8, Dp + ((size_t)blk * nb + gs) * 4 + part * 4);
     };
     auto fill_x = [&](int s) {                                 // activation side: codes and records of the CTA's tokens
         if (s >= nstage) return;
@@ -121,16 +133,24 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
         for (int t = threadIdx.x; t < NT * 128; t += 256) {    // 16 chunks of 16 bytes per token
             const int tok = t >> 4, ch = t & 15;
             int n = n00 + tok; n = n < S ? n : S - 1;
+            if (a.xmap) n = a.xmap[n];
             if (nb >= GCH || ch * 16 < nb * 32)
                 cp_async16(dst + L::B + tok * BTOK + ch * 16, a.xq + (size_t)n * I + (size_t)gs * 32 + ch * 16);
         }
-        for (int t = threadIdx.x; t < NT * GCH * 4; t += 256) {   // per N tile and group: four token pairs of 16 bytes
-            const int j = t / (GCH * 4), u = (t >> 2) % GCH, pr = t & 3;
-            if (gs + u < nb && n00 + j * 8 + pr * 2 < a.S8)        // token pairs past the padded batch: nothing to copy, nothing stored
-                cp_async16(dst + L::R + j * GCH * 64 + u * 64 + pr * 16, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + pr * 2);
+        if (!a.tiles) {
+            for (int t = threadIdx.x; t < NT * GCH * 4; t += 256) {   // per N tile and group: four token pairs of 16 bytes
+                const int j = t / (GCH * 4), u = (t >> 2) % GCH, pr = t & 3;
+                if (gs + u < nb && n00 + j * 8 + pr * 2 < a.S8)        // token pairs past the padded batch: nothing to copy, nothing stored
+                    cp_async16(dst + L::R + j * GCH * 64 + u * 64 + pr * 16, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + pr * 2);
+            }
+        } else {
+            for (int t = threadIdx.x; t < NT * GCH * 8; t += 256) {   // a tile may start at an odd row: single 8-byte records
+                const int j = t / (GCH * 8), u = (t >> 3) % GCH, k = t & 7;
+                if (gs + u < nb && n00 + j * 8 + k < S)
+                    cp_async8(dst + L::R + j * GCH * 64 + u * 64 + k * 8, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + k);
+            }
         }
     };
-    pdl_trigger();
     fill_w(0); fill_w(1);                                      // weights only: may overlap the previous kernel
     pdl_wait();                                                // codes and records come from the kernels before this one
     fill_x(0); cp_async_commit();
@@ -216,7 +236,7 @@ __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__
 }
 
 template <int NT>
-static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st) {
+static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st, int ntiles_max = 0) {
     constexpr int SMEM = NSTG * Q4Stage<NT>::BYTES;
     static bool attr_done[MOTY_MAX_DEV];
     int dev = 0;
@@ -227,7 +247,7 @@ static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st) {
         attr_done[dev] = true;
     }
     const int nmt = (a.O + 15) / 16;
-    dim3 grid((nmt + 7) / 8, (a.S + 8 * NT - 1) / (8 * NT));
+    dim3 grid((nmt + 7) / 8, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT));
     if (grid.y > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q4r4_mma: S=%d in one call", a.S);
     CK(moty_launch_pdl(q4r4_mma_kernel<NT>, grid, dim3(256), (size_t)SMEM, st, a));
     return 0;
@@ -243,11 +263,55 @@ int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const
     const long long nrec = (long long)S8 * nb;
     q4r4_rec_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, rec, form, S, S8, nb);
     CK(cudaGetLastError());
-    Q4MmaArgs a;
+    Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
     // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
     const long long mct = ((O + 15) / 16 + 7) / 8, want = (long long)sms * 2;
     if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4>(a, st);
     if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2>(a, st);
     return launch_mma_t<1>(a, st);
+}
+
+// records of a gathered batch: row p of the batch is row xmap[p] (null: p) of xs/xsum, its formula
+// flag form[p] comes with the plan; rows at and past *npairs_dev are zero
+__global__ void __launch_bounds__(256) q4r4_rec_gather_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
+                                                              const int *__restrict__ xmap, const uint8_t *__restrict__ form,
+                                                              const int *__restrict__ npairs_dev, int2 *__restrict__ rec,
+                                                              int P8, int nb) {
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= (long long)P8 * nb) return;
+    const int g = (int)(i / P8), p = (int)(i - (long long)g * P8);
+    int2 r = make_int2(0, 0);
+    if (p < *npairs_dev) {
+        const int t = xmap ? xmap[p] : p;
+        const float sc = xs[(size_t)t * nb + g]; const int sm = xsum[(size_t)t * nb + g];
+        r.x = __float_as_int(sc);
+        r.y = form[p] ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm;
+    }
+    rec[i] = r;
+}
+
+// Grouped products of a MoE batch: tiles[i] = {expert matrix, first row, rows <= tile_rows} over a
+// gathered batch of at most P rows (tile_rows is 8, 16 or 32 and is what the plan was built with).
+// y row p receives the product for batch row p.  xs/xsum are indexed like xq (through xmap).
+int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
+                            const int *npairs_dev, const int8_t *xq, const float *xs, const int32_t *xsum,
+                            const int *xmap, const uint8_t *form, int2 *rec, int build_rec, float *y, int ldy, int P,
+                            int I, int O, cudaStream_t st) {
+    if (I % 32 != 0 || I <= 0 || P <= 0 || (tile_rows != 8 && tile_rows != 16 && tile_rows != 32))
+        return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma_grouped: P=%d I=%d tile=%d", P, I, tile_rows);
+    if (O <= 0 || ntiles_max <= 0) return 0;
+    if (ntiles_max > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q4r4_mma_grouped: %d tiles in one call", ntiles_max);
+    const int nb = I / 32, P8 = (P + 7) / 8 * 8;
+    const long long nrec = (long long)P8 * nb;
+    if (build_rec) {                                           // gate and up share the records of the gathered input
+        q4r4_rec_gather_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, xmap, form, npairs_dev, rec, P8, nb);
+        CK(cudaGetLastError());
+    }
+    Q4MmaArgs a; memset(&a, 0, sizeof a);
+    a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = P; a.S8 = P8; a.I = I; a.O = O;
+    a.tiles = tiles; a.ntiles_dev = ntiles_dev; a.xmap = xmap;
+    if (tile_rows == 32) return launch_mma_t<4>(a, st, ntiles_max);
+    if (tile_rows == 16) return launch_mma_t<2>(a, st, ntiles_max);
+    return launch_mma_t<1>(a, st, ntiles_max);
 }

@@ -74,7 +74,7 @@ def test_moe_q8_vs_oracle(gpu, oracle, E, K, I, D, S):
     assert close(m.olmoe(x, logits, 0), want, 2e-3)
 
 
-@pytest.mark.parametrize("S", [1, 3, 21])
+@pytest.mark.parametrize("S", [1, 3, 21, 80, 130])        # 80 and 130: 16- and 32-row tiles of the grouped MMA kernel
 def test_moe_q4r4_vs_oracle(gpu, oracle, S):
     from oracle import Experts
     E, K, I, D = 16, 4, 96, 128
