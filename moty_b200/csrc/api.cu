@@ -236,6 +236,9 @@ extern "C" int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *
 // mat_apply
 // ---------------------------------------------------------------------------
 static const int Q8_TC_MIN_S = 9;
+// up to this many rows the register-accumulator MMA kernel (weights streamed once) is at least as fast
+// as the 128-row tcgen05 tiles; measured crossover on 15360x3840, 151936x1024, 3840x15360
+static const int Q8_MMA_MAX_S = 16;
 
 static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int S, int32_t *acc, cudaStream_t st) {
     if (S <= 0) return 0;
@@ -256,6 +259,9 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
+        if (vec && S > 8 && S <= Q8_MMA_MAX_S)                   // small batches: weights streamed once, mma.sync
+            return launch_q8_mma((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                                 (const float *)c->sx.p, y, acc, S, I, O, c->sms, st);
         if (tc) return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
         if (stream_ok) {
             for (int s0 = 0; s0 < S; s0 += 8) {
@@ -737,7 +743,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
     // rows per tile of the grouped products: 8 for the int8 tile kernel; 8, 16 or 32 for the Q4R4 MMA kernel
     // (more when experts see more rows each)
     int T = 8;
-    if (!q8) { long long per = (long long)S * K / (m->e_hi - m->e_lo > 0 ? m->e_hi - m->e_lo : 1); T = per >= 24 ? 32 : (per >= 12 ? 16 : 8); }
+    { long long per = (long long)S * K / (m->e_hi - m->e_lo > 0 ? m->e_hi - m->e_lo : 1); T = per >= 24 ? 32 : (per >= 12 ? 16 : 8); }
     CKR(moe_ensure_plan(m, eid_given ? (S + m->K - 1) / m->K : S));
     const int *idxp = m->idx; const float *wp = m->w;
     if (eid_given) {
@@ -836,22 +842,14 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         CKR(moty_grow(c, &c->hq, P * I + 16));
         CKR(moty_grow(c, &c->hs, P * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, D, st));
-        Q8Args a; memset(&a, 0, sizeof a);
-        a.ntiles_dev = m->counters; a.ntiles_max = ntiles_max;
-        a.xi = (const int8_t *)c->xi.p; a.sx = (const float *)c->sx.p; a.xmap = m->pair_tok;
-        a.ldy = I; a.S = (int)P; a.I = D; a.O = I;
-        a.tiles = (const Q8Tile *)m->t_gate; a.y = (float *)c->g.p;
-        CKR(launch_q8_small(a, c->sms, st));
-        a.tiles = (const Q8Tile *)m->t_up; a.y = (float *)c->u.p;
-        CKR(launch_q8_small(a, c->sms, st));
+        CKR(launch_q8_mma_grouped((const Q8Tile *)m->t_gate, m->counters, ntiles_max, T, (const int8_t *)c->xi.p,
+                                  (const float *)c->sx.p, m->pair_tok, (float *)c->g.p, I, D, I, st));
+        CKR(launch_q8_mma_grouped((const Q8Tile *)m->t_up, m->counters, ntiles_max, T, (const int8_t *)c->xi.p,
+                                  (const float *)c->sx.p, m->pair_tok, (float *)c->u.p, I, D, I, st));
         CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
         CKR(launch_qrow_i8((const float *)c->g.p, (int8_t *)c->hq.p, (float *)c->hs.p, (int)P, I, st));
-        Q8Args b; memset(&b, 0, sizeof b);
-        b.ntiles_dev = m->counters; b.ntiles_max = ntiles_max;
-        b.xi = (const int8_t *)c->hq.p; b.sx = (const float *)c->hs.p;
-        b.ldy = D; b.S = (int)P; b.I = I; b.O = D;
-        b.tiles = (const Q8Tile *)m->t_down; b.y = (float *)c->h.p;
-        CKR(launch_q8_small(b, c->sms, st));
+        CKR(launch_q8_mma_grouped((const Q8Tile *)m->t_down, m->counters, ntiles_max, T, (const int8_t *)c->hq.p,
+                                  (const float *)c->hs.p, nullptr, (float *)c->h.p, D, I, D, st));
     } else {
         int nbD = D / 32, nbI = I / 32;
         CKR(moty_grow(c, &c->xi, (size_t)S * D + 16));

@@ -100,6 +100,21 @@ inline cudaError_t moty_launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
 }
 
+// 16-byte and 8-byte asynchronous copies global -> shared (.cg: around L1, for data read once);
+// cp_async16_zfill copies nothing and writes 16 zero bytes when !valid (the source is not read)
+__device__ __forceinline__ void cp_async16(void *smem, const void *g) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async16_zfill(void *smem, const void *g, bool valid) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g),
+                 "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async8(void *smem, const void *g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 __device__ __forceinline__ int4 ldg_stream16(const void *p) {
     // weights are read exactly once: keep them out of L1
     int4 v;

@@ -74,6 +74,14 @@ int launch_q4r4_small(const Q4Args &a, int sms, cudaStream_t st);
 // which of the reference's two kernels each of S tokens goes through
 int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 
+// ---- q8_mma.cu: Q8_0 x a small batch (mma.sync, weights streamed once), dense and grouped ----
+bool q8_mma_supported(int S, int I, int O);
+int launch_q8_mma(const int8_t *w, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
+                  int S, int I, int O, int sms, cudaStream_t st);
+int launch_q8_mma_grouped(const Q8Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
+                          const int8_t *xi, const float *sx, const int *xmap, float *y, int ldy, int I, int O,
+                          cudaStream_t st);
+
 // ---- q4r4_mma.cu: Q4R4 x a batch of rows, integer MMA per group + the sequential f32 chain ----
 int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
                     int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int sms, cudaStream_t st);

@@ -63,16 +63,6 @@ __device__ __forceinline__ float q4_chain_step(float acc, int sum, float d, int 
     return acc;
 }
 
-// 16-byte and 8-byte asynchronous copies global -> shared (.cg: around L1, for data read once)
-__device__ __forceinline__ void cp_async16(void *smem, const void *g) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
-}
-__device__ __forceinline__ void cp_async8(void *smem, const void *g) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 // A CTA takes 8 M tiles (128 weight rows, one M tile per warp) x NT N tiles (8 NT tokens) and walks
 // the groups in stages of GCH = 8.  One stage in shared memory:
 //   W  per warp: its four blocks' codes, 4 x 512 bytes, each block padded by 64 bytes so that the two
