@@ -74,6 +74,10 @@ int launch_q4r4_small(const Q4Args &a, int sms, cudaStream_t st);
 // which of the reference's two kernels each of S tokens goes through
 int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 
+// ---- q4r4_gemv1.cu: Q4R4 decode GEMV for matrices with many rows (lane = row) ----
+bool q4r4_gemv1_supported(int I, int O, int sms);
+int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float *y, int I, int O, int sms, cudaStream_t st);
+
 // ---- q8_mma.cu: Q8_0 x a small batch (mma.sync, weights streamed once), dense and grouped ----
 bool q8_mma_supported(int S, int I, int O);
 int launch_q8_mma(const int8_t *w, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,

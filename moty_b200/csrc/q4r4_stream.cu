@@ -246,6 +246,7 @@ int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, cons
     if (O <= 0) return 0;
     Q4StreamArgs a;
     a.w = w; a.d = d; a.x = x; a.xq = xq; a.xs = xs; a.xsum = xsum; a.form = form; a.y = y; a.S = S; a.I = I; a.O = O;
+    if (S == 1 && x && q4r4_gemv1_supported(I, O, sms)) return launch_q4r4_gemv1(w, d, x, y, I, O, sms, st);   // many rows: lane = row
     if (S == 1 && x) return launch_q4s_gs<1, true>(a, sms, st);
     if (S == 1) return launch_q4s_gs<1, false>(a, sms, st);
     if (S == 2) return launch_q4s_gs<2, false>(a, sms, st);

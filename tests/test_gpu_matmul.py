@@ -72,6 +72,19 @@ def test_q4r4_batches_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I", [(57000, 256), (56833, 512), (151936, 1024)])
+def test_q4r4_decode_many_rows_vs_oracle(gpu, oracle, O, I):
+    """Matrices with enough rows for the lane-per-row decode kernel (one activation row), a row
+    count that is not a multiple of 32, and the vocabulary shape of the benchmark."""
+    rng = np.random.default_rng(O + I)
+    q4 = rng.integers(0, 256, (O + 3) // 4 * (I // 32) * 64, dtype=np.uint8)
+    s16 = rng.uniform(0.001, 0.01, (O + 3) // 4 * (I // 32) * 4).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal((1, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.q4r4(q4, s16, O, I), x)
+    yo = oracle.matmul_q4r4_s(x, q4, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
 def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
     """tests/q4r4_tests.c:88-172: extreme codes and activations, long rows."""
     O, I = 8, 16384
