@@ -81,6 +81,10 @@ __device__ __forceinline__ void umma_commit(uint64_t *bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// warp 0: TMA producer; warp 1: MMA issuer; warps 2..9: epilogue (two warps per TMEM lane quarter, each
+// taking half of the accumulator's columns)
+constexpr int TC_EPI_WARPS = 8, TC_THREADS = 64 + 32 * TC_EPI_WARPS;
+
 struct TcArgs {
     const float *scale; const float *sx; float *y; int32_t *acc;
     int S, I, O;
@@ -88,7 +92,7 @@ struct TcArgs {
 };
 
 template <int BN, int STAGES, int MT>
-__global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ CUtensorMap mapA,
+__global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_constant__ CUtensorMap mapA,
                                                        const __grid_constant__ CUtensorMap mapB, TcArgs a) {
     extern __shared__ uint8_t smem_raw[];
     // 1024-byte alignment for the swizzled tiles
@@ -112,7 +116,7 @@ __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ C
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int i = 0; i < STAGES; i++) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
-        for (int i = 0; i < 2; i++) { mbar_init(&tmem_full_bar[i], 1); mbar_init(&tmem_empty_bar[i], 4); }
+        for (int i = 0; i < 2; i++) { mbar_init(&tmem_full_bar[i], 1); mbar_init(&tmem_empty_bar[i], TC_EPI_WARPS); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -184,8 +188,11 @@ __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ C
             }
         }
     } else {
-        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31
-        const int q = warp & 3;
+        // epilogue: warp w may touch TMEM lanes 32*(w%4) .. +31; the two warps of a quarter split the columns
+        const int q = warp & 3, half = (warp - 2) >> 2;
+        constexpr int CPW = BN >= 32 ? BN / 2 : BN;                       // columns per warp (BN = 16: the second warp idles)
+        const int col_lo = BN >= 32 ? half * CPW : 0;
+        const bool works = BN >= 32 || half == 0;
         uint32_t tl = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
             const int m0 = (t / ntn) * MT * BM, n0 = (t % ntn) * BN;
@@ -196,30 +203,47 @@ __global__ void __launch_bounds__(192, 1) q8_tc_kernel(const __grid_constant__ C
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int mt = 0; mt < MT; mt++) {
-            const int o = m0 + mt * BM + q * 32 + lane;
-            const float sc = o < a.O ? __ldg(a.scale + o) : 0.f;
+            for (int mt = 0; mt < MT && works; mt++) {
+                const int o = m0 + mt * BM + q * 32 + lane;
+                const bool row_ok = o < a.O;
+                const float sc = row_ok ? __ldg(a.scale + o) : 0.f;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
-                if (n0 + c0 >= a.S) break;                                 // warp-uniform
-                uint32_t r[16];
-                uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt) * BN + (uint32_t)c0;
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                    : "r"(taddr));
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                for (int c0 = col_lo; c0 < col_lo + CPW; c0 += 16) {
+                    const int s0 = n0 + c0;
+                    if (s0 >= a.S) break;                                  // warp-uniform
+                    uint32_t r[16];
+                    uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (buf * MT + mt) * BN + (uint32_t)c0;
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                        : "r"(taddr));
+                    if (s0 + 16 <= a.S && !a.acc) {
+                        // full chunk: the 16 token scales arrive while the accumulator is read; per token one
+                        // conversion, two multiplies, one store of 32 consecutive rows
+                        float sx[16];
+                        const float4 *sx4 = reinterpret_cast<const float4 *>(a.sx + s0);
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    int s = n0 + c0 + j;
-                    if (s < a.S && o < a.O) {
-                        int v = (int)r[j];
-                        a.y[(size_t)s * a.O + o] = __fmul_rn(__fmul_rn(sc, __ldg(a.sx + s)), (float)v);
-                        if (a.acc) a.acc[(size_t)s * a.O + o] = v;
+                        for (int j = 0; j < 4; j++) { float4 v = __ldg(sx4 + j); sx[4 * j] = v.x; sx[4 * j + 1] = v.y; sx[4 * j + 2] = v.z; sx[4 * j + 3] = v.w; }
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (row_ok) {
+                            float *yp = a.y + (size_t)s0 * a.O + o;
+#pragma unroll
+                            for (int j = 0; j < 16; j++) yp[(size_t)j * a.O] = __fmul_rn(__fmul_rn(sc, sx[j]), (float)(int)r[j]);
+                        }
+                    } else {
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            int s = s0 + j;
+                            if (s < a.S && row_ok) {
+                                int v = (int)r[j];
+                                a.y[(size_t)s * a.O + o] = __fmul_rn(__fmul_rn(sc, __ldg(a.sx + s)), (float)v);
+                                if (a.acc) a.acc[(size_t)s * a.O + o] = v;
+                            }
+                        }
                     }
                 }
-            }
             }
             // this warp is done reading the accumulator: hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,7 +311,7 @@ int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi,
     a.scale = (const float *)w->scales; a.sx = sx; a.y = y; a.acc = acc; a.S = S; a.I = w->I; a.O = w->O; a.err = c->err_dev;
     int ntiles = ((w->O + MT * BM - 1) / (MT * BM)) * ((S + BN - 1) / BN);
     int grid = ntiles < c->sms ? ntiles : c->sms;             // persistent: one CTA per SM
-    k<<<grid, 192, smem, st>>>(mapA, mapB, a);
+    k<<<grid, TC_THREADS, smem, st>>>(mapA, mapB, a);
     CK(cudaGetLastError());
     return 0;
 }
