@@ -89,6 +89,9 @@ struct TcArgs {
     const float *scale; const float *sx; float *y; int32_t *acc;
     int S, I, O;
     int *err;
+    // split over K (matrices with few 128-row tiles): work item = (tile, split); every split leaves its
+    // exact int32 partial sums in part[split][S][O] and tc_splitk_finish_kernel adds and scales them
+    int ksplit; int32_t *part;
 };
 
 template <int BN, int STAGES, int MT>
@@ -108,8 +111,9 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (a.I + BKB - 1) / BKB;
     const int ntn = (a.S + BN - 1) / BN, ntm = (a.O + MT * BM - 1) / (MT * BM);
-    const int ntiles = ntm * ntn;
-    const int krot = (int)((blockIdx.x * 5u) % (unsigned)nkb);
+    const int KS = a.ksplit, nks = (nkb + KS - 1) / KS;                 // K blocks per split (the last may hold fewer, never none)
+    const int ntiles = ntm * ntn * KS;                                   // work items; item = tile * KS + split
+    const int krot = (int)((blockIdx.x * 5u) % (unsigned)nks);
     // two accumulators of BN columns: the epilogue of one tile overlaps the MMAs of the next
     constexpr uint32_t TMEM_COLS = NBUF * MT * BN < 32 ? 32 : NBUF * MT * BN;
 
@@ -136,9 +140,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
         if (lane == 0) {
             uint32_t it = 0;                                         // ring position, continuous across tiles
             for (int t = blockIdx.x; t < ntiles; t += gridDim.x) {
-                const int m0 = (t / ntn) * MT * BM, n0 = (t % ntn) * BN;
+                const int tile = t / KS, ks = t - tile * KS;
+                const int m0 = (tile / ntn) * MT * BM, n0 = (tile % ntn) * BN;
+                const int kb_lo = ks * nks, nk = nkb - kb_lo < nks ? nkb - kb_lo : nks;
                 bool ok = true;
-                for (int kb = 0; kb < nkb; kb++, it++) {
+                for (int kb = 0; kb < nk; kb++, it++) {
                     const int st = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     ok = mbar_wait(&empty_bar[st], ph ^ 1, abort_flag);
@@ -147,7 +153,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
                     uint8_t *sa = smem + (size_t)st * STAGE_BYTES;
                     // every CTA starts its K loop at another block: integer accumulation is order
                     // independent, and the CTAs stop hammering the same activation tile in L2 together
-                    const int kr = (kb + krot) % nkb;
+                    const int kr = kb_lo + (kb + krot) % nk;
                     tma_load_2d(sa, &mapA, kr * BKB, m0, &full_bar[st]);
                     if (MT == 2) tma_load_2d(sa + BM * BKB, &mapA, kr * BKB, m0 + BM, &full_bar[st]);
                     tma_load_2d(sa + A_BYTES, &mapB, kr * BKB, n0, &full_bar[st]);
@@ -167,7 +173,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tacc = tmem_base + buf * MT * BN;
-                for (int kb = 0; kb < nkb; kb++, it++) {
+                const int ks = t % KS, kb_lo = ks * nks, nk = nkb - kb_lo < nks ? nkb - kb_lo : nks;
+                for (int kb = 0; kb < nk; kb++, it++) {
                     const int st = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     ok = mbar_wait(&full_bar[st], ph, abort_flag);
@@ -177,7 +184,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
                     const uint32_t sb = sa + A_BYTES;
 #pragma unroll
                     for (int k4 = 0; k4 < BKB / 32; k4++) {
-                        if (((kb + krot) % nkb) * BKB + k4 * 32 >= a.I) break;   // nothing but zero fill beyond I
+                        if ((kb_lo + (kb + krot) % nk) * BKB + k4 * 32 >= a.I) break;   // nothing but zero fill beyond I
                         umma_i8(tacc, umma_desc(sa + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
                         if (MT == 2)
                             umma_i8(tacc + BN, umma_desc(sa + BM * BKB + k4 * 32), umma_desc(sb + k4 * 32), idesc, (kb | k4) != 0);
@@ -195,7 +202,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
         const bool works = BN >= 32 || half == 0;
         uint32_t tl = 0;
         for (int t = blockIdx.x; t < ntiles; t += gridDim.x, tl++) {
-            const int m0 = (t / ntn) * MT * BM, n0 = (t % ntn) * BN;
+            const int tile = t / KS, ks = t - tile * KS;
+            const int m0 = (tile / ntn) * MT * BM, n0 = (tile % ntn) * BN;
             const uint32_t buf = tl % NBUF, use = tl / NBUF;
             // one lane waits, the warp follows its verdict (tcgen05.ld is warp-collective)
             int ok = lane == 0 ? (int)mbar_wait(&tmem_full_bar[buf], use & 1, abort_flag) : 1;
@@ -218,7 +226,16 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
                         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
                           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
                         : "r"(taddr));
-                    if (s0 + 16 <= a.S && !a.acc) {
+                    if (KS > 1) {
+                        // a split's partial sums, exact int32: [split][token][row]
+                        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                        if (row_ok) {
+                            int32_t *pp = a.part + ((size_t)ks * a.S + s0) * a.O + o;
+#pragma unroll
+                            for (int j = 0; j < 16; j++)
+                                if (s0 + j < a.S) pp[(size_t)j * a.O] = (int)r[j];
+                        }
+                    } else if (s0 + 16 <= a.S && !a.acc) {
                         // full chunk: the 16 token scales arrive while the accumulator is read; per token one
                         // conversion, two multiplies, one store of 32 consecutive rows
                         float sx[16];
@@ -266,6 +283,19 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
     if (threadIdx.x == 0 && abort_s) atomicExch(a.err, 1);
 }
 
+// y[s][o] = (scale[o] * sx[s]) * (float)(sum of the splits' int32 partials): the reference epilogue (nn/matmul.c:34)
+__global__ void __launch_bounds__(256) tc_splitk_finish_kernel(const int32_t *__restrict__ part, int KS, const float *__restrict__ scale,
+                                                               const float *__restrict__ sx, float *__restrict__ y,
+                                                               int32_t *__restrict__ acc, int S, int O) {
+    const size_t n = (size_t)S * O, i = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (i >= n) return;
+    int v = 0;
+    for (int k = 0; k < KS; k++) v += part[(size_t)k * n + i];
+    const int s = (int)(i / O), o = (int)(i - (size_t)s * O);
+    y[i] = __fmul_rn(__fmul_rn(scale[o], sx[s]), (float)v);
+    if (acc) acc[i] = v;
+}
+
 typedef CUresult (*EncodeFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                              const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -310,9 +340,31 @@ int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi,
     TcArgs a;
     a.scale = (const float *)w->scales; a.sx = sx; a.y = y; a.acc = acc; a.S = S; a.I = w->I; a.O = w->O; a.err = c->err_dev;
     int ntiles = ((w->O + MT * BM - 1) / (MT * BM)) * ((S + BN - 1) / BN);
-    int grid = ntiles < c->sms ? ntiles : c->sms;             // persistent: one CTA per SM
+    // few tiles and a long K: split K so that every SM streams a share of the weights
+    const int nkb = (w->I + BKB - 1) / BKB;
+    int ks = 1;
+    // (measured on 3840 x 15360: 30 tiles 60 -> 31 us at S = 32..64; 60 tiles at S = 512 lose to the extra pass)
+    if (ntiles * 4 <= c->sms && nkb >= 16) {
+        ks = c->sms / ntiles;
+        if (ks > 8) ks = 8;
+        if (ks > nkb / 8) ks = nkb / 8;                         // at least 8 K blocks per split
+        const int nks = (nkb + ks - 1) / ks;
+        ks = (nkb + nks - 1) / nks;                             // no empty split
+    }
+    a.ksplit = ks; a.part = nullptr;
+    if (ks > 1) {
+        CKR(moty_grow(c, &c->pair, (size_t)ks * S * w->O * 4));
+        a.part = (int32_t *)c->pair.p;
+    }
+    int work = ntiles * ks;
+    int grid = work < c->sms ? work : c->sms;                  // persistent: one CTA per SM
     k<<<grid, TC_THREADS, smem, st>>>(mapA, mapB, a);
     CK(cudaGetLastError());
+    if (ks > 1) {
+        const size_t n = (size_t)S * w->O;
+        tc_splitk_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.part, ks, a.scale, sx, y, acc, S, w->O);
+        CK(cudaGetLastError());
+    }
     return 0;
 }
 
