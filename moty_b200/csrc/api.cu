@@ -259,7 +259,10 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
-        if (vec && S > 8 && S <= Q8_MMA_MAX_S)                   // small batches: weights streamed once, mma.sync
+        // small batches: weights streamed once, mma.sync -- unless the matrix has so few 128-row tiles that the
+        // tensor-core kernel's split over K is what keeps all SMs streaming
+        const bool few_tiles = tc && ((O + 127) / 128) * 4 <= c->sms && I >= 2048;
+        if (vec && S > 8 && S <= Q8_MMA_MAX_S && !few_tiles)
             return launch_q8_mma((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
                                  (const float *)c->sx.p, y, acc, S, I, O, c->sms, st);
         if (tc) return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
