@@ -142,74 +142,6 @@ int launch_q8_small(const Q8Args &a, int sms, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------
-// S = 1 with the activation quantizer fused in: every CTA quantizes the row
-// itself (moty_hw_qrow_i8, hw/hw_quant.h:9-16) into shared memory, so a decode
-// GEMV is one launch.  CTA 0 also publishes nothing: the scale stays in a register.
-// ---------------------------------------------------------------------------
-template <int R>
-__global__ void __launch_bounds__(256) q8_gemv_fused_kernel(const float *__restrict__ x, const int8_t *__restrict__ W,
-                                                            const float *__restrict__ scale, float *__restrict__ y,
-                                                            int32_t *__restrict__ acc, int I, int O) {
-    extern __shared__ int4 xsm[];
-    __shared__ float red[8];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    float amax = 0.f;
-    for (int i = threadIdx.x; i < I / 4; i += 256) {
-        float4 v = x4[i];
-        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-    }
-    amax = warp_max_f32(amax);
-    if (lane == 0) red[warp] = amax;
-    __syncthreads();
-    amax = red[0];
-#pragma unroll
-    for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
-    const float sx = quant_scale(amax, 1e-12f);
-    const float inv = __fdiv_rn(1.f, sx);
-    int *xq = reinterpret_cast<int *>(xsm);
-    for (int i = threadIdx.x; i < I / 4; i += 256) {
-        float4 v = x4[i];
-        int a = quant_code(v.x, inv) & 255, b = quant_code(v.y, inv) & 255;
-        int c = quant_code(v.z, inv) & 255, d = quant_code(v.w, inv) & 255;
-        xq[i] = a | (b << 8) | (c << 16) | (d << 24);
-    }
-    __syncthreads();
-    const int I16 = I / 16;
-    constexpr int SH = 5 - Log2<R>::v;
-    for (int rg = blockIdx.x * 8 + warp; rg * R < O; rg += gridDim.x * 8) {
-        int flat[R];
-        q8_rows<1, R>(W, xsm, I16, O, rg * R, lane, flat);
-        if ((lane & ((1 << SH) - 1)) == 0) {
-            int o = rg * R + (lane >> SH);
-            if (o < O) {
-                y[o] = __fmul_rn(__fmul_rn(scale[o], sx), (float)flat[0]);
-                if (acc) acc[o] = flat[0];
-            }
-        }
-    }
-}
-
-template <int R>
-static int launch_fused_t(const float *x, const int8_t *w, const float *scale, float *y, int32_t *acc,
-                          int I, int O, cudaStream_t st) {
-    int nrg = (O + R - 1) / R;
-    q8_gemv_fused_kernel<R><<<(nrg + 7) / 8, 256, (size_t)I, st>>>(x, w, scale, y, acc, I, O);
-    CK(cudaGetLastError());
-    return 0;
-}
-
-int launch_q8_gemv_fused(const float *x, const int8_t *w, const float *scale, float *y, int32_t *acc,
-                         int I, int O, int sms, cudaStream_t st) {
-    if (I % 16 != 0 || I > MOTY_QROW_MAX || (reinterpret_cast<uintptr_t>(x) & 15))
-        return moty_set_error(MOTY_CUDA_EARG, "q8_gemv_fused: I=%d or unaligned x", I);
-    if (O <= 0) return 0;
-    if ((long long)(O + 3) / 4 >= (long long)sms * 16) return launch_fused_t<4>(x, w, scale, y, acc, I, O, st);
-    if ((long long)(O + 1) / 2 >= (long long)sms * 8) return launch_fused_t<2>(x, w, scale, y, acc, I, O, st);
-    return launch_fused_t<1>(x, w, scale, y, acc, I, O, st);
-}
-
-// ---------------------------------------------------------------------------
 // Any-length dots (test entries and widths that are not a multiple of 16):
 // one warp per weight row, word loads where both pointers allow, bytes otherwise.
 // moty_hw_dot_i8i8 (hw/hw_scalar.h:8-12), moty_hw_dot_i4i8 (:14-22).

@@ -31,9 +31,6 @@ struct Q8Args {
     int S, I, O;
 };
 int launch_q8_small(const Q8Args &a, int sms, cudaStream_t st);
-// S = 1 with the activation quantizer fused in (x is f32; xi/sx unused)
-int launch_q8_gemv_fused(const float *x, const int8_t *w, const float *scale, float *y, int32_t *acc,
-                         int I, int O, int sms, cudaStream_t st);
 int launch_dot_i8i8_rows(const int8_t *w, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
 int launch_dot_i4i8_rows(const uint8_t *w4, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
 // per-row int4 weights (WF_I4) against int8 rows, same epilogue as Q8_0
