@@ -289,6 +289,15 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (w->fmt == MOTY_WF_Q4R4) {
         int nb = I / 32;
         if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q4R4 needs I %% 32 == 0");
+        if (S == 1 && q4r4_gemv_bulk_supported(I, O, c->sms)) {      // decode, few long rows: quantize once, then stream
+            CKR(moty_grow(c, &c->xi, (size_t)I + 16));
+            CKR(moty_grow(c, &c->xs, (size_t)nb * 4));
+            CKR(moty_grow(c, &c->xsum, (size_t)nb * 4));
+            CKR(launch_quant_g32(x, 1, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
+            return launch_q4r4_gemv_bulk((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
+                                         (const float *)c->xs.p, (const int32_t *)c->xsum.p, y, I, O, c->err_dev + 2,
+                                         c->sms, st);
+        }
         if (S == 1 && (reinterpret_cast<uintptr_t>(x) & 15) == 0)   // decode: one launch, the row is group-quantized in the kernel
             return launch_q4r4_stream((const uint8_t *)w->codes, (const uint16_t *)w->scales, x, nullptr, nullptr, nullptr,
                                       nullptr, y, 1, I, O, c->sms, st);

@@ -75,6 +75,11 @@ int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 bool q4r4_gemv1_supported(int I, int O, int sms);
 int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float *y, int I, int O, int sms, cudaStream_t st);
 
+// ---- q4r4_gemv_bulk.cu: Q4R4 decode GEMV for few long rows (lane = row, fed by bulk async copies) ----
+bool q4r4_gemv_bulk_supported(int I, int O, int sms);
+int launch_q4r4_gemv_bulk(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
+                          float *y, int I, int O, int *err, int sms, cudaStream_t st);
+
 // ---- q8_mma.cu: Q8_0 x a small batch (mma.sync, weights streamed once), dense and grouped ----
 bool q8_mma_supported(int S, int I, int O);
 int launch_q8_mma(const int8_t *w, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,

@@ -85,6 +85,20 @@ def test_q4r4_decode_many_rows_vs_oracle(gpu, oracle, O, I):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I", [(15360, 3840), (3838, 15360), (4001, 12800), (6002, 2176)])
+def test_q4r4_decode_few_long_rows_vs_oracle(gpu, oracle, O, I):
+    """Matrices the bulk-copy-fed decode kernel takes (one lane per row, shared-memory ring): the FFN
+    shapes of the benchmark, row counts that are not multiples of 4 or 32, a group count that is not a
+    multiple of the 16-group stage."""
+    rng = np.random.default_rng(O + I)
+    q4 = rng.integers(0, 256, (O + 3) // 4 * (I // 32) * 64, dtype=np.uint8)
+    s16 = rng.uniform(0.001, 0.01, (O + 3) // 4 * (I // 32) * 4).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal((1, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.q4r4(q4, s16, O, I), x)
+    yo = oracle.matmul_q4r4_s(x, q4, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
 def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
     """tests/q4r4_tests.c:88-172: extreme codes and activations, long rows."""
     O, I = 8, 16384
