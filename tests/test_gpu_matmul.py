@@ -85,11 +85,11 @@ def test_q4r4_decode_many_rows_vs_oracle(gpu, oracle, O, I):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
-@pytest.mark.parametrize("O,I", [(15360, 3840), (3838, 15360), (4001, 12800), (6002, 2176)])
+@pytest.mark.parametrize("O,I", [(15360, 3840), (9601, 5504), (3838, 15360), (4001, 12800)])
 def test_q4r4_decode_few_long_rows_vs_oracle(gpu, oracle, O, I):
     """Matrices the bulk-copy-fed decode kernel takes (one lane per row, shared-memory ring): the FFN
     shapes of the benchmark, row counts that are not multiples of 4 or 32, a group count that is not a
-    multiple of the 16-group stage."""
+    multiple of the 16-group stage; the last two have too few rows for it and take the general kernel."""
     rng = np.random.default_rng(O + I)
     q4 = rng.integers(0, 256, (O + 3) // 4 * (I // 32) * 64, dtype=np.uint8)
     s16 = rng.uniform(0.001, 0.01, (O + 3) // 4 * (I // 32) * 4).astype(np.float16).view(np.uint16)
