@@ -27,7 +27,7 @@ extern "C" {
 #endif
 
 /* weight formats: the values of the WF_* enum in hw/hw.h:53 */
-enum { MOTY_WF_F32 = 0, MOTY_WF_I8 = 1, MOTY_WF_I4 = 2, MOTY_WF_Q4R4 = 7 };
+enum { MOTY_WF_F32 = 0, MOTY_WF_I8 = 1, MOTY_WF_I4 = 2, MOTY_WF_Q4R4 = 7, MOTY_WF_Q8R4 = 8 };
 /* activations between the two halves of an FFN (hw/hw_ops.h:19-21, engines/gemma.c:389-391) */
 enum { MOTY_ACT_SILU = 0, MOTY_ACT_GELU_TANH = 1 };
 
@@ -68,6 +68,8 @@ int moty_cuda_host_free(void *p);
  *   MOTY_WF_I8   codes int8 [O][I] row-major, scales f32 [O]            (nn/quant.c:12-33)
  *   MOTY_WF_Q4R4 codes uint8 [ceil(O/4)][I/32][64], scales f16 [ceil(O/4)][I/32][4]
  *                                                                         (hw/hw_q4r4.h:3-11)
+ *   MOTY_WF_Q8R4 codes int8 [ceil(O/4)][I/32][128] (4 rows x 32 codes), scales as Q4R4
+ *                                                                         (hw/hw_q4r4.h:92-99)
  *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55)
  *   MOTY_WF_F32  codes float [O][I], scales NULL (router matrices only)
  * The hook point in the loader is right after load_mat_bits / load_mat_r4 /
@@ -75,7 +77,7 @@ int moty_cuda_host_free(void *p);
 int moty_cuda_upload_mat(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
                          int O, int I, int device);
 /* rows [o0, o1) of the same host matrix: the row shard of one GPU.  For
- * MOTY_WF_Q4R4 o0 must be a multiple of 4. */
+ * MOTY_WF_Q4R4 and MOTY_WF_Q8R4 o0 must be a multiple of 4. */
 int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void *codes, const void *scales,
                               int O, int I, int o0, int o1, int device);
 int moty_cuda_free_mat(MotyCudaMat *m);
@@ -118,6 +120,9 @@ int moty_cuda_q8_apply_noalloc(float *y_dev, const float *x_dev, const int8_t *q
 int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale, int S, int I, int O);
 /* moty_matmul_q4r4_s (nn/matmul.c:405) with host weights */
 int moty_cuda_matmul_q4r4_s(float *y, const float *x, const uint8_t *q4, const uint16_t *s16, int S, int I, int O);
+/* moty_matmul_q8r4_s (nn/matmul.c:435-461): the int8 sibling of Q4R4 used for mixed precision
+ * (tensors matched by Q8_TENSORS, runtime/rt_model_load.h:38-61); uploads per call like the two above */
+int moty_cuda_matmul_q8r4_s(float *y, const float *x, const int8_t *q8, const uint16_t *s16, int S, int I, int O);
 
 /* ---- kernels of the hw.h contract, host-callable ----------------------- */
 

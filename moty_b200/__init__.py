@@ -19,7 +19,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmoty_cuda.so")
 
-WF_F32, WF_I8, WF_I4, WF_Q4R4 = 0, 1, 2, 7
+WF_F32, WF_I8, WF_I4, WF_Q4R4, WF_Q8R4 = 0, 1, 2, 7, 8
 ACT_SILU, ACT_GELU_TANH = 0, 1
 QROW_MAX = 16384
 
@@ -133,6 +133,10 @@ class Mat:
         return cls(WF_Q4R4, np.ascontiguousarray(q4, np.uint8), np.ascontiguousarray(s16, np.uint16), O, I, device, rows)
 
     @classmethod
+    def q8r4(cls, q8, s16, O, I, device=0, rows=None):
+        return cls(WF_Q8R4, np.ascontiguousarray(q8, np.int8), np.ascontiguousarray(s16, np.uint16), O, I, device, rows)
+
+    @classmethod
     def i4(cls, q4, scale, O, I, device=0):
         return cls(WF_I4, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device)
 
@@ -194,6 +198,15 @@ def matmul_q4r4_s(x, q4, s16, O):
     x = _f32(x); S, I = x.shape
     y = np.empty((S, O), np.float32)
     _ck(lib().moty_cuda_matmul_q4r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q4, np.uint8)),
+                                      _p(np.ascontiguousarray(s16, np.uint16)), S, I, O))
+    return y
+
+
+def matmul_q8r4_s(x, q8, s16, O):
+    """moty_matmul_q8r4_s (nn/matmul.c:435-461) with host weights."""
+    x = _f32(x); S, I = x.shape
+    y = np.empty((S, O), np.float32)
+    _ck(lib().moty_cuda_matmul_q8r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q8, np.int8)),
                                       _p(np.ascontiguousarray(s16, np.uint16)), S, I, O))
     return y
 

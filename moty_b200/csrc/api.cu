@@ -163,6 +163,9 @@ static int mat_sizes(int fmt, int O, int I, size_t *cb, size_t *sb) {
         case MOTY_WF_Q4R4:
             if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "Q4R4 needs I %% 32 == 0 (I=%d)", I);
             *cb = (size_t)((O + 3) / 4) * (I / 32) * 64; *sb = (size_t)((O + 3) / 4) * (I / 32) * 8; return 0;
+        case MOTY_WF_Q8R4:
+            if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "Q8R4 needs I %% 32 == 0 (I=%d)", I);
+            *cb = (size_t)((O + 3) / 4) * (I / 32) * 128; *sb = (size_t)((O + 3) / 4) * (I / 32) * 8; return 0;
         default: return moty_set_error(MOTY_CUDA_EARG, "unsupported weight format %d", fmt);
     }
 }
@@ -174,7 +177,8 @@ extern "C" int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void 
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
     if (o0 < 0 || o1 > O || o0 >= o1) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: rows [%d,%d) of %d", o0, o1, O);
     if (fmt != MOTY_WF_F32 && !scales) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: scales missing");
-    if (fmt == MOTY_WF_Q4R4 && (o0 % 4)) return moty_set_error(MOTY_CUDA_EARG, "upload_mat: Q4R4 shard must start on a block (o0=%d)", o0);
+    if ((fmt == MOTY_WF_Q4R4 || fmt == MOTY_WF_Q8R4) && (o0 % 4))
+        return moty_set_error(MOTY_CUDA_EARG, "upload_mat: a Q4R4/Q8R4 shard must start on a block (o0=%d)", o0);
     size_t cb, sb, cb0, sb0;
     int rows = o1 - o0;
     CKR(mat_sizes(fmt, rows, I, &cb, &sb));
@@ -317,8 +321,22 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->misc, (size_t)S + 16));
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
                                (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
-                               (uint8_t *)c->misc.p, y, O, S, I, O,
+                               (uint8_t *)c->misc.p, y, O, S, I, O, 0,
                                c->sms, st);
+    }
+    if (w->fmt == MOTY_WF_Q8R4) {
+        // the int8 sibling of Q4R4: same group quantizer, same chain, no offset term; one kernel for every S
+        const int nb = I / 32;
+        if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q8R4 needs I %% 32 == 0");
+        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
+        CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
+        CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
+        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 8));
+        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+        CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
+        return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
+                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
+                               (uint8_t *)c->misc.p, y, O, S, I, O, 1, c->sms, st);
     }
     if (w->fmt == MOTY_WF_I4) {
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
@@ -382,6 +400,16 @@ extern "C" int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, c
     if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
     MotyCudaMat *m = nullptr;
     CKR(moty_cuda_upload_mat(&m, MOTY_WF_I8, q, scale, O, I, dev));
+    int r = moty_cuda_mat_apply(m, y, x, S);
+    moty_cuda_free_mat(m);
+    return r;
+}
+
+extern "C" int moty_cuda_matmul_q8r4_s(float *y, const float *x, const int8_t *q8, const uint16_t *s16, int S, int I, int O) {
+    int dev = first_device();
+    if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
+    MotyCudaMat *m = nullptr;
+    CKR(moty_cuda_upload_mat(&m, MOTY_WF_Q8R4, q8, s16, O, I, dev));
     int r = moty_cuda_mat_apply(m, y, x, S);
     moty_cuda_free_mat(m);
     return r;

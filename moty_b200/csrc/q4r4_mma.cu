@@ -48,6 +48,13 @@ __device__ __forceinline__ void mma_u8s8_16832(int (&c)[4], unsigned a0, unsigne
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+__device__ __forceinline__ void mma_s8s8_16832_z(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                                 unsigned b0, unsigned b1) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
 // int -> float for |i| < 2^22 without the conversion unit (a quarter-rate pipe that the chain would
 // saturate): 0x4B400000 is 1.5 * 2^23 as a float; adding i to its bit pattern gives the float
 // 1.5 * 2^23 + i exactly, and the subtraction is exact.  Group sums are below 2^17 in magnitude.
@@ -71,14 +78,20 @@ __device__ __forceinline__ float q4_chain_step(float acc, int sum, float d, int 
 //   B  the tokens' codes, 256 bytes per token, token stride 272 bytes (eight tokens -> eight bank groups)
 //   R  the records, [group][token pair] 16 bytes
 constexpr int GCH = 8, NSTG = 3;
-constexpr int WBLK = 512 + 64, STG_W1 = 4 * WBLK, STG_D1 = 4 * 64, BTOK = 272;
-template <int NT> struct Q4Stage {
+constexpr int STG_D1 = 4 * 64, BTOK = 272;
+// Q8 = the int8 sibling Q8R4 (hw/hw_q4r4.h:92-130): 128 bytes per (block, group) = 4 rows x 32 signed codes, no
+// offset term, the same chain.  Its blocks are padded by 16 bytes: a row's fragment words sit 32 bytes apart,
+// so the second block of a fragment load has to land 16 bytes off to miss the banks of the first.
+template <int NT, bool Q8> struct Q4Stage {
+    static constexpr int GB = Q8 ? 128 : 64;                   // bytes per (block, group)
+    static constexpr int WBLK = Q8 ? GCH * 128 + 16 : GCH * 64 + 64, STG_W1 = 4 * WBLK;
     static constexpr int W = 0, D = 8 * STG_W1, B = D + 8 * STG_D1, R = B + NT * 8 * BTOK, BYTES = R + NT * GCH * 64;
 };
 
-template <int NT>
+template <int NT, bool Q8>
 __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
-    using L = Q4Stage<NT>;
+    using L = Q4Stage<NT, Q8>;
+    constexpr int GB = L::GB, WBLK = L::WBLK, STG_W1 = L::STG_W1;
     extern __shared__ int4 smem_q4mma[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(smem_q4mma);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, gid = lane >> 2, tid = lane & 3;
@@ -97,7 +110,7 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
     const int row_a = mt * 16 + gid, row_b = row_a + 8;
     // where this thread's fragment words and scales sit inside a stage
     const int ba_l = gid >> 2, bb_l = ba_l + 2, rr = gid & 3;
-    const int offA = L::W + warp * STG_W1 + ba_l * WBLK + rr * 16 + tid * 4, offB = L::W + warp * STG_W1 + bb_l * WBLK + rr * 16 + tid * 4;
+    const int offA = L::W + warp * STG_W1 + ba_l * WBLK + rr * (GB / 4) + tid * 4, offB = L::W + warp * STG_W1 + bb_l * WBLK + rr * (GB / 4) + tid * 4;
     const int offdA = L::D + warp * STG_D1 + ba_l * 64 + rr * 2, offdB = L::D + warp * STG_D1 + bb_l * 64 + rr * 2;
     // first group held by stage s: a partial last stage is shifted back so that it never runs past the row
     auto stage_g0 = [&](int s) { const int g0 = s * GCH; return g0 + GCH <= nb ? g0 : (nb >= GCH ? nb - GCH : 0); };
@@ -108,8 +121,12 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
-            if (nb >= GCH || lane * 16 < nb * 64)
-                cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + lane * 16, Wp + ((size_t)blk * nb + gs) * 64 + lane * 16);
+#pragma unroll
+            for (int h = 0; h < GB / 64; h++) {                // 512 bytes per round of the warp
+                const int off = h * 512 + lane * 16;
+                if (nb >= GCH || off < nb * GB)
+                    cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + off, Wp + ((size_t)blk * nb + gs) * GB + off);
+            }
         }
         const int q = lane >> 3, part = lane & 7;
         int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
@@ -161,18 +178,25 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
         const unsigned char *st = smem + (size_t)(s % NSTG) * L::BYTES;
         const int g0 = s * GCH, gs = stage_g0(s);
         auto group_step = [&](int ul) {                        // ul: position of the group inside the stage
-            const unsigned wA = *reinterpret_cast<const unsigned *>(st + offA + ul * 64);
-            const unsigned wB = *reinterpret_cast<const unsigned *>(st + offB + ul * 64);
             const float dA = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdA + ul * 8));
             const float dB = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdB + ul * 8));
-            const unsigned a0 = wA & 0x0f0f0f0fu, a2 = (wA >> 4) & 0x0f0f0f0fu;
-            const unsigned a1 = wB & 0x0f0f0f0fu, a3 = (wB >> 4) & 0x0f0f0f0fu;
+            unsigned a0, a1, a2, a3;
+            if (Q8) {                                          // a row's codes k = 4 tid .. and k = 16 + 4 tid ..: two words
+                a0 = *reinterpret_cast<const unsigned *>(st + offA + ul * GB); a2 = *reinterpret_cast<const unsigned *>(st + offA + ul * GB + 16);
+                a1 = *reinterpret_cast<const unsigned *>(st + offB + ul * GB); a3 = *reinterpret_cast<const unsigned *>(st + offB + ul * GB + 16);
+            } else {                                           // one word: low nibbles -> a0/a1, high nibbles -> a2/a3
+                const unsigned wA = *reinterpret_cast<const unsigned *>(st + offA + ul * GB);
+                const unsigned wB = *reinterpret_cast<const unsigned *>(st + offB + ul * GB);
+                a0 = wA & 0x0f0f0f0fu; a2 = (wA >> 4) & 0x0f0f0f0fu;
+                a1 = wB & 0x0f0f0f0fu; a3 = (wB >> 4) & 0x0f0f0f0fu;
+            }
 #pragma unroll
             for (int j = 0; j < NT; j++) {
                 const unsigned char *bp = st + L::B + (j * 8 + gid) * BTOK + ul * 32 + tid * 4;
                 const unsigned b0 = *reinterpret_cast<const unsigned *>(bp), b1 = *reinterpret_cast<const unsigned *>(bp + 16);
                 int c[4];
-                mma_u8s8_16832(c, a0, a1, a2, a3, b0, b1);
+                if (Q8) mma_s8s8_16832_z(c, a0, a1, a2, a3, b0, b1);
+                else mma_u8s8_16832(c, a0, a1, a2, a3, b0, b1);
                 const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1
                 const int v0 = f0[j] ? 0 : q.y, v1 = f1[j] ? 0 : q.w;
                 acc[j][0] = q4_chain_step(acc[j][0], c[0], dA, q.x, v0, q.y, f0[j]);   // (row_a, t0)
@@ -208,7 +232,8 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
 // first (size / 4 * 4) tokens of a tile through the 4-token kernel, the rest through the
 // token-by-token kernel (nn/matmul.c:424-432)
 __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
-                                                       int2 *__restrict__ rec, uint8_t *__restrict__ form, int S, int S8, int nb) {
+                                                       int2 *__restrict__ rec, uint8_t *__restrict__ form, int S, int S8, int nb,
+                                                       int q8) {
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= (long long)S8 * nb) return;
     const int g = (int)(i / S8), t = (int)(i - (long long)g * S8);
@@ -216,8 +241,8 @@ __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__
     if (t < S) {
         const int t0 = t / 32 * 32;
         const int ns = S - t0 < 32 ? S - t0 : 32;
-        const int f = (t - t0) < ns / 4 * 4 ? 1 : 0;
-        const float sc = xs[(size_t)t * nb + g]; const int sm = xsum[(size_t)t * nb + g];
+        const int f = (!q8 && (t - t0) < ns / 4 * 4) ? 1 : 0;            // Q8R4 has one formula and no offset term
+        const float sc = xs[(size_t)t * nb + g]; const int sm = q8 ? 0 : xsum[(size_t)t * nb + g];
         r.x = __float_as_int(sc);
         r.y = f ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm;
         if (g == 0) form[t] = (uint8_t)f;
@@ -225,38 +250,44 @@ __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__
     rec[i] = r;
 }
 
-template <int NT>
+template <int NT, bool Q8 = false>
 static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st, int ntiles_max = 0) {
-    constexpr int SMEM = NSTG * Q4Stage<NT>::BYTES;
+    constexpr int SMEM = NSTG * Q4Stage<NT, Q8>::BYTES;
     static bool attr_done[MOTY_MAX_DEV];
     int dev = 0;
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: device %d", dev);
     if (!attr_done[dev]) {
-        CK(cudaFuncSetAttribute(q4r4_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        CK(cudaFuncSetAttribute(q4r4_mma_kernel<NT, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         attr_done[dev] = true;
     }
     const int nmt = (a.O + 15) / 16;
     dim3 grid((nmt + 7) / 8, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT));
     if (grid.y > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q4r4_mma: S=%d in one call", a.S);
-    CK(moty_launch_pdl(q4r4_mma_kernel<NT>, grid, dim3(256), (size_t)SMEM, st, a));
+    CK(moty_launch_pdl(q4r4_mma_kernel<NT, Q8>, grid, dim3(256), (size_t)SMEM, st, a));
     return 0;
 }
 
 // xq/xs/xsum: the group-quantized batch; rec: scratch for (I/32) * ceil8(S) records of 8 bytes;
 // form: scratch for S bytes
+// q8 != 0: w holds Q8R4 codes (128 bytes per block and group)
 int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
-                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int sms, cudaStream_t st) {
+                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int q8, int sms, cudaStream_t st) {
     if (I % 32 != 0 || I <= 0 || S <= 0) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: S=%d I=%d", S, I);
     if (O <= 0) return 0;
     const int nb = I / 32, S8 = (S + 7) / 8 * 8;
     const long long nrec = (long long)S8 * nb;
-    q4r4_rec_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, rec, form, S, S8, nb);
+    q4r4_rec_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, rec, form, S, S8, nb, q8);
     CK(cudaGetLastError());
     Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
     // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
     const long long mct = ((O + 15) / 16 + 7) / 8, want = (long long)sms * 2;
+    if (q8) {
+        if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4, true>(a, st);
+        if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2, true>(a, st);
+        return launch_mma_t<1, true>(a, st);
+    }
     if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4>(a, st);
     if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2>(a, st);
     return launch_mma_t<1>(a, st);

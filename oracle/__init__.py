@@ -177,6 +177,20 @@ class Oracle:
         self.lib.oracle_pack_q4r4(_p(w), C.c_int(O), C.c_int(I), _p(q4), _p(s16))
         return q4, s16
 
+    def pack_q8r4(self, w):
+        w = _f32(w); O, I = w.shape
+        nblk, nb = (O + 3) // 4, I // 32
+        q8 = np.empty(nblk * nb * 128, np.int8); s16 = np.empty(nblk * nb * 4, np.uint16)
+        self.lib.oracle_pack_q8r4(_p(w), C.c_int(O), C.c_int(I), _p(q8), _p(s16))
+        return q8, s16
+
+    def matmul_q8r4_s(self, x, q8, s16, O):
+        x = _f32(x); q8 = np.ascontiguousarray(q8, np.int8); s16 = np.ascontiguousarray(s16, np.uint16)
+        S, I = x.shape
+        y = np.empty((S, O), np.float32)
+        self.lib.oracle_matmul_q8r4_s(_p(y), _p(x), _p(q8), _p(s16), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
     # -- router ---------------------------------------------------------
     def softmax(self, x):
         x = _f32(x).copy()
@@ -374,6 +388,20 @@ class Ref:
         q4 = np.empty(nblk * nb * 64, np.uint8); s16 = np.empty(nblk * nb * 4, np.uint16)
         self.lib.refshim_pack_q4r4(_p(w), C.c_int(O), C.c_int(I), _p(q4), _p(s16))
         return q4, s16
+
+    def pack_q8r4(self, w):
+        w = _f32(w); O, I = w.shape
+        nblk, nb = (O + 3) // 4, I // 32
+        q8 = np.empty(nblk * nb * 128, np.int8); s16 = np.empty(nblk * nb * 4, np.uint16)
+        self.lib.refshim_pack_q8r4(_p(w), C.c_int(O), C.c_int(I), _p(q8), _p(s16))
+        return q8, s16
+
+    def matmul_q8r4_s(self, x, q8, s16, O):
+        x = _f32(x); S, I = x.shape
+        y = np.empty((S, O), np.float32)
+        self.lib.moty_matmul_q8r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q8, np.int8)),
+                                    _p(np.ascontiguousarray(s16, np.uint16)), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
 
     def softmax(self, x):
         x = _f32(x).copy(); rows = x.reshape(-1, x.shape[-1])

@@ -355,6 +355,77 @@ ORACLE_API void oracle_pack_q4r4_block(const float *w, int nr, int I, uint8_t *b
 
 /* runtime/rt_model_load.h:85-121 (r4_pack_part) -- a whole [O][I] matrix in
  * blocks of 4 rows; the last block may hold fewer than 4 rows. */
+/* ---------------------------------------------------------------------------
+ * Q8R4, the int8 sibling of Q4R4 (hw/hw_q4r4.h:92-130, nn/matmul.c:435-461,
+ * nn/quant.c:135-155): the same 4-row blocks, groups of 32 and f16 scale stream, 128 bytes
+ * per (block, group) = 4 rows x 32 signed codes, no offset term.  The single-token and the
+ * 4-token kernels of the reference compute the same thing per (row, token):
+ *   acc = fma((float)sum_g, f16(d[g][r]) * xs[t][g], acc), groups ascending
+ * (the compiler contracts the reference's acc += a * b; spelled out here).
+ * ------------------------------------------------------------------------- */
+ORACLE_API void oracle_matmul_q8r4_s(float *y, const float *x, const int8_t *q8, const uint16_t *s16,
+                                     int S, int I, int O) {
+    int nb = I / 32, nblk = (O + 3) / 4;
+    int8_t *xq = (int8_t *)malloc((size_t)S * I + 1);
+    float *xs = (float *)malloc(((size_t)S * nb + 1) * 4);
+    int32_t *xsum = (int32_t *)malloc(((size_t)S * nb + 1) * 4);
+    for (int s = 0; s < S; s++)
+        oracle_quant_g32(x + (size_t)s * I, I, xq + (size_t)s * I, xs + (size_t)s * nb, xsum + (size_t)s * nb);
+    #pragma omp parallel for schedule(dynamic, 8)
+    for (int ob = 0; ob < nblk; ob++) {
+        const int8_t *wb = q8 + (size_t)ob * nb * 128;
+        const uint16_t *db = s16 + (size_t)ob * nb * 4;
+        for (int t = 0; t < S; t++)
+            for (int r = 0; r < 4; r++) {
+                if (ob * 4 + r >= O) continue;
+                float acc = 0.f;
+                for (int g = 0; g < nb; g++) {
+                    const int8_t *wr = wb + (size_t)g * 128 + r * 32, *xg = xq + (size_t)t * I + g * 32;
+                    int32_t sum = 0;
+                    for (int j = 0; j < 32; j++) sum += (int32_t)wr[j] * xg[j];
+                    acc = fmaf((float)sum, oracle_f16_to_f32(db[(size_t)g * 4 + r]) * xs[(size_t)t * nb + g], acc);
+                }
+                y[(size_t)t * O + ob * 4 + r] = acc;
+            }
+    }
+    free(xq); free(xs); free(xsum);
+}
+
+ORACLE_API void oracle_pack_q8r4_block(const float *w, int nr, int I, int8_t *blk, uint16_t *d) {
+    int nb = I / 32;
+    for (int g = 0; g < nb; g++)
+        for (int r = 0; r < 4; r++) {
+            int8_t *out = blk + (size_t)g * 128 + r * 32;
+            if (r >= nr) { memset(out, 0, 32); d[(size_t)g * 4 + r] = 0; continue; }
+            const float *p = w + (size_t)r * I + g * 32;
+            float big = 0.f;
+            for (int j = 0; j < 32; j++) if (fabsf(p[j]) > fabsf(big)) big = p[j];
+            float other = 0.f;
+            for (int j = 0; j < 32; j++)
+                if ((p[j] > 0) != (big > 0) && fabsf(p[j]) > other) other = fabsf(p[j]);
+            float step = fmaxf(fabsf(big) / 128.f, other / 127.f);
+            uint16_t h = oracle_f32_to_f16(big > 0 ? -step : step);
+            float dd = oracle_f16_to_f32(h);
+            float inv = dd != 0.f ? 1.f / dd : 0.f;
+            for (int j = 0; j < 32; j++) {
+                int v = (int)lrintf(p[j] * inv);
+                if (v < -128) v = -128;
+                if (v > 127) v = 127;
+                out[j] = (int8_t)v;
+            }
+            d[(size_t)g * 4 + r] = h;
+        }
+}
+
+ORACLE_API void oracle_pack_q8r4(const float *w, int O, int I, int8_t *q8, uint16_t *s16) {
+    int nb = I / 32, nblk = (O + 3) / 4;
+    #pragma omp parallel for schedule(static)
+    for (int b = 0; b < nblk; b++) {
+        int nr = O - 4 * b < 4 ? O - 4 * b : 4;
+        oracle_pack_q8r4_block(w + (size_t)b * 4 * I, nr, I, q8 + (size_t)b * nb * 128, s16 + (size_t)b * nb * 4);
+    }
+}
+
 ORACLE_API void oracle_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16) {
     int nb = I / 32, nblk = (O + 3) / 4;
     #pragma omp parallel for schedule(static)

@@ -105,6 +105,15 @@ void refshim_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16)
     }
 }
 
+/* the same for Q8R4 (moty_pack_q8r4_block, nn/quant.c:135-155) */
+void refshim_pack_q8r4(const float *w, int O, int I, int8_t *q8, uint16_t *s16) {
+    int nb = I / 32;
+    for (int b = 0; b < (O + 3) / 4; b++) {
+        int nr = O - 4 * b < 4 ? O - 4 * b : 4;
+        moty_pack_q8r4_block(w + (size_t)b * 4 * I, nr, I, q8 + (size_t)b * nb * 128, s16 + (size_t)b * nb * 4);
+    }
+}
+
 /* moty_nn_dense_ffn (nn/ffn.c:26-55) over three WF_I8 or three WF_Q4R4 matrices */
 void refshim_dense_ffn(int fmt, const void *gq, const void *gs, const void *uq, const void *us,
                        const void *dq, const void *ds, int D, int I, const float *x, int S, float *out) {

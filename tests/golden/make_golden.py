@@ -130,6 +130,20 @@ def main():
         o, idx, w = r.olmoe_moe(ex, x, logits, 0)
         blk[f"olmoe_out{S}"] = o; blk[f"olmoe_idx{S}"] = idx; blk[f"olmoe_w{S}"] = w
     save("blocks", **blk)
+
+    # ---- Q8R4, the int8 sibling of Q4R4 (its own random stream: added after the files above were fixed)
+    rq8 = np.random.default_rng(20260811)
+    d = {}
+    for tag, (O, I) in {"a": (37, 96), "b": (66, 512)}.items():
+        Wf = (rq8.standard_normal((O, I)) * 0.02).astype(np.float32)
+        Wf[0, :32] = 0                                    # an all-zero group: scale 0, codes 0
+        q8, s16 = r.pack_q8r4(Wf)
+        d.update({f"Wf_{tag}": Wf, f"q8_{tag}": q8, f"s16_{tag}": s16, f"O_{tag}": np.int32(O)})
+        for S in (1, 3, 4, 5, 16, 37):
+            x = rq8.standard_normal((S, I)).astype(np.float32)
+            d[f"x_{tag}_{S}"] = x
+            d[f"y_{tag}_{S}"] = r.matmul_q8r4_s(x, q8, s16, O)
+    save("matmul_q8r4", **d)
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 

@@ -99,6 +99,32 @@ def test_q4r4_decode_few_long_rows_vs_oracle(gpu, oracle, O, I):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I", [(1024, 1024), (1022, 3072), (515, 3840), (258, 15360), (4, 32), (7, 96), (4100, 352)])
+@pytest.mark.parametrize("S", [1, 2, 4, 7, 12, 37, 163])
+def test_q8r4_vs_oracle(gpu, oracle, O, I, S):
+    """Q8R4 (the int8 sibling of Q4R4): every batch size through the MMA kernel, ragged rows, tokens and groups."""
+    rng = np.random.default_rng(O * 5 + I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q8, s16 = oracle.pack_q8r4(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.q8r4(q8, s16, O, I), x)
+    yo = oracle.matmul_q8r4_s(x, q8, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
+def test_q8r4_golden_and_extremes(gpu, oracle):
+    g = golden("matmul_q8r4")
+    for tag in ("a", "b"):
+        O = int(g[f"O_{tag}"])
+        for S in (1, 5, 37):
+            assert same_bits(gpu.matmul_q8r4_s(g[f"x_{tag}_{S}"], g[f"q8_{tag}"], g[f"s16_{tag}"], O), g[f"y_{tag}_{S}"])
+    O, I = 8, 16384                                           # extreme codes and activations, the longest row
+    q8 = np.full(2 * (I // 32) * 128, -128, np.int8)
+    s16 = np.full(2 * (I // 32) * 4, 0x3C00, np.uint16)      # scale 1.0
+    x = np.full((2, I), 127.0, np.float32); x[1] = -127.0
+    assert same_bits(gpu.mat_apply(gpu.Mat.q8r4(q8, s16, O, I), x), oracle.matmul_q8r4_s(x, q8, s16, O))
+
+
 def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
     """tests/q4r4_tests.c:88-172: extreme codes and activations, long rows."""
     O, I = 8, 16384

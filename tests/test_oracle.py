@@ -53,6 +53,18 @@ def test_drivers(oracle, tag):
         assert same_bits(oracle.matmul_q4r4_s(x, g["q4"], g["s16"], O), g[f"y4_{S}"])
 
 
+def test_q8r4_drivers(oracle):
+    """Q8R4 packer and product against vectors from the reference build (nn/quant.c:135-155,
+    nn/matmul.c:435-461)."""
+    g = golden("matmul_q8r4")
+    for tag in ("a", "b"):
+        O = int(g[f"O_{tag}"])
+        q8, s16 = oracle.pack_q8r4(g[f"Wf_{tag}"])
+        assert same_bits(q8, g[f"q8_{tag}"]) and same_bits(s16, g[f"s16_{tag}"])
+        for S in (1, 3, 4, 5, 16, 37):
+            assert same_bits(oracle.matmul_q8r4_s(g[f"x_{tag}_{S}"], q8, s16, O), g[f"y_{tag}_{S}"])
+
+
 def test_q4r4_batch_is_not_row_invariant(oracle):
     """The reference folds the -8 offset differently for tokens inside a complete
     group of 4 (nn/matmul.c:397-402): a batch is NOT always bitwise equal to its
@@ -125,6 +137,9 @@ def test_oracle_equals_reference_build(oracle, ref):
         a, b = oracle.pack_q4r4(Wf), ref.pack_q4r4(Wf)
         assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
         assert same_bits(oracle.matmul_q4r4_s(x, a[0], a[1], O), ref.matmul_q4r4_s(x, a[0], a[1], O))
+        a, b = oracle.pack_q8r4(Wf), ref.pack_q8r4(Wf)
+        assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
+        assert same_bits(oracle.matmul_q8r4_s(x, a[0], a[1], O), ref.matmul_q8r4_s(x, a[0], a[1], O))
     lg = (rng.standard_normal((500, 128)) * 0.05).astype(np.float32)
     a, b = oracle.route_topk(lg, 8), ref.route_topk(lg, 8)
     assert all(same_bits(u, v) for u, v in zip(a, b))
