@@ -477,6 +477,10 @@ def run_case(args):
     if fmt == "q8_0":
         w = mb.Mat.i8(rng.integers(-127, 128, (O, I), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
         nbytes = algo_bytes(O, I, S)
+    elif fmt == "q8r4":
+        nblk, nb = (O + 3) // 4, I // 32
+        w = mb.Mat.q8r4(rng.integers(-127, 128, nblk * nb * 128, dtype=np.int8), np.full(nblk * nb * 4, 0x1A00, np.uint16), O, I, device=0)
+        nbytes = nblk * nb * 136 + 4 * S * I + 4 * S * O
     else:
         nblk, nb = (O + 3) // 4, I // 32
         w = mb.Mat.q4r4(rng.integers(0, 256, nblk * nb * 64, dtype=np.uint8), np.full(nblk * nb * 4, 0x1A00, np.uint16), O, I, device=0)
@@ -507,7 +511,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
-    ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0 or q4r4) times only that product, "
+    ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
                                                 "times calls of one routed layer; prints one row and exits")
     args = ap.parse_args()

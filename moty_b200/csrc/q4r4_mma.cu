@@ -283,13 +283,15 @@ int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const
     a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
     // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
     const long long mct = ((O + 15) / 16 + 7) / 8, want = (long long)sms * 2;
+    // (never a tile wider than the batch: its empty token columns would cost the same chain work)
+    const bool nt4 = S > 16 && mct * ((S + 31) / 32) >= want, nt2 = S > 8 && mct * ((S + 15) / 16) >= want;
     if (q8) {
-        if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4, true>(a, st);
-        if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2, true>(a, st);
+        if (nt4) return launch_mma_t<4, true>(a, st);
+        if (nt2) return launch_mma_t<2, true>(a, st);
         return launch_mma_t<1, true>(a, st);
     }
-    if (mct * ((S + 31) / 32) >= want) return launch_mma_t<4>(a, st);
-    if (mct * ((S + 15) / 16) >= want) return launch_mma_t<2>(a, st);
+    if (nt4) return launch_mma_t<4>(a, st);
+    if (nt2) return launch_mma_t<2>(a, st);
     return launch_mma_t<1>(a, st);
 }
 
