@@ -455,12 +455,83 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+def run_ep_case(args, name, S):
+    """Expert-parallel MoE layer over the ranks of a torchrun launch (moty_b200/parallel.py): experts in
+    contiguous ranges per rank, S tokens per rank, routing at home, all-to-all out and back, ordered combine.
+    Prints the time per layer call (CUDA events, max over ranks) beside the same S * world tokens on one GPU."""
+    import torch
+    import torch.distributed as dist
+    import moty_b200 as mb
+    from moty_b200.parallel import ExpertParallelMoe
+    rank, world, local = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1"); os.environ.setdefault("MASTER_PORT", "29533")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    mb.init([local])
+    E, K, I, D, f = MOE_SHAPES[name]
+    fmt = mb.WF_I8 if f == "i8" else mb.WF_Q4R4
+    rng = np.random.default_rng(5)
+    ep = ExpertParallelMoe(E, K, I, D, efmt=fmt, device=local)
+    one = mb.Moe(E, K, I, D, efmt=fmt, device=local) if rank == 0 else None
+    for e in range(E):
+        if fmt == mb.WF_I8:
+            g = rng.integers(-127, 128, (I, D), dtype=np.int8); u = rng.integers(-127, 128, (I, D), dtype=np.int8)
+            d = rng.integers(-127, 128, (D, I), dtype=np.int8)
+            gs = rng.uniform(0.001, 0.02, I).astype(np.float32); us = rng.uniform(0.001, 0.02, I).astype(np.float32)
+            ds = rng.uniform(0.001, 0.02, D).astype(np.float32)
+        else:
+            ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
+            g = rng.integers(0, 256, ng * 64, dtype=np.uint8); u = rng.integers(0, 256, ng * 64, dtype=np.uint8)
+            d = rng.integers(0, 256, nd * 64, dtype=np.uint8)
+            gs = np.full(ng * 4, 0x1A00, np.uint16); us = np.full(ng * 4, 0x1A00, np.uint16); ds = np.full(nd * 4, 0x1A00, np.uint16)
+        ep.upload_expert(e, g, gs, u, us, d, ds)
+        if one is not None:
+            one.upload_expert(e, g, gs, u, us, d, ds)
+    x = torch.randn((S, D), device=dev); logits = torch.randn((S, E), device=dev)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+    us_ep = timed(lambda: ep.forward(x, logits, order=1), max(args.steps, 3))
+    us_one = None
+    if rank == 0:
+        xa = torch.randn((S * world, D), device=dev); la = torch.randn((S * world, E), device=dev); oa = torch.empty_like(xa)
+        st = mb.stream_handle(torch.cuda.current_stream())
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for _ in range(3):
+            one.apply_dev(oa.data_ptr(), xa.data_ptr(), S * world, la.data_ptr(), 1, 1, 0, 0, st)
+        torch.cuda.synchronize(); e0.record()
+        for _ in range(max(args.steps, 3)):
+            one.apply_dev(oa.data_ptr(), xa.data_ptr(), S * world, la.data_ptr(), 1, 1, 0, 0, st)
+        e1.record(); torch.cuda.synchronize()
+        us_one = e0.elapsed_time(e1) * 1e3 / max(args.steps, 3)
+    dist.barrier()
+    if rank == 0:
+        print(json.dumps({"case": args.case, "world": world, "tokens_per_rank": S, "us_per_layer_ep": round(us_ep, 1),
+                          "us_per_layer_one_gpu_same_tokens": round(us_one, 1)}), flush=True)
+    dist.destroy_process_group()
+
+
 def run_case(args):
     """One matrix product, launched --warmup + --steps times on one stream (a small, self-ending
     workload for ncu captures of a single kernel)."""
     import torch
     import moty_b200 as mb
     parts = args.case.split(":")
+    if parts[0] == "ep":                                       # ep:NAME:S -- run under torchrun: expert-parallel layer, S tokens per rank
+        run_ep_case(args, parts[1], int(parts[2]))
+        return
     mb.init([0])
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(3)
@@ -513,7 +584,8 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; prints one row and exits")
+                                                "times calls of one routed layer; ep:NAME:S under torchrun times the "
+                                                "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:
         run_case(args)

@@ -15,8 +15,10 @@
  * Pointer suffix convention: plain entries take HOST pointers for activations
  * and results (they copy in and out on the library's stream and return after
  * the result is in host memory); *_dev entries take DEVICE pointers, enqueue on
- * `stream` (a cudaStream_t passed as void*, NULL = the library's own stream) and
- * return without synchronising.
+ * `stream` (a cudaStream_t passed as void*, NULL = the library's own stream; a caller whose work is on CUDA's
+ * default stream passes cudaStreamLegacy or cudaStreamPerThread, not 0) and
+ * return without synchronising.  *_dev entries that take no matrix or layer handle run on the GPU that owns
+ * their first device pointer (which must have been initialised).
  */
 #ifndef MOTY_CUDA_H
 #define MOTY_CUDA_H

@@ -69,6 +69,17 @@ def init(devices=None) -> None:
         _ck(lib().moty_cuda_init(arr, len(devices)))
 
 
+CUDA_STREAM_LEGACY = 1        # cudaStreamLegacy: the handle that NAMES the default stream (0 means "the library's own")
+
+
+def stream_handle(torch_stream) -> int:
+    """The handle to pass as `stream` for a torch stream.  torch reports the default stream as 0, which the
+    library reads as "my own stream" -- work there would not be ordered with the caller's default-stream work --
+    so the default stream is passed by its explicit name instead."""
+    h = int(torch_stream.cuda_stream)
+    return h if h != 0 else CUDA_STREAM_LEGACY
+
+
 def shutdown() -> None:
     lib().moty_cuda_shutdown()
 

@@ -21,6 +21,15 @@ int moty_set_error(int code, const char *fmt, ...) {
 
 extern "C" const char *moty_cuda_last_error(void) { return g_err; }
 
+bool moty_debug_sync() {
+    static int on = -1;
+    if (on < 0) {
+        const char *e = getenv("MOTY_CUDA_DEBUG_SYNC");
+        on = (e && e[0] == '1') ? 1 : 0;
+    }
+    return on == 1;
+}
+
 // Programmatic dependent launch is on unless the environment says MOTY_CUDA_PDL=0 (read once).
 bool moty_pdl_enabled() {
     static int on = -1;
@@ -438,8 +447,23 @@ static int ctx0(DevCtx **c) {
     return 0;
 }
 
+// The *_dev entries that take no matrix or layer handle run on the GPU that OWNS their first device pointer
+// (a process may have initialised several GPUs; the first one is only the default of the host-pointer entries).
+static int ctx_of(const void *dev_ptr, DevCtx **c) {
+    cudaPointerAttributes at;
+    cudaError_t e = cudaPointerGetAttributes(&at, dev_ptr);
+    if (e != cudaSuccess || (at.type != cudaMemoryTypeDevice && at.type != cudaMemoryTypeManaged)) {
+        (void)cudaGetLastError();
+        return moty_set_error(MOTY_CUDA_EARG, "not a device pointer");
+    }
+    *c = moty_ctx(at.device);
+    if (!*c) return moty_set_error(MOTY_CUDA_EINIT, "device %d (owner of the pointer) not initialised", at.device);
+    CK(cudaSetDevice(at.device));
+    return 0;
+}
+
 extern "C" int moty_cuda_qrow_i8_dev(const float *x_dev, int8_t *q_dev, float *scale_dev, int rows, int n, void *stream) {
-    DevCtx *c; CKR(ctx0(&c));
+    DevCtx *c; CKR(ctx_of(x_dev, &c));
     return launch_qrow_i8(x_dev, q_dev, scale_dev, rows, n, pick_stream(c, stream));
 }
 
@@ -460,7 +484,7 @@ extern "C" int moty_cuda_qrow_i8(const float *x, int8_t *q, float *scale, int ro
 
 extern "C" int moty_cuda_quant_g32_dev(const float *x_dev, int rows, int I, int8_t *xq_dev, float *xs_dev,
                                        int32_t *xsum_dev, void *stream) {
-    DevCtx *c; CKR(ctx0(&c));
+    DevCtx *c; CKR(ctx_of(x_dev, &c));
     if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "quant_g32: I=%d", I);
     return launch_quant_g32(x_dev, rows, I, xq_dev, xs_dev, xsum_dev, pick_stream(c, stream));
 }
@@ -538,7 +562,7 @@ extern "C" int moty_cuda_route_topk(const float *logits, int rows, int E, int K,
 
 extern "C" int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E, int K, int *idx_dev, float *w_dev,
                                         float *probs_dev, int norm_topk, void *stream) {
-    DevCtx *c; CKR(ctx0(&c));
+    DevCtx *c; CKR(ctx_of(logits_dev, &c));
     return launch_route(logits_dev, rows, E, K, idx_dev, w_dev, probs_dev, 1, norm_topk, pick_stream(c, stream));
 }
 
@@ -546,7 +570,7 @@ extern "C" int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E
 // greedy token
 // ---------------------------------------------------------------------------
 extern "C" int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream) {
-    DevCtx *c; CKR(ctx0(&c));
+    DevCtx *c; CKR(ctx_of(v_dev, &c));
     CKR(moty_grow(c, &c->daux, 4096));
     return launch_argmax_scratch(v_dev, n, out_dev, (float *)c->daux.p, (int *)((char *)c->daux.p + 1024),
                                  pick_stream(c, stream));
@@ -992,6 +1016,6 @@ extern "C" int moty_cuda_moe_combine_dev(float *out_dev, const float *h_dev, con
     if (!out_dev || !h_dev || !w_dev || !idx_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: null argument");
     if (S <= 0) return 0;
     if (K < 1 || K > 64 || D < 1) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: K=%d D=%d", K, D);
-    DevCtx *c; CKR(ctx0(&c));
+    DevCtx *c; CKR(ctx_of(out_dev, &c));
     return launch_moe_combine_sk(out_dev, h_dev, w_dev, idx_dev, S, K, D, order, pick_stream(c, stream));
 }

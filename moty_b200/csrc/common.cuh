@@ -25,8 +25,22 @@ int moty_set_error(int code, const char *fmt, ...);
                                   cudaGetErrorString(e_));                             \
     } while (0)
 
+// With MOTY_CUDA_DEBUG_SYNC=1 in the environment every step of a driver is followed by a device
+// synchronisation, so that a kernel fault is reported at the step that caused it (a debugging aid;
+// it serialises everything and is off by default).
+bool moty_debug_sync();
+
 #define CKR(call)                                                                      \
-    do { int r_ = (call); if (r_ != 0) return r_; } while (0)
+    do {                                                                               \
+        int r_ = (call);                                                               \
+        if (r_ != 0) return r_;                                                        \
+        if (moty_debug_sync()) {                                                       \
+            cudaError_t e_ = cudaDeviceSynchronize();                                  \
+            if (e_ != cudaSuccess)                                                     \
+                return moty_set_error(MOTY_CUDA_ECUDA, "%s:%d after %s: %s", __FILE__, __LINE__, #call, \
+                                      cudaGetErrorString(e_));                         \
+        }                                                                              \
+    } while (0)
 
 // ---------------------------------------------------------------------------
 // per-device context: one stream, grow-only scratch, pinned staging

@@ -26,7 +26,7 @@ import numpy as np
 import torch
 import torch.distributed as dist
 
-from . import WF_I8, Mat, Moe, _ck, lib
+from . import WF_I8, Mat, Moe, _ck, lib, stream_handle
 
 
 def shard_rows(O: int, world: int, rank: int, align: int = 1):
@@ -71,11 +71,11 @@ class RowShardedMat:
             n = self.hi - self.lo
             if n == self.per:
                 from . import mat_apply_dev
-                mat_apply_dev(self.mat, part.data_ptr(), x.data_ptr(), S, st.cuda_stream)
+                mat_apply_dev(self.mat, part.data_ptr(), x.data_ptr(), S, stream_handle(st))
             else:                                   # ragged last shard: compute compact, copy into the padded slot
                 from . import mat_apply_dev
                 tmp = torch.empty((S, n), dtype=torch.float32, device=self.dev)
-                mat_apply_dev(self.mat, tmp.data_ptr(), x.data_ptr(), S, st.cuda_stream)
+                mat_apply_dev(self.mat, tmp.data_ptr(), x.data_ptr(), S, stream_handle(st))
                 part[:, :n] = tmp
         gathered = torch.empty((self.world, S, self.per), dtype=torch.float32, device=self.dev)
         dist.all_gather_into_tensor(gathered, part, group=self.group)
@@ -153,7 +153,7 @@ class ExpertParallelMoe:
         s = logits.shape[0]
         idx = torch.empty((s, self.K), dtype=torch.int32, device=logits.device)
         w = torch.empty((s, self.K), dtype=torch.float32, device=logits.device)
-        st = torch.cuda.current_stream(logits.device).cuda_stream
+        st = stream_handle(torch.cuda.current_stream(logits.device))
         _ck(lib().moty_cuda_route_topk_dev(C.c_void_p(logits.data_ptr()), s, self.E, self.K, C.c_void_p(idx.data_ptr()),
                                            C.c_void_p(w.data_ptr()), None, int(norm_topk), C.c_void_p(st)))
         return idx, w
@@ -163,7 +163,7 @@ class ExpertParallelMoe:
             return self.expert_fn(rows, eids)
         h = torch.empty_like(rows)
         if rows.shape[0]:
-            st = torch.cuda.current_stream(rows.device).cuda_stream
+            st = stream_handle(torch.cuda.current_stream(rows.device))
             _ck(lib().moty_cuda_moe_experts_dev(self.moe.h, C.c_void_p(h.data_ptr()), C.c_void_p(rows.data_ptr()),
                                                 C.c_void_p(eids.data_ptr()), rows.shape[0], C.c_void_p(st)))
         return h
@@ -174,7 +174,7 @@ class ExpertParallelMoe:
         s = w.shape[0]
         out = torch.empty((s, self.D), dtype=torch.float32, device=h_sk.device)
         if s:
-            st = torch.cuda.current_stream(h_sk.device).cuda_stream
+            st = stream_handle(torch.cuda.current_stream(h_sk.device))
             _ck(lib().moty_cuda_moe_combine_dev(C.c_void_p(out.data_ptr()), C.c_void_p(h_sk.data_ptr()),
                                                 C.c_void_p(w.data_ptr()), C.c_void_p(idx.data_ptr()),
                                                 s, self.K, self.D, int(order), C.c_void_p(st)))

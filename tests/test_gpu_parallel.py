@@ -27,7 +27,9 @@ def _worker(rank, world, port):
     try:
         import moty_b200 as mb
         from moty_b200.parallel import ExpertParallelMoe, RowShardedMat
-        mb.init([rank])
+        if world > 1:
+            mb.init([(rank + 1) % world])                    # another GPU first: entries without a handle must
+        mb.init([rank])                                      # follow their pointers, not "the first device"
         dev = torch.device("cuda", rank)
         rng = np.random.default_rng(7)                       # same data on every rank
 
