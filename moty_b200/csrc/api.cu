@@ -302,7 +302,12 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (w->fmt == MOTY_WF_Q4R4) {
         int nb = I / 32;
         if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q4R4 needs I %% 32 == 0");
-        if (S == 1 && q4r4_gemv_bulk_supported(I, O, c->sms)) {      // decode, few long rows: quantize once, then stream
+        if (S == 1 && q4r4_gemv2_supported(I, O, c->sms) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {   // decode, few long rows: two phases
+            CKR(moty_grow(c, &c->rec, q4r4_gemv2_scratch_bytes(I, O)));
+            return launch_q4r4_gemv2((const uint8_t *)w->codes, (const uint16_t *)w->scales, x, y, (float *)c->rec.p,
+                                     c->err_dev + 2, I, O, c->sms, st);
+        }
+        if (S == 1 && q4r4_gemv_bulk_supported(I, O, c->sms)) {      // decode, a middling row count: quantize once, then stream
             CKR(moty_grow(c, &c->xi, (size_t)I + 16));
             CKR(moty_grow(c, &c->xs, (size_t)nb * 4));
             CKR(moty_grow(c, &c->xsum, (size_t)nb * 4));
@@ -382,12 +387,19 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, acc ? (int32_t *)c->acc32.p : nullptr, c->stream));
     CK(cudaMemcpyAsync(y, c->dy.p, yb, cudaMemcpyDeviceToHost, c->stream));
     if (acc) CK(cudaMemcpyAsync(acc, c->acc32.p, yb, cudaMemcpyDeviceToHost, c->stream));
-    int kerr = 0;
-    if (S >= Q8_TC_MIN_S) CK(cudaMemcpyAsync(&kerr, c->err_dev, 4, cudaMemcpyDeviceToHost, c->stream));
+    // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
+    // kernels fed by bulk copies
+    int kerr[4] = {0, 0, 0, 0};
+    const bool check = S >= Q8_TC_MIN_S || (S == 1 && w->fmt == MOTY_WF_Q4R4);
+    if (check) CK(cudaMemcpyAsync(kerr, c->err_dev, 16, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
-    if (kerr) {
+    if (kerr[0]) {
         cudaMemsetAsync(c->err_dev, 0, 4, c->stream);
         return moty_set_error(MOTY_CUDA_EKERNEL, "tensor-core GEMM gave up on a bounded wait (no result written)");
+    }
+    if (kerr[2]) {
+        cudaMemsetAsync(c->err_dev + 2, 0, 4, c->stream);
+        return moty_set_error(MOTY_CUDA_EKERNEL, "Q4R4 decode kernel gave up on a bounded wait (result incomplete)");
     }
     return 0;
 }

@@ -1,0 +1,265 @@
+// q4r4_gemv2.cu -- the Q4R4 decode GEMV for matrices with too few rows to give every SM
+// a dozen warps of whole rows (FFN projections): two phases.
+//
+// The reference (moty_hw_q4r4_gemm_ref, hw/hw_q4r4.h:47-63) has two layers of arithmetic: per
+// group of 32 weights an exact integer sum, and across the groups of a row ONE sequential f32
+// chain, acc = fma((float)(sum - 8 * xsum), d * xs, acc) in ascending group order.  The integer
+// layer is where the bytes are and has no order; the chain must stay sequential but needs only
+// the two f32 factors of each fused multiply-add.  So:
+//   phase 1  every (block, group) cell of 64 bytes is independent.  A CTA owns a slab of 32
+//            consecutive groups and a share of the 4-row blocks: it group-quantizes just those
+//            1024 activations (moty_hw_quant_g32, hw/hw_q4r4.h:36-45), every lane keeps the codes
+//            of the 4 groups it will ever meet in registers, and the warps stream 2 KB pieces
+//            (one block x slab) in coalesced 512-byte loads, 4 lanes per cell, one per row.
+//            Both factors, (float)(sum - 8 * xsum) and d * xs, go to a scratch table laid out for
+//            phase 2, ab[32-row band][group pair][32 rows][a, b, a', b'] (O x I/32 x 8 bytes: a
+//            few MB, it stays in L2);
+//   phase 2  a CTA is one warp and takes a band of 32 rows: the band's table is one contiguous
+//            run that arrives in shared memory through bulk asynchronous copies of 8 KB, each
+//            with its own mbarrier (bounded waits), and the warp, lane = row, runs the chain as
+//            the pieces land: one conflict-free 16-byte shared load and two fmas per group pair.
+// Phase 1 runs at memory speed whatever the shape (a 3840 x 15360 matrix has 120 warps' worth of
+// rows but 1.8 M cells); phase 2 costs a few microseconds of dependent arithmetic.
+// Same bits as the one-phase kernels (q4r4_gemv1.cu, q4r4_stream.cu).
+#include "kernels.cuh"
+
+namespace {
+
+struct Q4G2Args {
+    const uint8_t *w; const uint16_t *d;
+    const float *x; float *y;
+    float *ab;                       // [bands][(nb + 1) / 2][32][4]
+    int I, O;
+    int cps;                         // phase 1: CTAs per slab
+    int *err;                        // phase 2: set when a bounded wait expired
+};
+
+__device__ __forceinline__ int dp4a_us2(unsigned a, int b, int c) {
+    int d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
+constexpr int G2_SLAB = 32;          // groups per slab: 2 KB of one block, 4 warp steps of 512 bytes
+
+__global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
+    __shared__ __align__(16) int xq_s[G2_SLAB * 8];                     // the slab's codes, 4 per word
+    __shared__ int x8_s[G2_SLAB];                                       // 8 * code sum per group
+    __shared__ float xs_s[G2_SLAB];                                     // group scales
+    const int nb = a.I / 32, nblk = (a.O + 3) / 4;
+    const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+    const int slab = blockIdx.x / a.cps, j = blockIdx.x - slab * a.cps;
+    const int g_base = slab * G2_SLAB;
+    const int ng = nb - g_base < G2_SLAB ? nb - g_base : G2_SLAB;
+    const int gl0 = lane >> 2, r = lane & 3;                            // the lane's cell in step q: group gl0 + 8 q, row r
+    const int bstride = a.cps * 8;
+    int blk = j * 8 + warp;
+
+    int4 wA[4], wB[4]; uint16_t dA[4], dB[4];
+    const uint8_t *lane_w = a.w + ((size_t)g_base + gl0) * 64 + r * 16;
+    const uint16_t *lane_d = a.d + ((size_t)g_base + gl0) * 4 + r;
+    auto load = [&](int4 (&wv)[4], uint16_t (&dv)[4], int b) {
+        const uint8_t *p = lane_w + (size_t)b * nb * 64;
+        const uint16_t *pd = lane_d + (size_t)b * nb * 4;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const bool in = gl0 + 8 * q < ng;
+            wv[q] = in ? ldg_stream16(p + q * 512) : make_int4(0, 0, 0, 0);
+            dv[q] = in ? __ldg(pd + q * 32) : (uint16_t)0;
+        }
+    };
+    pdl_trigger();
+    if (blk < nblk) load(wA, dA, blk);                                    // weights only: may overlap the previous kernel
+    pdl_wait();
+
+    {   // the slab of the activation row: 8 threads per group, 4 values each
+        const int g = t >> 3, part = t & 7;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (g < ng) v = reinterpret_cast<const float4 *>(a.x + ((size_t)g_base + g) * 32)[part];
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float s = quant_scale(amax, 1e-30f);
+        const float inv = __fdiv_rn(1.f, s);
+        const int c0 = quant_code(v.x, inv), c1 = quant_code(v.y, inv);
+        const int c2 = quant_code(v.z, inv), c3 = quant_code(v.w, inv);
+        int tot = c0 + c1 + c2 + c3;
+        tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+        xq_s[t] = (c0 & 255) | ((c1 & 255) << 8) | ((c2 & 255) << 16) | ((c3 & 255) << 24);
+        if (part == 0) {
+            x8_s[g] = 8 * tot;
+            xs_s[g] = s;
+        }
+    }
+    __syncthreads();
+    // the lane meets 4 groups only: their codes and offsets stay in registers
+    int xr[4][8], x8[4]; float xsr[4];
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+        const int4 *p = reinterpret_cast<const int4 *>(xq_s + (gl0 + 8 * q) * 8);
+        const int4 lo = p[0], hi = p[1];
+        xr[q][0] = lo.x; xr[q][1] = lo.y; xr[q][2] = lo.z; xr[q][3] = lo.w;
+        xr[q][4] = hi.x; xr[q][5] = hi.y; xr[q][6] = hi.z; xr[q][7] = hi.w;
+        x8[q] = x8_s[gl0 + 8 * q];
+        xsr[q] = xs_s[gl0 + 8 * q];
+    }
+    // ab[band][pair][32][4]: the lane's row inside its band depends on the block only
+    const int nb2 = (nb + 1) / 2;
+    auto consume = [&](const int4 (&cur)[4], const uint16_t (&dcur)[4], int4 (&nxt)[4], uint16_t (&dnxt)[4]) {
+        const int b = blk;
+        blk += bstride;
+        if (blk < nblk) load(nxt, dnxt, blk);
+        float *out = a.ab + (((size_t)(b >> 3) * nb2 + (g_base >> 1) + (gl0 >> 1)) * 32 + (b & 7) * 4 + r) * 4 + (gl0 & 1) * 2;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int4 w4 = cur[q];
+            // low nibbles as they are; high nibbles stay in place (16 x their value), are read as UNSIGNED bytes by
+            // dp4a and the exact factor 16 is shifted out of the sum afterwards
+            int sraw = __dp4a(w4.x & 0x0f0f0f0f, xr[q][0], 0);
+            sraw = __dp4a(w4.y & 0x0f0f0f0f, xr[q][1], sraw);
+            sraw = __dp4a(w4.z & 0x0f0f0f0f, xr[q][2], sraw);
+            sraw = __dp4a(w4.w & 0x0f0f0f0f, xr[q][3], sraw);
+            int s16 = dp4a_us2((unsigned)w4.x & 0xf0f0f0f0u, xr[q][4], 0);
+            s16 = dp4a_us2((unsigned)w4.y & 0xf0f0f0f0u, xr[q][5], s16);
+            s16 = dp4a_us2((unsigned)w4.z & 0xf0f0f0f0u, xr[q][6], s16);
+            s16 = dp4a_us2((unsigned)w4.w & 0xf0f0f0f0u, xr[q][7], s16);
+            sraw += s16 >> 4;
+            // the two factors of the chain's fma (hw/hw_q4r4.h:58-59)
+            if (gl0 + 8 * q < ng)
+                *reinterpret_cast<float2 *>(out + q * 512) =
+                    make_float2((float)(sraw - x8[q]), __fmul_rn(f16bits_to_f32(dcur[q]), xsr[q]));
+        }
+    };
+    while (blk < nblk) {
+        consume(wA, dA, wB, dB);
+        if (blk >= nblk) break;
+        consume(wB, dB, wA, dA);
+    }
+}
+
+// ---- phase 2: one warp per CTA, a band of 32 rows, lane = row (hw/hw_q4r4.h:58-59) ----
+constexpr int G2_PIECE = 16;                      // group pairs per bulk copy: 8 KB
+constexpr unsigned G2_WAIT_LIMIT = 1u << 26;
+
+__device__ __forceinline__ unsigned g2_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool g2_wait(unsigned long long *bar, unsigned parity) {
+    for (unsigned it = 0; it < G2_WAIT_LIMIT; it++) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(g2_smem(bar)), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(32) q4r4_g2_chain_kernel(Q4G2Args a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    const int nb = a.I / 32, nb2 = (nb + 1) / 2, O = a.O;
+    const int lane = threadIdx.x, band = blockIdx.x;
+    const int npieces = (nb2 + G2_PIECE - 1) / G2_PIECE;
+    float4 *ab_s = reinterpret_cast<float4 *>(smem);                     // [nb2][32]
+    unsigned long long *bars = reinterpret_cast<unsigned long long *>(smem + (size_t)nb2 * 512);
+    if (lane == 0) {
+        for (int p = 0; p < npieces; p++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(g2_smem(&bars[p])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+    pdl_trigger();
+    pdl_wait();                                                          // the table comes from phase 1
+    if (lane == 0) {
+        const float4 *src = reinterpret_cast<const float4 *>(a.ab) + (size_t)band * nb2 * 32;
+        for (int p = 0; p < npieces; p++) {
+            const int np = nb2 - p * G2_PIECE < G2_PIECE ? nb2 - p * G2_PIECE : G2_PIECE;
+            const unsigned bytes = (unsigned)np * 512u;
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(g2_smem(&bars[p])), "r"(bytes) : "memory");
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"(g2_smem(ab_s + (size_t)p * G2_PIECE * 32)), "l"(src + (size_t)p * G2_PIECE * 32), "r"(bytes),
+                           "r"(g2_smem(&bars[p])) : "memory");
+        }
+    }
+    const int nfull = nb / 2;                                            // pairs with both groups
+    float acc = 0.f;
+    bool ok = true;
+    for (int p = 0; p < npieces && ok; p++) {
+        ok = g2_wait(&bars[p], 0);
+        if (!ok) break;
+        const float4 *v = ab_s + (size_t)p * G2_PIECE * 32 + lane;
+        const int n = nfull - p * G2_PIECE < G2_PIECE ? nfull - p * G2_PIECE : G2_PIECE;
+        if (n == G2_PIECE) {
+#pragma unroll
+            for (int h = 0; h < G2_PIECE; h += 8) {                       // 8 loads on their way before the first fma needs one
+                float4 f[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) f[i] = v[(h + i) * 32];
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    acc = fmaf(f[i].x, f[i].y, acc);
+                    acc = fmaf(f[i].z, f[i].w, acc);
+                }
+            }
+        } else {
+            for (int i = 0; i < n; i++) {
+                const float4 f = v[i * 32];
+                acc = fmaf(f.x, f.y, acc);
+                acc = fmaf(f.z, f.w, acc);
+            }
+        }
+    }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) {
+        // a bounded wait expired: copies may still be in flight towards this CTA's memory; give them time, report
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+        if (lane == 0) atomicExch(a.err, 1);
+        return;
+    }
+    if (nb & 1) {                                                        // an odd group count: the last pair is half full
+        const float4 f = ab_s[(size_t)nfull * 32 + lane];
+        acc = fmaf(f.x, f.y, acc);
+    }
+    if (band * 32 + lane < O) a.y[band * 32 + lane] = acc;
+}
+
+}  // namespace
+
+// Worth two launches: enough cells to occupy the machine, and few enough rows that the lane-per-row kernels starve
+// (3840 x 15360: 9.7 us against 31.6 us of the bulk-fed kernel, 15360 x 3840: 9.1 against 15.2, 5120 x 13824: 10.5
+// against 28.5; from 32000 x 4096 on the one-phase kernels are level or ahead: 19.7 against 18.5 us, and the
+// vocabulary matrix 151936 x 1024 takes 20.5 against 17.2 us of q4r4_gemv1_kernel).
+bool q4r4_gemv2_supported(int I, int O, int sms) {
+    const int nbands = (O + 31) / 32;
+    return I % 32 == 0 && I > 0 && I <= MOTY_QROW_MAX && nbands < sms * 6 &&
+           (long long)((O + 3) / 4) * (I / 32) >= 400000;
+}
+
+size_t q4r4_gemv2_scratch_bytes(int I, int O) { return (size_t)((O + 31) / 32) * ((I / 32 + 1) / 2) * 32 * 16; }
+
+// x: 16-byte aligned; ab: q4r4_gemv2_scratch_bytes(I, O), 128-byte aligned; err: set when a bounded wait expired
+int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float *y, float *ab, int *err,
+                      int I, int O, int sms, cudaStream_t st) {
+    if (!q4r4_gemv2_supported(I, O, sms)) return moty_set_error(MOTY_CUDA_EARG, "q4r4_gemv2: I=%d O=%d", I, O);
+    Q4G2Args a; a.w = w; a.d = d; a.x = x; a.y = y; a.ab = ab; a.err = err; a.I = I; a.O = O;
+    const int nb = I / 32, nslab = (nb + G2_SLAB - 1) / G2_SLAB, nblk = (O + 3) / 4;
+    int cps = sms * 2 / nslab;
+    if (cps < 1) cps = 1;
+    if (cps > (nblk + 7) / 8) cps = (nblk + 7) / 8;
+    a.cps = cps;
+    const int nb2 = (nb + 1) / 2;
+    const size_t smem2 = (size_t)nb2 * 512 + (size_t)((nb2 + G2_PIECE - 1) / G2_PIECE) * 8;   // at most 256 pairs: 128 KB
+    static bool attr_set[MOTY_MAX_DEV];
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q4r4_gemv2: device %d", dev);
+    if (!attr_set[dev]) {
+        CK(cudaFuncSetAttribute(q4r4_g2_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                MOTY_QROW_MAX / 64 * 512 + 16 * 8));
+        attr_set[dev] = true;
+    }
+    CK(moty_launch_pdl(q4r4_g2_sums_kernel, dim3((unsigned)(cps * nslab)), dim3(256), (size_t)0, st, a));
+    CK(moty_launch_pdl(q4r4_g2_chain_kernel, dim3((unsigned)((O + 31) / 32)), dim3(32), smem2, st, a));
+    return 0;
+}

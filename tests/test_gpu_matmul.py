@@ -85,11 +85,14 @@ def test_q4r4_decode_many_rows_vs_oracle(gpu, oracle, O, I):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
-@pytest.mark.parametrize("O,I", [(15360, 3840), (9601, 5504), (3838, 15360), (4001, 12800)])
+@pytest.mark.parametrize("O,I", [(15360, 3840), (9601, 5504), (3838, 15360), (4001, 12800), (3199, 16384), (3200, 16352),
+                                 (30001, 2048), (28417, 1920)])
 def test_q4r4_decode_few_long_rows_vs_oracle(gpu, oracle, O, I):
-    """Matrices the bulk-copy-fed decode kernel takes (one lane per row, shared-memory ring): the FFN
-    shapes of the benchmark, row counts that are not multiples of 4 or 32, a group count that is not a
-    multiple of the 16-group stage; the last two have too few rows for it and take the general kernel."""
+    """One activation row against matrices with too few rows for the lane-per-row kernel.  The first six take the
+    two-phase kernel (integer sums in parallel, then the chain from a table of factors): the FFN shapes of the
+    benchmark, row counts that are not multiples of 4 or 32, group counts that are not multiples of the 32-group
+    slab, the longest row allowed and an odd group count.  The last two have a middling row count and take the
+    kernel fed by bulk copies."""
     rng = np.random.default_rng(O + I)
     q4 = rng.integers(0, 256, (O + 3) // 4 * (I // 32) * 64, dtype=np.uint8)
     s16 = rng.uniform(0.001, 0.01, (O + 3) // 4 * (I // 32) * 4).astype(np.float16).view(np.uint16)
