@@ -114,7 +114,7 @@ inline cudaError_t moty_launch_pdl(void (*k)(KArgs...), dim3 grid, dim3 block, s
     return cudaLaunchKernelEx(&cfg, k, static_cast<KArgs>(args)...);
 }
 
-// 16-byte and 8-byte asynchronous copies global -> shared (.cg: around L1, for data read once);
+// 16-, 8- and 4-byte asynchronous copies global -> shared (.cg: around L1, for data read once);
 // cp_async16_zfill copies nothing and writes 16 zero bytes when !valid (the source is not read)
 __device__ __forceinline__ void cp_async16(void *smem, const void *g) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
@@ -122,6 +122,9 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *g) {
 __device__ __forceinline__ void cp_async16_zfill(void *smem, const void *g, bool valid) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g),
                  "r"(valid ? 16 : 0) : "memory");
+}
+__device__ __forceinline__ void cp_async4(void *smem, const void *g) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
 }
 __device__ __forceinline__ void cp_async8(void *smem, const void *g) {
     asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"((unsigned)__cvta_generic_to_shared(smem)), "l"(g) : "memory");

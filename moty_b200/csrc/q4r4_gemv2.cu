@@ -41,8 +41,12 @@ __device__ __forceinline__ int dp4a_us2(unsigned a, int b, int c) {
 }
 
 constexpr int G2_SLAB = 32;          // groups per slab: 2 KB of one block, 4 warp steps of 512 bytes
+constexpr int G2_NST = 4;            // stages in a warp's ring: 3 blocks x slab on their way while one is consumed
+constexpr int G2_STAGE = 2048 + 512; // codes as they lie in memory, then one 4-byte slot per lane and step for its f16 scale
+constexpr size_t G2_RING = (size_t)8 * G2_NST * G2_STAGE;
 
 __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
+    extern __shared__ __align__(16) unsigned char ring[];               // [warp][stage][G2_STAGE]
     __shared__ __align__(16) int xq_s[G2_SLAB * 8];                     // the slab's codes, 4 per word
     __shared__ int x8_s[G2_SLAB];                                       // 8 * code sum per group
     __shared__ float xs_s[G2_SLAB];                                     // group scales
@@ -52,24 +56,31 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
     const int g_base = slab * G2_SLAB;
     const int ng = nb - g_base < G2_SLAB ? nb - g_base : G2_SLAB;
     const int gl0 = lane >> 2, r = lane & 3;                            // the lane's cell in step q: group gl0 + 8 q, row r
-    const int bstride = a.cps * 8;
-    int blk = j * 8 + warp;
+    const int bstride = a.cps * 8, blk0 = j * 8 + warp;
+    const int nmine = blk0 < nblk ? (nblk - 1 - blk0) / bstride + 1 : 0;  // blocks this warp takes: blk0 + i * bstride
 
-    int4 wA[4], wB[4]; uint16_t dA[4], dB[4];
+    // Every lane copies exactly the bytes it will consume (its 16 bytes of codes per step, the aligned 4 bytes that
+    // hold its f16 scale), so a stage needs no barrier: cp.async.wait_group orders a thread's own copies.
+    unsigned char *my = ring + (size_t)warp * G2_NST * G2_STAGE + lane * 16;
     const uint8_t *lane_w = a.w + ((size_t)g_base + gl0) * 64 + r * 16;
-    const uint16_t *lane_d = a.d + ((size_t)g_base + gl0) * 4 + r;
-    auto load = [&](int4 (&wv)[4], uint16_t (&dv)[4], int b) {
-        const uint8_t *p = lane_w + (size_t)b * nb * 64;
-        const uint16_t *pd = lane_d + (size_t)b * nb * 4;
+    const uint8_t *lane_d = reinterpret_cast<const uint8_t *>(a.d) + (((size_t)g_base + gl0) * 4 + (r & 2)) * 2;
+    auto issue = [&](int i) {
+        if (i < nmine) {
+            const size_t b = (size_t)(blk0 + i * bstride);
+            const uint8_t *pw = lane_w + b * nb * 64, *pd = lane_d + b * nb * 8;
+            unsigned char *st = my + (i % G2_NST) * G2_STAGE;
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            const bool in = gl0 + 8 * q < ng;
-            wv[q] = in ? ldg_stream16(p + q * 512) : make_int4(0, 0, 0, 0);
-            dv[q] = in ? __ldg(pd + q * 32) : (uint16_t)0;
+            for (int q = 0; q < 4; q++)
+                if (gl0 + 8 * q < ng) {
+                    cp_async16(st + q * 512, pw + q * 512);
+                    cp_async4(st + 2048 + q * 128 - lane * 12, pd + q * 64);   // slot q * 128 + lane * 4
+                }
         }
+        cp_async_commit();
     };
     pdl_trigger();
-    if (blk < nblk) load(wA, dA, blk);                                    // weights only: may overlap the previous kernel
+#pragma unroll
+    for (int i = 0; i < G2_NST - 1; i++) issue(i);                      // weights only: may overlap the previous kernel
     pdl_wait();
 
     {   // the slab of the activation row: 8 threads per group, 4 values each
@@ -95,7 +106,7 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
         }
     }
     __syncthreads();
-    // the lane meets 4 groups only: their codes and offsets stay in registers
+    // the lane meets 4 groups only: their codes, offsets and scales stay in registers
     int xr[4][8], x8[4]; float xsr[4];
 #pragma unroll
     for (int q = 0; q < 4; q++) {
@@ -108,14 +119,16 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
     }
     // ab[band][pair][32][4]: the lane's row inside its band depends on the block only
     const int nb2 = (nb + 1) / 2;
-    auto consume = [&](const int4 (&cur)[4], const uint16_t (&dcur)[4], int4 (&nxt)[4], uint16_t (&dnxt)[4]) {
-        const int b = blk;
-        blk += bstride;
-        if (blk < nblk) load(nxt, dnxt, blk);
+    for (int i = 0; i < nmine; i++) {
+        issue(i + G2_NST - 1);
+        cp_async_wait<G2_NST - 1>();                                     // stage i has landed
+        const int b = blk0 + i * bstride;
+        const unsigned char *st = my + (i % G2_NST) * G2_STAGE;
         float *out = a.ab + (((size_t)(b >> 3) * nb2 + (g_base >> 1) + (gl0 >> 1)) * 32 + (b & 7) * 4 + r) * 4 + (gl0 & 1) * 2;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
-            const int4 w4 = cur[q];
+            const int4 w4 = *reinterpret_cast<const int4 *>(st + q * 512);
+            const uint16_t dq = *reinterpret_cast<const uint16_t *>(st + 2048 + q * 128 - lane * 12 + (r & 1) * 2);
             // low nibbles as they are; high nibbles stay in place (16 x their value), are read as UNSIGNED bytes by
             // dp4a and the exact factor 16 is shifted out of the sum afterwards
             int sraw = __dp4a(w4.x & 0x0f0f0f0f, xr[q][0], 0);
@@ -130,14 +143,10 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
             // the two factors of the chain's fma (hw/hw_q4r4.h:58-59)
             if (gl0 + 8 * q < ng)
                 *reinterpret_cast<float2 *>(out + q * 512) =
-                    make_float2((float)(sraw - x8[q]), __fmul_rn(f16bits_to_f32(dcur[q]), xsr[q]));
+                    make_float2((float)(sraw - x8[q]), __fmul_rn(f16bits_to_f32(dq), xsr[q]));
         }
-    };
-    while (blk < nblk) {
-        consume(wA, dA, wB, dB);
-        if (blk >= nblk) break;
-        consume(wB, dB, wA, dA);
     }
+    cp_async_wait<0>();
 }
 
 // ---- phase 2: one warp per CTA, a band of 32 rows, lane = row (hw/hw_q4r4.h:58-59) ----
@@ -257,9 +266,10 @@ int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float
     if (!attr_set[dev]) {
         CK(cudaFuncSetAttribute(q4r4_g2_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 MOTY_QROW_MAX / 64 * 512 + 16 * 8));
+        CK(cudaFuncSetAttribute(q4r4_g2_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G2_RING));
         attr_set[dev] = true;
     }
-    CK(moty_launch_pdl(q4r4_g2_sums_kernel, dim3((unsigned)(cps * nslab)), dim3(256), (size_t)0, st, a));
+    CK(moty_launch_pdl(q4r4_g2_sums_kernel, dim3((unsigned)(cps * nslab)), dim3(256), G2_RING, st, a));
     CK(moty_launch_pdl(q4r4_g2_chain_kernel, dim3((unsigned)((O + 31) / 32)), dim3(32), smem2, st, a));
     return 0;
 }
