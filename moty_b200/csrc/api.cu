@@ -302,10 +302,10 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (w->fmt == MOTY_WF_Q4R4) {
         int nb = I / 32;
         if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q4R4 needs I %% 32 == 0");
-        if (S == 1 && q4r4_gemv2_supported(I, O, c->sms) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {   // decode, few long rows: two phases
+        if (S == 1 && q4r4_gemv2_supported(I, O, 0, c->sms) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {   // decode, few long rows: two phases
             CKR(moty_grow(c, &c->rec, q4r4_gemv2_scratch_bytes(I, O)));
             return launch_q4r4_gemv2((const uint8_t *)w->codes, (const uint16_t *)w->scales, x, y, (float *)c->rec.p,
-                                     c->err_dev + 2, I, O, c->sms, st);
+                                     c->err_dev + 2, I, O, 0, c->sms, st);
         }
         if (S == 1 && q4r4_gemv_bulk_supported(I, O, c->sms)) {      // decode, a middling row count: quantize once, then stream
             CKR(moty_grow(c, &c->xi, (size_t)I + 16));
@@ -344,6 +344,11 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         // the int8 sibling of Q4R4: same group quantizer, same chain, no offset term; one kernel for every S
         const int nb = I / 32;
         if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: Q8R4 needs I %% 32 == 0");
+        if (S == 1 && q4r4_gemv2_supported(I, O, 1, c->sms) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {   // decode: two phases
+            CKR(moty_grow(c, &c->rec, q4r4_gemv2_scratch_bytes(I, O)));
+            return launch_q4r4_gemv2((const uint8_t *)w->codes, (const uint16_t *)w->scales, x, y, (float *)c->rec.p,
+                                     c->err_dev + 2, I, O, 1, c->sms, st);
+        }
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
         CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
@@ -390,7 +395,7 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
     // kernels fed by bulk copies
     int kerr[4] = {0, 0, 0, 0};
-    const bool check = S >= Q8_TC_MIN_S || (S == 1 && w->fmt == MOTY_WF_Q4R4);
+    const bool check = S >= Q8_TC_MIN_S || (S == 1 && (w->fmt == MOTY_WF_Q4R4 || w->fmt == MOTY_WF_Q8R4));
     if (check) CK(cudaMemcpyAsync(kerr, c->err_dev, 16, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     if (kerr[0]) {
@@ -399,7 +404,7 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     }
     if (kerr[2]) {
         cudaMemsetAsync(c->err_dev + 2, 0, 4, c->stream);
-        return moty_set_error(MOTY_CUDA_EKERNEL, "Q4R4 decode kernel gave up on a bounded wait (result incomplete)");
+        return moty_set_error(MOTY_CUDA_EKERNEL, "Q4R4/Q8R4 decode kernel gave up on a bounded wait (result incomplete)");
     }
     return 0;
 }

@@ -20,7 +20,8 @@
 //            the pieces land: one conflict-free 16-byte shared load and two fmas per group pair.
 // Phase 1 runs at memory speed whatever the shape (a 3840 x 15360 matrix has 120 warps' worth of
 // rows but 1.8 M cells); phase 2 costs a few microseconds of dependent arithmetic.
-// Same bits as the one-phase kernels (q4r4_gemv1.cu, q4r4_stream.cu).
+// Same bits as the one-phase kernels (q4r4_gemv1.cu, q4r4_stream.cu).  Q8R4 matrices (the int8 sibling, 128 bytes per
+// cell, no offset term) take the same two phases for every shape.
 #include "kernels.cuh"
 
 namespace {
@@ -40,40 +41,49 @@ __device__ __forceinline__ int dp4a_us2(unsigned a, int b, int c) {
     return d;
 }
 
-constexpr int G2_SLAB = 32;          // groups per slab: 2 KB of one block, 4 warp steps of 512 bytes
-constexpr int G2_NST = 4;            // stages in a warp's ring: 3 blocks x slab on their way while one is consumed
+// Phase 1 works in warp steps of 512 bytes, four steps to a stage.  Q4R4: a cell is 64 bytes, 4 lanes per cell (one
+// per row), 8 cells per step, so a stage is one block x a slab of 32 groups.  Q8R4 (Q8 = true; hw/hw_q4r4.h:92-130:
+// 128 bytes per cell = 4 rows x 32 signed codes, no offset term): 8 lanes per cell (two per row, 16 codes each, sums
+// joined by one shuffle), 4 cells per step, a slab of 16 groups.
+constexpr int G2_NST = 4;            // stages in a warp's ring: 3 on their way while one is consumed
 constexpr int G2_STAGE = 2048 + 512; // codes as they lie in memory, then one 4-byte slot per lane and step for its f16 scale
 constexpr size_t G2_RING = (size_t)8 * G2_NST * G2_STAGE;
 
+template <bool Q8>
 __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
+    constexpr int SLAB = Q8 ? 16 : 32;                                  // groups per slab
+    constexpr int LPC = Q8 ? 8 : 4, CPS = 32 / LPC;                     // lanes per cell, cells per step
+    constexpr int CELL = Q8 ? 128 : 64;
+    constexpr int XW = Q8 ? 4 : 8;                                      // words of activation codes a lane needs per group
     extern __shared__ __align__(16) unsigned char ring[];               // [warp][stage][G2_STAGE]
-    __shared__ __align__(16) int xq_s[G2_SLAB * 8];                     // the slab's codes, 4 per word
-    __shared__ int x8_s[G2_SLAB];                                       // 8 * code sum per group
-    __shared__ float xs_s[G2_SLAB];                                     // group scales
+    __shared__ __align__(16) int xq_s[32 * 8];                          // the slab's codes, 4 per word
+    __shared__ int x8_s[32];                                            // 8 * code sum per group (Q4R4's offset term)
+    __shared__ float xs_s[32];                                          // group scales
     const int nb = a.I / 32, nblk = (a.O + 3) / 4;
     const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
     const int slab = blockIdx.x / a.cps, j = blockIdx.x - slab * a.cps;
-    const int g_base = slab * G2_SLAB;
-    const int ng = nb - g_base < G2_SLAB ? nb - g_base : G2_SLAB;
-    const int gl0 = lane >> 2, r = lane & 3;                            // the lane's cell in step q: group gl0 + 8 q, row r
+    const int g_base = slab * SLAB;
+    const int ng = nb - g_base < SLAB ? nb - g_base : SLAB;
+    // the lane's cell in step q: group cl + CPS q; its row; (Q8R4) which 16 of the row's 32 codes
+    const int cl = lane / LPC, r = Q8 ? (lane >> 1) & 3 : lane & 3, half = Q8 ? lane & 1 : 0;
     const int bstride = a.cps * 8, blk0 = j * 8 + warp;
     const int nmine = blk0 < nblk ? (nblk - 1 - blk0) / bstride + 1 : 0;  // blocks this warp takes: blk0 + i * bstride
 
     // Every lane copies exactly the bytes it will consume (its 16 bytes of codes per step, the aligned 4 bytes that
     // hold its f16 scale), so a stage needs no barrier: cp.async.wait_group orders a thread's own copies.
     unsigned char *my = ring + (size_t)warp * G2_NST * G2_STAGE + lane * 16;
-    const uint8_t *lane_w = a.w + ((size_t)g_base + gl0) * 64 + r * 16;
-    const uint8_t *lane_d = reinterpret_cast<const uint8_t *>(a.d) + (((size_t)g_base + gl0) * 4 + (r & 2)) * 2;
+    const uint8_t *lane_w = a.w + (size_t)g_base * CELL + lane * 16;    // a step is 512 consecutive bytes
+    const uint8_t *lane_d = reinterpret_cast<const uint8_t *>(a.d) + (((size_t)g_base + cl) * 4 + (r & 2)) * 2;
     auto issue = [&](int i) {
         if (i < nmine) {
             const size_t b = (size_t)(blk0 + i * bstride);
-            const uint8_t *pw = lane_w + b * nb * 64, *pd = lane_d + b * nb * 8;
+            const uint8_t *pw = lane_w + b * nb * CELL, *pd = lane_d + b * nb * 8;
             unsigned char *st = my + (i % G2_NST) * G2_STAGE;
 #pragma unroll
             for (int q = 0; q < 4; q++)
-                if (gl0 + 8 * q < ng) {
+                if (cl + CPS * q < ng) {
                     cp_async16(st + q * 512, pw + q * 512);
-                    cp_async4(st + 2048 + q * 128 - lane * 12, pd + q * 64);   // slot q * 128 + lane * 4
+                    cp_async4(st + 2048 + q * 128 - lane * 12, pd + q * CPS * 8);   // slot q * 128 + lane * 4
                 }
         }
         cp_async_commit();
@@ -101,21 +111,25 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
         tot += __shfl_xor_sync(0xffffffffu, tot, 4);
         xq_s[t] = (c0 & 255) | ((c1 & 255) << 8) | ((c2 & 255) << 16) | ((c3 & 255) << 24);
         if (part == 0) {
-            x8_s[g] = 8 * tot;
+            x8_s[g] = Q8 ? 0 : 8 * tot;
             xs_s[g] = s;
         }
     }
     __syncthreads();
     // the lane meets 4 groups only: their codes, offsets and scales stay in registers
-    int xr[4][8], x8[4]; float xsr[4];
+    int xr[4][XW], x8[4]; float xsr[4];
 #pragma unroll
     for (int q = 0; q < 4; q++) {
-        const int4 *p = reinterpret_cast<const int4 *>(xq_s + (gl0 + 8 * q) * 8);
-        const int4 lo = p[0], hi = p[1];
+        const int gq = cl + CPS * q;
+        const int4 *p = reinterpret_cast<const int4 *>(xq_s + gq * 8 + half * 4);
+        const int4 lo = p[0];
         xr[q][0] = lo.x; xr[q][1] = lo.y; xr[q][2] = lo.z; xr[q][3] = lo.w;
-        xr[q][4] = hi.x; xr[q][5] = hi.y; xr[q][6] = hi.z; xr[q][7] = hi.w;
-        x8[q] = x8_s[gl0 + 8 * q];
-        xsr[q] = xs_s[gl0 + 8 * q];
+        if (!Q8) {
+            const int4 hi = p[1];
+            xr[q][XW - 4] = hi.x; xr[q][XW - 3] = hi.y; xr[q][XW - 2] = hi.z; xr[q][XW - 1] = hi.w;
+        }
+        x8[q] = x8_s[gq];
+        xsr[q] = xs_s[gq];
     }
     // ab[band][pair][32][4]: the lane's row inside its band depends on the block only
     const int nb2 = (nb + 1) / 2;
@@ -124,25 +138,34 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
         cp_async_wait<G2_NST - 1>();                                     // stage i has landed
         const int b = blk0 + i * bstride;
         const unsigned char *st = my + (i % G2_NST) * G2_STAGE;
-        float *out = a.ab + (((size_t)(b >> 3) * nb2 + (g_base >> 1) + (gl0 >> 1)) * 32 + (b & 7) * 4 + r) * 4 + (gl0 & 1) * 2;
+        float *out = a.ab + (((size_t)(b >> 3) * nb2 + (g_base >> 1) + (cl >> 1)) * 32 + (b & 7) * 4 + r) * 4 + (cl & 1) * 2;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const int4 w4 = *reinterpret_cast<const int4 *>(st + q * 512);
             const uint16_t dq = *reinterpret_cast<const uint16_t *>(st + 2048 + q * 128 - lane * 12 + (r & 1) * 2);
-            // low nibbles as they are; high nibbles stay in place (16 x their value), are read as UNSIGNED bytes by
-            // dp4a and the exact factor 16 is shifted out of the sum afterwards
-            int sraw = __dp4a(w4.x & 0x0f0f0f0f, xr[q][0], 0);
-            sraw = __dp4a(w4.y & 0x0f0f0f0f, xr[q][1], sraw);
-            sraw = __dp4a(w4.z & 0x0f0f0f0f, xr[q][2], sraw);
-            sraw = __dp4a(w4.w & 0x0f0f0f0f, xr[q][3], sraw);
-            int s16 = dp4a_us2((unsigned)w4.x & 0xf0f0f0f0u, xr[q][4], 0);
-            s16 = dp4a_us2((unsigned)w4.y & 0xf0f0f0f0u, xr[q][5], s16);
-            s16 = dp4a_us2((unsigned)w4.z & 0xf0f0f0f0u, xr[q][6], s16);
-            s16 = dp4a_us2((unsigned)w4.w & 0xf0f0f0f0u, xr[q][7], s16);
-            sraw += s16 >> 4;
-            // the two factors of the chain's fma (hw/hw_q4r4.h:58-59)
-            if (gl0 + 8 * q < ng)
-                *reinterpret_cast<float2 *>(out + q * 512) =
+            int sraw;
+            if (Q8) {                                                    // 16 of the row's 32 products, the other lane has the rest
+                sraw = __dp4a(w4.x, xr[q][0], 0);
+                sraw = __dp4a(w4.y, xr[q][1], sraw);
+                sraw = __dp4a(w4.z, xr[q][2], sraw);
+                sraw = __dp4a(w4.w, xr[q][3], sraw);
+                sraw += __shfl_xor_sync(0xffffffffu, sraw, 1);
+            } else {
+                // low nibbles as they are; high nibbles stay in place (16 x their value), are read as UNSIGNED bytes by
+                // dp4a and the exact factor 16 is shifted out of the sum afterwards
+                sraw = __dp4a(w4.x & 0x0f0f0f0f, xr[q][0], 0);
+                sraw = __dp4a(w4.y & 0x0f0f0f0f, xr[q][1], sraw);
+                sraw = __dp4a(w4.z & 0x0f0f0f0f, xr[q][2], sraw);
+                sraw = __dp4a(w4.w & 0x0f0f0f0f, xr[q][3], sraw);
+                int s16 = dp4a_us2((unsigned)w4.x & 0xf0f0f0f0u, xr[q][XW - 4], 0);
+                s16 = dp4a_us2((unsigned)w4.y & 0xf0f0f0f0u, xr[q][XW - 3], s16);
+                s16 = dp4a_us2((unsigned)w4.z & 0xf0f0f0f0u, xr[q][XW - 2], s16);
+                s16 = dp4a_us2((unsigned)w4.w & 0xf0f0f0f0u, xr[q][XW - 1], s16);
+                sraw += s16 >> 4;
+            }
+            // the two factors of the chain's fma (hw/hw_q4r4.h:58-59, :103-104)
+            if (cl + CPS * q < ng && half == 0)
+                *reinterpret_cast<float2 *>(out + q * (CPS / 2) * 128) =
                     make_float2((float)(sraw - x8[q]), __fmul_rn(f16bits_to_f32(dq), xsr[q]));
         }
     }
@@ -235,24 +258,27 @@ __global__ void __launch_bounds__(32) q4r4_g2_chain_kernel(Q4G2Args a) {
 
 }  // namespace
 
-// Worth two launches: enough cells to occupy the machine, and few enough rows that the lane-per-row kernels starve
-// (3840 x 15360: 9.7 us against 31.6 us of the bulk-fed kernel, 15360 x 3840: 9.1 against 15.2, 5120 x 13824: 10.5
-// against 28.5; from 32000 x 4096 on the one-phase kernels are level or ahead: 19.7 against 18.5 us, and the
-// vocabulary matrix 151936 x 1024 takes 20.5 against 17.2 us of q4r4_gemv1_kernel).
-bool q4r4_gemv2_supported(int I, int O, int sms) {
+// Q4R4: worth two launches when there are enough cells to occupy the machine and few enough rows that the lane-per-row
+// kernels starve (3840 x 15360: 9.7 us against 31.6 us of the bulk-fed kernel, 15360 x 3840: 9.1 against 15.2,
+// 5120 x 13824: 10.5 against 28.5; from 32000 x 4096 on the one-phase kernels are level or ahead: 19.7 against
+// 18.5 us, and the vocabulary matrix 151936 x 1024 takes 20.5 against 17.2 us of q4r4_gemv1_kernel).
+// Q8R4 has no one-phase decode kernel: every matrix comes here.
+bool q4r4_gemv2_supported(int I, int O, int q8, int sms) {
+    if (I % 32 != 0 || I <= 0 || I > MOTY_QROW_MAX || O <= 0) return false;
+    if (q8) return true;
     const int nbands = (O + 31) / 32;
-    return I % 32 == 0 && I > 0 && I <= MOTY_QROW_MAX && nbands < sms * 6 &&
-           (long long)((O + 3) / 4) * (I / 32) >= 400000;
+    return nbands < sms * 6 && (long long)((O + 3) / 4) * (I / 32) >= 400000;
 }
 
 size_t q4r4_gemv2_scratch_bytes(int I, int O) { return (size_t)((O + 31) / 32) * ((I / 32 + 1) / 2) * 32 * 16; }
 
-// x: 16-byte aligned; ab: q4r4_gemv2_scratch_bytes(I, O), 128-byte aligned; err: set when a bounded wait expired
+// x: 16-byte aligned; ab: q4r4_gemv2_scratch_bytes(I, O), 128-byte aligned; err: set when a bounded wait expired;
+// q8 != 0: w holds Q8R4 codes
 int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float *y, float *ab, int *err,
-                      int I, int O, int sms, cudaStream_t st) {
-    if (!q4r4_gemv2_supported(I, O, sms)) return moty_set_error(MOTY_CUDA_EARG, "q4r4_gemv2: I=%d O=%d", I, O);
+                      int I, int O, int q8, int sms, cudaStream_t st) {
+    if (!q4r4_gemv2_supported(I, O, q8, sms)) return moty_set_error(MOTY_CUDA_EARG, "q4r4_gemv2: I=%d O=%d", I, O);
     Q4G2Args a; a.w = w; a.d = d; a.x = x; a.y = y; a.ab = ab; a.err = err; a.I = I; a.O = O;
-    const int nb = I / 32, nslab = (nb + G2_SLAB - 1) / G2_SLAB, nblk = (O + 3) / 4;
+    const int nb = I / 32, slab = q8 ? 16 : 32, nslab = (nb + slab - 1) / slab, nblk = (O + 3) / 4;
     int cps = sms * 2 / nslab;
     if (cps < 1) cps = 1;
     if (cps > (nblk + 7) / 8) cps = (nblk + 7) / 8;
@@ -266,10 +292,12 @@ int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float
     if (!attr_set[dev]) {
         CK(cudaFuncSetAttribute(q4r4_g2_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                 MOTY_QROW_MAX / 64 * 512 + 16 * 8));
-        CK(cudaFuncSetAttribute(q4r4_g2_sums_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G2_RING));
+        CK(cudaFuncSetAttribute(q4r4_g2_sums_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G2_RING));
+        CK(cudaFuncSetAttribute(q4r4_g2_sums_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)G2_RING));
         attr_set[dev] = true;
     }
-    CK(moty_launch_pdl(q4r4_g2_sums_kernel, dim3((unsigned)(cps * nslab)), dim3(256), G2_RING, st, a));
+    if (q8) CK(moty_launch_pdl(q4r4_g2_sums_kernel<true>, dim3((unsigned)(cps * nslab)), dim3(256), G2_RING, st, a));
+    else CK(moty_launch_pdl(q4r4_g2_sums_kernel<false>, dim3((unsigned)(cps * nslab)), dim3(256), G2_RING, st, a));
     CK(moty_launch_pdl(q4r4_g2_chain_kernel, dim3((unsigned)((O + 31) / 32)), dim3(32), smem2, st, a));
     return 0;
 }

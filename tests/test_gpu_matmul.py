@@ -115,6 +115,20 @@ def test_q8r4_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I", [(15360, 3840), (3838, 15360), (9601, 5504), (3200, 16352), (56833, 512)])
+def test_q8r4_decode_large_vs_oracle(gpu, oracle, O, I):
+    """One activation row against large Q8R4 matrices (the two-phase decode kernel): FFN shapes, row counts that are
+    not multiples of 4 or 32, group counts that are not multiples of the 16-group slab, an odd group count, many
+    short rows."""
+    rng = np.random.default_rng(O * 3 + I)
+    q8 = rng.integers(-127, 128, (O + 3) // 4 * (I // 32) * 128, dtype=np.int8)
+    s16 = rng.uniform(0.001, 0.01, (O + 3) // 4 * (I // 32) * 4).astype(np.float16).view(np.uint16)
+    x = rng.standard_normal((1, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.q8r4(q8, s16, O, I), x)
+    yo = oracle.matmul_q8r4_s(x, q8, s16, O)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
 def test_q8r4_golden_and_extremes(gpu, oracle):
     g = golden("matmul_q8r4")
     for tag in ("a", "b"):
