@@ -123,7 +123,7 @@ extern "C" void moty_cuda_shutdown(void) {
         cudaSetDevice(c->dev);
         cudaStreamSynchronize(c->stream);
         Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
-                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec};
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec, &c->mmak};
         for (Buf *b : bs) free_buf(b);
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
@@ -272,12 +272,18 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
-        // small batches: weights streamed once, mma.sync -- unless the matrix has so few 128-row tiles that the
-        // tensor-core kernel's split over K is what keeps all SMs streaming
-        const bool few_tiles = tc && ((O + 127) / 128) * 4 <= c->sms && I >= 2048;
-        if (vec && S > 8 && S <= Q8_MMA_MAX_S && !few_tiles)
+        // small batches: weights streamed once, mma.sync (split over K when the matrix has few 128-row tiles) -- unless
+        // the rows are so long that the tensor-core kernel's split over K does better (3840 x 15360: 29.0 against 31.5 us)
+        const bool few_tiles = tc && ((O + 127) / 128) * 4 <= c->sms && I >= 8192;
+        if (vec && S > 8 && S <= Q8_MMA_MAX_S && !few_tiles) {
+            void *scratch = nullptr;
+            if (q8_mma_ksplit(S, I, O, c->sms) > 1) {
+                CKR(moty_grow_zero(c, &c->mmak, q8_mma_scratch_bytes(S, O)));
+                scratch = c->mmak.p;
+            }
             return launch_q8_mma((const int8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
-                                 (const float *)c->sx.p, y, acc, S, I, O, c->sms, st);
+                                 (const float *)c->sx.p, y, acc, S, I, O, scratch, c->sms, st);
+        }
         if (tc) return launch_q8_tc(w, (const int8_t *)c->xi.p, (const float *)c->sx.p, y, acc, S, c, st);
         if (stream_ok) {
             for (int s0 = 0; s0 < S; s0 += 8) {

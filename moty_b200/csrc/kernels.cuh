@@ -88,8 +88,10 @@ int launch_q4r4_gemv_bulk(const uint8_t *w, const uint16_t *d, const int8_t *xq,
 
 // ---- q8_mma.cu: Q8_0 x a small batch (mma.sync, weights streamed once), dense and grouped ----
 bool q8_mma_supported(int S, int I, int O);
+int q8_mma_ksplit(int S, int I, int O, int sms);
+size_t q8_mma_scratch_bytes(int S, int O);
 int launch_q8_mma(const int8_t *w, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
-                  int S, int I, int O, int sms, cudaStream_t st);
+                  int S, int I, int O, void *scratch, int sms, cudaStream_t st);
 int launch_q8_mma_grouped(const Q8Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
                           const int8_t *xi, const float *sx, const int *xmap, float *y, int ldy, int I, int O,
                           cudaStream_t st);

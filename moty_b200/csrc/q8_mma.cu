@@ -21,6 +21,9 @@ struct Q8MmaArgs {
     // grouped mode: CTA row y of the grid is a tile = up to 8 NT consecutive rows of the gathered
     // batch that share one expert's matrix; activation rows are found through xmap (null: identity)
     const Q8Tile *tiles; const int *ntiles_dev; const int *xmap;
+    // dense split-K: grid.z CTAs share a tile's K range; their int32 partials meet in part[S][O] (zero between calls),
+    // the CTA that arrives last at ctr[tile] (zero between calls) writes the result and leaves both zero again
+    int ksplit; int32_t *part; unsigned *ctr;
 };
 
 __device__ __forceinline__ void mma_s8s8_16832(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -52,13 +55,16 @@ __global__ void __launch_bounds__(256) q8_mma_kernel(Q8MmaArgs a) {
         Wp = t.w; Sc = t.scale; n00 = t.row0; S = t.row0 + t.nrows;
     }
     const int row0 = blockIdx.x * 128;
-    const int nstage = (I + Q8M_KCH - 1) / Q8M_KCH;
+    const int nstage_all = (I + Q8M_KCH - 1) / Q8M_KCH;
+    // this CTA's share of the K stages (dense split-K; otherwise everything)
+    const int per_z = (nstage_all + (int)gridDim.z - 1) / (int)gridDim.z;
+    const int s_lo = (int)blockIdx.z * per_z, nstage = nstage_all - s_lo < per_z ? (nstage_all - s_lo > 0 ? nstage_all - s_lo : 0) : per_z;
     // copies: a row's 128 bytes of a stage are 8 chunks of 16; thread t takes chunk t & 7 of rows t >> 3, + 32, ...
     const int ch = threadIdx.x & 7, r_first = threadIdx.x >> 3;
     auto fill_w = [&](int s) {
         if (s >= nstage) return;
         unsigned char *dst = smem + (size_t)(s % Q8M_NSTG) * L::BYTES + L::W;
-        const int k = s * Q8M_KCH + ch * 16;
+        const int k = (s_lo + s) * Q8M_KCH + ch * 16;
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const int r = r_first + q * 32;
@@ -69,7 +75,7 @@ __global__ void __launch_bounds__(256) q8_mma_kernel(Q8MmaArgs a) {
     auto fill_x = [&](int s) {
         if (s >= nstage) return;
         unsigned char *dst = smem + (size_t)(s % Q8M_NSTG) * L::BYTES + L::B;
-        const int k = s * Q8M_KCH + ch * 16;
+        const int k = (s_lo + s) * Q8M_KCH + ch * 16;
         for (int r = r_first; r < NT * 8; r += 32) {
             int n = n00 + r; n = n < S ? n : S - 1;
             if (a.xmap) n = a.xmap[n];
@@ -105,6 +111,41 @@ __global__ void __launch_bounds__(256) q8_mma_kernel(Q8MmaArgs a) {
     }
     cp_async_wait<0>();
     const int ra = row0 + warp * 16 + gid, rb = ra + 8;
+    if (gridDim.z > 1) {
+        // integer partials are exact in any order: add them up in global memory, the last CTA of the tile finishes
+        __shared__ unsigned s_last;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int t = n00 + j * 8 + tid * 2 + h;
+                if (t >= S) continue;
+                if (ra < O) atomicAdd(a.part + (size_t)t * O + ra, acc[j][h]);
+                if (rb < O) atomicAdd(a.part + (size_t)t * O + rb, acc[j][2 + h]);
+            }
+        }
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            const unsigned tile = blockIdx.y * gridDim.x + blockIdx.x;
+            const unsigned prev = atomicAdd(a.ctr + tile, 1u);
+            s_last = prev == gridDim.z - 1;
+            if (s_last) a.ctr[tile] = 0;                       // ready for the next call
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int t = n00 + j * 8 + tid * 2 + h;
+                if (t >= S) continue;
+                if (ra < O) { acc[j][h] = __ldcg(a.part + (size_t)t * O + ra); a.part[(size_t)t * O + ra] = 0; }
+                if (rb < O) { acc[j][2 + h] = __ldcg(a.part + (size_t)t * O + rb); a.part[(size_t)t * O + rb] = 0; }
+            }
+        }
+    }
     const float sa = ra < O ? Sc[ra] : 0.f, sb = rb < O ? Sc[rb] : 0.f;
 #pragma unroll
     for (int j = 0; j < NT; j++) {
@@ -136,7 +177,7 @@ static int launch_q8m_t(const Q8MmaArgs &a, cudaStream_t st, int ntiles_max) {
         CK(cudaFuncSetAttribute(q8_mma_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         attr_done[dev] = true;
     }
-    dim3 grid((a.O + 127) / 128, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT));
+    dim3 grid((a.O + 127) / 128, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT), a.tiles || a.ksplit < 2 ? 1 : a.ksplit);
     if (grid.y > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q8_mma: %u token tiles in one call", grid.y);
     CK(moty_launch_pdl(q8_mma_kernel<NT>, grid, dim3(256), (size_t)SMEM, st, a));
     return 0;
@@ -144,16 +185,43 @@ static int launch_q8m_t(const Q8MmaArgs &a, cudaStream_t st, int ntiles_max) {
 
 bool q8_mma_supported(int S, int I, int O) { return S >= 1 && I % 16 == 0 && I >= 16 && O >= 1; }
 
-// xi/sx: the S quantized rows.  y (and acc, optional) [S][O].
+// K splits worth taking for a dense product: none while the row and token tiles alone give every SM a CTA (the
+// partials cost one atomic per output and split: 15360 x 3840 at S = 16, 240 CTAs, lost 6 us to a split in two);
+// else enough for two CTAs per SM, at most 8, each with at least 8 stages (5120 x 13824 at S = 12: 45.7 -> 35.7 us,
+// 1024 x 3072 at S = 16: 16.4 -> 10.5 us)
+int q8_mma_ksplit(int S, int I, int O, int sms) {
+    const long long mct = (O + 127) / 128, want = (long long)sms * 2;
+    const int nt = S > 16 && mct * ((S + 31) / 32) >= want ? 4 : (S > 8 && mct * ((S + 15) / 16) >= want ? 2 : 1);
+    const long long ctas = mct * ((S + 8 * nt - 1) / (8 * nt));
+    const int nstage = (I + Q8M_KCH - 1) / Q8M_KCH;
+    if (ctas >= sms || nstage < 16) return 1;
+    int ks = (int)((want + ctas - 1) / ctas);
+    if (ks > 8) ks = 8;
+    if (ks > nstage / 8) ks = nstage / 8;
+    return ks < 2 ? 1 : ks;
+}
+
+// scratch for split-K: S * O int32 partials after 4096 tile counters, all zero between calls
+size_t q8_mma_scratch_bytes(int S, int O) { return 4096 * 4 + (size_t)S * O * 4; }
+
+// xi/sx: the S quantized rows.  y (and acc, optional) [S][O].  scratch: null, or q8_mma_scratch_bytes(S, O) zero-filled
+// bytes that stay zero from call to call (allows split-K, see q8_mma_ksplit).
 int launch_q8_mma(const int8_t *w, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
-                  int S, int I, int O, int sms, cudaStream_t st) {
+                  int S, int I, int O, void *scratch, int sms, cudaStream_t st) {
     if (!q8_mma_supported(S, I, O)) return moty_set_error(MOTY_CUDA_EARG, "q8_mma: S=%d I=%d O=%d", S, I, O);
     Q8MmaArgs a; memset(&a, 0, sizeof a);
     a.w = w; a.scale = scale; a.xi = xi; a.sx = sx; a.y = y; a.acc = acc; a.ldy = O; a.S = S; a.I = I; a.O = O;
     // wider token tiles read the weights fewer times; narrower ones give more CTAs
     const long long mct = (O + 127) / 128, want = (long long)sms * 2;
-    if (S > 16 && mct * ((S + 31) / 32) >= want) return launch_q8m_t<4>(a, st, 0);
-    if (S > 8 && mct * ((S + 15) / 16) >= want) return launch_q8m_t<2>(a, st, 0);
+    const int nt = S > 16 && mct * ((S + 31) / 32) >= want ? 4 : (S > 8 && mct * ((S + 15) / 16) >= want ? 2 : 1);
+    a.ksplit = 1;
+    if (scratch && mct * ((S + 8 * nt - 1) / (8 * nt)) <= 4096) {
+        a.ksplit = q8_mma_ksplit(S, I, O, sms);
+        a.ctr = reinterpret_cast<unsigned *>(scratch);
+        a.part = reinterpret_cast<int32_t *>(reinterpret_cast<unsigned char *>(scratch) + 4096 * 4);
+    }
+    if (nt == 4) return launch_q8m_t<4>(a, st, 0);
+    if (nt == 2) return launch_q8m_t<2>(a, st, 0);
     return launch_q8m_t<1>(a, st, 0);
 }
 

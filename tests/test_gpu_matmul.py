@@ -45,6 +45,22 @@ def test_q8_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo)
 
 
+@pytest.mark.parametrize("O,I,S", [(1024, 3072, 16), (515, 3840, 9), (2000, 4096, 12), (5121, 6912, 12), (3000, 2176, 16)])
+def test_q8_small_batch_split_k(gpu, oracle, O, I, S):
+    """9..16 rows against matrices with few 128-row tiles: the MMA kernel splits K over several CTAs whose int32
+    partials meet in a scratch table that has to be zero again afterwards -- so every case runs twice, the second
+    time on other activations.  Row counts off the tile size, a row length that is not a multiple of the 128-byte stage."""
+    rng = np.random.default_rng(O + I * 3 + S)
+    Wq = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    W = gpu.Mat.i8(Wq, sc)
+    for _ in range(2):
+        x = rng.standard_normal((S, I)).astype(np.float32)
+        y, acc = gpu.mat_apply(W, x, want_acc=True)
+        yo, acco = oracle.matmul_q_s(x, Wq, sc, want_acc=True)
+        assert np.array_equal(acc, acco)
+        assert same_bits(y, yo)
+
+
 @pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1022, 3072), (515, 3840), (258, 15360), (768, 2048), (4, 32), (7, 64)])
 @pytest.mark.parametrize("S", [1, 2, 3, 4, 7, 12, 37])
 def test_q4r4_vs_oracle(gpu, oracle, O, I, S):
