@@ -548,6 +548,9 @@ def run_case(args):
     if fmt == "q8_0":
         w = mb.Mat.i8(rng.integers(-127, 128, (O, I), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
         nbytes = algo_bytes(O, I, S)
+    elif fmt == "i4g":
+        w = mb.Mat.i4g(rng.integers(0, 256, (O, I // 2), dtype=np.uint8), rng.uniform(0.001, 0.02, (O, I // 32)).astype(np.float32), O, I, device=0)
+        nbytes = O * I // 2 + 4 * O * (I // 32) + 4 * S * I + 4 * S * O
     elif fmt == "q8r4":
         nblk, nb = (O + 3) // 4, I // 32
         w = mb.Mat.q8r4(rng.integers(-127, 128, nblk * nb * 128, dtype=np.int8), np.full(nblk * nb * 4, 0x1A00, np.uint16), O, I, device=0)

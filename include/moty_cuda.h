@@ -29,7 +29,7 @@ extern "C" {
 #endif
 
 /* weight formats: the values of the WF_* enum in hw/hw.h:53 */
-enum { MOTY_WF_F32 = 0, MOTY_WF_I8 = 1, MOTY_WF_I4 = 2, MOTY_WF_Q4R4 = 7, MOTY_WF_Q8R4 = 8 };
+enum { MOTY_WF_F32 = 0, MOTY_WF_I8 = 1, MOTY_WF_I4 = 2, MOTY_WF_I4G = 4, MOTY_WF_Q4R4 = 7, MOTY_WF_Q8R4 = 8 };
 /* activations between the two halves of an FFN (hw/hw_ops.h:19-21, engines/gemma.c:389-391) */
 enum { MOTY_ACT_SILU = 0, MOTY_ACT_GELU_TANH = 1 };
 
@@ -73,6 +73,9 @@ int moty_cuda_host_free(void *p);
  *   MOTY_WF_Q8R4 codes int8 [ceil(O/4)][I/32][128] (4 rows x 32 codes), scales as Q4R4
  *                                                                         (hw/hw_q4r4.h:92-99)
  *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55)
+ *   MOTY_WF_I4G  codes uint8 [O][I/2] (even element in the low nibble), scales f32 [O][I/32]: grouped int4,
+ *                group size 32 (nn/quant.c:57-83); applied through the integer path of
+ *                moty_matmul_i4_grouped_s (nn/matmul.c:164-197, IDOT4=1): I % 32 == 0, I <= 16384
  *   MOTY_WF_F32  codes float [O][I], scales NULL (router matrices only)
  * The hook point in the loader is right after load_mat_bits / load_mat_r4 /
  * load_embed_q8 (runtime/rt_model_load.h:85-177, 209-226). */
@@ -122,6 +125,9 @@ int moty_cuda_q8_apply_noalloc(float *y_dev, const float *x_dev, const int8_t *q
 int moty_cuda_matmul_q_s(float *y, const float *x, const int8_t *q, const float *scale, int S, int I, int O);
 /* moty_matmul_q4r4_s (nn/matmul.c:405) with host weights */
 int moty_cuda_matmul_q4r4_s(float *y, const float *x, const uint8_t *q4, const uint16_t *s16, int S, int I, int O);
+/* moty_matmul_i4_grouped_s (nn/matmul.c:164) with host weights, integer path (IDOT4=1), gs = 32 only */
+int moty_cuda_matmul_i4_grouped_s(float *y, const float *x, const uint8_t *q4, const float *scale,
+                                  int S, int I, int O, int gs);
 /* moty_matmul_q8r4_s (nn/matmul.c:435-461): the int8 sibling of Q4R4 used for mixed precision
  * (tensors matched by Q8_TENSORS, runtime/rt_model_load.h:38-61); uploads per call like the two above */
 int moty_cuda_matmul_q8r4_s(float *y, const float *x, const int8_t *q8, const uint16_t *s16, int S, int I, int O);
@@ -227,6 +233,12 @@ int moty_cuda_moe_combine_dev(float *out_dev, const float *h_dev, const float *w
  * moty_argmax_v (nn/sample.c:9-13): first index of the maximum of v [n]. */
 int moty_cuda_argmax(const float *v, int n, int *out);
 int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream);
+/* The lm_head and the greedy pick in one call (moty_nn_head_apply without the speculative head,
+ * nn/head.c:134-135, followed by moty_argmax_v, nn/sample.c:9-13, as the engines' decode step does):
+ * ids [S] receives the first index of each row's maximum; the S x O logits stay on the device unless
+ * `logits` (host, [S][O]) / `logits_dev` is given.  x: [S][I].  Results equal mat_apply + argmax. */
+int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, int *ids, float *logits);
+int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, int S, int *ids_dev, float *logits_dev, void *stream);
 
 /* ---- load-time quantizers (weights) -----------------------------------------
  * moty_quantize_rows (nn/quant.c:12-33) with bits = 8: w [O][I] f32 host ->

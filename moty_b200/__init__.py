@@ -19,7 +19,7 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libmoty_cuda.so")
 
-WF_F32, WF_I8, WF_I4, WF_Q4R4, WF_Q8R4 = 0, 1, 2, 7, 8
+WF_F32, WF_I8, WF_I4, WF_I4G, WF_Q4R4, WF_Q8R4 = 0, 1, 2, 4, 7, 8
 ACT_SILU, ACT_GELU_TANH = 0, 1
 QROW_MAX = 16384
 
@@ -152,6 +152,11 @@ class Mat:
         return cls(WF_I4, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device)
 
     @classmethod
+    def i4g(cls, q4, scale, O, I, device=0):
+        """WF_I4G: q4 [O][I/2] (even element in the low nibble), scale f32 [O][I/32]; group size 32."""
+        return cls(WF_I4G, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device)
+
+    @classmethod
     def f32(cls, w, device=0):
         w = _f32(w)
         return cls(WF_F32, w, None, w.shape[0], w.shape[1], device)
@@ -210,6 +215,15 @@ def matmul_q4r4_s(x, q4, s16, O):
     y = np.empty((S, O), np.float32)
     _ck(lib().moty_cuda_matmul_q4r4_s(_p(y), _p(x), _p(np.ascontiguousarray(q4, np.uint8)),
                                       _p(np.ascontiguousarray(s16, np.uint16)), S, I, O))
+    return y
+
+
+def matmul_i4_grouped_s(x, q4, scale, O, gs=32):
+    """moty_matmul_i4_grouped_s (nn/matmul.c:164-197, integer path) with host weights."""
+    x = _f32(x); S, I = x.shape
+    y = np.empty((S, O), np.float32)
+    _ck(lib().moty_cuda_matmul_i4_grouped_s(_p(y), _p(x), _p(np.ascontiguousarray(q4, np.uint8)), _p(_f32(scale)),
+                                            S, I, O, gs))
     return y
 
 
@@ -284,6 +298,18 @@ def argmax(v) -> int:
     out = C.c_int(0)
     _ck(lib().moty_cuda_argmax(_p(v), v.size, C.byref(out)))
     return out.value
+
+
+def head_argmax(head: "Mat", x, want_logits=False):
+    """lm_head + greedy pick in one call (nn/head.c:134-135 then nn/sample.c:9-13): ids [S], optionally the logits."""
+    x = _f32(x)
+    if x.ndim == 1:
+        x = x[None]
+    S = x.shape[0]
+    ids = np.empty(S, np.int32)
+    lg = np.empty((S, head.O), np.float32) if want_logits else None
+    _ck(lib().moty_cuda_head_argmax(head.h, _p(x), S, _p(ids), _p(lg) if want_logits else None))
+    return (ids, lg) if want_logits else ids
 
 
 def quantize_rows(w):

@@ -169,6 +169,9 @@ static int mat_sizes(int fmt, int O, int I, size_t *cb, size_t *sb) {
         case MOTY_WF_I8: *cb = (size_t)O * I; *sb = (size_t)O * 4; return 0;
         case MOTY_WF_I4: *cb = (size_t)O * ((I + 1) / 2); *sb = (size_t)O * 4; return 0;
         case MOTY_WF_F32: *cb = (size_t)O * I * 4; *sb = 0; return 0;
+        case MOTY_WF_I4G:
+            if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "I4G is built for group size 32 and I %% 32 == 0 (I=%d)", I);
+            *cb = (size_t)O * (I / 2); *sb = (size_t)O * (I / 32) * 4; return 0;
         case MOTY_WF_Q4R4:
             if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "Q4R4 needs I %% 32 == 0 (I=%d)", I);
             *cb = (size_t)((O + 3) / 4) * (I / 32) * 64; *sb = (size_t)((O + 3) / 4) * (I / 32) * 8; return 0;
@@ -372,6 +375,21 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         return launch_i4_rows((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
                               (const float *)c->sx.p, y, S, I, O, st);
     }
+    if (w->fmt == MOTY_WF_I4G) {
+        // the integer path of moty_matmul_i4_grouped_s (IDOT4=1): rows longer than the quantizer's limit would take the
+        // reference's f32 dequant product, which is not built
+        if (I > MOTY_QROW_MAX) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: I4G rows up to %d (I=%d)", MOTY_QROW_MAX, I);
+        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
+        CKR(moty_grow(c, &c->sx, (size_t)S * 4));
+        CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
+        if (S == 1) {                                           // decode: integer sums in parallel, then the chain
+            CKR(moty_grow(c, &c->rec, q4r4_gemv2_scratch_bytes(I, O)));
+            return launch_i4g_gemv2((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                                    (const float *)c->sx.p, y, (float *)c->rec.p, c->err_dev + 2, I, O, c->sms, st);
+        }
+        return launch_i4g_rows((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                               (const float *)c->sx.p, y, S, I, O, st);
+    }
     return moty_set_error(MOTY_CUDA_EARG, "mat_apply: format %d", w->fmt);
 }
 
@@ -401,7 +419,7 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
     // kernels fed by bulk copies
     int kerr[4] = {0, 0, 0, 0};
-    const bool check = S >= Q8_TC_MIN_S || (S == 1 && (w->fmt == MOTY_WF_Q4R4 || w->fmt == MOTY_WF_Q8R4));
+    const bool check = S >= Q8_TC_MIN_S || (S == 1 && (w->fmt == MOTY_WF_Q4R4 || w->fmt == MOTY_WF_Q8R4 || w->fmt == MOTY_WF_I4G));
     if (check) CK(cudaMemcpyAsync(kerr, c->err_dev, 16, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     if (kerr[0]) {
@@ -444,6 +462,18 @@ extern "C" int moty_cuda_matmul_q8r4_s(float *y, const float *x, const int8_t *q
     if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
     MotyCudaMat *m = nullptr;
     CKR(moty_cuda_upload_mat(&m, MOTY_WF_Q8R4, q8, s16, O, I, dev));
+    int r = moty_cuda_mat_apply(m, y, x, S);
+    moty_cuda_free_mat(m);
+    return r;
+}
+
+extern "C" int moty_cuda_matmul_i4_grouped_s(float *y, const float *x, const uint8_t *q4, const float *scale,
+                                             int S, int I, int O, int gs) {
+    int dev = first_device();
+    if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
+    if (gs != 32) return moty_set_error(MOTY_CUDA_EARG, "matmul_i4_grouped_s: group size 32 only (gs=%d)", gs);
+    MotyCudaMat *m = nullptr;
+    CKR(moty_cuda_upload_mat(&m, MOTY_WF_I4G, q4, scale, O, I, dev));
     int r = moty_cuda_mat_apply(m, y, x, S);
     moty_cuda_free_mat(m);
     return r;
@@ -608,6 +638,47 @@ extern "C" int moty_cuda_argmax(const float *v, int n, int *out) {
     int *dout = (int *)((char *)c->daux.p + 2048);
     CKR(launch_argmax_scratch((const float *)c->dx.p, n, dout, (float *)c->daux.p, (int *)((char *)c->daux.p + 1024), c->stream));
     CK(cudaMemcpyAsync(out, dout, 4, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// lm_head + greedy token in one call: the logits stay on the device, one int per row comes back
+extern "C" int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, int S, int *ids_dev, float *logits_dev,
+                                         void *stream) {
+    if (!head || !x_dev || !ids_dev) return moty_set_error(MOTY_CUDA_EARG, "head_argmax_dev: null argument");
+    if (S <= 0) return 0;
+    DevCtx *c = moty_ctx(head->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", head->device);
+    CK(cudaSetDevice(head->device));
+    cudaStream_t st = pick_stream(c, stream);
+    float *lg = logits_dev;
+    if (!lg) {
+        CKR(moty_grow(c, &c->dlogits, (size_t)S * head->O * 4));
+        lg = (float *)c->dlogits.p;
+    }
+    CKR(moty_grow(c, &c->daux, 4096));
+    CKR(mat_apply_on(c, head, lg, x_dev, S, nullptr, st));
+    for (int s = 0; s < S; s++)
+        CKR(launch_argmax_scratch(lg + (size_t)s * head->O, head->O, ids_dev + s, (float *)c->daux.p,
+                                  (int *)((char *)c->daux.p + 1024), st));
+    return 0;
+}
+
+extern "C" int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, int *ids, float *logits) {
+    if (!head || !x || !ids) return moty_set_error(MOTY_CUDA_EARG, "head_argmax: null argument");
+    if (S <= 0) return 0;
+    DevCtx *c = moty_ctx(head->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", head->device);
+    CK(cudaSetDevice(head->device));
+    const size_t xb = (size_t)S * head->I * 4, lb = (size_t)S * head->O * 4;
+    CKR(moty_grow(c, &c->dx, xb));
+    CKR(moty_grow(c, &c->dlogits, lb));
+    CKR(moty_grow(c, &c->daux, 4096 + (size_t)S * 4));
+    int *dids = (int *)((char *)c->daux.p + 4096);
+    CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
+    CKR(moty_cuda_head_argmax_dev(head, (const float *)c->dx.p, S, dids, (float *)c->dlogits.p, c->stream));
+    CK(cudaMemcpyAsync(ids, dids, (size_t)S * 4, cudaMemcpyDeviceToHost, c->stream));
+    if (logits) CK(cudaMemcpyAsync(logits, c->dlogits.p, lb, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     return 0;
 }

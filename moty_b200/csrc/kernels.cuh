@@ -75,11 +75,18 @@ int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 bool q4r4_gemv1_supported(int I, int O, int sms);
 int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float *y, int I, int O, int sms, cudaStream_t st);
 
+// ---- i4g.cu: WF_I4G (grouped int4, group 32, f32 group scales) x row-quantized activations ----
+int launch_i4g_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx, float *y,
+                    int S, int I, int O, cudaStream_t st);
+
 // ---- q4r4_gemv2.cu: Q4R4 / Q8R4 decode GEMV in two phases (parallel integer sums, then the chain) ----
 bool q4r4_gemv2_supported(int I, int O, int q8, int sms);
 size_t q4r4_gemv2_scratch_bytes(int I, int O);
 int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float *y, float *ab, int *err,
                       int I, int O, int q8, int sms, cudaStream_t st);
+
+int launch_i4g_gemv2(const uint8_t *w4, const float *gscale, const int8_t *xi, const float *sx, float *y, float *ab,
+                     int *err, int I, int O, int sms, cudaStream_t st);
 
 // ---- q4r4_gemv_bulk.cu: Q4R4 decode GEMV for few long rows (lane = row, fed by bulk async copies) ----
 bool q4r4_gemv_bulk_supported(int I, int O, int sms);

@@ -23,6 +23,7 @@
 // Same bits as the one-phase kernels (q4r4_gemv1.cu, q4r4_stream.cu).  Q8R4 matrices (the int8 sibling, 128 bytes per
 // cell, no offset term) take the same two phases for every shape.
 #include "kernels.cuh"
+#include <string.h>
 
 namespace {
 
@@ -33,6 +34,8 @@ struct Q4G2Args {
     int I, O;
     int cps;                         // phase 1: CTAs per slab
     int *err;                        // phase 2: set when a bounded wait expired
+    // WF_I4G (i4g_g2_sums_kernel): f32 group scales [O][nb], the row's int8 codes and its scale from qrow_i8
+    const float *gscale; const int8_t *xi; const float *sx;
 };
 
 __device__ __forceinline__ int dp4a_us2(unsigned a, int b, int c) {
@@ -172,6 +175,81 @@ __global__ void __launch_bounds__(256, 2) q4r4_g2_sums_kernel(Q4G2Args a) {
     cp_async_wait<0>();
 }
 
+// ---- phase 1 for WF_I4G (grouped int4, rows of I/2 bytes, f32 group scales [O][nb]; nn/matmul.c:164-197 with
+// IDOT4=1, hw/hw_quant.h:35-50): a CTA owns a slab of 32 groups = 512 consecutive bytes of every row, lane = group.
+// The activation row was quantized per ROW by qrow_i8; the lane keeps its group's codes, split into even and odd
+// elements (a byte holds the even element in its low nibble), in registers.  A warp step is four rows: four
+// coalesced 512-byte loads of codes and four 128-byte loads of scales, two register buffers alternate.
+// Factors of the chain's fma: (float)(sum(nibble * x) - 8 * sum(x)) and scl[g]; the chain kernel multiplies by sx.
+constexpr int G2I_R = 4;
+__global__ void __launch_bounds__(256, 2) i4g_g2_sums_kernel(Q4G2Args a) {
+    const int nb = a.I / 32, O = a.O;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int slab = blockIdx.x / a.cps, j = blockIdx.x - slab * a.cps;
+    const int g = slab * 32 + lane;
+    const bool gin = g < nb;
+    const int gc = gin ? g : nb - 1;                                    // groups past the row: a valid address, nothing stored
+    const int rstride = a.cps * 8 * G2I_R;
+    int row = (j * 8 + warp) * G2I_R;
+    const uint8_t *wp = a.w + (size_t)gc * 16;
+    const float *sp = a.gscale + gc;
+    const size_t rb = (size_t)a.I / 2;
+
+    uint4 wA[G2I_R], wB[G2I_R]; float cA[G2I_R], cB[G2I_R];
+    auto load = [&](uint4 (&wv)[G2I_R], float (&cv)[G2I_R], int r0) {
+#pragma unroll
+        for (int u = 0; u < G2I_R; u++) {
+            const int r = r0 + u < O ? r0 + u : O - 1;
+            const int4 t = ldg_stream16(wp + (size_t)r * rb);
+            wv[u] = make_uint4((unsigned)t.x, (unsigned)t.y, (unsigned)t.z, (unsigned)t.w);
+            cv[u] = __ldg(sp + (size_t)r * nb);
+        }
+    };
+    pdl_trigger();
+    if (row < O) load(wA, cA, row);                                     // weights only: may overlap the previous kernel
+    pdl_wait();                                                         // the codes come from the quantizer launch
+    int xe[4], xo[4], x8;
+    {
+        const int4 *src = reinterpret_cast<const int4 *>(a.xi + (size_t)gc * 32);
+        const int4 x0 = src[0], x1 = src[1];
+        xe[0] = __byte_perm(x0.x, x0.y, 0x6420); xo[0] = __byte_perm(x0.x, x0.y, 0x7531);
+        xe[1] = __byte_perm(x0.z, x0.w, 0x6420); xo[1] = __byte_perm(x0.z, x0.w, 0x7531);
+        xe[2] = __byte_perm(x1.x, x1.y, 0x6420); xo[2] = __byte_perm(x1.x, x1.y, 0x7531);
+        xe[3] = __byte_perm(x1.z, x1.w, 0x6420); xo[3] = __byte_perm(x1.z, x1.w, 0x7531);
+        int sum = 0;
+#pragma unroll
+        for (int k = 0; k < 4; k++) { sum = __dp4a(xe[k], 0x01010101, sum); sum = __dp4a(xo[k], 0x01010101, sum); }
+        x8 = 8 * sum;
+    }
+    const int nb2 = (nb + 1) / 2;
+    float *out0 = a.ab + ((size_t)(g >> 1) * 32) * 4 + (g & 1) * 2;      // + (band * nb2 * 32 + row in band) * 4
+    auto consume = [&](const uint4 (&cur)[G2I_R], const float (&ccur)[G2I_R], uint4 (&nxt)[G2I_R], float (&cnxt)[G2I_R]) {
+        const int r0 = row;
+        row += rstride;
+        if (row < O) load(nxt, cnxt, row);
+#pragma unroll
+        for (int u = 0; u < G2I_R; u++) {
+            const int r = r0 + u;
+            const uint4 w = cur[u];
+            int d = __dp4a((int)(w.x & 0x0f0f0f0fu), xe[0], -x8);
+            d = __dp4a((int)(w.y & 0x0f0f0f0fu), xe[1], d);
+            d = __dp4a((int)(w.z & 0x0f0f0f0fu), xe[2], d);
+            d = __dp4a((int)(w.w & 0x0f0f0f0fu), xe[3], d);
+            d = __dp4a((int)((w.x >> 4) & 0x0f0f0f0fu), xo[0], d);
+            d = __dp4a((int)((w.y >> 4) & 0x0f0f0f0fu), xo[1], d);
+            d = __dp4a((int)((w.z >> 4) & 0x0f0f0f0fu), xo[2], d);
+            d = __dp4a((int)((w.w >> 4) & 0x0f0f0f0fu), xo[3], d);
+            if (gin && r < O)
+                *reinterpret_cast<float2 *>(out0 + ((size_t)(r >> 5) * nb2 * 32 + (r & 31)) * 4) = make_float2((float)d, ccur[u]);
+        }
+    };
+    while (row < O) {
+        consume(wA, cA, wB, cB);
+        if (row >= O) break;
+        consume(wB, cB, wA, cA);
+    }
+}
+
 // ---- phase 2: one warp per CTA, a band of 32 rows, lane = row (hw/hw_q4r4.h:58-59) ----
 constexpr int G2_PIECE = 16;                      // group pairs per bulk copy: 8 KB
 constexpr unsigned G2_WAIT_LIMIT = 1u << 26;
@@ -253,6 +331,7 @@ __global__ void __launch_bounds__(32) q4r4_g2_chain_kernel(Q4G2Args a) {
         const float4 f = ab_s[(size_t)nfull * 32 + lane];
         acc = fmaf(f.x, f.y, acc);
     }
+    if (a.sx) acc = __fmul_rn(*a.sx, acc);                              // WF_I4G: sx * dot (nn/matmul.c:157)
     if (band * 32 + lane < O) a.y[band * 32 + lane] = acc;
 }
 
@@ -270,6 +349,33 @@ bool q4r4_gemv2_supported(int I, int O, int q8, int sms) {
     return nbands < sms * 6 && (long long)((O + 3) / 4) * (I / 32) >= 400000;
 }
 
+// WF_I4G through the two phases: xi/sx are the row quantized by qrow_i8 (same stream, just before)
+int launch_i4g_gemv2(const uint8_t *w4, const float *gscale, const int8_t *xi, const float *sx, float *y, float *ab,
+                     int *err, int I, int O, int sms, cudaStream_t st) {
+    if (I % 32 != 0 || I <= 0 || I > MOTY_QROW_MAX || O <= 0) return moty_set_error(MOTY_CUDA_EARG, "i4g_gemv2: I=%d O=%d", I, O);
+    Q4G2Args a; memset(&a, 0, sizeof a);
+    a.w = w4; a.gscale = gscale; a.xi = xi; a.sx = sx; a.y = y; a.ab = ab; a.err = err; a.I = I; a.O = O;
+    const int nb = I / 32, nslab = (nb + 31) / 32;
+    int cps = sms * 2 / nslab;
+    if (cps < 1) cps = 1;
+    if (cps > (O + 8 * G2I_R - 1) / (8 * G2I_R)) cps = (O + 8 * G2I_R - 1) / (8 * G2I_R);
+    a.cps = cps;
+    const int nb2 = (nb + 1) / 2;
+    const size_t smem2 = (size_t)nb2 * 512 + (size_t)((nb2 + G2_PIECE - 1) / G2_PIECE) * 8;
+    static bool attr_set[MOTY_MAX_DEV];
+    int dev = 0;
+    CK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "i4g_gemv2: device %d", dev);
+    if (!attr_set[dev]) {
+        CK(cudaFuncSetAttribute(q4r4_g2_chain_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                MOTY_QROW_MAX / 64 * 512 + 16 * 8));
+        attr_set[dev] = true;
+    }
+    CK(moty_launch_pdl(i4g_g2_sums_kernel, dim3((unsigned)(cps * nslab)), dim3(256), (size_t)0, st, a));
+    CK(moty_launch_pdl(q4r4_g2_chain_kernel, dim3((unsigned)((O + 31) / 32)), dim3(32), smem2, st, a));
+    return 0;
+}
+
 size_t q4r4_gemv2_scratch_bytes(int I, int O) { return (size_t)((O + 31) / 32) * ((I / 32 + 1) / 2) * 32 * 16; }
 
 // x: 16-byte aligned; ab: q4r4_gemv2_scratch_bytes(I, O), 128-byte aligned; err: set when a bounded wait expired;
@@ -277,7 +383,8 @@ size_t q4r4_gemv2_scratch_bytes(int I, int O) { return (size_t)((O + 31) / 32) *
 int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float *y, float *ab, int *err,
                       int I, int O, int q8, int sms, cudaStream_t st) {
     if (!q4r4_gemv2_supported(I, O, q8, sms)) return moty_set_error(MOTY_CUDA_EARG, "q4r4_gemv2: I=%d O=%d", I, O);
-    Q4G2Args a; a.w = w; a.d = d; a.x = x; a.y = y; a.ab = ab; a.err = err; a.I = I; a.O = O;
+    Q4G2Args a; memset(&a, 0, sizeof a);
+    a.w = w; a.d = d; a.x = x; a.y = y; a.ab = ab; a.err = err; a.I = I; a.O = O;
     const int nb = I / 32, slab = q8 ? 16 : 32, nslab = (nb + slab - 1) / slab, nblk = (O + 3) / 4;
     int cps = sms * 2 / nslab;
     if (cps < 1) cps = 1;

@@ -141,6 +141,20 @@ class Oracle:
         self.lib.oracle_matmul_i4_idot_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
         return y
 
+    def pack_int4_grouped(self, w, gs=32):
+        w = _f32(w); O, I = w.shape
+        q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty((O, (I + gs - 1) // gs), np.float32)
+        self.lib.oracle_pack_int4_grouped(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I), C.c_int(gs))
+        return q4, s
+
+    def matmul_i4g_idot_s(self, x, q4, scale):
+        """WF_I4G, group 32, integer path (IDOT4=1): x [S][I], q4 [O][I/2], scale [O][I/32]."""
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); scale = _f32(scale)
+        S, I = x.shape; O = scale.shape[0]
+        y = np.empty((S, O), np.float32)
+        self.lib.oracle_matmul_i4g_idot_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
     def matmul_q4r4_s(self, x, q4, s16, O):
         x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); s16 = np.ascontiguousarray(s16, np.uint16)
         S, I = x.shape
@@ -309,6 +323,7 @@ class Ref:
             raise RuntimeError("reference library not built (oracle/_ref is empty)")
         self.tier = "native" if p.endswith("native.so") else "x86-64-v3"
         os.environ.setdefault("MOTY_NO_OMP_TUNE", "1")
+        os.environ.setdefault("IDOT4", "1")      # the int4 drivers read it once, on their first call
         self.lib = C.CDLL(p)
         L = self.lib
         L.moty_hw_qrow_i8.restype = C.c_float
@@ -381,6 +396,25 @@ class Ref:
         q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty(O, np.float32)
         self.lib.moty_pack_int4(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I))
         return q4, s
+
+    def pack_int4_grouped(self, w, gs=32):
+        w = _f32(w); O, I = w.shape
+        q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty((O, (I + gs - 1) // gs), np.float32)
+        self.lib.moty_pack_int4_grouped(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I), C.c_int(gs))
+        return q4, s
+
+    def has_i4g_idot(self):
+        """The reference takes the integer path of WF_I4G only in builds with AVX512-VNNI (nn/matmul.c:168)."""
+        return self.tier == "native" and _cpu_has("avx512_vnni")
+
+    def matmul_i4g_idot_s(self, x, q4, scale):
+        """moty_matmul_i4_grouped_s with IDOT4=1 (set before the library is loaded), gs = 32, I % 64 == 0."""
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); scale = _f32(scale)
+        S, I = x.shape; O = scale.shape[0]
+        assert I % 64 == 0 and self.has_i4g_idot()
+        y = np.empty((S, O), np.float32)
+        self.lib.moty_matmul_i4_grouped_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O), C.c_int(32))
+        return y
 
     def pack_q4r4(self, w):
         w = _f32(w); O, I = w.shape

@@ -165,6 +165,72 @@ ORACLE_API void oracle_matmul_i4_idot_s(float *y, const float *x, const uint8_t 
     free(xi); free(sx);
 }
 
+/* nn/quant.c:57-83 -- grouped int4 (WF_I4G): per row and group of gs weights the
+ * scale is amax/7 floored at 1e-8, code = clamp(lrintf(w/s), -8, 7) + 8, the even
+ * element in the low nibble.  Row o: (I+1)/2 bytes, scales [O][ceil(I/gs)] f32. */
+ORACLE_API void oracle_pack_int4_grouped(const float *w, uint8_t *q4, float *scale, int O, int I, int gs) {
+    int rb = (I + 1) / 2, ng = (I + gs - 1) / gs;
+    for (int o = 0; o < O; o++) {
+        const float *wr = w + (size_t)o * I;
+        for (int g = 0; g * gs < I; g++) {
+            int base = g * gs, glen = gs;
+            if (base + glen > I) glen = I - base;
+            float amax = 0.f;
+            for (int i = base; i < base + glen; i++) { float a = fabsf(wr[i]); if (a > amax) amax = a; }
+            float sc = amax / 7.f;
+            if (sc < 1e-8f) sc = 1e-8f;
+            scale[(size_t)o * ng + g] = sc;
+            for (int i = base; i < base + glen; i += 2) {
+                int v0 = (int)lrintf(wr[i] / sc), v1 = 0;
+                if (v0 > 7) v0 = 7;
+                if (v0 < -8) v0 = -8;
+                if (i + 1 < base + glen) {
+                    v1 = (int)lrintf(wr[i + 1] / sc);
+                    if (v1 > 7) v1 = 7;
+                    if (v1 < -8) v1 = -8;
+                }
+                q4[(size_t)o * rb + (i >> 1)] = (uint8_t)((v0 + 8) | ((v1 + 8) << 4));
+            }
+        }
+    }
+}
+
+/* nn/matmul.c:164-197 with IDOT4=1 and gs = 32 (the integer path of WF_I4G): the
+ * activation row is quantized per ROW (qrow_i8); per group the integer sum of
+ * (nibble - 8) * x is exact (hw/hw_quant.h:35-50; the AVX512-VNNI kernel
+ * hw/hw_avx512.h:155-176 computes the same integers as sum(nibble * x) - 8 * xgsum);
+ * one f32 term per group is added in ascending group order, acc += scl[g] * (float)d,
+ * which the reference's builds contract into a fused multiply-add (gcc -O2 keeps
+ * -ffp-contract=fast and both of its x86 tiers have FMA); the result is sx * acc. */
+ORACLE_API void oracle_matmul_i4g_idot_s(float *y, const float *x, const uint8_t *q4, const float *scale,
+                                         int S, int I, int O) {
+    int8_t *xi = (int8_t *)malloc((size_t)S * I + 1);
+    float *sx = (float *)malloc(sizeof(float) * (S ? S : 1));
+    int rb = (I + 1) / 2, ng = I / 32;
+    for (int s = 0; s < S; s++) sx[s] = oracle_qrow_i8(x + (size_t)s * I, xi + (size_t)s * I, I);
+    #pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++) {
+        const uint8_t *w4 = q4 + (size_t)o * rb;
+        const float *scl = scale + (size_t)o * ng;
+        for (int s = 0; s < S; s++) {
+            const int8_t *xr = xi + (size_t)s * I;
+            float acc = 0.f;
+            for (int g = 0; g < ng; g++) {
+                int32_t d = 0;
+                for (int j = 0; j < 32; j++) {
+                    int e = g * 32 + j;
+                    uint8_t b = w4[e >> 1];
+                    int v = (e & 1) ? (b >> 4) : (b & 0xF);
+                    d += (v - 8) * xr[e];
+                }
+                acc = fmaf(scl[g], (float)d, acc);
+            }
+            y[(size_t)s * O + o] = sx[s] * acc;
+        }
+    }
+    free(xi); free(sx);
+}
+
 /* ------------------------------------------------------------------ */
 /* Q4R4: 4-row blocks, groups of 32, f16 scale stream                  */
 /* ------------------------------------------------------------------ */

@@ -144,6 +144,25 @@ def main():
             d[f"x_{tag}_{S}"] = x
             d[f"y_{tag}_{S}"] = r.matmul_q8r4_s(x, q8, s16, O)
     save("matmul_q8r4", **d)
+
+    # ---- WF_I4G, grouped int4 (group 32), integer path (IDOT4=1): needs the reference's AVX512-VNNI tier
+    if r.has_i4g_idot():
+        rg = np.random.default_rng(20260812)
+        d = {}
+        for tag, (O, I) in {"a": (37, 128), "b": (40, 1792)}.items():
+            Wf = (rg.standard_normal((O, I)) * 0.02).astype(np.float32)
+            Wf[0, :32] = 0                                # an all-zero group: floor scale, codes 8
+            q4, sc = r.pack_int4_grouped(Wf)
+            d.update({f"q4_{tag}": q4, f"scale_{tag}": sc})
+            if tag == "a":
+                d["Wf_a"] = Wf                            # pins the packer too
+            for S in (1, 2, 5, 9):
+                x = rg.standard_normal((S, I)).astype(np.float32)
+                d[f"x_{tag}_{S}"] = x
+                d[f"y_{tag}_{S}"] = r.matmul_i4g_idot_s(x, q4, sc)
+        save("matmul_i4g", **d)
+    else:
+        print("WF_I4G vectors not regenerated: the reference build here has no AVX512-VNNI tier")
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 

@@ -97,6 +97,28 @@ def test_route_topk_indices_match_cpu(gpu, oracle):
         assert np.array_equal(idx, io), f"{(idx != io).any(axis=1).sum()} rows differ at sd={sd}"
 
 
+@pytest.mark.parametrize("fmt", ["q8_0", "q4r4"])
+@pytest.mark.parametrize("S", [1, 3])
+def test_head_argmax(gpu, oracle, fmt, S):
+    """lm_head + greedy pick in one call equals the reference's mat_apply followed by moty_argmax_v
+    (nn/head.c:134-135, nn/sample.c:9-13): same ids, same logits; ties resolve to the first index."""
+    rng = np.random.default_rng(S + len(fmt))
+    V, D = 50304, 1024
+    x = rng.standard_normal((S, D)).astype(np.float32)
+    if fmt == "q8_0":
+        Wq = rng.integers(-127, 128, (V, D), dtype=np.int8); sc = rng.uniform(0.001, 0.02, V).astype(np.float32)
+        Wq[4000] = Wq[77]; sc[4000] = sc[77]            # two identical rows: equal logits
+        W = gpu.Mat.i8(Wq, sc); lo = oracle.matmul_q_s(x, Wq, sc)
+    else:
+        Wf = (rng.standard_normal((V, D)) * 0.02).astype(np.float32)
+        q4, s16 = oracle.pack_q4r4(Wf)
+        W = gpu.Mat.q4r4(q4, s16, V, D); lo = oracle.matmul_q4r4_s(x, q4, s16, V)
+    ids, lg = gpu.head_argmax(W, x, want_logits=True)
+    assert same_bits(lg, lo)
+    assert [int(i) for i in ids] == [oracle.argmax(lo[s]) for s in range(S)]
+    assert np.array_equal(gpu.head_argmax(W, x), ids)
+
+
 def test_argmax(gpu, oracle):
     g = golden("router")
     assert gpu.argmax(g["argmax_v"]) == int(g["argmax_i"])

@@ -178,6 +178,36 @@ def test_i4_rows(gpu, oracle):
         assert same_bits(gpu.mat_apply(W, x), oracle.matmul_i4_idot_s(x, q4, sc, I))
 
 
+@pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1022, 3072), (515, 3840), (258, 15360), (77, 16384), (5, 32), (300, 96)])
+@pytest.mark.parametrize("S", [1, 2, 3, 4, 7, 8, 19])
+def test_i4g_vs_oracle(gpu, oracle, O, I, S):
+    """WF_I4G (grouped int4, group 32, f32 group scales), integer path: ragged rows and token tiles, the longest row."""
+    rng = np.random.default_rng(O * 11 + I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, sc = oracle.pack_int4_grouped(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.i4g(q4, sc, O, I), x)
+    yo = oracle.matmul_i4g_idot_s(x, q4, sc)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+
+
+def test_i4g_golden_and_extremes(gpu, oracle):
+    g = golden("matmul_i4g")
+    for tag in ("a", "b"):
+        q4, sc = g[f"q4_{tag}"], g[f"scale_{tag}"]
+        O, I = q4.shape[0], q4.shape[1] * 2
+        W = gpu.Mat.i4g(q4, sc, O, I)
+        for S in (1, 2, 5, 9):
+            assert same_bits(gpu.mat_apply(W, g[f"x_{tag}_{S}"]), g[f"y_{tag}_{S}"])
+        assert same_bits(gpu.matmul_i4_grouped_s(g[f"x_{tag}_5"], q4, sc, O), g[f"y_{tag}_5"])
+    # every code at an extreme, saturating activations, a zero row
+    O, I = 64, 2048
+    for fill in (0x00, 0xFF):
+        q4 = np.full((O, I // 2), fill, np.uint8); sc = np.full((O, I // 32), 0.37, np.float32)
+        x = np.zeros((3, I), np.float32); x[0] = 1000.0; x[1, ::2] = -3.0; x[1, 1::2] = 3.0
+        assert same_bits(gpu.mat_apply(gpu.Mat.i4g(q4, sc, O, I), x), oracle.matmul_i4g_idot_s(x, q4, sc))
+
+
 def test_host_weight_entries(gpu, oracle):
     g = golden("matmul_a")
     assert same_bits(gpu.matmul_q_s(g["x5"], g["W8"], g["sc"]), g["y8_5"])

@@ -65,6 +65,17 @@ def test_q8r4_drivers(oracle):
             assert same_bits(oracle.matmul_q8r4_s(g[f"x_{tag}_{S}"], q8, s16, O), g[f"y_{tag}_{S}"])
 
 
+def test_i4g_drivers(oracle):
+    """WF_I4G (grouped int4, group 32): packer and the integer path of the product against vectors from the
+    reference's AVX512-VNNI build (nn/quant.c:57-83, nn/matmul.c:164-197 with IDOT4=1)."""
+    g = golden("matmul_i4g")
+    q4, sc = oracle.pack_int4_grouped(g["Wf_a"])
+    assert same_bits(q4, g["q4_a"]) and same_bits(sc, g["scale_a"])
+    for tag in ("a", "b"):
+        for S in (1, 2, 5, 9):
+            assert same_bits(oracle.matmul_i4g_idot_s(g[f"x_{tag}_{S}"], g[f"q4_{tag}"], g[f"scale_{tag}"]), g[f"y_{tag}_{S}"])
+
+
 def test_q4r4_batch_is_not_row_invariant(oracle):
     """The reference folds the -8 offset differently for tokens inside a complete
     group of 4 (nn/matmul.c:397-402): a batch is NOT always bitwise equal to its
@@ -141,5 +152,11 @@ def test_oracle_equals_reference_build(oracle, ref):
         assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
         assert same_bits(oracle.matmul_q8r4_s(x, a[0], a[1], O), ref.matmul_q8r4_s(x, a[0], a[1], O))
     lg = (rng.standard_normal((500, 128)) * 0.05).astype(np.float32)
+    Wg = (rng.standard_normal((50, 1024)) * 0.02).astype(np.float32)
+    a, b = oracle.pack_int4_grouped(Wg), ref.pack_int4_grouped(Wg)
+    assert same_bits(a[0], b[0]) and same_bits(a[1], b[1])
+    if ref.has_i4g_idot():                              # the reference takes the integer path only with AVX512-VNNI
+        xg = rng.standard_normal((5, 1024)).astype(np.float32)
+        assert same_bits(oracle.matmul_i4g_idot_s(xg, a[0], a[1]), ref.matmul_i4g_idot_s(xg, a[0], a[1]))
     a, b = oracle.route_topk(lg, 8), ref.route_topk(lg, 8)
     assert all(same_bits(u, v) for u, v in zip(a, b))
