@@ -533,6 +533,8 @@ def run_case(args):
         run_ep_case(args, parts[1], int(parts[2]))
         return
     mb.init([0])
+    if args.fast_path >= 0:
+        mb.lib().moty_cuda_set_moe_fast_path(args.fast_path)
     dev = torch.device("cuda:0")
     rng = np.random.default_rng(3)
     if parts[0] == "moe":                                      # moe:NAME:S -- layer calls of a routed layer, two weight sets
@@ -542,6 +544,24 @@ def run_case(args):
         with torch.cuda.stream(stream):
             us = time_moe(torch, layers, name, S, dev, stream, reps=max(1, args.steps // 16), run=16)
         print(json.dumps({"case": args.case, "us_per_layer": round(us, 2)}), flush=True)
+        return
+    if parts[0] == "ffn":                               # ffn:S:D:I -- one dense int8 SiLU FFN block (gate/up [I][D], down [D][I])
+        S, D, I = int(parts[1]), int(parts[2]), int(parts[3])
+        mk = lambda O, K: mb.Mat.i8(rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
+        G, U, Dn = mk(I, D), mk(I, D), mk(D, I)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            x = torch.randn((S, D), device=dev); y = torch.empty((S, D), device=dev)
+            for _ in range(max(args.warmup, 1)):
+                mb.dense_ffn_dev(G, U, Dn, y.data_ptr(), x.data_ptr(), S, stream=stream.cuda_stream)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                mb.dense_ffn_dev(G, U, Dn, y.data_ptr(), x.data_ptr(), S, stream=stream.cuda_stream)
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        print(json.dumps({"case": args.case, "us_per_block": round(us, 2), "GBs": round(3.0 * I * D / us / 1e3, 1)}), flush=True)
         return
     fmt, S, O, I = parts
     S, O, I = int(S), int(O), int(I)
@@ -584,10 +604,12 @@ def main():
     ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
+    ap.add_argument("--fast-path", type=int, default=-1, help="profiling aid for --case: 0/1/2 passed to moty_cuda_set_moe_fast_path "
+                                                            "(0 = step-by-step FFN and general MoE path, 1 = one-launch decode kernels)")
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; ep:NAME:S under torchrun times the "
+                                                "times calls of one routed layer; ffn:S:D:I one dense int8 SiLU FFN block; ep:NAME:S under torchrun times the "
                                                 "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:

@@ -123,7 +123,7 @@ extern "C" void moty_cuda_shutdown(void) {
         cudaSetDevice(c->dev);
         cudaStreamSynchronize(c->stream);
         Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
-                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec, &c->mmak};
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec, &c->mmak, &c->ffn1};
         for (Buf *b : bs) free_buf(b);
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
@@ -720,6 +720,8 @@ extern "C" int moty_cuda_pack_q4r4(const float *w, int O, int I, uint8_t *q4, ui
 // ---------------------------------------------------------------------------
 // dense FFN
 // ---------------------------------------------------------------------------
+static int g_moe_fast = 1;      // 1: one-launch decode kernels; 2: the split decode path; 0: general path only
+
 static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
                   float *out, const float *x, int S, cudaStream_t st) {
     int I = gate->O, D = gate->I;
@@ -729,6 +731,19 @@ static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
     if (act != MOTY_ACT_SILU && act != MOTY_ACT_GELU_TANH) return moty_set_error(MOTY_CUDA_EARG, "ffn: activation %d", act);
     size_t hb = (size_t)S * I * 4;
     CKR(moty_grow(c, &c->g, hb));
+    // Decode with int8 matrices and SiLU: the block is the MoE decode block with one expert of weight 1 (softmax of a
+    // single logit is exp(0)/exp(0) = 1 and 1 * h = h exactly), so the one-launch kernel takes it: gate/up rows, a
+    // grid barrier, the down rows -- same quantizers, same (scale * sx) * acc, same SiLU expression as the steps below.
+    if (S == 1 && act == MOTY_ACT_SILU && g_moe_fast == 1 && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 &&
+        down->fmt == MOTY_WF_I8 && moe_decode_fused_q8_supported(1, 1, I, D) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        CKR(moty_grow_zero(c, &c->ffn1, 64));               // [0] the single logit (0), [4] index out, [8] weight out
+        char *z = (char *)c->ffn1.p;
+        return launch_moe_decode_fused_q8((const float *)z, 1, 0, (int *)(z + 16), (float *)(z + 32),
+                                          (const int8_t *)gate->codes, (const int8_t *)up->codes, (const int8_t *)down->codes,
+                                          (const float *)gate->scales, (const float *)up->scales, (const float *)down->scales,
+                                          0, 0, 0, 0, x, (float *)c->g.p, out, 1, I, D, 0, 1,
+                                          reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st);
+    }
     CKR(moty_grow(c, &c->u, hb));
     CKR(mat_apply_on(c, gate, (float *)c->g.p, x, S, nullptr, st));
     CKR(mat_apply_on(c, up, (float *)c->u.p, x, S, nullptr, st));
@@ -759,7 +774,14 @@ extern "C" int moty_cuda_ffn(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
     CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
     CKR(ffn_on(c, gate, up, down, act, (float *)c->dy.p, (const float *)c->dx.p, S, c->stream));
     CK(cudaMemcpyAsync(out, c->dy.p, xb, cudaMemcpyDeviceToHost, c->stream));
+    int kerr = 0;
+    if (S == 1) CK(cudaMemcpyAsync(&kerr, c->err_dev + 1, 4, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
+    if (kerr) {
+        cudaMemsetAsync(c->err_dev + 1, 0, 4, c->stream);
+        cudaMemsetAsync(reinterpret_cast<unsigned *>(c->ctr) + 4, 0, 8, c->stream);
+        return moty_set_error(MOTY_CUDA_EKERNEL, "fused FFN decode gave up on its grid barrier (result incomplete)");
+    }
     return 0;
 }
 
@@ -884,7 +906,6 @@ static int moe_ensure_plan(MotyCudaMoe *m, int S) {
 
 // 0: generic tile path; 1: best decode path (one fused launch where supported); 2: the split
 // decode path (router, gate/up and down as separate launches)
-static int g_moe_fast = 1;
 
 extern "C" int moty_cuda_set_moe_fast_path(int on) {
     int prev = g_moe_fast;

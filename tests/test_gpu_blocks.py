@@ -32,6 +32,26 @@ def test_ffn_q8_and_q4r4(gpu, oracle):
         assert close(y, oracle.matmul_q_s(h, g["dq"], g["ds"]), 2e-3)
 
 
+@pytest.mark.parametrize("D,I", [(1024, 3072), (2048, 4096), (1008, 2064), (64, 48)])
+def test_ffn_decode_one_launch_equals_steps(gpu, oracle, D, I):
+    """One token, int8 matrices, SiLU: the block runs as a one-expert MoE decode block in a single launch.  Its output
+    equals the step-by-step path (gate, up, activation, down) bit for bit, and the oracle within the tolerance of exp."""
+    rng = np.random.default_rng(D + I)
+    mk = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32))
+    (gq, gs), (uq, us), (dq, ds) = mk(I, D), mk(I, D), mk(D, I)
+    G, U, Dn = gpu.Mat.i8(gq, gs), gpu.Mat.i8(uq, us), gpu.Mat.i8(dq, ds)
+    for _ in range(2):                                  # twice: the grid barrier's words have to be back at zero
+        x = rng.standard_normal((1, D)).astype(np.float32)
+        prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
+        y1 = gpu.dense_ffn(G, U, Dn, x)
+        gpu.lib().moty_cuda_set_moe_fast_path(0)
+        y0 = gpu.dense_ffn(G, U, Dn, x)
+        gpu.lib().moty_cuda_set_moe_fast_path(prev)
+        assert same_bits(y1, y0)
+        h = oracle.silu_mul(oracle.matmul_q_s(x, gq, gs), oracle.matmul_q_s(x, uq, us))
+        assert close(y1, oracle.matmul_q_s(h, dq, ds), 2e-3)
+
+
 def _moe_from_golden(gpu, g):
     E, K, I, D = (int(v) for v in g["moe_dims"])
     m = gpu.Moe(E, K, I, D)
