@@ -240,6 +240,26 @@ int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream);
 int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, int *ids, float *logits);
 int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, int S, int *ids_dev, float *logits_dev, void *stream);
 
+/* ---- attention core between the projections --------------------------------
+ * attn_tail of nn/attn.c:29-74 without the q/k/v/o projections (those are mat_apply calls) and
+ * without the optional output gate: QK-norm (moty_rmsnorm_row per head with qn / kn [head_dim],
+ * NULL = none) and RoPE (moty_rope_head: half-split over the first `rot` dimensions, base theta),
+ * K and V rows stored at positions pos_base .. pos_base+S-1 of the layer's cache (f32, or with
+ * kv8 != 0 int8 rows with one qrow_i8 scale per head and position, moty_kv_store_row), then per
+ * head and token the scores against positions 0..pos, softmax and accumulation
+ * (moty_att_scores_* / moty_softmax_row / moty_att_accum_*).  One MotyCudaAttn per layer holds the
+ * KV cache of max_t positions on the device (MotyCommon's K/V or K8/V8/Ks/Vs of that layer).
+ * q [S][H*hd], k, v [S][KV*hd] -> ctx [S][H*hd].  f32 arithmetic with libm calls whose summation
+ * order already differs between the reference's CPU tiers: results agree to a few 1e-6, not bit
+ * for bit.  The _dev entry norms and rotates q_dev and k_dev in place, as the reference does. */
+typedef struct MotyCudaAttn MotyCudaAttn;
+int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_heads, int head_dim, int rot, float theta,
+                          float eps, const float *qn, const float *kn, int max_t, int kv8, int device);
+int moty_cuda_attn_free(MotyCudaAttn *a);
+int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S, int pos_base);
+int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
+                            int S, int pos_base, void *stream);
+
 /* ---- load-time quantizers (weights) -----------------------------------------
  * moty_quantize_rows (nn/quant.c:12-33) with bits = 8: w [O][I] f32 host ->
  * q [O][I] int8, scale [O] f32 host, computed on the GPU. */

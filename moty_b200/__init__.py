@@ -312,6 +312,40 @@ def head_argmax(head: "Mat", x, want_logits=False):
     return (ids, lg) if want_logits else ids
 
 
+class Attn:
+    """The attention core of one layer with its KV cache on a GPU (nn/attn.c:29-74 without the projections):
+    ``core(q, k, v, pos_base)`` norms and rotates q and k, stores k and v at their positions and returns ctx."""
+
+    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False, device=0):
+        self.H, self.KV, self.hd, self.max_t = H, KV, hd, max_t
+        h = C.c_void_p()
+        qn = None if qn is None else _f32(qn); kn = None if kn is None else _f32(kn)
+        _ck(lib().moty_cuda_attn_create(C.byref(h), H, KV, hd, hd if rot is None else rot, C.c_float(theta), C.c_float(eps),
+                                        _p(qn) if qn is not None else None, _p(kn) if kn is not None else None,
+                                        max_t, 1 if kv8 else 0, device))
+        self.h = h
+
+    def core(self, q, k, v, pos_base):
+        q = _f32(q); k = _f32(k); v = _f32(v); S = q.shape[0]
+        ctx = np.empty((S, self.H * self.hd), np.float32)
+        _ck(lib().moty_cuda_attn_core(self.h, _p(ctx), _p(q), _p(k), _p(v), S, pos_base))
+        return ctx
+
+    def core_dev(self, ctx_ptr, q_ptr, k_ptr, v_ptr, S, pos_base, stream=0):
+        _ck(lib().moty_cuda_attn_core_dev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
+                                          S, pos_base, C.c_void_p(stream)))
+
+    def close(self):
+        if self.h:
+            lib().moty_cuda_attn_free(self.h); self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
 def quantize_rows(w):
     """moty_quantize_rows (bits=8) computed on the GPU."""
     w = _f32(w); O, I = w.shape

@@ -684,6 +684,104 @@ extern "C" int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, i
 }
 
 // ---------------------------------------------------------------------------
+// attention core of one layer (KV cache resident on the device)
+// ---------------------------------------------------------------------------
+struct MotyCudaAttn {
+    int H, KV, hd, rot, max_t, kv8, device;
+    float theta, eps;
+    float *qn, *kn;
+    float *K, *V; int8_t *K8, *V8; float *Ks, *Vs;
+};
+
+extern "C" int moty_cuda_attn_free(MotyCudaAttn *a) {
+    if (!a) return 0;
+    DevCtx *c = moty_ctx(a->device);
+    if (c) { cudaSetDevice(a->device); cudaStreamSynchronize(c->stream); }
+    void *ps[] = {a->qn, a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs};
+    for (void *p : ps) if (p) cudaFree(p);
+    delete a;
+    return 0;
+}
+
+extern "C" int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_heads, int head_dim, int rot, float theta,
+                                     float eps, const float *qn, const float *kn, int max_t, int kv8, int device) {
+    if (!out) return moty_set_error(MOTY_CUDA_EARG, "attn_create: null argument");
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || head_dim > 256 || rot < 0 ||
+        rot > head_dim || (rot & 1) || max_t <= 0)
+        return moty_set_error(MOTY_CUDA_EARG, "attn_create: H=%d KV=%d hd=%d rot=%d max_t=%d", n_heads, n_kv_heads, head_dim, rot, max_t);
+    CK(cudaSetDevice(device));
+    MotyCudaAttn *a = new (std::nothrow) MotyCudaAttn();
+    if (!a) return moty_set_error(MOTY_CUDA_ENOMEM, "attn_create: host allocation");
+    memset(a, 0, sizeof *a);
+    a->H = n_heads; a->KV = n_kv_heads; a->hd = head_dim; a->rot = rot; a->max_t = max_t; a->kv8 = kv8 ? 1 : 0;
+    a->device = device; a->theta = theta; a->eps = eps;
+    const size_t rows = (size_t)n_kv_heads * max_t;
+    cudaError_t e = cudaSuccess;
+    if (qn) e = cudaMalloc(&a->qn, (size_t)head_dim * 4);
+    if (e == cudaSuccess && kn) e = cudaMalloc(&a->kn, (size_t)head_dim * 4);
+    if (e == cudaSuccess && a->kv8) {
+        e = cudaMalloc(&a->K8, rows * head_dim);
+        if (e == cudaSuccess) e = cudaMalloc(&a->V8, rows * head_dim);
+        if (e == cudaSuccess) e = cudaMalloc(&a->Ks, rows * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&a->Vs, rows * 4);
+    } else if (e == cudaSuccess) {
+        e = cudaMalloc(&a->K, rows * head_dim * 4);
+        if (e == cudaSuccess) e = cudaMalloc(&a->V, rows * head_dim * 4);
+    }
+    // positions never written read as zero rows (score 0, value 0), the same on every run
+    if (e == cudaSuccess && a->kv8) {
+        e = cudaMemsetAsync(a->K8, 0, rows * head_dim, c->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(a->V8, 0, rows * head_dim, c->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(a->Ks, 0, rows * 4, c->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(a->Vs, 0, rows * 4, c->stream);
+    } else if (e == cudaSuccess) {
+        e = cudaMemsetAsync(a->K, 0, rows * head_dim * 4, c->stream);
+        if (e == cudaSuccess) e = cudaMemsetAsync(a->V, 0, rows * head_dim * 4, c->stream);
+    }
+    if (e == cudaSuccess && qn) e = cudaMemcpyAsync(a->qn, qn, (size_t)head_dim * 4, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess && kn) e = cudaMemcpyAsync(a->kn, kn, (size_t)head_dim * 4, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    if (e != cudaSuccess) {
+        moty_cuda_attn_free(a);
+        return moty_set_error(MOTY_CUDA_ENOMEM, "attn_create: %s", cudaGetErrorString(e));
+    }
+    *out = a;
+    return 0;
+}
+
+extern "C" int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
+                                       int S, int pos_base, void *stream) {
+    if (!a || !ctx_dev || !q_dev || !k_dev || !v_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_core_dev: null argument");
+    DevCtx *c = moty_ctx(a->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
+    CK(cudaSetDevice(a->device));
+    return launch_attn_core(ctx_dev, q_dev, k_dev, v_dev, S, pos_base, a->H, a->KV, a->hd, a->rot, a->theta, a->eps, a->qn,
+                            a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S,
+                                   int pos_base) {
+    if (!a || !ctx || !q || !k || !v) return moty_set_error(MOTY_CUDA_EARG, "attn_core: null argument");
+    if (S <= 0) return 0;
+    DevCtx *c = moty_ctx(a->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
+    CK(cudaSetDevice(a->device));
+    const size_t qb = (size_t)S * a->H * a->hd * 4, kb = (size_t)S * a->KV * a->hd * 4;
+    CKR(moty_grow(c, &c->dx, qb + 2 * kb));
+    CKR(moty_grow(c, &c->dy, qb));
+    float *dq = (float *)c->dx.p, *dk = (float *)((char *)c->dx.p + qb), *dv = (float *)((char *)c->dx.p + qb + kb);
+    CK(cudaMemcpyAsync(dq, q, qb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(dk, k, kb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(dv, v, kb, cudaMemcpyHostToDevice, c->stream));
+    CKR(moty_cuda_attn_core_dev(a, (float *)c->dy.p, dq, dk, dv, S, pos_base, c->stream));
+    CK(cudaMemcpyAsync(ctx, c->dy.p, qb, cudaMemcpyDeviceToHost, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
+// ---------------------------------------------------------------------------
 // load-time quantizers
 // ---------------------------------------------------------------------------
 extern "C" int moty_cuda_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I) {

@@ -65,6 +65,21 @@ class Experts:
         self.c = _ExpertsI8(E, K, I, D, *(a.ctypes.data for a in (self.g, self.u, self.d, self.gs, self.us, self.ds)))
 
 
+class AttnCache:
+    """Host-side KV storage of one layer for the CPU checkers: f32 K, V [KV][max_t][hd], or int8 rows with one scale
+    per (head, position) (K8, V8, Ks, Vs), plus the layer's attention parameters."""
+
+    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False):
+        self.H, self.KV, self.hd, self.max_t = H, KV, hd, max_t
+        self.theta, self.eps, self.rot, self.kv8 = float(theta), float(eps), hd if rot is None else rot, bool(kv8)
+        self.qn = None if qn is None else _f32(qn); self.kn = None if kn is None else _f32(kn)
+        if kv8:
+            self.K8 = np.zeros((KV, max_t, hd), np.int8); self.V8 = np.zeros((KV, max_t, hd), np.int8)
+            self.Ks = np.zeros((KV, max_t), np.float32); self.Vs = np.zeros((KV, max_t), np.float32)
+        else:
+            self.K = np.zeros((KV, max_t, hd), np.float32); self.V = np.zeros((KV, max_t, hd), np.float32)
+
+
 class Oracle:
     """The C restatement.  Shapes follow the reference: x [S][I], y [S][O]."""
 
@@ -140,6 +155,21 @@ class Oracle:
         y = np.empty((S, O), np.float32)
         self.lib.oracle_matmul_i4_idot_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
         return y
+
+    def attn_core(self, q, k, v, pos_base, cache):
+        """nn/attn.c:29-74 without projections: QK-norm + RoPE (q, k are modified in place), KV store into
+        ``cache`` (an AttnCache), scores / softmax / accumulation.  q [S][H*hd], k, v [S][KV*hd] -> ctx [S][H*hd]."""
+        c = cache
+        q = _f32(q); k = _f32(k); v = _f32(v); S = q.shape[0]
+        ctx = np.empty_like(q)
+        null = C.c_void_p(0)
+        self.lib.oracle_attn_core(_p(ctx), _p(q), _p(k), _p(v), C.c_int(S), C.c_int(pos_base), C.c_int(c.H), C.c_int(c.KV),
+                                  C.c_int(c.hd), C.c_float(c.theta), C.c_float(c.eps), C.c_int(c.rot),
+                                  _p(c.qn) if c.qn is not None else null, _p(c.kn) if c.kn is not None else null,
+                                  _p(c.K) if not c.kv8 else null, _p(c.V) if not c.kv8 else null,
+                                  _p(c.K8) if c.kv8 else null, _p(c.V8) if c.kv8 else null,
+                                  _p(c.Ks) if c.kv8 else null, _p(c.Vs) if c.kv8 else null, C.c_int(c.max_t))
+        return ctx
 
     def pack_int4_grouped(self, w, gs=32):
         w = _f32(w); O, I = w.shape
@@ -396,6 +426,52 @@ class Ref:
         q4 = np.empty((O, (I + 1) // 2), np.uint8); s = np.empty(O, np.float32)
         self.lib.moty_pack_int4(_p(w), _p(q4), _p(s), C.c_int(O), C.c_int(I))
         return q4, s
+
+    def attn_core(self, q, k, v, pos_base, cache):
+        """The same steps through the reference's own functions, composed as attn_tail does (nn/attn.c:29-74):
+        moty_rmsnorm_row, moty_rope_head, memcpy / moty_kv_store_row, moty_att_scores_*, moty_softmax_row,
+        moty_att_accum_*."""
+        c = cache; L = self.lib
+        q = _f32(q); k = _f32(k); v = _f32(v); S = q.shape[0]; hd = c.hd; G = c.H // c.KV
+        for s in range(S):
+            for hh in range(c.H):
+                row = q[s, hh * hd:(hh + 1) * hd]
+                if c.qn is not None:
+                    L.moty_rmsnorm_row(_p(row), _p(row), _p(c.qn), C.c_int(hd), C.c_float(c.eps))
+                L.moty_rope_head(_p(row), C.c_int(pos_base + s), C.c_float(c.theta), C.c_int(c.rot))
+            for hh in range(c.KV):
+                row = k[s, hh * hd:(hh + 1) * hd]
+                if c.kn is not None:
+                    L.moty_rmsnorm_row(_p(row), _p(row), _p(c.kn), C.c_int(hd), C.c_float(c.eps))
+                L.moty_rope_head(_p(row), C.c_int(pos_base + s), C.c_float(c.theta), C.c_int(c.rot))
+        for s in range(S):
+            for hh in range(c.KV):
+                t = pos_base + s
+                if c.kv8:
+                    sc = C.c_float(0)
+                    L.moty_kv_store_row(_p(c.K8[hh, t]), C.byref(sc), _p(k[s, hh * hd:(hh + 1) * hd]), C.c_int(hd)); c.Ks[hh, t] = sc.value
+                    L.moty_kv_store_row(_p(c.V8[hh, t]), C.byref(sc), _p(v[s, hh * hd:(hh + 1) * hd]), C.c_int(hd)); c.Vs[hh, t] = sc.value
+                else:
+                    c.K[hh, t] = k[s, hh * hd:(hh + 1) * hd]; c.V[hh, t] = v[s, hh * hd:(hh + 1) * hd]
+        ctx = np.empty_like(q)
+        scale = C.c_float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+        for hh in range(c.H):
+            for s in range(S):
+                qpos = pos_base + s; kvh = hh // G
+                sc = np.empty(qpos + 1, np.float32); cx = np.empty(hd, np.float32)
+                qv = np.ascontiguousarray(q[s, hh * hd:(hh + 1) * hd])
+                base = C.c_int64(kvh * c.max_t)
+                if c.kv8:
+                    L.moty_att_scores_i8(_p(sc), _p(qv), _p(c.K8), _p(c.Ks), base, C.c_int(0), C.c_int(qpos), C.c_int(hd), scale)
+                else:
+                    L.moty_att_scores_f32(_p(sc), _p(qv), _p(c.K), base, C.c_int(0), C.c_int(qpos), C.c_int(hd), scale)
+                L.moty_softmax_row(_p(sc), C.c_int(qpos + 1))
+                if c.kv8:
+                    L.moty_att_accum_i8(_p(cx), _p(sc), _p(c.V8), _p(c.Vs), base, C.c_int(0), C.c_int(qpos), C.c_int(hd))
+                else:
+                    L.moty_att_accum_f32(_p(cx), _p(sc), _p(c.V), base, C.c_int(0), C.c_int(qpos), C.c_int(hd))
+                ctx[s, hh * hd:(hh + 1) * hd] = cx
+        return ctx
 
     def pack_int4_grouped(self, w, gs=32):
         w = _f32(w); O, I = w.shape

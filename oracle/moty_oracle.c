@@ -768,3 +768,108 @@ ORACLE_API void oracle_moe_q4r4(const OracleExpertsQ4 *ex, const float *x, int S
     if (w_out) memcpy(w_out, rw, sizeof(float) * (size_t)S * K);
     free(idx); free(rw); free(tl); free(xsub); free(g); free(u); free(h);
 }
+
+/* ------------------------------------------------------------------ */
+/* Attention core between the projections (nn/attn.c:29-74)            */
+/* ------------------------------------------------------------------ */
+
+/* hw/hw_ops.h:14-18 -- RMS norm of one head: mean of squares in double, then x * r * w. */
+static void attn_rmsnorm(float *out, const float *x, const float *w, int n, float eps) {
+    double ms = 0;
+    for (int i = 0; i < n; i++) ms += (double)x[i] * x[i];
+    float r = 1.f / sqrtf((float)(ms / n) + eps);
+    for (int i = 0; i < n; i++) out[i] = x[i] * r * w[i];
+}
+
+/* nn/rope.c:39-49 -- half-split rotation of the first rot dimensions of a head;
+ * angle = pos / powf(theta, 2i / rot) (the cached table holds the same expression). */
+ORACLE_API void oracle_rope_head(float *x, int pos, float theta, int rot) {
+    for (int i = 0; i < rot / 2; i++) {
+        float angle = pos / powf(theta, (float)(2 * i) / rot);
+        float c = cosf(angle), s = sinf(angle);
+        float a = x[i], b = x[i + rot / 2];
+        x[i] = a * c - b * s;
+        x[i + rot / 2] = a * s + b * c;
+    }
+}
+
+/* nn/attn.c:29-74 (attn_tail without the projections and the optional gate): q [S][H*hd], k, v
+ * [S][KV*hd] are the projected rows of tokens pos_base .. pos_base+S-1.  QK-norm (qn/kn per head
+ * dimension, NULL = none) and RoPE in place; K and V rows go to the cache at their positions --
+ * f32 (K, V: [KV][max_t][hd]) or, when K8 is given, int8 rows with one scale per (head, position)
+ * from qrow_i8 (nn/mat.c:15-17); per (head, token): scores against positions 0..pos
+ * (hw/hw_ops.h:53-55, hw/hw_scalar.h:24-34; int8 keys: Ks * dot * scale, nn/attn_kernels.c:14-17),
+ * softmax (hw/hw_ops.h:22-26), accumulation over positions in order (hw/hw_ops.h:56-59; int8 values:
+ * nn/attn_kernels.c:26-35).  ctx [S][H*hd].  Plain f32 statements, nothing contracted: the
+ * reference's tiers differ in summation order here, parity is by tolerance. */
+ORACLE_API void oracle_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base,
+                                 int H, int KV, int hd, float theta, float eps, int rot,
+                                 const float *qn, const float *kn,
+                                 float *K, float *V, int8_t *K8, int8_t *V8, float *Ks, float *Vs, int max_t) {
+    int G = H / KV;
+    size_t qw = (size_t)H * hd, kw = (size_t)KV * hd;
+    for (int s = 0; s < S; s++) {
+        int pos = pos_base + s;
+        for (int hh = 0; hh < H; hh++) {
+            float *p = q + s * qw + (size_t)hh * hd;
+            if (qn) attn_rmsnorm(p, p, qn, hd, eps);
+            oracle_rope_head(p, pos, theta, rot);
+        }
+        for (int hh = 0; hh < KV; hh++) {
+            float *p = k + s * kw + (size_t)hh * hd;
+            if (kn) attn_rmsnorm(p, p, kn, hd, eps);
+            oracle_rope_head(p, pos, theta, rot);
+        }
+    }
+    for (int s = 0; s < S; s++)
+        for (int hh = 0; hh < KV; hh++) {
+            size_t slot = (size_t)hh * max_t + pos_base + s;
+            if (K8) {
+                Ks[slot] = oracle_qrow_i8(k + s * kw + (size_t)hh * hd, K8 + slot * hd, hd);
+                Vs[slot] = oracle_qrow_i8(v + s * kw + (size_t)hh * hd, V8 + slot * hd, hd);
+            } else {
+                memcpy(K + slot * hd, k + s * kw + (size_t)hh * hd, sizeof(float) * hd);
+                memcpy(V + slot * hd, v + s * kw + (size_t)hh * hd, sizeof(float) * hd);
+            }
+        }
+    float scale = 1.f / sqrtf((float)hd);
+    #pragma omp parallel
+    {
+        float *sc = (float *)malloc(sizeof(float) * (size_t)(pos_base + S + 1));
+        #pragma omp for schedule(static)
+        for (int r = 0; r < H * S; r++) {
+            int hh = r / S, s = r % S, kvh = hh / G, qpos = pos_base + s, n = qpos + 1;
+            const float *qv = q + s * qw + (size_t)hh * hd;
+            size_t base = (size_t)kvh * max_t;
+            for (int t = 0; t < n; t++) {
+                float d = 0.f;
+                if (K8) {
+                    const int8_t *kr = K8 + (base + t) * hd;
+                    for (int i = 0; i < hd; i++) d += qv[i] * (float)kr[i];
+                    sc[t] = Ks[base + t] * d * scale;
+                } else {
+                    const float *kr = K + (base + t) * hd;
+                    for (int i = 0; i < hd; i++) d += qv[i] * kr[i];
+                    sc[t] = d * scale;
+                }
+            }
+            float m = -1e30f, sum = 0.f;
+            for (int t = 0; t < n; t++) if (sc[t] > m) m = sc[t];
+            for (int t = 0; t < n; t++) { sc[t] = expf(sc[t] - m); sum += sc[t]; }
+            for (int t = 0; t < n; t++) sc[t] /= sum;
+            float *cx = ctx + s * qw + (size_t)hh * hd;
+            for (int i = 0; i < hd; i++) cx[i] = 0.f;
+            for (int t = 0; t < n; t++) {
+                if (V8) {
+                    const int8_t *vr = V8 + (base + t) * hd;
+                    float a = sc[t] * Vs[base + t];
+                    for (int i = 0; i < hd; i++) cx[i] += a * (float)vr[i];
+                } else {
+                    const float *vr = V + (base + t) * hd;
+                    for (int i = 0; i < hd; i++) cx[i] += sc[t] * vr[i];
+                }
+            }
+        }
+        free(sc);
+    }
+}

@@ -163,6 +163,30 @@ def main():
         save("matmul_i4g", **d)
     else:
         print("WF_I4G vectors not regenerated: the reference build here has no AVX512-VNNI tier")
+
+    # ---- attention core between the projections (nn/attn.c:29-74), composed from the reference's own functions
+    from oracle import AttnCache
+    ra = np.random.default_rng(20260813)
+    d = {}
+    cases = {"a": dict(H=4, KV=2, hd=64, rot=64, norm=True, kv8=False), "b": dict(H=8, KV=2, hd=128, rot=64, norm=False, kv8=False),
+             "c": dict(H=4, KV=2, hd=64, rot=64, norm=True, kv8=True), "d": dict(H=6, KV=3, hd=96, rot=32, norm=True, kv8=True)}
+    for tag, cf in cases.items():
+        hd = cf["hd"]
+        qn = ra.uniform(0.5, 1.5, hd).astype(np.float32) if cf["norm"] else None
+        kn = ra.uniform(0.5, 1.5, hd).astype(np.float32) if cf["norm"] else None
+        cache = AttnCache(cf["H"], cf["KV"], hd, 16, theta=1e6, eps=1e-6, rot=cf["rot"], qn=qn, kn=kn, kv8=cf["kv8"])
+        d[f"cfg_{tag}"] = np.array([cf["H"], cf["KV"], hd, cf["rot"], int(cf["norm"]), int(cf["kv8"])], np.int32)
+        if cf["norm"]:
+            d[f"qn_{tag}"] = qn; d[f"kn_{tag}"] = kn
+        pos = 0
+        for step, S in enumerate((5, 1, 3)):
+            q = ra.standard_normal((S, cf["H"] * hd)).astype(np.float32)
+            k = ra.standard_normal((S, cf["KV"] * hd)).astype(np.float32)
+            v = ra.standard_normal((S, cf["KV"] * hd)).astype(np.float32)
+            d[f"q_{tag}_{step}"] = q; d[f"k_{tag}_{step}"] = k; d[f"v_{tag}_{step}"] = v
+            d[f"ctx_{tag}_{step}"] = r.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
+            pos += S
+    save("attn", **d)
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 

@@ -52,6 +52,55 @@ def test_ffn_decode_one_launch_equals_steps(gpu, oracle, D, I):
         assert close(y1, oracle.matmul_q_s(h, dq, ds), 2e-3)
 
 
+def test_attn_core_golden(gpu):
+    """Attention core on the GPU against the vectors composed from the reference's functions: three calls per case
+    (a prompt of 5, one decode step, 3 more tokens) on one cache; f32 and int8 KV, QK-norm on and off, partial rotary.
+    f32 sums in another order and libm against CUDA's powf/cosf/sinf/expf: 5e-5 of the output magnitude (2e-3 with
+    the int8 cache, where an ulp before the row quantizer can move a code)."""
+    from test_oracle import _attn_golden_cases
+    g = golden("attn")
+    for tag, _, steps in _attn_golden_cases():
+        H, KV, hd, rot, norm, kv8 = (int(v) for v in g[f"cfg_{tag}"])
+        a = gpu.Attn(H, KV, hd, 16, theta=1e6, eps=1e-6, rot=rot, qn=g[f"qn_{tag}"] if norm else None,
+                     kn=g[f"kn_{tag}"] if norm else None, kv8=bool(kv8))
+        pos = 0
+        for q, k, v, ctx in steps:
+            y = a.core(q, k, v, pos)
+            assert np.abs(y - ctx).max() <= (2e-3 if kv8 else 5e-5) * np.abs(ctx).max(), (tag, pos, float(np.abs(y - ctx).max()))
+            pos += q.shape[0]
+        a.close()
+
+
+@pytest.mark.parametrize("H,KV,hd,rot,kv8", [(16, 8, 128, 128, False), (16, 8, 128, 128, True), (8, 4, 256, 128, False),
+                                              (14, 2, 64, 64, True), (5, 5, 80, 40, False)])
+def test_attn_core_vs_oracle(gpu, oracle, H, KV, hd, rot, kv8):
+    """Model-sized heads and longer contexts: a prompt of 300 tokens, then decode steps, on one cache; grouped-query
+    ratios 1..7, head sizes that are not powers of two, positions past 2048 (large RoPE angles)."""
+    from oracle import AttnCache
+    rng = np.random.default_rng(H * 3 + hd + int(kv8))
+    qn = rng.uniform(0.5, 1.5, hd).astype(np.float32); kn = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    max_t = 2400
+    cache = AttnCache(H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=rot, qn=qn, kn=kn, kv8=kv8)
+    a = gpu.Attn(H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=rot, qn=qn, kn=kn, kv8=kv8)
+    pos = 2050
+    # positions below pos_base are zero rows in both caches: they take part in the softmax identically
+    for S in (300, 1, 1, 17):
+        q = rng.standard_normal((S, H * hd)).astype(np.float32)
+        k = rng.standard_normal((S, KV * hd)).astype(np.float32); v = rng.standard_normal((S, KV * hd)).astype(np.float32)
+        yo = oracle.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
+        y = a.core(q, k, v, pos)
+        # int8 cache: an ulp of difference before the row quantizer can move a code by one (1/127 of one term)
+        tol = 2e-3 if kv8 else 5e-5
+        err, mag = float(np.abs(y - yo).max()), float(np.abs(yo).max())
+        print(f"attn H={H} hd={hd} kv8={kv8} S={S} pos={pos}: max err {err:.3g} of {mag:.3g}")
+        assert err <= tol * mag, (S, pos, err, mag)
+        pos += S
+    a.close()
+    with pytest.raises(RuntimeError):
+        gpu.Attn(H, KV, hd, 8).core(np.zeros((9, H * hd), np.float32), np.zeros((9, KV * hd), np.float32),
+                                    np.zeros((9, KV * hd), np.float32), 0)
+
+
 def _moe_from_golden(gpu, g):
     E, K, I, D = (int(v) for v in g["moe_dims"])
     m = gpu.Moe(E, K, I, D)

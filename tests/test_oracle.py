@@ -76,6 +76,29 @@ def test_i4g_drivers(oracle):
             assert same_bits(oracle.matmul_i4g_idot_s(g[f"x_{tag}_{S}"], g[f"q4_{tag}"], g[f"scale_{tag}"]), g[f"y_{tag}_{S}"])
 
 
+def _attn_golden_cases():
+    from oracle import AttnCache
+    g = golden("attn")
+    for tag in ("a", "b", "c", "d"):
+        H, KV, hd, rot, norm, kv8 = (int(v) for v in g[f"cfg_{tag}"])
+        qn = g[f"qn_{tag}"] if norm else None; kn = g[f"kn_{tag}"] if norm else None
+        mk = lambda: AttnCache(H, KV, hd, 16, theta=1e6, eps=1e-6, rot=rot, qn=qn, kn=kn, kv8=bool(kv8))
+        steps = [(g[f"q_{tag}_{i}"], g[f"k_{tag}_{i}"], g[f"v_{tag}_{i}"], g[f"ctx_{tag}_{i}"]) for i in range(3)]
+        yield tag, mk, steps
+
+
+def test_attn_core_golden(oracle):
+    """The attention core (nn/attn.c:29-74: QK-norm, RoPE, f32 and int8 KV store, scores, softmax, accumulation)
+    against vectors composed from the reference's own functions.  The reference's tiers sum in different orders
+    and contract multiply-adds, so this level is pinned by tolerance: 5e-6 of the output magnitude."""
+    for tag, mk, steps in _attn_golden_cases():
+        cache = mk(); pos = 0
+        for q, k, v, ctx in steps:
+            y = oracle.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
+            assert np.abs(y - ctx).max() <= 5e-6 * np.abs(ctx).max(), tag
+            pos += q.shape[0]
+
+
 def test_q4r4_batch_is_not_row_invariant(oracle):
     """The reference folds the -8 offset differently for tokens inside a complete
     group of 4 (nn/matmul.c:397-402): a batch is NOT always bitwise equal to its
