@@ -545,6 +545,27 @@ def run_case(args):
             us = time_moe(torch, layers, name, S, dev, stream, reps=max(1, args.steps // 16), run=16)
         print(json.dumps({"case": args.case, "us_per_layer": round(us, 2)}), flush=True)
         return
+    if parts[0] == "attn":                              # attn:S:POS:H:KV:hd[:kv8] -- S tokens at position POS of one layer's cache
+        S, POS, H, KV, hd = (int(v) for v in parts[1:6])
+        kv8 = len(parts) > 6 and parts[6] == "kv8"
+        a = mb.Attn(H, KV, hd, POS + S, qn=np.ones(hd, np.float32), kn=np.ones(hd, np.float32), kv8=kv8)
+        stream = torch.cuda.Stream(device=dev)
+        with torch.cuda.stream(stream):
+            q0 = torch.randn((S, H * hd), device=dev); k0 = torch.randn((S, KV * hd), device=dev)
+            q = q0.clone(); k = k0.clone(); v = torch.randn((S, KV * hd), device=dev); ctx = torch.empty((S, H * hd), device=dev)
+            run = lambda: a.core_dev(ctx.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), S, POS, stream=stream.cuda_stream)
+            for _ in range(max(args.warmup, 1)):
+                run()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(args.steps):
+                run()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / args.steps
+        kvb = 2.0 * KV * (POS + S) * hd * (1 if kv8 else 4)           # cache bytes a decode step reads
+        print(json.dumps({"case": args.case, "us": round(us, 2), "kv_GBs": round(kvb / us / 1e3, 1)}), flush=True)
+        return
     if parts[0] == "ffn":                               # ffn:S:D:I -- one dense int8 SiLU FFN block (gate/up [I][D], down [D][I])
         S, D, I = int(parts[1]), int(parts[2]), int(parts[3])
         mk = lambda O, K: mb.Mat.i8(rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
@@ -609,7 +630,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; ffn:S:D:I one dense int8 SiLU FFN block; ep:NAME:S under torchrun times the "
+                                                "times calls of one routed layer; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8] the attention core with S tokens at position POS; ep:NAME:S under torchrun times the "
                                                 "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:

@@ -123,7 +123,7 @@ extern "C" void moty_cuda_shutdown(void) {
         cudaSetDevice(c->dev);
         cudaStreamSynchronize(c->stream);
         Buf *bs[] = {&c->xi, &c->sx, &c->xs, &c->xsum, &c->acc32, &c->dx, &c->dy, &c->dlogits, &c->daux,
-                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec, &c->mmak, &c->ffn1};
+                     &c->g, &c->u, &c->h, &c->hq, &c->hs, &c->hxs, &c->hxsum, &c->pair, &c->misc, &c->kcell, &c->rec, &c->mmak, &c->ffn1, &c->attn};
         for (Buf *b : bs) free_buf(b);
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
@@ -757,8 +757,11 @@ extern "C" int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q
     DevCtx *c = moty_ctx(a->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
     CK(cudaSetDevice(a->device));
+    const size_t sb = attn_scratch_bytes(S, a->H, a->KV, a->hd, c->sms);
+    if (sb) CKR(moty_grow(c, &c->attn, sb));
     return launch_attn_core(ctx_dev, q_dev, k_dev, v_dev, S, pos_base, a->H, a->KV, a->hd, a->rot, a->theta, a->eps, a->qn,
-                            a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, pick_stream(c, stream));
+                            a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, sb ? (float *)c->attn.p : nullptr,
+                            c->sms, pick_stream(c, stream));
 }
 
 extern "C" int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S,

@@ -59,6 +59,8 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(AttnArgs a) {
     __shared__ float red32[8];
     __shared__ float xs[256];
     const int s = blockIdx.x, slot = blockIdx.y, i = threadIdx.x, hd = a.hd;
+    pdl_trigger();
+    pdl_wait();                                                // q, k, v come from the projections before this launch
     const bool isq = slot < a.H;
     const int hh = isq ? slot : slot - a.H;
     float *row = isq ? a.q + (size_t)s * a.H * hd + (size_t)hh * hd : a.k + (size_t)s * a.KV * hd + (size_t)hh * hd;
@@ -100,72 +102,207 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(AttnArgs a) {
     }
 }
 
-// One CTA per (token, query head): scores against positions 0..qpos, softmax, accumulation.
-// Shared memory: q[hd], sc[n], partial[ngrp][hd].
-__global__ void __launch_bounds__(256) attn_core_kernel(AttnArgs a) {
+// Scores, softmax and accumulation.  A CTA takes one token, up to AT_G query heads that share a KV head (the key and
+// value rows are read once for all of them) and one split of the positions 0..qpos; it walks its positions in
+// sub-chunks of AT_CH with a running maximum and sum (the softmax of hw/hw_ops.h:22-26 evaluated piecewise:
+// exp(s - m) terms are rescaled when the maximum moves), so shared memory does not grow with the context.  With one
+// split the CTA writes ctx itself; otherwise it leaves {m, l, acc[hd]} per head in `part` and attn_merge_kernel joins
+// the splits.  Decode steps (few tokens, long context) are split so that every SM has work; prompts are not.
+constexpr int AT_CH = 128, AT_G = 4, AT_PB = 8, AT_WARPS = 8;
+
+// four consecutive dimensions of a cached row as floats: f32 cache or int8 cache (codes only; the row scale is applied
+// by the caller as the reference does, nn/attn_kernels.c:16,31)
+__device__ __forceinline__ float4 attn_row4(const float *f, const int8_t *q, size_t off) {
+    if (q) {
+        const char4 c = *reinterpret_cast<const char4 *>(q + off);
+        return make_float4((float)c.x, (float)c.y, (float)c.z, (float)c.w);
+    }
+    return *reinterpret_cast<const float4 *>(f + off);
+}
+
+// NV = float4 rounds a lane needs to cover a head: lane l holds dimensions 128 r + 4 l .. + 3 (head_dim <= 128 NV)
+template <int NV>
+__global__ void __launch_bounds__(AT_WARPS * 32) attn_flash_kernel(AttnArgs a, int nsplit, int span, float *part) {
     extern __shared__ float sm_attn[];
+    __shared__ float m_s[AT_G], l_s[AT_G], f_s[AT_G];
+    const int hd = a.hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.H / a.KV, ngy = (G + AT_G - 1) / AT_G;
+    const int s = blockIdx.z, kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G, split = blockIdx.x;
+    const int ng = G - g0 < AT_G ? G - g0 : AT_G, head0 = kvh * G + g0;
+    const int n = a.pos_base + s + 1;                                   // positions 0..qpos
+    const int t_lo = split * span, t_hi = t_lo + span < n ? t_lo + span : n;
+    const size_t base = (size_t)kvh * a.max_t;
+    float *qs = sm_attn, *sc = qs + AT_G * NV * 128, *ps = sc + AT_G * AT_CH;   // q[AT_G][NV*128], sc[AT_G][AT_CH], partial[warps][AT_G][NV*128]
+    pdl_trigger();
+    pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel
+    for (int i = tid; i < AT_G * NV * 128; i += AT_WARPS * 32) {
+        const int g = i / (NV * 128), dd = i - g * (NV * 128);
+        qs[i] = g < ng && dd < hd ? a.q[(size_t)s * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
+    }
+    if (tid < AT_G) { m_s[tid] = -1e30f; l_s[tid] = 0.f; }
+    bool dv[NV];                                                        // does round r of this lane lie inside the head
+#pragma unroll
+    for (int r = 0; r < NV; r++) dv[r] = r * 128 + lane * 4 < hd;
+    float4 acc[AT_G][NV];
+#pragma unroll
+    for (int g = 0; g < AT_G; g++)
+#pragma unroll
+        for (int r = 0; r < NV; r++) acc[g][r] = make_float4(0.f, 0.f, 0.f, 0.f);
+    __syncthreads();
+    for (int c0 = t_lo; c0 < t_hi; c0 += AT_CH) {
+        const int nc = t_hi - c0 < AT_CH ? t_hi - c0 : AT_CH;
+        // scores (hw/hw_ops.h:53-55; int8 keys nn/attn_kernels.c:14-17): a warp takes AT_PB positions at a time, all their
+        // key rows requested before the first dot
+        for (int tb = warp * AT_PB; tb < nc; tb += AT_WARPS * AT_PB) {
+            float4 kr[AT_PB][NV];
+#pragma unroll
+            for (int u = 0; u < AT_PB; u++) {
+                const size_t row = base + c0 + (tb + u < nc ? tb + u : nc - 1);
+#pragma unroll
+                for (int r = 0; r < NV; r++)
+                    kr[u][r] = dv[r] ? attn_row4(a.K, a.K8, row * hd + r * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < AT_PB; u++) {
+                if (tb + u >= nc) break;
+                const float ks = a.K8 ? a.Ks[base + c0 + tb + u] : 1.f;
+                for (int g = 0; g < ng; g++) {
+                    float dsum = 0.f;
+#pragma unroll
+                    for (int r = 0; r < NV; r++) {
+                        const float4 q4 = *reinterpret_cast<const float4 *>(qs + g * NV * 128 + r * 128 + lane * 4);
+                        dsum = fmaf(q4.x, kr[u][r].x, dsum); dsum = fmaf(q4.y, kr[u][r].y, dsum);
+                        dsum = fmaf(q4.z, kr[u][r].z, dsum); dsum = fmaf(q4.w, kr[u][r].w, dsum);
+                    }
+                    for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
+                    if (lane == 0) sc[g * AT_CH + tb + u] = a.K8 ? __fmul_rn(__fmul_rn(ks, dsum), a.scale) : __fmul_rn(dsum, a.scale);
+                }
+            }
+        }
+        __syncthreads();
+        // running maximum and sum: warp g looks after head g
+        if (warp < ng) {
+            float mc = -1e30f;
+            for (int t = lane; t < nc; t += 32) mc = fmaxf(mc, sc[warp * AT_CH + t]);
+            for (int off = 16; off > 0; off >>= 1) mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, off));
+            const float m_old = m_s[warp], m_new = fmaxf(m_old, mc);
+            float sum = 0.f;
+            for (int t = lane; t < nc; t += 32) {
+                const float e = expf(__fsub_rn(sc[warp * AT_CH + t], m_new));
+                sc[warp * AT_CH + t] = e; sum += e;
+            }
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            if (lane == 0) {
+                const float f = expf(__fsub_rn(m_old, m_new));              // 0 on the first sub-chunk, 1 when the maximum stays
+                f_s[warp] = f; m_s[warp] = m_new; l_s[warp] = fmaf(l_s[warp], f, sum);
+            }
+        }
+        __syncthreads();
+        // accumulation (hw/hw_ops.h:56-59; int8 values nn/attn_kernels.c:26-35): the warps take the positions in turn,
+        // AT_PB value rows requested at a time
+#pragma unroll
+        for (int g = 0; g < AT_G; g++) {
+            const float f = g < ng ? f_s[g] : 0.f;
+#pragma unroll
+            for (int r = 0; r < NV; r++) { acc[g][r].x *= f; acc[g][r].y *= f; acc[g][r].z *= f; acc[g][r].w *= f; }
+        }
+        for (int tb = warp * AT_PB; tb < nc; tb += AT_WARPS * AT_PB) {
+            float4 vr[AT_PB][NV];
+#pragma unroll
+            for (int u = 0; u < AT_PB; u++) {
+                const size_t row = base + c0 + (tb + u < nc ? tb + u : nc - 1);
+#pragma unroll
+                for (int r = 0; r < NV; r++)
+                    vr[u][r] = dv[r] ? attn_row4(a.V, a.V8, row * hd + r * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int u = 0; u < AT_PB; u++) {
+                if (tb + u >= nc) break;
+                const float vs = a.V8 ? a.Vs[base + c0 + tb + u] : 1.f;
+#pragma unroll
+                for (int g = 0; g < AT_G; g++) {
+                    if (g >= ng) break;
+                    const float p = sc[g * AT_CH + tb + u];
+                    const float w = a.V8 ? __fmul_rn(p, vs) : p;            // nn/attn_kernels.c:31: a = sc * Vs
+#pragma unroll
+                    for (int r = 0; r < NV; r++) {
+                        acc[g][r].x = fmaf(w, vr[u][r].x, acc[g][r].x); acc[g][r].y = fmaf(w, vr[u][r].y, acc[g][r].y);
+                        acc[g][r].z = fmaf(w, vr[u][r].z, acc[g][r].z); acc[g][r].w = fmaf(w, vr[u][r].w, acc[g][r].w);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int g = 0; g < AT_G; g++)
+#pragma unroll
+        for (int r = 0; r < NV; r++)
+            *reinterpret_cast<float4 *>(ps + ((size_t)warp * AT_G + g) * NV * 128 + r * 128 + lane * 4) = acc[g][r];
+    __syncthreads();
+    for (int i = tid; i < ng * hd; i += AT_WARPS * 32) {
+        const int g = i / hd, dd = i - g * hd;
+        float tot = ps[(size_t)g * NV * 128 + dd];
+        for (int w = 1; w < AT_WARPS; w++) tot += ps[((size_t)w * AT_G + g) * NV * 128 + dd];
+        if (nsplit == 1) {
+            a.ctx[(size_t)s * a.H * hd + (size_t)(head0 + g) * hd + dd] = __fdiv_rn(tot, l_s[g]);
+        } else {
+            float *p = part + (((size_t)s * a.H + head0 + g) * nsplit + split) * (hd + 2);
+            p[2 + dd] = tot;
+            if (dd == 0) { p[0] = m_s[g]; p[1] = l_s[g]; }
+        }
+    }
+}
+
+// joins the splits of one (token, head): M = max m_c, ctx = sum acc_c exp(m_c - M) / sum l_c exp(m_c - M)
+__global__ void __launch_bounds__(256) attn_merge_kernel(AttnArgs a, int nsplit, const float *part) {
+    extern __shared__ float fm[];                                       // per split: its factor exp(m_c - M), 0 for an empty one
     __shared__ float red32[8];
     const int s = blockIdx.x, hh = blockIdx.y, hd = a.hd, tid = threadIdx.x, nth = blockDim.x;
-    const int lane = tid & 31, warp = tid >> 5, nwarp = nth >> 5;
-    const int kvh = hh / (a.H / a.KV), qpos = a.pos_base + s, n = qpos + 1;
-    const size_t base = (size_t)kvh * a.max_t;
-    float *qs = sm_attn, *sc = sm_attn + hd, *part = sc + (a.pos_base + a.S);
-    const float *qv = a.q + (size_t)s * a.H * hd + (size_t)hh * hd;
-    for (int i = tid; i < hd; i += nth) qs[i] = qv[i];
-    __syncthreads();
-    // scores (hw/hw_ops.h:53-55; int8 keys nn/attn_kernels.c:14-17): a warp per position
-    for (int t = warp; t < n; t += nwarp) {
-        float d = 0.f;
-        if (a.K8) {
-            const int8_t *kr = a.K8 + (base + t) * hd;
-            for (int i = lane; i < hd; i += 32) d = fmaf(qs[i], (float)kr[i], d);
-        } else {
-            const float *kr = a.K + (base + t) * hd;
-            for (int i = lane; i < hd; i += 32) d = fmaf(qs[i], kr[i], d);
-        }
-        for (int off = 16; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-        if (lane == 0) sc[t] = a.K8 ? __fmul_rn(__fmul_rn(a.Ks[base + t], d), a.scale) : __fmul_rn(d, a.scale);
-    }
-    __syncthreads();
-    // softmax (hw/hw_ops.h:22-26)
+    const float *p = part + ((size_t)s * a.H + hh) * nsplit * (hd + 2);
+    pdl_trigger();
+    pdl_wait();
     float m = -1e30f;
-    for (int t = tid; t < n; t += nth) m = fmaxf(m, sc[t]);
-    m = block_max_f32(m, red32);
-    float sum = 0.f;
-    for (int t = tid; t < n; t += nth) { const float e = expf(__fsub_rn(sc[t], m)); sc[t] = e; sum += e; }
-    sum = block_sum_f32(sum, red32);
-    for (int t = tid; t < n; t += nth) sc[t] = __fdiv_rn(sc[t], sum);
-    __syncthreads();
-    // accumulation (hw/hw_ops.h:56-59; int8 values nn/attn_kernels.c:26-35): thread = dimension, groups of threads
-    // take positions round-robin, partial sums are added in group order
-    const int ngrp = nth / hd > 0 ? nth / hd : 1;
-    const int grp = tid / hd, d = tid - grp * hd;
-    if (grp < ngrp && d < hd) {
-        float acc = 0.f;
-        if (a.V8) {
-            for (int t = grp; t < n; t += ngrp)
-                acc = fmaf(__fmul_rn(sc[t], a.Vs[base + t]), (float)a.V8[(base + t) * hd + d], acc);
-        } else {
-            for (int t = grp; t < n; t += ngrp) acc = fmaf(sc[t], a.V[(base + t) * hd + d], acc);
-        }
-        part[grp * hd + d] = acc;
+    for (int c = tid; c < nsplit; c += nth) { fm[c] = p[(size_t)c * (hd + 2)]; m = fmaxf(m, fm[c]); }
+    const float M = block_max_f32(m, red32);
+    float l = 0.f;
+    for (int c = tid; c < nsplit; c += nth) {
+        const float lc = p[(size_t)c * (hd + 2) + 1];
+        const float f = lc == 0.f ? 0.f : expf(__fsub_rn(fm[c], M));     // a split past the token's position has nothing in it
+        fm[c] = f; l = fmaf(lc, f, l);
     }
-    __syncthreads();
+    const float L = block_sum_f32(l, red32);                             // (its barriers also publish fm)
     if (tid < hd) {
-        float acc = part[tid];
-        for (int g = 1; g < ngrp; g++) acc += part[g * hd + tid];
-        a.ctx[(size_t)s * a.H * hd + (size_t)hh * hd + tid] = acc;
+        float acc = 0.f;
+        for (int c0 = 0; c0 < nsplit; c0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = c0 + u < nsplit ? p[(size_t)(c0 + u) * (hd + 2) + 2 + tid] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) if (c0 + u < nsplit) acc = fmaf(v[u], fm[c0 + u], acc);
+        }
+        a.ctx[(size_t)s * a.H * hd + (size_t)hh * hd + tid] = __fdiv_rn(acc, L);
     }
 }
 
 }  // namespace
 
+// room for the partial results of a call whose positions are split (at most 4 * sms + 1 splits in all)
+size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {
+    const int G = H / KV, ngy = (G + AT_G - 1) / AT_G;
+    const long long units = (long long)S * KV * ngy;
+    if (units >= 2LL * sms) return 0;
+    const long long nsplit = (4LL * sms + units - 1) / units + 1;
+    return (size_t)S * H * nsplit * (hd + 2) * 4;
+}
+
 // q, k: modified in place (normed, rotated), as the reference does.  Caches: f32 (K, V) or int8 (K8, V8, Ks, Vs).
+// part: scratch of attn_scratch_bytes(...) for decode-sized calls (null: never split the positions).
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, cudaStream_t st) {
+                     float *Ks, float *Vs, int max_t, float *part, int sms, cudaStream_t st) {
     if (S <= 0) return 0;
-    if (hd <= 0 || hd > 256 || rot < 0 || rot > hd || (rot & 1) || H <= 0 || KV <= 0 || H % KV || pos_base < 0 ||
+    if (hd <= 0 || hd > 256 || hd % 4 || rot < 0 || rot > hd || (rot & 1) || H <= 0 || KV <= 0 || H % KV || pos_base < 0 ||
         pos_base + S > max_t)
         return moty_set_error(MOTY_CUDA_EARG, "attn_core: S=%d pos=%d max_t=%d H=%d KV=%d hd=%d rot=%d", S, pos_base, max_t, H, KV, hd, rot);
     AttnArgs a;
@@ -173,21 +310,36 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     a.S = S; a.pos_base = pos_base; a.H = H; a.KV = KV; a.hd = hd; a.rot = rot; a.max_t = max_t;
     a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd);
     const int nth_prep = (hd + 31) / 32 * 32;
-    attn_prep_kernel<<<dim3(S, H + KV), nth_prep, 0, st>>>(a);
-    CK(cudaGetLastError());
-    const int nth = nth_prep > 128 ? nth_prep : 128;
-    const int ngrp = nth / hd > 0 ? nth / hd : 1;
-    const size_t smem = ((size_t)hd + (size_t)(pos_base + S) + (size_t)ngrp * hd) * 4;
-    if (smem > 200 * 1024) return moty_set_error(MOTY_CUDA_ELIMIT, "attn_core: %d positions need %zu bytes of shared memory", pos_base + S, smem);
-    static size_t attr_smem[MOTY_MAX_DEV];
+    CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
+    const int NVr = hd > 128 ? 2 : 1;
+    const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;
+    const int G = H / KV, ngy = (G + AT_G - 1) / AT_G, T = pos_base + S;
+    // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
+    int nsplit = 1;
+    const long long units = (long long)S * KV * ngy;
+    if (units < 2LL * sms) {
+        nsplit = (int)((4LL * sms + units - 1) / units);
+        const int most = (T + AT_CH - 1) / AT_CH;
+        if (nsplit > most) nsplit = most;
+        if (nsplit < 1) nsplit = 1;
+    }
+    int span = (T + nsplit - 1) / nsplit;
+    span = (span + AT_CH - 1) / AT_CH * AT_CH;
+    nsplit = (T + span - 1) / span;
+    if (nsplit > 1 && !part) return moty_set_error(MOTY_CUDA_EARG, "attn_core: scratch for %d splits missing", nsplit);
+    static bool attr_done[MOTY_MAX_DEV];
     int dev = 0;
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "attn_core: device %d", dev);
-    if (smem > 48 * 1024 && smem > attr_smem[dev]) {
-        CK(cudaFuncSetAttribute(attn_core_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr_smem[dev] = 200 * 1024;
+    if (!attr_done[dev]) {
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        attr_done[dev] = true;
     }
-    attn_core_kernel<<<dim3(S, H), nth, smem, st>>>(a);
-    CK(cudaGetLastError());
+    if ((unsigned)S > 65535u) return moty_set_error(MOTY_CUDA_ELIMIT, "attn_core: S=%d in one call", S);
+    if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1>, dim3(nsplit, KV * ngy, S), dim3(AT_WARPS * 32), smem, st, a, nsplit, span, part));
+    else CK(moty_launch_pdl(attn_flash_kernel<2>, dim3(nsplit, KV * ngy, S), dim3(AT_WARPS * 32), smem, st, a, nsplit, span, part));
+    if (nsplit > 1)
+        CK(moty_launch_pdl(attn_merge_kernel, dim3(S, H), dim3(nth_prep), (size_t)nsplit * 4, st, a, nsplit, (const float *)part));
     return 0;
 }

@@ -63,6 +63,7 @@ struct DevCtx {
     // FFN / MoE intermediates
     Buf g, u, h, hq, hs, hxs, hxsum, pair, misc;
     Buf rec;                         // per (token, group) records of the Q4R4 batch kernel
+    Buf attn;                        // partial results of an attention call whose positions are split over CTAs
     Buf ffn1;                        // the constant logit and the index/weight outputs of a dense FFN run as a one-expert MoE block
     Buf mmak;                        // split-K scratch of the Q8_0 MMA kernel: tile counters + int32 partials, zero between calls
     // streaming GEMV: ticket/exit counters and K-split cells, all zero between launches

@@ -78,7 +78,8 @@ int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, cudaStream_t st);
+                     float *Ks, float *Vs, int max_t, float *part, int sms, cudaStream_t st);
+size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
 
 // ---- i4g.cu: WF_I4G (grouped int4, group 32, f32 group scales) x row-quantized activations ----
 int launch_i4g_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx, float *y,
