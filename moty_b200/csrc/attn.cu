@@ -254,6 +254,131 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_flash_kernel(AttnArgs a, i
     }
 }
 
+// Prompts (head_dim <= 128).  A CTA takes eight consecutive tokens and up to four query heads of one KV head: 32 query
+// rows that share every key and value row.  The positions are walked 64 at a time: the sub-chunk's key and value rows
+// are staged in shared memory once (int8 rows as their codes, scales aside), the 32 x 64 scores are register-tiled
+// dot products from shared memory (thread = one position x eight rows, no shuffles), one warp per token keeps the
+// running maximum and sum of its four rows, and the same warp accumulates its token's rows over the staged value
+// rows (lane = four dimensions).  Causal: a position past a token's own scores -1e30 and weighs 0.
+constexpr int AP_TQ = 8, AP_CH = 64, AP_HD = 128, AP_KP = AP_HD + 4, AP_PP = AP_CH + 4;
+constexpr size_t AP_SMEM = ((size_t)32 * AP_KP + (size_t)AP_CH * AP_KP + (size_t)AP_CH * AP_HD + (size_t)32 * AP_PP + 2 * AP_CH + 3 * 32) * 4;
+
+__global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
+    extern __shared__ float sm_attn[];
+    float *Qs = sm_attn;                                  // [32][AP_KP]   row = token * 4 + head
+    float *Kc = Qs + 32 * AP_KP;                          // [AP_CH][AP_KP]
+    float *Vc = Kc + AP_CH * AP_KP;                       // [AP_CH][AP_HD]
+    float *P = Vc + AP_CH * AP_HD;                        // [32][AP_PP]   scores, then weights
+    float *ksc = P + 32 * AP_PP, *vsc = ksc + AP_CH;      // row scales of an int8 cache
+    float *m_s = vsc + AP_CH, *l_s = m_s + 32, *f_s = l_s + 32;
+    const int hd = a.hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.H / a.KV, ngy = (G + AT_G - 1) / AT_G;
+    const int s0 = blockIdx.x * AP_TQ, kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G;
+    const int ng = G - g0 < AT_G ? G - g0 : AT_G, head0 = kvh * G + g0;
+    const int ntok = a.S - s0 < AP_TQ ? a.S - s0 : AP_TQ;
+    const int n_all = a.pos_base + s0 + ntok;             // positions 0 .. the last token's own
+    const size_t base = (size_t)kvh * a.max_t;
+    pdl_trigger();
+    pdl_wait();
+    for (int i = tid; i < 32 * AP_HD; i += 256) {
+        const int row = i >> 7, dd = i & 127, tok = row >> 2, g = row & 3;
+        Qs[row * AP_KP + dd] = tok < ntok && g < ng && dd < hd ? a.q[(size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
+    }
+    if (tid < 32) { m_s[tid] = -1e30f; l_s[tid] = 0.f; }
+    float4 acc[4];                                        // this warp's token, heads 0..3, dimensions 4 lane .. 4 lane + 3
+#pragma unroll
+    for (int j = 0; j < 4; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    const int p_me = tid & 63, rg = tid >> 6;             // scores: my position in the sub-chunk, my eight rows rg * 8 ..
+    const int hd4 = hd >> 2;
+    for (int c0 = 0; c0 < n_all; c0 += AP_CH) {
+        const int nc = n_all - c0 < AP_CH ? n_all - c0 : AP_CH;
+        __syncthreads();                                  // everyone is done with the previous sub-chunk (and Qs is written)
+        for (int i = tid; i < AP_CH * 32; i += 256) {     // stage: position i >> 5, dimensions 4 (i & 31) ..
+            const int pp = i >> 5, q4 = i & 31;
+            float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
+            if (pp < nc && q4 < hd4) {
+                const size_t off = (base + c0 + pp) * hd + q4 * 4;
+                kv = attn_row4(a.K, a.K8, off); vv = attn_row4(a.V, a.V8, off);
+            }
+            *reinterpret_cast<float4 *>(Kc + pp * AP_KP + q4 * 4) = kv;
+            *reinterpret_cast<float4 *>(Vc + pp * AP_HD + q4 * 4) = vv;
+        }
+        if (tid < AP_CH) {
+            ksc[tid] = a.K8 && tid < nc ? a.Ks[base + c0 + tid] : 1.f;
+            vsc[tid] = a.V8 && tid < nc ? a.Vs[base + c0 + tid] : 1.f;
+        }
+        __syncthreads();
+        {   // scores (hw/hw_ops.h:53-55; int8 keys nn/attn_kernels.c:14-17)
+            float d8[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) d8[j] = 0.f;
+            const float *kp = Kc + p_me * AP_KP, *qp = Qs + rg * 8 * AP_KP;
+            for (int k4 = 0; k4 < hd4; k4++) {
+                const float4 kv = *reinterpret_cast<const float4 *>(kp + k4 * 4);
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float4 qv = *reinterpret_cast<const float4 *>(qp + j * AP_KP + k4 * 4);
+                    d8[j] = fmaf(qv.x, kv.x, d8[j]); d8[j] = fmaf(qv.y, kv.y, d8[j]);
+                    d8[j] = fmaf(qv.z, kv.z, d8[j]); d8[j] = fmaf(qv.w, kv.w, d8[j]);
+                }
+            }
+            const float ks = ksc[p_me];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int row = rg * 8 + j, tok = row >> 2;
+                const bool seen = p_me < nc && c0 + p_me <= a.pos_base + s0 + tok;
+                const float v = a.K8 ? __fmul_rn(__fmul_rn(ks, d8[j]), a.scale) : __fmul_rn(d8[j], a.scale);
+                P[row * AP_PP + p_me] = seen ? v : -1e30f;
+            }
+        }
+        __syncthreads();
+        // warp = token: running maximum and sum of its four rows (hw/hw_ops.h:22-26, piecewise), weights in place
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            float *row = P + (warp * 4 + j) * AP_PP;
+            const float x0 = row[lane], x1 = row[lane + 32];
+            float mc = fmaxf(x0, x1);
+            for (int off = 16; off > 0; off >>= 1) mc = fmaxf(mc, __shfl_xor_sync(0xffffffffu, mc, off));
+            const float m_old = m_s[warp * 4 + j], m_new = fmaxf(m_old, mc);
+            const float e0 = x0 <= -1e30f ? 0.f : expf(__fsub_rn(x0, m_new)), e1 = x1 <= -1e30f ? 0.f : expf(__fsub_rn(x1, m_new));
+            float sum = e0 + e1;
+            for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+            const float f = expf(__fsub_rn(m_old, m_new));
+            // int8 values: a = weight * Vs (nn/attn_kernels.c:31)
+            row[lane] = a.V8 ? __fmul_rn(e0, vsc[lane]) : e0;
+            row[lane + 32] = a.V8 ? __fmul_rn(e1, vsc[lane + 32]) : e1;
+            __syncwarp();
+            if (lane == 0) { m_s[warp * 4 + j] = m_new; l_s[warp * 4 + j] = fmaf(l_s[warp * 4 + j], f, sum); }
+            acc[j].x *= f; acc[j].y *= f; acc[j].z *= f; acc[j].w *= f;
+        }
+        __syncwarp();
+        // accumulation (hw/hw_ops.h:56-59): this warp's token over the staged value rows, lane = four dimensions
+        if (lane < hd4) {
+            const float *pr = P + warp * 4 * AP_PP;
+            for (int pp = 0; pp < nc; pp++) {
+                const float4 vv = *reinterpret_cast<const float4 *>(Vc + pp * AP_HD + lane * 4);
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const float w = pr[j * AP_PP + pp];
+                    acc[j].x = fmaf(w, vv.x, acc[j].x); acc[j].y = fmaf(w, vv.y, acc[j].y);
+                    acc[j].z = fmaf(w, vv.z, acc[j].z); acc[j].w = fmaf(w, vv.w, acc[j].w);
+                }
+            }
+        }
+    }
+    __syncwarp();
+    if (warp < ntok && lane < hd4) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            if (j >= ng) break;
+            const float l = l_s[warp * 4 + j];
+            float4 o = acc[j];
+            o.x = __fdiv_rn(o.x, l); o.y = __fdiv_rn(o.y, l); o.z = __fdiv_rn(o.z, l); o.w = __fdiv_rn(o.w, l);
+            *reinterpret_cast<float4 *>(a.ctx + (size_t)(s0 + warp) * a.H * hd + (size_t)(head0 + j) * hd + lane * 4) = o;
+        }
+    }
+}
+
 // joins the splits of one (token, head): M = max m_c, ctx = sum acc_c exp(m_c - M) / sum l_c exp(m_c - M)
 __global__ void __launch_bounds__(256) attn_merge_kernel(AttnArgs a, int nsplit, const float *part) {
     extern __shared__ float fm[];                                       // per split: its factor exp(m_c - M), 0 for an empty one
@@ -314,6 +439,20 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     const int NVr = hd > 128 ? 2 : 1;
     const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;
     const int G = H / KV, ngy = (G + AT_G - 1) / AT_G, T = pos_base + S;
+    // prompts: eight tokens per CTA share staged key and value rows, when that still gives every SM a CTA
+    const long long tiles = (long long)((S + AP_TQ - 1) / AP_TQ) * KV * ngy;
+    if (S >= AP_TQ && hd <= AP_HD && tiles >= sms) {
+        static bool attr_p[MOTY_MAX_DEV];
+        int devp = 0;
+        CK(cudaGetDevice(&devp));
+        if (devp < 0 || devp >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "attn_core: device %d", devp);
+        if (!attr_p[devp]) {
+            CK(cudaFuncSetAttribute(attn_prompt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AP_SMEM));
+            attr_p[devp] = true;
+        }
+        CK(moty_launch_pdl(attn_prompt_kernel, dim3((S + AP_TQ - 1) / AP_TQ, KV * ngy), dim3(256), AP_SMEM, st, a));
+        return 0;
+    }
     // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
     int nsplit = 1;
     const long long units = (long long)S * KV * ngy;
