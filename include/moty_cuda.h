@@ -259,6 +259,9 @@ int moty_cuda_attn_free(MotyCudaAttn *a);
 int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S, int pos_base);
 int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
                             int S, int pos_base, void *stream);
+/* the last step of the gated variant (moty_nn_attention_gated, nn/attn.c:68-69): ctx[i] *= 1 / (1 + expf(-gate[i])),
+ * ctx_dev and gate_dev [S][H*hd] on the handle's device */
+int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream);
 
 /* ---- load-time quantizers (weights) -----------------------------------------
  * moty_quantize_rows (nn/quant.c:12-33) with bits = 8: w [O][I] f32 host ->

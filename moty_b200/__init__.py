@@ -335,6 +335,10 @@ class Attn:
         _ck(lib().moty_cuda_attn_core_dev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
                                           S, pos_base, C.c_void_p(stream)))
 
+    def gate_dev(self, ctx_ptr, gate_ptr, S, stream=0):
+        """ctx *= sigmoid(gate) (moty_nn_attention_gated's last step), both [S][H*hd] on the device."""
+        _ck(lib().moty_cuda_attn_gate_dev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(gate_ptr), S, C.c_void_p(stream)))
+
     def close(self):
         if self.h:
             lib().moty_cuda_attn_free(self.h); self.h = None

@@ -764,6 +764,14 @@ extern "C" int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q
                             c->sms, pick_stream(c, stream));
 }
 
+extern "C" int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream) {
+    if (!a || !ctx_dev || !gate_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_gate_dev: null argument");
+    DevCtx *c = moty_ctx(a->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
+    CK(cudaSetDevice(a->device));
+    return launch_attn_gate(ctx_dev, gate_dev, (long long)S * a->H * a->hd, pick_stream(c, stream));
+}
+
 extern "C" int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S,
                                    int pos_base) {
     if (!a || !ctx || !q || !k || !v) return moty_set_error(MOTY_CUDA_EARG, "attn_core: null argument");

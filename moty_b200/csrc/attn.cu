@@ -410,7 +410,21 @@ __global__ void __launch_bounds__(256) attn_merge_kernel(AttnArgs a, int nsplit,
     }
 }
 
+// the gated variant's last step (nn/attn.c:68-69): ctx[i] *= 1 / (1 + expf(-gate[i]))
+__global__ void __launch_bounds__(256) attn_gate_kernel(float *ctx, const float *gate, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) ctx[i] = __fmul_rn(ctx[i], __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gate[i]))));
+}
+
 }  // namespace
+
+int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    CK(moty_launch_pdl(attn_gate_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, st, ctx, gate, n));
+    return 0;
+}
 
 // room for the partial results of a call whose positions are split (at most 4 * sms + 1 splits in all)
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {

@@ -80,6 +80,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
                      float *Ks, float *Vs, int max_t, float *part, int sms, cudaStream_t st);
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
+int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st);
 
 // ---- i4g.cu: WF_I4G (grouped int4, group 32, f32 group scales) x row-quantized activations ----
 int launch_i4g_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx, float *y,

@@ -101,6 +101,34 @@ def test_attn_core_vs_oracle(gpu, oracle, H, KV, hd, rot, kv8):
                                     np.zeros((9, KV * hd), np.float32), 0)
 
 
+def test_attn_gate_and_device_entry(gpu, oracle):
+    """The device-pointer entry on torch buffers (q and k are normed and rotated in place, as the reference does) and
+    the gated variant's last step, ctx *= 1 / (1 + expf(-gate)) (nn/attn.c:68-69)."""
+    import torch
+    from oracle import AttnCache
+    H, KV, hd, S = 8, 4, 64, 5
+    rng = np.random.default_rng(11)
+    qn = rng.uniform(0.5, 1.5, hd).astype(np.float32); kn = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    q = rng.standard_normal((S, H * hd)).astype(np.float32); k = rng.standard_normal((S, KV * hd)).astype(np.float32)
+    v = rng.standard_normal((S, KV * hd)).astype(np.float32); gate = rng.standard_normal((S, H * hd)).astype(np.float32)
+    qo, ko = q.copy(), k.copy()
+    yo = oracle.attn_core(qo, ko, v.copy(), 3, AttnCache(H, KV, hd, 16, qn=qn, kn=kn))
+    a = gpu.Attn(H, KV, hd, 16, qn=qn, kn=kn)
+    dq, dk, dv, dg = (torch.from_numpy(t).cuda() for t in (q, k, v, gate))
+    ctx = torch.empty((S, H * hd), device="cuda")
+    torch.cuda.synchronize()
+    sh = gpu.stream_handle(torch.cuda.current_stream())
+    a.core_dev(ctx.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), S, 3, stream=sh)
+    torch.cuda.synchronize()
+    assert np.abs(ctx.cpu().numpy() - yo).max() <= 5e-5 * np.abs(yo).max()
+    assert np.abs(dq.cpu().numpy() - qo).max() <= 1e-5 and np.abs(dk.cpu().numpy() - ko).max() <= 1e-5
+    a.gate_dev(ctx.data_ptr(), dg.data_ptr(), S, stream=sh)
+    torch.cuda.synchronize()
+    yg = yo * (np.float32(1) / (np.float32(1) + np.exp(-gate, dtype=np.float32)))
+    assert np.abs(ctx.cpu().numpy() - yg).max() <= 5e-5 * np.abs(yg).max()
+    a.close()
+
+
 def _moe_from_golden(gpu, g):
     E, K, I, D = (int(v) for v in g["moe_dims"])
     m = gpu.Moe(E, K, I, D)
