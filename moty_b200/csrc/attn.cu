@@ -426,12 +426,12 @@ int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st
     return 0;
 }
 
-// room for the partial results of a call whose positions are split (at most 4 * sms + 1 splits in all)
+// room for the partial results of a call whose positions are split (at most 3 * sms + 1 splits in all)
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {
     const int G = H / KV, ngy = (G + AT_G - 1) / AT_G;
     const long long units = (long long)S * KV * ngy;
     if (units >= 2LL * sms) return 0;
-    const long long nsplit = (4LL * sms + units - 1) / units + 1;
+    const long long nsplit = (3LL * sms + units - 1) / units + 1;
     return (size_t)S * H * nsplit * (hd + 2) * 4;
 }
 
@@ -471,7 +471,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     int nsplit = 1;
     const long long units = (long long)S * KV * ngy;
     if (units < 2LL * sms) {
-        nsplit = (int)((4LL * sms + units - 1) / units);
+        nsplit = (int)((3LL * sms + units - 1) / units);
         const int most = (T + AT_CH - 1) / AT_CH;
         if (nsplit > most) nsplit = most;
         if (nsplit < 1) nsplit = 1;
