@@ -225,7 +225,40 @@ def run_extras(torch, mb, dev, stream, W8, local):
             del xs, ys
     del W4
     out["moe"] = run_moe_extras(torch, mb, dev, stream, local)
+    out["blocks"] = run_block_extras(torch, mb, dev, stream, local)
     return out
+
+
+def run_block_extras(torch, mb, dev, stream, local):
+    """The callers either side of the matmuls, one decode token: a dense int8 SiLU FFN block (Qwen3-0.6B shape) and the
+    attention core against a 4096-position f32 cache (16 heads, 8 KV heads, head_dim 128); CUDA events over 50 calls."""
+    rng = np.random.default_rng(5)
+    res = {}
+    sp = stream.cuda_stream
+    def timed(fn, n=50):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return round(e0.elapsed_time(e1) * 1e3 / n, 2)
+    with torch.cuda.stream(stream):
+        D, I = 1024, 3072
+        mk = lambda O, K: mb.Mat.i8(rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=local)
+        G, U, Dn = mk(I, D), mk(I, D), mk(D, I)
+        x = torch.randn((1, D), device=dev); y = torch.empty((1, D), device=dev)
+        res["ffn_decode_1024x3072_us"] = timed(lambda: mb.dense_ffn_dev(G, U, Dn, y.data_ptr(), x.data_ptr(), 1, stream=sp))
+        del G, U, Dn
+        H, KV, hd, POS = 16, 8, 128, 4096
+        a = mb.Attn(H, KV, hd, POS + 1, qn=np.ones(hd, np.float32), kn=np.ones(hd, np.float32), device=local)
+        q = torch.randn((1, H * hd), device=dev); k = torch.randn((1, KV * hd), device=dev); v = torch.randn((1, KV * hd), device=dev)
+        ctx = torch.empty((1, H * hd), device=dev)
+        res["attn_decode_pos4096_us"] = timed(lambda: a.core_dev(ctx.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), 1, POS, stream=sp))
+        a.close()
+    return res
 
 
 MOE_SHAPES = {"olmoe": (64, 8, 1024, 2048, "i8"), "qwen3-30b-a3b": (128, 8, 768, 2048, "q4r4")}
