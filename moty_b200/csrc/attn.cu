@@ -120,9 +120,24 @@ __device__ __forceinline__ float4 attn_row4(const float *f, const int8_t *q, siz
     return *reinterpret_cast<const float4 *>(f + off);
 }
 
+// 32 per-lane partial sums -> lane L holds the total of value L
+__device__ __forceinline__ void attn_reduce32(float (&v)[32], int lane) {
+    int off = 16;
+#pragma unroll
+    for (int n = 32; n > 1; n >>= 1, off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < n / 2; i++) {
+            const bool up = (lane & off) != 0;
+            const float send = up ? v[i] : v[i + n / 2];
+            const float keep = up ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+}
+
 // NV = float4 rounds a lane needs to cover a head: lane l holds dimensions 128 r + 4 l .. + 3 (head_dim <= 128 NV)
 template <int NV>
-__global__ void __launch_bounds__(AT_WARPS * 32) attn_flash_kernel(AttnArgs a, int nsplit, int span, float *part) {
+__global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_kernel(AttnArgs a, int nsplit, int span, float *part) {
     extern __shared__ float sm_attn[];
     __shared__ float m_s[AT_G], l_s[AT_G], f_s[AT_G];
     const int hd = a.hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -162,20 +177,28 @@ __global__ void __launch_bounds__(AT_WARPS * 32) attn_flash_kernel(AttnArgs a, i
                 for (int r = 0; r < NV; r++)
                     kr[u][r] = dv[r] ? attn_row4(a.K, a.K8, row * hd + r * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
+            // the lane's share of all AT_PB x AT_G dots, then ONE butterfly that leaves dot number L in lane L
+            // (31 shuffles for 32 dots instead of five per dot); value u * AT_G + g = position tb + u, head g
+            float dsum[AT_PB * AT_G];
 #pragma unroll
-            for (int u = 0; u < AT_PB; u++) {
-                if (tb + u >= nc) break;
-                const float ks = a.K8 ? a.Ks[base + c0 + tb + u] : 1.f;
-                for (int g = 0; g < ng; g++) {
-                    float dsum = 0.f;
+            for (int u = 0; u < AT_PB; u++)
+#pragma unroll
+                for (int g = 0; g < AT_G; g++) {
+                    float d = 0.f;
 #pragma unroll
                     for (int r = 0; r < NV; r++) {
-                        const float4 q4 = *reinterpret_cast<const float4 *>(qs + g * NV * 128 + r * 128 + lane * 4);
-                        dsum = fmaf(q4.x, kr[u][r].x, dsum); dsum = fmaf(q4.y, kr[u][r].y, dsum);
-                        dsum = fmaf(q4.z, kr[u][r].z, dsum); dsum = fmaf(q4.w, kr[u][r].w, dsum);
+                        const float4 q4 = *reinterpret_cast<const float4 *>(qs + g * NV * 128 + r * 128 + lane * 4);   // zero rows for g >= ng
+                        d = fmaf(q4.x, kr[u][r].x, d); d = fmaf(q4.y, kr[u][r].y, d);
+                        d = fmaf(q4.z, kr[u][r].z, d); d = fmaf(q4.w, kr[u][r].w, d);
                     }
-                    for (int off = 16; off > 0; off >>= 1) dsum += __shfl_xor_sync(0xffffffffu, dsum, off);
-                    if (lane == 0) sc[g * AT_CH + tb + u] = a.K8 ? __fmul_rn(__fmul_rn(ks, dsum), a.scale) : __fmul_rn(dsum, a.scale);
+                    dsum[u * AT_G + g] = d;
+                }
+            attn_reduce32(dsum, lane);
+            {
+                const int u = lane / AT_G, g = lane - u * AT_G;
+                if (tb + u < nc && g < ng) {
+                    const float d = dsum[0];
+                    sc[g * AT_CH + tb + u] = a.K8 ? __fmul_rn(__fmul_rn(a.Ks[base + c0 + tb + u], d), a.scale) : __fmul_rn(d, a.scale);
                 }
             }
         }
