@@ -277,13 +277,13 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     }
 }
 
-// Prompts (head_dim <= 128).  A CTA takes eight consecutive tokens and up to four query heads of one KV head: 32 query
-// rows that share every key and value row.  The positions are walked 64 at a time: the sub-chunk's key and value rows
+// Prompts (head_dim <= 128).  A CTA takes 32 query rows that share every key and value row: consecutive tokens x the
+// query heads of one KV head (8 tokens x 4 heads, 16 x 2 or 32 x 1).  The positions are walked 64 at a time: the sub-chunk's key and value rows
 // are staged in shared memory once (int8 rows as their codes, scales aside), the 32 x 64 scores are register-tiled
 // dot products from shared memory (thread = one position x eight rows, no shuffles), one warp per token keeps the
 // running maximum and sum of its four rows, and the same warp accumulates its token's rows over the staged value
 // rows (lane = four dimensions).  Causal: a position past a token's own scores -1e30 and weighs 0.
-constexpr int AP_TQ = 8, AP_CH = 64, AP_HD = 128, AP_KP = AP_HD + 4, AP_PP = AP_CH + 4;
+constexpr int AP_CH = 64, AP_HD = 128, AP_KP = AP_HD + 4, AP_PP = AP_CH + 4;
 constexpr size_t AP_SMEM = ((size_t)32 * AP_KP + (size_t)AP_CH * AP_KP + (size_t)AP_CH * AP_HD + (size_t)32 * AP_PP + 2 * AP_CH + 3 * 32) * 4;
 
 __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
@@ -296,15 +296,19 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
     float *m_s = vsc + AP_CH, *l_s = m_s + 32, *f_s = l_s + 32;
     const int hd = a.hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.H / a.KV, ngy = (G + AT_G - 1) / AT_G;
-    const int s0 = blockIdx.x * AP_TQ, kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G;
+    const int kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G;
     const int ng = G - g0 < AT_G ? G - g0 : AT_G, head0 = kvh * G + g0;
-    const int ntok = a.S - s0 < AP_TQ ? a.S - s0 : AP_TQ;
+    // the 32 query rows are (32 / ngp) tokens x ngp heads, ngp = the head count rounded up to 1, 2 or 4: row = token * ngp + head
+    const int ngc = G < AT_G ? G : AT_G;                  // (the same for every CTA of the launch; a last group may have fewer heads)
+    const int lg = ngc > 2 ? 2 : ngc - 1, ngp = 1 << lg, tq = 32 >> lg;
+    const int s0 = blockIdx.x * tq;
+    const int ntok = a.S - s0 < tq ? a.S - s0 : tq;
     const int n_all = a.pos_base + s0 + ntok;             // positions 0 .. the last token's own
     const size_t base = (size_t)kvh * a.max_t;
     pdl_trigger();
     pdl_wait();
     for (int i = tid; i < 32 * AP_HD; i += 256) {
-        const int row = i >> 7, dd = i & 127, tok = row >> 2, g = row & 3;
+        const int row = i >> 7, dd = i & 127, tok = row >> lg, g = row & (ngp - 1);
         Qs[row * AP_KP + dd] = tok < ntok && g < ng && dd < hd ? a.q[(size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
     }
     if (tid < 32) { m_s[tid] = -1e30f; l_s[tid] = 0.f; }
@@ -348,7 +352,7 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
             const float ks = ksc[p_me];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-                const int row = rg * 8 + j, tok = row >> 2;
+                const int row = rg * 8 + j, tok = row >> lg;
                 const bool seen = p_me < nc && c0 + p_me <= a.pos_base + s0 + tok;
                 const float v = a.K8 ? __fmul_rn(__fmul_rn(ks, d8[j]), a.scale) : __fmul_rn(d8[j], a.scale);
                 P[row * AP_PP + p_me] = seen ? v : -1e30f;
@@ -390,14 +394,15 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
         }
     }
     __syncwarp();
-    if (warp < ntok && lane < hd4) {
+    if (lane < hd4) {
 #pragma unroll
         for (int j = 0; j < 4; j++) {
-            if (j >= ng) break;
-            const float l = l_s[warp * 4 + j];
+            const int row = warp * 4 + j, tok = row >> lg, g = row & (ngp - 1);
+            if (tok >= ntok || g >= ng) continue;
+            const float l = l_s[row];
             float4 o = acc[j];
             o.x = __fdiv_rn(o.x, l); o.y = __fdiv_rn(o.y, l); o.z = __fdiv_rn(o.z, l); o.w = __fdiv_rn(o.w, l);
-            *reinterpret_cast<float4 *>(a.ctx + (size_t)(s0 + warp) * a.H * hd + (size_t)(head0 + j) * hd + lane * 4) = o;
+            *reinterpret_cast<float4 *>(a.ctx + (size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + lane * 4) = o;
         }
     }
 }
@@ -477,8 +482,9 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;
     const int G = H / KV, ngy = (G + AT_G - 1) / AT_G, T = pos_base + S;
     // prompts: eight tokens per CTA share staged key and value rows, when that still gives every SM a CTA
-    const long long tiles = (long long)((S + AP_TQ - 1) / AP_TQ) * KV * ngy;
-    if (S >= AP_TQ && hd <= AP_HD && tiles >= sms) {
+    const int ng_cta = G < AT_G ? G : AT_G, tq = ng_cta > 2 ? 8 : (ng_cta == 2 ? 16 : 32);
+    const long long tiles = (long long)((S + tq - 1) / tq) * KV * ngy;
+    if (S >= 8 && hd <= AP_HD && tiles >= sms) {
         static bool attr_p[MOTY_MAX_DEV];
         int devp = 0;
         CK(cudaGetDevice(&devp));
@@ -487,7 +493,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
             CK(cudaFuncSetAttribute(attn_prompt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AP_SMEM));
             attr_p[devp] = true;
         }
-        CK(moty_launch_pdl(attn_prompt_kernel, dim3((S + AP_TQ - 1) / AP_TQ, KV * ngy), dim3(256), AP_SMEM, st, a));
+        CK(moty_launch_pdl(attn_prompt_kernel, dim3((S + tq - 1) / tq, KV * ngy), dim3(256), AP_SMEM, st, a));
         return 0;
     }
     // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
