@@ -120,11 +120,12 @@ __device__ __forceinline__ float4 attn_row4(const float *f, const int8_t *q, siz
     return *reinterpret_cast<const float4 *>(f + off);
 }
 
-// 32 per-lane partial sums -> lane L holds the total of value L
-__device__ __forceinline__ void attn_reduce32(float (&v)[32], int lane) {
+// N per-lane partial sums (N = 16 or 32) -> lane L holds the total of value L >> (5 - log2 N)
+template <int N>
+__device__ __forceinline__ void attn_reduce(float (&v)[N], int lane) {
     int off = 16;
 #pragma unroll
-    for (int n = 32; n > 1; n >>= 1, off >>= 1) {
+    for (int n = N; n > 1; n >>= 1, off >>= 1) {
 #pragma unroll
         for (int i = 0; i < n / 2; i++) {
             const bool up = (lane & off) != 0;
@@ -133,10 +134,12 @@ __device__ __forceinline__ void attn_reduce32(float (&v)[32], int lane) {
             v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
         }
     }
+    for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
 }
 
 // NV = float4 rounds a lane needs to cover a head: lane l holds dimensions 128 r + 4 l .. + 3 (head_dim <= 128 NV)
-template <int NV>
+// NH = query heads whose dots are formed per key row (2 when a KV head serves at most two, else 4)
+template <int NV, int NH>
 __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_kernel(AttnArgs a, int nsplit, int span, float *part) {
     extern __shared__ float sm_attn[];
     __shared__ float m_s[AT_G], l_s[AT_G], f_s[AT_G];
@@ -177,13 +180,13 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
                 for (int r = 0; r < NV; r++)
                     kr[u][r] = dv[r] ? attn_row4(a.K, a.K8, row * hd + r * 128 + lane * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
-            // the lane's share of all AT_PB x AT_G dots, then ONE butterfly that leaves dot number L in lane L
-            // (31 shuffles for 32 dots instead of five per dot); value u * AT_G + g = position tb + u, head g
-            float dsum[AT_PB * AT_G];
+            // the lane's share of all AT_PB x NH dots, then ONE butterfly that leaves dot number L (NH = 4) or L / 2 in lane L
+            // (31 shuffles for 32 dots instead of five per dot); value u * NH + g = position tb + u, head g
+            float dsum[AT_PB * NH];
 #pragma unroll
             for (int u = 0; u < AT_PB; u++)
 #pragma unroll
-                for (int g = 0; g < AT_G; g++) {
+                for (int g = 0; g < NH; g++) {
                     float d = 0.f;
 #pragma unroll
                     for (int r = 0; r < NV; r++) {
@@ -191,12 +194,12 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
                         d = fmaf(q4.x, kr[u][r].x, d); d = fmaf(q4.y, kr[u][r].y, d);
                         d = fmaf(q4.z, kr[u][r].z, d); d = fmaf(q4.w, kr[u][r].w, d);
                     }
-                    dsum[u * AT_G + g] = d;
+                    dsum[u * NH + g] = d;
                 }
-            attn_reduce32(dsum, lane);
+            attn_reduce<AT_PB * NH>(dsum, lane);
             {
-                const int u = lane / AT_G, g = lane - u * AT_G;
-                if (tb + u < nc && g < ng) {
+                const int val = NH == 4 ? lane : lane >> 1, u = val / NH, g = val - u * NH;
+                if (tb + u < nc && g < ng && (NH == 4 || !(lane & 1))) {
                     const float d = dsum[0];
                     sc[g * AT_CH + tb + u] = a.K8 ? __fmul_rn(__fmul_rn(a.Ks[base + c0 + tb + u], d), a.scale) : __fmul_rn(d, a.scale);
                 }
@@ -514,13 +517,18 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "attn_core: device %d", dev);
     if (!attr_done[dev]) {
-        CK(cudaFuncSetAttribute(attn_flash_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        CK(cudaFuncSetAttribute(attn_flash_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
         attr_done[dev] = true;
     }
     if ((unsigned)S > 65535u) return moty_set_error(MOTY_CUDA_ELIMIT, "attn_core: S=%d in one call", S);
-    if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1>, dim3(nsplit, KV * ngy, S), dim3(AT_WARPS * 32), smem, st, a, nsplit, span, part));
-    else CK(moty_launch_pdl(attn_flash_kernel<2>, dim3(nsplit, KV * ngy, S), dim3(AT_WARPS * 32), smem, st, a, nsplit, span, part));
+    const dim3 fgrid(nsplit, KV * ngy, S), fblock(AT_WARPS * 32);
+    if (NVr == 1 && G <= 2) CK(moty_launch_pdl(attn_flash_kernel<1, 2>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1, 4>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else if (G <= 2) CK(moty_launch_pdl(attn_flash_kernel<2, 2>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else CK(moty_launch_pdl(attn_flash_kernel<2, 4>, fgrid, fblock, smem, st, a, nsplit, span, part));
     if (nsplit > 1)
         CK(moty_launch_pdl(attn_merge_kernel, dim3(S, H), dim3(nth_prep), (size_t)nsplit * 4, st, a, nsplit, (const float *)part));
     return 0;
