@@ -240,6 +240,17 @@ int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream);
 int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, int *ids, float *logits);
 int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, int S, int *ids_dev, float *logits_dev, void *stream);
 
+/* ---- the f32 steps of a decoder layer around the matmuls (device pointers) ----
+ * So that a layer's activations can stay on the device between the entries above.
+ * rmsnorm: moty_rmsnorm_row per row (nn/norm.c:7, hw/hw_ops.h:14-18): mean of squares in double,
+ *          out = x * (1 / sqrtf((float)(ms / D) + eps)) * w;  x, out [S][D], w [D] (all device).
+ * add:     moty_hw_add (hw/hw_ops.h:30-32): y[i] += x[i].
+ * embed_rows: embed_row for an int8 table (runtime/rt_model_load.h:656-660; the tied lm_head uploaded as
+ *          MOTY_WF_I8 [vocab][D]): out[s][i] = (qs[id] * scale) * (float)q[id][i], ids_dev int32 [S] on the device. */
+int moty_cuda_rmsnorm_dev(float *out_dev, const float *x_dev, const float *w_dev, int S, int D, float eps, void *stream);
+int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *stream);
+int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream);
+
 /* ---- attention core between the projections --------------------------------
  * attn_tail of nn/attn.c:29-74 without the q/k/v/o projections (those are mat_apply calls) and
  * without the optional output gate: QK-norm (moty_rmsnorm_row per head with qn / kn [head_dim],

@@ -684,6 +684,31 @@ extern "C" int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, i
 }
 
 // ---------------------------------------------------------------------------
+// the f32 steps of a decoder layer around the matmuls (device pointers; they run on the GPU that owns `x_dev`)
+// ---------------------------------------------------------------------------
+extern "C" int moty_cuda_rmsnorm_dev(float *out_dev, const float *x_dev, const float *w_dev, int S, int D, float eps, void *stream) {
+    if (!out_dev || !x_dev || !w_dev) return moty_set_error(MOTY_CUDA_EARG, "rmsnorm_dev: null argument");
+    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    return launch_rmsnorm_rows(out_dev, x_dev, w_dev, S, D, eps, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *stream) {
+    if (!y_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "add_dev: null argument");
+    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    return launch_add(y_dev, x_dev, n, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream) {
+    if (!embed || !out_dev || !ids_dev) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: null argument");
+    if (embed->fmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: MOTY_WF_I8 table only");
+    DevCtx *c = moty_ctx(embed->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", embed->device);
+    CK(cudaSetDevice(embed->device));
+    return launch_embed_rows(out_dev, (const int8_t *)embed->codes, (const float *)embed->scales, ids_dev, S, embed->I, embed->O,
+                             scale, pick_stream(c, stream));
+}
+
+// ---------------------------------------------------------------------------
 // attention core of one layer (KV cache resident on the device)
 // ---------------------------------------------------------------------------
 struct MotyCudaAttn {

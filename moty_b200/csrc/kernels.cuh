@@ -75,6 +75,11 @@ int launch_q4r4_forms(uint8_t *form, int S, cudaStream_t st);
 bool q4r4_gemv1_supported(int I, int O, int sms);
 int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float *y, int I, int O, int sms, cudaStream_t st);
 
+// ---- norm.cu: RMS norm of rows, residual add, int8 embedding rows ----
+int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps, cudaStream_t st);
+int launch_add(float *y, const float *x, long long n, cudaStream_t st);
+int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *ids, int S, int D, int V, float scale, cudaStream_t st);
+
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,

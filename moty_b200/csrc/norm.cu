@@ -1,0 +1,64 @@
+// norm.cu -- the small f32 steps of a decoder layer around the matmuls, so that a layer's
+// activations can stay on the device: RMS norm of a row (moty_rmsnorm_row, nn/norm.c:7 ->
+// moty_hw_rmsnorm_ref, hw/hw_ops.h:14-18), the residual add (moty_hw_add_ref, hw/hw_ops.h:30-32)
+// and the int8 embedding row (embed_row, runtime/rt_model_load.h:656-660).
+#include "kernels.cuh"
+
+namespace {
+
+// one CTA per row: mean of squares in double, r = 1 / sqrtf((float)(ms / n) + eps), out = (x * r) * w
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *out, const float *x, const float *w, int D, float eps) {
+    __shared__ double red[8];
+    pdl_trigger();
+    pdl_wait();
+    const float *xr = x + (size_t)blockIdx.x * D;
+    float *orow = out + (size_t)blockIdx.x * D;
+    double ms = 0;
+    for (int i = threadIdx.x; i < D; i += 256) { const double v = xr[i]; ms += v * v; }
+    for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ms;
+    __syncthreads();
+    ms = 0;
+    for (int i = 0; i < 8; i++) ms += red[i];
+    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+    for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);
+}
+
+__global__ void __launch_bounds__(256) add_kernel(float *y, const float *x, long long n) {
+    pdl_trigger();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i < n) y[i] = __fadd_rn(y[i], x[i]);
+}
+
+// dst[s][i] = (qs[id] * scale) * (float)q[id][i]
+__global__ void __launch_bounds__(256) embed_rows_kernel(float *dst, const int8_t *q, const float *qs, const int *ids, int D, int V,
+                                                         float scale) {
+    pdl_trigger();
+    pdl_wait();
+    int id = ids[blockIdx.x];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const float es = __fmul_rn(qs[id], scale);
+    for (int i = threadIdx.x; i < D; i += 256) dst[(size_t)blockIdx.x * D + i] = __fmul_rn(es, (float)q[(size_t)id * D + i]);
+}
+
+}  // namespace
+
+int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps, cudaStream_t st) {
+    if (S <= 0) return 0;
+    if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "rmsnorm: D=%d", D);
+    CK(moty_launch_pdl(rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, out, x, w, D, eps));
+    return 0;
+}
+
+int launch_add(float *y, const float *x, long long n, cudaStream_t st) {
+    if (n <= 0) return 0;
+    CK(moty_launch_pdl(add_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, st, y, x, n));
+    return 0;
+}
+
+int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *ids, int S, int D, int V, float scale, cudaStream_t st) {
+    if (S <= 0) return 0;
+    CK(moty_launch_pdl(embed_rows_kernel, dim3(S), dim3(256), (size_t)0, st, dst, q, qs, ids, D, V, scale));
+    return 0;
+}

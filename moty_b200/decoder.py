@@ -1,0 +1,102 @@
+"""A dense decoder step on one GPU, composed from the library's device entries the way the reference's
+``qwen`` engine composes its CPU functions (engines/qwen.c:681-740, ``step``): embedding rows, then per
+layer RMS norm -> q/k/v projections -> attention core -> o projection -> residual add -> RMS norm ->
+SwiGLU FFN -> residual add, then the final norm of the last token, the (tied) lm_head and the greedy
+pick.  Activations stay on the device; only token ids go in and one id (or the logits) comes out.
+
+This is host-side glue for tests and for the decode rows of ``bench.py``; the arithmetic is in the C-ABI
+entries it calls (``moty_cuda_mat_apply_dev``, ``moty_cuda_attn_core_dev``, ``moty_cuda_ffn_dev``,
+``moty_cuda_rmsnorm_dev``, ``moty_cuda_add_dev``, ``moty_cuda_embed_rows_dev``, ``moty_cuda_head_argmax_dev``).
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import Attn, Mat, MotyCudaError, lib, stream_handle, ACT_SILU
+
+
+def _ck(rc):
+    if rc != 0:
+        raise MotyCudaError(f"libmoty_cuda error {rc}: {lib().moty_cuda_last_error().decode()}")
+
+
+class DenseLayer:
+    """One layer's weights: int8 matrices (q, k, v, o, gate, up, down) and f32 norm gains."""
+
+    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_ln, qn=None, kn=None):
+        self.q, self.k, self.v, self.o, self.gate, self.up, self.down = q, k, v, o, gate, up, down
+        self.in_ln, self.post_ln, self.qn, self.kn = in_ln, post_ln, qn, kn
+
+
+class DenseDecoder:
+    """``layers``: list of DenseLayer (matrices as ``moty_b200.Mat``, gains as numpy f32); ``head``: the lm_head
+    ``Mat`` (MOTY_WF_I8 [vocab][D]; with tied embeddings it is also the embedding table); ``final_norm`` [D]."""
+
+    def __init__(self, layers, head: Mat, final_norm, n_heads, n_kv_heads, head_dim, max_t, theta=1e6, eps=1e-6,
+                 rot=None, kv8=False, device=0, max_S=64):
+        import torch
+        self.torch = torch
+        self.dev = torch.device(f"cuda:{device}")
+        self.layers, self.head = layers, head
+        self.H, self.KV, self.hd, self.eps, self.max_t = n_heads, n_kv_heads, head_dim, float(eps), max_t
+        self.D = head.I
+        self.I = layers[0].gate.O
+        f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
+        self.final_norm = f(final_norm)
+        self.ln = [(f(l.in_ln), f(l.post_ln)) for l in layers]
+        self.attn = [Attn(n_heads, n_kv_heads, head_dim, max_t, theta=theta, eps=eps, rot=rot, qn=l.qn, kn=l.kn, kv8=kv8,
+                          device=device) for l in layers]
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self._alloc(max_S)
+
+    def _alloc(self, S):
+        t, dev = self.torch, self.dev
+        qw, kw = self.H * self.hd, self.KV * self.hd
+        e = lambda *shape: t.empty(shape, device=dev, dtype=t.float32)
+        self.cap = S
+        self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
+        self.qb, self.kb, self.vb, self.ctx = e(S, qw), e(S, kw), e(S, kw), e(S, qw)
+        self.ids = t.empty((S,), device=dev, dtype=t.int32)
+        self.out_id = t.empty((1,), device=dev, dtype=t.int32)
+        self.logits = e(1, self.head.O)
+
+    def step(self, ids, pos_base, want_logits=False):
+        """Tokens ``ids`` at positions pos_base.. : returns the greedy next token after the last of them
+        (and the last token's logits when asked)."""
+        t, L = self.torch, lib()
+        ids = np.ascontiguousarray(ids, np.int32).ravel()
+        S = ids.size
+        if S > self.cap:
+            self._alloc(S)
+        if pos_base + S > self.max_t:
+            raise MotyCudaError(f"positions {pos_base}..{pos_base + S} exceed the cache of {self.max_t}")
+        D = self.D
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        with t.cuda.stream(self.stream):
+            sh = C.c_void_p(stream_handle(self.stream))
+            self.ids[:S].copy_(t.from_numpy(ids), non_blocking=True)
+            _ck(L.moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), S, C.c_float(1.0), sh))
+            for l, (in_ln, post_ln), a in zip(self.layers, self.ln, self.attn):
+                _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(in_ln), S, D, C.c_float(self.eps), sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.q.h, p(self.qb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.k.h, p(self.kb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.v.h, p(self.vb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_attn_core_dev(a.h, p(self.ctx), p(self.qb), p(self.kb), p(self.vb), S, pos_base, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
+                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
+                _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(post_ln), S, D, C.c_float(self.eps), sh))
+                _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
+            last = self.x[S - 1:S]
+            _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(last), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
+            _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
+            tok = int(self.out_id.cpu()[0])          # waits for the stream
+            if want_logits:
+                return tok, self.logits.cpu().numpy()[0]
+        return tok
+
+    def close(self):
+        for a in self.attn:
+            a.close()

@@ -1,0 +1,105 @@
+"""A whole decoder step on the GPU (moty_b200.decoder.DenseDecoder, composed like engines/qwen.c:681-740) against the
+same composition of the CPU oracle's functions: a prompt, then greedy decoding, on a small Qwen3-shaped model."""
+import numpy as np
+import pytest
+
+from conftest import same_bits
+
+pytestmark = pytest.mark.gpu
+
+
+def _rmsnorm(x, w, eps):
+    """moty_hw_rmsnorm_ref (hw/hw_ops.h:14-18), row by row."""
+    out = np.empty_like(x)
+    for s in range(x.shape[0]):
+        ms = np.float64(0)
+        for v in x[s].astype(np.float64):
+            ms += v * v
+        r = np.float32(1) / np.sqrt(np.float32(ms / x.shape[1]) + np.float32(eps), dtype=np.float32)
+        out[s] = (x[s] * r) * w
+    return out
+
+
+class _OracleModel:
+    def __init__(self, oracle, W, cfg, max_t):
+        from oracle import AttnCache
+        self.o, self.W, self.cfg = oracle, W, cfg
+        self.caches = [AttnCache(cfg["H"], cfg["KV"], cfg["hd"], max_t, theta=1e6, eps=1e-6, qn=l["qn"], kn=l["kn"]) for l in W["layers"]]
+
+    def step(self, ids, pos):
+        o, W = self.o, self.W
+        hq, hs = W["head"]
+        x = np.stack([(hs[i] * np.float32(1.0)) * hq[i].astype(np.float32) for i in ids]).astype(np.float32)
+        for l, cache in zip(W["layers"], self.caches):
+            n = _rmsnorm(x, l["in_ln"], 1e-6)
+            q, k, v = (o.matmul_q_s(n, *l[m]) for m in ("q", "k", "v"))
+            ctx = o.attn_core(q, k, v, pos, cache)
+            x = x + o.matmul_q_s(ctx, *l["o"])
+            n = _rmsnorm(x, l["post_ln"], 1e-6)
+            h = o.silu_mul(o.matmul_q_s(n, *l["gate"]), o.matmul_q_s(n, *l["up"]))
+            x = x + o.matmul_q_s(h, *l["down"])
+        last = _rmsnorm(x[-1:], W["final_norm"], 1e-6)
+        lg = o.matmul_q_s(last, hq, hs)[0]
+        return o.argmax(lg), lg
+
+
+def test_kernels_of_the_layer_glue(gpu):
+    """RMS norm, residual add and embedding rows on device buffers against their definitions."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(2)
+    S, D, V = 5, 1000, 77
+    x = rng.standard_normal((S, D)).astype(np.float32); w = rng.uniform(0.5, 1.5, D).astype(np.float32)
+    dx, dw = torch.from_numpy(x).cuda(), torch.from_numpy(w).cuda(); out = torch.empty_like(dx)
+    torch.cuda.synchronize()
+    sh = C.c_void_p(gpu.stream_handle(torch.cuda.current_stream()))
+    L = gpu.lib()
+    assert L.moty_cuda_rmsnorm_dev(C.c_void_p(out.data_ptr()), C.c_void_p(dx.data_ptr()), C.c_void_p(dw.data_ptr()), S, D, C.c_float(1e-6), sh) == 0
+    ref = _rmsnorm(x, w, 1e-6)
+    assert np.abs(out.cpu().numpy() - ref).max() <= 2e-7 * np.abs(ref).max()
+    y = rng.standard_normal((S, D)).astype(np.float32); dy = torch.from_numpy(y).cuda()
+    torch.cuda.synchronize()
+    assert L.moty_cuda_add_dev(C.c_void_p(dy.data_ptr()), C.c_void_p(dx.data_ptr()), C.c_longlong(S * D), sh) == 0
+    assert same_bits(dy.cpu().numpy(), y + x)
+    q = rng.integers(-127, 128, (V, D), dtype=np.int8); qs = rng.uniform(0.001, 0.02, V).astype(np.float32)
+    E = gpu.Mat.i8(q, qs)
+    ids = np.array([3, 76, 0, 3, 41], np.int32); dids = torch.from_numpy(ids).cuda()
+    torch.cuda.synchronize()
+    assert L.moty_cuda_embed_rows_dev(E.h, C.c_void_p(out.data_ptr()), C.c_void_p(dids.data_ptr()), S, C.c_float(1.0), sh) == 0
+    assert same_bits(out.cpu().numpy(), np.stack([(qs[i] * np.float32(1)) * q[i].astype(np.float32) for i in ids]))
+
+
+def test_greedy_tokens_match_the_oracle(gpu, oracle):
+    """A 3-layer model (hidden 256, 8 query / 4 KV heads of 32, FFN 512, vocabulary 1000, tied int8 head): a prompt of 9
+    tokens and 24 greedy steps give the same token ids as the oracle's composition.  Every stage agrees with its oracle
+    to 1e-6 or bit for bit, but an ulp before a row quantizer moves an int8 code, and a network of random weights
+    amplifies that from layer to layer: the logits are compared at 3e-2 of their magnitude, the token ids exactly."""
+    from moty_b200.decoder import DenseDecoder, DenseLayer
+    rng = np.random.default_rng(7)
+    cfg = dict(H=8, KV=4, hd=32); D, I, V, NL = 256, 512, 1000, 3
+    mk = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.0005, 0.0015, O).astype(np.float32))
+    W = {"layers": [], "head": mk(V, D), "final_norm": np.ones(D, np.float32)}
+    W["head"] = (W["head"][0], (W["head"][1] * 20).astype(np.float32))          # embedding rows of unit size
+    for _ in range(NL):
+        W["layers"].append(dict(q=mk(cfg["H"] * cfg["hd"], D), k=mk(cfg["KV"] * cfg["hd"], D), v=mk(cfg["KV"] * cfg["hd"], D),
+                                o=mk(D, cfg["H"] * cfg["hd"]), gate=mk(I, D), up=mk(I, D), down=mk(D, I),
+                                in_ln=np.ones(D, np.float32), post_ln=np.ones(D, np.float32),
+                                qn=np.ones(cfg["hd"], np.float32), kn=np.ones(cfg["hd"], np.float32)))
+    max_t = 64
+    layers = [DenseLayer(*(gpu.Mat.i8(*l[m]) for m in ("q", "k", "v", "o", "gate", "up", "down")), l["in_ln"], l["post_ln"], l["qn"], l["kn"])
+              for l in W["layers"]]
+    dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t)
+    om = _OracleModel(oracle, W, cfg, max_t)
+    prompt = rng.integers(0, V, 9).astype(np.int32)
+    tg, lg = dec.step(prompt, 0, want_logits=True)
+    to, lo = om.step(prompt, 0)
+    assert np.abs(lg - lo).max() <= 3e-2 * np.abs(lo).max()
+    assert tg == to
+    pos, got, want = len(prompt), [tg], [to]
+    for _ in range(24):
+        tg, lg = dec.step([got[-1]], pos, want_logits=True)
+        to, lo = om.step([want[-1]], pos)
+        assert np.abs(lg - lo).max() <= 3e-2 * np.abs(lo).max(), pos
+        got.append(tg); want.append(to); pos += 1
+    assert got == want
+    dec.close()
