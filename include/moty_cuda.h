@@ -249,6 +249,10 @@ int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, int S, int 
  *          MOTY_WF_I8 [vocab][D]): out[s][i] = (qs[id] * scale) * (float)q[id][i], ids_dev int32 [S] on the device. */
 int moty_cuda_rmsnorm_dev(float *out_dev, const float *x_dev, const float *w_dev, int S, int D, float eps, void *stream);
 int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *stream);
+/* add_rmsnorm: the residual add followed by the next norm, one launch: x += t, then out = rmsnorm(x) with gains w
+ * (same results as add_dev followed by rmsnorm_dev). */
+int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
+                              float eps, void *stream);
 int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream);
 
 /* ---- attention core between the projections --------------------------------
@@ -270,6 +274,11 @@ int moty_cuda_attn_free(MotyCudaAttn *a);
 int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S, int pos_base);
 int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
                             int S, int pos_base, void *stream);
+/* The same with the first position read from a device int at run time: a decode step captured once into a CUDA graph
+ * is replayed while the position moves.  pos_max = the largest value *pos_dev may take (it sizes the launch);
+ * pos_max + S must fit the cache.  Results equal attn_core_dev at the same position. */
+int moty_cuda_attn_core_posdev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
+                               int S, const int *pos_dev, int pos_max, void *stream);
 /* the last step of the gated variant (moty_nn_attention_gated, nn/attn.c:68-69): ctx[i] *= 1 / (1 + expf(-gate[i])),
  * ctx_dev and gate_dev [S][H*hd] on the handle's device */
 int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream);

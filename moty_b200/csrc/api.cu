@@ -698,6 +698,13 @@ extern "C" int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, 
     return launch_add(y_dev, x_dev, n, pick_stream(c, stream));
 }
 
+extern "C" int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
+                                         float eps, void *stream) {
+    if (!x_dev || !t_dev || !out_dev || !w_dev) return moty_set_error(MOTY_CUDA_EARG, "add_rmsnorm_dev: null argument");
+    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    return launch_add_rmsnorm_rows(x_dev, t_dev, out_dev, w_dev, S, D, eps, pick_stream(c, stream));
+}
+
 extern "C" int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream) {
     if (!embed || !out_dev || !ids_dev) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: null argument");
     if (embed->fmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: MOTY_WF_I8 table only");
@@ -776,8 +783,22 @@ extern "C" int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_h
     return 0;
 }
 
+static int attn_core_on(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev, int S, int pos_base,
+                        const int *pos_dev, void *stream);
+
 extern "C" int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
                                        int S, int pos_base, void *stream) {
+    return attn_core_on(a, ctx_dev, q_dev, k_dev, v_dev, S, pos_base, nullptr, stream);
+}
+
+extern "C" int moty_cuda_attn_core_posdev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
+                                          int S, const int *pos_dev, int pos_max, void *stream) {
+    if (!pos_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_core_posdev: null position");
+    return attn_core_on(a, ctx_dev, q_dev, k_dev, v_dev, S, pos_max, pos_dev, stream);
+}
+
+static int attn_core_on(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev, int S, int pos_base,
+                        const int *pos_dev, void *stream) {
     if (!a || !ctx_dev || !q_dev || !k_dev || !v_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_core_dev: null argument");
     DevCtx *c = moty_ctx(a->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
@@ -786,7 +807,7 @@ extern "C" int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q
     if (sb) CKR(moty_grow(c, &c->attn, sb));
     return launch_attn_core(ctx_dev, q_dev, k_dev, v_dev, S, pos_base, a->H, a->KV, a->hd, a->rot, a->theta, a->eps, a->qn,
                             a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, sb ? (float *)c->attn.p : nullptr,
-                            c->sms, pick_stream(c, stream));
+                            pos_dev, c->sms, pick_stream(c, stream));
 }
 
 extern "C" int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream) {

@@ -19,6 +19,8 @@ struct AttnArgs {
     int8_t *K8, *V8; float *Ks, *Vs;     // int8 cache [KV][max_t][hd] + scales [KV][max_t], or null
     int S, pos_base, H, KV, hd, rot, max_t;
     float theta, eps, scale;
+    const int *pos_dev;                  // when set, the first position is read from the device (a captured decode step
+                                         // is replayed with a position that moves); pos_base then only sizes the launch
 };
 
 __device__ __forceinline__ double block_sum_f64(double v, double *red) {
@@ -65,7 +67,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(AttnArgs a) {
     const int hh = isq ? slot : slot - a.H;
     float *row = isq ? a.q + (size_t)s * a.H * hd + (size_t)hh * hd : a.k + (size_t)s * a.KV * hd + (size_t)hh * hd;
     const float *nw = isq ? a.qn : a.kn;
-    const int pos = a.pos_base + s;
+    const int pos = (a.pos_dev ? *a.pos_dev : a.pos_base) + s;
     float x = i < hd ? row[i] : 0.f;
     if (nw) {                                                  // hw/hw_ops.h:14-18
         const double ms = block_sum_f64((double)x * (double)x, red64);
@@ -147,12 +149,14 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     const int G = a.H / a.KV, ngy = (G + AT_G - 1) / AT_G;
     const int s = blockIdx.z, kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G, split = blockIdx.x;
     const int ng = G - g0 < AT_G ? G - g0 : AT_G, head0 = kvh * G + g0;
-    const int n = a.pos_base + s + 1;                                   // positions 0..qpos
-    const int t_lo = split * span, t_hi = t_lo + span < n ? t_lo + span : n;
+    int n = a.pos_base + s + 1;                                         // positions 0..qpos (re-read after the wait when it lives on the device)
+    const int t_lo = split * span;
+    int t_hi = t_lo + span < n ? t_lo + span : n;
     const size_t base = (size_t)kvh * a.max_t;
     float *qs = sm_attn, *sc = qs + AT_G * NV * 128, *ps = sc + AT_G * AT_CH;   // q[AT_G][NV*128], sc[AT_G][AT_CH], partial[warps][AT_G][NV*128]
     pdl_trigger();
     pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel
+    if (a.pos_dev) { n = *a.pos_dev + s + 1; t_hi = t_lo + span < n ? t_lo + span : n; }
     for (int i = tid; i < AT_G * NV * 128; i += AT_WARPS * 32) {
         const int g = i / (NV * 128), dd = i - g * (NV * 128);
         qs[i] = g < ng && dd < hd ? a.q[(size_t)s * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
@@ -468,9 +472,11 @@ size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {
 
 // q, k: modified in place (normed, rotated), as the reference does.  Caches: f32 (K, V) or int8 (K8, V8, Ks, Vs).
 // part: scratch of attn_scratch_bytes(...) for decode-sized calls (null: never split the positions).
+// pos_dev: null, or a device int holding the first position; pos_base is then the LARGEST value it may take (it sizes
+// the launch, so that one captured launch serves every position up to it).
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, int sms, cudaStream_t st) {
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int sms, cudaStream_t st) {
     if (S <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4 || rot < 0 || rot > hd || (rot & 1) || H <= 0 || KV <= 0 || H % KV || pos_base < 0 ||
         pos_base + S > max_t)
@@ -478,7 +484,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     AttnArgs a;
     a.q = q; a.k = k; a.v = v; a.ctx = ctx; a.qn = qn; a.kn = kn; a.K = K; a.V = V; a.K8 = K8; a.V8 = V8; a.Ks = Ks; a.Vs = Vs;
     a.S = S; a.pos_base = pos_base; a.H = H; a.KV = KV; a.hd = hd; a.rot = rot; a.max_t = max_t;
-    a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd);
+    a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd); a.pos_dev = pos_dev;
     const int nth_prep = (hd + 31) / 32 * 32;
     CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
     const int NVr = hd > 128 ? 2 : 1;
@@ -487,7 +493,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     // prompts: eight tokens per CTA share staged key and value rows, when that still gives every SM a CTA
     const int ng_cta = G < AT_G ? G : AT_G, tq = ng_cta > 2 ? 8 : (ng_cta == 2 ? 16 : 32);
     const long long tiles = (long long)((S + tq - 1) / tq) * KV * ngy;
-    if (S >= 8 && hd <= AP_HD && tiles >= sms) {
+    if (S >= 8 && hd <= AP_HD && tiles >= sms && !pos_dev) {
         static bool attr_p[MOTY_MAX_DEV];
         int devp = 0;
         CK(cudaGetDevice(&devp));
@@ -502,7 +508,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
     int nsplit = 1;
     const long long units = (long long)S * KV * ngy;
-    if (units < 2LL * sms) {
+    if (units < 2LL * sms && T > 2 * AT_CH) {                           // (a context of two sub-chunks is not worth a merge launch)
         nsplit = (int)((3LL * sms + units - 1) / units);
         const int most = (T + AT_CH - 1) / AT_CH;
         if (nsplit > most) nsplit = most;

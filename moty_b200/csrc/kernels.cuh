@@ -78,12 +78,13 @@ int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float
 // ---- norm.cu: RMS norm of rows, residual add, int8 embedding rows ----
 int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps, cudaStream_t st);
 int launch_add(float *y, const float *x, long long n, cudaStream_t st);
+int launch_add_rmsnorm_rows(float *x, const float *t, float *out, const float *w, int S, int D, float eps, cudaStream_t st);
 int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *ids, int S, int D, int V, float scale, cudaStream_t st);
 
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, int sms, cudaStream_t st);
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int sms, cudaStream_t st);
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
 int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st);
 

@@ -24,6 +24,29 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *out, const flo
     for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);
 }
 
+// the residual add and the next norm in one pass over the row: x += t (hw/hw_ops.h:30-32), out = rmsnorm(x) as above
+__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float *x, const float *t, float *out, const float *w, int D, float eps) {
+    __shared__ double red[8];
+    pdl_trigger();
+    pdl_wait();
+    float *xr = x + (size_t)blockIdx.x * D;
+    const float *tr = t + (size_t)blockIdx.x * D;
+    float *orow = out + (size_t)blockIdx.x * D;
+    double ms = 0;
+    for (int i = threadIdx.x; i < D; i += 256) {
+        const float v = __fadd_rn(xr[i], tr[i]);
+        xr[i] = v;
+        ms += (double)v * (double)v;
+    }
+    for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ms;
+    __syncthreads();
+    ms = 0;
+    for (int i = 0; i < 8; i++) ms += red[i];
+    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+    for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);   // the thread's own writes above
+}
+
 __global__ void __launch_bounds__(256) add_kernel(float *y, const float *x, long long n) {
     pdl_trigger();
     pdl_wait();
@@ -48,6 +71,13 @@ int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D
     if (S <= 0) return 0;
     if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "rmsnorm: D=%d", D);
     CK(moty_launch_pdl(rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, out, x, w, D, eps));
+    return 0;
+}
+
+int launch_add_rmsnorm_rows(float *x, const float *t, float *out, const float *w, int S, int D, float eps, cudaStream_t st) {
+    if (S <= 0) return 0;
+    if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "add_rmsnorm: D=%d", D);
+    CK(moty_launch_pdl(add_rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, x, t, out, w, D, eps));
     return 0;
 }
 

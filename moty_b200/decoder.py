@@ -25,9 +25,12 @@ def _ck(rc):
 class DenseLayer:
     """One layer's weights: int8 matrices (q, k, v, o, gate, up, down) and f32 norm gains."""
 
-    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_ln, qn=None, kn=None):
+    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_ln, qn=None, kn=None, qkv=None):
         self.q, self.k, self.v, self.o, self.gate, self.up, self.down = q, k, v, o, gate, up, down
         self.in_ln, self.post_ln, self.qn, self.kn = in_ln, post_ln, qn, kn
+        # optional: the rows of q, k and v in one matrix (the reference's fused [q|k|v], nn/attn.h:24): one product
+        # per decode token instead of three; per-row quantization makes the concatenation exact
+        self.qkv = qkv
 
 
 class DenseDecoder:
@@ -58,6 +61,7 @@ class DenseDecoder:
         self.cap = S
         self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
         self.qb, self.kb, self.vb, self.ctx = e(S, qw), e(S, kw), e(S, kw), e(S, qw)
+        self.qkvb = e(1, qw + 2 * kw)
         self.ids = t.empty((S,), device=dev, dtype=t.int32)
         self.out_id = t.empty((1,), device=dev, dtype=t.int32)
         self.logits = e(1, self.head.O)
@@ -78,17 +82,7 @@ class DenseDecoder:
             sh = C.c_void_p(stream_handle(self.stream))
             self.ids[:S].copy_(t.from_numpy(ids), non_blocking=True)
             _ck(L.moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), S, C.c_float(1.0), sh))
-            for l, (in_ln, post_ln), a in zip(self.layers, self.ln, self.attn):
-                _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(in_ln), S, D, C.c_float(self.eps), sh))
-                _ck(L.moty_cuda_mat_apply_dev(l.q.h, p(self.qb), p(self.nrm), S, sh))
-                _ck(L.moty_cuda_mat_apply_dev(l.k.h, p(self.kb), p(self.nrm), S, sh))
-                _ck(L.moty_cuda_mat_apply_dev(l.v.h, p(self.vb), p(self.nrm), S, sh))
-                _ck(L.moty_cuda_attn_core_dev(a.h, p(self.ctx), p(self.qb), p(self.kb), p(self.vb), S, pos_base, sh))
-                _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
-                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
-                _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(post_ln), S, D, C.c_float(self.eps), sh))
-                _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
-                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
+            self._layers(S, pos_base, None, sh)
             last = self.x[S - 1:S]
             _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(last), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
             _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
@@ -96,6 +90,80 @@ class DenseDecoder:
             if want_logits:
                 return tok, self.logits.cpu().numpy()[0]
         return tok
+
+    def _layers(self, S, pos_base, pos_dev, sh):
+        """The layers of engines/qwen.c:696-712 on self.x [S][D].  A residual add and the norm that follows it are one
+        launch (same results); with S = 1 and a fused matrix the three projections are one product."""
+        L, D, eps = lib(), self.D, C.c_float(self.eps)
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        qw, kw = self.H * self.hd, self.KV * self.hd
+        nl = len(self.layers)
+        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(self.ln[0][0]), S, D, eps, sh))
+        for i, (l, (in_ln, post_ln), a) in enumerate(zip(self.layers, self.ln, self.attn)):
+            if S == 1 and l.qkv is not None:
+                _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
+                base = self.qkvb.data_ptr()
+                qp, kp, vp = C.c_void_p(base), C.c_void_p(base + 4 * qw), C.c_void_p(base + 4 * (qw + kw))
+            else:
+                _ck(L.moty_cuda_mat_apply_dev(l.q.h, p(self.qb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.k.h, p(self.kb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.v.h, p(self.vb), p(self.nrm), S, sh))
+                qp, kp, vp = p(self.qb), p(self.kb), p(self.vb)
+            if pos_dev is None:
+                _ck(L.moty_cuda_attn_core_dev(a.h, p(self.ctx), qp, kp, vp, S, pos_base, sh))
+            else:
+                _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
+            _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
+            _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
+            _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
+            if i + 1 < nl:
+                _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(self.ln[i + 1][0]), S, D, eps, sh))
+            else:
+                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
+
+    def _decode_body(self, sh):
+        """One greedy step with everything on the device: the token comes from ``self.ids[0]``, the position from
+        ``self.pos_dev``; the new token goes to ``self.ids[0]`` and ``self.hist[self.cnt]``, position and count move on."""
+        L, D = lib(), self.D
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        _ck(L.moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), 1, C.c_float(1.0), sh))
+        self._layers(1, self.max_t - 1, self.pos_dev, sh)
+        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
+        _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
+        self.ids[:1].copy_(self.out_id)
+        self.hist.index_copy_(0, self.cnt, self.out_id)
+        self.pos_dev += 1
+        self.cnt += 1
+
+    def greedy_graph(self, first_tok, pos0, n):
+        """n greedy tokens after ``first_tok`` at position pos0, the decode step captured ONCE into a CUDA graph and
+        replayed n times (the attention core reads its position from the device).  Returns the n token ids."""
+        t = self.torch
+        if pos0 + n > self.max_t:
+            raise MotyCudaError(f"positions {pos0}..{pos0 + n} exceed the cache of {self.max_t}")
+        if getattr(self, "pos_dev", None) is None:                       # persistent: the captured graph holds their addresses
+            self.pos_dev = t.zeros((1,), device=self.dev, dtype=t.int32)
+            self.cnt = t.zeros((1,), device=self.dev, dtype=t.int64)
+            self.hist = t.zeros((self.max_t + 1,), device=self.dev, dtype=t.int32)
+
+        def reset(tok, pos):
+            self.ids[:1].fill_(int(tok)); self.pos_dev.fill_(int(pos)); self.cnt.zero_()
+
+        if getattr(self, "_graph", None) is None:
+            with t.cuda.stream(self.stream):                             # one plain run first: scratch buffers, kernel attributes
+                reset(first_tok, pos0)
+                self._decode_body(C.c_void_p(stream_handle(self.stream)))
+            self.stream.synchronize()
+            g = t.cuda.CUDAGraph()
+            with t.cuda.graph(g, stream=self.stream):
+                self._decode_body(C.c_void_p(stream_handle(t.cuda.current_stream())))
+            self._graph = g
+        with t.cuda.stream(self.stream):
+            reset(first_tok, pos0)
+            for _ in range(n):
+                self._graph.replay()
+        self.stream.synchronize()
+        return [int(v) for v in self.hist[:n].cpu().numpy()]
 
     def close(self):
         for a in self.attn:

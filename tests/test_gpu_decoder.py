@@ -86,8 +86,10 @@ def test_greedy_tokens_match_the_oracle(gpu, oracle):
                                 in_ln=np.ones(D, np.float32), post_ln=np.ones(D, np.float32),
                                 qn=np.ones(cfg["hd"], np.float32), kn=np.ones(cfg["hd"], np.float32)))
     max_t = 64
-    layers = [DenseLayer(*(gpu.Mat.i8(*l[m]) for m in ("q", "k", "v", "o", "gate", "up", "down")), l["in_ln"], l["post_ln"], l["qn"], l["kn"])
-              for l in W["layers"]]
+    fuse = lambda l: gpu.Mat.i8(np.concatenate([l[m][0] for m in "qkv"]), np.concatenate([l[m][1] for m in "qkv"]))
+    layers = [DenseLayer(*(gpu.Mat.i8(*l[m]) for m in ("q", "k", "v", "o", "gate", "up", "down")), l["in_ln"], l["post_ln"], l["qn"], l["kn"],
+                         qkv=fuse(l) if i != 1 else None)                # one layer without the fused [q|k|v] matrix
+              for i, l in enumerate(W["layers"])]
     dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t)
     om = _OracleModel(oracle, W, cfg, max_t)
     prompt = rng.integers(0, V, 9).astype(np.int32)
@@ -102,4 +104,8 @@ def test_greedy_tokens_match_the_oracle(gpu, oracle):
         assert np.abs(lg - lo).max() <= 3e-2 * np.abs(lo).max(), pos
         got.append(tg); want.append(to); pos += 1
     assert got == want
+    # the same steps from a CUDA graph captured once (the attention core reads its position from the device): same ids,
+    # also when the graph is used a second time from another position
+    assert dec.greedy_graph(got[0], len(prompt), 24) == got[1:]
+    assert dec.greedy_graph(got[4], len(prompt) + 4, 10) == got[5:15]
     dec.close()
