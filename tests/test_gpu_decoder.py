@@ -61,6 +61,15 @@ def test_kernels_of_the_layer_glue(gpu):
     torch.cuda.synchronize()
     assert L.moty_cuda_add_dev(C.c_void_p(dy.data_ptr()), C.c_void_p(dx.data_ptr()), C.c_longlong(S * D), sh) == 0
     assert same_bits(dy.cpu().numpy(), y + x)
+    # add + norm in one launch: the same bits as the two entries one after the other
+    t2 = rng.standard_normal((S, D)).astype(np.float32); dt2 = torch.from_numpy(t2).cuda()
+    a1, a2 = dy.clone(), dy.clone(); o1, o2 = torch.empty_like(dx), torch.empty_like(dx)
+    torch.cuda.synchronize()
+    P = lambda t: C.c_void_p(t.data_ptr())
+    assert L.moty_cuda_add_dev(P(a1), P(dt2), C.c_longlong(S * D), sh) == 0
+    assert L.moty_cuda_rmsnorm_dev(P(o1), P(a1), P(dw), S, D, C.c_float(1e-6), sh) == 0
+    assert L.moty_cuda_add_rmsnorm_dev(P(a2), P(dt2), P(o2), P(dw), S, D, C.c_float(1e-6), sh) == 0
+    assert same_bits(a1.cpu().numpy(), a2.cpu().numpy()) and same_bits(o1.cpu().numpy(), o2.cpu().numpy())
     q = rng.integers(-127, 128, (V, D), dtype=np.int8); qs = rng.uniform(0.001, 0.02, V).astype(np.float32)
     E = gpu.Mat.i8(q, qs)
     ids = np.array([3, 76, 0, 3, 41], np.int32); dids = torch.from_numpy(ids).cuda()
