@@ -578,6 +578,45 @@ def run_case(args):
             us = time_moe(torch, layers, name, S, dev, stream, reps=max(1, args.steps // 16), run=16)
         print(json.dumps({"case": args.case, "us_per_layer": round(us, 2)}), flush=True)
         return
+    if parts[0] == "decode" and parts[1] == "olmoe":    # decode:olmoe[:NGEN] -- configs[2] shape: int8 attention matrices and experts
+        import time
+        from moty_b200.decoder import DenseDecoder, DenseLayer
+        ngen = int(parts[2]) if len(parts) > 2 else 256
+        NL, D, H, hd, V, PROMPT = 16, 2048, 16, 128, 50304, 512
+        E, K, I, _, _ = MOE_SHAPES["olmoe"]
+        moes, per_expert = make_moe_layers(mb, "olmoe", 4, 0, rng)          # four expert sets, cycled over the 16 layers
+        for m in moes:
+            m.set_router(mb.Mat.f32((rng.standard_normal((E, D)) * 0.02).astype(np.float32), device=0))
+        one = lambda n: np.ones(n, np.float32)
+        raw = lambda O, Kk: (rng.integers(-127, 128, (O, Kk), dtype=np.int8), rng.uniform(0.0002, 0.0006, O).astype(np.float32))
+        layers = []
+        for i in range(NL):
+            q, k, v = raw(H * hd, D), raw(H * hd, D), raw(H * hd, D)
+            qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=0)
+            layers.append(DenseLayer(mb.Mat.i8(*q, device=0), mb.Mat.i8(*k, device=0), mb.Mat.i8(*v, device=0), mb.Mat.i8(*raw(D, H * hd), device=0),
+                                     None, None, None, one(D), one(D), one(hd), one(hd), qkv=qkv, moe=moes[i % 4], norm_topk=0))
+        head = mb.Mat.i8(rng.integers(-127, 128, (V, D), dtype=np.int8), rng.uniform(0.005, 0.015, V).astype(np.float32), device=0)
+        dec = DenseDecoder(layers, head, one(D), H, H, hd, PROMPT + ngen + 8, max_S=PROMPT)
+        prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
+        dec.step(prompt, 0); dec.step([1], PROMPT)
+        torch.cuda.synchronize(); t0 = time.perf_counter()
+        tok = dec.step(prompt, 0)
+        torch.cuda.synchronize(); t1 = time.perf_counter()
+        toks = [tok]
+        for i in range(ngen):
+            toks.append(dec.step([toks[-1]], PROMPT + i))
+        torch.cuda.synchronize(); t2 = time.perf_counter()
+        tg = dec.greedy_graph(tok, PROMPT, ngen)
+        torch.cuda.synchronize(); t3 = time.perf_counter()
+        tg = dec.greedy_graph(tok, PROMPT, ngen)
+        torch.cuda.synchronize(); t4 = time.perf_counter()
+        wbytes = NL * (K * per_expert + 4 * D * H * hd + 4 * E * D) + head.nbytes()
+        print(json.dumps({"case": args.case, "prefill_tok_s": round(PROMPT / (t1 - t0), 1), "decode_tok_s": round(ngen / (t2 - t1), 1),
+                          "ms_per_token": round((t2 - t1) / ngen * 1e3, 3), "weight_MB_per_token": round(wbytes / 1e6, 1),
+                          "graph_decode_tok_s": round(ngen / (t4 - t3), 1), "graph_ms_per_token": round((t4 - t3) / ngen * 1e3, 3),
+                          "graph_GBs": round(wbytes * ngen / (t4 - t3) / 1e9, 1), "graph_equals_direct": tg == toks[1:]}), flush=True)
+        dec.close()
+        return
     if parts[0] == "decode":                            # decode:qwen3-0.6b[:NGEN] -- configs[0] shape, synthetic int8 weights
         import time
         from moty_b200.decoder import DenseDecoder, DenseLayer
@@ -700,7 +739,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8] the attention core with S tokens at position POS; ep:NAME:S under torchrun times the "
+                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder, decode:olmoe[:NGEN] a 512-token prompt and NGEN steps of the configs[2]-shaped MoE decoder; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8] the attention core with S tokens at position POS; ep:NAME:S under torchrun times the "
                                                 "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:

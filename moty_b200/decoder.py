@@ -25,12 +25,15 @@ def _ck(rc):
 class DenseLayer:
     """One layer's weights: int8 matrices (q, k, v, o, gate, up, down) and f32 norm gains."""
 
-    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_ln, qn=None, kn=None, qkv=None):
+    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_ln, qn=None, kn=None, qkv=None, moe=None, norm_topk=1):
         self.q, self.k, self.v, self.o, self.gate, self.up, self.down = q, k, v, o, gate, up, down
         self.in_ln, self.post_ln, self.qn, self.kn = in_ln, post_ln, qn, kn
         # optional: the rows of q, k and v in one matrix (the reference's fused [q|k|v], nn/attn.h:24): one product
         # per decode token instead of three; per-row quantization makes the concatenation exact
         self.qkv = qkv
+        # optional: a routed layer (moty_b200.Moe with its router set) in place of the dense FFN, combined per token in
+        # selection order as engines/olmoe.c:219-244 does; gate/up/down may then be None
+        self.moe, self.norm_topk = moe, norm_topk
 
 
 class DenseDecoder:
@@ -45,7 +48,6 @@ class DenseDecoder:
         self.layers, self.head = layers, head
         self.H, self.KV, self.hd, self.eps, self.max_t = n_heads, n_kv_heads, head_dim, float(eps), max_t
         self.D = head.I
-        self.I = layers[0].gate.O
         f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
         self.final_norm = f(final_norm)
         self.ln = [(f(l.in_ln), f(l.post_ln)) for l in layers]
@@ -115,7 +117,10 @@ class DenseDecoder:
                 _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
             _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
             _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
-            _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
+            if l.moe is not None:
+                _ck(L.moty_cuda_moe_apply_dev(l.moe.h, p(self.tmp), p(self.nrm), S, None, 0, l.norm_topk, None, None, sh))
+            else:
+                _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
             if i + 1 < nl:
                 _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(self.ln[i + 1][0]), S, D, eps, sh))
             else:

@@ -118,3 +118,51 @@ def test_greedy_tokens_match_the_oracle(gpu, oracle):
     assert dec.greedy_graph(got[0], len(prompt), 24) == got[1:]
     assert dec.greedy_graph(got[4], len(prompt) + 4, 10) == got[5:15]
     dec.close()
+
+
+def test_greedy_tokens_match_with_routed_layers(gpu, oracle):
+    """The same with routed layers in place of the dense FFN (8 experts, top-2, combined per token in selection order as
+    engines/olmoe.c:219-244 does; the router logits come from an f32 router matrix): prompt of 6 tokens, 12 greedy steps."""
+    from moty_b200.decoder import DenseDecoder, DenseLayer
+    from oracle import AttnCache, Experts
+    rng = np.random.default_rng(21)
+    H, KV, hd, D, I, V, NL, E, K = 4, 4, 32, 128, 64, 500, 2, 8, 2
+    mk = lambda O, Kk: (rng.integers(-127, 128, (O, Kk), dtype=np.int8), rng.uniform(0.0005, 0.0015, O).astype(np.float32))
+    hq, hs = mk(V, D); hs = (hs * 20).astype(np.float32)
+    ones = lambda n: np.ones(n, np.float32)
+    Ls, layers = [], []
+    for _ in range(NL):
+        l = dict(q=mk(H * hd, D), k=mk(KV * hd, D), v=mk(KV * hd, D), o=mk(D, H * hd), R=(rng.standard_normal((E, D)) * 0.5).astype(np.float32))
+        g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
+        d = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
+        gs, us = (rng.uniform(0.0005, 0.0015, (E, I)).astype(np.float32) for _ in range(2))
+        ds = rng.uniform(0.0005, 0.0015, (E, D)).astype(np.float32)
+        l["ex"] = Experts(E, K, I, D, g, u, d, gs, us, ds)
+        m = gpu.Moe(E, K, I, D)
+        for e in range(E):
+            m.upload_expert(e, g[e], gs[e], u[e], us[e], d[e], ds[e])
+        m.set_router(gpu.Mat.f32(l["R"]))
+        Ls.append(l)
+        layers.append(DenseLayer(*(gpu.Mat.i8(*l[k]) for k in "qkvo"), None, None, None, ones(D), ones(D), ones(hd), ones(hd), moe=m, norm_topk=0))
+    max_t = 32
+    dec = DenseDecoder(layers, gpu.Mat.i8(hq, hs), ones(D), H, KV, hd, max_t)
+    caches = [AttnCache(H, KV, hd, max_t, qn=ones(hd), kn=ones(hd)) for _ in Ls]
+
+    def ostep(ids, pos):
+        x = np.stack([(hs[i] * np.float32(1.0)) * hq[i].astype(np.float32) for i in ids]).astype(np.float32)
+        for l, cache in zip(Ls, caches):
+            n = _rmsnorm(x, ones(D), 1e-6)
+            q, k, v = (oracle.matmul_q_s(n, *l[m]) for m in "qkv")
+            x = x + oracle.matmul_q_s(oracle.attn_core(q, k, v, pos, cache), *l["o"])
+            n = _rmsnorm(x, ones(D), 1e-6)
+            logits = (n.astype(np.float64) @ l["R"].astype(np.float64).T).astype(np.float32)
+            x = x + oracle.olmoe_moe(l["ex"], n, logits, 0)[0]
+        return oracle.argmax(oracle.matmul_q_s(_rmsnorm(x[-1:], ones(D), 1e-6), hq, hs)[0])
+
+    prompt = rng.integers(0, V, 6).astype(np.int32)
+    got, want = [dec.step(prompt, 0)], [ostep(prompt, 0)]
+    for i in range(12):
+        got.append(dec.step([got[-1]], 6 + i)); want.append(ostep([want[-1]], 6 + i))
+    assert got == want
+    assert dec.greedy_graph(got[0], 6, 12) == got[1:]
+    dec.close()
