@@ -6,37 +6,42 @@
 
 namespace {
 
-// one CTA per row: mean of squares in double, r = 1 / sqrtf((float)(ms / n) + eps), out = (x * r) * w
-__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *out, const float *x, const float *w, int D, float eps) {
-    __shared__ double red[8];
-    pdl_trigger();
-    pdl_wait();
-    const float *xr = x + (size_t)blockIdx.x * D;
-    float *orow = out + (size_t)blockIdx.x * D;
-    double ms = 0;
-    for (int i = threadIdx.x; i < D; i += 256) { const double v = xr[i]; ms += v * v; }
-    for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
-    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ms;
-    __syncthreads();
-    ms = 0;
-    for (int i = 0; i < 8; i++) ms += red[i];
-    const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
-    for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);
-}
+// One CTA per row: x (+ t), mean of squares in double, r = 1 / sqrtf((float)(ms / n) + eps), out = (x * r) * w.
+// Rows of up to 2048 values stay in registers and the gains are requested with them, so the kernel is one memory
+// round trip; longer rows are re-read.  ADD: x += t first (hw/hw_ops.h:30-32), the sum is written back.
+constexpr int NR_PER = 8;
 
-// the residual add and the next norm in one pass over the row: x += t (hw/hw_ops.h:30-32), out = rmsnorm(x) as above
-__global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float *x, const float *t, float *out, const float *w, int D, float eps) {
+template <bool ADD>
+__global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *x, const float *t, float *out, const float *w, int D, float eps) {
     __shared__ double red[8];
     pdl_trigger();
     pdl_wait();
     float *xr = x + (size_t)blockIdx.x * D;
-    const float *tr = t + (size_t)blockIdx.x * D;
+    const float *tr = ADD ? t + (size_t)blockIdx.x * D : nullptr;
     float *orow = out + (size_t)blockIdx.x * D;
+    const bool in_regs = D <= 256 * NR_PER;
+    float v[NR_PER], wv[NR_PER];
     double ms = 0;
-    for (int i = threadIdx.x; i < D; i += 256) {
-        const float v = __fadd_rn(xr[i], tr[i]);
-        xr[i] = v;
-        ms += (double)v * (double)v;
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < NR_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            v[j] = i < D ? xr[i] : 0.f;
+            wv[j] = i < D ? w[i] : 0.f;
+            if (ADD && i < D) v[j] = __fadd_rn(v[j], tr[i]);
+        }
+#pragma unroll
+        for (int j = 0; j < NR_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (ADD && i < D) xr[i] = v[j];
+            ms += (double)v[j] * (double)v[j];
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += 256) {
+            float a = xr[i];
+            if (ADD) { a = __fadd_rn(a, tr[i]); xr[i] = a; }
+            ms += (double)a * (double)a;
+        }
     }
     for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
     if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ms;
@@ -44,7 +49,15 @@ __global__ void __launch_bounds__(256) add_rmsnorm_rows_kernel(float *x, const f
     ms = 0;
     for (int i = 0; i < 8; i++) ms += red[i];
     const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
-    for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);   // the thread's own writes above
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < NR_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < D) orow[i] = __fmul_rn(__fmul_rn(v[j], r), wv[j]);
+        }
+    } else {
+        for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], r), w[i]);   // the thread's own writes above
+    }
 }
 
 __global__ void __launch_bounds__(256) add_kernel(float *y, const float *x, long long n) {
@@ -70,14 +83,14 @@ __global__ void __launch_bounds__(256) embed_rows_kernel(float *dst, const int8_
 int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps, cudaStream_t st) {
     if (S <= 0) return 0;
     if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "rmsnorm: D=%d", D);
-    CK(moty_launch_pdl(rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, out, x, w, D, eps));
+    CK(moty_launch_pdl(rmsnorm_rows_kernel<false>, dim3(S), dim3(256), (size_t)0, st, const_cast<float *>(x), (const float *)nullptr, out, w, D, eps));
     return 0;
 }
 
 int launch_add_rmsnorm_rows(float *x, const float *t, float *out, const float *w, int S, int D, float eps, cudaStream_t st) {
     if (S <= 0) return 0;
     if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "add_rmsnorm: D=%d", D);
-    CK(moty_launch_pdl(add_rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, x, t, out, w, D, eps));
+    CK(moty_launch_pdl(rmsnorm_rows_kernel<true>, dim3(S), dim3(256), (size_t)0, st, x, t, out, w, D, eps));
     return 0;
 }
 
