@@ -276,7 +276,9 @@ int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float
                             int S, int pos_base, void *stream);
 /* The same with the first position read from a device int at run time: a decode step captured once into a CUDA graph
  * is replayed while the position moves.  pos_max = the largest value *pos_dev may take (it sizes the launch);
- * pos_max + S must fit the cache.  Results equal attn_core_dev at the same position. */
+ * pos_max + S must fit the cache.  Results equal attn_core_dev at the same position.  With S = 1 the norm, the rotation
+ * and the cache store happen inside the scores launch (one launch less per decode step) and q_dev, k_dev are left as
+ * they came instead of being rotated in place. */
 int moty_cuda_attn_core_posdev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,
                                int S, const int *pos_dev, int pos_max, void *stream);
 /* the last step of the gated variant (moty_nn_attention_gated, nn/attn.c:68-69): ctx[i] *= 1 / (1 + expf(-gate[i])),

@@ -335,6 +335,12 @@ class Attn:
         _ck(lib().moty_cuda_attn_core_dev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
                                           S, pos_base, C.c_void_p(stream)))
 
+    def core_posdev(self, ctx_ptr, q_ptr, k_ptr, v_ptr, S, pos_dev_ptr, pos_max, stream=0):
+        """The same with the first position read from a device int32 (for CUDA graph replay); pos_max bounds it.  With
+        S = 1 the whole core is one scores launch (plus the merge) and q, k are NOT written back."""
+        _ck(lib().moty_cuda_attn_core_posdev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(q_ptr), C.c_void_p(k_ptr), C.c_void_p(v_ptr),
+                                             S, C.c_void_p(pos_dev_ptr), pos_max, C.c_void_p(stream)))
+
     def gate_dev(self, ctx_ptr, gate_ptr, S, stream=0):
         """ctx *= sigmoid(gate) (moty_nn_attention_gated's last step), both [S][H*hd] on the device."""
         _ck(lib().moty_cuda_attn_gate_dev(self.h, C.c_void_p(ctx_ptr), C.c_void_p(gate_ptr), S, C.c_void_p(stream)))

@@ -141,7 +141,11 @@ __device__ __forceinline__ void attn_reduce(float (&v)[N], int lane) {
 
 // NV = float4 rounds a lane needs to cover a head: lane l holds dimensions 128 r + 4 l .. + 3 (head_dim <= 128 NV)
 // NH = query heads whose dots are formed per key row (2 when a KV head serves at most two, else 4)
-template <int NV, int NH>
+// FUSE (one token, position on the device): the work of attn_prep_kernel happens here, so a decode step is one launch
+// less.  Every CTA norms and rotates its own query heads into shared memory (a warp per head; q and k in global memory
+// are left as they came), and the CTA whose positions include the token's own also norms and rotates the key row and
+// stores key and value rows in the cache before the block-wide barrier; it then reads them back like any other row.
+template <int NV, int NH, bool FUSE>
 __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_kernel(AttnArgs a, int nsplit, int span, float *part) {
     extern __shared__ float sm_attn[];
     __shared__ float m_s[AT_G], l_s[AT_G], f_s[AT_G];
@@ -154,12 +158,105 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     int t_hi = t_lo + span < n ? t_lo + span : n;
     const size_t base = (size_t)kvh * a.max_t;
     float *qs = sm_attn, *sc = qs + AT_G * NV * 128, *ps = sc + AT_G * AT_CH;   // q[AT_G][NV*128], sc[AT_G][AT_CH], partial[warps][AT_G][NV*128]
+    // FUSE: warps past AT_G form the rotation table; theta^(2 j / rot) needs no input, so it is ready before the wait
+    constexpr int ROPE_T = (AT_WARPS - AT_G - 1) * 32;                  // rot / 2 <= 128 <= 2 ROPE_T
+    float den0 = 1.f, den1 = 1.f;
+    if (FUSE && warp > AT_G) {
+        const int jj = tid - (AT_G + 1) * 32;
+        den0 = powf(a.theta, __fdiv_rn((float)(2 * jj), (float)a.rot));
+        den1 = powf(a.theta, __fdiv_rn((float)(2 * (jj + ROPE_T)), (float)a.rot));
+    }
     pdl_trigger();
-    pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel
+    pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel (without FUSE)
     if (a.pos_dev) { n = *a.pos_dev + s + 1; t_hi = t_lo + span < n ? t_lo + span : n; }
-    for (int i = tid; i < AT_G * NV * 128; i += AT_WARPS * 32) {
-        const int g = i / (NV * 128), dd = i - g * (NV * 128);
-        qs[i] = g < ng && dd < hd ? a.q[(size_t)s * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
+    if (FUSE) {
+        const int pos = n - 1;
+        const bool own = pos >= t_lo && pos < t_lo + span;
+        for (int i = ng * NV * 128 + tid; i < AT_G * NV * 128; i += AT_WARPS * 32) qs[i] = 0.f;
+        constexpr int NJ = NV * 4;                                      // lane l holds dimensions l + 32 j
+        const bool mine = warp < ng || (warp == AT_G && own), isq = warp < ng;
+        const int half = a.rot / 2;
+        float *xs = ps + warp * (NV * 128);
+        float x[NJ];
+        if (mine) {
+            const float *row = isq ? a.q + (size_t)(head0 + warp) * hd : a.k + (size_t)kvh * hd;
+            const float *nw = isq ? a.qn : a.kn;
+            double ss = 0.0;
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {
+                const int d = lane + 32 * j;
+                x[j] = d < hd ? row[d] : 0.f;
+                ss += (double)x[j] * (double)x[j];
+            }
+            if (nw) {                                                   // hw/hw_ops.h:14-18
+                for (int off = 16; off > 0; off >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+                const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ss / hd), a.eps)));
+#pragma unroll
+                for (int j = 0; j < NJ; j++) {
+                    const int d = lane + 32 * j;
+                    if (d < hd) x[j] = __fmul_rn(__fmul_rn(x[j], r), nw[d]);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < NJ; j++) xs[lane + 32 * j] = x[j];
+        } else if (warp > AT_G) {                                       // the other warps: cos and sin of the rot / 2 angles, once
+            const int jj = tid - (AT_G + 1) * 32;                       // nn/rope.c:39-44
+            if (jj < half) { const float an = __fdiv_rn((float)pos, den0); sc[jj] = cosf(an); sc[128 + jj] = sinf(an); }
+            if (jj + ROPE_T < half) { const float an = __fdiv_rn((float)pos, den1); sc[jj + ROPE_T] = cosf(an); sc[128 + jj + ROPE_T] = sinf(an); }
+        }
+        __syncthreads();
+        if (mine) {
+#pragma unroll
+            for (int j = 0; j < NJ; j++) {                              // nn/rope.c:45-49
+                const int d = lane + 32 * j;
+                if (d < a.rot) {
+                    const int jj = d < half ? d : d - half;
+                    const float c = sc[jj], sn = sc[128 + jj];
+                    const float lo = xs[jj], hi = xs[jj + half];
+                    x[j] = d < half ? __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)) : __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
+                }
+            }
+            if (isq) {
+#pragma unroll
+                for (int j = 0; j < NJ; j++) qs[warp * NV * 128 + lane + 32 * j] = x[j];   // zero past the head
+            } else {                                                    // KV store (nn/attn.c:49-60)
+                const size_t slotp = base + pos;
+                float vv[NJ];
+#pragma unroll
+                for (int j = 0; j < NJ; j++) vv[j] = lane + 32 * j < hd ? a.v[(size_t)kvh * hd + lane + 32 * j] : 0.f;
+                if (a.K8) {                                             // nn/mat.c:15-17: qrow_i8 per row
+                    float ak = 0.f, av = 0.f;
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) { ak = fmaxf(ak, fabsf(x[j])); av = fmaxf(av, fabsf(vv[j])); }
+                    for (int off = 16; off > 0; off >>= 1) {
+                        ak = fmaxf(ak, __shfl_xor_sync(0xffffffffu, ak, off));
+                        av = fmaxf(av, __shfl_xor_sync(0xffffffffu, av, off));
+                    }
+                    const float sk = quant_scale(ak, 1e-12f), ik = __fdiv_rn(1.f, sk);
+                    const float sv = quant_scale(av, 1e-12f), iv = __fdiv_rn(1.f, sv);
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) {
+                        const int d = lane + 32 * j;
+                        if (d < hd) {
+                            a.K8[slotp * hd + d] = (int8_t)quant_code(x[j], ik);
+                            a.V8[slotp * hd + d] = (int8_t)quant_code(vv[j], iv);
+                        }
+                    }
+                    if (lane == 0) { a.Ks[slotp] = sk; a.Vs[slotp] = sv; }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) {
+                        const int d = lane + 32 * j;
+                        if (d < hd) { a.K[slotp * hd + d] = x[j]; a.V[slotp * hd + d] = vv[j]; }
+                    }
+                }
+            }
+        }
+    } else {
+        for (int i = tid; i < AT_G * NV * 128; i += AT_WARPS * 32) {
+            const int g = i / (NV * 128), dd = i - g * (NV * 128);
+            qs[i] = g < ng && dd < hd ? a.q[(size_t)s * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
+        }
     }
     if (tid < AT_G) { m_s[tid] = -1e30f; l_s[tid] = 0.f; }
     bool dv[NV];                                                        // does round r of this lane lie inside the head
@@ -486,7 +583,10 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     a.S = S; a.pos_base = pos_base; a.H = H; a.KV = KV; a.hd = hd; a.rot = rot; a.max_t = max_t;
     a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd); a.pos_dev = pos_dev;
     const int nth_prep = (hd + 31) / 32 * 32;
-    CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
+    // one token at a position read from the device (a replayed decode step): norm, rotation and cache store ride in the
+    // scores launch, and q and k are not written back
+    const bool fuse = pos_dev && S == 1;
+    if (!fuse) CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
     const int NVr = hd > 128 ? 2 : 1;
     const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;
     const int G = H / KV, ngy = (G + AT_G - 1) / AT_G, T = pos_base + S;
@@ -523,18 +623,27 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "attn_core: device %d", dev);
     if (!attr_done[dev]) {
-        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
-        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 2, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<1, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 2, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+        CK(cudaFuncSetAttribute(attn_flash_kernel<2, 4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
         attr_done[dev] = true;
     }
     if ((unsigned)S > 65535u) return moty_set_error(MOTY_CUDA_ELIMIT, "attn_core: S=%d in one call", S);
     const dim3 fgrid(nsplit, KV * ngy, S), fblock(AT_WARPS * 32);
-    if (NVr == 1 && G <= 2) CK(moty_launch_pdl(attn_flash_kernel<1, 2>, fgrid, fblock, smem, st, a, nsplit, span, part));
-    else if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1, 4>, fgrid, fblock, smem, st, a, nsplit, span, part));
-    else if (G <= 2) CK(moty_launch_pdl(attn_flash_kernel<2, 2>, fgrid, fblock, smem, st, a, nsplit, span, part));
-    else CK(moty_launch_pdl(attn_flash_kernel<2, 4>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    if (fuse) {
+        if (NVr == 1 && G <= 2) CK(moty_launch_pdl(attn_flash_kernel<1, 2, true>, fgrid, fblock, smem, st, a, nsplit, span, part));
+        else if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1, 4, true>, fgrid, fblock, smem, st, a, nsplit, span, part));
+        else if (G <= 2) CK(moty_launch_pdl(attn_flash_kernel<2, 2, true>, fgrid, fblock, smem, st, a, nsplit, span, part));
+        else CK(moty_launch_pdl(attn_flash_kernel<2, 4, true>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    } else if (NVr == 1 && G <= 2) CK(moty_launch_pdl(attn_flash_kernel<1, 2, false>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else if (NVr == 1) CK(moty_launch_pdl(attn_flash_kernel<1, 4, false>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else if (G <= 2) CK(moty_launch_pdl(attn_flash_kernel<2, 2, false>, fgrid, fblock, smem, st, a, nsplit, span, part));
+    else CK(moty_launch_pdl(attn_flash_kernel<2, 4, false>, fgrid, fblock, smem, st, a, nsplit, span, part));
     if (nsplit > 1)
         CK(moty_launch_pdl(attn_merge_kernel, dim3(S, H), dim3(nth_prep), (size_t)nsplit * 4, st, a, nsplit, (const float *)part));
     return 0;

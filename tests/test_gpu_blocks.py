@@ -101,6 +101,39 @@ def test_attn_core_vs_oracle(gpu, oracle, H, KV, hd, rot, kv8):
                                     np.zeros((9, KV * hd), np.float32), 0)
 
 
+@pytest.mark.parametrize("H,KV,hd,rot,kv8,T0", [(16, 8, 128, 128, False, 700), (16, 8, 128, 128, True, 700), (8, 2, 64, 32, False, 40),
+                                                 (4, 4, 256, 256, False, 300), (12, 2, 96, 96, True, 1500), (16, 2, 128, 64, False, 5)])
+def test_attn_decode_one_launch_equals_two(gpu, H, KV, hd, rot, kv8, T0):
+    """One token at a position read from the device: norm, rotation and cache store inside the scores launch.  Same
+    context rows and same cache rows as the prep + scores pair of attn_core_dev, step after step (the f64 sum of squares
+    is taken in another order, hence 1e-6 and not bit for bit), and q, k stay as they came."""
+    import torch
+    rng = np.random.default_rng(H * 1000 + hd + T0)
+    max_t = T0 + 8
+    qn = rng.uniform(0.5, 1.5, hd).astype(np.float32); kn = rng.uniform(0.5, 1.5, hd).astype(np.float32)
+    a = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8)
+    b = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8)
+    f = lambda *sh: rng.standard_normal(sh).astype(np.float32)
+    q0, k0, v0 = f(T0, H * hd), f(T0, KV * hd), f(T0, KV * hd)
+    a.core(q0.copy(), k0.copy(), v0, 0); b.core(q0.copy(), k0.copy(), v0, 0)        # the same prompt in both caches
+    sh = gpu.stream_handle(torch.cuda.current_stream())
+    pos_dev = torch.zeros((1,), dtype=torch.int32, device="cuda")
+    tol = 2e-3 if kv8 else 2e-6
+    for step in range(6):
+        q, k, v = f(1, H * hd), f(1, KV * hd), f(1, KV * hd)
+        da = [torch.from_numpy(t.copy()).cuda() for t in (q, k, v)]
+        db = [torch.from_numpy(t.copy()).cuda() for t in (q, k, v)]
+        ca = torch.empty((1, H * hd), device="cuda"); cb = torch.empty((1, H * hd), device="cuda")
+        pos_dev.fill_(T0 + step)
+        a.core_dev(ca.data_ptr(), da[0].data_ptr(), da[1].data_ptr(), da[2].data_ptr(), 1, T0 + step, stream=sh)
+        b.core_posdev(cb.data_ptr(), db[0].data_ptr(), db[1].data_ptr(), db[2].data_ptr(), 1, pos_dev.data_ptr(), max_t - 1, stream=sh)
+        torch.cuda.synchronize()
+        ya, yb = ca.cpu().numpy(), cb.cpu().numpy()
+        assert np.isfinite(yb).all() and np.abs(ya - yb).max() <= tol * np.abs(ya).max(), (step, np.abs(ya - yb).max())
+        assert np.array_equal(db[0].cpu().numpy(), q) and np.array_equal(db[1].cpu().numpy(), k)
+    a.close(); b.close()
+
+
 def test_attn_gate_and_device_entry(gpu, oracle):
     """The device-pointer entry on torch buffers (q and k are normed and rotated in place, as the reference does) and
     the gated variant's last step, ctx *= 1 / (1 + expf(-gate)) (nn/attn.c:68-69)."""
