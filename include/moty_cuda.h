@@ -253,6 +253,13 @@ int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *strea
  * (same results as add_dev followed by rmsnorm_dev). */
 int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
                               float eps, void *stream);
+/* The same add and norm folded into the decode product that consumes them (one launch instead of two):
+ * y = W * rmsnorm(x + t) with gains gain_dev, and xout = x + t (xout_dev apart from x_dev: every CTA reads x).
+ * One row; MOTY_WF_I8 matrices with I <= 4096, I a multiple of 16 (mat_addnorm_supported says whether a matrix
+ * qualifies).  Same bits as add_rmsnorm_dev followed by mat_apply_dev. */
+int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w);
+int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
+                                    float *xout_dev, const float *gain_dev, float eps, void *stream);
 int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream);
 
 /* ---- attention core between the projections --------------------------------

@@ -401,6 +401,26 @@ extern "C" int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float
     return mat_apply_on(c, w, y_dev, x_dev, S, nullptr, pick_stream(c, stream));
 }
 
+// One decode row through a MOTY_WF_I8 matrix with the residual add and the RMS norm before it in the same launch:
+// y = W * q(rmsnorm(x + t) * g), xout = x + t.  Same bits as add_rmsnorm_dev followed by mat_apply_dev.
+extern "C" int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w) {
+    return w && w->fmt == MOTY_WF_I8 && w->I % 16 == 0 && w->I <= 4096;
+}
+
+extern "C" int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
+                                               float *xout_dev, const float *gain_dev, float eps, void *stream) {
+    if (!w || !y_dev || !x_dev || !t_dev || !xout_dev || !gain_dev)
+        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: null argument");
+    if (!moty_cuda_mat_addnorm_supported(w) || xout_dev == x_dev || ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(t_dev)) & 15))
+        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: wants a MOTY_WF_I8 matrix with I <= 4096 (a multiple of 16) and xout apart from x");
+    DevCtx *c = moty_ctx(w->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
+    CK(cudaSetDevice(w->device));
+    return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, x_dev, nullptr, nullptr, y_dev, nullptr,
+                            1, w->I, w->O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, pick_stream(c, stream),
+                            t_dev, gain_dev, xout_dev, eps);
+}
+
 // host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
 static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
     if (!w || !y || !x) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: null argument");

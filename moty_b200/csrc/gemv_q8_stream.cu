@@ -18,6 +18,7 @@
 struct StreamArgs {
     const int8_t *w; const float *scale;
     const float *x;                 // FUSED: f32 row
+    const float *t, *g; float *xout; float eps;   // FUSED, optional: the row is rmsnorm(x + t) * g, and x + t goes to xout
     const int8_t *xi; const float *sx;   // not fused: quantized rows [S][I] and their scales
     float *y; int32_t *acc_out;     // [S][O]
     unsigned long long *cell;       // K-split cells [S][O], all 0 between launches
@@ -48,6 +49,7 @@ __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(Strea
     extern __shared__ int4 smem4[];
     __shared__ float red[8];
     __shared__ float sx_s[NS];
+    __shared__ double red64[8];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int I = a.I, I16 = I / 16, O = a.O, KS = a.KS, SEG = a.seg;
     const int nrg = (O + R - 1) / R;
@@ -92,6 +94,52 @@ __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(Strea
         float *xf = reinterpret_cast<float *>(xq_s + I);
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         float amax = 0.f;
+        if (a.t) {
+            // residual add and RMS norm first (hw/hw_ops.h:30-32 and 14-18), element for element and sum for sum as the
+            // separate add+norm launch does them, so both routes give the same bits.  Every CTA forms the row for
+            // itself; CTA 0 also writes the sum out (to another buffer: the others are still reading x).  I <= 4096.
+            // Loads go out four rounds at a time (a row of 1024 is one round trip), the gains of the first four with them.
+            double ms = 0;
+            float gv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) { const int i = threadIdx.x + 256 * j; gv[j] = i < I ? a.g[i] : 0.f; }
+            for (int i0 = threadIdx.x; i0 < I; i0 += 1024) {
+                float xv[4], tv[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) { const int i = i0 + 256 * j; xv[j] = i < I ? a.x[i] : 0.f; tv[j] = i < I ? a.t[i] : 0.f; }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int i = i0 + 256 * j;
+                    if (i < I) {
+                        const float v = __fadd_rn(xv[j], tv[j]);
+                        xf[i] = v;
+                        if (blockIdx.x == 0) a.xout[i] = v;
+                        ms += (double)v * (double)v;
+                    }
+                }
+            }
+            for (int off = 16; off > 0; off >>= 1) ms += __shfl_xor_sync(0xffffffffu, ms, off);
+            if (lane == 0) red64[warp] = ms;
+            __syncthreads();
+            ms = 0;
+            for (int i = 0; i < 8; i++) ms += red64[i];
+            const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / I), a.eps)));
+            for (int i0 = threadIdx.x; i0 < I; i0 += 1024) {
+                if (i0 >= 1024) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) { const int i = i0 + 256 * j; gv[j] = i < I ? a.g[i] : 0.f; }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int i = i0 + 256 * j;
+                    if (i < I) {
+                        const float nv = __fmul_rn(__fmul_rn(xf[i], r), gv[j]);
+                        xf[i] = nv;
+                        amax = fmaxf(amax, fabsf(nv));
+                    }
+                }
+            }
+        } else
         for (int i = threadIdx.x; i < I / 4; i += 256) {
             float4 v = x4[i];
             if (stage) reinterpret_cast<float4 *>(xf)[i] = v;
@@ -212,11 +260,14 @@ static int launch_ns(const StreamArgs &a, int lpr, int sms, cudaStream_t st) {
 // between launches) or null when I <= 4096.
 int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const int8_t *xi, const float *sx,
                      float *y, int32_t *acc, int S, int I, int O, int *counters, unsigned long long *cell,
-                     int sms, cudaStream_t st) {
+                     int sms, cudaStream_t st, const float *t, const float *g, float *xout, float eps) {
     if (I % 16 != 0 || I > MOTY_QROW_MAX || S < 1 || S > 8) return moty_set_error(MOTY_CUDA_EARG, "q8_stream: S=%d I=%d", S, I);
+    if (t && (S != 1 || !x || !g || !xout || xout == x || I > 4096))
+        return moty_set_error(MOTY_CUDA_EARG, "q8_stream: add+norm wants one f32 row of at most 4096 values and its own output");
     if (O <= 0) return 0;
     StreamArgs a;
     a.w = w; a.scale = scale; a.x = x; a.xi = xi; a.sx = sx; a.y = y; a.acc_out = acc;
+    a.t = t; a.g = g; a.xout = xout; a.eps = eps;
     a.cell = cell; (void)counters;
     a.S = S; a.I = I; a.O = O;
     int I16 = I / 16;

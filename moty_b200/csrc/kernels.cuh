@@ -45,7 +45,8 @@ int gemv_q8_init_device();
 // persistent streaming GEMV for 1..8 rows; S == 1 quantizes x (f32) in the kernel
 int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const int8_t *xi, const float *sx,
                      float *y, int32_t *acc, int S, int I, int O, int *counters, unsigned long long *cell,
-                     int sms, cudaStream_t st);
+                     int sms, cudaStream_t st, const float *t = nullptr, const float *g = nullptr, float *xout = nullptr,
+                     float eps = 0.f);   // t (S == 1, I <= 4096): the row is rmsnorm(x + t) * g, and x + t goes to xout
 int q4r4_init_device();
 
 // ---- gemm_q8_tc.cu --------------------------------------------------------------

@@ -41,13 +41,17 @@ class DenseDecoder:
     ``Mat`` (MOTY_WF_I8 [vocab][D]; with tied embeddings it is also the embedding table); ``final_norm`` [D]."""
 
     def __init__(self, layers, head: Mat, final_norm, n_heads, n_kv_heads, head_dim, max_t, theta=1e6, eps=1e-6,
-                 rot=None, kv8=False, device=0, max_S=64):
+                 rot=None, kv8=False, device=0, max_S=64, fold_addnorm=None):
         import torch
         self.torch = torch
         self.dev = torch.device(f"cuda:{device}")
         self.layers, self.head = layers, head
         self.H, self.KV, self.hd, self.eps, self.max_t = n_heads, n_kv_heads, head_dim, float(eps), max_t
         self.D = head.I
+        # fold the add+norm before a layer's [q|k|v] product into that product's launch: measured a gain at hidden 2048
+        # (1196 -> 1247 tok/s replayed) and a small loss at hidden 1024 (1245 -> 1232: every CTA of the product then reads
+        # three shared rows instead of one), so by default only from 2048 up
+        self.fold_addnorm = (self.D >= 2048) if fold_addnorm is None else bool(fold_addnorm)
         f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
         self.final_norm = f(final_norm)
         self.ln = [(f(l.in_ln), f(l.post_ln)) for l in layers]
@@ -62,6 +66,7 @@ class DenseDecoder:
         e = lambda *shape: t.empty(shape, device=dev, dtype=t.float32)
         self.cap = S
         self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
+        self.x_alt = e(1, self.D)
         self.qb, self.kb, self.vb, self.ctx = e(S, qw), e(S, kw), e(S, kw), e(S, qw)
         self.qkvb = e(1, qw + 2 * kw)
         self.ids = t.empty((S,), device=dev, dtype=t.int32)
@@ -84,8 +89,8 @@ class DenseDecoder:
             sh = C.c_void_p(stream_handle(self.stream))
             self.ids[:S].copy_(t.from_numpy(ids), non_blocking=True)
             _ck(L.moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), S, C.c_float(1.0), sh))
-            self._layers(S, pos_base, None, sh)
-            last = self.x[S - 1:S]
+            x = self._layers(S, pos_base, None, sh)
+            last = x[S - 1:S]
             _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(last), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
             _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
             tok = int(self.out_id.cpu()[0])          # waits for the stream
@@ -100,10 +105,20 @@ class DenseDecoder:
         p = lambda ten: C.c_void_p(ten.data_ptr())
         qw, kw = self.H * self.hd, self.KV * self.hd
         nl = len(self.layers)
-        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(self.ln[0][0]), S, D, eps, sh))
+        x, x_alt = self.x, self.x_alt
+        # a decode token: the add+norm between a layer's FFN and the next layer's fused [q|k|v] product rides inside that
+        # product (same bits, one launch less); the sum goes to the other of two residual buffers
+        fold = [self.fold_addnorm and S == 1 and l.qkv is not None and bool(L.moty_cuda_mat_addnorm_supported(l.qkv.h)) for l in self.layers]
+        pending = False
+        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(x), p(self.ln[0][0]), S, D, eps, sh))
         for i, (l, (in_ln, post_ln), a) in enumerate(zip(self.layers, self.ln, self.attn)):
             if S == 1 and l.qkv is not None:
-                _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
+                if pending:
+                    _ck(L.moty_cuda_mat_apply_addnorm_dev(l.qkv.h, p(self.qkvb), p(x), p(self.tmp), p(x_alt), p(in_ln), eps, sh))
+                    x, x_alt = x_alt, x
+                    pending = False
+                else:
+                    _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
                 base = self.qkvb.data_ptr()
                 qp, kp, vp = C.c_void_p(base), C.c_void_p(base + 4 * qw), C.c_void_p(base + 4 * (qw + kw))
             else:
@@ -116,15 +131,18 @@ class DenseDecoder:
             else:
                 _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
             _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
-            _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
+            _ck(L.moty_cuda_add_rmsnorm_dev(p(x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
             if l.moe is not None:
                 _ck(L.moty_cuda_moe_apply_dev(l.moe.h, p(self.tmp), p(self.nrm), S, None, 0, l.norm_topk, None, None, sh))
             else:
                 _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
-            if i + 1 < nl:
-                _ck(L.moty_cuda_add_rmsnorm_dev(p(self.x), p(self.tmp), p(self.nrm), p(self.ln[i + 1][0]), S, D, eps, sh))
+            if i + 1 < nl and fold[i + 1]:
+                pending = True
+            elif i + 1 < nl:
+                _ck(L.moty_cuda_add_rmsnorm_dev(p(x), p(self.tmp), p(self.nrm), p(self.ln[i + 1][0]), S, D, eps, sh))
             else:
-                _ck(L.moty_cuda_add_dev(p(self.x), p(self.tmp), C.c_longlong(S * D), sh))
+                _ck(L.moty_cuda_add_dev(p(x), p(self.tmp), C.c_longlong(S * D), sh))
+        return x
 
     def _decode_body(self, sh):
         """One greedy step with everything on the device: the token comes from ``self.ids[0]``, the position from
@@ -132,8 +150,8 @@ class DenseDecoder:
         L, D = lib(), self.D
         p = lambda ten: C.c_void_p(ten.data_ptr())
         _ck(L.moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), 1, C.c_float(1.0), sh))
-        self._layers(1, self.max_t - 1, self.pos_dev, sh)
-        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(self.x), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
+        x = self._layers(1, self.max_t - 1, self.pos_dev, sh)
+        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(x), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
         _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
         self.ids[:1].copy_(self.out_id)
         self.hist.index_copy_(0, self.cnt, self.out_id)

@@ -43,6 +43,33 @@ class _OracleModel:
         return o.argmax(lg), lg
 
 
+@pytest.mark.parametrize("O,I", [(4096, 1024), (640, 2048), (300, 4096), (1000, 112)])
+def test_product_with_add_and_norm_inside(gpu, O, I):
+    """y = W * rmsnorm(x + t) and xout = x + t in ONE launch (moty_cuda_mat_apply_addnorm_dev) against the two-launch
+    route (add_rmsnorm_dev, then mat_apply_dev): the same bits, and x itself is left alone."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(O + I)
+    q = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    m = gpu.Mat.i8(q, sc)
+    x = rng.standard_normal((1, I)).astype(np.float32); t = rng.standard_normal((1, I)).astype(np.float32)
+    g = rng.uniform(0.5, 1.5, I).astype(np.float32)
+    dx, dt, dg = (torch.from_numpy(a).cuda() for a in (x, t, g))
+    x2 = dx.clone(); nrm = torch.empty_like(dx); xout = torch.zeros_like(dx)
+    y1 = torch.empty((1, O), device="cuda"); y2 = torch.empty((1, O), device="cuda")
+    torch.cuda.synchronize()
+    sh = C.c_void_p(gpu.stream_handle(torch.cuda.current_stream()))
+    L, p, eps = gpu.lib(), (lambda a: C.c_void_p(a.data_ptr())), C.c_float(1e-6)
+    assert L.moty_cuda_mat_addnorm_supported(m.h) == 1
+    assert L.moty_cuda_add_rmsnorm_dev(p(x2), p(dt), p(nrm), p(dg), 1, I, eps, sh) == 0
+    assert L.moty_cuda_mat_apply_dev(m.h, p(y1), p(nrm), 1, sh) == 0
+    assert L.moty_cuda_mat_apply_addnorm_dev(m.h, p(y2), p(dx), p(dt), p(xout), p(dg), eps, sh) == 0
+    torch.cuda.synchronize()
+    assert same_bits(y1.cpu().numpy(), y2.cpu().numpy())
+    assert same_bits(x2.cpu().numpy(), xout.cpu().numpy()) and same_bits(dx.cpu().numpy(), x)
+    assert L.moty_cuda_mat_apply_addnorm_dev(m.h, p(y2), p(dx), p(dt), p(dx), p(dg), eps, sh) != 0      # xout must not be x
+
+
 def test_kernels_of_the_layer_glue(gpu):
     """RMS norm, residual add and embedding rows on device buffers against their definitions."""
     import ctypes as C
@@ -99,7 +126,8 @@ def test_greedy_tokens_match_the_oracle(gpu, oracle):
     layers = [DenseLayer(*(gpu.Mat.i8(*l[m]) for m in ("q", "k", "v", "o", "gate", "up", "down")), l["in_ln"], l["post_ln"], l["qn"], l["kn"],
                          qkv=fuse(l) if i != 1 else None)                # one layer without the fused [q|k|v] matrix
               for i, l in enumerate(W["layers"])]
-    dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t)
+    # fold_addnorm: layer 2's add+norm rides in its [q|k|v] product (layer 1 has no fused matrix: the plain route)
+    dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t, fold_addnorm=True)
     om = _OracleModel(oracle, W, cfg, max_t)
     prompt = rng.integers(0, V, 9).astype(np.int32)
     tg, lg = dec.step(prompt, 0, want_logits=True)
