@@ -207,6 +207,38 @@ __global__ void __launch_bounds__(256, 2) moe_dec_fused_kernel(MoeFusedArgs a) {
     }
 
     // ---------------- phase 2: h -> int8 per expert, down rows, weighted sum in selection order ----------------
+    if (K == 1) {
+        // one row (a dense FFN run as a one-expert block): the whole CTA quantizes it, one L2 round trip per pass,
+        // instead of one warp walking it alone
+        const bool local = loc_s[0] != 0;
+        const float4 *h4 = reinterpret_cast<const float4 *>(a.h);
+        float amax = 0.f;
+        if (local)
+            for (int i = threadIdx.x; i < I / 4; i += 256) {
+                float4 v = __ldcg(h4 + i);
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+        amax = warp_max_f32(amax);
+        if (lane == 0) red[warp] = amax;
+        __syncthreads();
+        amax = red[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
+        const float s = quant_scale(amax, 1e-12f);
+        const float inv = __fdiv_rn(1.f, s);
+        int *hq = reinterpret_cast<int *>(smem4);
+        for (int i = threadIdx.x; i < I / 4; i += 256) {
+            int word = 0;
+            if (local) {
+                float4 v = __ldcg(h4 + i);
+                int c0 = quant_code(v.x, inv) & 255, c1 = quant_code(v.y, inv) & 255;
+                int c2 = quant_code(v.z, inv) & 255, c3 = quant_code(v.w, inv) & 255;
+                word = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+            }
+            hq[i] = word;
+        }
+        if (threadIdx.x == 0) sh_s[0] = s;
+    } else
     for (int k = warp; k < K; k += 8) {
         const bool local = loc_s[k] != 0;
         const float4 *h4 = reinterpret_cast<const float4 *>(a.h + (size_t)k * I);
