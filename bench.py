@@ -226,7 +226,57 @@ def run_extras(torch, mb, dev, stream, W8, local):
     del W4
     out["moe"] = run_moe_extras(torch, mb, dev, stream, local)
     out["blocks"] = run_block_extras(torch, mb, dev, stream, local)
+    # the model-level view of the same kernels: a greedy decode of the configs[0] shape (wall clock, whole steps)
+    try:
+        out["decode_qwen3_0.6b"] = run_decode_qwen(torch, mb, np.random.default_rng(3), 64, local)
+    except Exception as e:                              # an extra must not cost the headline line
+        out["decode_qwen3_0.6b"] = {"error": str(e)[:200]}
     return out
+
+
+def run_decode_qwen(torch, mb, rng, ngen, device):
+    """A whole greedy decode of the configs[0] shape (Qwen3-0.6B: 28 layers, hidden 1024, 16/8 heads of 128, FFN 3072,
+    vocabulary 151936, tied int8 head) on synthetic int8 weights: a 64-token prompt, then ngen tokens launched entry by
+    entry from Python, then the same tokens as a replayed CUDA graph of one decode step."""
+    import time
+    from moty_b200.decoder import DenseDecoder, DenseLayer
+    NL, D, H, KV, hd, I, V, PROMPT = 28, 1024, 16, 8, 128, 3072, 151936, 64
+    raw = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.0002, 0.0006, O).astype(np.float32))
+    mk = lambda O, K: mb.Mat.i8(*raw(O, K), device=device)
+    one = lambda n: np.ones(n, np.float32)
+    def layer():
+        q, k, v = raw(H * hd, D), raw(KV * hd, D), raw(KV * hd, D)
+        qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=device)
+        return DenseLayer(mb.Mat.i8(*q, device=device), mb.Mat.i8(*k, device=device), mb.Mat.i8(*v, device=device), mk(D, H * hd),
+                          mk(I, D), mk(I, D), mk(D, I), one(D), one(D), one(hd), one(hd), qkv=qkv)
+    layers = [layer() for _ in range(NL)]
+    head = mb.Mat.i8(rng.integers(-127, 128, (V, D), dtype=np.int8), rng.uniform(0.005, 0.015, V).astype(np.float32), device=device)
+    dec = DenseDecoder(layers, head, one(D), H, KV, hd, PROMPT + ngen + 8, max_S=PROMPT, device=device)
+    prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
+    dec.step(prompt, 0); dec.step([1], PROMPT)                       # warm-up (allocations, attributes)
+    torch.cuda.synchronize(); t0 = time.perf_counter()
+    tok = dec.step(prompt, 0)
+    torch.cuda.synchronize(); t1 = time.perf_counter()
+    toks = [tok]
+    for i in range(ngen):
+        toks.append(dec.step([toks[-1]], PROMPT + i))
+    torch.cuda.synchronize(); t2 = time.perf_counter()
+    tg = dec.greedy_graph(tok, PROMPT, ngen)                          # captures on first use
+    torch.cuda.synchronize(); t3 = time.perf_counter()
+    tg = dec.greedy_graph(tok, PROMPT, ngen)
+    torch.cuda.synchronize(); t4 = time.perf_counter()
+    wbytes = sum(m.nbytes() for l in layers for m in (l.qkv, l.o, l.gate, l.up, l.down)) + head.nbytes()
+    res = {"prefill_tok_s": round(PROMPT / (t1 - t0), 1), "decode_tok_s": round(ngen / (t2 - t1), 1),
+           "ms_per_token": round((t2 - t1) / ngen * 1e3, 3), "weight_MB_per_token": round(wbytes / 1e6, 1),
+           "GBs": round(wbytes * ngen / (t2 - t1) / 1e9, 1), "launch": "python-driven device entries, no graph",
+           "graph_decode_tok_s": round(ngen / (t4 - t3), 1), "graph_ms_per_token": round((t4 - t3) / ngen * 1e3, 3),
+           "graph_GBs": round(wbytes * ngen / (t4 - t3) / 1e9, 1), "graph_equals_direct": tg == toks[1:]}
+    dec.close()
+    for l in layers:
+        for m in (l.q, l.k, l.v, l.o, l.gate, l.up, l.down, l.qkv):
+            m.free()
+    head.free()
+    return res
 
 
 def run_block_extras(torch, mb, dev, stream, local):
@@ -618,41 +668,8 @@ def run_case(args):
         dec.close()
         return
     if parts[0] == "decode":                            # decode:qwen3-0.6b[:NGEN] -- configs[0] shape, synthetic int8 weights
-        import time
-        from moty_b200.decoder import DenseDecoder, DenseLayer
-        ngen = int(parts[2]) if len(parts) > 2 else 128
-        NL, D, H, KV, hd, I, V, PROMPT = 28, 1024, 16, 8, 128, 3072, 151936, 64
-        mk = lambda O, K: mb.Mat.i8(rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.0002, 0.0006, O).astype(np.float32), device=0)
-        one = lambda n: np.ones(n, np.float32)
-        def layer():
-            raw = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.0002, 0.0006, O).astype(np.float32))
-            q, k, v = raw(H * hd, D), raw(KV * hd, D), raw(KV * hd, D)
-            qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=0)
-            return DenseLayer(mb.Mat.i8(*q, device=0), mb.Mat.i8(*k, device=0), mb.Mat.i8(*v, device=0), mk(D, H * hd), mk(I, D), mk(I, D),
-                              mk(D, I), one(D), one(D), one(hd), one(hd), qkv=qkv)
-        layers = [layer() for _ in range(NL)]
-        head = mb.Mat.i8(rng.integers(-127, 128, (V, D), dtype=np.int8), rng.uniform(0.005, 0.015, V).astype(np.float32), device=0)
-        dec = DenseDecoder(layers, head, one(D), H, KV, hd, PROMPT + ngen + 8, max_S=PROMPT)
-        prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
-        dec.step(prompt, 0); dec.step([1], PROMPT)                       # warm-up (allocations, attributes)
-        torch.cuda.synchronize(); t0 = time.perf_counter()
-        tok = dec.step(prompt, 0)
-        torch.cuda.synchronize(); t1 = time.perf_counter()
-        toks = [tok]
-        for i in range(ngen):
-            toks.append(dec.step([toks[-1]], PROMPT + i))
-        torch.cuda.synchronize(); t2 = time.perf_counter()
-        tg = dec.greedy_graph(tok, PROMPT, ngen)                          # captures on first use
-        torch.cuda.synchronize(); t3 = time.perf_counter()
-        tg = dec.greedy_graph(tok, PROMPT, ngen)
-        torch.cuda.synchronize(); t4 = time.perf_counter()
-        wbytes = sum(m.nbytes() for l in layers for m in (l.qkv, l.o, l.gate, l.up, l.down)) + head.nbytes()
-        print(json.dumps({"case": args.case, "prefill_tok_s": round(PROMPT / (t1 - t0), 1), "decode_tok_s": round(ngen / (t2 - t1), 1),
-                          "ms_per_token": round((t2 - t1) / ngen * 1e3, 3), "weight_MB_per_token": round(wbytes / 1e6, 1),
-                          "GBs": round(wbytes * ngen / (t2 - t1) / 1e9, 1), "launch": "python-driven device entries, no graph",
-                          "graph_decode_tok_s": round(ngen / (t4 - t3), 1), "graph_ms_per_token": round((t4 - t3) / ngen * 1e3, 3),
-                          "graph_GBs": round(wbytes * ngen / (t4 - t3) / 1e9, 1), "graph_equals_direct": tg == toks[1:]}), flush=True)
-        dec.close()
+        res = run_decode_qwen(torch, mb, rng, int(parts[2]) if len(parts) > 2 else 128, 0)
+        print(json.dumps({"case": args.case, **res}), flush=True)
         return
     if parts[0] == "attn":                              # attn:S:POS:H:KV:hd[:kv8] -- S tokens at position POS of one layer's cache
         S, POS, H, KV, hd = (int(v) for v in parts[1:6])
