@@ -671,15 +671,20 @@ def run_case(args):
         res = run_decode_qwen(torch, mb, rng, int(parts[2]) if len(parts) > 2 else 128, 0)
         print(json.dumps({"case": args.case, **res}), flush=True)
         return
-    if parts[0] == "attn":                              # attn:S:POS:H:KV:hd[:kv8] -- S tokens at position POS of one layer's cache
+    if parts[0] == "attn":                              # attn:S:POS:H:KV:hd[:kv8][:posdev] -- S tokens at position POS of one layer's cache
         S, POS, H, KV, hd = (int(v) for v in parts[1:6])
-        kv8 = len(parts) > 6 and parts[6] == "kv8"
+        kv8 = "kv8" in parts[6:]
+        posdev = "posdev" in parts[6:]                  # position read from the device: with S = 1 the one-launch decode core
         a = mb.Attn(H, KV, hd, POS + S, qn=np.ones(hd, np.float32), kn=np.ones(hd, np.float32), kv8=kv8)
         stream = torch.cuda.Stream(device=dev)
         with torch.cuda.stream(stream):
             q0 = torch.randn((S, H * hd), device=dev); k0 = torch.randn((S, KV * hd), device=dev)
             q = q0.clone(); k = k0.clone(); v = torch.randn((S, KV * hd), device=dev); ctx = torch.empty((S, H * hd), device=dev)
             run = lambda: a.core_dev(ctx.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), S, POS, stream=stream.cuda_stream)
+            if posdev:
+                pd = torch.full((1,), POS, device=dev, dtype=torch.int32)
+                run = lambda: a.core_posdev(ctx.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), S, pd.data_ptr(), POS,
+                                            stream=stream.cuda_stream)
             for _ in range(max(args.warmup, 1)):
                 run()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -756,7 +761,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder, decode:olmoe[:NGEN] a 512-token prompt and NGEN steps of the configs[2]-shaped MoE decoder; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8] the attention core with S tokens at position POS; ep:NAME:S under torchrun times the "
+                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder, decode:olmoe[:NGEN] a 512-token prompt and NGEN steps of the configs[2]-shaped MoE decoder; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8][:posdev] the attention core with S tokens at position POS (posdev: position read from the device, the one-launch decode core); ep:NAME:S under torchrun times the "
                                                 "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:
