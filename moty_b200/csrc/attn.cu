@@ -547,7 +547,7 @@ __global__ void __launch_bounds__(256) attn_gate_kernel(float *ctx, const float 
     pdl_trigger();
     pdl_wait();
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-    if (i < n) ctx[i] = __fmul_rn(ctx[i], __fdiv_rn(1.f, __fadd_rn(1.f, expf(-gate[i]))));
+    if (i < n) ctx[i] = __fmul_rn(ctx[i], __fdiv_rn(1.f, __fadd_rn(1.f, moty_expf(-gate[i]))));
 }
 
 }  // namespace

@@ -179,4 +179,54 @@ __device__ __forceinline__ float f16bits_to_f32(uint16_t h) {
     return __half2float(__ushort_as_half(h));     // exact, subnormals included
 }
 
+// expf as the reference's C library computes it.  The reference calls libm's expf in SiLU, in the
+// router softmax and in the output gate (hw/hw_ops.h:19-26, nn/moe.c:11,120,197, nn/attn.c:69), and an
+// ulp of difference there can move an int8 code of the re-quantized hidden row.  glibc's expf (2.27 and
+// later; the table-driven double-precision algorithm of ARM's optimized routines) is
+//   z = x * 32/ln2;  k = round(z);  r = z - k;  2^(k/32) from a 32-entry table and the exponent field;
+//   exp(x) = 2^(k/32) * (C0 r^3 + C1 r^2 + C2 r + 1) in f64, rounded ONCE to f32,
+// and x86-64 hosts with FMA run the build in which the compiler contracted the multiply-adds:
+// r = fma(32/ln2, x, -k) and the three polynomial steps below.  The restatement in
+// oracle/moty_oracle.c (oracle_expf) is the same sequence and is pinned against the host's expf on
+// every one of the 2^32 float inputs (tests/test_oracle.py checks a sample of them in each run); IEEE
+// f64 operations give the same bits here.  Entry i of the table is bits(2^(i/32) rounded to f64) - (i << 47).
+
+__device__ __forceinline__ float moty_expf(float x) {
+    static constexpr unsigned long long MOTY_EXP2_TAB[32] = {
+        0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,
+        0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,
+        0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,
+        0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,
+        0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,
+        0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,
+        0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
+        0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
+    const unsigned top = (__float_as_uint(x) >> 20) & 0x7ffu;
+    if (top >= 0x42bu) {                                              // |x| >= 88, infinities and NaN
+        if (__float_as_uint(x) == 0xff800000u) return 0.f;
+        if (top >= 0x7f8u) return __fadd_rn(x, x);
+        if (x > 0x1.62e42ep6f) return __int_as_float(0x7f800000);
+        if (x < -0x1.9fe368p6f) return 0.f;
+    }
+    constexpr double INV_LN2_N = 0x1.71547652b82fep+0 * 32.0;
+    constexpr double C0 = 0x1.c6af84b912394p-5 / 32 / 32 / 32, C1 = 0x1.ebfce50fac4f3p-3 / 32 / 32, C2 = 0x1.62e42ff0c52d6p-1 / 32;
+    constexpr double SHIFT = 0x1.8p52;
+    const double xd = (double)x;
+    const double z = __dmul_rn(INV_LN2_N, xd);
+    double kd = __dadd_rn(z, SHIFT);
+    const unsigned long long ki = (unsigned long long)__double_as_longlong(kd);
+    kd = __dsub_rn(kd, SHIFT);
+    const double r = __fma_rn(INV_LN2_N, xd, -kd);
+    const double s = __longlong_as_double((long long)(MOTY_EXP2_TAB[ki & 31] + (ki << 47)));
+    const double p = __fma_rn(C0, r, C1);
+    const double r2 = __dmul_rn(r, r);
+    double y = __fma_rn(C2, r, 1.0);
+    y = __fma_rn(p, r2, y);
+    return __double2float_rn(__dmul_rn(y, s));
+}
+// SiLU(v) * u as the reference spells it: (v / (1 + expf(-v))) * u, three correctly rounded f32 steps
+__device__ __forceinline__ float moty_silu_mul(float v, float u) {
+    return __fmul_rn(__fdiv_rn(v, __fadd_rn(1.f, moty_expf(-v))), u);
+}
+
 #endif  // __CUDACC__

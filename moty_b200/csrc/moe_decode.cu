@@ -142,9 +142,7 @@ __global__ void __launch_bounds__(256, (LPR <= 2 ? 4 : 2)) moe_dec_gateup_kernel
             // scale * sx * dot, left to right (nn/moe.c:107), then silu(g) * u (nn/moe.c:119)
             float gv = __fmul_rn(__fmul_rn(sg, sx), (float)flat[0]);
             float uv = __fmul_rn(__fmul_rn(su, sx), (float)upsum);
-            float e = (float)exp((double)(-gv));
-            float t = __fdiv_rn(gv, __fadd_rn(1.f, e));
-            a.h[(size_t)k * I + i] = __fmul_rn(t, uv);
+            a.h[(size_t)k * I + i] = moty_silu_mul(gv, uv);
         }
     }
 }

@@ -115,9 +115,7 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
                 }
             }
             if (gl == 7) {
-                float e2 = (float)exp((double)(-accg));
-                float tt = __fdiv_rn(accg, __fadd_rn(1.f, e2));
-                hrow_s[warp * 4 + r] = __fmul_rn(tt, accu);
+                hrow_s[warp * 4 + r] = moty_silu_mul(accg, accu);
             }
             __syncthreads();
             if (warp == 0) {                                               // one quantization group (hw/hw_q4r4.h:36-45)

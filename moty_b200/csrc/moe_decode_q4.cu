@@ -73,9 +73,7 @@ __global__ void __launch_bounds__(256) moe_dec4_gateup_kernel(MoeDec4Args a) {
         }
         const int i = ob * 4 + r;
         if (gl == 7 && i < I) {
-            float e2 = (float)exp((double)(-accg));
-            float tt = __fdiv_rn(accg, __fadd_rn(1.f, e2));
-            a.h[(size_t)k * I + i] = __fmul_rn(tt, accu);
+            a.h[(size_t)k * I + i] = moty_silu_mul(accg, accu);
         }
     }
 }

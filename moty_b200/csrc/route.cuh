@@ -12,9 +12,8 @@ __device__ __forceinline__ unsigned route_key(float v) {
 
 // Softmax follows moty_hw_softmax_ref (hw/hw_ops.h:22-26): running maximum from -1e30,
 // e = exp(x - m) rounded to f32, the sum taken SEQUENTIALLY in index order in f32 (every lane runs
-// the same chain), then one true division per element.  exp is evaluated in f64
-// and rounded once, which agrees with a correctly rounded expf; a libm expf may differ from that
-// by one ulp on roughly one value in a thousand, which does not move the ranking in practice.
+// the same chain), then one true division per element.  exp is moty_expf (common.cuh), the
+// restatement of the C library's expf, so the probabilities carry the reference's bits.
 //
 // Top-K follows moty_moe_topk (runtime/moecache.c:97-111): K rounds of "largest value not yet
 // taken", strict > against a floor of -1e30, so equal values go to the lowest index.  The argmax
@@ -76,7 +75,7 @@ __device__ __forceinline__ void route_row_warp_reg(const float *__restrict__ lg,
         m = warp_max_f32(m);
 #pragma unroll
         for (int j = 0; j < EPL; j++)
-            if (lane + 32 * j < E) { v[j] = (float)exp((double)__fsub_rn(v[j], m)); p[lane + 32 * j] = v[j]; }
+            if (lane + 32 * j < E) { v[j] = moty_expf(__fsub_rn(v[j], m)); p[lane + 32 * j] = v[j]; }
         __syncwarp();
         const float total = route_seq_sum(p, E);
 #pragma unroll
@@ -118,7 +117,7 @@ __device__ __forceinline__ void route_row_warp_mem(const float *__restrict__ lg,
         float m = -1e30f;
         for (int e = lane; e < E; e += 32) m = fmaxf(m, p[e]);
         m = warp_max_f32(m);
-        for (int e = lane; e < E; e += 32) p[e] = (float)exp((double)__fsub_rn(p[e], m));
+        for (int e = lane; e < E; e += 32) p[e] = moty_expf(__fsub_rn(p[e], m));
         __syncwarp();
         const float total = route_seq_sum(p, E);
         __syncwarp();

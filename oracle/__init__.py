@@ -34,9 +34,16 @@ def _f32(a):
     return np.ascontiguousarray(a, dtype=np.float32)
 
 
-def build(ref_src: str = "/root/reference/c") -> None:
+def ref_src_dir() -> str:
+    """Where the reference's c/ directory is looked for: $MOTY_REF_SRC, else the make recipe's default."""
+    return os.environ.get("MOTY_REF_SRC", "")
+
+
+def build(ref_src: str | None = None) -> None:
     """Compile the restatement (always) and the reference (when its sources exist)."""
-    subprocess.check_call(["make", "-s", "-C", HERE, "all", f"REF={ref_src}"])
+    ref_src = ref_src or ref_src_dir()
+    cmd = ["make", "-s", "-C", HERE, "all"] + ([f"REF={ref_src}"] if ref_src else [])
+    subprocess.check_call(cmd)
 
 
 def _cpu_has(flag: str) -> bool:
@@ -97,8 +104,21 @@ class Oracle:
         L.oracle_dot_i8i8.restype = C.c_int32
         L.oracle_dot_i4i8.restype = C.c_int32
         L.oracle_argmax.restype = C.c_int
+        L.oracle_expf.restype = C.c_float
+        L.oracle_expf.argtypes = [C.c_float]
+        L.oracle_expf_mismatches.restype = C.c_int64
+        L.oracle_expf_mismatches.argtypes = [C.c_uint32, C.c_uint32, C.c_int64]
+        L.oracle_exp2_tab_entry.restype = C.c_uint64
+        L.oracle_exp2_tab_entry.argtypes = [C.c_int]
 
     # -- scalars -------------------------------------------------------
+    def expf(self, x):
+        return np.float32(self.lib.oracle_expf(float(np.float32(x))))
+
+    def expf_mismatches(self, first, stride, count):
+        """Inputs (as float bit patterns first, first+stride, ...) on which the restated expf and the host's differ."""
+        return int(self.lib.oracle_expf_mismatches(int(first), int(stride), int(count)))
+
     def f16_to_f32(self, h):
         return self.lib.oracle_f16_to_f32(int(h))
 

@@ -502,16 +502,89 @@ ORACLE_API void oracle_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint
 }
 
 /* ------------------------------------------------------------------ */
+/* expf                                                                 */
+/* ------------------------------------------------------------------ */
+
+/* The reference's SiLU, router softmax and output gate call the C library's expf
+ * (hw/hw_ops.h:19-26, nn/moe.c:11,120,197, nn/attn.c:69).  That function is not
+ * part of the reference tree: it is glibc's (2.39 in this image), whose algorithm
+ * since 2.27 is the published table-driven one of ARM's optimized routines:
+ *   z = x * 32/ln2,  k = round-to-nearest(z) taken by adding 1.5*2^52,  r = z - k,
+ *   s = 2^(k/32): a 32-entry table of 2^(i/32) plus k/32 in the exponent field,
+ *   exp(x) = s * (C0 r^3 + C1 r^2 + C2 r + 1), all in f64, rounded once to f32.
+ * x86-64 machines with FMA run the build of it in which the compiler contracted
+ * the multiply-adds: r = fma(32/ln2, x, -k), and the three polynomial steps as
+ * written below.  This restatement equals the host's expf on every one of the
+ * 2^32 float inputs (oracle_expf_mismatches over the full range; the test-suite
+ * checks a sample in each run).  Table entry i = bits(2^(i/32) rounded to nearest
+ * f64) - (i << 47); tests/test_oracle.py recomputes the entries at high precision. */
+static const uint64_t oracle_exp2_tab[32] = {
+    0x3ff0000000000000ULL, 0x3fefd9b0d3158574ULL, 0x3fefb5586cf9890fULL, 0x3fef9301d0125b51ULL,
+    0x3fef72b83c7d517bULL, 0x3fef54873168b9aaULL, 0x3fef387a6e756238ULL, 0x3fef1e9df51fdee1ULL,
+    0x3fef06fe0a31b715ULL, 0x3feef1a7373aa9cbULL, 0x3feedea64c123422ULL, 0x3feece086061892dULL,
+    0x3feebfdad5362a27ULL, 0x3feeb42b569d4f82ULL, 0x3feeab07dd485429ULL, 0x3feea47eb03a5585ULL,
+    0x3feea09e667f3bcdULL, 0x3fee9f75e8ec5f74ULL, 0x3feea11473eb0187ULL, 0x3feea589994cce13ULL,
+    0x3feeace5422aa0dbULL, 0x3feeb737b0cdc5e5ULL, 0x3feec49182a3f090ULL, 0x3feed503b23e255dULL,
+    0x3feee89f995ad3adULL, 0x3feeff76f2fb5e47ULL, 0x3fef199bdd85529cULL, 0x3fef3720dcef9069ULL,
+    0x3fef5818dcfba487ULL, 0x3fef7c97337b9b5fULL, 0x3fefa4afa2a490daULL, 0x3fefd0765b6e4540ULL};
+
+ORACLE_API uint64_t oracle_exp2_tab_entry(int i) { return oracle_exp2_tab[i & 31]; }
+
+ORACLE_API float oracle_expf(float x) {
+    uint32_t ux; memcpy(&ux, &x, 4);
+    const uint32_t top = (ux >> 20) & 0x7ffu;
+    if (top >= 0x42bu) {                          /* |x| >= 88, infinities, NaN */
+        if (ux == 0xff800000u) return 0.f;
+        if (top >= 0x7f8u) return x + x;
+        if (x > 0x1.62e42ep6f) return INFINITY;
+        if (x < -0x1.9fe368p6f) return 0.f;
+    }
+    const double inv_ln2_n = 0x1.71547652b82fep+0 * 32.0;
+    const double c0 = 0x1.c6af84b912394p-5 / 32 / 32 / 32, c1 = 0x1.ebfce50fac4f3p-3 / 32 / 32,
+                 c2 = 0x1.62e42ff0c52d6p-1 / 32;
+    const double shift = 0x1.8p52;
+    const double xd = (double)x;
+    const double z = inv_ln2_n * xd;
+    double kd = z + shift;
+    uint64_t ki; memcpy(&ki, &kd, 8);
+    kd -= shift;
+    const double r = fma(inv_ln2_n, xd, -kd);
+    const uint64_t sb = oracle_exp2_tab[ki & 31] + (ki << 47);
+    double s; memcpy(&s, &sb, 8);
+    const double p = fma(c0, r, c1);
+    const double r2 = r * r;
+    double y = fma(c2, r, 1.0);
+    y = fma(p, r2, y);
+    return (float)(y * s);
+}
+
+/* How many of the float bit patterns first, first+stride, ... (< first + count*stride,
+ * NaNs skipped) give different bits from the host C library's expf. */
+ORACLE_API int64_t oracle_expf_mismatches(uint32_t first, uint32_t stride, int64_t count) {
+    int64_t bad = 0;
+    #pragma omp parallel for reduction(+:bad) schedule(static)
+    for (int64_t j = 0; j < count; j++) {
+        uint32_t u = first + (uint32_t)j * stride;
+        float x; memcpy(&x, &u, 4);
+        if (x != x) continue;
+        float a = expf(x), b = oracle_expf(x);
+        uint32_t ua, ub; memcpy(&ua, &a, 4); memcpy(&ub, &b, 4);
+        if (ua != ub) bad++;
+    }
+    return bad;
+}
+
+/* ------------------------------------------------------------------ */
 /* router                                                              */
 /* ------------------------------------------------------------------ */
 
-/* hw/hw_ops.h:22-26 -- in-place softmax: max from -1e30, libm expf, sequential
+/* hw/hw_ops.h:22-26 -- in-place softmax: max from -1e30, expf (restated above), sequential
  * f32 sum, one division per element. */
 ORACLE_API void oracle_softmax(float *x, int n) {
     float m = -1e30f;
     for (int i = 0; i < n; i++) if (x[i] > m) m = x[i];
     float total = 0.f;
-    for (int i = 0; i < n; i++) { x[i] = expf(x[i] - m); total += x[i]; }
+    for (int i = 0; i < n; i++) { x[i] = oracle_expf(x[i] - m); total += x[i]; }
     for (int i = 0; i < n; i++) x[i] /= total;
 }
 
@@ -554,7 +627,7 @@ ORACLE_API int oracle_argmax(const float *v, int n) {
 
 /* hw/hw_ops.h:19-21 -- g = silu(g) * u, silu(v) = v / (1 + expf(-v)). */
 ORACLE_API void oracle_silu_mul(float *g, const float *u, int64_t n) {
-    for (int64_t i = 0; i < n; i++) { float v = g[i]; g[i] = (v / (1.f + expf(-v))) * u[i]; }
+    for (int64_t i = 0; i < n; i++) { float v = g[i]; g[i] = (v / (1.f + oracle_expf(-v))) * u[i]; }
 }
 
 /* engines/gemma.c:389-391,398 -- g = gelu_tanh(g) * u. */
@@ -855,7 +928,7 @@ ORACLE_API void oracle_attn_core(float *ctx, float *q, float *k, const float *v,
             }
             float m = -1e30f, sum = 0.f;
             for (int t = 0; t < n; t++) if (sc[t] > m) m = sc[t];
-            for (int t = 0; t < n; t++) { sc[t] = expf(sc[t] - m); sum += sc[t]; }
+            for (int t = 0; t < n; t++) { sc[t] = oracle_expf(sc[t] - m); sum += sc[t]; }
             for (int t = 0; t < n; t++) sc[t] /= sum;
             float *cx = ctx + s * qw + (size_t)hh * hd;
             for (int i = 0; i < hd; i++) cx[i] = 0.f;

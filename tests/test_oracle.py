@@ -183,3 +183,25 @@ def test_oracle_equals_reference_build(oracle, ref):
         assert same_bits(oracle.matmul_i4g_idot_s(xg, a[0], a[1]), ref.matmul_i4g_idot_s(xg, a[0], a[1]))
     a, b = oracle.route_topk(lg, 8), ref.route_topk(lg, 8)
     assert all(same_bits(u, v) for u, v in zip(a, b))
+
+
+def test_expf_restatement_equals_the_c_library(oracle):
+    """SiLU, the router softmax and the output gate of the reference call the C library's expf
+    (hw/hw_ops.h:19-26, nn/moe.c:120,197, nn/attn.c:69).  The restatement must give the same bits:
+    every 37th float bit pattern over the whole 2^32 range (1.16e8 inputs, all exponents, both signs),
+    and EVERY float in [-32, -1/64] and [1/64, 32] -- the range SiLU and softmax arguments live in."""
+    assert oracle.expf_mismatches(0, 37, (1 << 32) // 37) == 0
+    lo, hi = np.float32(1 / 64).view(np.uint32), np.float32(32).view(np.uint32)
+    for sign in (0, 0x80000000):
+        assert oracle.expf_mismatches(int(lo) | sign, 1, int(hi) - int(lo) + 1) == 0
+    assert oracle.expf(-np.inf) == 0 and oracle.expf(np.inf) == np.inf and np.isnan(oracle.expf(np.nan))
+
+
+def test_expf_table_is_two_to_the_i_over_32(oracle):
+    """Entry i of the restatement's table is 2^(i/32) rounded to nearest f64, less i << 47."""
+    mpmath = pytest.importorskip("mpmath")
+    mpmath.mp.prec = 200
+    for i in range(32):
+        d = float(mpmath.power(2, mpmath.mpf(i) / 32))
+        bits = int(np.float64(d).view(np.uint64)) - (i << 47)
+        assert int(oracle.lib.oracle_exp2_tab_entry(i)) == bits
