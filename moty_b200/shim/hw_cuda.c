@@ -1,0 +1,81 @@
+/* hw_cuda.c -- reference-side shim between moty's Mat / mat_apply and libmoty_cuda.so.
+ *
+ * The reference already has both seams this needs and neither is touched:
+ *   - Mat carries an opaque pointer `sh` that moty_mat_apply tests before its format switch, diverting
+ *     the call to a hook installed with moty_nn_set_stream_fn (nn/nn_mat.h:18-30, nn/mat.c:12-13,70-71);
+ *   - failures go through moty_fail_code (nn/fail.h:37): fatal in the CLI engines, a moty_status in
+ *     library mode.
+ * The device handle lives in `sh`; the hook is one call into the C ABI with host pointers.
+ */
+#include "hw_cuda.h"
+#include "nn/fail.h"
+#include "nn/nn_matmul.h"      /* NN_QROW_MAX */
+#include "moty_cuda.h"
+#include <stdlib.h>
+
+/* The library reproduces the integer paths: IDOT=1 for int8 rows (the default, nn/matmul.c:52-53) and
+ * IDOT4=1 for the two int4 row formats (opt-in, nn/matmul.c:77,171).  With the other setting of a knob
+ * the reference computes an f32 product instead; those matrices stay on the CPU. */
+static int env_is(const char *k, int dflt) { const char *e = getenv(k); return e && *e ? atoi(e) : dflt; }
+
+static int g_mats;
+static long long g_bytes, g_calls;
+
+static void cuda_apply(float *y, const float *x, const struct Mat *w, int S) {
+    g_calls++;
+    if (moty_cuda_mat_apply((MotyCudaMat *)w->sh, y, x, S) != 0)
+        moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] mat_apply %dx%d S=%d: %s\n", w->O, w->I, S, moty_cuda_last_error());
+}
+
+void moty_hw_cuda_open(const int *devs, int n) {
+    if (moty_cuda_init(devs, n) != 0)
+        moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] init: %s\n", moty_cuda_last_error());
+    moty_nn_set_stream_fn(cuda_apply);
+}
+
+int moty_hw_cuda_attach(Mat *w, int device) {
+    MotyCudaMat *h = NULL;
+    int rc;
+    if (w->sh || w->O <= 0 || w->I <= 0) return 0;
+    switch (w->fmt) {
+    case WF_I8:
+        if (!w->q || !w->qs || w->I > NN_QROW_MAX || !env_is("IDOT", 1)) return 0;   /* longer rows take the f32 path (nn/matmul.c:54) */
+        rc = moty_cuda_upload_mat(&h, MOTY_WF_I8, w->q, w->qs, w->O, w->I, device); break;
+    case WF_Q4R4:
+        if (!w->q4 || !w->s16) return 0;
+        rc = moty_cuda_upload_mat(&h, MOTY_WF_Q4R4, w->q4, w->s16, w->O, w->I, device); break;
+    case WF_Q8R4:                                                       /* its int8 codes live in q4 too */
+        if (!w->q4 || !w->s16) return 0;
+        rc = moty_cuda_upload_mat(&h, MOTY_WF_Q8R4, w->q4, w->s16, w->O, w->I, device); break;
+    case WF_I4:
+        if (!w->q4 || !w->qs || w->I > NN_QROW_MAX || !env_is("IDOT4", 0)) return 0;
+        rc = moty_cuda_upload_mat(&h, MOTY_WF_I4, w->q4, w->qs, w->O, w->I, device); break;
+    case WF_I4G:
+        if (!w->q4 || !w->qs || w->gs != 32 || w->I % 64 || w->I > NN_QROW_MAX || !env_is("IDOT4", 0)) return 0;
+        rc = moty_cuda_upload_mat(&h, MOTY_WF_I4G, w->q4, w->qs, w->O, w->I, device); break;
+    default:
+        return 0;                                                       /* stays on the CPU path */
+    }
+    if (rc != 0)
+        moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] upload %dx%d fmt %d: %s\n", w->O, w->I, w->fmt, moty_cuda_last_error());
+    w->sh = h;
+    g_mats++; g_bytes += moty_cuda_mat_bytes(h);
+    return 1;
+}
+
+void moty_hw_cuda_detach(Mat *w) {
+    if (!w->sh) return;
+    moty_cuda_free_mat((MotyCudaMat *)w->sh);
+    w->sh = NULL;
+}
+
+void moty_hw_cuda_close(void) {
+    moty_nn_set_stream_fn(NULL);
+    moty_cuda_shutdown();
+}
+
+void moty_hw_cuda_stats(int *n_mats, long long *bytes, long long *calls) {
+    if (n_mats) *n_mats = g_mats;
+    if (bytes) *bytes = g_bytes;
+    if (calls) *calls = g_calls;
+}
