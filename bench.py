@@ -385,6 +385,177 @@ def run_moe_extras(torch, mb, dev, stream, local):
 
 
 # ---------------------------------------------------------------------------
+# N > 1: the sharded forms of the path, timed beside the replicas of the headline sweep.
+# Expert-parallel routed layers of the two MoE shapes (experts in contiguous ranges per rank) and the
+# row-sharded decode products of the Gemma-4-12B shape with their all-gather.  Every time is CUDA events
+# around a run of calls on the rank's stream, max over ranks; rank 0 also runs the unsharded layer or
+# matrix on its own GPU for the same tokens, so efficiency = t(1 GPU) / (N * t(N GPUs)).
+# ---------------------------------------------------------------------------
+def _pool_expert(mb, name, rng):
+    E, K, I, D, f = MOE_SHAPES[name]
+    if f == "i8":
+        return (rng.integers(-127, 128, (I, D), dtype=np.int8), rng.uniform(0.001, 0.02, I).astype(np.float32),
+                rng.integers(-127, 128, (I, D), dtype=np.int8), rng.uniform(0.001, 0.02, I).astype(np.float32),
+                rng.integers(-127, 128, (D, I), dtype=np.int8), rng.uniform(0.001, 0.02, D).astype(np.float32))
+    ng, nd = (I // 4) * (D // 32), (D // 4) * (I // 32)
+    return (rng.integers(0, 256, ng * 64, dtype=np.uint8), np.full(ng * 4, 0x1A00, np.uint16),
+            rng.integers(0, 256, ng * 64, dtype=np.uint8), np.full(ng * 4, 0x1A00, np.uint16),
+            rng.integers(0, 256, nd * 64, dtype=np.uint8), np.full(nd * 4, 0x1A00, np.uint16))
+
+
+def run_sharded(torch, dist, mb, dev, local, rank, world, steps):
+    from moty_b200.parallel import ExpertParallelMoe, RowShardedMat, shard_rows
+    rows = []
+    gen = torch.Generator().manual_seed(11)
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        dist.barrier(); torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) * 1e3 / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def timed_local(fn, n):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record(); torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / n
+
+    def timed_graph(fn, collective, per_graph=16, replays=10):
+        """Decode-sized calls are host-bound when launched one by one from Python (a collective costs ~20 us of
+        dispatcher time): capture per_graph calls into one CUDA graph (NCCL collectives are capturable) and time replays."""
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):
+                fn()
+            side.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                for _ in range(per_graph):
+                    fn()
+            g.replay(); side.synchronize()
+            if collective:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(side)
+            for _ in range(replays):
+                g.replay()
+            e1.record(side); side.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / (replays * per_graph)
+        if collective:
+            t = torch.tensor([us], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            us = float(t.item())
+        torch.cuda.current_stream().wait_stream(side)
+        return us
+
+    NL = 4                                                     # weight sets cycled so that a layer's experts are not L2-resident
+    for name, prefill_tokens in (("olmoe", 512), ("qwen3-30b-a3b", 8192)):
+        E, K, I, D, f = MOE_SHAPES[name]
+        if E % world or prefill_tokens % world:
+            continue
+        fmt = mb.WF_I8 if f == "i8" else mb.WF_Q4R4
+        rng = np.random.default_rng(21)
+        pool = [_pool_expert(mb, name, rng) for _ in range(4)]
+        eps = [ExpertParallelMoe(E, K, I, D, efmt=fmt, device=local) for _ in range(NL)]
+        ones = [mb.Moe(E, K, I, D, efmt=fmt, device=local) for _ in range(NL)] if rank == 0 else []
+        for li in range(NL):
+            for e in range(E):
+                ex = pool[(e + li) % 4]
+                eps[li].upload_expert(e, *ex)
+                if rank == 0:
+                    ones[li].upload_expert(e, *ex)
+        it = [0]
+        # decode: the same token on every rank
+        x1 = torch.randn((1, D), generator=gen).to(dev); l1 = [torch.randn((1, E), generator=gen).to(dev) for _ in range(8)]
+        def ep_dec():
+            it[0] += 1
+            eps[it[0] % NL].decode(x1, l1[it[0] % 8])
+        us_ep_eager = timed(ep_dec, max(steps, 50))
+        us_ep = timed_graph(ep_dec, True)
+        us_one = None
+        if rank == 0:
+            o1 = torch.empty((1, D), device=dev)
+            def one_dec():
+                it[0] += 1
+                ones[it[0] % NL].apply_dev(o1.data_ptr(), x1.data_ptr(), 1, l1[it[0] % 8].data_ptr(), 0, 1, 0, 0,
+                                           mb.stream_handle(torch.cuda.current_stream()))
+            us_one = timed_graph(one_dec, False)
+        rows.append({"layer": name, "mode": "expert-parallel decode, one token replicated, all-reduce of the [K][D] row table",
+                     "tokens": 1, "experts_per_gpu": E // world, "us_sharded": round(us_ep, 1), "us_one_gpu": us_one and round(us_one, 1),
+                     "launch": "16 layer calls per replayed CUDA graph", "us_sharded_eager_python": round(us_ep_eager, 1)})
+        # prefill: the prompt's tokens split over the ranks, all-gather + partial sums + reduce-scatter
+        s = prefill_tokens // world
+        xs = torch.randn((s, D), generator=gen).to(dev); ls = torch.randn((s, E), generator=gen).to(dev)
+        def ep_pre():
+            it[0] += 1
+            eps[it[0] % NL].forward_gathered(xs, ls, order=1)
+        us_ep = timed(ep_pre, 5)
+        us_one = None
+        if rank == 0:
+            xa = torch.randn((prefill_tokens, D), generator=gen).to(dev); la = torch.randn((prefill_tokens, E), generator=gen).to(dev)
+            oa = torch.empty_like(xa)
+            def one_pre():
+                it[0] += 1
+                ones[it[0] % NL].apply_dev(oa.data_ptr(), xa.data_ptr(), prefill_tokens, la.data_ptr(), 1, 1, 0, 0,
+                                           mb.stream_handle(torch.cuda.current_stream()))
+            us_one = timed_local(one_pre, 5)
+            del xa, la, oa
+        rows.append({"layer": name, "mode": "expert-parallel prefill, all-gather + partial sums + reduce-scatter",
+                     "tokens": prefill_tokens, "experts_per_gpu": E // world, "us_sharded": round(us_ep, 1),
+                     "us_one_gpu": us_one and round(us_one, 1)})
+        for m in ones:
+            m.free()
+        for e_ in eps:
+            e_.moe.free()
+        del eps, ones
+    # row-sharded decode products of the Gemma-4-12B shape: up/gate, down and the 262144-row tied head, one pass of
+    # the three per call (more than L2 per GPU at every N), each followed by its all-gather
+    rng = np.random.default_rng(22)
+    shapes = [(15360, 3840), (3840, 15360), (262144, 3840)]
+    sh, full, xs_ = [], [], []
+    for (O, I) in shapes:
+        lo, hi, per = shard_rows(O, world, rank, 1)
+        # only this rank's rows are generated (timing does not depend on the values)
+        wq = rng.integers(-127, 128, (hi - lo, I), dtype=np.int8); sc = np.full(hi - lo, 0.01, np.float32)
+        sh.append(RowShardedMat.from_local_rows(mb.WF_I8, wq, sc, O, I, device=local))
+        xs_.append(torch.randn((1, I), generator=gen).to(dev))
+        if rank == 0:
+            wf = rng.integers(-127, 128, (O, I), dtype=np.int8)
+            full.append((mb.Mat.i8(wf, np.full(O, 0.01, np.float32), device=local), torch.empty((1, O), device=dev)))
+            del wf
+        del wq
+    us_sh_eager = timed(lambda: [m.decode(x) for m, x in zip(sh, xs_)], max(steps, 30))
+    us_sh = timed_graph(lambda: [m.decode(x) for m, x in zip(sh, xs_)], True, per_graph=4)
+    us_one = None
+    if rank == 0:
+        us_one = timed_graph(lambda: [mb.mat_apply_dev(w, y.data_ptr(), x.data_ptr(), 1, mb.stream_handle(torch.cuda.current_stream()))
+                                      for (w, y), x in zip(full, xs_)], False, per_graph=4)
+    rows.append({"layer": "gemma-4-12b dense", "mode": "row-sharded decode: 15360x3840 + 3840x15360 + 262144x3840 head, all-gather after each",
+                 "tokens": 1, "us_sharded": round(us_sh, 1), "us_one_gpu": us_one and round(us_one, 1),
+                 "launch": "4 passes per replayed CUDA graph", "us_sharded_eager_python": round(us_sh_eager, 1)})
+    for r in rows:
+        if r["us_one_gpu"]:
+            r["speedup_vs_one_gpu"] = round(r["us_one_gpu"] / r["us_sharded"], 3)
+            r["efficiency"] = round(r["us_one_gpu"] / (world * r["us_sharded"]), 3)
+    return {"world": world, "rows": rows,
+            "note": "efficiency = t(one GPU, same tokens) / (N * t(N GPUs)); one token on N GPUs is bound by launch and collective latency, not by bytes"}
+
+
+# ---------------------------------------------------------------------------
 # GPU arm
 # ---------------------------------------------------------------------------
 def run_gpu(args):
@@ -400,7 +571,9 @@ def run_gpu(args):
     dist = None
     if world > 1:
         import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        import datetime
+        # a rank that fails must not leave the others waiting in a collective for NCCL's default ten minutes
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local), timeout=datetime.timedelta(seconds=180))
     mb.init([local])
     dev = torch.device("cuda", local)
 
@@ -496,6 +669,12 @@ def run_gpu(args):
             assert ys[i].cpu().numpy().tobytes() == o.matmul_q_s(x, w, sc).tobytes(), "GPU result differs from the oracle"
             assert hy[i].tobytes() == ys[i].cpu().numpy().tobytes()
 
+    sharded = None
+    if dist is not None and not args.no_extras:
+        try:
+            sharded = run_sharded(torch, dist, mb, dev, local, rank, world, K)
+        except Exception as e:                                # an extra must not cost the headline line
+            sharded = {"error": f"{type(e).__name__}: {e}"[:300]}
     if dist is not None:
         t = torch.tensor([ms, dom_ms, e2e_s], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -518,6 +697,8 @@ def run_gpu(args):
     extras = None
     if world == 1 and not args.no_extras and len(SHAPES) == 6:
         extras = run_extras(torch, mb, dev, stream, W, local)
+    if sharded is not None:
+        extras = {"sharded": sharded}
     line = {"metric": METRIC, "value": round(value, 2), "unit": "GB/s", "n_gpus": world, "steps": K,
             "warmup": max(args.warmup, 3), "ms_per_step": round(ms / K, 6), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "int8xint8->int32", "data": "synthetic",

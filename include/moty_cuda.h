@@ -223,6 +223,15 @@ int moty_cuda_set_moe_fast_path(int on);
  * Per-row results equal what nn/moe.c:195-199 computes for that row. */
 int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_dev, const int *eid_dev,
                               int P, void *stream);
+/* One token, expert-parallel decode: like moe_apply_dev with S = 1 and selection order, and additionally
+ * rows_dev [K][D] receives every selected expert's OWN output row h_k (before the routing weight): the row itself
+ * for experts resident on this GPU, zeros for the others.  Every rank routes the same token redundantly (same
+ * logits -> same top-K), so the ranks' row tables have disjoint non-zero rows; their element-wise sum (an
+ * all-reduce, x + 0 is exact) is the full table on every rank, and moe_combine_dev(order 0) then adds the K rows
+ * in selection order exactly as nn/moe.c:146-149 does -- the result has the one-GPU bits.  out_dev [D] receives
+ * this GPU's partial sum.  Needs a layer shape the one-launch decode kernels take (MOTY_CUDA_ELIMIT otherwise). */
+int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float *out_dev, const float *x_dev,
+                              const float *logits_dev, int norm_topk, int *idx_dev, float *w_dev, void *stream);
 /* moe_combine_dev: out[s] = sum over the token's K selections of w[s][k] * h[s*K+k],
  * one fused multiply-add per step from 0, in selection order (order 0,
  * nn/moe.c:146-149) or ascending expert id (order 1, nn/moe.c:200-202). */

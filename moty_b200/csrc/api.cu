@@ -916,7 +916,7 @@ static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
         return launch_moe_decode_fused_q8((const float *)z, 1, 0, (int *)(z + 16), (float *)(z + 32),
                                           (const int8_t *)gate->codes, (const int8_t *)up->codes, (const int8_t *)down->codes,
                                           (const float *)gate->scales, (const float *)up->scales, (const float *)down->scales,
-                                          0, 0, 0, 0, x, (float *)c->g.p, out, 1, I, D, 0, 1,
+                                          0, 0, 0, 0, x, (float *)c->g.p, out, nullptr, 1, I, D, 0, 1,
                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st);
     }
     CKR(moty_grow(c, &c->u, hb));
@@ -1093,7 +1093,8 @@ extern "C" int moty_cuda_set_moe_fast_path(int on) {
 // expert-parallel peer sent here); out[i] is that expert's output for row i, zero when the
 // expert is not resident on this GPU.
 static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, int S, const float *logits,
-                        int order, int norm_topk, int *idx_out, float *w_out, const int *eid_given, cudaStream_t st) {
+                        int order, int norm_topk, int *idx_out, float *w_out, const int *eid_given, cudaStream_t st,
+                        float *rows = nullptr) {
     const int E = m->E, K = eid_given ? 1 : m->K, I = m->I, D = m->D;
     const bool q8 = m->efmt == MOTY_WF_I8;
     // rows per tile of the grouped products: 8 for the int8 tile kernel; 8, 16 or 32 for the Q4R4 MMA kernel
@@ -1117,7 +1118,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             CKR(launch_moe_decode_fused_q8(logits, E, norm_topk, m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u,
                                            (const int8_t *)m->d, (const float *)m->gs, (const float *)m->us,
                                            (const float *)m->ds, m->gcb, m->gsb / 4, m->dcb, m->dsb / 4, x,
-                                           (float *)c->g.p, out, K, I, D, m->e_lo, m->e_hi,
+                                           (float *)c->g.p, out, rows, K, I, D, m->e_lo, m->e_hi,
                                            reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st));
             if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
@@ -1131,13 +1132,14 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             CKR(launch_moe_decode_fused_q4(logits, E, norm_topk, m->idx, m->w, (const uint8_t *)m->g, (const uint8_t *)m->u,
                                            (const uint8_t *)m->d, (const uint16_t *)m->gs, (const uint16_t *)m->us,
                                            (const uint16_t *)m->ds, m->gcb, m->gsb / 2, m->dcb, m->dsb / 2, x,
-                                           (int8_t *)c->hq.p, (float *)c->hxs.p, (int *)c->hxsum.p, out, K, I, D,
+                                           (int8_t *)c->hq.p, (float *)c->hxs.p, (int *)c->hxsum.p, out, rows, K, I, D,
                                            m->e_lo, m->e_hi, reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1,
                                            c->sms, st));
             if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
         }
+        if (rows) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_d1_rows: this layer shape (E=%d K=%d I=%d D=%d) has no one-launch decode kernel", E, K, I, D);
         CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
     }
     // decode fast path: one token, int8 experts, selection-order combine -> two streaming kernels
@@ -1291,6 +1293,17 @@ extern "C" int moty_cuda_olmoe_moe(MotyCudaMoe *m, float *out, const float *x, i
 // ---------------------------------------------------------------------------
 // expert-parallel building blocks (device pointers)
 // ---------------------------------------------------------------------------
+extern "C" int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float *out_dev, const float *x_dev,
+                                         const float *logits_dev, int norm_topk, int *idx_dev, float *w_dev, void *stream) {
+    if (!m || !rows_dev || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev: null argument");
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    CK(cudaSetDevice(m->device));
+    if (g_moe_fast != 1) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev needs the one-launch decode path (set_moe_fast_path(1))");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev: x_dev must be 16-byte aligned");
+    return moe_apply_on(c, m, out_dev, x_dev, 1, logits_dev, 0, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream), rows_dev);
+}
+
 extern "C" int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_dev, const int *eid_dev,
                                          int P, void *stream) {
     if (!m || !h_dev || !x_rows_dev || !eid_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_experts_dev: null argument");

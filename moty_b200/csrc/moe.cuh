@@ -45,7 +45,7 @@ bool moe_decode_fused_q8_supported(int E, int K, int I, int D);
 int launch_moe_decode_fused_q8(const float *logits, int E, int norm_topk, int *idx_out, float *w_out,
                                const int8_t *g, const int8_t *u, const int8_t *d, const float *gs, const float *us,
                                const float *ds, size_t gstride, size_t gsstride, size_t dstride, size_t dsstride,
-                               const float *x, float *h, float *out, int K, int I, int D, int e_lo, int e_hi,
+                               const float *x, float *h, float *out, float *rows, int K, int I, int D, int e_lo, int e_hi,
                                unsigned *bar, int *err, int sms, cudaStream_t st);
 
 // ---- moe_decode_fused_q4.cu: the same for Q4R4 experts ----
@@ -54,5 +54,5 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                const uint8_t *g, const uint8_t *u, const uint8_t *d, const uint16_t *gs,
                                const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
-                               float *out, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
+                               float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
                                int sms, cudaStream_t st);

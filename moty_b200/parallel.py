@@ -8,12 +8,25 @@ process, so nothing here has a reference counterpart; the parity statement is
 * ``RowShardedMat``     rows of a matrix split over the ranks, all-gather of the
                         output slices.  Every output element is computed whole on
                         one GPU, so the gathered result is bit-identical.
-* ``ExpertParallelMoe`` experts split over the ranks in contiguous id ranges,
-                        tokens sharded over the ranks; routed rows travel to the
-                        expert's owner and the expert outputs travel back
-                        (all-to-all both ways); the home rank combines them in the
-                        reference's order, so the result is again bit-identical to
-                        the one-GPU block.
+* ``ExpertParallelMoe`` experts split over the ranks in contiguous id ranges.  Three routes:
+    ``decode``          one token replicated on every rank (its hidden state is, when the
+                        attention is replicated): every rank routes it redundantly and runs its
+                        resident experts in the one-launch decode kernel, which also leaves each
+                        selected expert's own output row in a [K][D] table (zeros for experts of
+                        other ranks).  ONE fixed-size all-reduce of that table (x + 0 is exact)
+                        and the combine in selection order: the one-GPU bits, no count exchange,
+                        no host synchronisation.
+    ``forward_gathered``  prefill: all-gather of the ranks' token shards and logits (with K = 8
+                        selections per token and 8 ranks this moves the bytes a dispatch of routed
+                        copies would), every rank routes all tokens redundantly and computes the
+                        partial sums of its experts, one reduce-scatter returns each rank its own
+                        tokens.  Two fixed-size collectives, no host synchronisation; the sum
+                        over ranks is taken in the collective's order, so the result agrees with
+                        the one-GPU block to f32 rounding (1e-5), not bit for bit.
+    ``forward``         the exact route: routed rows travel to the expert's owner and the
+                        expert outputs travel back (all-to-all both ways, sizes planned on the
+                        host); the home rank combines them in the reference's order:
+                        bit-identical to the one-GPU block.
 
 No kernel here waits on another rank: every exchange is a stream-ordered
 collective of the communication library.
@@ -62,6 +75,19 @@ class RowShardedMat:
         self.mat = Mat(fmt, codes, scales, O, I, device, rows=(self.lo, self.hi)) if self.hi > self.lo else None
         self.dev = torch.device("cuda", device)
 
+    @classmethod
+    def from_local_rows(cls, fmt, codes_local, scales_local, O, I, device=0, group=None):
+        """The same shard built from this rank's rows only (a loader that reads just its slice of a big matrix):
+        codes_local / scales_local hold rows [lo, hi) of the O x I matrix, lo/hi from shard_rows."""
+        self = cls.__new__(cls)
+        self.group = group
+        self.world = dist.get_world_size(group); self.rank = dist.get_rank(group)
+        self.O, self.I = O, I
+        self.lo, self.hi, self.per = shard_rows(O, self.world, self.rank, 4 if fmt != WF_I8 else 1)
+        self.mat = Mat(fmt, codes_local, scales_local, self.hi - self.lo, I, device) if self.hi > self.lo else None
+        self.dev = torch.device("cuda", device)
+        return self
+
     def apply(self, x: torch.Tensor, stream=None) -> torch.Tensor:
         """x [S][I] f32 on this GPU (replicated on every rank) -> y [S][O] on every rank."""
         S = x.shape[0]
@@ -80,6 +106,18 @@ class RowShardedMat:
         gathered = torch.empty((self.world, S, self.per), dtype=torch.float32, device=self.dev)
         dist.all_gather_into_tensor(gathered, part, group=self.group)
         return gathered.permute(1, 0, 2).reshape(S, self.world * self.per)[:, : self.O].contiguous()
+
+    def decode(self, x: torch.Tensor, stream=None) -> torch.Tensor:
+        """One row, x [1][I] replicated -> y [1][world * per] (the first O entries are the product).  The rank's slice is
+        written straight into its slot of a buffer kept across calls, one all-gather in place, nothing else."""
+        st = stream or torch.cuda.current_stream(self.dev)
+        if getattr(self, "_dec", None) is None:
+            self._dec = torch.zeros((self.world, self.per), dtype=torch.float32, device=self.dev)
+        if self.mat is not None:
+            from . import mat_apply_dev
+            mat_apply_dev(self.mat, self._dec[self.rank].data_ptr(), x.data_ptr(), 1, stream_handle(st))
+        dist.all_gather_into_tensor(self._dec, self._dec[self.rank], group=self.group)
+        return self._dec.view(1, self.world * self.per)
 
 
 # ---------------------------------------------------------------------------
@@ -130,7 +168,7 @@ class ExpertParallelMoe:
     the exchange logic pass numpy stand-ins."""
 
     def __init__(self, E, K, I, D, efmt=WF_I8, device=0, group=None, moe: Moe | None = None,
-                 expert_fn=None, combine_fn=None, route_fn=None):
+                 expert_fn=None, combine_fn=None, route_fn=None, rows_fn=None, partial_fn=None):
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
@@ -138,7 +176,8 @@ class ExpertParallelMoe:
         self.e_lo, self.e_hi = shard_experts(E, self.world, self.rank)
         self.per = E // self.world
         self.moe = moe
-        if moe is None and expert_fn is None:
+        self.rows_fn, self.partial_fn = rows_fn, partial_fn
+        if moe is None and expert_fn is None and rows_fn is None and partial_fn is None:
             self.moe = Moe(E, K, I, D, efmt, self.e_lo, self.e_hi, device)
         self.expert_fn, self.combine_fn, self.route_fn = expert_fn, combine_fn, route_fn
 
@@ -178,6 +217,51 @@ class ExpertParallelMoe:
             _ck(lib().moty_cuda_moe_combine_dev(C.c_void_p(out.data_ptr()), C.c_void_p(h_sk.data_ptr()),
                                                 C.c_void_p(w.data_ptr()), C.c_void_p(idx.data_ptr()),
                                                 s, self.K, self.D, int(order), C.c_void_p(st)))
+        return out
+
+    def decode(self, x: torch.Tensor, logits: torch.Tensor, norm_topk: int = 1) -> torch.Tensor:
+        """One token replicated on every rank: x [1][D], logits [1][E] -> out [1][D], the one-GPU bits."""
+        dev = x.device
+        if getattr(self, "_drows", None) is None:
+            self._drows = torch.empty((self.K, self.D), dtype=torch.float32, device=dev)
+            self._dpart = torch.empty((1, self.D), dtype=torch.float32, device=dev)
+            self._didx = torch.empty((1, self.K), dtype=torch.int32, device=dev)
+            self._dw = torch.empty((1, self.K), dtype=torch.float32, device=dev)
+            self._dout = torch.empty((1, self.D), dtype=torch.float32, device=dev)
+        st = stream_handle(torch.cuda.current_stream(dev)) if dev.type == "cuda" else 0
+        if self.rows_fn is not None:
+            self.rows_fn(self._drows, self._didx, self._dw, x, logits, norm_topk)
+        else:
+            _ck(lib().moty_cuda_moe_d1_rows_dev(self.moe.h, C.c_void_p(self._drows.data_ptr()), C.c_void_p(self._dpart.data_ptr()),
+                                                C.c_void_p(x.data_ptr()), C.c_void_p(logits.data_ptr()), int(norm_topk),
+                                                C.c_void_p(self._didx.data_ptr()), C.c_void_p(self._dw.data_ptr()), C.c_void_p(st)))
+        dist.all_reduce(self._drows, group=self.group)              # disjoint non-zero rows: the sum is exact
+        if self.combine_fn is not None:
+            return self.combine_fn(self._drows, self._dw, self._didx, 0)
+        _ck(lib().moty_cuda_moe_combine_dev(C.c_void_p(self._dout.data_ptr()), C.c_void_p(self._drows.data_ptr()),
+                                            C.c_void_p(self._dw.data_ptr()), C.c_void_p(self._didx.data_ptr()),
+                                            1, self.K, self.D, 0, C.c_void_p(st)))
+        return self._dout
+
+    def forward_gathered(self, x: torch.Tensor, logits: torch.Tensor, order: int = 1, norm_topk: int = 1) -> torch.Tensor:
+        """x [s][D], logits [s][E]: this rank's tokens, the same s on every rank -> out [s][D] (1e-5, see the module text)."""
+        s = x.shape[0]
+        x_all = torch.empty((self.world * s, self.D), dtype=torch.float32, device=x.device)
+        l_all = torch.empty((self.world * s, self.E), dtype=torch.float32, device=x.device)
+        dist.all_gather_into_tensor(x_all, x.contiguous(), group=self.group)
+        dist.all_gather_into_tensor(l_all, logits.contiguous(), group=self.group)
+        if self.partial_fn is not None:
+            part = self.partial_fn(x_all, l_all, order, norm_topk)
+        else:
+            part = torch.empty_like(x_all)
+            self.moe.apply_dev(part.data_ptr(), x_all.data_ptr(), self.world * s, l_all.data_ptr(), order, norm_topk, 0, 0,
+                               stream_handle(torch.cuda.current_stream(x.device)))
+        out = torch.empty((s, self.D), dtype=torch.float32, device=x.device)
+        if dist.get_backend(self.group) == "gloo":                  # the CPU tests: gloo has no reduce-scatter
+            dist.all_reduce(part, group=self.group)
+            out.copy_(part[self.rank * s:(self.rank + 1) * s])
+        else:
+            dist.reduce_scatter_tensor(out, part, group=self.group)
         return out
 
     def forward(self, x: torch.Tensor, logits: torch.Tensor, order: int = 1, norm_topk: int = 1) -> torch.Tensor:

@@ -42,9 +42,14 @@ def _worker(rank, world, port):
             y = sh.apply(torch.from_numpy(x).to(dev))
             torch.cuda.synchronize()
             assert y.cpu().numpy().tobytes() == whole.tobytes(), f"row shards differ at {O}x{I} S={S}"
+            if S == 1:                                       # the decode form: slice written in place, one all-gather
+                for _ in range(2):
+                    y1 = sh.decode(torch.from_numpy(x).to(dev))
+                    torch.cuda.synchronize()
+                    assert y1[:, :O].cpu().numpy().tobytes() == whole.tobytes(), "row-shard decode differs"
 
         # ---- expert parallel: tokens sharded, experts sharded, result bit-identical ----
-        E, K, I, D, S_total = 8, 2, 64, 128, 13
+        E, K, I, D, S_total = 8, 2, 64, 128, 13          # (with 2 ranks: 4 experts each)
         g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
         d = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
         gs, us = (rng.uniform(0.001, 0.02, (E, I)).astype(np.float32) for _ in range(2))
@@ -62,6 +67,36 @@ def _worker(rank, world, port):
             out = ep.forward(torch.from_numpy(x_all[mine]).to(dev), torch.from_numpy(lg_all[mine]).to(dev), order=order)
             torch.cuda.synchronize()
             assert out.cpu().numpy().tobytes() == whole[mine].tobytes(), f"expert-parallel result differs (order {order})"
+        # ---- the routes without a host-side plan ----
+        # decode: the same token on every rank, one all-reduce of the [K][D] row table -> the one-GPU bits
+        for t in range(3):
+            x1, l1 = x_all[t:t + 1], lg_all[t:t + 1]
+            out = ep.decode(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
+            torch.cuda.synchronize()
+            assert out.cpu().numpy().tobytes() == ref.d1(x1, l1).tobytes(), "expert-parallel decode differs"
+        # prefill: all-gather + partial sums + reduce-scatter (sum over ranks in the collective's order: 1e-5)
+        s_each = 6
+        xs, ls = x_all[:world * s_each], lg_all[:world * s_each]
+        whole = ref.batch(xs, ls)
+        mine2 = slice(rank * s_each, (rank + 1) * s_each)
+        out = ep.forward_gathered(torch.from_numpy(xs[mine2]).to(dev), torch.from_numpy(ls[mine2]).to(dev), order=1)
+        torch.cuda.synchronize()
+        assert np.abs(out.cpu().numpy() - whole[mine2]).max() <= 1e-5 * np.abs(whole).max()
+
+        # ---- Q4R4 experts, decode route ----
+        E4, K4, I4, D4 = 16, 4, 96, 128
+        mk = lambda n: (rng.integers(0, 256, n * 64, dtype=np.uint8), rng.uniform(0.001, 0.01, n * 4).astype(np.float16).view(np.uint16))
+        ng, nd = (I4 // 4) * (D4 // 32), (D4 // 4) * (I4 // 32)
+        ref4 = mb.Moe(E4, K4, I4, D4, efmt=mb.WF_Q4R4, device=rank)
+        ep4 = ExpertParallelMoe(E4, K4, I4, D4, efmt=mb.WF_Q4R4, device=rank)
+        for e in range(E4):
+            (g4, gs4), (u4, us4), (d4, ds4) = mk(ng), mk(ng), mk(nd)
+            ref4.upload_expert(e, g4, gs4, u4, us4, d4, ds4); ep4.upload_expert(e, g4, gs4, u4, us4, d4, ds4)
+        for t in range(3):
+            x1 = rng.standard_normal((1, D4)).astype(np.float32); l1 = (rng.standard_normal((1, E4)) * 0.7).astype(np.float32)
+            out = ep4.decode(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
+            torch.cuda.synchronize()
+            assert out.cpu().numpy().tobytes() == ref4.d1(x1, l1).tobytes(), "expert-parallel Q4R4 decode differs"
     finally:
         dist.destroy_process_group()
 

@@ -105,6 +105,72 @@ def test_expert_parallel_exchange_two_ranks(order):
     mp.spawn(_worker, args=(2, port, 11, order), nprocs=2, join=True)
 
 
+def _fixed_size_worker(rank, world, port):
+    """The two routes without a host-side plan: replicated-token decode (all-reduce of the [K][D] row table, exact)
+    and prefill by all-gather + reduce-scatter (f32 rounding)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from moty_b200.parallel import ExpertParallelMoe
+        from oracle import Experts, Oracle
+        o = Oracle()
+        E, K, I, D = 8, 3, 32, 64
+        g, u, d, gs, us, ds = _make_layer(5, E, K, I, D)
+        ex = Experts(E, K, I, D, g, u, d, gs, us, ds)
+        lo, hi = rank * (E // world), (rank + 1) * (E // world)
+
+        def expert_row(xr, e):
+            h = o.silu_mul(o.matmul_q_s(xr, g[e], gs[e]), o.matmul_q_s(xr, u[e], us[e]))
+            return o.matmul_q_s(h, d[e], ds[e])[0]
+
+        def fma32(a, b, c):
+            return (np.float64(a) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)
+
+        def rows_fn(rows, idx, w, x, logits, norm):
+            i_, w_, _ = o.route_topk(logits.numpy(), K)
+            idx.copy_(torch.from_numpy(i_)); w.copy_(torch.from_numpy(w_))
+            rows.zero_()
+            for k, e in enumerate(i_[0].tolist()):
+                if lo <= e < hi:
+                    rows[k] = torch.from_numpy(expert_row(x.numpy(), e))
+
+        def combine_fn(rows, w, idx, order_):
+            acc = np.zeros(D, np.float32)
+            for k in range(K):
+                acc = fma32(w[0, k].item(), rows[k].numpy(), acc)
+            return torch.from_numpy(acc[None])
+
+        def partial_fn(x_all, l_all, order_, norm):
+            i_, w_, _ = o.route_topk(l_all.numpy(), K)
+            out = np.zeros(x_all.shape, np.float32)
+            for t in range(x_all.shape[0]):
+                ks = sorted(range(K), key=lambda k: int(i_[t, k])) if order_ == 1 else list(range(K))
+                for k in ks:
+                    if lo <= i_[t, k] < hi:
+                        out[t] = fma32(w_[t, k], expert_row(x_all[t:t + 1].numpy(), int(i_[t, k])), out[t])
+            return torch.from_numpy(out)
+
+        ep = ExpertParallelMoe(E, K, I, D, rows_fn=rows_fn, combine_fn=combine_fn, partial_fn=partial_fn)
+        rng = np.random.default_rng(6)
+        for _ in range(3):                                   # the same token on every rank
+            x = rng.standard_normal((1, D)).astype(np.float32); lg = (rng.standard_normal((1, E)) * 0.7).astype(np.float32)
+            got = ep.decode(torch.from_numpy(x), torch.from_numpy(lg)).numpy()
+            assert got.tobytes() == o.moe_d1(ex, x, lg)[0].tobytes()
+        s = 5                                                # tokens per rank
+        x_all = rng.standard_normal((world * s, D)).astype(np.float32)
+        lg_all = (rng.standard_normal((world * s, E)) * 0.7).astype(np.float32)
+        mine = slice(rank * s, (rank + 1) * s)
+        got = ep.forward_gathered(torch.from_numpy(x_all[mine]), torch.from_numpy(lg_all[mine]), order=1).numpy()
+        want = o.moe_batch(ex, x_all, lg_all)[0][mine]
+        assert np.abs(got - want).max() <= 1e-5 * np.abs(want).max()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_expert_parallel_fixed_size_routes_two_ranks():
+    mp.spawn(_fixed_size_worker, args=(2, _free_port()), nprocs=2, join=True)
+
+
 def _bad_plan_worker(rank, world, port):
     os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
     dist.init_process_group("gloo", rank=rank, world_size=world)
