@@ -18,7 +18,12 @@
  * `stream` (a cudaStream_t passed as void*, NULL = the library's own stream; a caller whose work is on CUDA's
  * default stream passes cudaStreamLegacy or cudaStreamPerThread, not 0) and
  * return without synchronising.  *_dev entries that take no matrix or layer handle run on the GPU that owns
- * their first device pointer (which must have been initialised).
+ * their first device pointer (which must have been initialised).  Every entry leaves the caller's current CUDA
+ * device as it found it.
+ *
+ * CUDA graphs: the *_dev entries can be captured, with two rules.  The per-device scratch grows on demand (which
+ * frees and reallocates): run the largest call of the pipeline once, then moty_cuda_scratch_freeze(device, 1), then
+ * capture.  And the first call of any entry on a device may set kernel attributes: make it before the capture.
  */
 #ifndef MOTY_CUDA_H
 #define MOTY_CUDA_H
@@ -58,6 +63,29 @@ const char *moty_cuda_last_error(void);
 int moty_cuda_sm_count(int device);
 /* block until everything enqueued on the library's stream of `device` is done */
 int moty_cuda_sync(int device);
+
+/* Status of the kernels with bounded waits.  Nothing in this library waits without a limit (mbarrier waits of the
+ * tensor-core GEMM and of the bulk-copy fed Q4R4/Q8R4 decode kernels, the grid barrier of the one-launch MoE/FFN
+ * decode kernels); a wait that runs out makes its kernel set a device error word and return with an incomplete
+ * result.  The host-pointer entries check the words themselves and return MOTY_CUDA_EKERNEL.  A device-resident
+ * pipeline (the *_dev entries return before anything ran) calls this instead, e.g. once per generated token: it
+ * waits for `stream` (NULL = the library's), returns 0 when no wait expired since the last check, else clears the
+ * words, puts the grid-barrier counters back to zero and returns MOTY_CUDA_EKERNEL (last_error names the kernel
+ * class).  It also reports a device-side position of moty_cuda_attn_core_posdev that left [0, pos_max] (the kernels
+ * clamp it instead of writing past the KV cache).  The reference's kernels cannot fail (hw/hw.h:58-124 return no status); this is the GPU-side addition. */
+int moty_cuda_kernel_status(int device, void *stream);
+/* Diagnostic: enqueue a tiny kernel that runs the give-up path of one wait class on purpose -- the production wait
+ * function on something nobody completes, with a limit well under a millisecond; it polls, gives up, sets the
+ * error word and exits (no fault, no trap, no hang).  which: 0 = GEMM pipeline wait, 1 = grid barrier (leaves the
+ * barrier counters inconsistent, as a real expiry would), 2 = bulk-copy wait.  moty_cuda_kernel_status must then
+ * report MOTY_CUDA_EKERNEL once and the next ordinary call must succeed. */
+int moty_cuda_selftest_expire_wait(int device, int which, void *stream);
+/* The per-device scratch of the drivers grows on demand, which frees and reallocates it.  A captured CUDA graph
+ * holds the addresses it was captured with, so: run the largest call once, then freeze (on = 1) before capturing;
+ * from then on a call that would need more scratch returns MOTY_CUDA_ELIMIT instead of moving the buffers under
+ * the graph.  on = 0 lifts the freeze (graphs captured before must then be dropped).  No reference counterpart:
+ * its drivers grow function-level static scratch with malloc (nn/matmul.c:55-58). */
+int moty_cuda_scratch_freeze(int device, int on);
 
 /* pinned host memory for callers that want asynchronous copies on the plain
  * (host-pointer) entries; ordinary malloc'd memory works too, only slower */
@@ -110,7 +138,9 @@ int moty_cuda_mat_apply_acc(MotyCudaMat *w, float *y, int32_t *acc, const float 
  * The quantized activation rows live in a fixed array inside the library
  * (8 x 16384 bytes of codes + 8 scales per GPU, held until the process exits), so
  *   1 <= S <= 8, I a multiple of 16, 16 <= I <= 16384; anything else is
- *   MOTY_CUDA_ELIMIT.
+ *   MOTY_CUDA_ELIMIT.  q_dev must be 16-byte aligned (the product kernel reads weights with 128-bit loads;
+ *   a sliced tensor may not be), y_dev, x_dev and scale_dev 4-byte aligned: MOTY_CUDA_EARG otherwise, before
+ *   any launch.  The caller's current device is left as it was.
  * The call needs no moty_cuda_init and calls no allocating routine.  Its FIRST
  * call on a device looks up the array's device address and sets kernel
  * attributes; make that first call before any stream capture.  All calls share
@@ -263,7 +293,8 @@ int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *strea
 int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
                               float eps, void *stream);
 /* The same add and norm folded into the decode product that consumes them (one launch instead of two):
- * y = W * rmsnorm(x + t) with gains gain_dev, and xout = x + t (xout_dev apart from x_dev: every CTA reads x).
+ * y = W * rmsnorm(x + t) with gains gain_dev, and xout = x + t (xout_dev must overlap neither x_dev nor t_dev: one CTA
+ * writes xout while every other still reads x and t; MOTY_CUDA_EARG otherwise).
  * One row; MOTY_WF_I8 matrices with I <= 4096, I a multiple of 16 (mat_addnorm_supported says whether a matrix
  * qualifies).  Same bits as add_rmsnorm_dev followed by mat_apply_dev. */
 int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w);

@@ -54,7 +54,10 @@ DevCtx *moty_ctx(int device) {
 
 int moty_grow(DevCtx *c, Buf *b, size_t bytes) {
     if (bytes <= b->cap) return 0;
-    CK(cudaSetDevice(c->dev));
+    if (c->frozen)
+        return moty_set_error(MOTY_CUDA_ELIMIT, "scratch of device %d is frozen (moty_cuda_scratch_freeze) and this call needs %zu bytes "
+                              "where %zu are reserved: run the largest call before freezing", c->dev, bytes, b->cap);
+    MOTY_USE_DEVICE(c->dev);
     if (b->p) { CK(cudaStreamSynchronize(c->stream)); CK(cudaFree(b->p)); b->p = nullptr; b->cap = 0; }
     size_t want = bytes + bytes / 4 + 256;
     CK(cudaMalloc(&b->p, want));
@@ -64,7 +67,7 @@ int moty_grow(DevCtx *c, Buf *b, size_t bytes) {
 
 int moty_grow_pinned(DevCtx *c, Buf *b, size_t bytes) {
     if (bytes <= b->cap) return 0;
-    CK(cudaSetDevice(c->dev));
+    MOTY_USE_DEVICE(c->dev);
     if (b->p) { CK(cudaStreamSynchronize(c->stream)); CK(cudaFreeHost(b->p)); b->p = nullptr; b->cap = 0; }
     size_t want = bytes + bytes / 4 + 256;
     CK(cudaMallocHost(&b->p, want));
@@ -94,7 +97,7 @@ extern "C" int moty_cuda_init(const int *devices, int ndev) {
         if (d < 0 || d >= have) return moty_set_error(MOTY_CUDA_EARG, "init: device %d of %d", d, have);
         if (moty_ctx(d)) continue;
         if (g_nctx >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "init: context table full");
-        CK(cudaSetDevice(d));
+        MOTY_USE_DEVICE(d);
         cudaDeviceProp prop;
         CK(cudaGetDeviceProperties(&prop, d));
         if (prop.major != 10)
@@ -142,9 +145,42 @@ extern "C" int moty_cuda_sm_count(int device) {
 extern "C" int moty_cuda_sync(int device) {
     DevCtx *c = moty_ctx(device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
-    CK(cudaSetDevice(device));
+    MOTY_USE_DEVICE(device);
     CK(cudaStreamSynchronize(c->stream));
     return 0;
+}
+
+extern "C" int moty_cuda_scratch_freeze(int device, int on) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    c->frozen = on != 0;
+    return 0;
+}
+
+extern "C" int moty_cuda_kernel_status(int device, void *stream) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    cudaStream_t st = stream ? (cudaStream_t)stream : c->stream;
+    int w[4] = {0, 0, 0, 0};
+    CK(cudaMemcpyAsync(w, c->err_dev, 16, cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    if (!w[0] && !w[1] && !w[2] && !w[3]) return 0;
+    CK(cudaMemsetAsync(c->err_dev, 0, 16, st));
+    // a grid barrier that gave up leaves its arrival count and generation inconsistent: back to zero for the next launch
+    if (w[1]) CK(cudaMemsetAsync(c->ctr + 4, 0, 8, st));
+    CK(cudaStreamSynchronize(st));
+    return moty_set_error(MOTY_CUDA_EKERNEL, "kernel error since the last check:%s%s%s%s (results since then are incomplete or wrong)",
+                          w[0] ? " tensor-core GEMM pipeline wait expired;" : "", w[1] ? " grid barrier of a one-launch MoE/FFN decode kernel expired;" : "",
+                          w[2] ? " bulk-copy wait of a Q4R4/Q8R4 decode kernel expired;" : "",
+                          w[3] ? " attention position on the device was outside [0, pos_max] (clamped);" : "");
+}
+
+extern "C" int moty_cuda_selftest_expire_wait(int device, int which, void *stream) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    return launch_selftest_expire(which, c->err_dev, reinterpret_cast<unsigned *>(c->ctr) + 4, stream ? (cudaStream_t)stream : c->stream);
 }
 
 extern "C" int moty_cuda_host_alloc(void **p, size_t bytes) {
@@ -198,7 +234,7 @@ extern "C" int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void 
     size_t dummy;
     if (o0 > 0) { CKR(mat_sizes(fmt, o0, I, &cb0, &sb0)); } else { cb0 = sb0 = 0; }
     (void)dummy;
-    CK(cudaSetDevice(device));
+    MOTY_USE_DEVICE(device);
     MotyCudaMat *m = new (std::nothrow) MotyCudaMat();
     if (!m) return moty_set_error(MOTY_CUDA_ENOMEM, "upload_mat: host allocation");
     memset(m, 0, sizeof *m);
@@ -397,7 +433,7 @@ extern "C" int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float
     if (!w || !y_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_dev: null argument");
     DevCtx *c = moty_ctx(w->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
-    CK(cudaSetDevice(w->device));
+    MOTY_USE_DEVICE(w->device);
     return mat_apply_on(c, w, y_dev, x_dev, S, nullptr, pick_stream(c, stream));
 }
 
@@ -411,11 +447,19 @@ extern "C" int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, con
                                                float *xout_dev, const float *gain_dev, float eps, void *stream) {
     if (!w || !y_dev || !x_dev || !t_dev || !xout_dev || !gain_dev)
         return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: null argument");
-    if (!moty_cuda_mat_addnorm_supported(w) || xout_dev == x_dev || ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(t_dev)) & 15))
-        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: wants a MOTY_WF_I8 matrix with I <= 4096 (a multiple of 16) and xout apart from x");
+    // CTA 0 writes xout while every other CTA still reads x and t to form its own copy of the row: xout must not
+    // overlap either of them
+    auto overlaps = [&](const float *a) {
+        return reinterpret_cast<uintptr_t>(xout_dev) < reinterpret_cast<uintptr_t>(a + w->I) &&
+               reinterpret_cast<uintptr_t>(a) < reinterpret_cast<uintptr_t>(xout_dev + w->I);
+    };
+    if (!moty_cuda_mat_addnorm_supported(w) || overlaps(x_dev) || overlaps(t_dev) ||
+        ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(t_dev)) & 15))
+        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: wants a MOTY_WF_I8 matrix with I <= 4096 (a multiple of 16), x and t "
+                              "16-byte aligned, and xout overlapping neither x nor t");
     DevCtx *c = moty_ctx(w->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
-    CK(cudaSetDevice(w->device));
+    MOTY_USE_DEVICE(w->device);
     return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, x_dev, nullptr, nullptr, y_dev, nullptr,
                             1, w->I, w->O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, pick_stream(c, stream),
                             t_dev, gain_dev, xout_dev, eps);
@@ -427,7 +471,7 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     if (S <= 0) return 0;
     DevCtx *c = moty_ctx(w->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
-    CK(cudaSetDevice(w->device));
+    MOTY_USE_DEVICE(w->device);
     size_t xb = (size_t)S * w->I * 4, yb = (size_t)S * w->O * 4;
     CKR(moty_grow(c, &c->dx, xb));
     CKR(moty_grow(c, &c->dy, yb));
@@ -516,7 +560,7 @@ static int ctx0(DevCtx **c) {
     int dev = first_device();
     if (dev < 0) return moty_set_error(MOTY_CUDA_EINIT, "library not initialised");
     *c = moty_ctx(dev);
-    CK(cudaSetDevice(dev));
+    MOTY_USE_DEVICE(dev);
     return 0;
 }
 
@@ -531,7 +575,7 @@ static int ctx_of(const void *dev_ptr, DevCtx **c) {
     }
     *c = moty_ctx(at.device);
     if (!*c) return moty_set_error(MOTY_CUDA_EINIT, "device %d (owner of the pointer) not initialised", at.device);
-    CK(cudaSetDevice(at.device));
+    MOTY_USE_DEVICE(at.device);
     return 0;
 }
 
@@ -669,7 +713,7 @@ extern "C" int moty_cuda_head_argmax_dev(MotyCudaMat *head, const float *x_dev, 
     if (S <= 0) return 0;
     DevCtx *c = moty_ctx(head->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", head->device);
-    CK(cudaSetDevice(head->device));
+    MOTY_USE_DEVICE(head->device);
     cudaStream_t st = pick_stream(c, stream);
     float *lg = logits_dev;
     if (!lg) {
@@ -689,7 +733,7 @@ extern "C" int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, i
     if (S <= 0) return 0;
     DevCtx *c = moty_ctx(head->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", head->device);
-    CK(cudaSetDevice(head->device));
+    MOTY_USE_DEVICE(head->device);
     const size_t xb = (size_t)S * head->I * 4, lb = (size_t)S * head->O * 4;
     CKR(moty_grow(c, &c->dx, xb));
     CKR(moty_grow(c, &c->dlogits, lb));
@@ -730,7 +774,7 @@ extern "C" int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, cons
     if (embed->fmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: MOTY_WF_I8 table only");
     DevCtx *c = moty_ctx(embed->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", embed->device);
-    CK(cudaSetDevice(embed->device));
+    MOTY_USE_DEVICE(embed->device);
     return launch_embed_rows(out_dev, (const int8_t *)embed->codes, (const float *)embed->scales, ids_dev, S, embed->I, embed->O,
                              scale, pick_stream(c, stream));
 }
@@ -763,7 +807,7 @@ extern "C" int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_h
     if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads || head_dim <= 0 || head_dim > 256 || rot < 0 ||
         rot > head_dim || (rot & 1) || max_t <= 0)
         return moty_set_error(MOTY_CUDA_EARG, "attn_create: H=%d KV=%d hd=%d rot=%d max_t=%d", n_heads, n_kv_heads, head_dim, rot, max_t);
-    CK(cudaSetDevice(device));
+    MOTY_USE_DEVICE(device);
     MotyCudaAttn *a = new (std::nothrow) MotyCudaAttn();
     if (!a) return moty_set_error(MOTY_CUDA_ENOMEM, "attn_create: host allocation");
     memset(a, 0, sizeof *a);
@@ -822,19 +866,19 @@ static int attn_core_on(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_
     if (!a || !ctx_dev || !q_dev || !k_dev || !v_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_core_dev: null argument");
     DevCtx *c = moty_ctx(a->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
-    CK(cudaSetDevice(a->device));
+    MOTY_USE_DEVICE(a->device);
     const size_t sb = attn_scratch_bytes(S, a->H, a->KV, a->hd, c->sms);
     if (sb) CKR(moty_grow(c, &c->attn, sb));
     return launch_attn_core(ctx_dev, q_dev, k_dev, v_dev, S, pos_base, a->H, a->KV, a->hd, a->rot, a->theta, a->eps, a->qn,
                             a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, sb ? (float *)c->attn.p : nullptr,
-                            pos_dev, c->sms, pick_stream(c, stream));
+                            pos_dev, c->err_dev + 3, c->sms, pick_stream(c, stream));
 }
 
 extern "C" int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream) {
     if (!a || !ctx_dev || !gate_dev) return moty_set_error(MOTY_CUDA_EARG, "attn_gate_dev: null argument");
     DevCtx *c = moty_ctx(a->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
-    CK(cudaSetDevice(a->device));
+    MOTY_USE_DEVICE(a->device);
     return launch_attn_gate(ctx_dev, gate_dev, (long long)S * a->H * a->hd, pick_stream(c, stream));
 }
 
@@ -844,7 +888,7 @@ extern "C" int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, 
     if (S <= 0) return 0;
     DevCtx *c = moty_ctx(a->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", a->device);
-    CK(cudaSetDevice(a->device));
+    MOTY_USE_DEVICE(a->device);
     const size_t qb = (size_t)S * a->H * a->hd * 4, kb = (size_t)S * a->KV * a->hd * 4;
     CKR(moty_grow(c, &c->dx, qb + 2 * kb));
     CKR(moty_grow(c, &c->dy, qb));
@@ -931,7 +975,7 @@ extern "C" int moty_cuda_ffn_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat
     if (!gate || !up || !down || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "ffn_dev: null argument");
     DevCtx *c = moty_ctx(gate->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", gate->device);
-    CK(cudaSetDevice(gate->device));
+    MOTY_USE_DEVICE(gate->device);
     if (S <= 0) return 0;
     return ffn_on(c, gate, up, down, act, out_dev, x_dev, S, pick_stream(c, stream));
 }
@@ -941,7 +985,7 @@ extern "C" int moty_cuda_ffn(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
     if (!gate || !up || !down || !out || !x) return moty_set_error(MOTY_CUDA_EARG, "ffn: null argument");
     DevCtx *c = moty_ctx(gate->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", gate->device);
-    CK(cudaSetDevice(gate->device));
+    MOTY_USE_DEVICE(gate->device);
     if (S <= 0) return 0;
     size_t xb = (size_t)S * gate->I * 4;
     CKR(moty_grow(c, &c->dx, xb));
@@ -989,7 +1033,7 @@ extern "C" int moty_cuda_moe_create(MotyCudaMoe **out, int E, int K, int I, int 
     if (efmt == MOTY_WF_I8 && (I % 16 || D % 16)) return moty_set_error(MOTY_CUDA_EARG, "moe_create: int8 experts need I, D %% 16 == 0");
     if (efmt == MOTY_WF_Q4R4 && (I % 32 || D % 32)) return moty_set_error(MOTY_CUDA_EARG, "moe_create: Q4R4 experts need I, D %% 32 == 0");
     if (I > MOTY_QROW_MAX || D > MOTY_QROW_MAX) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_create: width above %d", MOTY_QROW_MAX);
-    CK(cudaSetDevice(device));
+    MOTY_USE_DEVICE(device);
     MotyCudaMoe *m = new (std::nothrow) MotyCudaMoe();
     if (!m) return moty_set_error(MOTY_CUDA_ENOMEM, "moe_create: host allocation");
     memset(m, 0, sizeof *m);
@@ -1032,7 +1076,7 @@ extern "C" int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *
     if (eid < m->e_lo || eid >= m->e_hi) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert: expert %d outside [%d,%d)", eid, m->e_lo, m->e_hi);
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
-    CK(cudaSetDevice(m->device));
+    MOTY_USE_DEVICE(m->device);
     size_t le = (size_t)(eid - m->e_lo);
     CK(cudaMemcpyAsync((char *)m->g + le * m->gcb, g, m->gcb, cudaMemcpyHostToDevice, c->stream));
     CK(cudaMemcpyAsync((char *)m->u + le * m->gcb, u, m->gcb, cudaMemcpyHostToDevice, c->stream));
@@ -1243,7 +1287,7 @@ extern "C" int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const flo
     if (!m || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_apply_dev: null argument");
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
-    CK(cudaSetDevice(m->device));
+    MOTY_USE_DEVICE(m->device);
     if (S <= 0) return 0;
     return moe_apply_on(c, m, out_dev, x_dev, S, logits_dev, order, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream));
 }
@@ -1252,7 +1296,7 @@ static int moe_host(MotyCudaMoe *m, float *out, const float *x, int S, const flo
     if (!m || !out || !x) return moty_set_error(MOTY_CUDA_EARG, "moe: null argument");
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
-    CK(cudaSetDevice(m->device));
+    MOTY_USE_DEVICE(m->device);
     if (S <= 0) return 0;
     size_t xb = (size_t)S * m->D * 4, lb = (size_t)S * m->E * 4;
     CKR(moty_grow(c, &c->dx, xb));
@@ -1298,7 +1342,7 @@ extern "C" int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float 
     if (!m || !rows_dev || !out_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev: null argument");
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
-    CK(cudaSetDevice(m->device));
+    MOTY_USE_DEVICE(m->device);
     if (g_moe_fast != 1) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev needs the one-launch decode path (set_moe_fast_path(1))");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev: x_dev must be 16-byte aligned");
     return moe_apply_on(c, m, out_dev, x_dev, 1, logits_dev, 0, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream), rows_dev);
@@ -1309,7 +1353,7 @@ extern "C" int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const flo
     if (!m || !h_dev || !x_rows_dev || !eid_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_experts_dev: null argument");
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
-    CK(cudaSetDevice(m->device));
+    MOTY_USE_DEVICE(m->device);
     if (P <= 0) return 0;
     return moe_apply_on(c, m, h_dev, x_rows_dev, P, nullptr, 0, 0, nullptr, nullptr, eid_dev, pick_stream(c, stream));
 }

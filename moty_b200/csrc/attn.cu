@@ -19,6 +19,7 @@ struct AttnArgs {
     int8_t *K8, *V8; float *Ks, *Vs;     // int8 cache [KV][max_t][hd] + scales [KV][max_t], or null
     int S, pos_base, H, KV, hd, rot, max_t;
     float theta, eps, scale;
+    int *err;                            // device word set when *pos_dev is outside [0, pos_base]
     const int *pos_dev;                  // when set, the first position is read from the device (a captured decode step
                                          // is replayed with a position that moves); pos_base then only sizes the launch
 };
@@ -67,7 +68,14 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(AttnArgs a) {
     const int hh = isq ? slot : slot - a.H;
     float *row = isq ? a.q + (size_t)s * a.H * hd + (size_t)hh * hd : a.k + (size_t)s * a.KV * hd + (size_t)hh * hd;
     const float *nw = isq ? a.qn : a.kn;
-    const int pos = (a.pos_dev ? *a.pos_dev : a.pos_base) + s;
+    int p0 = a.pos_base;
+    if (a.pos_dev) {
+        // the device counter may not leave [0, pos_base] (pos_base is the documented maximum and sized the cache check on
+        // the host): a stale or over-replayed counter is clamped instead of storing past the cache, and reported
+        p0 = *a.pos_dev;
+        if (p0 < 0 || p0 > a.pos_base) { if (i == 0 && a.err) atomicExch(a.err, 1); p0 = p0 < 0 ? 0 : a.pos_base; }
+    }
+    const int pos = p0 + s;
     float x = i < hd ? row[i] : 0.f;
     if (nw) {                                                  // hw/hw_ops.h:14-18
         const double ms = block_sum_f64((double)x * (double)x, red64);
@@ -168,7 +176,11 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     }
     pdl_trigger();
     pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel (without FUSE)
-    if (a.pos_dev) { n = *a.pos_dev + s + 1; t_hi = t_lo + span < n ? t_lo + span : n; }
+    if (a.pos_dev) {
+        int p0 = *a.pos_dev;                                            // clamped to [0, pos_base] like attn_prep_kernel does
+        if (p0 < 0 || p0 > a.pos_base) { if (tid == 0 && a.err) atomicExch(a.err, 1); p0 = p0 < 0 ? 0 : a.pos_base; }
+        n = p0 + s + 1; t_hi = t_lo + span < n ? t_lo + span : n;
+    }
     if (FUSE) {
         const int pos = n - 1;
         const bool own = pos >= t_lo && pos < t_lo + span;
@@ -573,7 +585,7 @@ size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {
 // the launch, so that one captured launch serves every position up to it).
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int sms, cudaStream_t st) {
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st) {
     if (S <= 0) return 0;
     if (hd <= 0 || hd > 256 || hd % 4 || rot < 0 || rot > hd || (rot & 1) || H <= 0 || KV <= 0 || H % KV || pos_base < 0 ||
         pos_base + S > max_t)
@@ -581,7 +593,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     AttnArgs a;
     a.q = q; a.k = k; a.v = v; a.ctx = ctx; a.qn = qn; a.kn = kn; a.K = K; a.V = V; a.K8 = K8; a.V8 = V8; a.Ks = Ks; a.Vs = Vs;
     a.S = S; a.pos_base = pos_base; a.H = H; a.KV = KV; a.hd = hd; a.rot = rot; a.max_t = max_t;
-    a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd); a.pos_dev = pos_dev;
+    a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd); a.pos_dev = pos_dev; a.err = err;
     const int nth_prep = (hd + 31) / 32 * 32;
     // one token at a position read from the device (a replayed decode step): norm, rotation and cache store ride in the
     // scores launch, and q and k are not written back

@@ -71,7 +71,26 @@ struct DevCtx {
     Buf kcell;
     // device error word written by kernels whose bounded waits expire
     int *err_dev = nullptr;
+    // set by moty_cuda_scratch_freeze: the grow-only buffers may no longer move (a captured CUDA graph holds their addresses)
+    bool frozen = false;
 };
+
+// Every entry point that makes a GPU current puts the caller's device back before it returns.
+struct MotyDevGuard {
+    int prev = -1;
+    cudaError_t set(int device) {
+        if (prev < 0) {
+            cudaError_t e = cudaGetDevice(&prev);
+            if (e != cudaSuccess) { prev = -1; return e; }
+        }
+        return cudaSetDevice(device);
+    }
+    ~MotyDevGuard() { if (prev >= 0) cudaSetDevice(prev); }
+};
+#define MOTY_CAT2(a, b) a##b
+#define MOTY_CAT(a, b) MOTY_CAT2(a, b)
+// make `device` current for the rest of the enclosing scope
+#define MOTY_USE_DEVICE(device) MotyDevGuard MOTY_CAT(moty_dg_, __LINE__); CK(MOTY_CAT(moty_dg_, __LINE__).set(device))
 
 DevCtx *moty_ctx(int device);                       // nullptr when not initialised
 int moty_grow(DevCtx *c, Buf *b, size_t bytes);     // device buffer, grow-only
@@ -186,10 +205,9 @@ __device__ __forceinline__ float f16bits_to_f32(uint16_t h) {
 //   z = x * 32/ln2;  k = round(z);  r = z - k;  2^(k/32) from a 32-entry table and the exponent field;
 //   exp(x) = 2^(k/32) * (C0 r^3 + C1 r^2 + C2 r + 1) in f64, rounded ONCE to f32,
 // and x86-64 hosts with FMA run the build in which the compiler contracted the multiply-adds:
-// r = fma(32/ln2, x, -k) and the three polynomial steps below.  The restatement in
-// oracle/moty_oracle.c (oracle_expf) is the same sequence and is pinned against the host's expf on
-// every one of the 2^32 float inputs (tests/test_oracle.py checks a sample of them in each run); IEEE
-// f64 operations give the same bits here.  Entry i of the table is bits(2^(i/32) rounded to f64) - (i << 47).
+// r = fma(32/ln2, x, -k) and the three polynomial steps below.  The same sequence written in C for the
+// CPU checker equals the host's expf on every one of the 2^32 float inputs (the test-suite checks a
+// sample of them in each run); IEEE f64 operations give the same bits here.  Entry i of the table is bits(2^(i/32) rounded to f64) - (i << 47).
 
 __device__ __forceinline__ float moty_expf(float x) {
     static constexpr unsigned long long MOTY_EXP2_TAB[32] = {

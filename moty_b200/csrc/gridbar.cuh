@@ -26,18 +26,22 @@ __device__ __forceinline__ void gb_add_release(unsigned *p, unsigned v) {
 
 // Called by ALL threads of the CTA.  Returns false when the wait expired (to every thread).
 // Global writes made by any thread of any CTA before the barrier are visible to every thread after it.
-__device__ __forceinline__ bool grid_barrier_bounded(unsigned *bar, int *gave_up_smem) {
+// `expected` arrivals complete the barrier (the grid size in every production kernel) and `limit` polls bound the
+// wait; both are parameters so that the give-up path can be run on purpose with a count nobody completes.
+__device__ __forceinline__ bool grid_barrier_bounded(unsigned *bar, int *gave_up_smem, unsigned expected = 0,
+                                                     unsigned limit = GRIDBAR_SPIN_LIMIT) {
+    if (expected == 0) expected = gridDim.x;
     __syncthreads();                                   // this CTA's writes are done (and ordered before thread 0's release)
     if (threadIdx.x == 0) {
         const unsigned gen = gb_ld_acquire(bar + 1);   // cannot change before this CTA has arrived
         const unsigned old = gb_add_acq_rel(bar, 1u);
-        if (old == gridDim.x - 1) {
+        if (old == expected - 1) {
             asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(bar), "r"(0u) : "memory");
             gb_add_release(bar + 1, 1u);
         } else {
             unsigned n = 0;
             while (gb_ld_acquire(bar + 1) == gen) {
-                if (++n > GRIDBAR_SPIN_LIMIT) { *gave_up_smem = 1; break; }
+                if (++n > limit) { *gave_up_smem = 1; break; }
             }
         }
     }

@@ -1,6 +1,7 @@
 // kernels.cuh -- launchers of the device kernels (all enqueue on `st`, none synchronise).
 #pragma once
 #include "common.cuh"
+#include "waits.cuh"
 
 // ---- quant.cu ---------------------------------------------------------------
 int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cudaStream_t st);
@@ -85,7 +86,7 @@ int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *i
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int sms, cudaStream_t st);
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st);
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
 int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st);
 
@@ -138,3 +139,6 @@ int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st
 // persistent Q4R4 GEMV for 1..4 rows; S == 1 with x != null quantizes the row in the kernel
 int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, const int8_t *xq, const float *xs,
                        const int32_t *xsum, const uint8_t *form, float *y, int S, int I, int O, int sms, cudaStream_t st);
+
+// ---- selftest.cu: the give-up path of the bounded waits, run on purpose with a short limit ----
+int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cudaStream_t st);

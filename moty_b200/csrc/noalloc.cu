@@ -27,8 +27,6 @@ static bool g_ready[MOTY_MAX_DEV];
 
 // once per device: device address of the scratch, SM count, kernel attributes; allocates nothing
 static int noalloc_setup(int device) {
-    if (device < 0 || device >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "noalloc: device %d", device);
-    CK(cudaSetDevice(device));
     if (g_ready[device]) return 0;
     void *p = nullptr;
     CK(cudaGetSymbolAddress(&p, g_q8_noalloc_scratch));
@@ -50,6 +48,14 @@ extern "C" int moty_cuda_q8_apply_noalloc(float *y_dev, const float *x_dev, cons
     if (I < 16 || I > NOALLOC_MAX_I || I % 16)
         return moty_set_error(MOTY_CUDA_ELIMIT, "q8_apply_noalloc: I=%d, this entry takes multiples of 16 up to %d", I, NOALLOC_MAX_I);
     if (O < 1) return moty_set_error(MOTY_CUDA_EARG, "q8_apply_noalloc: O=%d", O);
+    // the product kernel reads the weights with 16-byte loads; unlike the matrices the library uploads itself, these
+    // pointers are the caller's and may be slices: refuse before any launch instead of faulting on the GPU
+    if (reinterpret_cast<uintptr_t>(q_dev) & 15)
+        return moty_set_error(MOTY_CUDA_EARG, "q8_apply_noalloc: q_dev must be 16-byte aligned");
+    if ((reinterpret_cast<uintptr_t>(y_dev) | reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(scale_dev)) & 3)
+        return moty_set_error(MOTY_CUDA_EARG, "q8_apply_noalloc: y_dev, x_dev and scale_dev must be 4-byte aligned");
+    if (device < 0 || device >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q8_apply_noalloc: device %d", device);
+    MOTY_USE_DEVICE(device);                       // the caller's current device is put back on return
     CKR(noalloc_setup(device));
     cudaStream_t st = (cudaStream_t)stream;
     int8_t *xi = (int8_t *)g_scratch_ptr[device];

@@ -256,13 +256,7 @@ constexpr unsigned G2_WAIT_LIMIT = 1u << 26;
 
 __device__ __forceinline__ unsigned g2_smem(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ bool g2_wait(unsigned long long *bar, unsigned parity) {
-    for (unsigned it = 0; it < G2_WAIT_LIMIT; it++) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(g2_smem(bar)), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
+    return moty_mbar_wait_bounded(g2_smem(bar), parity, G2_WAIT_LIMIT);
 }
 
 __global__ void __launch_bounds__(32) q4r4_g2_chain_kernel(Q4G2Args a) {

@@ -38,13 +38,7 @@ __device__ __forceinline__ void gb_expect(unsigned long long *bar, unsigned byte
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(gb_smem(bar)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ bool gb_wait(unsigned long long *bar, unsigned parity) {
-    for (unsigned it = 0; it < GB_WAIT_LIMIT; it++) {
-        unsigned ok;
-        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                     : "=r"(ok) : "r"(gb_smem(bar)), "r"(parity) : "memory");
-        if (ok) return true;
-    }
-    return false;
+    return moty_mbar_wait_bounded(gb_smem(bar), parity, GB_WAIT_LIMIT);
 }
 __device__ __forceinline__ int dp4a_us3(unsigned a, int b, int c) {
     int d;

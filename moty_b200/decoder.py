@@ -64,6 +64,7 @@ class DenseDecoder:
         t, dev = self.torch, self.dev
         qw, kw = self.H * self.hd, self.KV * self.hd
         e = lambda *shape: t.empty(shape, device=dev, dtype=t.float32)
+        self._drop_graph()                       # a captured step holds the addresses of the buffers replaced below
         self.cap = S
         self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
         self.x_alt = e(1, self.D)
@@ -73,12 +74,25 @@ class DenseDecoder:
         self.out_id = t.empty((1,), device=dev, dtype=t.int32)
         self.logits = e(1, self.head.O)
 
+    def _drop_graph(self):
+        """Forget the captured decode step and let the library's scratch grow again."""
+        if getattr(self, "_graph", None) is not None:
+            self._graph = None
+            _ck(lib().moty_cuda_scratch_freeze(self.dev.index or 0, 0))
+
+    def _check_kernels(self):
+        """After a stream synchronisation: did a bounded wait inside a kernel run out (incomplete results)?"""
+        _ck(lib().moty_cuda_kernel_status(self.dev.index or 0, C.c_void_p(stream_handle(self.stream))))
+
     def step(self, ids, pos_base, want_logits=False):
         """Tokens ``ids`` at positions pos_base.. : returns the greedy next token after the last of them
         (and the last token's logits when asked)."""
         t, L = self.torch, lib()
         ids = np.ascontiguousarray(ids, np.int32).ravel()
         S = ids.size
+        if S > getattr(self, "_max_S", 0):
+            self._drop_graph()                   # a larger batch than any before may grow the library's scratch
+            self._max_S = S
         if S > self.cap:
             self._alloc(S)
         if pos_base + S > self.max_t:
@@ -94,6 +108,7 @@ class DenseDecoder:
             _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(last), p(self.final_norm), 1, D, C.c_float(self.eps), sh))
             _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
             tok = int(self.out_id.cpu()[0])          # waits for the stream
+            self._check_kernels()
             if want_logits:
                 return tok, self.logits.cpu().numpy()[0]
         return tok
@@ -177,6 +192,8 @@ class DenseDecoder:
                 reset(first_tok, pos0)
                 self._decode_body(C.c_void_p(stream_handle(self.stream)))
             self.stream.synchronize()
+            # from here on the library's scratch may not move: the graph holds its addresses
+            _ck(lib().moty_cuda_scratch_freeze(self.dev.index or 0, 1))
             g = t.cuda.CUDAGraph()
             with t.cuda.graph(g, stream=self.stream):
                 self._decode_body(C.c_void_p(stream_handle(t.cuda.current_stream())))
@@ -186,8 +203,16 @@ class DenseDecoder:
             for _ in range(n):
                 self._graph.replay()
         self.stream.synchronize()
+        self._check_kernels()
         return [int(v) for v in self.hist[:n].cpu().numpy()]
 
     def close(self):
+        self._drop_graph()                       # lifts the scratch freeze taken for the captured step
         for a in self.attn:
             a.close()
+
+    def __del__(self):
+        try:
+            self._drop_graph()
+        except Exception:
+            pass

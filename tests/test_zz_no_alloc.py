@@ -47,3 +47,11 @@ def test_noalloc_rejects_sizes_beyond_its_scratch(gpu):
     for (S, I) in ((9, 1024), (0, 1024), (1, 16400), (1, 100), (1, 32768)):
         with pytest.raises(gpu.MotyCudaError, match="q8_apply_noalloc"):
             gpu.q8_apply_noalloc(p, p, p, p, S, I, 4, 0, 0)
+    # a weight pointer off the 16-byte grid (a sliced tensor) is refused on the host, before any launch: the product
+    # kernel reads weights with 128-bit loads.  Likewise f32 pointers off the 4-byte grid.
+    with pytest.raises(gpu.MotyCudaError, match="16-byte aligned"):
+        gpu.q8_apply_noalloc(p, p, p + 1, p, 1, 16, 1, 0, 0)
+    with pytest.raises(gpu.MotyCudaError, match="4-byte aligned"):
+        gpu.q8_apply_noalloc(p + 2, p, p, p, 1, 16, 1, 0, 0)
+    torch.cuda.synchronize()                              # nothing was launched, the context is intact
+    assert float(t.sum()) == 0.0
