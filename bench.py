@@ -365,20 +365,27 @@ def time_moe(torch, layers, name, S, dev, stream, reps=5, run=16):
 
 
 def run_moe_extras(torch, mb, dev, stream, local):
-    """One routed MoE layer, decode (S=1) and a small prefill batch, on the two MoE shapes of the
-    baseline: OLMoE-1B-7B (E=64, K=8, expert FFN 1024, hidden 2048, int8 experts) and
-    Qwen3-30B-A3B (E=128, K=8, expert FFN 768, hidden 2048, Q4R4 experts).
-    Bytes = the touched experts' gate+up+down (codes and scales)."""
+    """One routed MoE layer on the two MoE shapes of the baseline: OLMoE-1B-7B (E=64, K=8, expert FFN 1024, hidden
+    2048, int8 experts) and Qwen3-30B-A3B (E=128, K=8, expert FFN 768, hidden 2048, Q4R4 experts): decode (S=1), a small
+    batch (S=64) and the prefill sizes of the configs (OLMoE: its 512-token prompt; Qwen3-30B-A3B: 1024 tokens of its
+    8 x 1024).  Bytes = the touched experts' gate+up+down (codes and scales); ops = 2 * S * K * 3 * I * D."""
     rng = np.random.default_rng(2)
     rows = []
     for name in MOE_SHAPES:
-        E, K = MOE_SHAPES[name][:2]
+        E, K, I, D, f = MOE_SHAPES[name]
         layers, per_expert = make_moe_layers(mb, name, 4, local, rng)
         with torch.cuda.stream(stream):
-            for S in (1, 64):
-                us = time_moe(torch, layers, name, S, dev, stream)
+            for S in (1, 64, 512 if f == "i8" else 1024):
+                us = time_moe(torch, layers, name, S, dev, stream, reps=5 if S <= 64 else 3, run=16 if S <= 64 else 4)
                 touched = K * per_expert if S == 1 else min(E, S * K) * per_expert
-                rows.append({"layer": name, "S": S, "us": round(us, 1), "expert_GBs": round(touched / us / 1e3, 1)})
+                row = {"layer": name, "S": S, "us": round(us, 1), "expert_GBs": round(touched / us / 1e3, 1),
+                       "TOPS": round(2.0 * S * K * 3 * I * D / us / 1e6, 1)}
+                if f == "i8" and S >= 64:
+                    prev = mb.lib().moty_cuda_set_moe_batch_path(0)
+                    row["us_mma_sync_tiles"] = round(time_moe(torch, layers, name, S, dev, stream, reps=3, run=4), 1)
+                    mb.lib().moty_cuda_set_moe_batch_path(prev)
+                    row["path"] = "tcgen05 grouped (gate+up+SiLU one pass), 7 launches"
+                rows.append(row)
         for m in layers:
             m.free()
     return rows

@@ -244,6 +244,11 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
  * counterpart.  If the fused kernel's barrier wait ever expires (a fraction of a
  * second), the host-pointer entries return MOTY_CUDA_EKERNEL. */
 int moty_cuda_set_moe_fast_path(int on);
+/* Batches through int8 experts (moty_nn_moe_topk_batch, nn/moe.c:159-205) run their grouped products on the tensor
+ * cores (tcgen05, gate+up+SiLU in one pass) when the experts see 8 or more routed rows each on average, else on
+ * mma.sync tiles that stream the weights once.  Same arithmetic, same bits.  This switch lets a test compare the two:
+ * 1 = as described (default), 0 = mma.sync tiles always.  Returns the previous value; no reference counterpart. */
+int moty_cuda_set_moe_batch_path(int tensor_core);
 
 /* Expert-parallel building blocks (no reference counterpart: the reference is one
  * process).  Arithmetic is that of the block entries above, cut at the exchange.

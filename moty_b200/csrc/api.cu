@@ -940,6 +940,7 @@ extern "C" int moty_cuda_pack_q4r4(const float *w, int O, int I, uint8_t *q4, ui
 // dense FFN
 // ---------------------------------------------------------------------------
 static int g_moe_fast = 1;      // 1: one-launch decode kernels; 2: the split decode path; 0: general path only
+static int g_moe_tc = 1;        // int8 batches: 1 = grouped products on tcgen05 where the experts see >= 8 rows each; 0 = mma.sync tiles
 
 static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
                   float *out, const float *x, int S, cudaStream_t st) {
@@ -1126,6 +1127,12 @@ static int moe_ensure_plan(MotyCudaMoe *m, int S) {
 // 0: generic tile path; 1: best decode path (one fused launch where supported); 2: the split
 // decode path (router, gate/up and down as separate launches)
 
+extern "C" int moty_cuda_set_moe_batch_path(int tensor_core) {
+    int prev = g_moe_tc;
+    g_moe_tc = tensor_core != 0;
+    return prev;
+}
+
 extern "C" int moty_cuda_set_moe_fast_path(int on) {
     int prev = g_moe_fast;
     g_moe_fast = on < 0 ? 0 : (on > 2 ? 1 : on);
@@ -1144,7 +1151,11 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
     // rows per tile of the grouped products: 8 for the int8 tile kernel; 8, 16 or 32 for the Q4R4 MMA kernel
     // (more when experts see more rows each)
     int T = 8;
-    { long long per = (long long)S * K / (m->e_hi - m->e_lo > 0 ? m->e_hi - m->e_lo : 1); T = per >= 24 ? 32 : (per >= 12 ? 16 : 8); }
+    const long long per = (long long)S * K / E;                // routed rows an expert sees on average
+    T = per >= 24 ? 32 : (per >= 12 ? 16 : 8);
+    // batches whose experts see enough rows each take the tensor-core path (moe_tc.cu); its tiles are 16..128 rows
+    const bool tc = q8 && g_moe_tc && per >= 8 && moe_tc_supported(I, D) && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+    if (tc) T = moe_tc_tile_rows(per);
     CKR(moe_ensure_plan(m, eid_given ? (S + m->K - 1) / m->K : S));
     const int *idxp = m->idx; const float *wp = m->w;
     if (eid_given) {
@@ -1235,10 +1246,23 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
     CKR(moty_grow(c, &c->g, P * I * 4));
     CKR(moty_grow(c, &c->u, P * I * 4));
     CKR(moty_grow(c, &c->h, P * D * 4));
-    // rows the plan leaves unused (non-local experts) must not feed NaNs to the quantizers
-    CK(cudaMemsetAsync(c->g.p, 0, P * I * 4, st));
-    CK(cudaMemsetAsync(c->u.p, 0, P * I * 4, st));
-    if (q8) {
+    if (tc) {
+        // gather folded into the row quantizer, gate+up+SiLU in one tensor-core pass, row quantizer, down pass
+        const int El = m->e_hi - m->e_lo;
+        CKR(moty_grow(c, &c->xi, P * D + 1024));
+        CKR(moty_grow(c, &c->sx, P * 4));
+        CKR(moty_grow(c, &c->hq, P * I + 1024));
+        CKR(moty_grow(c, &c->hs, P * 4));
+        CKR(launch_qrow_i8_scatter(x, m->pos_of, S, K, (int8_t *)c->xi.p, (float *)c->sx.p, D, st));
+        CKR(launch_moe_tc_gateup((const Q8Tile *)m->t_gate, (const Q8Tile *)m->t_up, m->counters, T, (const int8_t *)m->g,
+                                 (const int8_t *)m->u, El, (const int8_t *)c->xi.p, (const float *)c->sx.p, (int)P,
+                                 (float *)c->g.p, I, D, c->err_dev, c->sms, st));
+        CKR(launch_qrow_i8_counted((const float *)c->g.p, (int8_t *)c->hq.p, (float *)c->hs.p, (int)P, I, m->counters + 1, st));
+        CKR(launch_moe_tc_down((const Q8Tile *)m->t_down, m->counters, T, (const int8_t *)m->d, El, (const int8_t *)c->hq.p,
+                               (const float *)c->hs.p, (int)P, (float *)c->h.p, I, D, c->err_dev, c->sms, st));
+    } else if (q8) {
+        CK(cudaMemsetAsync(c->g.p, 0, P * I * 4, st));
+        CK(cudaMemsetAsync(c->u.p, 0, P * I * 4, st));
         CKR(moty_grow(c, &c->xi, (size_t)S * D + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(moty_grow(c, &c->hq, P * I + 16));
@@ -1253,6 +1277,9 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         CKR(launch_q8_mma_grouped((const Q8Tile *)m->t_down, m->counters, ntiles_max, T, (const int8_t *)c->hq.p,
                                   (const float *)c->hs.p, nullptr, (float *)c->h.p, D, I, D, st));
     } else {
+        // rows the plan leaves unused (non-local experts) must not feed NaNs to the quantizers
+        CK(cudaMemsetAsync(c->g.p, 0, P * I * 4, st));
+        CK(cudaMemsetAsync(c->u.p, 0, P * I * 4, st));
         int nbD = D / 32, nbI = I / 32;
         CKR(moty_grow(c, &c->xi, (size_t)S * D + 16));
         CKR(moty_grow(c, &c->xs, (size_t)S * nbD * 4));

@@ -4,6 +4,8 @@
 #include "waits.cuh"
 
 // ---- quant.cu ---------------------------------------------------------------
+int launch_qrow_i8_scatter(const float *x, const int *pos_of, int S, int K, int8_t *xg, float *sxg, int n, cudaStream_t st);
+int launch_qrow_i8_counted(const float *x, int8_t *q, float *scale, int rows_max, int n, const int *nrows_dev, cudaStream_t st);
 int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cudaStream_t st);
 int launch_quant_g32(const float *x, int rows, int I, int8_t *xq, float *xs, int32_t *xsum, cudaStream_t st);
 int launch_quantize_rows(const float *w, int8_t *q, float *scale, int O, int I, cudaStream_t st);

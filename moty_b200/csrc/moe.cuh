@@ -56,3 +56,12 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
                                float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
                                int sms, cudaStream_t st);
+
+// ---- moe_tc.cu: the grouped expert products of an int8 batch on tcgen05 (work list = plan tiles x 128-row blocks) ----
+bool moe_tc_supported(int I, int D);
+int moe_tc_tile_rows(long long rows_per_expert);
+int launch_moe_tc_gateup(const Q8Tile *t_gate, const Q8Tile *t_up, const int *ntiles_dev, int tile_rows,
+                         const int8_t *g_slab, const int8_t *u_slab, int E_local, const int8_t *xg, const float *sxg,
+                         int P, float *h, int I, int D, int *err, int sms, cudaStream_t st);
+int launch_moe_tc_down(const Q8Tile *t_down, const int *ntiles_dev, int tile_rows, const int8_t *d_slab, int E_local,
+                       const int8_t *hq, const float *hs, int P, float *hout, int I, int D, int *err, int sms, cudaStream_t st);

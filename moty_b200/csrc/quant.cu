@@ -54,6 +54,78 @@ __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ 
     if (threadIdx.x == 0) scale[row] = s;
 }
 
+// One routed token per CTA: quantize its row once (moty_hw_qrow_i8) and write the codes and the scale to every
+// position the routing plan gave its K selections in the per-expert gathered batch (pos_of[s*K + k], -1 = the
+// expert lives on another GPU).  This is the gather of nn/moe.c:172-186 folded into the row quantizer: the grouped
+// tensor-core products then read contiguous rows per expert.
+__global__ void __launch_bounds__(256) qrow_i8_scatter_kernel(const float *__restrict__ x, const int *__restrict__ pos_of, int K,
+                                                              int8_t *__restrict__ xg, float *__restrict__ sxg, int n) {
+    __shared__ float red[8];
+    __shared__ int pos_s[64];
+    const size_t row = blockIdx.x;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + row * n);
+    if (threadIdx.x < K) pos_s[threadIdx.x] = pos_of[row * K + threadIdx.x];
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < n / 4; i += 256) {
+        float4 v = x4[i];
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    amax = block_max_256(amax, red);
+    const float s = quant_scale(amax, 1e-12f);
+    const float inv = __fdiv_rn(1.f, s);
+    for (int i = threadIdx.x; i < n / 4; i += 256) {
+        float4 v = x4[i];
+        int a = quant_code(v.x, inv) & 255, b = quant_code(v.y, inv) & 255;
+        int c = quant_code(v.z, inv) & 255, d = quant_code(v.w, inv) & 255;
+        const int word = a | (b << 8) | (c << 16) | (d << 24);
+        for (int k = 0; k < K; k++) {
+            const int p = pos_s[k];
+            if (p >= 0) reinterpret_cast<int *>(xg + (size_t)p * n)[i] = word;
+        }
+    }
+    if (threadIdx.x < K && pos_s[threadIdx.x] >= 0) sxg[pos_s[threadIdx.x]] = s;
+}
+
+// n % 4 == 0, x rows 16-byte aligned, K <= 64
+int launch_qrow_i8_scatter(const float *x, const int *pos_of, int S, int K, int8_t *xg, float *sxg, int n, cudaStream_t st) {
+    if (S <= 0) return 0;
+    qrow_i8_scatter_kernel<<<S, 256, 0, st>>>(x, pos_of, K, xg, sxg, n);
+    CK(cudaGetLastError());
+    return 0;
+}
+
+// qrow_i8 over the first *nrows_dev rows only (a count the routing plan left on the device)
+__global__ void __launch_bounds__(256) qrow_i8_counted_kernel(const float *__restrict__ x, int8_t *__restrict__ q,
+                                                              float *__restrict__ scale, int n, const int *__restrict__ nrows_dev) {
+    __shared__ float red[8];
+    const size_t row = blockIdx.x;
+    if ((int)row >= *nrows_dev) return;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x + row * n);
+    float amax = 0.f;
+    for (int i = threadIdx.x; i < n / 4; i += 256) {
+        float4 v = x4[i];
+        amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    }
+    amax = block_max_256(amax, red);
+    const float s = quant_scale(amax, 1e-12f);
+    const float inv = __fdiv_rn(1.f, s);
+    int *q4 = reinterpret_cast<int *>(q + row * n);
+    for (int i = threadIdx.x; i < n / 4; i += 256) {
+        float4 v = x4[i];
+        int a = quant_code(v.x, inv) & 255, b = quant_code(v.y, inv) & 255;
+        int c = quant_code(v.z, inv) & 255, d = quant_code(v.w, inv) & 255;
+        q4[i] = a | (b << 8) | (c << 16) | (d << 24);
+    }
+    if (threadIdx.x == 0) scale[row] = s;
+}
+
+int launch_qrow_i8_counted(const float *x, int8_t *q, float *scale, int rows_max, int n, const int *nrows_dev, cudaStream_t st) {
+    if (rows_max <= 0) return 0;
+    qrow_i8_counted_kernel<<<rows_max, 256, 0, st>>>(x, q, scale, n, nrows_dev);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cudaStream_t st) {
     if (rows <= 0 || n <= 0) return 0;
     qrow_i8_kernel<<<rows, 256, 0, st>>>(x, q, scale, n);

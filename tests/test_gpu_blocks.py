@@ -305,3 +305,34 @@ def test_moe_q4r4_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, 
         cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
         ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
         assert same_bits(fast, oracle.moe_q4r4(ex, x, logits)[0])
+
+
+@pytest.mark.parametrize("E,K,I,D,S,lo,hi", [(8, 2, 256, 256, 300, 0, 8), (64, 8, 1024, 2048, 512, 0, 64), (4, 2, 384, 512, 700, 0, 4),
+                                             (16, 4, 144, 272, 40, 0, 16), (16, 4, 256, 384, 100, 4, 12), (8, 8, 128, 128, 33, 0, 8)])
+def test_moe_q8_batch_on_tensor_cores(gpu, oracle, E, K, I, D, S, lo, hi):
+    """Batches whose experts see 8+ routed rows each run the grouped products on tcgen05 (gate + up + SiLU in one pass,
+    work list from the routing plan).  Same bits as the mma.sync tile path and as the CPU reference: 16- to 128-row
+    tiles, FFN widths and hidden sizes off the 128-row / 128-byte blocks, the OLMoE layer shape at its 512-token
+    prompt, an expert shard (rows of non-resident experts contribute nothing), twice in a row on other inputs."""
+    from oracle import Experts
+    rng = np.random.default_rng(E * 1000 + S + lo)
+    g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
+    d = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
+    gs, us = (rng.uniform(0.001, 0.02, (E, I)).astype(np.float32) for _ in range(2))
+    ds = rng.uniform(0.001, 0.02, (E, D)).astype(np.float32)
+    m = gpu.Moe(E, K, I, D, e_lo=lo, e_hi=hi)
+    for e in range(lo, hi):
+        m.upload_expert(e, g[e], gs[e], u[e], us[e], d[e], ds[e])
+    L = gpu.lib()
+    for trial in range(2):
+        x = rng.standard_normal((S, D)).astype(np.float32)
+        logits = (rng.standard_normal((S, E)) * 0.5).astype(np.float32)
+        prev = L.moty_cuda_set_moe_batch_path(1)
+        tc = m.batch(x, logits); tc_ol = m.olmoe(x, logits, 1)
+        L.moty_cuda_set_moe_batch_path(0)
+        tiles = m.batch(x, logits); tiles_ol = m.olmoe(x, logits, 1)
+        L.moty_cuda_set_moe_batch_path(prev)
+        assert same_bits(tc, tiles) and same_bits(tc_ol, tiles_ol)
+        assert L.moty_cuda_kernel_status(0, None) == 0
+    if (lo, hi) == (0, E):
+        assert same_bits(tc, oracle.moe_batch(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0])
