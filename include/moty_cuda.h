@@ -216,6 +216,13 @@ int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *g, const vo
 /* optional router matrix [E][D]; without one the block entries need `logits` */
 int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router);
 
+/* LFM2's gate instead of the softmax one: route_sigmoid (nn/moe.c:10-25) -- probs = 1 / (1 + expf(-logit)), the K
+ * largest probs + expert_bias (strict >, ties to the lowest index), weights = the unbiased probabilities of the picks
+ * over their sum.  With on != 0 the block entries below compute moty_nn_moe_sigmoid_d1 / _batch (nn/moe.c:154,207)
+ * instead of the _topk_ ones; expert_bias [E] (host) may be NULL (MotyMoeView.expert_bias, nn/moe.h:22).  int8
+ * experts (ebits = 8); the reference's int4-packed expert rows (ebits <= 4, nn/moe.c:99-103) are not carried. */
+int moty_cuda_moe_set_sigmoid_gate(MotyCudaMoe *m, int on, const float *expert_bias);
+
 /* moty_nn_moe_topk_d1 (nn/moe.c:33-153): one token.  logits (optional, [E]) are
  * the router outputs; NULL = compute them with the router set above.  The K
  * weighted expert outputs are summed in selection order k = 0..K-1. */

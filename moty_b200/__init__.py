@@ -406,6 +406,11 @@ class Moe:
         arrs = [np.ascontiguousarray(a) for a in (g, gs, u, us, d, ds)]
         _ck(lib().moty_cuda_moe_upload_expert(self.h, eid, *(_p(a) for a in arrs)))
 
+    def set_sigmoid_gate(self, on: bool = True, expert_bias=None):
+        """LFM2's gate (sigmoid + expert bias, nn/moe.c:10-25) instead of softmax + top-K."""
+        b = None if expert_bias is None else np.ascontiguousarray(expert_bias, np.float32)
+        _ck(lib().moty_cuda_moe_set_sigmoid_gate(self.h, int(bool(on)), _p(b)))
+
     def set_router(self, router: Mat | None):
         self.router = router
         _ck(lib().moty_cuda_moe_set_router(self.h, router.h if router else None))

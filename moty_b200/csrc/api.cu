@@ -1014,6 +1014,8 @@ struct MotyCudaMoe {
     void *gs, *us, *ds;          // scale slabs
     size_t gcb, gsb, dcb, dsb;   // bytes per expert: gate/up codes, gate/up scales, down codes, down scales
     MotyCudaMat *router;
+    int sigmoid;                 // 1: LFM2's gate (sigmoid + expert bias) instead of softmax
+    float *bias;                 // [E] on the device, or null
     // plan buffers (device), sized for capS tokens
     int capS;
     int *idx, *pair_tok, *pos_of, *ord, *counters;
@@ -1064,7 +1066,7 @@ extern "C" int moty_cuda_moe_free(MotyCudaMoe *m) {
     if (!m) return 0;
     DevCtx *c = moty_ctx(m->device);
     if (c) { cudaSetDevice(m->device); cudaStreamSynchronize(c->stream); }
-    void *ps[] = {m->g, m->u, m->d, m->gs, m->us, m->ds};
+    void *ps[] = {m->g, m->u, m->d, m->gs, m->us, m->ds, m->bias};
     for (void *p : ps) if (p) cudaFree(p);
     moe_free_plan(m);
     delete m;
@@ -1094,6 +1096,21 @@ extern "C" int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router) {
     if (router && (router->O != m->E || router->I != m->D || router->device != m->device))
         return moty_set_error(MOTY_CUDA_EARG, "moe_set_router: router %dx%d on device %d", router->O, router->I, router->device);
     m->router = router;
+    return 0;
+}
+
+extern "C" int moty_cuda_moe_set_sigmoid_gate(MotyCudaMoe *m, int on, const float *expert_bias) {
+    if (!m) return moty_set_error(MOTY_CUDA_EARG, "moe_set_sigmoid_gate: null");
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    MOTY_USE_DEVICE(m->device);
+    CK(cudaStreamSynchronize(c->stream));
+    if (m->bias) { CK(cudaFree(m->bias)); m->bias = nullptr; }
+    m->sigmoid = on != 0;
+    if (on && expert_bias) {
+        CK(cudaMalloc(&m->bias, (size_t)m->E * 4));
+        CK(cudaMemcpy(m->bias, expert_bias, (size_t)m->E * 4, cudaMemcpyHostToDevice));
+    }
     return 0;
 }
 
@@ -1167,7 +1184,8 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             logits = m->logits;
         }
         // decode, int8 experts: router + gate/up + down in one cooperative launch
-        if (S == 1 && q8 && order == 0 && g_moe_fast == 1 && moe_decode_fused_q8_supported(E, K, I, D) &&
+        // (the one-launch kernels carry the softmax gate; the sigmoid gate takes the router launch + the two streaming launches)
+        if (S == 1 && q8 && order == 0 && g_moe_fast == 1 && !m->sigmoid && moe_decode_fused_q8_supported(E, K, I, D) &&
             (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
             CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
             CKR(launch_moe_decode_fused_q8(logits, E, norm_topk, m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u,
@@ -1179,7 +1197,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
         }
-        if (S == 1 && !q8 && order == 0 && g_moe_fast == 1 && moe_decode_fused_q4_supported(E, K, I, D) &&
+        if (S == 1 && !q8 && order == 0 && g_moe_fast == 1 && !m->sigmoid && moe_decode_fused_q4_supported(E, K, I, D) &&
             (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
             CKR(moty_grow(c, &c->hq, (size_t)K * I + 16));
             CKR(moty_grow(c, &c->hxs, (size_t)K * (I / 32) * 4));
@@ -1194,8 +1212,8 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
         }
-        if (rows) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_d1_rows: this layer shape (E=%d K=%d I=%d D=%d) has no one-launch decode kernel", E, K, I, D);
-        CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, 1, norm_topk, st));
+        if (rows) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_d1_rows: this layer (sigmoid gate, or shape E=%d K=%d I=%d D=%d) has no one-launch decode kernel", E, K, I, D);
+        CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, m->sigmoid ? 2 : 1, norm_topk, st, m->bias));
     }
     // decode fast path: one token, int8 experts, selection-order combine -> two streaming kernels
     if (S == 1 && q8 && !eid_given && order == 0 && g_moe_fast && moe_decode_q8_supported(K, I, D) &&

@@ -131,7 +131,7 @@ int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntil
 
 // ---- router.cu ----------------------------------------------------------------------
 int launch_route(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs,
-                 int do_softmax, int norm_topk, cudaStream_t st);
+                 int do_softmax, int norm_topk, cudaStream_t st, const float *bias = nullptr);
 int launch_argmax_scratch(const float *v, int n, int *out, float *pv, int *pi, cudaStream_t st);
 
 // ---- moe.cu / ffn -------------------------------------------------------------------

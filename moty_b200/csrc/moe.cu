@@ -118,18 +118,24 @@ __global__ void __launch_bounds__(1024) moe_plan_kernel(MoePlanArgs a) {
         if (hit && (m & ((1u << lane) - 1u)) == 0) wcnt[warp * E + e] += __popc(m);
         __syncwarp();
     }
-    // combine order per token
+    // combine order per token: the token's K expert ids are read once into local arrays and sorted there (the
+    // insertion sort's dependent reads would otherwise each be a round trip to global memory)
     for (int s = tid; s < a.S; s += 1024) {
         int *o = a.ord + (size_t)s * a.K;
-        for (int k = 0; k < a.K; k++) o[k] = k;
-        if (a.order == 1) {                              // ascending expert id: insertion sort of <= 64 entries
-            const int *ix = a.idx + (size_t)s * a.K;
-            for (int k = 1; k < a.K; k++) {
-                int v = o[k], j = k - 1;
-                while (j >= 0 && ix[o[j]] > ix[v]) { o[j + 1] = o[j]; j--; }
-                o[j + 1] = v;
-            }
+        if (a.order != 1) {
+            for (int k = 0; k < a.K; k++) o[k] = k;
+            continue;
         }
+        int ix[64], ok[64];                              // K <= 64; ascending expert id, stable
+        const int *src = a.idx + (size_t)s * a.K;
+        for (int k = 0; k < a.K; k++) { ix[k] = src[k]; ok[k] = k; }
+        for (int k = 1; k < a.K; k++) {
+            const int v = ok[k], ve = ix[k];
+            int j = k - 1;
+            while (j >= 0 && ix[j] > ve) { ix[j + 1] = ix[j]; ok[j + 1] = ok[j]; j--; }
+            ix[j + 1] = ve; ok[j + 1] = v;
+        }
+        for (int k = 0; k < a.K; k++) o[k] = ok[k];
     }
 }
 
@@ -149,23 +155,38 @@ int launch_moe_plan(const MoePlanArgs &a, cudaStream_t st) {
 __global__ void __launch_bounds__(256) moe_combine_kernel(float *__restrict__ out, const float *__restrict__ h,
                                                           const float *__restrict__ w, const int *__restrict__ pos_of,
                                                           const int *__restrict__ ord, int S, int K, int D) {
-    int s = blockIdx.y;
-    int d = blockIdx.x * 256 + threadIdx.x;
-    if (d >= D) return;
-    float acc = 0.f;
-    for (int j = 0; j < K; j++) {
-        int k = ord[(size_t)s * K + j];
-        int p = pos_of[(size_t)s * K + k];
-        if (p >= 0) acc = fmaf(w[(size_t)s * K + k], h[(size_t)p * D + d], acc);
+    // one CTA per token: the K (position, weight) pairs in combine order go to shared memory once, then every thread
+    // requests the K rows' values of its columns together (up to 8 loads in flight) before the ordered chain
+    __shared__ int p_s[64];
+    __shared__ float w_s[64];
+    const int s = blockIdx.x;
+    if (threadIdx.x < K) {
+        const int k = ord[(size_t)s * K + threadIdx.x];
+        p_s[threadIdx.x] = pos_of[(size_t)s * K + k];
+        w_s[threadIdx.x] = w[(size_t)s * K + k];
     }
-    out[(size_t)s * D + d] = acc;
+    __syncthreads();
+    for (int d = threadIdx.x; d < D; d += 256) {
+        float acc = 0.f;
+        for (int j0 = 0; j0 < K; j0 += 8) {
+            float v[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int p = j0 + j < K ? p_s[j0 + j] : -1;
+                v[j] = p >= 0 ? __ldcs(h + (size_t)p * D + d) : 0.f;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (j0 + j < K && p_s[j0 + j] >= 0) acc = fmaf(w_s[j0 + j], v[j], acc);
+        }
+        out[(size_t)s * D + d] = acc;
+    }
 }
 
 int launch_moe_combine(float *out, const float *h, const float *w, const int *pos_of, const int *ord,
                        int S, int K, int D, cudaStream_t st) {
     if (S <= 0) return 0;
-    dim3 grid((D + 255) / 256, S);
-    moe_combine_kernel<<<grid, 256, 0, st>>>(out, h, w, pos_of, ord, S, K, D);
+    moe_combine_kernel<<<S, 256, 0, st>>>(out, h, w, pos_of, ord, S, K, D);
     CK(cudaGetLastError());
     return 0;
 }

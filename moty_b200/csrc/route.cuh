@@ -149,6 +149,41 @@ __device__ __forceinline__ void route_row_warp_mem(const float *__restrict__ lg,
     if (lane + 32 < K) w_out[lane + 32] = mine2;
 }
 
+// LFM2's gate (route_sigmoid, nn/moe.c:10-25): probs = 1 / (1 + expf(-logit)); K rounds of "largest probs + bias not
+// yet taken" (strict >, ties to the lowest index); the weights are the UNBIASED probabilities of the picks divided by
+// their sequential sum when that is positive.  p: 2 E floats of scratch (selection values, then probabilities).
+__device__ __forceinline__ void route_row_warp_sigmoid(const float *__restrict__ lg, const float *__restrict__ bias, int E, int K,
+                                                       float *p, int lane, int *idx_out, float *w_out) {
+    float *pr = p + ((E + 3) & ~3);
+    for (int e = lane; e < E; e += 32) {
+        const float q = __fdiv_rn(1.f, __fadd_rn(1.f, moty_expf(-lg[e])));
+        pr[e] = q;
+        p[e] = bias ? __fadd_rn(q, bias[e]) : q;
+    }
+    __syncwarp();
+    float wsum = 0.f, mine = 0.f, mine2 = 0.f;
+    for (int k = 0; k < K; k++) {
+        float bv = -1e30f; int bi = -1;
+        for (int e = lane; e < E; e += 32) {
+            const float v = p[e];
+            if (v > bv) { bv = v; bi = e; }
+        }
+        float gv;
+        const int gi = route_pick(bv, bi, gv);
+        if (gi >= 0 && (gi & 31) == lane) p[gi] = __int_as_float(0xff800000);
+        const float q = gi >= 0 ? pr[gi] : 0.f;
+        if (lane == 0) idx_out[k] = gi;
+        if ((k & 31) == lane) { if (k < 32) mine = q; else mine2 = q; }
+        wsum = __fadd_rn(wsum, q);
+    }
+    if (wsum > 0.f) {
+        mine = __fdiv_rn(mine, wsum);
+        if (K > 32) mine2 = __fdiv_rn(mine2, wsum);
+    }
+    if (lane < K) w_out[lane] = mine;
+    if (lane + 32 < K) w_out[lane + 32] = mine2;
+}
+
 __device__ __forceinline__ void route_row_warp(const float *__restrict__ lg, int E, int K, float *p, int do_softmax,
                                                int norm_topk, int lane, int *idx_out, float *w_out, float *probs_out) {
     if (E <= 64) route_row_warp_reg<2>(lg, E, K, p, do_softmax, norm_topk, lane, idx_out, w_out, probs_out);

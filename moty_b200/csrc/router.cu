@@ -5,26 +5,33 @@
 // One warp per token row; the arithmetic is route_row_warp (route.cuh).
 __global__ void __launch_bounds__(128) route_kernel(const float *__restrict__ logits, int rows, int E, int K,
                                                     int *__restrict__ idx, float *__restrict__ w,
-                                                    float *__restrict__ probs, int do_softmax, int norm_topk) {
-    extern __shared__ __align__(16) float sm[];            // four scratch rows of E floats, each 16-byte aligned
+                                                    float *__restrict__ probs, int do_softmax, int norm_topk,
+                                                    const float *__restrict__ bias) {
+    extern __shared__ __align__(16) float sm[];            // four scratch rows of E floats (2 E for the sigmoid gate), 16-byte aligned
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int row = blockIdx.x * 4 + warp;
     pdl_trigger();
     pdl_wait();                              // the logits come from the kernel before this one
     if (row >= rows) return;
+    if (do_softmax == 2) {                   // sigmoid + expert bias (LFM2)
+        route_row_warp_sigmoid(logits + (size_t)row * E, bias, E, K, sm + (size_t)warp * 2 * ((E + 3) & ~3), lane,
+                               idx + (size_t)row * K, w + (size_t)row * K);
+        return;
+    }
     route_row_warp(logits + (size_t)row * E, E, K, sm + (size_t)warp * ((E + 3) & ~3), do_softmax, norm_topk, lane,
                    idx + (size_t)row * K, w + (size_t)row * K, probs ? probs + (size_t)row * E : nullptr);
 }
 
+// do_softmax: 0 = top-K of given probabilities, 1 = softmax then top-K, 2 = sigmoid + bias gate (bias may be null)
 int launch_route(const float *logits, int rows, int E, int K, int *idx, float *w, float *probs,
-                 int do_softmax, int norm_topk, cudaStream_t st) {
+                 int do_softmax, int norm_topk, cudaStream_t st, const float *bias) {
     if (rows <= 0) return 0;
     if (E <= 0 || E > 4096 || K <= 0 || K > 64 || K > E)
         return moty_set_error(MOTY_CUDA_EARG, "route: E=%d K=%d (E <= 4096, K <= 64, K <= E)", E, K);
-    size_t smem = (size_t)4 * ((E + 3) & ~3) * sizeof(float);
+    size_t smem = (size_t)4 * ((E + 3) & ~3) * sizeof(float) * (do_softmax == 2 ? 2 : 1);
     if (smem > 48 * 1024) CK(cudaFuncSetAttribute(route_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     CK(moty_launch_pdl(route_kernel, dim3((rows + 3) / 4), dim3(128), smem, st, logits, rows, E, K, idx, w, probs,
-                       do_softmax, norm_topk));
+                       do_softmax, norm_topk, bias));
     return 0;
 }
 

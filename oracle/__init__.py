@@ -330,6 +330,19 @@ class Oracle:
         self.lib.oracle_moe_batch(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(out), _p(idx), _p(w))
         return out, idx, w
 
+    def moe_sigmoid(self, ex, x, logits, bias=None):
+        """The block behind the sigmoid + expert-bias gate (nn/moe.c:10-25): S = 1 decode order, S > 1 batch order."""
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        lg = _f32(logits).reshape(S, ex.E).copy()
+        b = None if bias is None else _f32(bias)
+        out = np.empty((S, ex.D), np.float32)
+        idx = np.empty((S, ex.K), np.int32); w = np.empty((S, ex.K), np.float32)
+        if S == 1:
+            self.lib.oracle_moe_sigmoid_d1(C.byref(ex.c), _p(x), _p(lg), _p(b), _p(out), _p(idx), _p(w))
+        else:
+            self.lib.oracle_moe_sigmoid_batch(C.byref(ex.c), _p(x), C.c_int(S), _p(lg), _p(b), _p(out), _p(idx), _p(w))
+        return out, idx, w
+
     def olmoe_moe(self, ex, x, logits, norm_topk):
         x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
         lg = _f32(logits).reshape(S, ex.E).copy()
@@ -571,6 +584,14 @@ class Ref:
                                   _p(router_q) if router_q is not None else None,
                                   _p(_f32(router_qs)) if router_qs is not None else None,
                                   _p(x), C.c_int(S), _p(out))
+        return out
+
+    def moe_sigmoid_block(self, ex, x, bias, router_q, router_qs):
+        """nn/moe.c block behind the sigmoid + bias gate, int8 router."""
+        x = _f32(x).reshape(-1, ex.D); S = x.shape[0]
+        out = np.empty((S, ex.D), np.float32)
+        self.lib.refshim_moe_sigmoid(C.byref(ex.c), C.c_int(WF_I8), None, _p(router_q), _p(_f32(router_qs)),
+                                     _p(_f32(bias)) if bias is not None else None, _p(x), C.c_int(S), _p(out))
         return out
 
     def olmoe_moe(self, ex, x, logits, norm_topk):

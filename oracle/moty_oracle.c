@@ -614,6 +614,28 @@ ORACLE_API void oracle_route_topk(float *logits, int E, int K, int *idx, float *
     oracle_moe_topk(logits, E, K, idx, w, 1);
 }
 
+/* nn/moe.c:10-25 -- the LFM2 gate: probs = sigmoid(logit) with the C library's expf; K rounds of "largest
+ * probs + bias not yet taken" (strict > from -1e30: ties to the lowest index); the weights are the
+ * UNBIASED probabilities of the picks, divided by their sequential sum when that is positive. */
+ORACLE_API void oracle_route_sigmoid(const float *lb, const float *bias, int E, int K, int *idx, float *w) {
+    float *probs = (float *)malloc(sizeof(float) * (size_t)E);
+    for (int e = 0; e < E; e++) probs[e] = 1.f / (1.f + oracle_expf(-lb[e]));
+    for (int k = 0; k < K; k++) {
+        int best = -1; float bv = -1e30f;
+        for (int e = 0; e < E; e++) {
+            float v = probs[e] + (bias ? bias[e] : 0.f);
+            int used = 0;
+            for (int j = 0; j < k; j++) if (idx[j] == e) used = 1;
+            if (!used && v > bv) { bv = v; best = e; }
+        }
+        idx[k] = best;
+    }
+    float ws = 0.f;
+    for (int k = 0; k < K; k++) { w[k] = probs[idx[k]]; ws += w[k]; }
+    if (ws > 0) for (int k = 0; k < K; k++) w[k] /= ws;
+    free(probs);
+}
+
 /* nn/sample.c:9-13 -- greedy token: first index of the maximum. */
 ORACLE_API int oracle_argmax(const float *v, int n) {
     int best = 0; float bv = v[0];
@@ -684,11 +706,23 @@ typedef struct {
  * and up rows, SiLU*up then per-expert re-quantization, all down rows, and the
  * weighted sum accumulated in selection order k = 0..K-1 (one fused
  * multiply-add per element).  idx_out/w_out (optional) return the routing. */
+static void moe_d1_impl(const OracleExperts *ex, const float *x, float *logits, float *out,
+                        int *idx_out, float *w_out, int sig, const float *bias);
 ORACLE_API void oracle_moe_d1(const OracleExperts *ex, const float *x, float *logits, float *out,
                               int *idx_out, float *w_out) {
+    moe_d1_impl(ex, x, logits, out, idx_out, w_out, 0, NULL);
+}
+/* moty_nn_moe_sigmoid_d1 (nn/moe.c:154): the same block behind the sigmoid + bias gate */
+ORACLE_API void oracle_moe_sigmoid_d1(const OracleExperts *ex, const float *x, float *logits, const float *bias, float *out,
+                                      int *idx_out, float *w_out) {
+    moe_d1_impl(ex, x, logits, out, idx_out, w_out, 1, bias);
+}
+static void moe_d1_impl(const OracleExperts *ex, const float *x, float *logits, float *out,
+                        int *idx_out, float *w_out, int sig, const float *bias) {
     int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
     int idx[64]; float w[64];
-    oracle_route_topk(logits, E, K, idx, w);
+    if (sig) oracle_route_sigmoid(logits, bias, E, K, idx, w);
+    else oracle_route_topk(logits, E, K, idx, w);
     int8_t *xi = (int8_t *)malloc(D), *hi = (int8_t *)malloc(I);
     float *gb = (float *)malloc((size_t)I * 4), *ub = (float *)malloc((size_t)I * 4), *hb = (float *)malloc((size_t)D * 4);
     float sx = oracle_qrow_i8(x, xi, D);
@@ -722,12 +756,26 @@ ORACLE_API void oracle_moe_d1(const OracleExperts *ex, const float *x, float *lo
  * expert gathers its tokens in ascending token order, runs the three Q8_0
  * matmuls on the gathered rows and scatter-adds weight * h.  A token's output
  * is therefore accumulated in ascending EXPERT order, unlike the S=1 path. */
+static void moe_batch_impl(const OracleExperts *ex, const float *x, int S, float *logits, float *out,
+                           int *idx_out, float *w_out, int sig, const float *bias);
 ORACLE_API void oracle_moe_batch(const OracleExperts *ex, const float *x, int S, float *logits, float *out,
                                  int *idx_out, float *w_out) {
+    moe_batch_impl(ex, x, S, logits, out, idx_out, w_out, 0, NULL);
+}
+/* moty_nn_moe_sigmoid_batch (nn/moe.c:207) */
+ORACLE_API void oracle_moe_sigmoid_batch(const OracleExperts *ex, const float *x, int S, float *logits, const float *bias,
+                                         float *out, int *idx_out, float *w_out) {
+    moe_batch_impl(ex, x, S, logits, out, idx_out, w_out, 1, bias);
+}
+static void moe_batch_impl(const OracleExperts *ex, const float *x, int S, float *logits, float *out,
+                           int *idx_out, float *w_out, int sig, const float *bias) {
     int E = ex->E, K = ex->K, I = ex->I, D = ex->D;
     int *idx = (int *)malloc(sizeof(int) * (size_t)S * K);
     float *rw = (float *)malloc(sizeof(float) * (size_t)S * K);
-    for (int s = 0; s < S; s++) oracle_route_topk(logits + (size_t)s * E, E, K, idx + (size_t)s * K, rw + (size_t)s * K);
+    for (int s = 0; s < S; s++) {
+        if (sig) oracle_route_sigmoid(logits + (size_t)s * E, bias, E, K, idx + (size_t)s * K, rw + (size_t)s * K);
+        else oracle_route_topk(logits + (size_t)s * E, E, K, idx + (size_t)s * K, rw + (size_t)s * K);
+    }
     memset(out, 0, (size_t)S * D * 4);
     int *tl = (int *)malloc(sizeof(int) * (S ? S : 1));
     float *xsub = (float *)malloc((size_t)S * D * 4 + 4), *g = (float *)malloc((size_t)S * I * 4 + 4);

@@ -6,7 +6,7 @@
  * reference function.
  *
  * Reference entry points used (moty source tree, directory c/):
- *   moty_nn_moe_topk_d1 / _batch   nn/moe.c:155-156, 207-208
+ *   moty_nn_moe_topk_d1 / _batch, moty_nn_moe_sigmoid_d1 / _batch   nn/moe.c:154-156, 207-208
  *   moty_expert_cache_init/get     runtime/moecache.c:4-18, 50-89
  *   moty_matmul_q, moty_softmax_row, moty_moe_topk   (OLMoE block, engines/olmoe.c:219-244)
  *   moty_pack_q4r4_block           nn/quant.c:157-179
@@ -42,9 +42,21 @@ static void shim_load_expert(void *ctx, int layer, int eid, ExpertSlot *s, int i
  * (cache capacity = E, so nothing is ever evicted), no shared expert.
  * router_fmt: WF_F32 (router_f = [E][D] floats) or WF_I8 (router_q + router_qs).
  * S == 1 takes the decode path, S > 1 the batch path. */
+static void shim_moe_block(const ShimExperts *ex, int router_fmt, const float *router_f, const int8_t *router_q,
+                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias);
 void refshim_moe_topk(const ShimExperts *ex, int router_fmt, const float *router_f,
                       const int8_t *router_q, const float *router_qs,
                       const float *x, int S, float *out) {
+    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 0, NULL);
+}
+/* the same block behind the sigmoid + expert-bias gate of LFM2 (moty_nn_moe_sigmoid_d1 / _batch, nn/moe.c:154,207) */
+void refshim_moe_sigmoid(const ShimExperts *ex, int router_fmt, const float *router_f,
+                         const int8_t *router_q, const float *router_qs, const float *bias,
+                         const float *x, int S, float *out) {
+    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 1, bias);
+}
+static void shim_moe_block(const ShimExperts *ex, int router_fmt, const float *router_f, const int8_t *router_q,
+                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias) {
     Mat router; mat_reset_storage(&router);
     router.fmt = router_fmt; router.O = ex->E; router.I = ex->D;
     router.f = (float *)router_f; router.q = (int8_t *)router_q; router.qs = (float *)router_qs;
@@ -53,7 +65,9 @@ void refshim_moe_topk(const ShimExperts *ex, int router_fmt, const float *router
     MotyMoeView v; memset(&v, 0, sizeof v);
     v.router = &router; v.ec = &ec; v.load_expert = shim_load_expert; v.ectx = (void *)ex;
     v.E = ex->E; v.K = ex->K; v.I = ex->I; v.D = ex->D; v.li = 0; v.ebits = 8; v.scr = &scr;
-    if (S == 1) moty_nn_moe_topk_d1(&v, x, out);
+    v.expert_bias = bias;
+    if (sig) { if (S == 1) moty_nn_moe_sigmoid_d1(&v, x, out); else moty_nn_moe_sigmoid_batch(&v, x, S, out); }
+    else if (S == 1) moty_nn_moe_topk_d1(&v, x, out);
     else moty_nn_moe_topk_batch(&v, x, S, out);
     moty_expert_cache_free(&ec);
     moty_scr_free(&scr);

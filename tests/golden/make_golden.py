@@ -187,8 +187,35 @@ def main():
             d[f"ctx_{tag}_{step}"] = r.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
             pos += S
     save("attn", **d)
+    sigmoid_blocks(r, save)
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 
+def sigmoid_blocks(r, save):
+    """The MoE block behind LFM2's sigmoid + expert-bias gate (moty_nn_moe_sigmoid_d1 / _batch, nn/moe.c:10-25,154,207),
+    int8 experts and an int8 router; its own random stream (added after the files above were fixed).  `only` lets this
+    one file be written without touching the others:  python tests/golden/make_golden.py sigmoid"""
+    rs_ = np.random.default_rng(20261125)
+    E, K, I2, D2 = 16, 4, 64, 128
+    g = rs_.integers(-127, 128, (E, I2, D2), dtype=np.int8); u = rs_.integers(-127, 128, (E, I2, D2), dtype=np.int8)
+    d = rs_.integers(-127, 128, (E, D2, I2), dtype=np.int8)
+    gs = rs_.uniform(0.001, 0.02, (E, I2)).astype(np.float32); us = rs_.uniform(0.001, 0.02, (E, I2)).astype(np.float32)
+    ds = rs_.uniform(0.001, 0.02, (E, D2)).astype(np.float32)
+    ex = Experts(E, K, I2, D2, g, u, d, gs, us, ds)
+    rq, rsc = r.quantize_rows((rs_.standard_normal((E, D2)) * 0.1).astype(np.float32))
+    bias = (rs_.standard_normal(E) * 0.3).astype(np.float32)
+    blk = dict(g=g, u=u, d=d, gs=gs, us=us, ds=ds, rq=rq, rs=rsc, bias=bias, dims=np.array([E, K, I2, D2], np.int32))
+    for S in (1, 9):
+        x = rs_.standard_normal((S, D2)).astype(np.float32)
+        blk[f"x{S}"] = x; blk[f"logits{S}"] = r.matmul_q_s(x, rq, rsc)
+        blk[f"out_bias{S}"] = r.moe_sigmoid_block(ex, x, bias, rq, rsc)
+        blk[f"out_nobias{S}"] = r.moe_sigmoid_block(ex, x, None, rq, rsc)
+    save("blocks_sigmoid", **blk)
+
+
 if __name__ == "__main__":
-    main()
+    if sys.argv[1:] == ["sigmoid"]:
+        build()
+        sigmoid_blocks(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
+    else:
+        main()

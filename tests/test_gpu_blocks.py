@@ -336,3 +336,41 @@ def test_moe_q8_batch_on_tensor_cores(gpu, oracle, E, K, I, D, S, lo, hi):
         assert L.moty_cuda_kernel_status(0, None) == 0
     if (lo, hi) == (0, E):
         assert same_bits(tc, oracle.moe_batch(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0])
+
+
+def test_moe_sigmoid_gate_golden_and_oracle(gpu, oracle):
+    """LFM2's gate (sigmoid + expert bias, nn/moe.c:10-25) around int8 experts: vectors from the compiled reference's
+    moty_nn_moe_sigmoid_d1 / _batch bit for bit (router on the GPU as an int8 matrix, and with logits handed in), then
+    random layers against the oracle on every batch path (decode, mma.sync tiles, tensor cores)."""
+    from oracle import Experts
+    g = golden("blocks_sigmoid")
+    E, K, I, D = (int(v) for v in g["dims"])
+    m = gpu.Moe(E, K, I, D)
+    for e in range(E):
+        m.upload_expert(e, g["g"][e], g["gs"][e], g["u"][e], g["us"][e], g["d"][e], g["ds"][e])
+    for bias, tag in ((g["bias"], "bias"), (None, "nobias")):
+        m.set_sigmoid_gate(True, bias)
+        m.set_router(None)
+        assert same_bits(m.d1(g["x1"], g["logits1"]), g[f"out_{tag}1"])
+        assert same_bits(m.batch(g["x9"], g["logits9"]), g[f"out_{tag}9"])
+        m.set_router(gpu.Mat.i8(g["rq"], g["rs"]))
+        assert same_bits(m.d1(g["x1"]), g[f"out_{tag}1"]) and same_bits(m.batch(g["x9"]), g[f"out_{tag}9"])
+    m.set_sigmoid_gate(False)                                   # back to softmax: another result
+    m.set_router(None)
+    assert not same_bits(m.d1(g["x1"], g["logits1"]), g["out_bias1"])
+    rng = np.random.default_rng(77)
+    E, K, I, D = 32, 4, 256, 512                                # the LFM2-8B-A1B gate: 32 experts, top-4
+    gq = rng.integers(-127, 128, (E, I, D), dtype=np.int8); uq = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
+    dq = rng.integers(-127, 128, (E, D, I), dtype=np.int8)
+    gs, us = (rng.uniform(0.001, 0.02, (E, I)).astype(np.float32) for _ in range(2))
+    ds = rng.uniform(0.001, 0.02, (E, D)).astype(np.float32)
+    ex = Experts(E, K, I, D, gq, uq, dq, gs, us, ds)
+    m = gpu.Moe(E, K, I, D)
+    for e in range(E):
+        m.upload_expert(e, gq[e], gs[e], uq[e], us[e], dq[e], ds[e])
+    bias = (rng.standard_normal(E) * 0.2).astype(np.float32)
+    m.set_sigmoid_gate(True, bias)
+    for S in (1, 7, 200):                                       # decode, mma.sync tiles, tensor cores (25 rows per expert)
+        x = rng.standard_normal((S, D)).astype(np.float32); lg = rng.standard_normal((S, E)).astype(np.float32)
+        got = m.d1(x, lg) if S == 1 else m.batch(x, lg)
+        assert same_bits(got, oracle.moe_sigmoid(ex, x, lg, bias)[0]), S

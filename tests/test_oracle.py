@@ -205,3 +205,20 @@ def test_expf_table_is_two_to_the_i_over_32(oracle):
         d = float(mpmath.power(2, mpmath.mpf(i) / 32))
         bits = int(np.float64(d).view(np.uint64)) - (i << 47)
         assert int(oracle.lib.oracle_exp2_tab_entry(i)) == bits
+
+
+def test_sigmoid_gate_block_golden(oracle):
+    """LFM2's gate (sigmoid + expert bias, nn/moe.c:10-25) around the int8 expert block: the restatement against
+    vectors from moty_nn_moe_sigmoid_d1 / _batch of the compiled reference, with and without a bias."""
+    from oracle import Experts
+    g = golden("blocks_sigmoid")
+    E, K, I, D = (int(v) for v in g["dims"])
+    ex = Experts(E, K, I, D, g["g"], g["u"], g["d"], g["gs"], g["us"], g["ds"])
+    for S in (1, 9):
+        assert same_bits(oracle.matmul_q_s(g[f"x{S}"], g["rq"], g["rs"]), g[f"logits{S}"])
+        assert same_bits(oracle.moe_sigmoid(ex, g[f"x{S}"], g[f"logits{S}"], g["bias"])[0], g[f"out_bias{S}"])
+        assert same_bits(oracle.moe_sigmoid(ex, g[f"x{S}"], g[f"logits{S}"], None)[0], g[f"out_nobias{S}"])
+    # the bias moves the selection but not the weights' source: a large bias on one expert forces it in
+    b = np.zeros(E, np.float32); b[5] = 10
+    _, idx, w = oracle.moe_sigmoid(ex, g["x1"], g["logits1"], b)
+    assert idx[0, 0] == 5 and abs(float(w.sum()) - 1) < 1e-6
