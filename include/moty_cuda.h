@@ -126,6 +126,13 @@ int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *dev
  * integer paths (NN_QROW_MAX, nn/nn_matmul.h:35); larger I is MOTY_CUDA_ELIMIT. */
 int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
+/* n (1..8) independent one-row products in ONE launch: y_dev[m] = mat_apply(w[m], x_dev[m], S = 1) for MOTY_WF_I8
+ * matrices on one GPU with I % 16 == 0 and I <= 4096 (x_dev[m] 16-byte aligned; the pointers may repeat: the q, k, v
+ * projections of a layer share their row).  Small matrices cost a launch each otherwise (1-3 MB: 0.2-0.5 us of HBM
+ * time behind 4-5 us of fixed cost); here all rows of all matrices are dealt to one persistent grid.  Same bits as n
+ * calls of mat_apply_dev.  w, y_dev, x_dev are HOST arrays of n pointers.  No reference counterpart (the reference
+ * calls moty_mat_apply once per matrix, nn/mat.c:70). */
+int moty_cuda_mat_apply_multi_dev(int n, MotyCudaMat *const *w, float *const *y_dev, const float *const *x_dev, void *stream);
 /* same, also returning the int32 accumulators [S][O] of the Q8_0 path (the
  * values moty_hw_dot_i8i8 returns, hw/hw_scalar.h:8-12) for exact checks */
 int moty_cuda_mat_apply_acc(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S);
@@ -274,6 +281,17 @@ int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_
  * this GPU's partial sum.  Needs a layer shape the one-launch decode kernels take (MOTY_CUDA_ELIMIT otherwise). */
 int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float *out_dev, const float *x_dev,
                               const float *logits_dev, int norm_topk, int *idx_dev, float *w_dev, void *stream);
+/* The same expert-parallel decode with the exchange done by the library's own kernels over peer memory (NVLink)
+ * instead of a collective: tables[r] / flags[r] (host arrays of `world` DEVICE pointers, r = rank) are every rank's
+ * row tables (2 * K * D floats each: two tables used alternately) and flag words (`world` u32 each, zero before the
+ * first call) in memory that every GPU of the group can address (peer access or symmetric memory).  The decode
+ * kernel stores the rows of this GPU's experts straight into all ranks' tables; a second launch signals each peer
+ * (fence + one release store into the peer's word for this rank), waits -- BOUNDED, about a second; on expiry the
+ * error word is set, nothing is written and moty_cuda_kernel_status reports it -- until all ranks' rows of step
+ * `epoch` have arrived, and adds the K rows in selection order: the one-GPU bits.  epoch: 1, 2, 3, ... the same on
+ * every rank, one per call.  1 <= world <= 8; one rank per GPU (ranks that wait for each other must never share one). */
+int moty_cuda_moe_d1_peer_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, const float *logits_dev, int norm_topk,
+                              void *const *tables, void *const *flags, int world, int rank, unsigned epoch, void *stream);
 /* moe_combine_dev: out[s] = sum over the token's K selections of w[s][k] * h[s*K+k],
  * one fused multiply-add per step from 0, in selection order (order 0,
  * nn/moe.c:146-149) or ascending expert id (order 1, nn/moe.c:200-202). */

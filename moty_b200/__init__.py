@@ -200,6 +200,13 @@ def mat_apply_dev(w: Mat, y_ptr: int, x_ptr: int, S: int, stream: int = 0) -> No
     _ck(lib().moty_cuda_mat_apply_dev(w.h, C.c_void_p(y_ptr), C.c_void_p(x_ptr), S, C.c_void_p(stream)))
 
 
+def mat_apply_multi_dev(ws, y_ptrs, x_ptrs, stream: int = 0) -> None:
+    """Up to eight independent one-row Q8_0 products in one launch (device pointers)."""
+    n = len(ws)
+    _ck(lib().moty_cuda_mat_apply_multi_dev(n, (C.c_void_p * n)(*[w.h.value for w in ws]),
+                                            (C.c_void_p * n)(*y_ptrs), (C.c_void_p * n)(*x_ptrs), C.c_void_p(stream)))
+
+
 def matmul_q_s(x, q, scale):
     """moty_matmul_q_s (nn/matmul.c:51-66) with host weights."""
     x = _f32(x); q = np.ascontiguousarray(q, np.int8); scale = _f32(scale)

@@ -439,6 +439,21 @@ extern "C" int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float
 
 // One decode row through a MOTY_WF_I8 matrix with the residual add and the RMS norm before it in the same launch:
 // y = W * q(rmsnorm(x + t) * g), xout = x + t.  Same bits as add_rmsnorm_dev followed by mat_apply_dev.
+extern "C" int moty_cuda_mat_apply_multi_dev(int n, MotyCudaMat *const *w, float *const *y_dev, const float *const *x_dev, void *stream) {
+    if (n < 1 || n > 8 || !w || !y_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: n=%d (1..8) or null argument", n);
+    const int8_t *codes[8]; const float *scales[8]; int O[8], I[8];
+    for (int m = 0; m < n; m++) {
+        if (!w[m] || !y_dev[m] || !x_dev[m]) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: null argument for matrix %d", m);
+        if (w[m]->fmt != MOTY_WF_I8 || w[m]->device != w[0]->device || !q8_multi_supported(w[m]->I))
+            return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: matrix %d must be MOTY_WF_I8 on the same GPU with I %% 16 == 0, I <= 4096", m);
+        codes[m] = (const int8_t *)w[m]->codes; scales[m] = (const float *)w[m]->scales; O[m] = w[m]->O; I[m] = w[m]->I;
+    }
+    DevCtx *c = moty_ctx(w[0]->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w[0]->device);
+    MOTY_USE_DEVICE(w[0]->device);
+    return launch_q8_multi(n, codes, scales, x_dev, y_dev, O, I, c->sms, pick_stream(c, stream));
+}
+
 extern "C" int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w) {
     return w && w->fmt == MOTY_WF_I8 && w->I % 16 == 0 && w->I <= 4096;
 }
@@ -575,12 +590,13 @@ static int ctx_of(const void *dev_ptr, DevCtx **c) {
     }
     *c = moty_ctx(at.device);
     if (!*c) return moty_set_error(MOTY_CUDA_EINIT, "device %d (owner of the pointer) not initialised", at.device);
-    MOTY_USE_DEVICE(at.device);
     return 0;
 }
+// the context of the GPU that owns dev_ptr, and that GPU current until the end of the caller's scope
+#define MOTY_CTX_OF(dev_ptr, c) DevCtx *c; CKR(ctx_of(dev_ptr, &c)); MOTY_USE_DEVICE(c->dev)
 
 extern "C" int moty_cuda_qrow_i8_dev(const float *x_dev, int8_t *q_dev, float *scale_dev, int rows, int n, void *stream) {
-    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    MOTY_CTX_OF(x_dev, c);
     return launch_qrow_i8(x_dev, q_dev, scale_dev, rows, n, pick_stream(c, stream));
 }
 
@@ -601,7 +617,7 @@ extern "C" int moty_cuda_qrow_i8(const float *x, int8_t *q, float *scale, int ro
 
 extern "C" int moty_cuda_quant_g32_dev(const float *x_dev, int rows, int I, int8_t *xq_dev, float *xs_dev,
                                        int32_t *xsum_dev, void *stream) {
-    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    MOTY_CTX_OF(x_dev, c);
     if (I % 32) return moty_set_error(MOTY_CUDA_EARG, "quant_g32: I=%d", I);
     return launch_quant_g32(x_dev, rows, I, xq_dev, xs_dev, xsum_dev, pick_stream(c, stream));
 }
@@ -679,7 +695,7 @@ extern "C" int moty_cuda_route_topk(const float *logits, int rows, int E, int K,
 
 extern "C" int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E, int K, int *idx_dev, float *w_dev,
                                         float *probs_dev, int norm_topk, void *stream) {
-    DevCtx *c; CKR(ctx_of(logits_dev, &c));
+    MOTY_CTX_OF(logits_dev, c);
     return launch_route(logits_dev, rows, E, K, idx_dev, w_dev, probs_dev, 1, norm_topk, pick_stream(c, stream));
 }
 
@@ -687,7 +703,7 @@ extern "C" int moty_cuda_route_topk_dev(const float *logits_dev, int rows, int E
 // greedy token
 // ---------------------------------------------------------------------------
 extern "C" int moty_cuda_argmax_dev(const float *v_dev, int n, int *out_dev, void *stream) {
-    DevCtx *c; CKR(ctx_of(v_dev, &c));
+    MOTY_CTX_OF(v_dev, c);
     CKR(moty_grow(c, &c->daux, 4096));
     return launch_argmax_scratch(v_dev, n, out_dev, (float *)c->daux.p, (int *)((char *)c->daux.p + 1024),
                                  pick_stream(c, stream));
@@ -752,20 +768,20 @@ extern "C" int moty_cuda_head_argmax(MotyCudaMat *head, const float *x, int S, i
 // ---------------------------------------------------------------------------
 extern "C" int moty_cuda_rmsnorm_dev(float *out_dev, const float *x_dev, const float *w_dev, int S, int D, float eps, void *stream) {
     if (!out_dev || !x_dev || !w_dev) return moty_set_error(MOTY_CUDA_EARG, "rmsnorm_dev: null argument");
-    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    MOTY_CTX_OF(x_dev, c);
     return launch_rmsnorm_rows(out_dev, x_dev, w_dev, S, D, eps, pick_stream(c, stream));
 }
 
 extern "C" int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *stream) {
     if (!y_dev || !x_dev) return moty_set_error(MOTY_CUDA_EARG, "add_dev: null argument");
-    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    MOTY_CTX_OF(x_dev, c);
     return launch_add(y_dev, x_dev, n, pick_stream(c, stream));
 }
 
 extern "C" int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
                                          float eps, void *stream) {
     if (!x_dev || !t_dev || !out_dev || !w_dev) return moty_set_error(MOTY_CUDA_EARG, "add_rmsnorm_dev: null argument");
-    DevCtx *c; CKR(ctx_of(x_dev, &c));
+    MOTY_CTX_OF(x_dev, c);
     return launch_add_rmsnorm_rows(x_dev, t_dev, out_dev, w_dev, S, D, eps, pick_stream(c, stream));
 }
 
@@ -1162,7 +1178,7 @@ extern "C" int moty_cuda_set_moe_fast_path(int on) {
 // expert is not resident on this GPU.
 static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, int S, const float *logits,
                         int order, int norm_topk, int *idx_out, float *w_out, const int *eid_given, cudaStream_t st,
-                        float *rows = nullptr) {
+                        float *rows = nullptr, float *const *rows_peer = nullptr, int npeer = 0) {
     const int E = m->E, K = eid_given ? 1 : m->K, I = m->I, D = m->D;
     const bool q8 = m->efmt == MOTY_WF_I8;
     // rows per tile of the grouped products: 8 for the int8 tile kernel; 8, 16 or 32 for the Q4R4 MMA kernel
@@ -1192,7 +1208,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
                                            (const int8_t *)m->d, (const float *)m->gs, (const float *)m->us,
                                            (const float *)m->ds, m->gcb, m->gsb / 4, m->dcb, m->dsb / 4, x,
                                            (float *)c->g.p, out, rows, K, I, D, m->e_lo, m->e_hi,
-                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st));
+                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st, rows_peer, npeer));
             if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
@@ -1207,12 +1223,12 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
                                            (const uint16_t *)m->ds, m->gcb, m->gsb / 2, m->dcb, m->dsb / 2, x,
                                            (int8_t *)c->hq.p, (float *)c->hxs.p, (int *)c->hxsum.p, out, rows, K, I, D,
                                            m->e_lo, m->e_hi, reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1,
-                                           c->sms, st));
+                                           c->sms, st, rows_peer, npeer));
             if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
         }
-        if (rows) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_d1_rows: this layer (sigmoid gate, or shape E=%d K=%d I=%d D=%d) has no one-launch decode kernel", E, K, I, D);
+        if (rows || npeer) return moty_set_error(MOTY_CUDA_ELIMIT, "moe_d1_rows: this layer (sigmoid gate, or shape E=%d K=%d I=%d D=%d) has no one-launch decode kernel", E, K, I, D);
         CKR(launch_route(logits, S, E, K, m->idx, m->w, nullptr, m->sigmoid ? 2 : 1, norm_topk, st, m->bias));
     }
     // decode fast path: one token, int8 experts, selection-order combine -> two streaming kernels
@@ -1393,6 +1409,28 @@ extern "C" int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float 
     return moe_apply_on(c, m, out_dev, x_dev, 1, logits_dev, 0, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream), rows_dev);
 }
 
+extern "C" int moty_cuda_moe_d1_peer_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, const float *logits_dev, int norm_topk,
+                                         void *const *tables, void *const *flags, int world, int rank, unsigned epoch,
+                                         void *stream) {
+    if (!m || !out_dev || !x_dev || !tables || !flags) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev: null argument");
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev: rank %d of %d (1..8 ranks)", rank, world);
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    MOTY_USE_DEVICE(m->device);
+    if (g_moe_fast != 1) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev needs the one-launch decode path (set_moe_fast_path(1))");
+    if (reinterpret_cast<uintptr_t>(x_dev) & 15) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev: x_dev must be 16-byte aligned");
+    cudaStream_t st = pick_stream(c, stream);
+    float *tb[8]; unsigned *fl[8];
+    const size_t half = (size_t)m->K * m->D;                       // two tables per rank, used alternately
+    for (int r = 0; r < world; r++) {
+        if (!tables[r] || !flags[r]) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev: null table or flag pointer for rank %d", r);
+        tb[r] = (float *)tables[r] + (epoch & 1u) * half;
+        fl[r] = (unsigned *)flags[r];
+    }
+    CKR(moe_apply_on(c, m, out_dev, x_dev, 1, logits_dev, 0, norm_topk, nullptr, nullptr, nullptr, st, nullptr, tb, world));
+    return launch_moe_peer_combine(out_dev, tb[rank], m->w, m->idx, m->K, m->D, fl, fl[rank], world, rank, epoch, c->err_dev + 1, st);
+}
+
 extern "C" int moty_cuda_moe_experts_dev(MotyCudaMoe *m, float *h_dev, const float *x_rows_dev, const int *eid_dev,
                                          int P, void *stream) {
     if (!m || !h_dev || !x_rows_dev || !eid_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_experts_dev: null argument");
@@ -1408,6 +1446,6 @@ extern "C" int moty_cuda_moe_combine_dev(float *out_dev, const float *h_dev, con
     if (!out_dev || !h_dev || !w_dev || !idx_dev) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: null argument");
     if (S <= 0) return 0;
     if (K < 1 || K > 64 || D < 1) return moty_set_error(MOTY_CUDA_EARG, "moe_combine_dev: K=%d D=%d", K, D);
-    DevCtx *c; CKR(ctx_of(out_dev, &c));
+    MOTY_CTX_OF(out_dev, c);
     return launch_moe_combine_sk(out_dev, h_dev, w_dev, idx_dev, S, K, D, order, pick_stream(c, stream));
 }

@@ -144,3 +144,8 @@ int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, cons
 
 // ---- selftest.cu: the give-up path of the bounded waits, run on purpose with a short limit ----
 int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cudaStream_t st);
+
+// ---- gemv_q8_multi.cu: up to eight independent S = 1 Q8_0 products in one launch ----
+bool q8_multi_supported(int I);
+int launch_q8_multi(int n, const int8_t *const *w, const float *const *scale, const float *const *x, float *const *y,
+                    const int *O, const int *I, int sms, cudaStream_t st);

@@ -231,6 +231,70 @@ int launch_moe_combine_sk(float *out, const float *h, const float *w, const int 
     return 0;
 }
 
+
+// ---------------------------------------------------------------------------
+// Expert-parallel decode over peer memory: the exchange and the combine in one launch.
+// Every rank's one-launch decode kernel has stored the rows of ITS experts into the row tables of ALL ranks
+// (plain peer stores over NVLink).  This kernel, next on the rank's stream, (1) tells every peer "my rows of step
+// `epoch` are written" -- a system-scope fence, then one release store per peer into that peer's flag word for this
+// rank (each writer owns its word: no atomics, values only grow) -- and (2) waits until all ranks' words in the LOCAL
+// flag array have reached `epoch`, then adds the K rows of the local table in selection order (nn/moe.c:146-149).
+// The wait is BOUNDED: about a second of polling, after which the CTA sets the error word and writes nothing
+// (moty_cuda_kernel_status reports it).  One rank per GPU only: a kernel that waits for another rank's kernel must
+// never share a GPU with it.
+// ---------------------------------------------------------------------------
+constexpr unsigned PEER_WAIT_LIMIT = 1u << 21;
+
+struct PeerCombineArgs {
+    float *out; const float *table; const float *w; const int *idx;
+    unsigned *flags_peer[8]; unsigned *flags_local;
+    int K, D, world, rank; unsigned epoch; int *err;
+};
+
+__global__ void __launch_bounds__(256) moe_peer_combine_kernel(PeerCombineArgs a) {
+    __shared__ float w_s[64];
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) {
+        ok_s = 1;
+        if (blockIdx.x == 0) {
+            __threadfence_system();                 // the decode kernel's peer stores (earlier on this stream) before the flags
+            for (int r = 0; r < a.world; r++)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(a.flags_peer[r] + a.rank), "r"(a.epoch) : "memory");
+        }
+        for (int r = 0; r < a.world && ok_s; r++) {
+            unsigned n = 0, v;
+            for (;;) {
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(a.flags_local + r) : "memory");
+                if ((int)(v - a.epoch) >= 0) break;                  // that rank has reached this step (or a later one)
+                if (++n > PEER_WAIT_LIMIT) { ok_s = 0; break; }
+            }
+        }
+        if (!ok_s) atomicExch(a.err, 1);
+    }
+    if (threadIdx.x < a.K) w_s[threadIdx.x] = a.w[threadIdx.x];
+    __syncthreads();
+    if (!ok_s) return;
+    const int d = blockIdx.x * 256 + threadIdx.x;
+    if (d >= a.D) return;
+    float acc = 0.f;
+    for (int k = 0; k < a.K; k++) acc = fmaf(w_s[k], __ldcv(a.table + (size_t)k * a.D + d), acc);   // peer-written: no stale cache line
+    a.out[d] = acc;
+}
+
+int launch_moe_peer_combine(float *out, const float *table, const float *w, const int *idx, int K, int D,
+                            unsigned *const *flags_peer, unsigned *flags_local, int world, int rank, unsigned epoch,
+                            int *err, cudaStream_t st) {
+    if (world < 1 || world > 8 || rank < 0 || rank >= world || K < 1 || K > 64)
+        return moty_set_error(MOTY_CUDA_EARG, "moe_peer_combine: world=%d rank=%d K=%d", world, rank, K);
+    PeerCombineArgs a;
+    a.out = out; a.table = table; a.w = w; a.idx = idx; a.flags_local = flags_local;
+    for (int r = 0; r < 8; r++) a.flags_peer[r] = r < world ? flags_peer[r] : nullptr;
+    a.K = K; a.D = D; a.world = world; a.rank = rank; a.epoch = epoch; a.err = err;
+    moe_peer_combine_kernel<<<(D + 255) / 256, 256, 0, st>>>(a);
+    CK(cudaGetLastError());
+    return 0;
+}
+
 // ---------------------------------------------------------------------------
 // f32 matrix (router of an engine that keeps it unquantized): one warp per
 // output row, f32 accumulation.  Outside the quantized path; the summation

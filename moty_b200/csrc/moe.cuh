@@ -46,7 +46,7 @@ int launch_moe_decode_fused_q8(const float *logits, int E, int norm_topk, int *i
                                const int8_t *g, const int8_t *u, const int8_t *d, const float *gs, const float *us,
                                const float *ds, size_t gstride, size_t gsstride, size_t dstride, size_t dsstride,
                                const float *x, float *h, float *out, float *rows, int K, int I, int D, int e_lo, int e_hi,
-                               unsigned *bar, int *err, int sms, cudaStream_t st);
+                               unsigned *bar, int *err, int sms, cudaStream_t st, float *const *rows_peer = nullptr, int npeer = 0);
 
 // ---- moe_decode_fused_q4.cu: the same for Q4R4 experts ----
 bool moe_decode_fused_q4_supported(int E, int K, int I, int D);
@@ -55,7 +55,7 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
                                float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
-                               int sms, cudaStream_t st);
+                               int sms, cudaStream_t st, float *const *rows_peer = nullptr, int npeer = 0);
 
 // ---- moe_tc.cu: the grouped expert products of an int8 batch on tcgen05 (work list = plan tiles x 128-row blocks) ----
 bool moe_tc_supported(int I, int D);
@@ -65,3 +65,8 @@ int launch_moe_tc_gateup(const Q8Tile *t_gate, const Q8Tile *t_up, const int *nt
                          int P, float *h, int I, int D, int *err, int sms, cudaStream_t st);
 int launch_moe_tc_down(const Q8Tile *t_down, const int *ntiles_dev, int tile_rows, const int8_t *d_slab, int E_local,
                        const int8_t *hq, const float *hs, int P, float *hout, int I, int D, int *err, int sms, cudaStream_t st);
+
+// ---- moe.cu: the exchange step of the expert-parallel decode over peer memory ----
+int launch_moe_peer_combine(float *out, const float *table, const float *w, const int *idx, int K, int D,
+                            unsigned *const *flags_peer, unsigned *flags_local, int world, int rank, unsigned epoch,
+                            int *err, cudaStream_t st);

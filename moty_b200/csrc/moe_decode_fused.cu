@@ -51,6 +51,8 @@ struct MoeFusedArgs {
     const float *x; float *h; float *out;         // x [D], h [K][I] scratch, out [D]
     float *rows;                                  // optional [K][D]: every selected expert's own output row, zeros for experts
                                                   // that live on another GPU (the expert-parallel decode exchanges these)
+    float *rows_peer[8]; int npeer;               // or: the [K][D] row tables of ALL ranks (peer memory, own table included):
+                                                  // the rows of resident experts are stored straight into every table
     unsigned *bar;                                // [0] arrivals, [1] generation; arrivals are 0 between launches
     int *err;
     int K, I, D, e_lo, e_hi;
@@ -297,6 +299,7 @@ __global__ void __launch_bounds__(256, 2) moe_dec_fused_kernel(MoeFusedArgs a) {
                 const float v = __shfl_sync(0xffffffffu, val, kb << SHD);
                 if (k < K && loc_s[k]) acc = fmaf(w_s[k], v, acc);        // out += w[k] * value (nn/moe.c:148)
                 if (a.rows && lane == 0 && k < K) a.rows[(size_t)k * D + d] = loc_s[k] ? v : 0.f;
+                if (a.npeer > 0 && lane < a.npeer && k < K && loc_s[k]) a.rows_peer[lane][(size_t)k * D + d] = v;   // one peer per lane
             }
         }
         if (lane == 0) a.out[d] = acc;
@@ -348,14 +351,16 @@ int launch_moe_decode_fused_q8(const float *logits, int E, int norm_topk, int *i
                                const int8_t *g, const int8_t *u, const int8_t *d, const float *gs, const float *us,
                                const float *ds, size_t gstride, size_t gsstride, size_t dstride, size_t dsstride,
                                const float *x, float *h, float *out, float *rows, int K, int I, int D, int e_lo, int e_hi,
-                               unsigned *bar, int *err, int sms, cudaStream_t st) {
+                               unsigned *bar, int *err, int sms, cudaStream_t st, float *const *rows_peer, int npeer) {
     if (!moe_decode_fused_q8_supported(E, K, I, D))
         return moty_set_error(MOTY_CUDA_EARG, "moe_decode_fused: E=%d K=%d I=%d D=%d", E, K, I, D);
     MoeFusedArgs a;
     a.logits = logits; a.E = E; a.norm_topk = norm_topk; a.idx_out = idx_out; a.w_out = w_out;
     a.g = g; a.u = u; a.d = d; a.gs = gs; a.us = us; a.ds = ds;
     a.gstride = gstride; a.gsstride = gsstride; a.dstride = dstride; a.dsstride = dsstride;
-    a.x = x; a.h = h; a.out = out; a.rows = rows; a.bar = bar; a.err = err; a.K = K; a.I = I; a.D = D; a.e_lo = e_lo; a.e_hi = e_hi;
+    a.x = x; a.h = h; a.out = out; a.rows = rows; a.npeer = npeer > 8 ? 0 : npeer;
+    for (int r = 0; r < 8; r++) a.rows_peer[r] = rows_peer && r < npeer ? rows_peer[r] : nullptr;
+    a.bar = bar; a.err = err; a.K = K; a.I = I; a.D = D; a.e_lo = e_lo; a.e_hi = e_hi;
     const int lprg = (D / 16 + 31) / 32, lprd = (I / 16 + 31) / 32;
     if (lprg <= 2) {
         if (lprd <= 2) return launch_fused_t<2, 2, 8>(a, sms, st);

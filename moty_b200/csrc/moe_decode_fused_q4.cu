@@ -31,6 +31,7 @@ struct MoeFused4Args {
     size_t gstride, gsstride, dstride, dsstride;               // per expert, in elements
     const float *x; float *out;                                // x [D], out [D]
     float *rows;                                               // optional [K][D]: each selected expert's own output row (zeros if not resident)
+    float *rows_peer[8]; int npeer;                            // or: all ranks' [K][D] row tables (peer memory): resident experts' rows go to every table
     int8_t *hq; float *hs; int *hsum;                          // hidden row, quantized: [K][I], [K][I/32], [K][I/32]
     unsigned *bar; int *err;
     int K, I, D, e_lo, e_hi;
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
                 const float v = __shfl_sync(0xffffffffu, acc, kk * 4 + r);
                 if (k0 + kk < K && loc_s[k0 + kk < K ? k0 + kk : 0]) out = fmaf(w_s[k0 + kk], v, out);   // nn/moe.c:148
                 if (a.rows && kq == 0 && k0 + kk < K) a.rows[(size_t)(k0 + kk) * D + ob * 4 + r] = loc_s[k0 + kk] ? v : 0.f;
+                if (kq < a.npeer && k0 + kk < K && loc_s[k0 + kk]) a.rows_peer[kq][(size_t)(k0 + kk) * D + ob * 4 + r] = v;   // lane group kq serves peer kq
             }
         }
         if (kq == 0) a.out[ob * 4 + r] = out;
@@ -218,14 +220,16 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
                                float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
-                               int sms, cudaStream_t st) {
+                               int sms, cudaStream_t st, float *const *rows_peer, int npeer) {
     if (!moe_decode_fused_q4_supported(E, K, I, D))
         return moty_set_error(MOTY_CUDA_EARG, "moe_decode_fused_q4: E=%d K=%d I=%d D=%d", E, K, I, D);
     MoeFused4Args a;
     a.logits = logits; a.E = E; a.norm_topk = norm_topk; a.idx_out = idx_out; a.w_out = w_out;
     a.g = g; a.u = u; a.d = d; a.gs = gs; a.us = us; a.ds = ds;
     a.gstride = gstride; a.gsstride = gsstride; a.dstride = dstride; a.dsstride = dsstride;
-    a.x = x; a.out = out; a.rows = rows; a.hq = hq; a.hs = hs; a.hsum = hsum; a.bar = bar; a.err = err;
+    a.x = x; a.out = out; a.rows = rows; a.npeer = npeer > 8 ? 0 : npeer;
+    for (int r = 0; r < 8; r++) a.rows_peer[r] = rows_peer && r < npeer ? rows_peer[r] : nullptr;
+    a.hq = hq; a.hs = hs; a.hsum = hsum; a.bar = bar; a.err = err;
     a.K = K; a.I = I; a.D = D; a.e_lo = e_lo; a.e_hi = e_hi;
     size_t a1 = (size_t)D + (size_t)(D / 32) * 8, a2 = (size_t)K * (I + 16) + (size_t)K * ((I / 32) | 1) * 8;
     size_t smem = (((a1 > a2 ? a1 : a2) + 15) & ~(size_t)15) + (size_t)E * 4;

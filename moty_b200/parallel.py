@@ -16,6 +16,10 @@ process, so nothing here has a reference counterpart; the parity statement is
                         other ranks).  ONE fixed-size all-reduce of that table (x + 0 is exact)
                         and the combine in selection order: the one-GPU bits, no count exchange,
                         no host synchronisation.
+    ``decode_peer``     the same with the exchange done by the library's own kernels over NVLink peer
+                        memory: the decode kernel stores the rows of its experts straight into every rank's
+                        row table; the next launch signals the peers (fence + release store per peer), waits
+                        -- bounded -- for their rows and combines.  No collective; the one-GPU bits.
     ``forward_gathered``  prefill: all-gather of the ranks' token shards and logits (with K = 8
                         selections per token and 8 ranks this moves the bytes a dispatch of routed
                         copies would), every rank routes all tokens redundantly and computes the
@@ -242,6 +246,48 @@ class ExpertParallelMoe:
                                             C.c_void_p(self._dw.data_ptr()), C.c_void_p(self._didx.data_ptr()),
                                             1, self.K, self.D, 0, C.c_void_p(st)))
         return self._dout
+
+    def _peer_setup(self, dev):
+        """Row tables (two, used alternately) and flag words of every rank in memory all GPUs of the group can address:
+        torch's symmetric memory does the allocation and the handle exchange; the kernels only see raw pointers."""
+        n_tab = 2 * self.K * self.D
+        if self.world == 1:
+            buf = torch.zeros((n_tab + 64,), dtype=torch.float32, device=dev)
+            ptrs = [buf.data_ptr()]
+        else:
+            import torch.distributed._symmetric_memory as symm
+            group = self.group or dist.group.WORLD
+            try:
+                symm.enable_symm_mem_for_group(group.group_name)
+            except Exception:
+                pass                                             # newer versions enable it at rendezvous
+            buf = symm.empty((n_tab + 64,), dtype=torch.float32, device=dev)
+            buf.zero_()
+            hdl = symm.rendezvous(buf, group)
+            ptrs = [int(p) for p in hdl.buffer_ptrs]
+            self._peer_hdl = hdl
+        torch.cuda.synchronize(dev)
+        if self.world > 1:
+            dist.barrier(group=self.group)                       # every rank's flags are zero before anyone signals
+        self._peer_buf = buf
+        self._peer_tables = (C.c_void_p * self.world)(*ptrs)
+        self._peer_flags = (C.c_void_p * self.world)(*[p + 4 * n_tab for p in ptrs])
+        self._peer_epoch = 0
+        self._peer_out = torch.empty((1, self.D), dtype=torch.float32, device=dev)
+
+    def decode_peer(self, x: torch.Tensor, logits: torch.Tensor, norm_topk: int = 1) -> torch.Tensor:
+        """``decode`` with the exchange done by the library's own kernels over NVLink peer memory: the decode kernel
+        stores its experts' rows into every rank's table, a second launch signals the peers, waits (bounded) for
+        theirs and combines.  Two launches per layer, no collective, the one-GPU bits.  Every rank must call it the
+        same number of times (the step counter is part of the protocol)."""
+        if getattr(self, "_peer_buf", None) is None:
+            self._peer_setup(x.device)
+        self._peer_epoch += 1
+        st = stream_handle(torch.cuda.current_stream(x.device))
+        _ck(lib().moty_cuda_moe_d1_peer_dev(self.moe.h, C.c_void_p(self._peer_out.data_ptr()), C.c_void_p(x.data_ptr()),
+                                            C.c_void_p(logits.data_ptr()), int(norm_topk), self._peer_tables, self._peer_flags,
+                                            self.world, self.rank, C.c_uint(self._peer_epoch), C.c_void_p(st)))
+        return self._peer_out
 
     def forward_gathered(self, x: torch.Tensor, logits: torch.Tensor, order: int = 1, norm_topk: int = 1) -> torch.Tensor:
         """x [s][D], logits [s][E]: this rank's tokens, the same s on every rank -> out [s][D] (1e-5, see the module text)."""

@@ -238,3 +238,29 @@ def test_errors_are_loud(gpu):
         gpu.mat_apply(W, np.zeros((1, 16), np.float32))
     with pytest.raises(gpu.MotyCudaError):
         gpu.Mat.i8(np.zeros((4, 32), np.int8), np.ones(4, np.float32), device=7)     # not initialised
+
+
+def test_q8_multi_launch_equals_single_launches(gpu, oracle):
+    """Several independent one-row products in one launch (moty_cuda_mat_apply_multi_dev): the bits of one
+    mat_apply per matrix and of the oracle; rows shared between matrices (q, k, v of a layer); shapes from the sweep
+    and ragged ones; twice in a row."""
+    import torch
+    rng = np.random.default_rng(5)
+    shapes = [(1024, 1024), (3072, 1024), (1024, 3072), (515, 3840), (9, 16), (2048, 1024), (1, 4096), (77, 2064)]
+    mats = [(rng.integers(-127, 128, s, dtype=np.int8), rng.uniform(0.001, 0.02, s[0]).astype(np.float32)) for s in shapes]
+    W = [gpu.Mat.i8(q, sc) for q, sc in mats]
+    sh = gpu.stream_handle(torch.cuda.current_stream())
+    for trial in range(2):
+        xs = [rng.standard_normal((1, s[1])).astype(np.float32) for s in shapes]
+        xs[5] = xs[0]                                            # 2048x1024 shares the row of 1024x1024
+        dx = [torch.from_numpy(x).cuda() for x in xs]
+        dx[5] = dx[0]
+        dy = [torch.full((1, s[0]), float("nan"), device="cuda") for s in shapes]
+        gpu.mat_apply_multi_dev(W, [y.data_ptr() for y in dy], [x.data_ptr() for x in dx], sh)
+        torch.cuda.synchronize()
+        for (q, sc), w, x, y in zip(mats, W, xs, dy):
+            got = y.cpu().numpy()
+            assert same_bits(got, gpu.mat_apply(w, x)) and same_bits(got, oracle.matmul_q_s(x, q, sc))
+    with pytest.raises(gpu.MotyCudaError):                       # rows longer than 4096 need the K split of the single kernel
+        big = gpu.Mat.i8(rng.integers(-127, 128, (8, 8192), dtype=np.int8), np.ones(8, np.float32))
+        gpu.mat_apply_multi_dev([big], [dy[0].data_ptr()], [dx[0].data_ptr()], sh)

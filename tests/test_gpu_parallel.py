@@ -74,6 +74,14 @@ def _worker(rank, world, port):
             out = ep.decode(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
             torch.cuda.synchronize()
             assert out.cpu().numpy().tobytes() == ref.d1(x1, l1).tobytes(), "expert-parallel decode differs"
+        # the same decode with the exchange over peer memory (the library's own kernels, no collective): several steps in
+        # a row, the tables alternate, the step counter moves on every rank alike
+        for t in range(5):
+            x1, l1 = x_all[t:t + 1], lg_all[t:t + 1]
+            out = ep.decode_peer(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
+            torch.cuda.synchronize()
+            assert mb.lib().moty_cuda_kernel_status(rank, None) == 0, mb.lib().moty_cuda_last_error()
+            assert out.cpu().numpy().tobytes() == ref.d1(x1, l1).tobytes(), f"peer-memory expert-parallel decode differs at step {t}"
         # prefill: all-gather + partial sums + reduce-scatter (sum over ranks in the collective's order: 1e-5)
         s_each = 6
         xs, ls = x_all[:world * s_each], lg_all[:world * s_each]
@@ -97,6 +105,9 @@ def _worker(rank, world, port):
             out = ep4.decode(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
             torch.cuda.synchronize()
             assert out.cpu().numpy().tobytes() == ref4.d1(x1, l1).tobytes(), "expert-parallel Q4R4 decode differs"
+            out = ep4.decode_peer(torch.from_numpy(x1).to(dev), torch.from_numpy(l1).to(dev))
+            torch.cuda.synchronize()
+            assert out.cpu().numpy().tobytes() == ref4.d1(x1, l1).tobytes(), "peer-memory Q4R4 decode differs"
     finally:
         dist.destroy_process_group()
 
