@@ -55,20 +55,6 @@ __device__ __forceinline__ void mma_s8s8_16832_z(int (&c)[4], unsigned a0, unsig
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// the same MMAs with an accumulator input {c0, c1, c0, c1}: columns (tokens) 2 tid and 2 tid + 1 of rows gid and gid + 8
-__device__ __forceinline__ void mma_u8s8_16832_c(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                                 unsigned b0, unsigned b1, int c0, int c1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
-}
-__device__ __forceinline__ void mma_s8s8_16832_c(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
-                                                 unsigned b0, unsigned b1, int c0, int c1) {
-    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%10,%11};"
-        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
-        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c0), "r"(c1));
-}
-
 // int -> float for |i| < 2^22 without the conversion unit (a quarter-rate pipe that the chain would
 // saturate): 0x4B400000 is 1.5 * 2^23 as a float; adding i to its bit pattern gives the float
 // 1.5 * 2^23 + i exactly, and the subtraction is exact.  Group sums are below 2^17 in magnitude.
@@ -208,31 +194,15 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
             for (int j = 0; j < NT; j++) {
                 const unsigned char *bp = st + L::B + (j * 8 + gid) * BTOK + ul * 32 + tid * 4;
                 const unsigned b0 = *reinterpret_cast<const unsigned *>(bp), b1 = *reinterpret_cast<const unsigned *>(bp + 16);
-                const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1
-                // The chain step of an output is  acc = fma((float)(sum - voff), d * xs, acc)  [+ acc = fma(-d, v, acc) for a
-                // token in the 4-token-tile formula], voff = 8 * xsum for a token-formula token and 0 otherwise.  Three things
-                // take the instruction count of the step from five per output to about two:
-                //  - the MMA's accumulator input carries (magic - voff), so sum - voff + magic comes out of the tensor core;
-                //  - the two tokens of a row are one f32x2 operation (Blackwell's packed single-precision add/mul/fma: two
-                //    IEEE operations per instruction, same roundings);
-                //  - the tile-formula term runs for every token with v = 0 where it does not apply: fma(-d, 0, acc) = acc.
-                const int i0 = 0x4B400000 - (f0[j] ? 0 : q.y), i1 = 0x4B400000 - (f1[j] ? 0 : q.w);
                 int c[4];
-                if (Q8) mma_s8s8_16832_c(c, a0, a1, a2, a3, b0, b1, i0, i1);
-                else mma_u8s8_16832_c(c, a0, a1, a2, a3, b0, b1, i0, i1);
-                const float2 unmagic = make_float2(-12582912.0f, -12582912.0f);
-                const float2 fsA = __fadd2_rn(make_float2(__int_as_float(c[0]), __int_as_float(c[1])), unmagic);   // exact
-                const float2 fsB = __fadd2_rn(make_float2(__int_as_float(c[2]), __int_as_float(c[3])), unmagic);
-                const float2 xs2 = make_float2(__int_as_float(q.x), __int_as_float(q.z));
-                float2 aA = make_float2(acc[j][0], acc[j][1]), aB = make_float2(acc[j][2], acc[j][3]);
-                aA = __ffma2_rn(fsA, __fmul2_rn(make_float2(dA, dA), xs2), aA);
-                aB = __ffma2_rn(fsB, __fmul2_rn(make_float2(dB, dB), xs2), aB);
-                if (!Q8) {
-                    const float2 vv = make_float2(f0[j] ? __int_as_float(q.y) : 0.f, f1[j] ? __int_as_float(q.w) : 0.f);
-                    aA = __ffma2_rn(make_float2(-dA, -dA), vv, aA);
-                    aB = __ffma2_rn(make_float2(-dB, -dB), vv, aB);
-                }
-                acc[j][0] = aA.x; acc[j][1] = aA.y; acc[j][2] = aB.x; acc[j][3] = aB.y;
+                if (Q8) mma_s8s8_16832_z(c, a0, a1, a2, a3, b0, b1);
+                else mma_u8s8_16832(c, a0, a1, a2, a3, b0, b1);
+                const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1
+                const int v0 = f0[j] ? 0 : q.y, v1 = f1[j] ? 0 : q.w;
+                acc[j][0] = q4_chain_step(acc[j][0], c[0], dA, q.x, v0, q.y, f0[j]);   // (row_a, t0)
+                acc[j][1] = q4_chain_step(acc[j][1], c[1], dA, q.z, v1, q.w, f1[j]);   // (row_a, t1)
+                acc[j][2] = q4_chain_step(acc[j][2], c[2], dB, q.x, v0, q.y, f0[j]);   // (row_b, t0)
+                acc[j][3] = q4_chain_step(acc[j][3], c[3], dB, q.z, v1, q.w, f1[j]);   // (row_b, t1)
             }
         };
         if (g0 + GCH <= nb) {

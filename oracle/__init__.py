@@ -586,6 +586,22 @@ class Ref:
                                   _p(x), C.c_int(S), _p(out))
         return out
 
+    def gelu_mul(self, g, u):
+        """g = gelu_tanh(g) * u with the engine's own static gelu_tanh (engines/gemma.c:389-391,398)."""
+        g = _f32(g).copy(); u = _f32(u)
+        self.lib.refshim_gemma_gelu_mul(_p(g), _p(u), C.c_int64(g.size))
+        return g
+
+    def gemma_gnorm_row(self, x, w, eps=1e-6, zc_norm=True):
+        x = _f32(x); out = np.empty_like(x)
+        self.lib.refshim_gemma_gnorm_row(C.c_int(int(zc_norm)), C.c_float(eps), _p(out), _p(x), _p(_f32(w)), C.c_int(x.size))
+        return out
+
+    def gemma_rope_head(self, x, pos, theta, rot_angles):
+        x = _f32(x).copy()
+        self.lib.refshim_gemma_rope_head(_p(x), C.c_int(pos), C.c_float(theta), C.c_int(x.size), C.c_int(rot_angles))
+        return x
+
     def moe_sigmoid_block(self, ex, x, bias, router_q, router_qs):
         """nn/moe.c block behind the sigmoid + bias gate, int8 router."""
         x = _f32(x).reshape(-1, ex.D); S = x.shape[0]

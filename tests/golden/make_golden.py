@@ -188,6 +188,7 @@ def main():
             pos += S
     save("attn", **d)
     sigmoid_blocks(r, save)
+    gelu_vectors(r, save)
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 
@@ -213,8 +214,21 @@ def sigmoid_blocks(r, save):
     save("blocks_sigmoid", **blk)
 
 
+def gelu_vectors(r, save):
+    """gemma's GeGLU element step from the engine's own static gelu_tanh (engines/gemma.c:389-391,398): a dense sweep
+    of the activation's working range, large and tiny magnitudes, and normal draws; its own file and random stream."""
+    rg = np.random.default_rng(20261126)
+    g = np.concatenate([np.linspace(-12, 12, 6001, dtype=np.float32), rg.standard_normal(6000).astype(np.float32) * 3,
+                        (rg.standard_normal(500) * 1e-4).astype(np.float32), np.array([0.0, -0.0, 30.0, -30.0, 1e-20, 88.0, -88.0], np.float32)])
+    u = rg.standard_normal(g.size).astype(np.float32)
+    save("gelu", g=g, u=u, out=r.gelu_mul(g, u))
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["sigmoid"]:
+    if sys.argv[1:] == ["gelu"]:
+        build()
+        gelu_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
+    elif sys.argv[1:] == ["sigmoid"]:
         build()
         sigmoid_blocks(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
     else:

@@ -222,3 +222,10 @@ def test_sigmoid_gate_block_golden(oracle):
     b = np.zeros(E, np.float32); b[5] = 10
     _, idx, w = oracle.moe_sigmoid(ex, g["x1"], g["logits1"], b)
     assert idx[0, 0] == 5 and abs(float(w.sum()) - 1) < 1e-6
+
+
+def test_gelu_tanh_golden(oracle):
+    """gemma's GeGLU element step: the restatement (with the multiply-add contraction the reference build applies to
+    x + 0.044715 x^3) against vectors from the engine's own static gelu_tanh, bit for bit.  Both call the C library's tanhf."""
+    g = golden("gelu")
+    assert same_bits(oracle.gelu_mul(g["g"], g["u"]), g["out"])
