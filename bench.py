@@ -174,6 +174,7 @@ def decode_summary(extras):
             "gpu_device_resident_graph": d.get("graph_decode_tok_s"), "gpu_device_resident_python": d.get("decode_tok_s"),
             "reference_engine_cpu": (e.get("cpu_reference") or {}).get("decode_tok_s"),
             "reference_engine_gpu_hook": (e.get("gpu_through_mat_apply_hook") or {}).get("decode_tok_s"),
+            "reference_engine_gpu_device_resident_step": (e.get("gpu_device_resident_step") or {}).get("decode_tok_s"),
             "hbm_ceiling_tok_s": round(measured_peak()[0] * 1e9 / 598.0e6, 0)}
 
 
@@ -274,7 +275,7 @@ def run_engine_qwen(ngen=128):
         write_snapshot(tmp, prompt=64, gen=ngen)
         out = {}
         traces = {}
-        for name, cuda in (("cpu_reference", False), ("gpu_through_mat_apply_hook", True)):
+        for name, cuda in (("cpu_reference", 0), ("gpu_through_mat_apply_hook", 1), ("gpu_device_resident_step", 2)):
             tr = os.path.join(tmp, f"trace_{int(cuda)}.txt")
             r = shim.run_engine(tmp, cuda=cuda, trace=tr, timeout=600)
             if r.returncode != 0:
@@ -282,7 +283,11 @@ def run_engine_qwen(ngen=128):
             m = re.search(r"prefill (\d+) tok [\d.]+ s ([\d.]+) tok/s \| decode (\d+) tok [\d.]+ s ([\d.]+) tok/s", r.stdout)
             out[name] = {"prefill_tok_s": float(m.group(2)), "decode_tok_s": float(m.group(4))}
             traces[cuda] = open(tr).read()
-        out["ids_and_logit_rows_identical"] = traces[False] == traces[True]
+        ids_of = lambda t: [ln.split()[1] for ln in t.splitlines()]
+        out["hook_ids_and_logit_rows_identical_to_cpu"] = traces[0] == traces[1]
+        a, b = ids_of(traces[0]), ids_of(traces[2])
+        first = next((i for i, (u, v) in enumerate(zip(a, b)) if u != v), len(a))
+        out["device_resident_free_running_ids_equal_to_cpu_for_steps"] = first      # (attention sums in another order: see tests/test_engine_shim.py)
         out["host_threads"] = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else os.cpu_count()
         out["workload"] = f"Qwen3-0.6B shape, QBITS=8, 64-token prompt + {ngen} greedy steps, REF= mode of the reference's qwen engine"
         return out
@@ -808,7 +813,9 @@ def run_gpu(args):
             "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
             "roofline": {"bound": "hbm", "kernel": "q8_stream_kernel<1,4,2,fused> 151936x1024 S=1", "achieved": round(achieved, 1),
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                         "traffic": profile_traffic(), "algorithmic_bytes": algo_bytes(O, I),
+                         "traffic": profile_traffic(),
+                         "traffic_source": "committed ncu summary profiles/q8_stream_gemv_151936x1024.md (dram read + write bytes of one launch of this kernel), not measured in this run",
+                         "algorithmic_bytes": algo_bytes(O, I),
                          "avg_launch_us": round(dom_ms * 1e3, 3)},
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "steps": Ke,

@@ -87,6 +87,14 @@ int moty_cuda_selftest_expire_wait(int device, int which, void *stream);
  * its drivers grow function-level static scratch with malloc (nn/matmul.c:55-58). */
 int moty_cuda_scratch_freeze(int device, int on);
 
+/* Device memory for a C host that keeps its activations on the GPU between *_dev entries without the CUDA headers
+ * (the reference is plain C): allocate, free, copy in (enqueued on `stream`, NULL = the library's; returns at once)
+ * and copy out (returns when the bytes are in host memory).  Thin wrappers of cudaMalloc / cudaFree / cudaMemcpyAsync. */
+int moty_cuda_dev_alloc(void **p, size_t bytes, int device);
+int moty_cuda_dev_free(void *p);
+int moty_cuda_dev_upload(void *dst_dev, const void *src, size_t bytes, int device, void *stream);
+int moty_cuda_dev_download(void *dst, const void *src_dev, size_t bytes, int device, void *stream);
+
 /* pinned host memory for callers that want asynchronous copies on the plain
  * (host-pointer) entries; ordinary malloc'd memory works too, only slower */
 int moty_cuda_host_alloc(void **p, size_t bytes);
@@ -347,6 +355,15 @@ int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_
 typedef struct MotyCudaAttn MotyCudaAttn;
 int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_heads, int head_dim, int rot, float theta,
                           float eps, const float *qn, const float *kn, int max_t, int kv8, int device);
+/* gemma's attention (engines/gemma.c:299-386 without the projections, shared-KV layers and k_eq_v): qn / kn / vn are
+ * the norm MULTIPLIERS per head dimension (1 + w with the engine's default zc_norm, w with GEMMA_NORM_PLAIN, :279-284;
+ * vn = the value norm, NULL = none), p-RoPE on pairs (j, j + head_dim/2) for j < rot_pairs with frequency
+ * theta^(-2j/head_dim) (:287-297; sliding layers rotate all head_dim/2 pairs), scores scaled by `scale`
+ * (1/sqrt(query_pre_attn_scalar), :363; 0 = 1/sqrt(head_dim)), and with window > 0 a token attends to positions
+ * max(0, pos - window + 1) .. pos only (:373; 0 = a global layer).  The handle is then used with the core entries below. */
+int moty_cuda_attn_create_gemma(MotyCudaAttn **out, int n_heads, int n_kv_heads, int head_dim, int rot_pairs, float theta,
+                                float eps, const float *qn, const float *kn, const float *vn, int window, float scale,
+                                int max_t, int kv8, int device);
 int moty_cuda_attn_free(MotyCudaAttn *a);
 int moty_cuda_attn_core(MotyCudaAttn *a, float *ctx, const float *q, const float *k, const float *v, int S, int pos_base);
 int moty_cuda_attn_core_dev(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev,

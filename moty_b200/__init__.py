@@ -323,13 +323,22 @@ class Attn:
     """The attention core of one layer with its KV cache on a GPU (nn/attn.c:29-74 without the projections):
     ``core(q, k, v, pos_base)`` norms and rotates q and k, stores k and v at their positions and returns ctx."""
 
-    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False, device=0):
+    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False, device=0,
+                 gemma=False, window=0, scale=0.0, vn=None):
         self.H, self.KV, self.hd, self.max_t = H, KV, hd, max_t
         h = C.c_void_p()
         qn = None if qn is None else _f32(qn); kn = None if kn is None else _f32(kn)
-        _ck(lib().moty_cuda_attn_create(C.byref(h), H, KV, hd, hd if rot is None else rot, C.c_float(theta), C.c_float(eps),
-                                        _p(qn) if qn is not None else None, _p(kn) if kn is not None else None,
-                                        max_t, 1 if kv8 else 0, device))
+        if gemma:
+            # engines/gemma.c's attention: qn / kn / vn are the norm MULTIPLIERS (1 + w), rot = rotated pairs of the p-RoPE
+            vn = None if vn is None else _f32(vn)
+            _ck(lib().moty_cuda_attn_create_gemma(C.byref(h), H, KV, hd, hd // 2 if rot is None else rot, C.c_float(theta), C.c_float(eps),
+                                                  _p(qn) if qn is not None else None, _p(kn) if kn is not None else None,
+                                                  _p(vn) if vn is not None else None, int(window), C.c_float(scale),
+                                                  max_t, 1 if kv8 else 0, device))
+        else:
+            _ck(lib().moty_cuda_attn_create(C.byref(h), H, KV, hd, hd if rot is None else rot, C.c_float(theta), C.c_float(eps),
+                                            _p(qn) if qn is not None else None, _p(kn) if kn is not None else None,
+                                            max_t, 1 if kv8 else 0, device))
         self.h = h
 
     def core(self, q, k, v, pos_base):

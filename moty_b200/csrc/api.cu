@@ -183,6 +183,40 @@ extern "C" int moty_cuda_selftest_expire_wait(int device, int which, void *strea
     return launch_selftest_expire(which, c->err_dev, reinterpret_cast<unsigned *>(c->ctr) + 4, stream ? (cudaStream_t)stream : c->stream);
 }
 
+static cudaStream_t pick_stream(DevCtx *c, void *stream);
+
+extern "C" int moty_cuda_dev_alloc(void **p, size_t bytes, int device) {
+    if (!p) return moty_set_error(MOTY_CUDA_EARG, "dev_alloc: null");
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    CK(cudaMalloc(p, bytes ? bytes : 1));
+    return 0;
+}
+
+extern "C" int moty_cuda_dev_free(void *p) {
+    if (p) CK(cudaFree(p));
+    return 0;
+}
+
+extern "C" int moty_cuda_dev_upload(void *dst_dev, const void *src, size_t bytes, int device, void *stream) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    CK(cudaMemcpyAsync(dst_dev, src, bytes, cudaMemcpyHostToDevice, pick_stream(c, stream)));
+    return 0;
+}
+
+extern "C" int moty_cuda_dev_download(void *dst, const void *src_dev, size_t bytes, int device, void *stream) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    cudaStream_t st = pick_stream(c, stream);
+    CK(cudaMemcpyAsync(dst, src_dev, bytes, cudaMemcpyDeviceToHost, st));
+    CK(cudaStreamSynchronize(st));
+    return 0;
+}
+
 extern "C" int moty_cuda_host_alloc(void **p, size_t bytes) {
     if (!p) return moty_set_error(MOTY_CUDA_EARG, "host_alloc: null");
     CK(cudaMallocHost(p, bytes ? bytes : 1));
@@ -489,10 +523,12 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     MOTY_USE_DEVICE(w->device);
     size_t xb = (size_t)S * w->I * 4, yb = (size_t)S * w->O * 4;
     CKR(moty_grow(c, &c->dx, xb));
-    CKR(moty_grow(c, &c->dy, yb));
     if (acc) CKR(moty_grow(c, &c->acc32, yb));
+    CKR(moty_grow(c, &c->dy, yb));
     CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
     CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, acc ? (int32_t *)c->acc32.p : nullptr, c->stream));
+    // (letting the GEMV write a pinned result buffer directly, so that the bytes cross PCIe while the weights stream, was
+    // measured slower than this copy: 1142 against 1203 GB/s end to end on the six-matrix pass)
     CK(cudaMemcpyAsync(y, c->dy.p, yb, cudaMemcpyDeviceToHost, c->stream));
     if (acc) CK(cudaMemcpyAsync(acc, c->acc32.p, yb, cudaMemcpyDeviceToHost, c->stream));
     // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
@@ -801,7 +837,8 @@ extern "C" int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, cons
 struct MotyCudaAttn {
     int H, KV, hd, rot, max_t, kv8, device;
     float theta, eps;
-    float *qn, *kn;
+    int gemma, window; float scale;      // engines/gemma.c's attention: p-RoPE pairs, sliding window, given score scale
+    float *qn, *kn, *vn;
     float *K, *V; int8_t *K8, *V8; float *Ks, *Vs;
 };
 
@@ -809,7 +846,7 @@ extern "C" int moty_cuda_attn_free(MotyCudaAttn *a) {
     if (!a) return 0;
     DevCtx *c = moty_ctx(a->device);
     if (c) { cudaSetDevice(a->device); cudaStreamSynchronize(c->stream); }
-    void *ps[] = {a->qn, a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs};
+    void *ps[] = {a->qn, a->kn, a->vn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs};
     for (void *p : ps) if (p) cudaFree(p);
     delete a;
     return 0;
@@ -863,6 +900,26 @@ extern "C" int moty_cuda_attn_create(MotyCudaAttn **out, int n_heads, int n_kv_h
     return 0;
 }
 
+extern "C" int moty_cuda_attn_create_gemma(MotyCudaAttn **out, int n_heads, int n_kv_heads, int head_dim, int rot_pairs, float theta,
+                                           float eps, const float *qn, const float *kn, const float *vn, int window, float scale,
+                                           int max_t, int kv8, int device) {
+    if (rot_pairs < 0 || rot_pairs > head_dim / 2 || (head_dim & 1) || window < 0 || scale < 0.f)
+        return moty_set_error(MOTY_CUDA_EARG, "attn_create_gemma: hd=%d rot_pairs=%d window=%d scale=%g", head_dim, rot_pairs, window, (double)scale);
+    MotyCudaAttn *a = nullptr;
+    CKR(moty_cuda_attn_create(&a, n_heads, n_kv_heads, head_dim, 0, theta, eps, qn, kn, max_t, kv8, device));
+    a->gemma = 1; a->rot = rot_pairs; a->window = window; a->scale = scale;
+    if (vn) {
+        DevCtx *c = moty_ctx(device);
+        MOTY_USE_DEVICE(device);
+        cudaError_t e = cudaMalloc(&a->vn, (size_t)head_dim * 4);
+        if (e == cudaSuccess) e = cudaMemcpyAsync(a->vn, vn, (size_t)head_dim * 4, cudaMemcpyHostToDevice, c->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+        if (e != cudaSuccess) { moty_cuda_attn_free(a); return moty_set_error(MOTY_CUDA_ENOMEM, "attn_create_gemma: %s", cudaGetErrorString(e)); }
+    }
+    *out = a;
+    return 0;
+}
+
 static int attn_core_on(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_dev, const float *v_dev, int S, int pos_base,
                         const int *pos_dev, void *stream);
 
@@ -887,7 +944,7 @@ static int attn_core_on(MotyCudaAttn *a, float *ctx_dev, float *q_dev, float *k_
     if (sb) CKR(moty_grow(c, &c->attn, sb));
     return launch_attn_core(ctx_dev, q_dev, k_dev, v_dev, S, pos_base, a->H, a->KV, a->hd, a->rot, a->theta, a->eps, a->qn,
                             a->kn, a->K, a->V, a->K8, a->V8, a->Ks, a->Vs, a->max_t, sb ? (float *)c->attn.p : nullptr,
-                            pos_dev, c->err_dev + 3, c->sms, pick_stream(c, stream));
+                            pos_dev, c->err_dev + 3, c->sms, pick_stream(c, stream), a->gemma, a->window, a->scale, a->vn);
 }
 
 extern "C" int moty_cuda_attn_gate_dev(MotyCudaAttn *a, float *ctx_dev, const float *gate_dev, int S, void *stream) {

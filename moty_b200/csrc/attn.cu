@@ -19,6 +19,9 @@ struct AttnArgs {
     int8_t *K8, *V8; float *Ks, *Vs;     // int8 cache [KV][max_t][hd] + scales [KV][max_t], or null
     int S, pos_base, H, KV, hd, rot, max_t;
     float theta, eps, scale;
+    // gemma's attention (engines/gemma.c:299-386): p-RoPE on pairs (j, j + hd/2) with rot = rotated pairs and frequency
+    // theta^(-2j/hd); a value norm with gains vn; on sliding layers only the last `window` positions (0 = all)
+    int gemma, window; const float *vn;
     int *err;                            // device word set when *pos_dev is outside [0, pos_base]
     const int *pos_dev;                  // when set, the first position is read from the device (a captured decode step
                                          // is replayed with a position that moves); pos_base then only sizes the launch
@@ -84,19 +87,29 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(AttnArgs a) {
     }
     if (i < hd) xs[i] = x;
     __syncthreads();
-    const int half = a.rot / 2;
-    if (i < a.rot) {                                           // nn/rope.c:39-49
+    // nn/rope.c:39-49: pairs (j, j + rot/2), angle = pos / theta^(2j/rot); gemma (engines/gemma.c:287-297): pairs
+    // (j, j + hd/2) for j < rot, angle = pos * theta^(-2j/hd)
+    const int half = a.gemma ? hd / 2 : a.rot / 2, nang = a.gemma ? a.rot : a.rot / 2;
+    if (i < 2 * half) {
         const int j = i < half ? i : i - half;
-        const float angle = __fdiv_rn((float)pos, powf(a.theta, __fdiv_rn((float)(2 * j), (float)a.rot)));
-        const float c = cosf(angle), sn = sinf(angle);
-        const float lo = xs[j], hi = xs[j + half];
-        x = i < half ? __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)) : __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
+        if (j < nang) {
+            const float angle = a.gemma ? __fmul_rn((float)pos, powf(a.theta, __fdiv_rn(__fmul_rn(-2.0f, (float)j), (float)hd)))
+                                        : __fdiv_rn((float)pos, powf(a.theta, __fdiv_rn((float)(2 * j), (float)a.rot)));
+            const float c = cosf(angle), sn = sinf(angle);
+            const float lo = xs[j], hi = xs[j + half];
+            x = i < half ? __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)) : __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
+        }
     }
     if (i < hd) row[i] = x;
     if (isq) return;
     // KV store (nn/attn.c:49-60)
     const size_t slotp = (size_t)hh * a.max_t + pos;
-    const float vv = i < hd ? a.v[(size_t)s * a.KV * hd + (size_t)hh * hd + i] : 0.f;
+    float vv = i < hd ? a.v[(size_t)s * a.KV * hd + (size_t)hh * hd + i] : 0.f;
+    if (a.vn) {                                                // gemma's value norm (engines/gemma.c:320-324): same norm, gains vn
+        const double ms = block_sum_f64((double)vv * (double)vv, red64);
+        const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / hd), a.eps)));
+        if (i < hd) vv = __fmul_rn(__fmul_rn(vv, r), a.vn[i]);
+    }
     if (a.K8) {                                                // nn/mat.c:15-17: qrow_i8 per row
         float am = block_max_f32(fabsf(x), red32);
         float sc = quant_scale(am, 1e-12f), inv = __fdiv_rn(1.f, sc);
@@ -162,7 +175,7 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     const int s = blockIdx.z, kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G, split = blockIdx.x;
     const int ng = G - g0 < AT_G ? G - g0 : AT_G, head0 = kvh * G + g0;
     int n = a.pos_base + s + 1;                                         // positions 0..qpos (re-read after the wait when it lives on the device)
-    const int t_lo = split * span;
+    int t_lo = split * span;
     int t_hi = t_lo + span < n ? t_lo + span : n;
     const size_t base = (size_t)kvh * a.max_t;
     float *qs = sm_attn, *sc = qs + AT_G * NV * 128, *ps = sc + AT_G * AT_CH;   // q[AT_G][NV*128], sc[AT_G][AT_CH], partial[warps][AT_G][NV*128]
@@ -180,6 +193,10 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
         int p0 = *a.pos_dev;                                            // clamped to [0, pos_base] like attn_prep_kernel does
         if (p0 < 0 || p0 > a.pos_base) { if (tid == 0 && a.err) atomicExch(a.err, 1); p0 = p0 < 0 ? 0 : a.pos_base; }
         n = p0 + s + 1; t_hi = t_lo + span < n ? t_lo + span : n;
+    }
+    if (a.window > 0 && n > a.window) {                                 // a sliding layer: positions qpos - window + 1 .. qpos (engines/gemma.c:373)
+        t_lo += n - a.window;
+        t_hi = t_lo + span < n ? t_lo + span : n;
     }
     if (FUSE) {
         const int pos = n - 1;
@@ -469,7 +486,8 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const int row = rg * 8 + j, tok = row >> lg;
-                const bool seen = p_me < nc && c0 + p_me <= a.pos_base + s0 + tok;
+                const int qpos = a.pos_base + s0 + tok;
+                const bool seen = p_me < nc && c0 + p_me <= qpos && (a.window <= 0 || c0 + p_me > qpos - a.window);
                 const float v = a.K8 ? __fmul_rn(__fmul_rn(ks, d8[j]), a.scale) : __fmul_rn(d8[j], a.scale);
                 P[row * AP_PP + p_me] = seen ? v : -1e30f;
             }
@@ -585,23 +603,27 @@ size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms) {
 // the launch, so that one captured launch serves every position up to it).
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st) {
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st,
+                     int gemma, int window, float scale, const float *vn) {
     if (S <= 0) return 0;
-    if (hd <= 0 || hd > 256 || hd % 4 || rot < 0 || rot > hd || (rot & 1) || H <= 0 || KV <= 0 || H % KV || pos_base < 0 ||
+    const bool rot_bad = gemma ? (rot < 0 || rot > hd / 2) : (rot < 0 || rot > hd || (rot & 1));
+    if (hd <= 0 || hd > 256 || hd % 4 || rot_bad || H <= 0 || KV <= 0 || H % KV || pos_base < 0 || window < 0 ||
         pos_base + S > max_t)
         return moty_set_error(MOTY_CUDA_EARG, "attn_core: S=%d pos=%d max_t=%d H=%d KV=%d hd=%d rot=%d", S, pos_base, max_t, H, KV, hd, rot);
     AttnArgs a;
     a.q = q; a.k = k; a.v = v; a.ctx = ctx; a.qn = qn; a.kn = kn; a.K = K; a.V = V; a.K8 = K8; a.V8 = V8; a.Ks = Ks; a.Vs = Vs;
     a.S = S; a.pos_base = pos_base; a.H = H; a.KV = KV; a.hd = hd; a.rot = rot; a.max_t = max_t;
-    a.theta = theta; a.eps = eps; a.scale = 1.f / sqrtf((float)hd); a.pos_dev = pos_dev; a.err = err;
+    a.theta = theta; a.eps = eps; a.scale = scale > 0.f ? scale : 1.f / sqrtf((float)hd); a.pos_dev = pos_dev; a.err = err;
+    a.gemma = gemma; a.window = window; a.vn = vn;
     const int nth_prep = (hd + 31) / 32 * 32;
     // one token at a position read from the device (a replayed decode step): norm, rotation and cache store ride in the
     // scores launch, and q and k are not written back
-    const bool fuse = pos_dev && S == 1;
+    const bool fuse = pos_dev && S == 1 && !gemma && !vn;              // (the fused form carries the qwen-style rotation only)
     if (!fuse) CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
     const int NVr = hd > 128 ? 2 : 1;
     const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;
-    const int G = H / KV, ngy = (G + AT_G - 1) / AT_G, T = pos_base + S;
+    const int G = H / KV, ngy = (G + AT_G - 1) / AT_G;
+    const int T = window > 0 && pos_base + S > window ? window : pos_base + S;      // the most positions any token attends to
     // prompts: eight tokens per CTA share staged key and value rows, when that still gives every SM a CTA
     const int ng_cta = G < AT_G ? G : AT_G, tq = ng_cta > 2 ? 8 : (ng_cta == 2 ? 16 : 32);
     const long long tiles = (long long)((S + tq - 1) / tq) * KV * ngy;

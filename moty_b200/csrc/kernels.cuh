@@ -88,7 +88,8 @@ int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *i
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
 int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base, int H, int KV, int hd, int rot,
                      float theta, float eps, const float *qn, const float *kn, float *K, float *V, int8_t *K8, int8_t *V8,
-                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st);
+                     float *Ks, float *Vs, int max_t, float *part, const int *pos_dev, int *err, int sms, cudaStream_t st,
+                     int gemma = 0, int window = 0, float scale = 0.f, const float *vn = nullptr);
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
 int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st);
 

@@ -39,14 +39,14 @@ def engine_binary() -> str | None:
     return v3 if os.path.exists(v3) else None
 
 
-def run_engine(snap: str, cuda: bool, trace: str | None = None, qbits: int = 8, threads: int | None = None,
+def run_engine(snap: str, cuda, trace: str | None = None, qbits: int = 8, threads: int | None = None,
                gpu: int = 0, extra_env: dict | None = None, timeout: float = 1200) -> subprocess.CompletedProcess:
     """SNAP=<snap> QBITS=<qbits> REF=<snap>/ref.json [MOTY_CUDA=1] qwen_cuda, output captured."""
     exe = engine_binary()
     if exe is None:
         raise RuntimeError("the shimmed engine is not built (make -C moty_b200/shim needs the reference checkout)")
     env = dict(os.environ, SNAP=snap, QBITS=str(qbits), REF=os.path.join(snap, "ref.json"), MOTY_NO_OMP_TUNE="1",
-               MOTY_CUDA="1" if cuda else "0", MOTY_GPU=str(gpu))
+               MOTY_CUDA=str(int(cuda)), MOTY_GPU=str(gpu))       # 0 = CPU, 1 = mat_apply hook, 2 = whole step on the GPU
     if trace:
         env["MOTY_SHIM_TRACE"] = trace
     if threads:

@@ -76,9 +76,14 @@ class AttnCache:
     """Host-side KV storage of one layer for the CPU checkers: f32 K, V [KV][max_t][hd], or int8 rows with one scale
     per (head, position) (K8, V8, Ks, Vs), plus the layer's attention parameters."""
 
-    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False):
+    def __init__(self, H, KV, hd, max_t, theta=1e6, eps=1e-6, rot=None, qn=None, kn=None, kv8=False,
+                 gemma=False, window=0, scale=0.0, vn=None):
+        """gemma=True: engines/gemma.c's attention -- qn/kn/vn are the RAW norm weights w (the multipliers are 1 + w),
+        rot = rotated pairs of the p-RoPE, window > 0 = a sliding layer, scale > 0 overrides 1/sqrt(hd)."""
         self.H, self.KV, self.hd, self.max_t = H, KV, hd, max_t
         self.theta, self.eps, self.rot, self.kv8 = float(theta), float(eps), hd if rot is None else rot, bool(kv8)
+        self.gemma, self.window, self.scale = bool(gemma), int(window), float(scale)
+        self.vn = None if vn is None else _f32(vn)
         self.qn = None if qn is None else _f32(qn); self.kn = None if kn is None else _f32(kn)
         if kv8:
             self.K8 = np.zeros((KV, max_t, hd), np.int8); self.V8 = np.zeros((KV, max_t, hd), np.int8)
@@ -183,6 +188,18 @@ class Oracle:
         q = _f32(q); k = _f32(k); v = _f32(v); S = q.shape[0]
         ctx = np.empty_like(q)
         null = C.c_void_p(0)
+        if c.gemma:
+            one = np.float32(1)
+            mul = lambda w: None if w is None else (one + w).astype(np.float32)      # the (1 + w) multipliers, in f32
+            qn, kn, vn = mul(c.qn), mul(c.kn), mul(c.vn)
+            self.lib.oracle_attn_core_gemma(_p(ctx), _p(q), _p(k), _p(v), C.c_int(S), C.c_int(pos_base), C.c_int(c.H), C.c_int(c.KV),
+                                            C.c_int(c.hd), C.c_float(c.theta), C.c_float(c.eps), C.c_int(c.rot),
+                                            _p(qn) if qn is not None else null, _p(kn) if kn is not None else null,
+                                            _p(vn) if vn is not None else null, C.c_int(c.window), C.c_float(c.scale),
+                                            _p(c.K) if not c.kv8 else null, _p(c.V) if not c.kv8 else null,
+                                            _p(c.K8) if c.kv8 else null, _p(c.V8) if c.kv8 else null,
+                                            _p(c.Ks) if c.kv8 else null, _p(c.Vs) if c.kv8 else null, C.c_int(c.max_t))
+            return ctx
         self.lib.oracle_attn_core(_p(ctx), _p(q), _p(k), _p(v), C.c_int(S), C.c_int(pos_base), C.c_int(c.H), C.c_int(c.KV),
                                   C.c_int(c.hd), C.c_float(c.theta), C.c_float(c.eps), C.c_int(c.rot),
                                   _p(c.qn) if c.qn is not None else null, _p(c.kn) if c.kn is not None else null,
@@ -466,7 +483,26 @@ class Ref:
         moty_att_accum_*."""
         c = cache; L = self.lib
         q = _f32(q); k = _f32(k); v = _f32(v); S = q.shape[0]; hd = c.hd; G = c.H // c.KV
-        for s in range(S):
+        if c.gemma:
+            # engines/gemma.c:299-386 through the engine's own static gnorm_row / gemma_rope_head (zc_norm gains 1 + w)
+            def gn(row, w):
+                L.refshim_gemma_gnorm_row(C.c_int(1), C.c_float(c.eps), _p(row), _p(row), _p(w), C.c_int(hd))
+            def rope(row, pos):
+                L.refshim_gemma_rope_head(_p(row), C.c_int(pos), C.c_float(c.theta), C.c_int(hd), C.c_int(c.rot))
+            for s in range(S):
+                for hh in range(c.KV):
+                    row = k[s, hh * hd:(hh + 1) * hd]
+                    if c.kn is not None:
+                        gn(row, c.kn)
+                    if c.vn is not None:
+                        gn(v[s, hh * hd:(hh + 1) * hd], c.vn)
+                    rope(row, pos_base + s)
+                for hh in range(c.H):
+                    row = q[s, hh * hd:(hh + 1) * hd]
+                    if c.qn is not None:
+                        gn(row, c.qn)
+                    rope(row, pos_base + s)
+        for s in range(S if not c.gemma else 0):
             for hh in range(c.H):
                 row = q[s, hh * hd:(hh + 1) * hd]
                 if c.qn is not None:
@@ -487,22 +523,23 @@ class Ref:
                 else:
                     c.K[hh, t] = k[s, hh * hd:(hh + 1) * hd]; c.V[hh, t] = v[s, hh * hd:(hh + 1) * hd]
         ctx = np.empty_like(q)
-        scale = C.c_float(np.float32(1.0) / np.sqrt(np.float32(hd)))
+        scale = C.c_float(np.float32(c.scale) if c.scale > 0 else np.float32(1.0) / np.sqrt(np.float32(hd)))
         for hh in range(c.H):
             for s in range(S):
                 qpos = pos_base + s; kvh = hh // G
-                sc = np.empty(qpos + 1, np.float32); cx = np.empty(hd, np.float32)
+                t0 = max(0, qpos - c.window + 1) if c.window > 0 else 0          # engines/gemma.c:373
+                sc = np.empty(qpos - t0 + 1, np.float32); cx = np.empty(hd, np.float32)
                 qv = np.ascontiguousarray(q[s, hh * hd:(hh + 1) * hd])
                 base = C.c_int64(kvh * c.max_t)
                 if c.kv8:
-                    L.moty_att_scores_i8(_p(sc), _p(qv), _p(c.K8), _p(c.Ks), base, C.c_int(0), C.c_int(qpos), C.c_int(hd), scale)
+                    L.moty_att_scores_i8(_p(sc), _p(qv), _p(c.K8), _p(c.Ks), base, C.c_int(t0), C.c_int(qpos), C.c_int(hd), scale)
                 else:
-                    L.moty_att_scores_f32(_p(sc), _p(qv), _p(c.K), base, C.c_int(0), C.c_int(qpos), C.c_int(hd), scale)
-                L.moty_softmax_row(_p(sc), C.c_int(qpos + 1))
+                    L.moty_att_scores_f32(_p(sc), _p(qv), _p(c.K), base, C.c_int(t0), C.c_int(qpos), C.c_int(hd), scale)
+                L.moty_softmax_row(_p(sc), C.c_int(qpos - t0 + 1))
                 if c.kv8:
-                    L.moty_att_accum_i8(_p(cx), _p(sc), _p(c.V8), _p(c.Vs), base, C.c_int(0), C.c_int(qpos), C.c_int(hd))
+                    L.moty_att_accum_i8(_p(cx), _p(sc), _p(c.V8), _p(c.Vs), base, C.c_int(t0), C.c_int(qpos), C.c_int(hd))
                 else:
-                    L.moty_att_accum_f32(_p(cx), _p(sc), _p(c.V), base, C.c_int(0), C.c_int(qpos), C.c_int(hd))
+                    L.moty_att_accum_f32(_p(cx), _p(sc), _p(c.V), base, C.c_int(t0), C.c_int(qpos), C.c_int(hd))
                 ctx[s, hh * hd:(hh + 1) * hd] = cx
         return ctx
 

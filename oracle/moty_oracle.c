@@ -923,10 +923,46 @@ ORACLE_API void oracle_rope_head(float *x, int pos, float theta, int rot) {
  * softmax (hw/hw_ops.h:22-26), accumulation over positions in order (hw/hw_ops.h:56-59; int8 values:
  * nn/attn_kernels.c:26-35).  ctx [S][H*hd].  Plain f32 statements, nothing contracted: the
  * reference's tiers differ in summation order here, parity is by tolerance. */
+/* engines/gemma.c:287-297 -- p-RoPE: pairs (j, j + hd/2), rotated for j < rot_angles, frequency theta^(-2j/hd),
+ * angle = pos * that. */
+ORACLE_API void oracle_gemma_rope_head(float *x, int pos, float theta, int hd, int rot_angles) {
+    int h = hd / 2;
+    for (int j = 0; j < rot_angles && j < h; j++) {
+        float inv = powf(theta, -2.0f * j / hd);
+        float ang = pos * inv, cs = cosf(ang), sn = sinf(ang);
+        float a = x[j], b = x[j + h];
+        x[j] = a * cs - b * sn;
+        x[j + h] = b * cs + a * sn;
+    }
+}
+
+static void attn_core_impl(float *ctx, float *q, float *k, float *v, int S, int pos_base,
+                           int H, int KV, int hd, float theta, float eps, int rot,
+                           const float *qn, const float *kn,
+                           float *K, float *V, int8_t *K8, int8_t *V8, float *Ks, float *Vs, int max_t,
+                           int gemma, int window, float scale_in, const float *vn);
 ORACLE_API void oracle_attn_core(float *ctx, float *q, float *k, const float *v, int S, int pos_base,
                                  int H, int KV, int hd, float theta, float eps, int rot,
                                  const float *qn, const float *kn,
                                  float *K, float *V, int8_t *K8, int8_t *V8, float *Ks, float *Vs, int max_t) {
+    attn_core_impl(ctx, q, k, (float *)v, S, pos_base, H, KV, hd, theta, eps, rot, qn, kn, K, V, K8, V8, Ks, Vs, max_t, 0, 0, 0.f, NULL);
+}
+/* engines/gemma.c:299-386 (attention() without the projections, shared-KV layers and k_eq_v): the same steps with
+ * gemma's own pieces -- norm gains given as the multipliers (1 + w with the default zc_norm, :279-284), an optional
+ * VALUE norm (vn, :320-324; v is normed in place), p-RoPE (rot = rotated pairs; hd/2 on sliding layers, :306), score
+ * scale 1/sqrt(query_pre_attn_scalar) when given (:363), and on sliding layers only positions
+ * max(0, qpos - window + 1) .. qpos (:373).  window = 0: a global layer. */
+ORACLE_API void oracle_attn_core_gemma(float *ctx, float *q, float *k, float *v, int S, int pos_base,
+                                       int H, int KV, int hd, float theta, float eps, int rot_angles,
+                                       const float *qn, const float *kn, const float *vn, int window, float scale,
+                                       float *K, float *V, int8_t *K8, int8_t *V8, float *Ks, float *Vs, int max_t) {
+    attn_core_impl(ctx, q, k, v, S, pos_base, H, KV, hd, theta, eps, rot_angles, qn, kn, K, V, K8, V8, Ks, Vs, max_t, 1, window, scale, vn);
+}
+static void attn_core_impl(float *ctx, float *q, float *k, float *v, int S, int pos_base,
+                           int H, int KV, int hd, float theta, float eps, int rot,
+                           const float *qn, const float *kn,
+                           float *K, float *V, int8_t *K8, int8_t *V8, float *Ks, float *Vs, int max_t,
+                           int gemma, int window, float scale_in, const float *vn) {
     int G = H / KV;
     size_t qw = (size_t)H * hd, kw = (size_t)KV * hd;
     for (int s = 0; s < S; s++) {
@@ -934,12 +970,13 @@ ORACLE_API void oracle_attn_core(float *ctx, float *q, float *k, const float *v,
         for (int hh = 0; hh < H; hh++) {
             float *p = q + s * qw + (size_t)hh * hd;
             if (qn) attn_rmsnorm(p, p, qn, hd, eps);
-            oracle_rope_head(p, pos, theta, rot);
+            if (gemma) oracle_gemma_rope_head(p, pos, theta, hd, rot); else oracle_rope_head(p, pos, theta, rot);
         }
         for (int hh = 0; hh < KV; hh++) {
             float *p = k + s * kw + (size_t)hh * hd;
             if (kn) attn_rmsnorm(p, p, kn, hd, eps);
-            oracle_rope_head(p, pos, theta, rot);
+            if (gemma) oracle_gemma_rope_head(p, pos, theta, hd, rot); else oracle_rope_head(p, pos, theta, rot);
+            if (vn) { float *pv = v + s * kw + (size_t)hh * hd; attn_rmsnorm(pv, pv, vn, hd, eps); }
         }
     }
     for (int s = 0; s < S; s++)
@@ -953,15 +990,17 @@ ORACLE_API void oracle_attn_core(float *ctx, float *q, float *k, const float *v,
                 memcpy(V + slot * hd, v + s * kw + (size_t)hh * hd, sizeof(float) * hd);
             }
         }
-    float scale = 1.f / sqrtf((float)hd);
+    float scale = scale_in > 0.f ? scale_in : 1.f / sqrtf((float)hd);
     #pragma omp parallel
     {
         float *sc = (float *)malloc(sizeof(float) * (size_t)(pos_base + S + 1));
         #pragma omp for schedule(static)
         for (int r = 0; r < H * S; r++) {
-            int hh = r / S, s = r % S, kvh = hh / G, qpos = pos_base + s, n = qpos + 1;
+            int hh = r / S, s = r % S, kvh = hh / G, qpos = pos_base + s;
+            int t0 = window > 0 && qpos - window + 1 > 0 ? qpos - window + 1 : 0;
+            int n = qpos + 1 - t0;
             const float *qv = q + s * qw + (size_t)hh * hd;
-            size_t base = (size_t)kvh * max_t;
+            size_t base = (size_t)kvh * max_t + t0;                     /* positions t0 .. qpos, indexed from 0 below */
             for (int t = 0; t < n; t++) {
                 float d = 0.f;
                 if (K8) {

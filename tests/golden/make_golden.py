@@ -189,6 +189,7 @@ def main():
     save("attn", **d)
     sigmoid_blocks(r, save)
     gelu_vectors(r, save)
+    gemma_attn_vectors(r, save)
     print("golden vectors written to", OUT, "by reference tier", r.tier)
 
 
@@ -224,8 +225,46 @@ def gelu_vectors(r, save):
     save("gelu", g=g, u=u, out=r.gelu_mul(g, u))
 
 
+GEMMA_ATTN_CASES = {
+    "s": dict(H=4, KV=2, hd=64, rot=32, window=6, scale=0.0, norm=True, vnorm=True, kv8=False),      # sliding: full p-RoPE (hd/2 pairs)
+    "t": dict(H=4, KV=2, hd=64, rot=32, window=5, scale=0.0, norm=True, vnorm=False, kv8=True),      # sliding, int8 cache
+    "g": dict(H=6, KV=2, hd=128, rot=16, window=0, scale=0.0625, norm=True, vnorm=True, kv8=False),  # global: partial rotation, given scale
+}
+
+
+def gemma_attn_vectors(r, save):
+    """gemma's attention core (engines/gemma.c:299-386 without projections, shared-KV layers and k_eq_v), composed from
+    the engine's own static gnorm_row / gemma_rope_head and the reference's score / softmax / accumulate functions with
+    the sliding window's start; four calls per case on one cache (5, 1, 3, 4 tokens: past the window)."""
+    from oracle import AttnCache
+    ra = np.random.default_rng(20261127)
+    d = {}
+    for tag, cf in GEMMA_ATTN_CASES.items():
+        hd = cf["hd"]
+        w = lambda: (ra.standard_normal(hd) * 0.2).astype(np.float32)
+        qn, kn = (w(), w()) if cf["norm"] else (None, None)
+        vn = w() if cf["vnorm"] else None
+        cache = AttnCache(cf["H"], cf["KV"], hd, 16, theta=1e4, eps=1e-6, rot=cf["rot"], qn=qn, kn=kn, kv8=cf["kv8"],
+                          gemma=True, window=cf["window"], scale=cf["scale"], vn=vn)
+        for nm, arr in (("qn", qn), ("kn", kn), ("vn", vn)):
+            if arr is not None:
+                d[f"{nm}_{tag}"] = arr
+        pos = 0
+        for step, S in enumerate((5, 1, 3, 4)):
+            q = ra.standard_normal((S, cf["H"] * hd)).astype(np.float32)
+            k = ra.standard_normal((S, cf["KV"] * hd)).astype(np.float32)
+            v = ra.standard_normal((S, cf["KV"] * hd)).astype(np.float32)
+            d[f"q_{tag}_{step}"] = q; d[f"k_{tag}_{step}"] = k; d[f"v_{tag}_{step}"] = v
+            d[f"ctx_{tag}_{step}"] = r.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
+            pos += S
+    save("attn_gemma", **d)
+
+
 if __name__ == "__main__":
-    if sys.argv[1:] == ["gelu"]:
+    if sys.argv[1:] == ["gemma_attn"]:
+        build()
+        gemma_attn_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
+    elif sys.argv[1:] == ["gelu"]:
         build()
         gelu_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
     elif sys.argv[1:] == ["sigmoid"]:

@@ -72,3 +72,27 @@ def test_qwen_engine_greedy_tokens_and_logits_through_the_gpu(tmp_path, layers, 
     # the plain REF route of the reference (run_ref) gives the same ids through the GPU
     r = shim.run_engine(snap, cuda=True)
     assert r.returncode in (0, 2) and _ids(r.stdout) == ids_cpu
+
+    # MOTY_CUDA=2: the wrapper's device-resident step (the same operations as engines/qwen.c step(), every one a *_dev
+    # entry, the KV cache on the GPU).  The attention core sums in another order than the CPU tier (a few 1e-7 per
+    # stage, MOTY_SHIM_CHECK prints them), and an ulp before a row quantizer moves an int8 code, so the logits agree to
+    # a tolerance and a free-running greedy decode of a random-weight model may part ways at a step whose top-1/top-2
+    # margin is below it.  So the comparison is teacher-forced: both runs are fed the CPU run's tokens, and at every
+    # step the device-resident run must pick the same token wherever the CPU margin is above the logits' tolerance.
+    import json
+    ref2 = json.load(open(os.path.join(snap, "ref.json")))
+    ref2["full_ids"] = ref2["prompt_ids"] + ids_cpu
+    json.dump(ref2, open(os.path.join(snap, "ref.json"), "w"))
+    t2 = str(tmp_path / "trace2.txt")
+    r = shim.run_engine(snap, cuda=2, trace=t2, extra_env={"MOTY_SHIM_FORCE": "1", "MOTY_SHIM_CHECK": "1"})
+    assert r.returncode == 0, r.stderr[-2000:]
+    tr_dev = _trace(t2)
+    top_dev = np.array([x[2] for x in tr_dev], np.uint32).view(np.float32)
+    tol = 5e-2 * float(np.abs(top).max())
+    assert np.abs(top_dev - top).max() <= tol, float(np.abs(top_dev - top).max())
+    clear = (top - second) > tol
+    same = np.array([a[1] == b[1] for a, b in zip(tr_dev, tr_cpu)])
+    assert same[clear].all(), "the device-resident step picks another token at a step with a clear margin"
+    print(f"device-resident step, teacher-forced: {int(same.sum())} of {gen} picks equal ({int(clear.sum())} steps with a margin above "
+          f"{tol:.3g}, all equal); top-1 logit max diff {float(np.abs(top_dev - top).max()):.3g};", r.stdout.splitlines()[-1])
+    print("\n".join(ln for ln in r.stderr.splitlines() if ln.startswith("[check]")))

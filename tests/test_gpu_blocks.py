@@ -30,7 +30,13 @@ def test_ffn_q8_and_q4r4(gpu, oracle):
         assert same_bits(gpu.dense_ffn(G4, U4, D4, x), g[f"ffn4_{S}"])
         y = gpu.dense_ffn(G, U, Dn, x, act=gpu.ACT_GELU_TANH)
         h = oracle.gelu_mul(oracle.matmul_q_s(x, g["gq"], g["gs"]), oracle.matmul_q_s(x, g["uq"], g["us"]))
-        assert close(y, oracle.matmul_q_s(h, g["dq"], g["ds"]), 2e-3)
+        yo = oracle.matmul_q_s(h, g["dq"], g["ds"])
+        # tanh-GeLU: the C library's tanhf is not restated (the GPU rounds tanh once from f64), so a hidden value can differ
+        # by an ulp and move one int8 code of the re-quantized row: rows whose codes agree come out bit for bit, the others
+        # differ by 1/127 of one term
+        exact = int(sum(y[r].tobytes() == yo[r].tobytes() for r in range(S)))
+        print(f"GeLU FFN S={S}: {exact} of {S} output rows bit-identical to the CPU reference's arithmetic")
+        assert close(y, yo, 2e-3)
 
 
 @pytest.mark.parametrize("D,I", [(1024, 3072), (2048, 4096), (1008, 2064), (64, 48)])
@@ -374,3 +380,44 @@ def test_moe_sigmoid_gate_golden_and_oracle(gpu, oracle):
         x = rng.standard_normal((S, D)).astype(np.float32); lg = rng.standard_normal((S, E)).astype(np.float32)
         got = m.d1(x, lg) if S == 1 else m.batch(x, lg)
         assert same_bits(got, oracle.moe_sigmoid(ex, x, lg, bias)[0]), S
+
+
+def test_gemma_attention_golden_and_oracle(gpu, oracle):
+    """gemma's attention core (engines/gemma.c:299-386): (1 + w) norms, value norm, p-RoPE on pairs (j, j + hd/2), the
+    sliding window, a given score scale.  Against the vectors composed from the engine's own static functions, then at
+    the Gemma-4-12B head shape (16 query / 8 KV heads of 256, window 1024) against the oracle: a prompt that crosses the
+    window, decode steps past it, and a global layer with partial rotation."""
+    from oracle import AttnCache
+    from test_oracle import _gemma_attn_cases
+    g = golden("attn_gemma")
+    one = np.float32(1)
+    for tag, cf in _gemma_attn_cases().items():
+        get = lambda nm: (one + g[f"{nm}_{tag}"]).astype(np.float32) if f"{nm}_{tag}" in g else None
+        a = gpu.Attn(cf["H"], cf["KV"], cf["hd"], 16, theta=1e4, eps=1e-6, rot=cf["rot"], qn=get("qn"), kn=get("kn"), vn=get("vn"),
+                     kv8=cf["kv8"], gemma=True, window=cf["window"], scale=cf["scale"])
+        pos = 0
+        for step, S in enumerate((5, 1, 3, 4)):
+            want = g[f"ctx_{tag}_{step}"]
+            y = a.core(g[f"q_{tag}_{step}"], g[f"k_{tag}_{step}"], g[f"v_{tag}_{step}"], pos)
+            tol = 2e-3 if cf["kv8"] else 5e-5
+            assert np.abs(y - want).max() <= tol * np.abs(want).max(), (tag, step, float(np.abs(y - want).max()))
+            pos += S
+        a.close()
+    rng = np.random.default_rng(12)
+    H, KV, hd, max_t = 16, 8, 256, 1400
+    for window, rot, kv8 in ((1024, 128, False), (0, 32, False), (1024, 128, True)):
+        w = lambda: (rng.standard_normal(hd) * 0.1).astype(np.float32)
+        qn, kn, vn = w(), w(), w()
+        cache = AttnCache(H, KV, hd, max_t, theta=1e4, eps=1e-6, rot=rot, qn=qn, kn=kn, vn=vn, kv8=kv8, gemma=True, window=window, scale=0.0)
+        a = gpu.Attn(H, KV, hd, max_t, theta=1e4, eps=1e-6, rot=rot, qn=one + qn, kn=one + kn, vn=one + vn, kv8=kv8, gemma=True, window=window)
+        pos = 0
+        for S in (900, 300, 1, 1, 9):                           # the second prompt chunk crosses the window; decode steps past it
+            q = rng.standard_normal((S, H * hd)).astype(np.float32)
+            k = rng.standard_normal((S, KV * hd)).astype(np.float32); v = rng.standard_normal((S, KV * hd)).astype(np.float32)
+            yo = oracle.attn_core(q.copy(), k.copy(), v.copy(), pos, cache)
+            y = a.core(q, k, v, pos)
+            tol = 2e-3 if kv8 else 5e-5
+            err, mag = float(np.abs(y - yo).max()), float(np.abs(yo).max())
+            assert err <= tol * mag, (window, rot, kv8, S, pos, err, mag)
+            pos += S
+        a.close()

@@ -1,5 +1,7 @@
 """CPU: the C restatement against the golden vectors (made by the reference's own
 compiled code) and, where the reference library exists, bit for bit against it."""
+import os
+
 import numpy as np
 import pytest
 
@@ -229,3 +231,29 @@ def test_gelu_tanh_golden(oracle):
     x + 0.044715 x^3) against vectors from the engine's own static gelu_tanh, bit for bit.  Both call the C library's tanhf."""
     g = golden("gelu")
     assert same_bits(oracle.gelu_mul(g["g"], g["u"]), g["out"])
+
+
+def _gemma_attn_cases():
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(os.path.dirname(__file__), "golden", "make_golden.py"))
+    mod = importlib.util.module_from_spec(spec); spec.loader.exec_module(mod)
+    return mod.GEMMA_ATTN_CASES
+
+
+def test_gemma_attention_golden(oracle):
+    """gemma's attention core -- (1 + w) norms, value norm, p-RoPE on pairs (j, j + hd/2), sliding window, given score
+    scale -- against vectors composed from the engine's own static functions and the reference's score / softmax /
+    accumulate kernels.  f32 arithmetic in tier-dependent order: 5e-6 of the output magnitude (2e-3 with the int8 cache)."""
+    from oracle import AttnCache
+    g = golden("attn_gemma")
+    for tag, cf in _gemma_attn_cases().items():
+        get = lambda nm: g[f"{nm}_{tag}"] if f"{nm}_{tag}" in g else None
+        cache = AttnCache(cf["H"], cf["KV"], cf["hd"], 16, theta=1e4, eps=1e-6, rot=cf["rot"], qn=get("qn"), kn=get("kn"),
+                          kv8=cf["kv8"], gemma=True, window=cf["window"], scale=cf["scale"], vn=get("vn"))
+        pos = 0
+        for step, S in enumerate((5, 1, 3, 4)):
+            want = g[f"ctx_{tag}_{step}"]
+            got = oracle.attn_core(g[f"q_{tag}_{step}"].copy(), g[f"k_{tag}_{step}"].copy(), g[f"v_{tag}_{step}"].copy(), pos, cache)
+            tol = 2e-3 if cf["kv8"] else 5e-6
+            assert np.abs(got - want).max() <= tol * np.abs(want).max(), (tag, step, float(np.abs(got - want).max()))
+            pos += S
