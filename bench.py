@@ -665,9 +665,13 @@ def run_gpu(args):
     sp = stream.cuda_stream
     total_bytes = sum(algo_bytes(*s) for s in SHAPES)
 
-    # the three small matrices (1-3 MB each: a launch costs ten times their HBM time) go out as ONE launch
-    # (moty_cuda_mat_apply_multi_dev); --no-multi launches them one by one
-    multi = [i for i in range(len(SHAPES)) if SHAPES[i][0] * SHAPES[i][1] <= (4 << 20) and SHAPES[i][1] <= 4096] if not args.no_multi else []
+    # Every launch of this pass carries about 5 us that is not streaming (launch, the per-CTA row quantizer, the tail):
+    # for the 1-3 MB matrices that is ten times their HBM time.  They go out as ONE launch
+    # (moty_cuda_mat_apply_multi_dev); --no-multi launches them one by one.  --multi-max-mb 64 also folds the
+    # 15360 x 3840 matrix in (measured: no gain -- the generic two-row units of that kernel stream a 59 MB matrix less
+    # well than its own launch does, which cancels the saved fixed cost: 66.3 against 66.2 us per pass).
+    multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 4096 and i != DOMINANT and
+             SHAPES[i][0] * SHAPES[i][1] <= (args.multi_max_mb << 20)] if not args.no_multi else []
     singles = [i for i in range(len(SHAPES)) if i not in multi]
 
     def launch(idxs):
@@ -808,7 +812,7 @@ def run_gpu(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "int8xint8->int32", "data": "synthetic",
             "config": config_dict(world),
             "launch": ("direct" if args.no_graph else "cuda_graph_replay") +
-                      (f"; the {len(multi)} matrices of at most 4 MB in one launch" if len(multi) > 1 else ""),
+                      (f"; the {len(multi)} matrices of at most {args.multi_max_mb} MB in one launch" if len(multi) > 1 else ""),
             "timed_region": f"median of {ROUNDS} rounds of {K} steps",
             "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
             "roofline": {"bound": "hbm", "kernel": "q8_stream_kernel<1,4,2,fused> 151936x1024 S=1", "achieved": round(achieved, 1),
@@ -1043,6 +1047,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
+    ap.add_argument("--multi-max-mb", type=int, default=4, help="largest matrix (MB) that joins the several-products-in-one-launch call")
     ap.add_argument("--no-multi", action="store_true", help="launch the small matrices one by one instead of in one launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")

@@ -20,7 +20,7 @@ OBJ = os.path.join(HERE, "build")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
-FLAGS += os.environ.get("MOTY_NVCC_EXTRA", "").split()      # developer builds, e.g. -DMOTY_DBG_STAMPS
+FLAGS += os.environ.get("MOTY_NVCC_EXTRA", "").split()      # extra nvcc flags for a developer build
 
 
 def sources():
