@@ -960,6 +960,49 @@ def run_case(args):
                           "graph_GBs": round(wbytes * ngen / (t4 - t3) / 1e9, 1), "graph_equals_direct": tg == toks[1:]}), flush=True)
         dec.close()
         return
+    if parts[0] == "decode" and parts[1] == "gemma":    # decode:gemma[:NGEN[:PROMPT[:NL]]] -- configs[4] shape, synthetic int8 weights
+        import time
+        from moty_b200.decoder import GemmaDecoder, GemmaLayer
+        ngen = int(parts[2]) if len(parts) > 2 else 256
+        PROMPT = int(parts[3]) if len(parts) > 3 else 4096
+        NL = int(parts[4]) if len(parts) > 4 else 48
+        D, H, KV, hd, I, V, WINDOW = 3840, 16, 8, 256, 15360, 262144, 1024
+        def raw(O, Kk, lo=0.0002, hi=0.0006):
+            q = np.frombuffer(rng.bytes(O * Kk), np.int8).reshape(O, Kk)
+            return np.maximum(q, -127), rng.uniform(lo, hi, O).astype(np.float32)
+        mk = lambda O, Kk: mb.Mat.i8(*raw(O, Kk), device=0)
+        one = lambda n: np.ones(n, np.float32)
+        layers = []
+        for i in range(NL):
+            q, k, v = raw(H * hd, D), raw(KV * hd, D), raw(KV * hd, D)
+            qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=0)
+            sliding = (i + 1) % 6 != 0                                  # 5 of every 6 layers slide, the sixth is global
+            layers.append(GemmaLayer(mb.Mat.i8(*q, device=0), mb.Mat.i8(*k, device=0), mb.Mat.i8(*v, device=0), mk(D, H * hd),
+                                     mk(I, D), mk(I, D), mk(D, I), one(D), one(D), one(D), one(D), one(hd), one(hd), one(hd),
+                                     n_kv_heads=KV, head_dim=hd, theta=1e4 if sliding else 1e6, window=WINDOW if sliding else 0, qkv=qkv))
+        head = mb.Mat.i8(*raw(V, D, 0.0001, 0.0003), device=0)
+        dec = GemmaDecoder(layers, head, one(D), H, PROMPT + ngen + 8, max_S=512)
+        prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
+        dec.prefill(prompt[:min(PROMPT, 512)], 0); dec.step([1], min(PROMPT, 512))      # warm-up (allocations, attributes)
+        torch.cuda.synchronize(); t0 = time.perf_counter()
+        tok = dec.prefill(prompt, 0, block=512)
+        torch.cuda.synchronize(); t1 = time.perf_counter()
+        toks = [tok]
+        for i in range(ngen):
+            toks.append(dec.step([toks[-1]], PROMPT + i))
+        torch.cuda.synchronize(); t2 = time.perf_counter()
+        tg = dec.greedy_graph(tok, PROMPT, ngen)
+        torch.cuda.synchronize(); t3 = time.perf_counter()
+        tg = dec.greedy_graph(tok, PROMPT, ngen)
+        torch.cuda.synchronize(); t4 = time.perf_counter()
+        wbytes = sum(m.nbytes() for l in layers for m in (l.qkv, l.o, l.gate, l.up, l.down)) + head.nbytes()
+        print(json.dumps({"case": args.case, "layers": NL, "prompt": PROMPT, "prefill_tok_s": round(PROMPT / (t1 - t0), 1),
+                          "prefill_s": round(t1 - t0, 3), "decode_tok_s": round(ngen / (t2 - t1), 1),
+                          "ms_per_token": round((t2 - t1) / ngen * 1e3, 3), "weight_MB_per_token": round(wbytes / 1e6, 1),
+                          "graph_decode_tok_s": round(ngen / (t4 - t3), 1), "graph_ms_per_token": round((t4 - t3) / ngen * 1e3, 3),
+                          "graph_GBs": round(wbytes * ngen / (t4 - t3) / 1e9, 1), "graph_equals_direct": tg == toks[1:]}), flush=True)
+        dec.close()
+        return
     if parts[0] == "decode":                            # decode:qwen3-0.6b[:NGEN] -- configs[0] shape, synthetic int8 weights
         res = run_decode_qwen(torch, mb, rng, int(parts[2]) if len(parts) > 2 else 128, 0)
         print(json.dumps({"case": args.case, **res}), flush=True)
@@ -1056,7 +1099,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the per-shape S=16/512 and Q4R4 rows")
     ap.add_argument("--case", default="", help="profiling aid: FMT:S:O:I (FMT q8_0, q4r4 or q8r4) times only that product, "
                                                 "--steps launches after --warmup; moe:NAME:S (NAME olmoe or qwen3-30b-a3b) "
-                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder, decode:olmoe[:NGEN] a 512-token prompt and NGEN steps of the configs[2]-shaped MoE decoder; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8][:posdev] the attention core with S tokens at position POS (posdev: position read from the device, the one-launch decode core); ep:NAME:S under torchrun times the "
+                                                "times calls of one routed layer; decode:qwen3-0.6b[:NGEN] a 64-token prompt and NGEN greedy steps of the configs[0]-shaped dense decoder, decode:olmoe[:NGEN] a 512-token prompt and NGEN steps of the configs[2]-shaped MoE decoder; decode:gemma[:NGEN[:PROMPT[:NL]]] a PROMPT-token (4096) blocked prefill and NGEN (256) steps of the configs[4]-shaped dense decoder with NL (48) layers; ffn:S:D:I one dense int8 SiLU FFN block; attn:S:POS:H:KV:hd[:kv8][:posdev] the attention core with S tokens at position POS (posdev: position read from the device, the one-launch decode core); ep:NAME:S under torchrun times the "
                                                 "expert-parallel layer with S tokens per rank; prints one row and exits")
     args = ap.parse_args()
     if args.case:

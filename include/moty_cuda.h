@@ -330,6 +330,12 @@ int moty_cuda_add_dev(float *y_dev, const float *x_dev, long long n, void *strea
  * (same results as add_dev followed by rmsnorm_dev). */
 int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, const float *w_dev, int S, int D,
                               float eps, void *stream);
+/* normadd_rmsnorm: the sandwich step of engines/gemma.c:468-474 / :478-482, one launch: x += rmsnorm(t) with gains
+ * g_t (the post-block norm, done in place on the block's output there), then -- when out_dev is not NULL --
+ * out = rmsnorm(x) with gains g_x (the norm that opens the next block).  The gains are the multipliers themselves:
+ * pass 1 + w for a zero-centred checkpoint (gnorm_row, engines/gemma.c:279-284).  t is left as it was. */
+int moty_cuda_normadd_rmsnorm_dev(float *x_dev, const float *t_dev, const float *g_t_dev, float *out_dev, const float *g_x_dev,
+                                  int S, int D, float eps, void *stream);
 /* The same add and norm folded into the decode product that consumes them (one launch instead of two):
  * y = W * rmsnorm(x + t) with gains gain_dev, and xout = x + t (xout_dev must overlap neither x_dev nor t_dev: one CTA
  * writes xout while every other still reads x and t; MOTY_CUDA_EARG otherwise).

@@ -821,6 +821,13 @@ extern "C" int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float
     return launch_add_rmsnorm_rows(x_dev, t_dev, out_dev, w_dev, S, D, eps, pick_stream(c, stream));
 }
 
+extern "C" int moty_cuda_normadd_rmsnorm_dev(float *x_dev, const float *t_dev, const float *g_t_dev, float *out_dev, const float *g_x_dev,
+                                             int S, int D, float eps, void *stream) {
+    if (!x_dev || !t_dev || !g_t_dev || (out_dev && !g_x_dev)) return moty_set_error(MOTY_CUDA_EARG, "normadd_rmsnorm_dev: null argument");
+    MOTY_CTX_OF(x_dev, c);
+    return launch_normadd_rmsnorm_rows(x_dev, t_dev, g_t_dev, out_dev, g_x_dev, S, D, eps, pick_stream(c, stream));
+}
+
 extern "C" int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream) {
     if (!embed || !out_dev || !ids_dev) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: null argument");
     if (embed->fmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "embed_rows_dev: MOTY_WF_I8 table only");
@@ -1036,6 +1043,14 @@ static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
                                           (const float *)gate->scales, (const float *)up->scales, (const float *)down->scales,
                                           0, 0, 0, 0, x, (float *)c->g.p, out, nullptr, 1, I, D, 0, 1,
                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st);
+    }
+    // The other one-token int8 blocks (tanh-GeLU, or SiLU beyond that kernel's sizes) with rows of at most 4096 values:
+    // gate, up and the activation in one launch, then the down product.  Same bits as the four steps below.
+    if (S == 1 && g_moe_fast == 1 && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 && q8_gateup_supported(I, D) &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        CKR(launch_q8_gateup((const int8_t *)gate->codes, (const float *)gate->scales, (const int8_t *)up->codes, (const float *)up->scales,
+                             x, (float *)c->g.p, I, D, act, c->sms, st));
+        return mat_apply_on(c, down, out, (const float *)c->g.p, S, nullptr, st);
     }
     CKR(moty_grow(c, &c->u, hb));
     CKR(mat_apply_on(c, gate, (float *)c->g.p, x, S, nullptr, st));

@@ -246,5 +246,12 @@ __device__ __forceinline__ float moty_expf(float x) {
 __device__ __forceinline__ float moty_silu_mul(float v, float u) {
     return __fmul_rn(__fdiv_rn(v, __fadd_rn(1.f, moty_expf(-v))), u);
 }
+// tanh-GeLU(v) * u as engines/gemma.c:389-391,398 spells it: 0.5 v (1 + tanhf(0.79788456 (v + 0.044715 v^3))) * u.
+// v + 0.044715 v v v: the CPU build fuses the last multiply with the add; tanh is evaluated in f64 and rounded once.
+__device__ __forceinline__ float moty_gelu_mul(float v, float u) {
+    const float inner = __fmul_rn(0.7978845608028654f, fmaf(__fmul_rn(__fmul_rn(0.044715f, v), v), v, v));
+    const float th = (float)tanh((double)inner);
+    return __fmul_rn(__fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, th)), u);
+}
 
 #endif  // __CUDACC__

@@ -83,6 +83,9 @@ int launch_q4r4_gemv1(const uint8_t *w, const uint16_t *d, const float *x, float
 int launch_rmsnorm_rows(float *out, const float *x, const float *w, int S, int D, float eps, cudaStream_t st);
 int launch_add(float *y, const float *x, long long n, cudaStream_t st);
 int launch_add_rmsnorm_rows(float *x, const float *t, float *out, const float *w, int S, int D, float eps, cudaStream_t st);
+// x += rmsnorm(t) * g1, then (out given) out = rmsnorm(x) * g2
+int launch_normadd_rmsnorm_rows(float *x, const float *t, const float *g1, float *out, const float *g2, int S, int D, float eps,
+                                cudaStream_t st);
 int launch_embed_rows(float *dst, const int8_t *q, const float *qs, const int *ids, int S, int D, int V, float scale, cudaStream_t st);
 
 // ---- attn.cu: attention core between the projections (QK-norm + RoPE, KV store, scores, softmax, accumulation) ----
@@ -145,6 +148,11 @@ int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, cons
 
 // ---- selftest.cu: the give-up path of the bounded waits, run on purpose with a short limit ----
 int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cudaStream_t st);
+
+// ---- gemv_q8_gateup.cu: h = act(gate . x) * (up . x) for one token in one launch (rows of at most 4096 values) ----
+bool q8_gateup_supported(int I, int D);
+int launch_q8_gateup(const int8_t *g, const float *gs, const int8_t *u, const float *us, const float *x, float *h, int I, int D,
+                     int act, int sms, cudaStream_t st);
 
 // ---- gemv_q8_multi.cu: up to eight independent S = 1 Q8_0 products in one launch ----
 bool q8_multi_supported(int I);

@@ -7,22 +7,12 @@
 // ---------------------------------------------------------------------------
 // g = act(g) * u.  SiLU: v / (1 + exp(-v)) (hw/hw_ops.h:19-21); tanh-GeLU:
 // 0.5 v (1 + tanh(0.79788456 (v + 0.044715 v^3))) (engines/gemma.c:389-391).
-// exp is moty_expf (the C library's expf restated, common.cuh); tanh is evaluated in f64 and rounded
-// once; the surrounding f32 steps are spelled out so that nothing is fused or reassociated.
+// Both expressions live in common.cuh (moty_silu_mul, moty_gelu_mul), f32 step by f32 step.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) act_mul_kernel(float *__restrict__ g, const float *__restrict__ u, long long n, int act) {
     long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
-    float v = g[i], t;
-    if (act == MOTY_ACT_SILU) {
-        t = __fdiv_rn(v, __fadd_rn(1.f, moty_expf(-v)));
-    } else {
-        // v + 0.044715 v v v: the CPU build fuses the last multiply with the add
-        float inner = __fmul_rn(0.7978845608028654f, fmaf(__fmul_rn(__fmul_rn(0.044715f, v), v), v, v));
-        float th = (float)tanh((double)inner);
-        t = __fmul_rn(__fmul_rn(0.5f, v), __fadd_rn(1.f, th));
-    }
-    g[i] = __fmul_rn(t, u[i]);
+    g[i] = act == MOTY_ACT_SILU ? moty_silu_mul(g[i], u[i]) : moty_gelu_mul(g[i], u[i]);
 }
 
 int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st) {

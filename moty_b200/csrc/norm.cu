@@ -60,6 +60,81 @@ __global__ void __launch_bounds__(256) rmsnorm_rows_kernel(float *x, const float
     }
 }
 
+// The sandwich step of engines/gemma.c:468-474 and :478-482, one CTA per row: tn = (t * r_t) * g1 (the norm of the
+// block's output, in place there), x += tn, then -- when out is given -- out = (x * r_x) * g2, the norm that opens the
+// next block.  Both means of squares in double as in gnorm_row (engines/gemma.c:279-284); the gains are the multipliers
+// themselves (1 + w for a zero-centred checkpoint).  Rows of up to 4096 values stay in registers.
+constexpr int NA_PER = 16;
+
+__device__ __forceinline__ double block_sum_256(double v, double *red) {
+    for (int off = 16; off > 0; off >>= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+    __syncthreads();                                          // red may still be read from a previous sum
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    double s = 0;
+    for (int i = 0; i < 8; i++) s += red[i];
+    return s;
+}
+
+__global__ void __launch_bounds__(256) normadd_rmsnorm_rows_kernel(float *x, const float *t, const float *g1, float *out, const float *g2,
+                                                                   int D, float eps) {
+    __shared__ double red[8];
+    pdl_trigger();
+    pdl_wait();
+    float *xr = x + (size_t)blockIdx.x * D;
+    const float *tr = t + (size_t)blockIdx.x * D;
+    float *orow = out ? out + (size_t)blockIdx.x * D : nullptr;
+    if (D <= 256 * NA_PER) {
+        float tv[NA_PER], xv[NA_PER], g1v[NA_PER], g2v[NA_PER];       // every load of the kernel goes out at once
+        double ms = 0;
+#pragma unroll
+        for (int j = 0; j < NA_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            tv[j] = i < D ? tr[i] : 0.f;
+            xv[j] = i < D ? xr[i] : 0.f;
+            g1v[j] = i < D ? g1[i] : 0.f;
+            g2v[j] = i < D && orow ? g2[i] : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < NA_PER; j++) ms += (double)tv[j] * (double)tv[j];
+        ms = block_sum_256(ms, red);
+        const float rt = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+        ms = 0;
+#pragma unroll
+        for (int j = 0; j < NA_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < D) {
+                xv[j] = __fadd_rn(xv[j], __fmul_rn(__fmul_rn(tv[j], rt), g1v[j]));
+                xr[i] = xv[j];
+            }
+            ms += (double)xv[j] * (double)xv[j];
+        }
+        if (!orow) return;
+        ms = block_sum_256(ms, red);
+        const float rx = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+#pragma unroll
+        for (int j = 0; j < NA_PER; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (i < D) orow[i] = __fmul_rn(__fmul_rn(xv[j], rx), g2v[j]);
+        }
+        return;
+    }
+    double ms = 0;
+    for (int i = threadIdx.x; i < D; i += 256) ms += (double)tr[i] * (double)tr[i];
+    ms = block_sum_256(ms, red);
+    const float rt = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+    ms = 0;
+    for (int i = threadIdx.x; i < D; i += 256) {
+        const float a = __fadd_rn(xr[i], __fmul_rn(__fmul_rn(tr[i], rt), g1[i]));
+        xr[i] = a;
+        ms += (double)a * (double)a;
+    }
+    if (!orow) return;
+    ms = block_sum_256(ms, red);
+    const float rx = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(ms / D), eps)));
+    for (int i = threadIdx.x; i < D; i += 256) orow[i] = __fmul_rn(__fmul_rn(xr[i], rx), g2[i]);   // the thread's own writes above
+}
+
 __global__ void __launch_bounds__(256) add_kernel(float *y, const float *x, long long n) {
     pdl_trigger();
     pdl_wait();
@@ -91,6 +166,14 @@ int launch_add_rmsnorm_rows(float *x, const float *t, float *out, const float *w
     if (S <= 0) return 0;
     if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "add_rmsnorm: D=%d", D);
     CK(moty_launch_pdl(rmsnorm_rows_kernel<true>, dim3(S), dim3(256), (size_t)0, st, x, t, out, w, D, eps));
+    return 0;
+}
+
+int launch_normadd_rmsnorm_rows(float *x, const float *t, const float *g1, float *out, const float *g2, int S, int D, float eps,
+                                cudaStream_t st) {
+    if (S <= 0) return 0;
+    if (D <= 0) return moty_set_error(MOTY_CUDA_EARG, "normadd_rmsnorm: D=%d", D);
+    CK(moty_launch_pdl(normadd_rmsnorm_rows_kernel, dim3(S), dim3(256), (size_t)0, st, x, t, g1, out, g2, D, eps));
     return 0;
 }
 

@@ -14,7 +14,7 @@ import ctypes as C
 
 import numpy as np
 
-from . import Attn, Mat, MotyCudaError, lib, stream_handle, ACT_SILU
+from . import Attn, Mat, MotyCudaError, lib, stream_handle, ACT_GELU_TANH, ACT_SILU
 
 
 def _ck(rc):
@@ -216,3 +216,138 @@ class DenseDecoder:
             self._drop_graph()
         except Exception:
             pass
+
+
+class GemmaLayer:
+    """One layer of the reference's ``gemma`` engine (engines/gemma.c:299-386, :392-401, :466-483): int8 matrices
+    (q, k, v, o, gate, up, down; optionally the rows of q, k and v in one matrix), the four sandwich norms and the three
+    per-head norms as MULTIPLIERS (1 + w for a zero-centred checkpoint), and the layer's own attention geometry: a
+    sliding layer has ``window`` > 0 and rotates every pair (``rot`` = head_dim / 2); a global one has ``window`` = 0,
+    its own head_dim / KV-head count / theta, and ``rot`` rotated pairs of the p-RoPE."""
+
+    def __init__(self, q, k, v, o, gate, up, down, in_ln, post_attn_ln, pre_ff_ln, post_ff_ln, qn, kn, vn=None, *, n_kv_heads, head_dim,
+                 theta, window=0, rot=None, scale=0.0, qkv=None):
+        self.q, self.k, self.v, self.o, self.gate, self.up, self.down, self.qkv = q, k, v, o, gate, up, down, qkv
+        self.in_ln, self.post_attn_ln, self.pre_ff_ln, self.post_ff_ln = in_ln, post_attn_ln, pre_ff_ln, post_ff_ln
+        self.qn, self.kn, self.vn = qn, kn, vn
+        self.KV, self.hd, self.theta, self.window, self.scale = n_kv_heads, head_dim, float(theta), int(window), float(scale)
+        self.rot = head_dim // 2 if rot is None else int(rot)
+
+
+class GemmaDecoder(DenseDecoder):
+    """The step of engines/gemma.c:453-497 without the per-layer-embedding branch (ple_dim = 0) and without shared KV
+    layers: embedding rows scaled by sqrt(hidden), per layer  x += post_attn_norm(attn(in_norm(x)))  and
+    x += post_ff_norm(gelu_mlp(pre_ff_norm(x))), the final norm of the last token, the lm_head and the greedy pick.
+    The final logit soft-cap (softcap * tanhf(logit / softcap)) is monotonic, so the greedy pick is taken from the
+    uncapped logits; ``step(..., want_logits=True)`` returns them uncapped."""
+
+    def __init__(self, layers, head: Mat, final_norm, n_heads, max_t, eps=1e-6, kv8=False, device=0, max_S=64):
+        import torch
+        self.torch = torch
+        self.dev = torch.device(f"cuda:{device}")
+        self.layers, self.head = layers, head
+        self.H, self.eps, self.max_t = n_heads, float(eps), max_t
+        self.D = head.I
+        self.embed_scale = float(np.sqrt(np.float32(self.D)))
+        self.fold_addnorm = False
+        f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
+        self.final_norm = f(final_norm)
+        self.ln = [tuple(f(g) for g in (l.in_ln, l.post_attn_ln, l.pre_ff_ln, l.post_ff_ln)) for l in layers]
+        self.attn = [Attn(n_heads, l.KV, l.hd, max_t, theta=l.theta, eps=eps, rot=l.rot, qn=l.qn, kn=l.kn, vn=l.vn, kv8=kv8,
+                          device=device, gemma=True, window=l.window, scale=l.scale) for l in layers]
+        # buffers sized for the widest layer
+        self.hd, self.KV = max(l.hd for l in layers), 0
+        self._qw = max(n_heads * l.hd for l in layers)
+        self._kw = max(l.KV * l.hd for l in layers)
+        self.stream = torch.cuda.Stream(device=self.dev)
+        self._alloc(max_S)
+
+    def _alloc(self, S):
+        t, dev = self.torch, self.dev
+        e = lambda *shape: t.empty(shape, device=dev, dtype=t.float32)
+        self._drop_graph()
+        self.cap = S
+        self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
+        self.qb, self.kb, self.vb, self.ctx = e(S, self._qw), e(S, self._kw), e(S, self._kw), e(S, self._qw)
+        self.qkvb = e(1, self._qw + 2 * self._kw)
+        self.ids = t.empty((S,), device=dev, dtype=t.int32)
+        self.out_id = t.empty((1,), device=dev, dtype=t.int32)
+        self.logits = e(1, self.head.O)
+
+    def _embed(self, S, sh):
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        _ck(lib().moty_cuda_embed_rows_dev(self.head.h, p(self.x), p(self.ids), S, C.c_float(self.embed_scale), sh))
+
+    def _layers(self, S, pos_base, pos_dev, sh):
+        """engines/gemma.c:466-483 on self.x [S][D]; on return self.nrm holds the FINAL norm of every row (the last
+        sandwich step opens it), so the caller goes straight to the lm_head."""
+        L, D, eps = lib(), self.D, C.c_float(self.eps)
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        nl = len(self.layers)
+        x = self.x
+        _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(x), p(self.ln[0][0]), S, D, eps, sh))
+        for i, (l, (in_ln, post_attn, pre_ff, post_ff), a) in enumerate(zip(self.layers, self.ln, self.attn)):
+            qw, kw = self.H * l.hd, l.KV * l.hd
+            if S == 1 and l.qkv is not None:
+                _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
+                base = self.qkvb.data_ptr()
+                qp, kp, vp = C.c_void_p(base), C.c_void_p(base + 4 * qw), C.c_void_p(base + 4 * (qw + kw))
+            else:
+                _ck(L.moty_cuda_mat_apply_dev(l.q.h, p(self.qb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.k.h, p(self.kb), p(self.nrm), S, sh))
+                _ck(L.moty_cuda_mat_apply_dev(l.v.h, p(self.vb), p(self.nrm), S, sh))
+                qp, kp, vp = p(self.qb), p(self.kb), p(self.vb)
+            if pos_dev is None:
+                _ck(L.moty_cuda_attn_core_dev(a.h, p(self.ctx), qp, kp, vp, S, pos_base, sh))
+            else:
+                _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
+            _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
+            _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_attn), p(self.nrm), p(pre_ff), S, D, eps, sh))
+            _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_GELU_TANH, p(self.tmp), p(self.nrm), S, sh))
+            nxt = self.ln[i + 1][0] if i + 1 < nl else self.final_norm
+            _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_ff), p(self.nrm), p(nxt), S, D, eps, sh))
+        return x
+
+    def step(self, ids, pos_base, want_logits=False):
+        t, L = self.torch, lib()
+        ids = np.ascontiguousarray(ids, np.int32).ravel()
+        S = ids.size
+        if S > getattr(self, "_max_S", 0):
+            self._drop_graph()
+            self._max_S = S
+        if S > self.cap:
+            self._alloc(S)
+        if pos_base + S > self.max_t:
+            raise MotyCudaError(f"positions {pos_base}..{pos_base + S} exceed the cache of {self.max_t}")
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        with t.cuda.stream(self.stream):
+            sh = C.c_void_p(stream_handle(self.stream))
+            self.ids[:S].copy_(t.from_numpy(ids), non_blocking=True)
+            self._embed(S, sh)
+            self._layers(S, pos_base, None, sh)
+            _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm[S - 1:S]), 1, p(self.out_id), p(self.logits), sh))
+            tok = int(self.out_id.cpu()[0])
+            self._check_kernels()
+            if want_logits:
+                return tok, self.logits.cpu().numpy()[0]
+        return tok
+
+    def prefill(self, ids, pos_base=0, block=512):
+        """A long prompt in blocks of ``block`` tokens (the blocked prefill of engines/gemma.c:484-485: the blocks
+        before the last need no logits); returns the greedy token after the last one."""
+        ids = np.ascontiguousarray(ids, np.int32).ravel()
+        tok = None
+        for lo in range(0, ids.size, block):
+            tok = self.step(ids[lo:lo + block], pos_base + lo)
+        return tok
+
+    def _decode_body(self, sh):
+        L = lib()
+        p = lambda ten: C.c_void_p(ten.data_ptr())
+        self._embed(1, sh)
+        self._layers(1, self.max_t - 1, self.pos_dev, sh)
+        _ck(L.moty_cuda_head_argmax_dev(self.head.h, p(self.nrm), 1, p(self.out_id), p(self.logits), sh))
+        self.ids[:1].copy_(self.out_id)
+        self.hist.index_copy_(0, self.cnt, self.out_id)
+        self.pos_dev += 1
+        self.cnt += 1

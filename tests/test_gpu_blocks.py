@@ -59,6 +59,27 @@ def test_ffn_decode_one_launch_equals_steps(gpu, oracle, D, I):
         assert same_bits(y1, oracle.matmul_q_s(h, dq, ds))
 
 
+@pytest.mark.parametrize("D,I,act", [(3840, 1536, 1), (2560, 5000, 0), (1024, 3072, 1), (4096, 520, 0), (48, 40, 1)])
+def test_ffn_decode_gate_up_in_one_launch(gpu, oracle, D, I, act):
+    """One token, int8 matrices, the blocks the one-launch kernel above does not take (tanh-GeLU, or sizes beyond it):
+    gate, up and the activation run as one launch (q8_gateup_kernel), then the down product.  The output equals the
+    step-by-step path bit for bit, and -- with SiLU -- the oracle bit for bit (GeLU: see test_ffn_q8_and_q4r4)."""
+    rng = np.random.default_rng(D + I + act)
+    mk = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32))
+    (gq, gs), (uq, us), (dq, ds) = mk(I, D), mk(I, D), mk(D, I)
+    G, U, Dn = gpu.Mat.i8(gq, gs), gpu.Mat.i8(uq, us), gpu.Mat.i8(dq, ds)
+    x = rng.standard_normal((1, D)).astype(np.float32)
+    prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
+    y1 = gpu.dense_ffn(G, U, Dn, x, act=act)
+    gpu.lib().moty_cuda_set_moe_fast_path(0)
+    y0 = gpu.dense_ffn(G, U, Dn, x, act=act)
+    gpu.lib().moty_cuda_set_moe_fast_path(prev)
+    assert same_bits(y1, y0)
+    gx, ux = oracle.matmul_q_s(x, gq, gs), oracle.matmul_q_s(x, uq, us)
+    yo = oracle.matmul_q_s(oracle.silu_mul(gx, ux) if act == 0 else oracle.gelu_mul(gx, ux), dq, ds)
+    assert same_bits(y1, yo) if act == 0 else close(y1, yo, 2e-3)
+
+
 def test_attn_core_golden(gpu):
     """Attention core on the GPU against the vectors composed from the reference's functions: three calls per case
     (a prompt of 5, one decode step, 3 more tokens) on one cache; f32 and int8 KV, QK-norm on and off, partial rotary.

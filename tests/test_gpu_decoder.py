@@ -1,5 +1,6 @@
-"""A whole decoder step on the GPU (moty_b200.decoder.DenseDecoder, composed like engines/qwen.c:681-740) against the
-same composition of the CPU oracle's functions: a prompt, then greedy decoding, on a small Qwen3-shaped model."""
+"""A whole decoder step on the GPU (moty_b200.decoder.DenseDecoder, composed like engines/qwen.c:681-740, and
+GemmaDecoder, composed like engines/gemma.c:453-497) against the same composition of the CPU oracle's functions: a
+prompt, then greedy decoding, on small models of those shapes."""
 import numpy as np
 import pytest
 
@@ -193,4 +194,96 @@ def test_greedy_tokens_match_with_routed_layers(gpu, oracle):
         got.append(dec.step([got[-1]], 6 + i)); want.append(ostep([want[-1]], 6 + i))
     assert got == want
     assert dec.greedy_graph(got[0], 6, 12) == got[1:]
+    dec.close()
+
+
+@pytest.mark.parametrize("D", [3840, 1000, 5000])
+def test_sandwich_norm_step(gpu, D):
+    """x += rmsnorm(t) * g1, out = rmsnorm(x) * g2 in one launch (moty_cuda_normadd_rmsnorm_dev) against the three
+    entries one after the other: the same bits (rows held in registers up to 4096 values, re-read beyond)."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(D)
+    S = 3
+    x, t = (rng.standard_normal((S, D)).astype(np.float32) for _ in range(2))
+    g1, g2 = (rng.uniform(0.5, 1.5, D).astype(np.float32) for _ in range(2))
+    dx, dt, dg1, dg2 = (torch.from_numpy(a).cuda() for a in (x, t, g1, g2))
+    x1, x2, x3 = dx.clone(), dx.clone(), dx.clone()
+    tn, o1, o2 = torch.empty_like(dx), torch.empty_like(dx), torch.empty_like(dx)
+    torch.cuda.synchronize()
+    sh = C.c_void_p(gpu.stream_handle(torch.cuda.current_stream()))
+    L, P, eps = gpu.lib(), (lambda a: C.c_void_p(a.data_ptr())), C.c_float(1e-6)
+    assert L.moty_cuda_rmsnorm_dev(P(tn), P(dt), P(dg1), S, D, eps, sh) == 0
+    assert L.moty_cuda_add_dev(P(x1), P(tn), C.c_longlong(S * D), sh) == 0
+    assert L.moty_cuda_rmsnorm_dev(P(o1), P(x1), P(dg2), S, D, eps, sh) == 0
+    assert L.moty_cuda_normadd_rmsnorm_dev(P(x2), P(dt), P(dg1), P(o2), P(dg2), S, D, eps, sh) == 0
+    assert L.moty_cuda_normadd_rmsnorm_dev(P(x3), P(dt), P(dg1), None, None, S, D, eps, sh) == 0      # without the second norm
+    torch.cuda.synchronize()
+    assert same_bits(x1.cpu().numpy(), x2.cpu().numpy()) and same_bits(o1.cpu().numpy(), o2.cpu().numpy())
+    assert same_bits(x1.cpu().numpy(), x3.cpu().numpy()) and same_bits(dt.cpu().numpy(), t)
+    ref = x + _rmsnorm(t, g1, 1e-6)
+    assert np.abs(x2.cpu().numpy() - ref).max() <= 4e-7 * np.abs(ref).max()
+
+
+def test_gemma_greedy_tokens_match_the_oracle(gpu, oracle):
+    """A 3-layer model shaped like the gemma engine's (hidden 256, 4 query heads; two sliding layers of 2 KV heads x 32
+    with window 8 and theta 1e4, one global layer of 1 KV head x 64, theta 1e6, 8 rotated pairs; GeGLU FFN 512; four
+    sandwich norms and q/k/v head norms with zero-centred weights; embedding rows scaled by sqrt(hidden)): a prompt of
+    12 tokens (longer than the window) and 20 greedy steps give the oracle's token ids; logits at 3e-2 of their
+    magnitude for the reason given for the qwen-shaped model above (the GeLU adds ~1e-7 of its own: tanhf)."""
+    from moty_b200.decoder import GemmaDecoder, GemmaLayer
+    from oracle import AttnCache
+    rng = np.random.default_rng(11)
+    H, D, I, V = 4, 256, 512, 900
+    geo = [dict(KV=2, hd=32, theta=1e4, window=8, rot=16), dict(KV=2, hd=32, theta=1e4, window=8, rot=16),
+           dict(KV=1, hd=64, theta=1e6, window=0, rot=8)]
+    mk = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.0005, 0.0015, O).astype(np.float32))
+    w = lambda n: rng.uniform(-0.2, 0.2, n).astype(np.float32)             # zero-centred norm weights
+    mult = lambda a: (np.float32(1) + a).astype(np.float32)
+    hq, hs = mk(V, D); hs = (hs * 20 / 16).astype(np.float32)               # rows of unit size after the sqrt(256) scale
+    fin = w(D)
+    max_t = 48
+    Ls, layers, caches = [], [], []
+    for g in geo:
+        qw, kw = H * g["hd"], g["KV"] * g["hd"]
+        l = dict(q=mk(qw, D), k=mk(kw, D), v=mk(kw, D), o=mk(D, qw), gate=mk(I, D), up=mk(I, D), down=mk(D, I),
+                 ln=[w(D) for _ in range(4)], qn=w(g["hd"]), kn=w(g["hd"]), vn=w(g["hd"]))
+        Ls.append(l)
+        fuse = gpu.Mat.i8(np.concatenate([l[m][0] for m in "qkv"]), np.concatenate([l[m][1] for m in "qkv"]))
+        layers.append(GemmaLayer(*(gpu.Mat.i8(*l[m]) for m in ("q", "k", "v", "o", "gate", "up", "down")), *(mult(a) for a in l["ln"]),
+                                 mult(l["qn"]), mult(l["kn"]), mult(l["vn"]), n_kv_heads=g["KV"], head_dim=g["hd"], theta=g["theta"],
+                                 window=g["window"], rot=g["rot"], qkv=fuse if len(layers) != 1 else None))
+        caches.append(AttnCache(H, g["KV"], g["hd"], max_t, theta=g["theta"], eps=1e-6, rot=g["rot"], qn=l["qn"], kn=l["kn"], vn=l["vn"],
+                                gemma=True, window=g["window"]))
+    dec = GemmaDecoder(layers, gpu.Mat.i8(hq, hs), mult(fin), H, max_t)
+    es = np.sqrt(np.float32(D))
+
+    def ostep(ids, pos):
+        x = np.stack([(hs[i] * es) * hq[i].astype(np.float32) for i in ids]).astype(np.float32)
+        for l, cache in zip(Ls, caches):
+            n = _rmsnorm(x, mult(l["ln"][0]), 1e-6)
+            q, k, v = (oracle.matmul_q_s(n, *l[m]) for m in "qkv")
+            t = oracle.matmul_q_s(oracle.attn_core(q, k, v, pos, cache), *l["o"])
+            x = x + _rmsnorm(t, mult(l["ln"][1]), 1e-6)
+            n = _rmsnorm(x, mult(l["ln"][2]), 1e-6)
+            h = oracle.gelu_mul(oracle.matmul_q_s(n, *l["gate"]), oracle.matmul_q_s(n, *l["up"]))
+            x = x + _rmsnorm(oracle.matmul_q_s(h, *l["down"]), mult(l["ln"][3]), 1e-6)
+        lg = oracle.matmul_q_s(_rmsnorm(x[-1:], mult(fin), 1e-6), hq, hs)[0]
+        return oracle.argmax(lg), lg
+
+    prompt = rng.integers(0, V, 12).astype(np.int32)
+    tg, lg = dec.step(prompt, 0, want_logits=True)
+    to, lo = ostep(prompt, 0)
+    assert np.abs(lg - lo).max() <= 3e-2 * np.abs(lo).max()
+    assert tg == to
+    got, want, pos = [tg], [to], len(prompt)
+    for _ in range(20):
+        tg, lg = dec.step([got[-1]], pos, want_logits=True)
+        to, lo = ostep([want[-1]], pos)
+        assert np.abs(lg - lo).max() <= 3e-2 * np.abs(lo).max(), pos
+        got.append(tg); want.append(to); pos += 1
+    assert got == want
+    assert dec.greedy_graph(got[0], len(prompt), 20) == got[1:]
+    # the blocked prefill (blocks of 5 tokens) reaches the same first token
+    assert dec.prefill(prompt, 0, block=5) == got[0]
     dec.close()
