@@ -262,7 +262,10 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
  * launches.  Same arithmetic, same bits as the general grouped path that batches use.
  * This switch lets a test run them all and compare: 1 = best decode path (default),
  * 2 = the split decode path (separate router / gate-up / down launches, both
- * formats), 0 = the grouped path.  Returns the previous value; no reference
+ * formats), 0 = the grouped path, 3 = as 1, except that a one-token dense int8
+ * SiLU FFN block (moty_cuda_ffn[_dev]) runs in the cooperative kernel as a
+ * one-expert layer instead of its default two chained launches (gate + up +
+ * activation, then down).  Returns the previous value; no reference
  * counterpart.  If the fused kernel's barrier wait ever expires (a fraction of a
  * second), the host-pointer entries return MOTY_CUDA_EKERNEL. */
 int moty_cuda_set_moe_fast_path(int on);

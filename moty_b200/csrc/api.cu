@@ -1019,7 +1019,8 @@ extern "C" int moty_cuda_pack_q4r4(const float *w, int O, int I, uint8_t *q4, ui
 // ---------------------------------------------------------------------------
 // dense FFN
 // ---------------------------------------------------------------------------
-static int g_moe_fast = 1;      // 1: one-launch decode kernels; 2: the split decode path; 0: general path only
+static int g_moe_fast = 1;      // 1: best decode paths; 2: the split decode path; 3: as 1, dense FFN in the cooperative kernel; 0: general path only
+static inline bool moe_fast_one() { return g_moe_fast == 1 || g_moe_fast == 3; }
 static int g_moe_tc = 1;        // int8 batches: 1 = grouped products on tcgen05 where the experts see >= 8 rows each; 0 = mma.sync tiles
 
 static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,
@@ -1031,10 +1032,22 @@ static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
     if (act != MOTY_ACT_SILU && act != MOTY_ACT_GELU_TANH) return moty_set_error(MOTY_CUDA_EARG, "ffn: activation %d", act);
     size_t hb = (size_t)S * I * 4;
     CKR(moty_grow(c, &c->g, hb));
-    // Decode with int8 matrices and SiLU: the block is the MoE decode block with one expert of weight 1 (softmax of a
-    // single logit is exp(0)/exp(0) = 1 and 1 * h = h exactly), so the one-launch kernel takes it: gate/up rows, a
-    // grid barrier, the down rows -- same quantizers, same (scale * sx) * acc, same SiLU expression as the steps below.
-    if (S == 1 && act == MOTY_ACT_SILU && g_moe_fast == 1 && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 &&
+    // One token, int8 gate and up with rows of at most 4096 values: gate, up and the activation in one launch, then the
+    // down product, both chained to their neighbours by programmatic dependent launch.  Same bits as the four steps below.
+    // (Measured against the one-launch cooperative kernel further down: 9.6 against 12.0 us for the 1024/3072 block, 9.9
+    // against 12.3 us for 2048/4096, 1406 against 1257 tok/s over a whole Qwen3-0.6B-shaped decode -- a cooperative launch
+    // cannot be chained, so it pays its whole launch latency and the next kernel's as well.)
+    if (S == 1 && (g_moe_fast == 1 || g_moe_fast == 2) && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 && q8_gateup_supported(I, D) &&
+        (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+        CKR(launch_q8_gateup((const int8_t *)gate->codes, (const float *)gate->scales, (const int8_t *)up->codes, (const float *)up->scales,
+                             x, (float *)c->g.p, I, D, act, c->sms, st));
+        return mat_apply_on(c, down, out, (const float *)c->g.p, S, nullptr, st);
+    }
+    // Kept as a cross-check (set_moe_fast_path(3)): with int8 matrices and SiLU the block is the MoE decode block with one
+    // expert of weight 1 (softmax of a single logit is exp(0)/exp(0) = 1 and 1 * h = h exactly), so the one-launch
+    // cooperative kernel takes it: gate/up rows, a grid barrier, the down rows -- same quantizers, same (scale * sx) * acc,
+    // same SiLU expression as the steps below.
+    if (S == 1 && act == MOTY_ACT_SILU && g_moe_fast == 3 && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 &&
         down->fmt == MOTY_WF_I8 && moe_decode_fused_q8_supported(1, 1, I, D) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
         CKR(moty_grow_zero(c, &c->ffn1, 64));               // [0] the single logit (0), [4] index out, [8] weight out
         char *z = (char *)c->ffn1.p;
@@ -1043,14 +1056,6 @@ static int ffn_on(DevCtx *c, MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *do
                                           (const float *)gate->scales, (const float *)up->scales, (const float *)down->scales,
                                           0, 0, 0, 0, x, (float *)c->g.p, out, nullptr, 1, I, D, 0, 1,
                                           reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1, c->sms, st);
-    }
-    // The other one-token int8 blocks (tanh-GeLU, or SiLU beyond that kernel's sizes) with rows of at most 4096 values:
-    // gate, up and the activation in one launch, then the down product.  Same bits as the four steps below.
-    if (S == 1 && g_moe_fast == 1 && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 && q8_gateup_supported(I, D) &&
-        (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
-        CKR(launch_q8_gateup((const int8_t *)gate->codes, (const float *)gate->scales, (const int8_t *)up->codes, (const float *)up->scales,
-                             x, (float *)c->g.p, I, D, act, c->sms, st));
-        return mat_apply_on(c, down, out, (const float *)c->g.p, S, nullptr, st);
     }
     CKR(moty_grow(c, &c->u, hb));
     CKR(mat_apply_on(c, gate, (float *)c->g.p, x, S, nullptr, st));
@@ -1240,7 +1245,7 @@ extern "C" int moty_cuda_set_moe_batch_path(int tensor_core) {
 
 extern "C" int moty_cuda_set_moe_fast_path(int on) {
     int prev = g_moe_fast;
-    g_moe_fast = on < 0 ? 0 : (on > 2 ? 1 : on);
+    g_moe_fast = on < 0 ? 0 : (on > 3 ? 1 : on);
     return prev;
 }
 
@@ -1273,7 +1278,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         }
         // decode, int8 experts: router + gate/up + down in one cooperative launch
         // (the one-launch kernels carry the softmax gate; the sigmoid gate takes the router launch + the two streaming launches)
-        if (S == 1 && q8 && order == 0 && g_moe_fast == 1 && !m->sigmoid && moe_decode_fused_q8_supported(E, K, I, D) &&
+        if (S == 1 && q8 && order == 0 && moe_fast_one() && !m->sigmoid && moe_decode_fused_q8_supported(E, K, I, D) &&
             (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
             CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
             CKR(launch_moe_decode_fused_q8(logits, E, norm_topk, m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u,
@@ -1285,7 +1290,7 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;
         }
-        if (S == 1 && !q8 && order == 0 && g_moe_fast == 1 && !m->sigmoid && moe_decode_fused_q4_supported(E, K, I, D) &&
+        if (S == 1 && !q8 && order == 0 && moe_fast_one() && !m->sigmoid && moe_decode_fused_q4_supported(E, K, I, D) &&
             (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
             CKR(moty_grow(c, &c->hq, (size_t)K * I + 16));
             CKR(moty_grow(c, &c->hxs, (size_t)K * (I / 32) * 4));
@@ -1476,7 +1481,7 @@ extern "C" int moty_cuda_moe_d1_rows_dev(MotyCudaMoe *m, float *rows_dev, float 
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
     MOTY_USE_DEVICE(m->device);
-    if (g_moe_fast != 1) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev needs the one-launch decode path (set_moe_fast_path(1))");
+    if (!moe_fast_one()) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev needs the one-launch decode path (set_moe_fast_path(1))");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_rows_dev: x_dev must be 16-byte aligned");
     return moe_apply_on(c, m, out_dev, x_dev, 1, logits_dev, 0, norm_topk, idx_dev, w_dev, nullptr, pick_stream(c, stream), rows_dev);
 }
@@ -1489,7 +1494,7 @@ extern "C" int moty_cuda_moe_d1_peer_dev(MotyCudaMoe *m, float *out_dev, const f
     DevCtx *c = moty_ctx(m->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
     MOTY_USE_DEVICE(m->device);
-    if (g_moe_fast != 1) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev needs the one-launch decode path (set_moe_fast_path(1))");
+    if (!moe_fast_one()) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev needs the one-launch decode path (set_moe_fast_path(1))");
     if (reinterpret_cast<uintptr_t>(x_dev) & 15) return moty_set_error(MOTY_CUDA_EARG, "moe_d1_peer_dev: x_dev must be 16-byte aligned");
     cudaStream_t st = pick_stream(c, stream);
     float *tb[8]; unsigned *fl[8];

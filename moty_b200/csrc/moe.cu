@@ -10,6 +10,8 @@
 // Both expressions live in common.cuh (moty_silu_mul, moty_gelu_mul), f32 step by f32 step.
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) act_mul_kernel(float *__restrict__ g, const float *__restrict__ u, long long n, int act) {
+    pdl_trigger();
+    pdl_wait();
     long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     g[i] = act == MOTY_ACT_SILU ? moty_silu_mul(g[i], u[i]) : moty_gelu_mul(g[i], u[i]);
@@ -17,8 +19,7 @@ __global__ void __launch_bounds__(256) act_mul_kernel(float *__restrict__ g, con
 
 int launch_act_mul(float *g, const float *u, int64_t n, int act, cudaStream_t st) {
     if (n <= 0) return 0;
-    act_mul_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(g, u, n, act);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(act_mul_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, st, g, u, (long long)n, act));
     return 0;
 }
 
@@ -150,6 +151,8 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float *__restrict__ ou
     __shared__ int p_s[64];
     __shared__ float w_s[64];
     const int s = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (threadIdx.x < K) {
         const int k = ord[(size_t)s * K + threadIdx.x];
         p_s[threadIdx.x] = pos_of[(size_t)s * K + k];
@@ -176,8 +179,7 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(float *__restrict__ ou
 int launch_moe_combine(float *out, const float *h, const float *w, const int *pos_of, const int *ord,
                        int S, int K, int D, cudaStream_t st) {
     if (S <= 0) return 0;
-    moe_combine_kernel<<<S, 256, 0, st>>>(out, h, w, pos_of, ord, S, K, D);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(moe_combine_kernel, dim3(S), dim3(256), (size_t)0, st, out, h, w, pos_of, ord, S, K, D));
     return 0;
 }
 
@@ -190,6 +192,8 @@ __global__ void __launch_bounds__(256) moe_combine_sk_kernel(float *__restrict__
     __shared__ int ord[64];
     __shared__ float ws[64];
     const int s = blockIdx.x;
+    pdl_trigger();
+    pdl_wait();
     if (threadIdx.x == 0) {
         for (int k = 0; k < K; k++) ord[k] = k;
         if (order == 1) {
@@ -216,8 +220,7 @@ __global__ void __launch_bounds__(256) moe_combine_sk_kernel(float *__restrict__
 int launch_moe_combine_sk(float *out, const float *h, const float *w, const int *idx,
                           int S, int K, int D, int order, cudaStream_t st) {
     if (S <= 0) return 0;
-    moe_combine_sk_kernel<<<S, 256, 0, st>>>(out, h, w, idx, K, D, order);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(moe_combine_sk_kernel, dim3(S), dim3(256), (size_t)0, st, out, h, w, idx, K, D, order));
     return 0;
 }
 
@@ -293,6 +296,8 @@ int launch_moe_peer_combine(float *out, const float *table, const float *w, cons
 __global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__ W, const float *__restrict__ x,
                                                        float *__restrict__ y, int S, int I, int O) {
     int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    pdl_trigger();
+    pdl_wait();
     if (o >= O) return;
     for (int s = 0; s < S; s++) {
         float acc = 0.f;
@@ -305,6 +310,8 @@ __global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__
 
 int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st) {
     if (O <= 0 || S <= 0) return 0;
+    // a plain launch on purpose: chained programmatically it measured 2 % slower over a whole OLMoE-shaped decode step
+    // (1095 against 1116 tok/s replayed, same GPU, twice) -- the cooperative layer kernel that follows cannot be chained
     f32_rows_kernel<<<(O + 7) / 8, 256, 0, st>>>(W, x, y, S, I, O);
     CK(cudaGetLastError());
     return 0;

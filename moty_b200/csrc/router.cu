@@ -46,6 +46,8 @@ __device__ __forceinline__ void argmax_combine(float &bv, int &bi, float ov, int
 __global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restrict__ v, int n, float *pv, int *pi) {
     __shared__ float sv[8]; __shared__ int si[8];
     float bv = 0.f; int bi = -1;
+    pdl_trigger();
+    pdl_wait();
     for (int i = blockIdx.x * 256 + threadIdx.x; i < n; i += gridDim.x * 256) {
         float x = v[i];
         if (bi < 0 || x > bv) { bv = x; bi = i; }       // ascending i per thread: strict > keeps the first
@@ -66,6 +68,8 @@ __global__ void __launch_bounds__(256) argmax_part_kernel(const float *__restric
 __global__ void __launch_bounds__(256) argmax_final_kernel(const float *pv, const int *pi, int nparts, int *out) {
     __shared__ float sv[8]; __shared__ int si[8];
     float bv = 0.f; int bi = -1;
+    pdl_trigger();
+    pdl_wait();
     for (int i = threadIdx.x; i < nparts; i += 256) argmax_combine(bv, bi, pv[i], pi[i]);
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) {
@@ -84,9 +88,7 @@ __global__ void __launch_bounds__(256) argmax_final_kernel(const float *pv, cons
 int launch_argmax_scratch(const float *v, int n, int *out, float *pv, int *pi, cudaStream_t st) {
     if (n <= 0) return moty_set_error(MOTY_CUDA_EARG, "argmax: n=%d", n);
     int parts = (n + 255) / 256; if (parts > 256) parts = 256;
-    argmax_part_kernel<<<parts, 256, 0, st>>>(v, n, pv, pi);
-    CK(cudaGetLastError());
-    argmax_final_kernel<<<1, 256, 0, st>>>(pv, pi, parts, out);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(argmax_part_kernel, dim3(parts), dim3(256), (size_t)0, st, v, n, pv, pi));
+    CK(moty_launch_pdl(argmax_final_kernel, dim3(1), dim3(256), (size_t)0, st, (const float *)pv, (const int *)pi, parts, out));
     return 0;
 }

@@ -41,8 +41,9 @@ def test_ffn_q8_and_q4r4(gpu, oracle):
 
 @pytest.mark.parametrize("D,I", [(1024, 3072), (2048, 4096), (1008, 2064), (64, 48)])
 def test_ffn_decode_one_launch_equals_steps(gpu, oracle, D, I):
-    """One token, int8 matrices, SiLU: the block runs as a one-expert MoE decode block in a single launch.  Its output
-    equals the step-by-step path (gate, up, activation, down) and the oracle bit for bit."""
+    """One token, int8 matrices, SiLU: the default route (gate + up + activation in one launch, then the down product), the
+    one-launch cooperative kernel that runs the block as a one-expert MoE decode block (fast path 3) and the step-by-step
+    path (gate, up, activation, down) give the same bits, and those of the oracle."""
     rng = np.random.default_rng(D + I)
     mk = lambda O, K: (rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32))
     (gq, gs), (uq, us), (dq, ds) = mk(I, D), mk(I, D), mk(D, I)
@@ -51,17 +52,19 @@ def test_ffn_decode_one_launch_equals_steps(gpu, oracle, D, I):
         x = rng.standard_normal((1, D)).astype(np.float32)
         prev = gpu.lib().moty_cuda_set_moe_fast_path(1)
         y1 = gpu.dense_ffn(G, U, Dn, x)
+        gpu.lib().moty_cuda_set_moe_fast_path(3)
+        y3 = gpu.dense_ffn(G, U, Dn, x)
         gpu.lib().moty_cuda_set_moe_fast_path(0)
         y0 = gpu.dense_ffn(G, U, Dn, x)
         gpu.lib().moty_cuda_set_moe_fast_path(prev)
-        assert same_bits(y1, y0)
+        assert same_bits(y1, y0) and same_bits(y3, y0)
         h = oracle.silu_mul(oracle.matmul_q_s(x, gq, gs), oracle.matmul_q_s(x, uq, us))
         assert same_bits(y1, oracle.matmul_q_s(h, dq, ds))
 
 
 @pytest.mark.parametrize("D,I,act", [(3840, 1536, 1), (2560, 5000, 0), (1024, 3072, 1), (4096, 520, 0), (48, 40, 1)])
 def test_ffn_decode_gate_up_in_one_launch(gpu, oracle, D, I, act):
-    """One token, int8 matrices, the blocks the one-launch kernel above does not take (tanh-GeLU, or sizes beyond it):
+    """One token, int8 matrices, tanh-GeLU and SiLU, sizes up to rows of 4096 values (the gemma block's 3840 among them):
     gate, up and the activation run as one launch (q8_gateup_kernel), then the down product.  The output equals the
     step-by-step path bit for bit, and -- with SiLU -- the oracle bit for bit (GeLU: see test_ffn_q8_and_q4r4)."""
     rng = np.random.default_rng(D + I + act)
