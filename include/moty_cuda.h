@@ -257,17 +257,20 @@ int moty_cuda_moe_apply_dev(MotyCudaMoe *m, float *out_dev, const float *x_dev, 
                             int *idx_dev, float *w_dev, void *stream);
 
 /* One token through a routed layer normally takes a decode path that streams the
- * selected experts once: for int8 experts ONE cooperative launch (router, gate/up,
- * a bounded grid barrier, down); for Q4R4 experts a router launch and two streaming
- * launches.  Same arithmetic, same bits as the general grouped path that batches use.
- * This switch lets a test run them all and compare: 1 = best decode path (default),
- * 2 = the split decode path (separate router / gate-up / down launches, both
- * formats), 0 = the grouped path, 3 = as 1, except that a one-token dense int8
- * SiLU FFN block (moty_cuda_ffn[_dev]) runs in the cooperative kernel as a
- * one-expert layer instead of its default two chained launches (gate + up +
- * activation, then down).  Returns the previous value; no reference
- * counterpart.  If the fused kernel's barrier wait ever expires (a fraction of a
- * second), the host-pointer entries return MOTY_CUDA_EKERNEL. */
+ * selected experts once.  int8 experts with the softmax gate: two launches chained by
+ * programmatic dependent launch (route + gate/up + SiLU, then down + ordered sum);
+ * the expert-parallel decode entries below use ONE cooperative launch instead (router,
+ * gate/up, a bounded grid barrier, down), which also holds their exchange.  Q4R4
+ * experts: one cooperative launch.  Same arithmetic, same bits as the general grouped
+ * path that batches use.  This switch lets a test run them all and compare:
+ * 1 = best decode path (default), 2 = the split decode path (separate router /
+ * gate-up / down launches, both formats), 0 = the grouped path, 3 = as 1 with the
+ * cooperative kernel wherever one exists: int8 decode tokens, and a one-token dense
+ * int8 SiLU FFN block (moty_cuda_ffn[_dev]) run as a one-expert layer instead of its
+ * default two chained launches (gate + up + activation, then down).  Returns the
+ * previous value; no reference counterpart.  If a cooperative kernel's barrier wait
+ * ever expires (a fraction of a second), the host-pointer entries return
+ * MOTY_CUDA_EKERNEL. */
 int moty_cuda_set_moe_fast_path(int on);
 /* Batches through int8 experts (moty_nn_moe_topk_batch, nn/moe.c:159-205) run their grouped products on the tensor
  * cores (tcgen05, gate+up+SiLU in one pass) when the experts see 8 or more routed rows each on average, else on

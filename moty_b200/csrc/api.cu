@@ -1276,7 +1276,22 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
             CKR(mat_apply_on(c, m->router, m->logits, x, S, nullptr, st));
             logits = m->logits;
         }
-        // decode, int8 experts: router + gate/up + down in one cooperative launch
+        // decode, int8 experts, softmax gate, nothing to exchange: two chained launches -- route + gate/up + SiLU, then
+        // down + ordered sum.  (Measured against the one-launch cooperative kernel below, which cannot be chained to its
+        // neighbours by programmatic dependent launch: see the dense FFN above.)
+        if (S == 1 && q8 && order == 0 && g_moe_fast == 1 && !m->sigmoid && !rows && !npeer && E <= 2048 &&
+            moe_decode_q8_supported(K, I, D) && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+            CKR(moty_grow(c, &c->g, (size_t)K * I * 4));
+            CKR(launch_moe_decode_q8(m->idx, m->w, (const int8_t *)m->g, (const int8_t *)m->u, (const int8_t *)m->d,
+                                     (const float *)m->gs, (const float *)m->us, (const float *)m->ds,
+                                     m->gcb, m->gsb / 4, m->dcb, m->dsb / 4, x, (float *)c->g.p, out,
+                                     K, I, D, m->e_lo, m->e_hi, c->sms, st, logits, E, norm_topk));
+            if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
+            return 0;
+        }
+        // the same in one cooperative launch (router, gate/up, bounded grid barrier, down): the expert-parallel decode
+        // routes (row table, peer tables) live in this kernel, and set_moe_fast_path(3) sends every decode token here
         // (the one-launch kernels carry the softmax gate; the sigmoid gate takes the router launch + the two streaming launches)
         if (S == 1 && q8 && order == 0 && moe_fast_one() && !m->sigmoid && moe_decode_fused_q8_supported(E, K, I, D) &&
             (reinterpret_cast<uintptr_t>(x) & 15) == 0) {

@@ -310,8 +310,9 @@ __global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__
 
 int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int O, cudaStream_t st) {
     if (O <= 0 || S <= 0) return 0;
-    // a plain launch on purpose: chained programmatically it measured 2 % slower over a whole OLMoE-shaped decode step
-    // (1095 against 1116 tok/s replayed, same GPU, twice) -- the cooperative layer kernel that follows cannot be chained
+    // a plain launch on purpose: chained programmatically it measured slower over a whole OLMoE-shaped decode step, with
+    // the cooperative layer kernel after it (1095 against 1116 tok/s replayed) and with the two chained layer launches
+    // (1129 against 1217; same GPU, twice each)
     f32_rows_kernel<<<(O + 7) / 8, 256, 0, st>>>(W, x, y, S, I, O);
     CK(cudaGetLastError());
     return 0;

@@ -31,7 +31,10 @@ bool moe_decode_q8_supported(int K, int I, int D);
 int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const int8_t *u, const int8_t *d,
                          const float *gs, const float *us, const float *ds, size_t gstride, size_t gsstride,
                          size_t dstride, size_t dsstride, const float *x, float *h, float *out,
-                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st);
+                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st,
+                         const float *logits = nullptr, int E = 0, int norm_topk = 0);   // logits given (E <= 2048): the first
+                                                                                         // kernel routes the token itself and
+                                                                                         // leaves the selections in idx / w
 
 // ---- moe_decode_q4.cu: the same for Q4R4 experts ----
 bool moe_decode_q4_supported(int K, int I, int D);

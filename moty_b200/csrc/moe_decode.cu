@@ -15,6 +15,7 @@
 // contribute nothing to out.
 #include "kernels.cuh"
 #include "moe.cuh"
+#include "route.cuh"
 
 namespace {
 
@@ -36,6 +37,11 @@ __device__ __forceinline__ void reduce_multi_d(int (&v)[N], int lane) {
 
 struct MoeDecArgs {
     const int *idx; const float *w;               // routing of the one token: [K]
+    // kernel A may route the token itself (softmax gate; runtime/moecache.c:97-111): logits [E] -> every CTA's warp 0
+    // forms the K selections in shared memory (redundantly: 64-128 logits) while the other warps take the maximum of x,
+    // and CTA 0 leaves them in idx_out / w_out ( = idx / w) for kernel B.  logits == nullptr: idx / w were written by a
+    // router launch before.
+    const float *logits; int E, norm_topk; int *idx_out; float *w_out;
     const int8_t *g, *u, *d; const float *gs, *us, *ds;   // expert slabs (local experts only)
     size_t gstride, gsstride, dstride, dsstride;  // per expert, in elements
     const float *x; float *h; float *out;         // x [D], h [K][I] scratch, out [D]
@@ -49,11 +55,14 @@ __global__ void __launch_bounds__(256, (LPR <= 2 ? 4 : 2)) moe_dec_gateup_kernel
     extern __shared__ int4 smem4[];
     __shared__ float red[8];
     __shared__ float sx_s;
+    __shared__ int idx_s[64];
+    __shared__ float w_s[64];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int D = a.D, D16 = D / 16, I = a.I;
     constexpr int R = 2;
     const int nrg = (I + R - 1) / R, nunits = a.K * nrg;
     const int nwarps = gridDim.x * 8;
+    const bool routing = a.logits != nullptr;
 
     int4 wg[R][LPR], wu[R][LPR];
     float sc_g = 0.f, sc_u = 0.f;
@@ -62,7 +71,7 @@ __global__ void __launch_bounds__(256, (LPR <= 2 ? 4 : 2)) moe_dec_gateup_kernel
     const int my = lane >> 3, my_r = my & 1;
     auto issue = [&](int t) {
         const int k = t / nrg, rg = t - k * nrg;
-        const int e = a.idx[k];
+        const int e = routing ? idx_s[k] : a.idx[k];
         local = e >= a.e_lo && e < a.e_hi;
         if (!local) return;
         const size_t le = (size_t)(e - a.e_lo);
@@ -84,20 +93,30 @@ __global__ void __launch_bounds__(256, (LPR <= 2 ? 4 : 2)) moe_dec_gateup_kernel
     };
     int t0 = blockIdx.x * 8 + warp;
     pdl_trigger();
-    pdl_wait();                                   // the routing and x come from earlier kernels
-    if (t0 < nunits) issue(t0);
+    pdl_wait();                                   // the logits (or the routing) and x come from earlier kernels
+    if (!routing && t0 < nunits) issue(t0);
 
-    // x -> int8 codes in shared memory (moty_hw_qrow_i8, hw/hw_quant.h:9-16)
+    // x -> int8 codes in shared memory (moty_hw_qrow_i8, hw/hw_quant.h:9-16); with routing inside, warp 0 routes meanwhile
     {
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         float amax = 0.f;
-        for (int i = threadIdx.x; i < D / 4; i += 256) {
-            float4 v = x4[i];
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+        if (routing && warp == 0) {
+            float *p_s = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem4) + (((size_t)D + 15) & ~(size_t)15));
+            route_row_warp(a.logits, a.E, a.K, p_s, 1, a.norm_topk, lane, idx_s, w_s, nullptr);
+        } else {
+            const int first = routing ? threadIdx.x - 32 : threadIdx.x, step = routing ? 224 : 256;
+            for (int i = first; i < D / 4; i += step) {
+                float4 v = x4[i];
+                amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            }
+            amax = warp_max_f32(amax);
         }
-        amax = warp_max_f32(amax);
         if (lane == 0) red[warp] = amax;
         __syncthreads();
+        if (routing) {
+            if (t0 < nunits) issue(t0);
+            if (blockIdx.x == 0 && threadIdx.x < a.K) { a.idx_out[threadIdx.x] = idx_s[threadIdx.x]; a.w_out[threadIdx.x] = w_s[threadIdx.x]; }
+        }
         amax = red[0];
 #pragma unroll
         for (int i = 1; i < 8; i++) amax = fmaxf(amax, red[i]);
@@ -256,9 +275,12 @@ bool moe_decode_q8_supported(int K, int I, int D) {
 int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const int8_t *u, const int8_t *d,
                          const float *gs, const float *us, const float *ds, size_t gstride, size_t gsstride,
                          size_t dstride, size_t dsstride, const float *x, float *h, float *out,
-                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st) {
+                         int K, int I, int D, int e_lo, int e_hi, int sms, cudaStream_t st,
+                         const float *logits, int E, int norm_topk) {
     if (!moe_decode_q8_supported(K, I, D)) return moty_set_error(MOTY_CUDA_EARG, "moe_decode: K=%d I=%d D=%d", K, I, D);
+    if (logits && (E < K || E > 2048)) return moty_set_error(MOTY_CUDA_EARG, "moe_decode: routing inside wants K <= E <= 2048 (E=%d)", E);
     MoeDecArgs a;
+    a.logits = logits; a.E = E; a.norm_topk = norm_topk; a.idx_out = const_cast<int *>(idx); a.w_out = const_cast<float *>(w);
     a.idx = idx; a.w = w; a.g = g; a.u = u; a.d = d; a.gs = gs; a.us = us; a.ds = ds;
     a.gstride = gstride; a.gsstride = gsstride; a.dstride = dstride; a.dsstride = dsstride;
     a.x = x; a.h = h; a.out = out; a.K = K; a.I = I; a.D = D; a.e_lo = e_lo; a.e_hi = e_hi;
@@ -266,7 +288,7 @@ int launch_moe_decode_q8(const int *idx, const float *w, const int8_t *g, const 
         int units = K * ((I + 1) / 2);
         int ctas = sms * 4; if (ctas > (units + 7) / 8) ctas = (units + 7) / 8;
         int lpr = (D / 16 + 31) / 32;
-        size_t smem = (size_t)D;
+        size_t smem = logits ? (((size_t)D + 15) & ~(size_t)15) + (size_t)E * 4 : (size_t)D;
         if (lpr <= 2) CK(moty_launch_pdl(moe_dec_gateup_kernel<2>, dim3(ctas), dim3(256), smem, st, a));
         else CK(moty_launch_pdl(moe_dec_gateup_kernel<4>, dim3(ctas), dim3(256), smem, st, a));
     }

@@ -273,9 +273,10 @@ def test_expert_shards_sum_to_the_whole(gpu, oracle):
 @pytest.mark.parametrize("E,K,I,D,lo,hi", [(64, 8, 1024, 2048, 0, 64), (16, 4, 96, 160, 0, 16), (16, 4, 96, 160, 4, 12),
                                            (8, 8, 48, 2048, 0, 8), (32, 6, 2064, 512, 0, 32), (12, 10, 4096, 64, 0, 12)])
 def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, hi):
-    """The fused one-launch decode path (1), the split decode path (2) and the grouped path (0) are
-    the same arithmetic: bit-identical, also on an expert shard (non-resident experts contribute
-    nothing), and repeated calls keep the fused kernel's grid barrier consistent."""
+    """The default decode path (1: route + gate/up, then down, two chained launches), the split decode path (2: a router
+    launch first), the one-launch cooperative kernel (3) and the grouped path (0) are the same arithmetic: bit-identical,
+    also on an expert shard (non-resident experts contribute nothing), and repeated calls keep the cooperative kernel's
+    grid barrier consistent."""
     from oracle import Experts
     rng = np.random.default_rng(E * K + I + lo)
     g = rng.integers(-127, 128, (E, I, D), dtype=np.int8); u = rng.integers(-127, 128, (E, I, D), dtype=np.int8)
@@ -292,11 +293,14 @@ def test_moe_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, lo, h
         fast = m.d1(x, logits); fast_ol = m.olmoe(x, logits, 0)
         gpu.lib().moty_cuda_set_moe_fast_path(2)
         split = m.d1(x, logits); split_ol = m.olmoe(x, logits, 0)
+        gpu.lib().moty_cuda_set_moe_fast_path(3)
+        coop = m.d1(x, logits); coop_ol = m.olmoe(x, logits, 0)
         gpu.lib().moty_cuda_set_moe_fast_path(0)
         slow = m.d1(x, logits); slow_ol = m.olmoe(x, logits, 0)
         gpu.lib().moty_cuda_set_moe_fast_path(prev)
         assert same_bits(fast, slow) and same_bits(fast_ol, slow_ol)
         assert same_bits(split, slow) and same_bits(split_ol, slow_ol)
+        assert same_bits(coop, slow) and same_bits(coop_ol, slow_ol)
     if (lo, hi) == (0, E):
         want = oracle.moe_d1(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0]
         assert same_bits(fast, want)
