@@ -296,8 +296,6 @@ int launch_moe_peer_combine(float *out, const float *table, const float *w, cons
 __global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__ W, const float *__restrict__ x,
                                                        float *__restrict__ y, int S, int I, int O) {
     int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    pdl_trigger();
-    pdl_wait();
     if (o >= O) return;
     for (int s = 0; s < S; s++) {
         float acc = 0.f;
