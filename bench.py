@@ -297,7 +297,7 @@ def run_engine_qwen(ngen=128):
         shutil.rmtree(tmp, ignore_errors=True)
 
 
-def run_decode_qwen(torch, mb, rng, ngen, device):
+def run_decode_qwen(torch, mb, rng, ngen, device, fold=None):
     """A whole greedy decode of the configs[0] shape (Qwen3-0.6B: 28 layers, hidden 1024, 16/8 heads of 128, FFN 3072,
     vocabulary 151936, tied int8 head) on synthetic int8 weights: a 64-token prompt, then ngen tokens launched entry by
     entry from Python, then the same tokens as a replayed CUDA graph of one decode step."""
@@ -314,7 +314,7 @@ def run_decode_qwen(torch, mb, rng, ngen, device):
                           mk(I, D), mk(I, D), mk(D, I), one(D), one(D), one(hd), one(hd), qkv=qkv)
     layers = [layer() for _ in range(NL)]
     head = mb.Mat.i8(rng.integers(-127, 128, (V, D), dtype=np.int8), rng.uniform(0.005, 0.015, V).astype(np.float32), device=device)
-    dec = DenseDecoder(layers, head, one(D), H, KV, hd, PROMPT + ngen + 8, max_S=PROMPT, device=device)
+    dec = DenseDecoder(layers, head, one(D), H, KV, hd, PROMPT + ngen + 8, max_S=PROMPT, device=device, fold_addnorm=fold)
     prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
     dec.step(prompt, 0); dec.step([1], PROMPT)                       # warm-up (allocations, attributes)
     torch.cuda.synchronize(); t0 = time.perf_counter()
@@ -1029,7 +1029,8 @@ def run_case(args):
         dec.close()
         return
     if parts[0] == "decode":                            # decode:qwen3-0.6b[:NGEN] -- configs[0] shape, synthetic int8 weights
-        res = run_decode_qwen(torch, mb, rng, int(parts[2]) if len(parts) > 2 else 128, 0)
+        fold = {"fold": True, "nofold": False}.get(parts[3]) if len(parts) > 3 else None      # decode:qwen3-0.6b:NGEN[:fold|nofold]
+        res = run_decode_qwen(torch, mb, rng, int(parts[2]) if len(parts) > 2 else 128, 0, fold)
         print(json.dumps({"case": args.case, **res}), flush=True)
         return
     if parts[0] == "attn":                              # attn:S:POS:H:KV:hd[:kv8][:posdev] -- S tokens at position POS of one layer's cache

@@ -342,14 +342,24 @@ int moty_cuda_add_rmsnorm_dev(float *x_dev, const float *t_dev, float *out_dev, 
  * pass 1 + w for a zero-centred checkpoint (gnorm_row, engines/gemma.c:279-284).  t is left as it was. */
 int moty_cuda_normadd_rmsnorm_dev(float *x_dev, const float *t_dev, const float *g_t_dev, float *out_dev, const float *g_x_dev,
                                   int S, int D, float eps, void *stream);
-/* The same add and norm folded into the decode product that consumes them (one launch instead of two):
- * y = W * rmsnorm(x + t) with gains gain_dev, and xout = x + t (xout_dev must overlap neither x_dev nor t_dev: one CTA
- * writes xout while every other still reads x and t; MOTY_CUDA_EARG otherwise).
- * One row; MOTY_WF_I8 matrices with I <= 4096, I a multiple of 16 (mat_addnorm_supported says whether a matrix
- * qualifies).  Same bits as add_rmsnorm_dev followed by mat_apply_dev. */
+/* The same residual step and norm folded into the one-token product or FFN block that consumes them (one launch less
+ * per fold; every CTA of the consumer forms the row for itself):
+ *   xout = x + t                      when g_t_dev is NULL   (add_rmsnorm_dev),
+ *   xout = x + rmsnorm(t) * g_t       otherwise              (normadd_rmsnorm_dev, gemma's sandwich),
+ *   row  = rmsnorm(xout) * g_x,   then   y = W * row   (mat_apply_resnorm_dev)   or   out = FFN(row)   (ffn_resnorm_dev).
+ * xout_dev must overlap neither x_dev nor t_dev (one CTA writes xout while every other still reads x and t;
+ * MOTY_CUDA_EARG otherwise); x_dev and t_dev 16-byte aligned.  MOTY_WF_I8 matrices whose rows (I of W; D of gate/up)
+ * are a multiple of 16 and at most 4096 values: mat_addnorm_supported / ffn_resnorm_supported say whether they qualify.
+ * Same bits as the separate entries one after the other.  mat_apply_addnorm_dev is mat_apply_resnorm_dev without g_t. */
 int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w);
 int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
                                     float *xout_dev, const float *gain_dev, float eps, void *stream);
+int moty_cuda_mat_apply_resnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
+                                    const float *g_t_dev, float *xout_dev, const float *g_x_dev, float eps, void *stream);
+int moty_cuda_ffn_resnorm_supported(const MotyCudaMat *gate, const MotyCudaMat *up);
+int moty_cuda_ffn_resnorm_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act, float *out_dev,
+                              const float *x_dev, const float *t_dev, const float *g_t_dev, float *xout_dev,
+                              const float *g_x_dev, float eps, void *stream);
 int moty_cuda_embed_rows_dev(MotyCudaMat *embed, float *out_dev, const int *ids_dev, int S, float scale, void *stream);
 
 /* ---- attention core between the projections --------------------------------

@@ -492,26 +492,33 @@ extern "C" int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w) {
     return w && w->fmt == MOTY_WF_I8 && w->I % 16 == 0 && w->I <= 4096;
 }
 
-extern "C" int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
-                                               float *xout_dev, const float *gain_dev, float eps, void *stream) {
-    if (!w || !y_dev || !x_dev || !t_dev || !xout_dev || !gain_dev)
-        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: null argument");
-    // CTA 0 writes xout while every other CTA still reads x and t to form its own copy of the row: xout must not
-    // overlap either of them
+// CTA 0 writes xout while every other CTA still reads x and t to form its own copy of the row: xout must not overlap either
+static bool resnorm_args_ok(const float *x, const float *t, const float *xout, int I) {
     auto overlaps = [&](const float *a) {
-        return reinterpret_cast<uintptr_t>(xout_dev) < reinterpret_cast<uintptr_t>(a + w->I) &&
-               reinterpret_cast<uintptr_t>(a) < reinterpret_cast<uintptr_t>(xout_dev + w->I);
+        return reinterpret_cast<uintptr_t>(xout) < reinterpret_cast<uintptr_t>(a + I) &&
+               reinterpret_cast<uintptr_t>(a) < reinterpret_cast<uintptr_t>(xout + I);
     };
-    if (!moty_cuda_mat_addnorm_supported(w) || overlaps(x_dev) || overlaps(t_dev) ||
-        ((reinterpret_cast<uintptr_t>(x_dev) | reinterpret_cast<uintptr_t>(t_dev)) & 15))
-        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_addnorm_dev: wants a MOTY_WF_I8 matrix with I <= 4096 (a multiple of 16), x and t "
+    return !overlaps(x) && !overlaps(t) && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(t)) & 15) == 0;
+}
+
+extern "C" int moty_cuda_mat_apply_resnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
+                                               const float *g_t_dev, float *xout_dev, const float *g_x_dev, float eps, void *stream) {
+    if (!w || !y_dev || !x_dev || !t_dev || !xout_dev || !g_x_dev)
+        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_resnorm_dev: null argument");
+    if (!moty_cuda_mat_addnorm_supported(w) || !resnorm_args_ok(x_dev, t_dev, xout_dev, w->I))
+        return moty_set_error(MOTY_CUDA_EARG, "mat_apply_resnorm_dev: wants a MOTY_WF_I8 matrix with I <= 4096 (a multiple of 16), x and t "
                               "16-byte aligned, and xout overlapping neither x nor t");
     DevCtx *c = moty_ctx(w->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w->device);
     MOTY_USE_DEVICE(w->device);
     return launch_q8_stream((const int8_t *)w->codes, (const float *)w->scales, x_dev, nullptr, nullptr, y_dev, nullptr,
                             1, w->I, w->O, c->ctr, (unsigned long long *)c->kcell.p, c->sms, pick_stream(c, stream),
-                            t_dev, gain_dev, xout_dev, eps);
+                            t_dev, g_x_dev, xout_dev, eps, g_t_dev);
+}
+
+extern "C" int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, const float *t_dev,
+                                               float *xout_dev, const float *gain_dev, float eps, void *stream) {
+    return moty_cuda_mat_apply_resnorm_dev(w, y_dev, x_dev, t_dev, nullptr, xout_dev, gain_dev, eps, stream);
 }
 
 // host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
@@ -1072,6 +1079,32 @@ extern "C" int moty_cuda_ffn_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat
     MOTY_USE_DEVICE(gate->device);
     if (S <= 0) return 0;
     return ffn_on(c, gate, up, down, act, out_dev, x_dev, S, pick_stream(c, stream));
+}
+
+extern "C" int moty_cuda_ffn_resnorm_supported(const MotyCudaMat *gate, const MotyCudaMat *up) {
+    return gate && up && gate->fmt == MOTY_WF_I8 && up->fmt == MOTY_WF_I8 && gate->O == up->O && gate->I == up->I &&
+           q8_gateup_supported(gate->O, gate->I);
+}
+
+extern "C" int moty_cuda_ffn_resnorm_dev(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act, float *out_dev,
+                                         const float *x_dev, const float *t_dev, const float *g_t_dev, float *xout_dev,
+                                         const float *g_x_dev, float eps, void *stream) {
+    if (!gate || !up || !down || !out_dev || !x_dev || !t_dev || !xout_dev || !g_x_dev)
+        return moty_set_error(MOTY_CUDA_EARG, "ffn_resnorm_dev: null argument");
+    if (!moty_cuda_ffn_resnorm_supported(gate, up) || down->O != gate->I || down->I != gate->O || !resnorm_args_ok(x_dev, t_dev, xout_dev, gate->I))
+        return moty_set_error(MOTY_CUDA_EARG, "ffn_resnorm_dev: wants MOTY_WF_I8 gate and up [I][D] with D <= 4096 (a multiple of 16), down [D][I], "
+                              "x and t 16-byte aligned, and xout overlapping neither x nor t");
+    if (gate->device != up->device || gate->device != down->device) return moty_set_error(MOTY_CUDA_EARG, "ffn_resnorm_dev: matrices on different devices");
+    if (act != MOTY_ACT_SILU && act != MOTY_ACT_GELU_TANH) return moty_set_error(MOTY_CUDA_EARG, "ffn_resnorm_dev: activation %d", act);
+    DevCtx *c = moty_ctx(gate->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", gate->device);
+    MOTY_USE_DEVICE(gate->device);
+    cudaStream_t st = pick_stream(c, stream);
+    const int I = gate->O, D = gate->I;
+    CKR(moty_grow(c, &c->g, (size_t)I * 4));
+    CKR(launch_q8_gateup((const int8_t *)gate->codes, (const float *)gate->scales, (const int8_t *)up->codes, (const float *)up->scales,
+                         x_dev, (float *)c->g.p, I, D, act, c->sms, st, t_dev, g_t_dev, g_x_dev, xout_dev, eps));
+    return mat_apply_on(c, down, out_dev, (const float *)c->g.p, 1, nullptr, st);
 }
 
 extern "C" int moty_cuda_ffn(MotyCudaMat *gate, MotyCudaMat *up, MotyCudaMat *down, int act,

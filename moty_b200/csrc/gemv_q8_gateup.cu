@@ -8,8 +8,11 @@
 // Every CTA quantizes the activation row (moty_hw_qrow_i8, hw/hw_quant.h:9-16) into shared memory behind its first
 // weight loads.  Same dp4a sums, the same (scale[i] * sx) * (float)dot products (nn/matmul.c:34) and the same
 // activation expression as the separate launches: same bits.
+// Optionally the residual step and the RMS norm in front of the block ride in the prologue (resnorm.cuh): the row is
+// rmsnorm(x + t) * g_x -- or, gemma's sandwich, rmsnorm(x + rmsnorm(t) * g_t) * g_x -- and CTA 0 writes the sum out.
 // Limits: rows of 16..4096 int8 values, a multiple of 16; x 16-byte aligned.
 #include "kernels.cuh"
+#include "resnorm.cuh"
 
 namespace {
 
@@ -19,11 +22,13 @@ struct GateUpArgs {
     const int8_t *g, *u; const float *gs, *us;
     const float *x; float *h;
     int O, I16, act;
+    const float *t, *g_t, *g_x; float *xout; float eps;    // optional residual + norm prologue (t != nullptr)
 };
 
 __global__ void __launch_bounds__(256, 2) q8_gateup_kernel(GateUpArgs a) {
     extern __shared__ int4 smem4[];
     __shared__ float red[8];
+    __shared__ double red64[8];
     __shared__ float sx_s;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int I16 = a.I16, O = a.O, nwarps = gridDim.x * 8;
@@ -50,7 +55,20 @@ __global__ void __launch_bounds__(256, 2) q8_gateup_kernel(GateUpArgs a) {
     if (o < O) issue(o);                                   // weights only: may run before the previous kernel has finished
     pdl_wait();                                            // the activation row and h from here on
 
-    {   // quantize the row: two passes over x (it sits in L2)
+    if (a.t) {   // residual step + norm, then quantize from the f32 copy in shared memory
+        float *xf = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(smem4) + I16 * 16);
+        const float amax = resnorm_row(a.x, a.t, a.g_t, a.g_x, a.xout, a.eps, I16 * 16, xf, red64, red, blockIdx.x == 0);
+        const float sx = quant_scale(amax, 1e-12f);
+        const float inv = __fdiv_rn(1.f, sx);
+        int *xq = reinterpret_cast<int *>(smem4);
+        for (int i = threadIdx.x; i < I16 * 4; i += 256) {
+            const float4 v = reinterpret_cast<const float4 *>(xf)[i];
+            const int c0 = quant_code(v.x, inv) & 255, c1 = quant_code(v.y, inv) & 255;
+            const int c2 = quant_code(v.z, inv) & 255, c3 = quant_code(v.w, inv) & 255;
+            xq[i] = c0 | (c1 << 8) | (c2 << 16) | (c3 << 24);
+        }
+        if (threadIdx.x == 0) sx_s = sx;
+    } else {   // quantize the row: two passes over x (it sits in L2)
         const int I4 = I16 * 4;
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         float amax = 0.f;
@@ -108,12 +126,14 @@ bool q8_gateup_supported(int I, int D) { return D % 16 == 0 && D >= 16 && D <= 4
 
 // h[i] = act(gate[i] . x) * (up[i] . x), i < I; gate, up [I][D] int8 with per-row scales; x [D] f32.
 int launch_q8_gateup(const int8_t *g, const float *gs, const int8_t *u, const float *us, const float *x, float *h, int I, int D,
-                     int act, int sms, cudaStream_t st) {
+                     int act, int sms, cudaStream_t st, const float *t, const float *g_t, const float *g_x, float *xout, float eps) {
     if (!q8_gateup_supported(I, D) || (reinterpret_cast<uintptr_t>(x) & 15))
         return moty_set_error(MOTY_CUDA_EARG, "q8_gateup: %dx%d (rows of 16..4096 bytes, x 16-byte aligned)", I, D);
+    if (t && (!g_x || !xout || xout == x)) return moty_set_error(MOTY_CUDA_EARG, "q8_gateup: the residual prologue wants gains and its own output");
     GateUpArgs a;
     a.g = g; a.u = u; a.gs = gs; a.us = us; a.x = x; a.h = h; a.O = I; a.I16 = D / 16; a.act = act;
-    const size_t smem = (size_t)D;
+    a.t = t; a.g_t = t ? g_t : nullptr; a.g_x = g_x; a.xout = xout; a.eps = eps;
+    const size_t smem = t ? (size_t)D * 5 : (size_t)D;
     auto k = q8_gateup_kernel;
     static size_t cached_smem[MOTY_MAX_DEV];
     static int cached_per_sm[MOTY_MAX_DEV];

@@ -14,11 +14,13 @@
 // added into a global cell (exact, order independent) and the lane that brings
 // the last part writes the f32 result and re-zeroes the cell.
 #include "kernels.cuh"
+#include "resnorm.cuh"
 
 struct StreamArgs {
     const int8_t *w; const float *scale;
     const float *x;                 // FUSED: f32 row
     const float *t, *g; float *xout; float eps;   // FUSED, optional: the row is rmsnorm(x + t) * g, and x + t goes to xout
+    const float *gt;                              // FUSED == 2: the sandwich form, x + rmsnorm(t) * gt in place of x + t
     const int8_t *xi; const float *sx;   // not fused: quantized rows [S][I] and their scales
     float *y; int32_t *acc_out;     // [S][O]
     unsigned long long *cell;       // K-split cells [S][O], all 0 between launches
@@ -44,7 +46,10 @@ __device__ __forceinline__ void reduce_multi(int (&v)[N], int lane) {
     for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
 }
 
-template <int NS, int R, int LPR, bool FUSED>
+// FUSED: 0 = quantized rows come in; 1 = one f32 row, quantized here (optionally after x + t and the RMS norm);
+// 2 = the same with gemma's sandwich step in front (resnorm.cuh) -- its own instantiation, so that the common ones keep
+// their register budget
+template <int NS, int R, int LPR, int FUSED>
 __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(StreamArgs a) {
     extern __shared__ int4 smem4[];
     __shared__ float red[8];
@@ -94,7 +99,9 @@ __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(Strea
         float *xf = reinterpret_cast<float *>(xq_s + I);
         const float4 *x4 = reinterpret_cast<const float4 *>(a.x);
         float amax = 0.f;
-        if (a.t) {
+        if (FUSED == 2) {
+            amax = resnorm_row(a.x, a.t, a.gt, a.g, a.xout, a.eps, I, xf, red64, red, blockIdx.x == 0);
+        } else if (a.t) {
             // residual add and RMS norm first (hw/hw_ops.h:30-32 and 14-18), element for element and sum for sum as the
             // separate add+norm launch does them, so both routes give the same bits.  Every CTA forms the row for
             // itself; CTA 0 also writes the sum out (to another buffer: the others are still reading x).  I <= 4096.
@@ -223,7 +230,7 @@ __global__ void __launch_bounds__(256, (NS <= 2 ? 4 : 2)) q8_stream_kernel(Strea
     }
 }
 
-template <int NS, int R, int LPR, bool FUSED>
+template <int NS, int R, int LPR, int FUSED>
 static int launch_t(const StreamArgs &a, int sms, cudaStream_t st) {
     size_t smem = FUSED ? (a.I <= 4096 ? (size_t)a.I * 5 : (size_t)a.I) : (size_t)NS * a.I;
     auto k = q8_stream_kernel<NS, R, LPR, FUSED>;
@@ -248,7 +255,7 @@ static int launch_t(const StreamArgs &a, int sms, cudaStream_t st) {
     return 0;
 }
 
-template <int NS, bool FUSED>
+template <int NS, int FUSED>
 static int launch_ns(const StreamArgs &a, int lpr, int sms, cudaStream_t st) {
     if (lpr <= 2) return launch_t<NS, 4, 2, FUSED>(a, sms, st);
     if (lpr <= 4) return launch_t<NS, 2, 4, FUSED>(a, sms, st);
@@ -260,14 +267,14 @@ static int launch_ns(const StreamArgs &a, int lpr, int sms, cudaStream_t st) {
 // between launches) or null when I <= 4096.
 int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const int8_t *xi, const float *sx,
                      float *y, int32_t *acc, int S, int I, int O, int *counters, unsigned long long *cell,
-                     int sms, cudaStream_t st, const float *t, const float *g, float *xout, float eps) {
+                     int sms, cudaStream_t st, const float *t, const float *g, float *xout, float eps, const float *gt) {
     if (I % 16 != 0 || I > MOTY_QROW_MAX || S < 1 || S > 8) return moty_set_error(MOTY_CUDA_EARG, "q8_stream: S=%d I=%d", S, I);
     if (t && (S != 1 || !x || !g || !xout || xout == x || I > 4096))
         return moty_set_error(MOTY_CUDA_EARG, "q8_stream: add+norm wants one f32 row of at most 4096 values and its own output");
     if (O <= 0) return 0;
     StreamArgs a;
     a.w = w; a.scale = scale; a.x = x; a.xi = xi; a.sx = sx; a.y = y; a.acc_out = acc;
-    a.t = t; a.g = g; a.xout = xout; a.eps = eps;
+    a.t = t; a.g = g; a.xout = xout; a.eps = eps; a.gt = t ? gt : nullptr;
     a.cell = cell; (void)counters;
     a.S = S; a.I = I; a.O = O;
     int I16 = I / 16;
@@ -275,9 +282,10 @@ int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const 
     a.seg = (I16 + a.KS - 1) / a.KS;
     if (a.KS > 1 && !cell) return moty_set_error(MOTY_CUDA_EARG, "q8_stream: K-split cells missing");
     int lpr = (a.seg + 31) / 32;                     // 128-bit loads per lane and row
-    if (S == 1 && x) return launch_ns<1, true>(a, lpr, sms, st);     // f32 row: quantized inside the kernel
-    if (S == 1) return launch_ns<1, false>(a, lpr, sms, st);         // already quantized (tail of a chunked batch)
-    if (S == 2) return launch_ns<2, false>(a, lpr, sms, st);
-    if (S <= 4) return launch_ns<4, false>(a, lpr, sms, st);
-    return launch_ns<8, false>(a, lpr, sms, st);
+    if (S == 1 && x && a.gt) return launch_ns<1, 2>(a, lpr, sms, st);   // f32 row behind gemma's sandwich step
+    if (S == 1 && x) return launch_ns<1, 1>(a, lpr, sms, st);        // f32 row: quantized inside the kernel
+    if (S == 1) return launch_ns<1, 0>(a, lpr, sms, st);             // already quantized (tail of a chunked batch)
+    if (S == 2) return launch_ns<2, 0>(a, lpr, sms, st);
+    if (S <= 4) return launch_ns<4, 0>(a, lpr, sms, st);
+    return launch_ns<8, 0>(a, lpr, sms, st);
 }

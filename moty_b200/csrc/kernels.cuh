@@ -49,7 +49,9 @@ int gemv_q8_init_device();
 int launch_q8_stream(const int8_t *w, const float *scale, const float *x, const int8_t *xi, const float *sx,
                      float *y, int32_t *acc, int S, int I, int O, int *counters, unsigned long long *cell,
                      int sms, cudaStream_t st, const float *t = nullptr, const float *g = nullptr, float *xout = nullptr,
-                     float eps = 0.f);   // t (S == 1, I <= 4096): the row is rmsnorm(x + t) * g, and x + t goes to xout
+                     float eps = 0.f, const float *gt = nullptr);
+                                         // t (S == 1, I <= 4096): the row is rmsnorm(x + t) * g, and x + t goes to xout;
+                                         // with gt the sum is x + rmsnorm(t) * gt (resnorm.cuh)
 int q4r4_init_device();
 
 // ---- gemm_q8_tc.cu --------------------------------------------------------------
@@ -152,7 +154,9 @@ int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cud
 // ---- gemv_q8_gateup.cu: h = act(gate . x) * (up . x) for one token in one launch (rows of at most 4096 values) ----
 bool q8_gateup_supported(int I, int D);
 int launch_q8_gateup(const int8_t *g, const float *gs, const int8_t *u, const float *us, const float *x, float *h, int I, int D,
-                     int act, int sms, cudaStream_t st);
+                     int act, int sms, cudaStream_t st, const float *t = nullptr, const float *g_t = nullptr,
+                     const float *g_x = nullptr, float *xout = nullptr, float eps = 0.f);
+                                         // t: the activation row is rmsnorm(x + t) * g_x (g_t: x + rmsnorm(t) * g_t), the sum goes to xout
 
 // ---- gemv_q8_multi.cu: up to eight independent S = 1 Q8_0 products in one launch ----
 bool q8_multi_supported(int I);

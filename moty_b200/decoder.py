@@ -41,17 +41,19 @@ class DenseDecoder:
     ``Mat`` (MOTY_WF_I8 [vocab][D]; with tied embeddings it is also the embedding table); ``final_norm`` [D]."""
 
     def __init__(self, layers, head: Mat, final_norm, n_heads, n_kv_heads, head_dim, max_t, theta=1e6, eps=1e-6,
-                 rot=None, kv8=False, device=0, max_S=64, fold_addnorm=None):
+                 rot=None, kv8=False, device=0, max_S=64, fold_addnorm=None, fold_ffn=False):
         import torch
         self.torch = torch
         self.dev = torch.device(f"cuda:{device}")
         self.layers, self.head = layers, head
         self.H, self.KV, self.hd, self.eps, self.max_t = n_heads, n_kv_heads, head_dim, float(eps), max_t
         self.D = head.I
-        # fold the add+norm before a layer's [q|k|v] product into that product's launch: measured a gain at hidden 2048
-        # (1196 -> 1247 tok/s replayed) and a small loss at hidden 1024 (1245 -> 1232: every CTA of the product then reads
-        # three shared rows instead of one), so by default only from 2048 up
-        self.fold_addnorm = (self.D >= 2048) if fold_addnorm is None else bool(fold_addnorm)
+        # fold the add+norm in front of a layer's [q|k|v] product into that launch (one token): measured a gain at hidden
+        # 1024 (1391 -> 1428 tok/s replayed) and 2048 once every launch of the layer was chained to the next.  The same
+        # fold in front of the dense FFN block (fold_ffn) is built and bit-identical but measured a loss (1428 -> 1398):
+        # the ~600 CTAs of the gate/up launch each redo the row, where the separate one-CTA launch is nearly free
+        self.fold_addnorm = True if fold_addnorm is None else bool(fold_addnorm)
+        self.fold_ffn = bool(fold_ffn)
         f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
         self.final_norm = f(final_norm)
         self.ln = [(f(l.in_ln), f(l.post_ln)) for l in layers]
@@ -115,21 +117,24 @@ class DenseDecoder:
 
     def _layers(self, S, pos_base, pos_dev, sh):
         """The layers of engines/qwen.c:696-712 on self.x [S][D].  A residual add and the norm that follows it are one
-        launch (same results); with S = 1 and a fused matrix the three projections are one product."""
+        launch (same results); with S = 1 and a fused matrix the three projections are one product, and the add+norm in
+        front of that product and in front of a dense FFN block ride inside those launches (same bits; the sum goes to
+        the other of two residual buffers)."""
         L, D, eps = lib(), self.D, C.c_float(self.eps)
         p = lambda ten: C.c_void_p(ten.data_ptr())
         qw, kw = self.H * self.hd, self.KV * self.hd
         nl = len(self.layers)
         x, x_alt = self.x, self.x_alt
-        # a decode token: the add+norm between a layer's FFN and the next layer's fused [q|k|v] product rides inside that
-        # product (same bits, one launch less); the sum goes to the other of two residual buffers
-        fold = [self.fold_addnorm and S == 1 and l.qkv is not None and bool(L.moty_cuda_mat_addnorm_supported(l.qkv.h)) for l in self.layers]
-        pending = False
+        one = self.fold_addnorm and S == 1
+        fold_qkv = [one and l.qkv is not None and bool(L.moty_cuda_mat_addnorm_supported(l.qkv.h)) for l in self.layers]
+        fold_ffn = [self.fold_ffn and S == 1 and l.moe is None and bool(L.moty_cuda_ffn_resnorm_supported(l.gate.h, l.up.h))
+                    for l in self.layers]
+        pending = False                          # self.tmp holds a block output that has not been added to x yet
         _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(x), p(self.ln[0][0]), S, D, eps, sh))
         for i, (l, (in_ln, post_ln), a) in enumerate(zip(self.layers, self.ln, self.attn)):
             if S == 1 and l.qkv is not None:
                 if pending:
-                    _ck(L.moty_cuda_mat_apply_addnorm_dev(l.qkv.h, p(self.qkvb), p(x), p(self.tmp), p(x_alt), p(in_ln), eps, sh))
+                    _ck(L.moty_cuda_mat_apply_resnorm_dev(l.qkv.h, p(self.qkvb), p(x), p(self.tmp), None, p(x_alt), p(in_ln), eps, sh))
                     x, x_alt = x_alt, x
                     pending = False
                 else:
@@ -146,12 +151,17 @@ class DenseDecoder:
             else:
                 _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
             _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
-            _ck(L.moty_cuda_add_rmsnorm_dev(p(x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
-            if l.moe is not None:
-                _ck(L.moty_cuda_moe_apply_dev(l.moe.h, p(self.tmp), p(self.nrm), S, None, 0, l.norm_topk, None, None, sh))
+            if fold_ffn[i]:
+                _ck(L.moty_cuda_ffn_resnorm_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(x), p(self.tmp), None, p(x_alt),
+                                                p(post_ln), eps, sh))
+                x, x_alt = x_alt, x
             else:
-                _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
-            if i + 1 < nl and fold[i + 1]:
+                _ck(L.moty_cuda_add_rmsnorm_dev(p(x), p(self.tmp), p(self.nrm), p(post_ln), S, D, eps, sh))
+                if l.moe is not None:
+                    _ck(L.moty_cuda_moe_apply_dev(l.moe.h, p(self.tmp), p(self.nrm), S, None, 0, l.norm_topk, None, None, sh))
+                else:
+                    _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_SILU, p(self.tmp), p(self.nrm), S, sh))
+            if i + 1 < nl and fold_qkv[i + 1]:
                 pending = True
             elif i + 1 < nl:
                 _ck(L.moty_cuda_add_rmsnorm_dev(p(x), p(self.tmp), p(self.nrm), p(self.ln[i + 1][0]), S, D, eps, sh))
@@ -241,7 +251,11 @@ class GemmaDecoder(DenseDecoder):
     The final logit soft-cap (softcap * tanhf(logit / softcap)) is monotonic, so the greedy pick is taken from the
     uncapped logits; ``step(..., want_logits=True)`` returns them uncapped."""
 
-    def __init__(self, layers, head: Mat, final_norm, n_heads, max_t, eps=1e-6, kv8=False, device=0, max_S=64):
+    def __init__(self, layers, head: Mat, final_norm, n_heads, max_t, eps=1e-6, kv8=False, device=0, max_S=64, fold_addnorm=False,
+                 fold_ffn=False):
+        # the folds of the sandwich steps into their consumers are built and bit-identical, and off by default: at hidden
+        # 3840 they measured a loss (289 -> 263 tok/s replayed on the 48-layer shape; every CTA of the consumer redoes two
+        # reductions over the row, where the separate one-CTA launch is nearly free under programmatic dependent launch)
         import torch
         self.torch = torch
         self.dev = torch.device(f"cuda:{device}")
@@ -249,7 +263,7 @@ class GemmaDecoder(DenseDecoder):
         self.H, self.eps, self.max_t = n_heads, float(eps), max_t
         self.D = head.I
         self.embed_scale = float(np.sqrt(np.float32(self.D)))
-        self.fold_addnorm = False
+        self.fold_addnorm, self.fold_ffn = bool(fold_addnorm), bool(fold_ffn)
         f = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(self.dev)
         self.final_norm = f(final_norm)
         self.ln = [tuple(f(g) for g in (l.in_ln, l.post_attn_ln, l.pre_ff_ln, l.post_ff_ln)) for l in layers]
@@ -268,6 +282,7 @@ class GemmaDecoder(DenseDecoder):
         self._drop_graph()
         self.cap = S
         self.x, self.nrm, self.tmp = e(S, self.D), e(S, self.D), e(S, self.D)
+        self.x_alt = e(1, self.D)
         self.qb, self.kb, self.vb, self.ctx = e(S, self._qw), e(S, self._kw), e(S, self._kw), e(S, self._qw)
         self.qkvb = e(1, self._qw + 2 * self._kw)
         self.ids = t.empty((S,), device=dev, dtype=t.int32)
@@ -280,16 +295,26 @@ class GemmaDecoder(DenseDecoder):
 
     def _layers(self, S, pos_base, pos_dev, sh):
         """engines/gemma.c:466-483 on self.x [S][D]; on return self.nrm holds the FINAL norm of every row (the last
-        sandwich step opens it), so the caller goes straight to the lm_head."""
+        sandwich step opens it), so the caller goes straight to the lm_head.  With one token the sandwich steps in front
+        of the fused [q|k|v] product and in front of the FFN block ride inside those launches (same bits)."""
         L, D, eps = lib(), self.D, C.c_float(self.eps)
         p = lambda ten: C.c_void_p(ten.data_ptr())
         nl = len(self.layers)
-        x = self.x
+        x, x_alt = self.x, self.x_alt
+        one = self.fold_addnorm and S == 1
+        fold_qkv = [one and l.qkv is not None and bool(L.moty_cuda_mat_addnorm_supported(l.qkv.h)) for l in self.layers]
+        fold_ffn = [self.fold_ffn and S == 1 and bool(L.moty_cuda_ffn_resnorm_supported(l.gate.h, l.up.h)) for l in self.layers]
+        pending = None                           # gains of the post-FFN norm whose sandwich step is still owed (t in self.tmp)
         _ck(L.moty_cuda_rmsnorm_dev(p(self.nrm), p(x), p(self.ln[0][0]), S, D, eps, sh))
         for i, (l, (in_ln, post_attn, pre_ff, post_ff), a) in enumerate(zip(self.layers, self.ln, self.attn)):
             qw, kw = self.H * l.hd, l.KV * l.hd
             if S == 1 and l.qkv is not None:
-                _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
+                if pending is not None:
+                    _ck(L.moty_cuda_mat_apply_resnorm_dev(l.qkv.h, p(self.qkvb), p(x), p(self.tmp), p(pending), p(x_alt), p(in_ln), eps, sh))
+                    x, x_alt = x_alt, x
+                    pending = None
+                else:
+                    _ck(L.moty_cuda_mat_apply_dev(l.qkv.h, p(self.qkvb), p(self.nrm), 1, sh))
                 base = self.qkvb.data_ptr()
                 qp, kp, vp = C.c_void_p(base), C.c_void_p(base + 4 * qw), C.c_void_p(base + 4 * (qw + kw))
             else:
@@ -302,10 +327,18 @@ class GemmaDecoder(DenseDecoder):
             else:
                 _ck(L.moty_cuda_attn_core_posdev(a.h, p(self.ctx), qp, kp, vp, S, p(pos_dev), pos_base, sh))
             _ck(L.moty_cuda_mat_apply_dev(l.o.h, p(self.tmp), p(self.ctx), S, sh))
-            _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_attn), p(self.nrm), p(pre_ff), S, D, eps, sh))
-            _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_GELU_TANH, p(self.tmp), p(self.nrm), S, sh))
-            nxt = self.ln[i + 1][0] if i + 1 < nl else self.final_norm
-            _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_ff), p(self.nrm), p(nxt), S, D, eps, sh))
+            if fold_ffn[i]:
+                _ck(L.moty_cuda_ffn_resnorm_dev(l.gate.h, l.up.h, l.down.h, ACT_GELU_TANH, p(self.tmp), p(x), p(self.tmp), p(post_attn),
+                                                p(x_alt), p(pre_ff), eps, sh))
+                x, x_alt = x_alt, x
+            else:
+                _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_attn), p(self.nrm), p(pre_ff), S, D, eps, sh))
+                _ck(L.moty_cuda_ffn_dev(l.gate.h, l.up.h, l.down.h, ACT_GELU_TANH, p(self.tmp), p(self.nrm), S, sh))
+            if i + 1 < nl and fold_qkv[i + 1]:
+                pending = post_ff
+            else:
+                nxt = self.ln[i + 1][0] if i + 1 < nl else self.final_norm
+                _ck(L.moty_cuda_normadd_rmsnorm_dev(p(x), p(self.tmp), p(post_ff), p(self.nrm), p(nxt), S, D, eps, sh))
         return x
 
     def step(self, ids, pos_base, want_logits=False):

@@ -128,7 +128,7 @@ def test_greedy_tokens_match_the_oracle(gpu, oracle):
                          qkv=fuse(l) if i != 1 else None)                # one layer without the fused [q|k|v] matrix
               for i, l in enumerate(W["layers"])]
     # fold_addnorm: layer 2's add+norm rides in its [q|k|v] product (layer 1 has no fused matrix: the plain route)
-    dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t, fold_addnorm=True)
+    dec = DenseDecoder(layers, gpu.Mat.i8(*W["head"]), W["final_norm"], cfg["H"], cfg["KV"], cfg["hd"], max_t, fold_addnorm=True, fold_ffn=True)
     om = _OracleModel(oracle, W, cfg, max_t)
     prompt = rng.integers(0, V, 9).astype(np.int32)
     tg, lg = dec.step(prompt, 0, want_logits=True)
@@ -197,6 +197,43 @@ def test_greedy_tokens_match_with_routed_layers(gpu, oracle):
     dec.close()
 
 
+@pytest.mark.parametrize("D,I,act,sandwich", [(3840, 1536, 1, True), (1024, 3072, 0, False), (2048, 520, 0, True), (112, 40, 1, False)])
+def test_residual_and_norm_inside_the_consumers(gpu, D, I, act, sandwich):
+    """The residual step (x + t, or gemma's x + rmsnorm(t) * g_t) and the norm that follows it, folded into the one-token
+    product (moty_cuda_mat_apply_resnorm_dev) and into the FFN block (moty_cuda_ffn_resnorm_dev), against the separate
+    entries one after the other: the same bits for y / out and for the new residual; x and t are left alone."""
+    import ctypes as C
+    import torch
+    rng = np.random.default_rng(D + I)
+    mk = lambda O, K: gpu.Mat.i8(rng.integers(-127, 128, (O, K), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32))
+    W, G, U, Dn = mk(I, D), mk(I, D), mk(I, D), mk(D, I)
+    x, t = (rng.standard_normal((1, D)).astype(np.float32) for _ in range(2))
+    gt, gx = (rng.uniform(0.5, 1.5, D).astype(np.float32) for _ in range(2))
+    dx, dt, dgt, dgx = (torch.from_numpy(a).cuda() for a in (x, t, gt, gx))
+    xs, nrm = dx.clone(), torch.empty_like(dx)
+    y1, y2 = torch.empty((1, I), device="cuda"), torch.empty((1, I), device="cuda")
+    o1, o2 = torch.empty_like(dx), torch.empty_like(dx)
+    xo1, xo2 = torch.zeros_like(dx), torch.zeros_like(dx)
+    torch.cuda.synchronize()
+    sh = C.c_void_p(gpu.stream_handle(torch.cuda.current_stream()))
+    L, P, eps = gpu.lib(), (lambda a: C.c_void_p(a.data_ptr())), C.c_float(1e-6)
+    pgt = P(dgt) if sandwich else None
+    if sandwich:
+        assert L.moty_cuda_normadd_rmsnorm_dev(P(xs), P(dt), P(dgt), P(nrm), P(dgx), 1, D, eps, sh) == 0
+    else:
+        assert L.moty_cuda_add_rmsnorm_dev(P(xs), P(dt), P(nrm), P(dgx), 1, D, eps, sh) == 0
+    assert L.moty_cuda_mat_apply_dev(W.h, P(y1), P(nrm), 1, sh) == 0
+    assert L.moty_cuda_ffn_dev(G.h, U.h, Dn.h, act, P(o1), P(nrm), 1, sh) == 0
+    assert L.moty_cuda_mat_addnorm_supported(W.h) == 1 and L.moty_cuda_ffn_resnorm_supported(G.h, U.h) == 1
+    assert L.moty_cuda_mat_apply_resnorm_dev(W.h, P(y2), P(dx), P(dt), pgt, P(xo1), P(dgx), eps, sh) == 0, L.moty_cuda_last_error()
+    assert L.moty_cuda_ffn_resnorm_dev(G.h, U.h, Dn.h, act, P(o2), P(dx), P(dt), pgt, P(xo2), P(dgx), eps, sh) == 0, L.moty_cuda_last_error()
+    torch.cuda.synchronize()
+    assert same_bits(y1.cpu().numpy(), y2.cpu().numpy()) and same_bits(o1.cpu().numpy(), o2.cpu().numpy())
+    assert same_bits(xs.cpu().numpy(), xo1.cpu().numpy()) and same_bits(xs.cpu().numpy(), xo2.cpu().numpy())
+    assert same_bits(dx.cpu().numpy(), x) and same_bits(dt.cpu().numpy(), t)
+    assert L.moty_cuda_ffn_resnorm_dev(G.h, U.h, Dn.h, act, P(o2), P(dx), P(dt), pgt, P(dx), P(dgx), eps, sh) != 0       # xout must not be x
+
+
 @pytest.mark.parametrize("D", [3840, 1000, 5000])
 def test_sandwich_norm_step(gpu, D):
     """x += rmsnorm(t) * g1, out = rmsnorm(x) * g2 in one launch (moty_cuda_normadd_rmsnorm_dev) against the three
@@ -255,7 +292,7 @@ def test_gemma_greedy_tokens_match_the_oracle(gpu, oracle):
                                  window=g["window"], rot=g["rot"], qkv=fuse if len(layers) != 1 else None))
         caches.append(AttnCache(H, g["KV"], g["hd"], max_t, theta=g["theta"], eps=1e-6, rot=g["rot"], qn=l["qn"], kn=l["kn"], vn=l["vn"],
                                 gemma=True, window=g["window"]))
-    dec = GemmaDecoder(layers, gpu.Mat.i8(hq, hs), mult(fin), H, max_t)
+    dec = GemmaDecoder(layers, gpu.Mat.i8(hq, hs), mult(fin), H, max_t, fold_addnorm=True, fold_ffn=True)   # sandwich steps folded into their consumers
     es = np.sqrt(np.float32(D))
 
     def ostep(ids, pos):
@@ -287,3 +324,12 @@ def test_gemma_greedy_tokens_match_the_oracle(gpu, oracle):
     # the blocked prefill (blocks of 5 tokens) reaches the same first token
     assert dec.prefill(prompt, 0, block=5) == got[0]
     dec.close()
+    # the same without the folds (every sandwich step its own launch): the same logits bit for bit
+    plain = GemmaDecoder(layers, gpu.Mat.i8(hq, hs), mult(fin), H, max_t)
+    dec2 = GemmaDecoder(layers, gpu.Mat.i8(hq, hs), mult(fin), H, max_t, fold_addnorm=True, fold_ffn=True)
+    ta, la = plain.step(prompt, 0, want_logits=True); tb, lb = dec2.step(prompt, 0, want_logits=True)
+    assert ta == tb and same_bits(la, lb)
+    for i in range(4):
+        ta, la = plain.step([ta], len(prompt) + i, want_logits=True); tb, lb = dec2.step([tb], len(prompt) + i, want_logits=True)
+        assert ta == tb and same_bits(la, lb)
+    plain.close(); dec2.close()
