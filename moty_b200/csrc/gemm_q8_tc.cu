@@ -59,6 +59,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
     // two accumulators of BN columns: the epilogue of one tile overlaps the MMAs of the next
     constexpr uint32_t TMEM_COLS = NBUF * MT * BN < 32 ? 32 : NBUF * MT * BN;
 
+    pdl_trigger();                                                       // barriers and TMEM are set up under the previous kernel's tail
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int i = 0; i < STAGES; i++) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
@@ -75,6 +76,7 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     volatile int *abort_flag = &abort_s;
+    pdl_wait();                                                          // activation codes and scales come from the quantizer launch
 
     // Persistent over output tiles.  Consecutive tile numbers share the weight rows (same m,
     // next n), so CTAs running side by side fetch the same W tile and the second fetch hits L2.
@@ -229,6 +231,8 @@ __global__ void __launch_bounds__(TC_THREADS, 1) q8_tc_kernel(const __grid_const
 __global__ void __launch_bounds__(256) tc_splitk_finish_kernel(const int32_t *__restrict__ part, int KS, const float *__restrict__ scale,
                                                                const float *__restrict__ sx, float *__restrict__ y,
                                                                int32_t *__restrict__ acc, int S, int O) {
+    pdl_trigger();
+    pdl_wait();
     const size_t n = (size_t)S * O, i = (size_t)blockIdx.x * 256 + threadIdx.x;
     if (i >= n) return;
     int v = 0;
@@ -267,12 +271,11 @@ int launch_tc_t(const CUtensorMap &mapA, const MotyCudaMat *w, const int8_t *xi,
     }
     int work = ntiles * ks;
     int grid = work < c->sms ? work : c->sms;                  // persistent: one CTA per SM
-    k<<<grid, TC_THREADS, smem, st>>>(mapA, mapB, a);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(k, dim3(grid), dim3(TC_THREADS), smem, st, mapA, mapB, a));
     if (ks > 1) {
         const size_t n = (size_t)S * w->O;
-        tc_splitk_finish_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(a.part, ks, a.scale, sx, y, acc, S, w->O);
-        CK(cudaGetLastError());
+        CK(moty_launch_pdl(tc_splitk_finish_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), (size_t)0, st,
+                           (const int32_t *)a.part, ks, a.scale, sx, y, acc, S, w->O));
     }
     return 0;
 }

@@ -55,8 +55,8 @@ __global__ void __launch_bounds__(MT_THREADS, 1) moe_tc_kernel(const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int nkb = (a.Kdim + BKB - 1) / BKB;
     const int ntm = (a.M + BM - 1) / BM;
-    const int nitems = *a.ntiles_dev * ntm;          // written by the plan kernel earlier on this stream
 
+    pdl_trigger();                                   // barriers and TMEM are set up under the previous kernel's tail
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int i = 0; i < STAGES; i++) { mbar_init(&full_bar[i], 1); mbar_init(&empty_bar[i], 1); }
@@ -73,6 +73,8 @@ __global__ void __launch_bounds__(MT_THREADS, 1) moe_tc_kernel(const __grid_cons
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_base = tmem_base_s;
     volatile int *abort_flag = &abort_s;
+    pdl_wait();                                      // the plan, the gathered codes and their scales come from earlier launches
+    const int nitems = *a.ntiles_dev * ntm;          // written by the plan kernel earlier on this stream
 
     // item -> (row tile entry, 128-row block of the expert); consecutive items share the entry, so CTAs running side by
     // side read the same activation tile (second fetch from L2) against different weight blocks
@@ -213,8 +215,7 @@ int launch_moe_tc_t(const MoeTcArgs &a, const void *slab, const void *slab2, int
     size_t smem = (size_t)STAGES * (NA * BM * BKB + BN * BKB) + 1024;
     auto k = moe_tc_kernel<BN, STAGES, GATEUP>;
     CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    k<<<sms, MT_THREADS, smem, st>>>(mapA, mapA2, mapB, a);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(k, dim3(sms), dim3(MT_THREADS), smem, st, mapA, mapA2, mapB, a));
     return 0;
 }
 

@@ -234,6 +234,8 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
 __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
                                                        int2 *__restrict__ rec, uint8_t *__restrict__ form, int S, int S8, int nb,
                                                        int q8) {
+    pdl_wait();                                   // (no early trigger: the product after this one is not persistent, and its
+                                                  // CTAs spread unevenly when they arrive while others are still resident)
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= (long long)S8 * nb) return;
     const int g = (int)(i / S8), t = (int)(i - (long long)g * S8);
@@ -277,8 +279,7 @@ int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const
     if (O <= 0) return 0;
     const int nb = I / 32, S8 = (S + 7) / 8 * 8;
     const long long nrec = (long long)S8 * nb;
-    q4r4_rec_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, rec, form, S, S8, nb, q8);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(q4r4_rec_kernel, dim3((unsigned)((nrec + 255) / 256)), dim3(256), (size_t)0, st, xs, xsum, rec, form, S, S8, nb, q8));
     Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
     // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
@@ -301,6 +302,7 @@ __global__ void __launch_bounds__(256) q4r4_rec_gather_kernel(const float *__res
                                                               const int *__restrict__ xmap, const uint8_t *__restrict__ form,
                                                               const int *__restrict__ npairs_dev, int2 *__restrict__ rec,
                                                               int P8, int nb) {
+    pdl_wait();
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= (long long)P8 * nb) return;
     const int g = (int)(i / P8), p = (int)(i - (long long)g * P8);
@@ -328,8 +330,8 @@ int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntil
     const int nb = I / 32, P8 = (P + 7) / 8 * 8;
     const long long nrec = (long long)P8 * nb;
     if (build_rec) {                                           // gate and up share the records of the gathered input
-        q4r4_rec_gather_kernel<<<(unsigned)((nrec + 255) / 256), 256, 0, st>>>(xs, xsum, xmap, form, npairs_dev, rec, P8, nb);
-        CK(cudaGetLastError());
+        CK(moty_launch_pdl(q4r4_rec_gather_kernel, dim3((unsigned)((nrec + 255) / 256)), dim3(256), (size_t)0, st, xs, xsum, xmap, form,
+                           npairs_dev, rec, P8, nb));
     }
     Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = P; a.S8 = P8; a.I = I; a.O = O;

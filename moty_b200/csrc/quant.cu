@@ -21,6 +21,8 @@ __device__ __forceinline__ float block_max_256(float v, float *red) {
 __global__ void __launch_bounds__(256) qrow_i8_kernel(const float *__restrict__ x, int8_t *__restrict__ q,
                                                       float *__restrict__ scale, int n) {
     __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
     const size_t row = blockIdx.x;
     const float *xr = x + row * n;
     int8_t *qr = q + row * n;
@@ -62,6 +64,8 @@ __global__ void __launch_bounds__(256) qrow_i8_scatter_kernel(const float *__res
                                                               int8_t *__restrict__ xg, float *__restrict__ sxg, int n) {
     __shared__ float red[8];
     __shared__ int pos_s[64];
+    pdl_trigger();
+    pdl_wait();
     const size_t row = blockIdx.x;
     const float4 *x4 = reinterpret_cast<const float4 *>(x + row * n);
     if (threadIdx.x < K) pos_s[threadIdx.x] = pos_of[row * K + threadIdx.x];
@@ -89,8 +93,7 @@ __global__ void __launch_bounds__(256) qrow_i8_scatter_kernel(const float *__res
 // n % 4 == 0, x rows 16-byte aligned, K <= 64
 int launch_qrow_i8_scatter(const float *x, const int *pos_of, int S, int K, int8_t *xg, float *sxg, int n, cudaStream_t st) {
     if (S <= 0) return 0;
-    qrow_i8_scatter_kernel<<<S, 256, 0, st>>>(x, pos_of, K, xg, sxg, n);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(qrow_i8_scatter_kernel, dim3(S), dim3(256), (size_t)0, st, x, pos_of, K, xg, sxg, n));
     return 0;
 }
 
@@ -98,6 +101,8 @@ int launch_qrow_i8_scatter(const float *x, const int *pos_of, int S, int K, int8
 __global__ void __launch_bounds__(256) qrow_i8_counted_kernel(const float *__restrict__ x, int8_t *__restrict__ q,
                                                               float *__restrict__ scale, int n, const int *__restrict__ nrows_dev) {
     __shared__ float red[8];
+    pdl_trigger();
+    pdl_wait();
     const size_t row = blockIdx.x;
     if ((int)row >= *nrows_dev) return;
     const float4 *x4 = reinterpret_cast<const float4 *>(x + row * n);
@@ -121,15 +126,13 @@ __global__ void __launch_bounds__(256) qrow_i8_counted_kernel(const float *__res
 
 int launch_qrow_i8_counted(const float *x, int8_t *q, float *scale, int rows_max, int n, const int *nrows_dev, cudaStream_t st) {
     if (rows_max <= 0) return 0;
-    qrow_i8_counted_kernel<<<rows_max, 256, 0, st>>>(x, q, scale, n, nrows_dev);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(qrow_i8_counted_kernel, dim3(rows_max), dim3(256), (size_t)0, st, x, q, scale, n, nrows_dev));
     return 0;
 }
 
 int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cudaStream_t st) {
     if (rows <= 0 || n <= 0) return 0;
-    qrow_i8_kernel<<<rows, 256, 0, st>>>(x, q, scale, n);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(qrow_i8_kernel, dim3(rows), dim3(256), (size_t)0, st, x, q, scale, n));
     return 0;
 }
 
@@ -139,6 +142,8 @@ int launch_qrow_i8(const float *x, int8_t *q, float *scale, int rows, int n, cud
 __global__ void __launch_bounds__(256) quant_g32_kernel(const float *__restrict__ x, int8_t *__restrict__ xq,
                                                         float *__restrict__ xs, int32_t *__restrict__ xsum,
                                                         long long ngroups) {
+    pdl_trigger();
+    pdl_wait();
     long long g = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (g >= ngroups) return;
     int lane = threadIdx.x & 31;
@@ -155,8 +160,7 @@ __global__ void __launch_bounds__(256) quant_g32_kernel(const float *__restrict_
 int launch_quant_g32(const float *x, int rows, int I, int8_t *xq, float *xs, int32_t *xsum, cudaStream_t st) {
     long long ng = (long long)rows * (I / 32);
     if (ng <= 0) return 0;
-    quant_g32_kernel<<<(unsigned)((ng + 7) / 8), 256, 0, st>>>(x, xq, xs, xsum, ng);
-    CK(cudaGetLastError());
+    CK(moty_launch_pdl(quant_g32_kernel, dim3((unsigned)((ng + 7) / 8)), dim3(256), (size_t)0, st, x, xq, xs, xsum, ng));
     return 0;
 }
 
