@@ -1348,7 +1348,10 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
                                            (const uint16_t *)m->ds, m->gcb, m->gsb / 2, m->dcb, m->dsb / 2, x,
                                            (int8_t *)c->hq.p, (float *)c->hxs.p, (int *)c->hxsum.p, out, rows, K, I, D,
                                            m->e_lo, m->e_hi, reinterpret_cast<unsigned *>(c->ctr) + 4, c->err_dev + 1,
-                                           c->sms, st, rows_peer, npeer));
+                                           c->sms, st, rows_peer, npeer,
+                                           // the same kernel as two chained launches (see the int8 route above); the row table and
+                                           // the peer stores of the expert-parallel routes sit in its second half either way
+                                           g_moe_fast == 1 ? 1 : 0));
             if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             if (w_out) CK(cudaMemcpyAsync(w_out, m->w, (size_t)K * 4, cudaMemcpyDeviceToDevice, st));
             return 0;

@@ -58,7 +58,7 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
                                float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
-                               int sms, cudaStream_t st, float *const *rows_peer = nullptr, int npeer = 0);
+                               int sms, cudaStream_t st, float *const *rows_peer = nullptr, int npeer = 0, int chained = 0);
 
 // ---- moe_tc.cu: the grouped expert products of an int8 batch on tcgen05 (work list = plan tiles x 128-row blocks) ----
 bool moe_tc_supported(int I, int D);

@@ -40,6 +40,11 @@ struct MoeFused4Args {
 constexpr int CH1 = 8;                                         // gate/up steps in flight per warp (x2 matrices)
 constexpr int CHD = 12;                                        // down groups in flight per lane
 
+// PHASE 0: the whole layer in one cooperative launch.  PHASE 1 / PHASE 2: the same code as two launches chained by
+// programmatic dependent launch, split where the grid barrier stands -- the first leaves the hidden codes and the routing
+// in global memory, the second picks the routing up from there (a cooperative launch cannot overlap its launch, or its
+// successor's, with its neighbours; chained launches can).
+template <int PHASE>
 __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a) {
     extern __shared__ int4 sm4[];
     __shared__ int idx_s[64];
@@ -63,6 +68,14 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
     int *hsum_s = reinterpret_cast<int *>(hs_s + (size_t)K * nbs);
     float *p_s = reinterpret_cast<float *>(reinterpret_cast<unsigned char *>(sm4) + abytes);
 
+    if (PHASE != 0) { pdl_trigger(); pdl_wait(); }                    // logits / x (PHASE 1), hidden codes and routing (PHASE 2)
+    if (PHASE == 2) {
+        for (int k = threadIdx.x; k < K; k += 256) {
+            const int e = a.idx_out[k];
+            idx_s[k] = e; w_s[k] = a.w_out[k]; loc_s[k] = e >= a.e_lo && e < a.e_hi;
+        }
+        if (threadIdx.x == 0) gave_up = 0;
+    } else
     // ---------------- phase 0: route || x -> group-quantized codes ----------------
     if (warp == 0) {
         route_row_warp(a.logits, a.E, K, p_s, 1, a.norm_topk, lane, idx_s, w_s, nullptr);
@@ -79,7 +92,7 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
     __syncthreads();
 
     // ---------------- phase 1: (expert, 32 FFN rows) per CTA; the hidden group is quantized on the spot ----------------
-    {
+    if (PHASE != 2) {
         const int gl = lane >> 2, r = lane & 3, prev = (lane + 28) & 31;
         const int nit = (nbD + 7) / 8;
         for (int cu = blockIdx.x; cu < K * nbI; cu += gridDim.x) {
@@ -132,6 +145,8 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
         }
     }
 
+    if (PHASE == 1) return;
+
     // ---------------- down: lane = (expert, row) of a 4-row block; first groups requested before the barrier ----------------
     const int kq = lane >> 2, r = lane & 3;
     const int nblkD = D / 4;
@@ -154,7 +169,7 @@ __global__ void __launch_bounds__(256, 2) moe_dec4_fused_kernel(MoeFused4Args a)
     const int nslots = gridDim.x * 8, slot = warp * gridDim.x + blockIdx.x;
     if (slot < nblkD) issue_down(slot, kq, 0);
 
-    if (!grid_barrier_bounded(a.bar, &gave_up)) {
+    if (PHASE == 0 && !grid_barrier_bounded(a.bar, &gave_up)) {
         if (threadIdx.x == 0) atomicExch(a.err, 1);
         return;
     }
@@ -220,7 +235,7 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
                                const uint16_t *us, const uint16_t *ds, size_t gstride, size_t gsstride,
                                size_t dstride, size_t dsstride, const float *x, int8_t *hq, float *hs, int *hsum,
                                float *out, float *rows, int K, int I, int D, int e_lo, int e_hi, unsigned *bar, int *err,
-                               int sms, cudaStream_t st, float *const *rows_peer, int npeer) {
+                               int sms, cudaStream_t st, float *const *rows_peer, int npeer, int chained) {
     if (!moe_decode_fused_q4_supported(E, K, I, D))
         return moty_set_error(MOTY_CUDA_EARG, "moe_decode_fused_q4: E=%d K=%d I=%d D=%d", E, K, I, D);
     MoeFused4Args a;
@@ -233,14 +248,18 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
     a.K = K; a.I = I; a.D = D; a.e_lo = e_lo; a.e_hi = e_hi;
     size_t a1 = (size_t)D + (size_t)(D / 32) * 8, a2 = (size_t)K * (I + 16) + (size_t)K * ((I / 32) | 1) * 8;
     size_t smem = (((a1 > a2 ? a1 : a2) + 15) & ~(size_t)15) + (size_t)E * 4;
-    auto k = moe_dec4_fused_kernel;
+    auto k = moe_dec4_fused_kernel<0>;
     static size_t cached_smem[MOTY_MAX_DEV];
     static int cached_per_sm[MOTY_MAX_DEV];
     int dev = 0;
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "moe_decode_fused_q4: device %d", dev);
     if (smem + 1 != cached_smem[dev]) {
-        if (smem > 48 * 1024) CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (smem > 48 * 1024) {
+            CK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CK(cudaFuncSetAttribute(moe_dec4_fused_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            CK(cudaFuncSetAttribute(moe_dec4_fused_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        }
         CK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&cached_per_sm[dev], k, 256, smem));
         cached_smem[dev] = smem + 1;
     }
@@ -250,6 +269,11 @@ int launch_moe_decode_fused_q4(const float *logits, int E, int norm_topk, int *i
     if (units < units2) units = units2;
     int ctas = sms * per_sm;
     if (ctas > units) ctas = units;
+    if (chained) {                                             // the same grid twice: the down blocks are dealt over it warp-major
+        CK(moty_launch_pdl(moe_dec4_fused_kernel<1>, dim3(ctas), dim3(256), smem, st, a));
+        CK(moty_launch_pdl(moe_dec4_fused_kernel<2>, dim3(ctas), dim3(256), smem, st, a));
+        return 0;
+    }
     // cooperative: every CTA is resident before any runs, which the grid barrier relies on
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(ctas); cfg.blockDim = dim3(256); cfg.dynamicSmemBytes = smem; cfg.stream = st;

@@ -331,10 +331,13 @@ def test_moe_q4r4_decode_fast_path_equals_generic_path(gpu, oracle, E, K, I, D, 
         fast = m.d1(x, logits); fast2 = m.d1(x, logits)        # twice: the fused kernel's counters must come back to zero
         gpu.lib().moty_cuda_set_moe_fast_path(2)
         split = m.d1(x, logits)
+        gpu.lib().moty_cuda_set_moe_fast_path(3)                # the one-launch cooperative form of the default's two chained launches
+        coop = m.d1(x, logits); coop2 = m.d1(x, logits)
         gpu.lib().moty_cuda_set_moe_fast_path(0)
         slow = m.d1(x, logits)
         gpu.lib().moty_cuda_set_moe_fast_path(prev)
         assert same_bits(fast, slow) and same_bits(fast2, slow) and same_bits(split, slow)
+        assert same_bits(coop, slow) and same_bits(coop2, slow)
     if small and (lo, hi) == (0, E):
         cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
         ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
