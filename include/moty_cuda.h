@@ -131,7 +131,12 @@ int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *dev
  *   WF_Q4R4 -> moty_matmul_q4r4_s   (nn/matmul.c:405-433)
  *   WF_I4   -> moty_matmul_i4_s with IDOT4=1 (nn/matmul.c:75-96)
  * x is [S][I] f32, y is [S][O] f32.  Like the reference, I <= 16384 for the
- * integer paths (NN_QROW_MAX, nn/nn_matmul.h:35); larger I is MOTY_CUDA_ELIMIT. */
+ * integer paths (NN_QROW_MAX, nn/nn_matmul.h:35); larger I is MOTY_CUDA_ELIMIT.
+ * Host pointers; returns with y written.  When x and y both lie in page-locked memory (moty_cuda_host_alloc,
+ * cudaHostAlloc, cudaHostRegister; 16-byte aligned) and the product has no error word to report (MOTY_WF_I8 below 9
+ * rows and the like), the bytes move by kernels chained to the product and the call waits on a flag word instead of
+ * synchronising the stream; pageable buffers take copy-engine transfers.  Same results; MOTY_CUDA_HOST_KERNELS=0 in the
+ * environment forces the copies. */
 int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
 /* n (1..8) independent one-row products in ONE launch: y_dev[m] = mat_apply(w[m], x_dev[m], S = 1) for MOTY_WF_I8

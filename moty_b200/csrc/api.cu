@@ -111,6 +111,9 @@ extern "C" int moty_cuda_init(const int *devices, int ndev) {
         CK(cudaMemset(c->err_dev, 0, 64));
         CK(cudaMalloc(&c->ctr, 64));
         CK(cudaMemset(c->ctr, 0, 64));
+        CK(cudaHostAlloc((void **)&c->hflag, 64, cudaHostAllocMapped | cudaHostAllocPortable));
+        c->hflag[0] = 0; c->hseq = 0;
+        CK(cudaHostGetDevicePointer((void **)&c->hflag_dev, c->hflag, 0));
         CKR(gemv_q8_init_device());
         CKR(q4r4_init_device());
         c->ready = true;
@@ -131,6 +134,7 @@ extern "C" void moty_cuda_shutdown(void) {
         free_pinned(&c->hpin_in); free_pinned(&c->hpin_out);
         if (c->err_dev) cudaFree(c->err_dev);
         if (c->ctr) cudaFree(c->ctr);
+        if (c->hflag) cudaFreeHost(c->hflag);
         cudaStreamDestroy(c->stream);
         c->ready = false;
     }
@@ -521,6 +525,23 @@ extern "C" int moty_cuda_mat_apply_addnorm_dev(MotyCudaMat *w, float *y_dev, con
     return moty_cuda_mat_apply_resnorm_dev(w, y_dev, x_dev, t_dev, nullptr, xout_dev, gain_dev, eps, stream);
 }
 
+// the device-side address of a page-locked host buffer of `bytes` bytes, 16-byte aligned, or null (pageable memory,
+// device memory, an odd alignment, a range that leaves the page-locked allocation)
+static void *mapped_alias(const void *p, size_t bytes) {
+    cudaPointerAttributes at, end;
+    if (cudaPointerGetAttributes(&at, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (at.type != cudaMemoryTypeHost || !at.devicePointer || (reinterpret_cast<uintptr_t>(at.devicePointer) & 15)) return nullptr;
+    if (cudaPointerGetAttributes(&end, (const char *)p + bytes - 1) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    if (end.type != cudaMemoryTypeHost || (const char *)end.devicePointer != (const char *)at.devicePointer + bytes - 1) return nullptr;
+    return at.devicePointer;
+}
+// MOTY_CUDA_HOST_KERNELS=0 in the environment: the host-pointer entries always use copy-engine transfers (read once)
+static bool host_kernels_on() {
+    static int on = -1;
+    if (on < 0) { const char *e = getenv("MOTY_CUDA_HOST_KERNELS"); on = (e && e[0] == '0') ? 0 : 1; }
+    return on == 1;
+}
+
 // host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
 static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
     if (!w || !y || !x) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: null argument");
@@ -532,16 +553,42 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     CKR(moty_grow(c, &c->dx, xb));
     if (acc) CKR(moty_grow(c, &c->acc32, yb));
     CKR(moty_grow(c, &c->dy, yb));
+    // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
+    // kernels fed by bulk copies
+    const bool check = S >= Q8_TC_MIN_S || (S == 1 && (w->fmt == MOTY_WF_Q4R4 || w->fmt == MOTY_WF_Q8R4 || w->fmt == MOTY_WF_I4G));
+    // Pinned buffers at both ends and nothing else to bring back: kernels move x in and y out, chained to the product, and
+    // the host waits for the flag word the last of them writes (hostio.cu) -- no copy-engine transfer, no stream
+    // synchronisation.  Anything else (pageable buffers, the accumulator output, kernels with an error word) takes the
+    // copies below.
+    const float *x_map = nullptr; float *y_map = nullptr;
+    if (!acc && !check && host_kernels_on() && (x_map = (const float *)mapped_alias(x, xb)) != nullptr &&
+        (y_map = (float *)mapped_alias(y, yb)) != nullptr) {
+        const unsigned seq = ++c->hseq;
+        CKR(launch_stage_in((float *)c->dx.p, x_map, (long long)S * w->I, c->stream));
+        CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, nullptr, c->stream));
+        CKR(launch_tail_out(y_map, (const float *)c->dy.p, (long long)S * w->O, reinterpret_cast<unsigned *>(c->ctr) + 8, c->hflag_dev, seq,
+                            c->sms, c->stream));
+        volatile unsigned *flag = c->hflag;
+        for (long long spin = 0; *flag != seq; spin++) {
+            if (spin >= (1LL << 22)) {                             // a fraction of a second: let the driver wait (and report)
+                CK(cudaStreamSynchronize(c->stream));
+                if (*flag != seq) return moty_set_error(MOTY_CUDA_EKERNEL, "mat_apply: the result copy did not report completion");
+                break;
+            }
+            if ((spin & 1023) == 1023 && cudaStreamQuery(c->stream) != cudaErrorNotReady) {   // finished or failed: look once more
+                if (*flag == seq) break;
+                CK(cudaStreamSynchronize(c->stream));
+            }
+        }
+        return 0;
+    }
     CK(cudaMemcpyAsync(c->dx.p, x, xb, cudaMemcpyHostToDevice, c->stream));
     CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, acc ? (int32_t *)c->acc32.p : nullptr, c->stream));
     // (letting the GEMV write a pinned result buffer directly, so that the bytes cross PCIe while the weights stream, was
     // measured slower than this copy: 1142 against 1203 GB/s end to end on the six-matrix pass)
     CK(cudaMemcpyAsync(y, c->dy.p, yb, cudaMemcpyDeviceToHost, c->stream));
     if (acc) CK(cudaMemcpyAsync(acc, c->acc32.p, yb, cudaMemcpyDeviceToHost, c->stream));
-    // kernels with bounded waits leave a word behind when one expired: [0] the tensor-core GEMM, [2] the Q4R4 decode
-    // kernels fed by bulk copies
     int kerr[4] = {0, 0, 0, 0};
-    const bool check = S >= Q8_TC_MIN_S || (S == 1 && (w->fmt == MOTY_WF_Q4R4 || w->fmt == MOTY_WF_Q8R4 || w->fmt == MOTY_WF_I4G));
     if (check) CK(cudaMemcpyAsync(kerr, c->err_dev, 16, cudaMemcpyDeviceToHost, c->stream));
     CK(cudaStreamSynchronize(c->stream));
     if (kerr[0]) {

@@ -73,6 +73,9 @@ struct DevCtx {
     int *err_dev = nullptr;
     // set by moty_cuda_scratch_freeze: the grow-only buffers may no longer move (a captured CUDA graph holds their addresses)
     bool frozen = false;
+    // host-pointer entries with pinned buffers (hostio.cu): a pinned flag word the last kernel of a call writes, its
+    // device alias, and the sequence number of the latest call
+    unsigned *hflag = nullptr, *hflag_dev = nullptr, hseq = 0;
 };
 
 // Every entry point that makes a GPU current puts the caller's device back before it returns.

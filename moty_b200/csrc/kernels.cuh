@@ -151,6 +151,11 @@ int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, cons
 // ---- selftest.cu: the give-up path of the bounded waits, run on purpose with a short limit ----
 int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cudaStream_t st);
 
+// ---- hostio.cu: activations in / results out between mapped (pinned) host buffers and the device, by kernels ----
+int launch_stage_in(float *dst, const float *src_host, long long n, cudaStream_t st);
+int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, unsigned seq, int sms,
+                    cudaStream_t st);
+
 // ---- gemv_q8_gateup.cu: h = act(gate . x) * (up . x) for one token in one launch (rows of at most 4096 values) ----
 bool q8_gateup_supported(int I, int D);
 int launch_q8_gateup(const int8_t *g, const float *gs, const int8_t *u, const float *us, const float *x, float *h, int I, int D,

@@ -264,3 +264,26 @@ def test_q8_multi_launch_equals_single_launches(gpu, oracle):
     with pytest.raises(gpu.MotyCudaError):                       # rows longer than 4096 need the K split of the single kernel
         big = gpu.Mat.i8(rng.integers(-127, 128, (8, 8192), dtype=np.int8), np.ones(8, np.float32))
         gpu.mat_apply_multi_dev([big], [dy[0].data_ptr()], [dx[0].data_ptr()], sh)
+
+
+def test_host_entry_with_pinned_buffers_equals_pageable(gpu, oracle):
+    """moty_cuda_mat_apply with page-locked buffers at both ends moves x in and y out with kernels and waits on a flag
+    word instead of synchronising the stream; with pageable buffers (or an odd alignment) it uses copy-engine transfers.
+    Same bits either way, call after call, odd sizes included."""
+    rng = np.random.default_rng(41)
+    for (O, I, S) in ((1024, 1024, 1), (515, 3840, 1), (3, 16, 1), (4099, 1024, 3), (1000, 112, 8)):
+        Wq = rng.integers(-127, 128, (O, I), dtype=np.int8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+        W = gpu.Mat.i8(Wq, sc)
+        hx = gpu.pinned_empty((S, I), np.float32); hy = gpu.pinned_empty((S, O), np.float32)
+        pad = gpu.pinned_empty((S * I + 1,), np.float32)                   # a pinned buffer 4 bytes off the 16-byte grid
+        for rep in range(3):
+            x = rng.standard_normal((S, I)).astype(np.float32)
+            hx[...] = x; hy[...] = np.nan
+            gpu.mat_apply(W, hx, hy)                                       # pinned -> kernels
+            want = oracle.matmul_q_s(x, Wq, sc)
+            assert hy.tobytes() == want.tobytes(), (O, I, S, rep)
+            assert gpu.mat_apply(W, x).tobytes() == want.tobytes()         # pageable -> copies
+            off = pad[1:].reshape(S, I); off[...] = x
+            y2 = gpu.pinned_empty((S, O), np.float32)
+            gpu.mat_apply(W, off, y2)                                      # misaligned pinned x -> copies
+            assert y2.tobytes() == want.tobytes()
