@@ -233,6 +233,13 @@ int moty_cuda_moe_free(MotyCudaMoe *m);
 /* what LoadExpertFn (runtime/moe.h:56, engines/olmoe.c:141-151) fills for one expert */
 int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *g, const void *gs,
                                 const void *u, const void *us, const void *d, const void *ds);
+/* The same for LFM2's int4 experts (ExpertSlot rows with ebits <= 4, nn/moe.h:12, nn/moe.c:42,99-103,138,193-198):
+ * g4, u4 [I][(D+1)/2] and d4 [D][(I+1)/2] nibble rows (element 2j in the low nibble), f32 row scales.  The layer must
+ * have been created with MOTY_WF_I8: the rows are expanded to the signed codes nibble - 8 on the way in, whose integer
+ * dots are the reference's dot_i4i8p sums, so decode, batches and both gates give the reference's bits (the reference's
+ * batch path is integer under IDOT4=1, nn/matmul.c:75-96).  Costs int8 bytes in HBM, not int4. */
+int moty_cuda_moe_upload_expert_i4(MotyCudaMoe *m, int eid, const void *g4, const float *gs,
+                                   const void *u4, const float *us, const void *d4, const float *ds);
 /* optional router matrix [E][D]; without one the block entries need `logits` */
 int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router);
 

@@ -422,6 +422,12 @@ class Moe:
         arrs = [np.ascontiguousarray(a) for a in (g, gs, u, us, d, ds)]
         _ck(lib().moty_cuda_moe_upload_expert(self.h, eid, *(_p(a) for a in arrs)))
 
+    def upload_expert_i4(self, eid, g4, gs, u4, us, d4, ds):
+        """LFM2's int4 expert rows (nibble rows + f32 row scales); the layer must hold MOTY_WF_I8 experts."""
+        a4 = [np.ascontiguousarray(a, np.uint8) for a in (g4, u4, d4)]
+        sc = [np.ascontiguousarray(a, np.float32) for a in (gs, us, ds)]
+        _ck(lib().moty_cuda_moe_upload_expert_i4(self.h, eid, _p(a4[0]), _p(sc[0]), _p(a4[1]), _p(sc[1]), _p(a4[2]), _p(sc[2])))
+
     def set_sigmoid_gate(self, on: bool = True, expert_bias=None):
         """LFM2's gate (sigmoid + expert bias, nn/moe.c:10-25) instead of softmax + top-K."""
         b = None if expert_bias is None else np.ascontiguousarray(expert_bias, np.float32)

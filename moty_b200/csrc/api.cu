@@ -1264,6 +1264,34 @@ extern "C" int moty_cuda_moe_upload_expert(MotyCudaMoe *m, int eid, const void *
     return 0;
 }
 
+// LFM2's int4 experts (ebits <= 4; nn/moe.c:42,99-103,138,193-198): the nibble rows are expanded to the codes nibble - 8
+// on the way in and live in the layer's int8 slabs, so every int8 path (decode, batches, expert-parallel routes, both
+// gates) serves them with the reference's integer sums.  Twice the bytes of a packed layout in HBM.
+extern "C" int moty_cuda_moe_upload_expert_i4(MotyCudaMoe *m, int eid, const void *g4, const float *gs,
+                                              const void *u4, const float *us, const void *d4, const float *ds) {
+    if (!m || !g4 || !gs || !u4 || !us || !d4 || !ds) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert_i4: null argument");
+    if (m->efmt != MOTY_WF_I8) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert_i4: the layer must be created with MOTY_WF_I8 experts");
+    if (eid < m->e_lo || eid >= m->e_hi) return moty_set_error(MOTY_CUDA_EARG, "moe_upload_expert_i4: expert %d outside [%d,%d)", eid, m->e_lo, m->e_hi);
+    DevCtx *c = moty_ctx(m->device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", m->device);
+    MOTY_USE_DEVICE(m->device);
+    const size_t le = (size_t)(eid - m->e_lo);
+    const size_t gb4 = (size_t)m->I * ((m->D + 1) / 2), db4 = (size_t)m->D * ((m->I + 1) / 2);
+    CKR(moty_grow(c, &c->daux, 2 * gb4 + db4));
+    uint8_t *s4 = (uint8_t *)c->daux.p;
+    CK(cudaMemcpyAsync(s4, g4, gb4, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(s4 + gb4, u4, gb4, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync(s4 + 2 * gb4, d4, db4, cudaMemcpyHostToDevice, c->stream));
+    CKR(launch_i4_rows_to_i8(s4, (int8_t *)m->g + le * m->gcb, m->I, m->D, c->stream));
+    CKR(launch_i4_rows_to_i8(s4 + gb4, (int8_t *)m->u + le * m->gcb, m->I, m->D, c->stream));
+    CKR(launch_i4_rows_to_i8(s4 + 2 * gb4, (int8_t *)m->d + le * m->dcb, m->D, m->I, c->stream));
+    CK(cudaMemcpyAsync((char *)m->gs + le * m->gsb, gs, m->gsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->us + le * m->gsb, us, m->gsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaMemcpyAsync((char *)m->ds + le * m->dsb, ds, m->dsb, cudaMemcpyHostToDevice, c->stream));
+    CK(cudaStreamSynchronize(c->stream));
+    return 0;
+}
+
 extern "C" int moty_cuda_moe_set_router(MotyCudaMoe *m, MotyCudaMat *router) {
     if (!m) return moty_set_error(MOTY_CUDA_EARG, "moe_set_router: null");
     if (router && (router->O != m->E || router->I != m->D || router->device != m->device))

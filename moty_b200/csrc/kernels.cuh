@@ -151,6 +151,9 @@ int launch_q4r4_stream(const uint8_t *w, const uint16_t *d, const float *x, cons
 // ---- selftest.cu: the give-up path of the bounded waits, run on purpose with a short limit ----
 int launch_selftest_expire(int which, int *err_dev, unsigned *gridbar_words, cudaStream_t st);
 
+// per-row int4 rows -> int8 codes (nibble - 8), quant.cu
+int launch_i4_rows_to_i8(const uint8_t *q4, int8_t *q8, long long rows, int n, cudaStream_t st);
+
 // ---- hostio.cu: activations in / results out between mapped (pinned) host buffers and the device, by kernels ----
 int launch_stage_in(float *dst, const float *src_host, long long n, cudaStream_t st);
 int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, unsigned seq, int sms,

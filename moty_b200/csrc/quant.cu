@@ -244,3 +244,28 @@ int launch_pack_q4r4(const float *w, int O, int I, uint8_t *q4, uint16_t *s16, c
     CK(cudaGetLastError());
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Per-row int4 rows (element 2j in the low nibble, 2j + 1 in the high one; hw/hw_scalar.h:14-22) -> signed int8 codes
+// nibble - 8, rows of n codes from rows of (n + 1) / 2 bytes.  The integer dot over these codes IS the reference's
+// dot_i4i8 / dot_i4i8p sum (hw/hw_avx512.h:106-145), so an int4 expert stored this way runs through the int8 kernels
+// with the reference's bits.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) i4_rows_to_i8_kernel(const uint8_t *__restrict__ q4, int8_t *__restrict__ q8, long long rows, int n) {
+    const int rb = (n + 1) / 2;
+    const long long total = rows * (long long)n;
+    for (long long i = (long long)blockIdx.x * 256 + threadIdx.x; i < total; i += (long long)gridDim.x * 256) {
+        const long long r = i / n; const int j = (int)(i - r * n);
+        const uint8_t b = q4[r * rb + (j >> 1)];
+        q8[i] = (int8_t)(((j & 1) ? (b >> 4) : (b & 15)) - 8);
+    }
+}
+
+int launch_i4_rows_to_i8(const uint8_t *q4, int8_t *q8, long long rows, int n, cudaStream_t st) {
+    if (rows <= 0 || n <= 0) return 0;
+    long long blocks = (rows * (long long)n + 255) / 256;
+    if (blocks > 4096) blocks = 4096;
+    i4_rows_to_i8_kernel<<<(unsigned)blocks, 256, 0, st>>>(q4, q8, rows, n);
+    CK(cudaGetLastError());
+    return 0;
+}

@@ -63,6 +63,16 @@ class _ExpertsI8(C.Structure):
                 ("gs", C.c_void_p), ("us", C.c_void_p), ("ds", C.c_void_p)]
 
 
+def unpack_i4_rows(q4, n):
+    """Per-row int4 rows [..., (n+1)/2] (element 2j in the low nibble, 2j+1 in the high one; hw/hw_scalar.h:14-22) as the
+    signed codes nibble - 8 in int8 [..., n]: the integer dots over them are the reference's dot_i4i8 / dot_i4i8p sums."""
+    q4 = np.ascontiguousarray(q4, np.uint8)
+    out = np.empty(q4.shape[:-1] + (q4.shape[-1] * 2,), np.int8)
+    out[..., 0::2] = (q4 & 15).astype(np.int16) - 8
+    out[..., 1::2] = (q4 >> 4).astype(np.int16) - 8
+    return np.ascontiguousarray(out[..., :n])
+
+
 class Experts:
     """Expert-major arrays of one MoE layer (int8 per-row or Q4R4)."""
 
@@ -645,6 +655,16 @@ class Ref:
         out = np.empty((S, ex.D), np.float32)
         self.lib.refshim_moe_sigmoid(C.byref(ex.c), C.c_int(WF_I8), None, _p(router_q), _p(_f32(router_qs)),
                                      _p(_f32(bias)) if bias is not None else None, _p(x), C.c_int(S), _p(out))
+        return out
+
+    def moe_i4_block(self, ex4, x, router_q, router_qs, sig=False, bias=None):
+        """nn/moe.c block over per-row int4 experts (ebits = 4; ``ex4`` is an Experts whose g / u / d hold the nibble
+        rows [E][I][(D+1)/2], [E][I][(D+1)/2], [E][D][(I+1)/2]), softmax or sigmoid gate, int8 router.  The batch path
+        (S > 1) is integer only with IDOT4=1, which this module sets before the library is loaded."""
+        x = _f32(x).reshape(-1, ex4.D); S = x.shape[0]
+        out = np.empty((S, ex4.D), np.float32)
+        self.lib.refshim_moe_i4(C.byref(ex4.c), C.c_int(WF_I8), None, _p(router_q), _p(_f32(router_qs)), C.c_int(1 if sig else 0),
+                                _p(_f32(bias)) if bias is not None else None, _p(x), C.c_int(S), _p(out))
         return out
 
     def olmoe_moe(self, ex, x, logits, norm_topk):

@@ -38,33 +38,52 @@ static void shim_load_expert(void *ctx, int layer, int eid, ExpertSlot *s, int i
     memcpy(s->ds, ex->ds + (size_t)eid * hidden, sizeof(float) * hidden);
 }
 
+/* the same for experts stored as per-row int4 (ebits <= 4: nibble rows, element 2j in the low nibble; nn/moe.h:12):
+ * ex->g / u / d then point at [E][I][(D+1)/2], [E][I][(D+1)/2], [E][D][(I+1)/2] bytes */
+static void shim_load_expert_i4(void *ctx, int layer, int eid, ExpertSlot *s, int inter, int hidden) {
+    const ShimExperts *ex = ctx; (void)layer;
+    size_t ngu = (size_t)inter * ((hidden + 1) / 2), nd = (size_t)hidden * ((inter + 1) / 2);
+    memcpy(s->g, ex->g + (size_t)eid * ngu, ngu);
+    memcpy(s->u, ex->u + (size_t)eid * ngu, ngu);
+    memcpy(s->d, ex->d + (size_t)eid * nd, nd);
+    memcpy(s->gs, ex->gs + (size_t)eid * inter, sizeof(float) * inter);
+    memcpy(s->us, ex->us + (size_t)eid * inter, sizeof(float) * inter);
+    memcpy(s->ds, ex->ds + (size_t)eid * hidden, sizeof(float) * hidden);
+}
+
 /* The reference MoE block with a softmax/top-k gate, all experts resident
  * (cache capacity = E, so nothing is ever evicted), no shared expert.
  * router_fmt: WF_F32 (router_f = [E][D] floats) or WF_I8 (router_q + router_qs).
  * S == 1 takes the decode path, S > 1 the batch path. */
 static void shim_moe_block(const ShimExperts *ex, int router_fmt, const float *router_f, const int8_t *router_q,
-                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias);
+                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias, int ebits);
+/* either gate over per-row int4 experts (the decode path is integer throughout; the batch path goes through
+ * moty_matmul_i4_s, whose integer form needs IDOT4=1 in the environment before its first call) */
+void refshim_moe_i4(const ShimExperts *ex, int router_fmt, const float *router_f, const int8_t *router_q,
+                    const float *router_qs, int sig, const float *bias, const float *x, int S, float *out) {
+    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, sig, bias, 4);
+}
 void refshim_moe_topk(const ShimExperts *ex, int router_fmt, const float *router_f,
                       const int8_t *router_q, const float *router_qs,
                       const float *x, int S, float *out) {
-    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 0, NULL);
+    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 0, NULL, 8);
 }
 /* the same block behind the sigmoid + expert-bias gate of LFM2 (moty_nn_moe_sigmoid_d1 / _batch, nn/moe.c:154,207) */
 void refshim_moe_sigmoid(const ShimExperts *ex, int router_fmt, const float *router_f,
                          const int8_t *router_q, const float *router_qs, const float *bias,
                          const float *x, int S, float *out) {
-    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 1, bias);
+    shim_moe_block(ex, router_fmt, router_f, router_q, router_qs, x, S, out, 1, bias, 8);
 }
 static void shim_moe_block(const ShimExperts *ex, int router_fmt, const float *router_f, const int8_t *router_q,
-                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias) {
+                           const float *router_qs, const float *x, int S, float *out, int sig, const float *bias, int ebits) {
     Mat router; mat_reset_storage(&router);
     router.fmt = router_fmt; router.O = ex->E; router.I = ex->D;
     router.f = (float *)router_f; router.q = (int8_t *)router_q; router.qs = (float *)router_qs;
     ExpertCache ec; moty_expert_cache_init(&ec, ex->E, ex->E);
     Scratch scr; memset(&scr, 0, sizeof scr);
     MotyMoeView v; memset(&v, 0, sizeof v);
-    v.router = &router; v.ec = &ec; v.load_expert = shim_load_expert; v.ectx = (void *)ex;
-    v.E = ex->E; v.K = ex->K; v.I = ex->I; v.D = ex->D; v.li = 0; v.ebits = 8; v.scr = &scr;
+    v.router = &router; v.ec = &ec; v.load_expert = ebits <= 4 ? shim_load_expert_i4 : shim_load_expert; v.ectx = (void *)ex;
+    v.E = ex->E; v.K = ex->K; v.I = ex->I; v.D = ex->D; v.li = 0; v.ebits = ebits; v.scr = &scr;
     v.expert_bias = bias;
     if (sig) { if (S == 1) moty_nn_moe_sigmoid_d1(&v, x, out); else moty_nn_moe_sigmoid_batch(&v, x, S, out); }
     else if (S == 1) moty_nn_moe_topk_d1(&v, x, out);

@@ -215,6 +215,28 @@ def sigmoid_blocks(r, save):
     save("blocks_sigmoid", **blk)
 
 
+def i4_expert_blocks(r, save):
+    """The MoE block over per-row int4 experts (LFM2's ebits = 4; nn/moe.c:42,99-103,138,193-198), both gates, decode and
+    batch (the batch path through moty_matmul_i4_s with IDOT4=1); its own file and random stream:
+    python tests/golden/make_golden.py i4experts"""
+    rs_ = np.random.default_rng(20261128)
+    E, K, I2, D2 = 12, 3, 96, 192                       # row lengths that leave a scalar tail behind the 64-wide steps
+    g4 = rs_.integers(0, 256, (E, I2, D2 // 2), dtype=np.uint8); u4 = rs_.integers(0, 256, (E, I2, D2 // 2), dtype=np.uint8)
+    d4 = rs_.integers(0, 256, (E, D2, I2 // 2), dtype=np.uint8)
+    gs = rs_.uniform(0.01, 0.2, (E, I2)).astype(np.float32); us = rs_.uniform(0.01, 0.2, (E, I2)).astype(np.float32)
+    ds = rs_.uniform(0.01, 0.2, (E, D2)).astype(np.float32)
+    ex4 = Experts(E, K, I2, D2, g4, u4, d4, gs, us, ds)
+    rq, rsc = r.quantize_rows((rs_.standard_normal((E, D2)) * 0.1).astype(np.float32))
+    bias = (rs_.standard_normal(E) * 0.3).astype(np.float32)
+    blk = dict(g4=g4, u4=u4, d4=d4, gs=gs, us=us, ds=ds, rq=rq, rs=rsc, bias=bias, dims=np.array([E, K, I2, D2], np.int32))
+    for S in (1, 7):
+        x = rs_.standard_normal((S, D2)).astype(np.float32)
+        blk[f"x{S}"] = x; blk[f"logits{S}"] = r.matmul_q_s(x, rq, rsc)
+        blk[f"out_topk{S}"] = r.moe_i4_block(ex4, x, rq, rsc)
+        blk[f"out_sig{S}"] = r.moe_i4_block(ex4, x, rq, rsc, sig=True, bias=bias)
+    save("blocks_i4", **blk)
+
+
 def gelu_vectors(r, save):
     """gemma's GeGLU element step from the engine's own static gelu_tanh (engines/gemma.c:389-391,398): a dense sweep
     of the activation's working range, large and tiny magnitudes, and normal draws; its own file and random stream."""
@@ -267,6 +289,9 @@ if __name__ == "__main__":
     elif sys.argv[1:] == ["gelu"]:
         build()
         gelu_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
+    elif sys.argv[1:] == ["i4experts"]:
+        build()
+        i4_expert_blocks(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
     elif sys.argv[1:] == ["sigmoid"]:
         build()
         sigmoid_blocks(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))

@@ -375,6 +375,27 @@ def test_moe_q8_batch_on_tensor_cores(gpu, oracle, E, K, I, D, S, lo, hi):
         assert same_bits(tc, oracle.moe_batch(Experts(E, K, I, D, g, u, d, gs, us, ds), x, logits)[0])
 
 
+def test_moe_int4_experts_golden(gpu):
+    """LFM2's int4 experts (ebits = 4: per-row nibble rows, nn/moe.c:42,99-103,138,193-198) uploaded through
+    moty_cuda_moe_upload_expert_i4: vectors from the compiled reference's blocks over the PACKED rows, decode and batch,
+    softmax and sigmoid + bias gates, bit for bit (router on the GPU as an int8 matrix, and with logits handed in)."""
+    g = golden("blocks_i4")
+    E, K, I, D = (int(v) for v in g["dims"])
+    m = gpu.Moe(E, K, I, D)
+    for e in range(E):
+        m.upload_expert_i4(e, g["g4"][e], g["gs"][e], g["u4"][e], g["us"][e], g["d4"][e], g["ds"][e])
+    for router in (None, gpu.Mat.i8(g["rq"], g["rs"])):
+        m.set_router(router)
+        lg = (lambda S: g[f"logits{S}"]) if router is None else (lambda S: None)
+        m.set_sigmoid_gate(False)
+        assert same_bits(m.d1(g["x1"], lg(1)), g["out_topk1"]) and same_bits(m.batch(g["x7"], lg(7)), g["out_topk7"])
+        m.set_sigmoid_gate(True, g["bias"])
+        assert same_bits(m.d1(g["x1"], lg(1)), g["out_sig1"]) and same_bits(m.batch(g["x7"], lg(7)), g["out_sig7"])
+    q = gpu.Moe(E, K, I, D, efmt=gpu.WF_Q4R4)
+    with pytest.raises(gpu.MotyCudaError, match="MOTY_WF_I8"):
+        q.upload_expert_i4(0, g["g4"][0], g["gs"][0], g["u4"][0], g["us"][0], g["d4"][0], g["ds"][0])
+
+
 def test_moe_sigmoid_gate_golden_and_oracle(gpu, oracle):
     """LFM2's gate (sigmoid + expert bias, nn/moe.c:10-25) around int8 experts: vectors from the compiled reference's
     moty_nn_moe_sigmoid_d1 / _batch bit for bit (router on the GPU as an int8 matrix, and with logits handed in), then

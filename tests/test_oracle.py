@@ -226,6 +226,20 @@ def test_sigmoid_gate_block_golden(oracle):
     assert idx[0, 0] == 5 and abs(float(w.sum()) - 1) < 1e-6
 
 
+def test_int4_experts_are_the_int8_blocks_over_unpacked_codes(oracle):
+    """LFM2's int4 experts (nn/moe.c:42,99-103,138,193-198): the reference's blocks over the packed nibble rows equal
+    the restated int8 blocks over the codes nibble - 8 bit for bit -- decode (dot_i4i8p) and batch (moty_matmul_i4_s with
+    IDOT4=1), softmax and sigmoid + bias gates.  That identity is what the GPU upload of such experts relies on."""
+    from oracle import Experts, unpack_i4_rows
+    g = golden("blocks_i4")
+    E, K, I, D = (int(v) for v in g["dims"])
+    ex = Experts(E, K, I, D, unpack_i4_rows(g["g4"], D), unpack_i4_rows(g["u4"], D), unpack_i4_rows(g["d4"], I), g["gs"], g["us"], g["ds"])
+    assert same_bits(oracle.moe_d1(ex, g["x1"], g["logits1"])[0], g["out_topk1"])
+    assert same_bits(oracle.moe_batch(ex, g["x7"], g["logits7"])[0], g["out_topk7"])
+    assert same_bits(oracle.moe_sigmoid(ex, g["x1"], g["logits1"], g["bias"])[0], g["out_sig1"])
+    assert same_bits(oracle.moe_sigmoid(ex, g["x7"], g["logits7"], g["bias"])[0], g["out_sig7"])
+
+
 def test_gelu_tanh_golden(oracle):
     """gemma's GeGLU element step: the restatement (with the multiply-add contraction the reference build applies to
     x + 0.044715 x^3) against vectors from the engine's own static gelu_tanh, bit for bit.  Both call the C library's tanhf."""
