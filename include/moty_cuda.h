@@ -111,7 +111,9 @@ int moty_cuda_host_free(void *p);
  *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55)
  *   MOTY_WF_I4G  codes uint8 [O][I/2] (even element in the low nibble), scales f32 [O][I/32]: grouped int4,
  *                group size 32 (nn/quant.c:57-83); applied through the integer path of
- *                moty_matmul_i4_grouped_s (nn/matmul.c:164-197, IDOT4=1): I % 32 == 0, I <= 16384
+ *                moty_matmul_i4_grouped_s (nn/matmul.c:164-197, IDOT4=1) when I % 64 == 0 and I <= 16384,
+ *                else -- and always after moty_cuda_set_i4g_float_path(1) -- through its default product,
+ *                f32 activations x dequantized int4 (i4g_f32_rows, nn/matmul.c:196-253)
  *   MOTY_WF_F32  codes float [O][I], scales NULL (router matrices only)
  * The hook point in the loader is right after load_mat_bits / load_mat_r4 /
  * load_embed_q8 (runtime/rt_model_load.h:85-177, 209-226). */
@@ -138,6 +140,10 @@ int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *dev
  * synchronising the stream; pageable buffers take copy-engine transfers.  Same results; MOTY_CUDA_HOST_KERNELS=0 in the
  * environment forces the copies. */
 int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
+/* MOTY_WF_I4G products: 0 (default) = the integer path the reference takes with IDOT4=1 (bit-exact), 1 = the product it
+ * takes without that switch, f32 x int4 with one scale multiply per group of 32 (agrees with the reference to the f32
+ * rounding of a 32-term sum: its own SIMD tiers order that sum differently too).  Returns the previous value. */
+int moty_cuda_set_i4g_float_path(int on);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
 /* n (1..8) independent one-row products in ONE launch: y_dev[m] = mat_apply(w[m], x_dev[m], S = 1) for MOTY_WF_I8
  * matrices on one GPU with I % 16 == 0 and I <= 4096 (x_dev[m] 16-byte aligned; the pointers may repeat: the q, k, v

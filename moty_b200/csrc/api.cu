@@ -30,6 +30,8 @@ bool moty_debug_sync() {
     return on == 1;
 }
 
+static int g_i4g_float = 0;     // MOTY_WF_I4G products: 0 = integer path (the reference with IDOT4=1), 1 = f32 x int4 (its default)
+
 // Programmatic dependent launch is on unless the environment says MOTY_CUDA_PDL=0 (read once).
 bool moty_pdl_enabled() {
     static int on = -1;
@@ -334,7 +336,7 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
     if (S <= 0) return 0;
     const int I = w->I, O = w->O;
     if (w->fmt == MOTY_WF_F32) return launch_f32_rows((const float *)w->codes, x, y, S, I, O, st);
-    if (I > MOTY_QROW_MAX)
+    if (I > MOTY_QROW_MAX && w->fmt != MOTY_WF_I4G)             // (the grouped int4 layout has its f32 product below)
         return moty_set_error(MOTY_CUDA_ELIMIT, "mat_apply: I=%d exceeds %d (the reference switches to an f32 path there)", I, MOTY_QROW_MAX);
     if (w->fmt == MOTY_WF_I8) {
         // more than 8 rows go to the tensor cores (a 16-token tile, rows past S are zero fill);
@@ -450,9 +452,11 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
                               (const float *)c->sx.p, y, S, I, O, st);
     }
     if (w->fmt == MOTY_WF_I4G) {
-        // the integer path of moty_matmul_i4_grouped_s (IDOT4=1): rows longer than the quantizer's limit would take the
-        // reference's f32 dequant product, which is not built
-        if (I > MOTY_QROW_MAX) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: I4G rows up to %d (I=%d)", MOTY_QROW_MAX, I);
+        // moty_matmul_i4_grouped_s: the integer path (IDOT4=1) unless the caller asked for the reference's default, the
+        // f32 x int4 product (moty_cuda_set_i4g_float_path); rows the integer path does not take (longer than the
+        // quantizer's limit, or not a multiple of 64: nn/matmul.c:172) go to the f32 product there and here
+        if (g_i4g_float || I > MOTY_QROW_MAX || (I & 63))
+            return launch_i4g_f32_rows((const uint8_t *)w->codes, (const float *)w->scales, x, y, S, I, O, st);
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->sx, (size_t)S * 4));
         CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
@@ -465,6 +469,12 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
                                (const float *)c->sx.p, y, S, I, O, st);
     }
     return moty_set_error(MOTY_CUDA_EARG, "mat_apply: format %d", w->fmt);
+}
+
+extern "C" int moty_cuda_set_i4g_float_path(int on) {
+    const int prev = g_i4g_float;
+    g_i4g_float = on ? 1 : 0;
+    return prev;
 }
 
 extern "C" int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream) {

@@ -108,6 +108,8 @@ size_t q4r4_gemv2_scratch_bytes(int I, int O);
 int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float *y, float *ab, int *err,
                       int I, int O, int q8, int sms, cudaStream_t st);
 
+// the reference's default (IDOT4 unset) product for the same layout: f32 activations x dequantized int4
+int launch_i4g_f32_rows(const uint8_t *w4, const float *scale, const float *x, float *y, int S, int I, int O, cudaStream_t st);
 int launch_i4g_gemv2(const uint8_t *w4, const float *gscale, const int8_t *xi, const float *sx, float *y, float *ab,
                      int *err, int I, int O, int sms, cudaStream_t st);
 

@@ -232,6 +232,14 @@ class Oracle:
         self.lib.oracle_matmul_i4g_idot_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
         return y
 
+    def matmul_i4g_f32_s(self, x, q4, scale):
+        """WF_I4G, group 32, the reference's default product (no IDOT4): f32 x dequantized int4."""
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); scale = _f32(scale)
+        S, I = x.shape; O = scale.shape[0]
+        y = np.empty((S, O), np.float32)
+        self.lib.oracle_matmul_i4g_f32_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O))
+        return y
+
     def matmul_q4r4_s(self, x, q4, s16, O):
         x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); s16 = np.ascontiguousarray(s16, np.uint16)
         S, I = x.shape
@@ -571,6 +579,16 @@ class Ref:
         y = np.empty((S, O), np.float32)
         self.lib.moty_matmul_i4_grouped_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O), C.c_int(32))
         return y
+
+    def matmul_i4g_any(self, x, q4, scale):
+        """moty_matmul_i4_grouped_s as the process's IDOT4 setting and the shape select it (gs = 32): rows that are not a
+        multiple of 64 always take the f32 x int4 product (nn/matmul.c:172), whatever IDOT4 says."""
+        x = _f32(x); q4 = np.ascontiguousarray(q4, np.uint8); scale = _f32(scale)
+        S, I = x.shape; O = scale.shape[0]
+        y = np.empty((S, O), np.float32)
+        self.lib.moty_matmul_i4_grouped_s(_p(y), _p(x), _p(q4), _p(scale), C.c_int(S), C.c_int(I), C.c_int(O), C.c_int(32))
+        return y
+
 
     def pack_q4r4(self, w):
         w = _f32(w); O, I = w.shape

@@ -231,6 +231,34 @@ ORACLE_API void oracle_matmul_i4g_idot_s(float *y, const float *x, const uint8_t
     free(xi); free(sx);
 }
 
+/* The same layout through the reference's DEFAULT product (no IDOT4): f32 activations x dequantized int4, one scale
+ * multiply per group (i4g_f32_rows, nn/matmul.c:196-253): a += (sum_j x[j] * (float)(nibble_j - 8)) * scl[g] in
+ * ascending group order.  The sum inside a group is taken here in element order; the reference's SIMD tiers take it in
+ * their own lane orders, so this restatement agrees with the compiled reference to f32 rounding, not bit for bit. */
+ORACLE_API void oracle_matmul_i4g_f32_s(float *y, const float *x, const uint8_t *q4, const float *scale,
+                                        int S, int I, int O) {
+    int rb = (I + 1) / 2, ng = (I + 31) / 32;
+    #pragma omp parallel for schedule(static)
+    for (int o = 0; o < O; o++) {
+        const uint8_t *w4 = q4 + (size_t)o * rb;
+        const float *scl = scale + (size_t)o * ng;
+        for (int s = 0; s < S; s++) {
+            const float *xs = x + (size_t)s * I;
+            float a = 0.f;
+            for (int g = 0; g < ng; g++) {
+                float p = 0.f;
+                for (int e = g * 32; e < g * 32 + 32 && e < I; e++) {
+                    uint8_t b = w4[e >> 1];
+                    int v = (e & 1) ? (b >> 4) : (b & 0xF);
+                    p += xs[e] * (float)(v - 8);
+                }
+                a += p * scl[g];
+            }
+            y[(size_t)s * O + o] = a;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ */
 /* Q4R4: 4-row blocks, groups of 32, f16 scale stream                  */
 /* ------------------------------------------------------------------ */

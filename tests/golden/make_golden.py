@@ -237,6 +237,22 @@ def i4_expert_blocks(r, save):
     save("blocks_i4", **blk)
 
 
+def i4g_f32_vectors(r, save):
+    """WF_I4G through the reference's default product, f32 x dequantized int4 (i4g_f32_rows, nn/matmul.c:196-253).  The
+    driver latches IDOT4 on its first call, so this function must run in a process started with IDOT4=0 (the __main__
+    branch below re-executes itself that way); the row length 96 takes this product under either setting.
+    python tests/golden/make_golden.py i4g_f32"""
+    assert os.environ.get("IDOT4") == "0"
+    rg = np.random.default_rng(20261129)
+    d = {}
+    for tag, (O, I, S) in {"a": (40, 256, 3), "b": (17, 96, 2), "c": (64, 1024, 1)}.items():
+        q4 = rg.integers(0, 256, (O, I // 2), dtype=np.uint8)
+        sc = rg.uniform(0.001, 0.02, (O, I // 32)).astype(np.float32)
+        x = rg.standard_normal((S, I)).astype(np.float32)
+        d[f"q4_{tag}"] = q4; d[f"s_{tag}"] = sc; d[f"x_{tag}"] = x; d[f"y_{tag}"] = r.matmul_i4g_any(x, q4, sc)
+    save("i4g_f32", **d)
+
+
 def gelu_vectors(r, save):
     """gemma's GeGLU element step from the engine's own static gelu_tanh (engines/gemma.c:389-391,398): a dense sweep
     of the activation's working range, large and tiny magnitudes, and normal draws; its own file and random stream."""
@@ -289,6 +305,12 @@ if __name__ == "__main__":
     elif sys.argv[1:] == ["gelu"]:
         build()
         gelu_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
+    elif sys.argv[1:] == ["i4g_f32"]:
+        if os.environ.get("IDOT4") != "0":                  # the reference reads IDOT4 once per process
+            import subprocess
+            sys.exit(subprocess.call([sys.executable, os.path.abspath(__file__), "i4g_f32"], env={**os.environ, "IDOT4": "0"}))
+        build()
+        i4g_f32_vectors(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))
     elif sys.argv[1:] == ["i4experts"]:
         build()
         i4_expert_blocks(Ref(), lambda name, **kw: np.savez_compressed(os.path.join(OUT, name + ".npz"), **kw))

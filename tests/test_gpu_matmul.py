@@ -181,12 +181,17 @@ def test_i4_rows(gpu, oracle):
 @pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1022, 3072), (515, 3840), (258, 15360), (77, 16384), (5, 32), (300, 96)])
 @pytest.mark.parametrize("S", [1, 2, 3, 4, 7, 8, 19])
 def test_i4g_vs_oracle(gpu, oracle, O, I, S):
-    """WF_I4G (grouped int4, group 32, f32 group scales), integer path: ragged rows and token tiles, the longest row."""
+    """WF_I4G (grouped int4, group 32, f32 group scales), integer path: ragged rows and token tiles, the longest row.
+    Row lengths that are not a multiple of 64 take the f32 x int4 product, as in the reference (nn/matmul.c:172)."""
     rng = np.random.default_rng(O * 11 + I + S)
     Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
     q4, sc = oracle.pack_int4_grouped(Wf)
     x = rng.standard_normal((S, I)).astype(np.float32)
     y = gpu.mat_apply(gpu.Mat.i4g(q4, sc, O, I), x)
+    if I % 64:
+        yo = oracle.matmul_i4g_f32_s(x, q4, sc)
+        assert np.abs(y - yo).max() <= 2e-6 * np.abs(yo).max()
+        return
     yo = oracle.matmul_i4g_idot_s(x, q4, sc)
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
@@ -287,3 +292,35 @@ def test_host_entry_with_pinned_buffers_equals_pageable(gpu, oracle):
             y2 = gpu.pinned_empty((S, O), np.float32)
             gpu.mat_apply(W, off, y2)                                      # misaligned pinned x -> copies
             assert y2.tobytes() == want.tobytes()
+
+
+def test_i4g_float_path(gpu, oracle):
+    """MOTY_WF_I4G through the reference's default product (f32 x int4, no activation quantizer) after
+    moty_cuda_set_i4g_float_path(1): the reference's vectors and the oracle at 1e-6 of the output magnitude (a 32-term f32
+    sum in another order); row lengths that are not a multiple of 64 take it under either setting, as in the reference;
+    the default stays the bit-exact integer path."""
+    g = golden("i4g_f32")
+    L = gpu.lib()
+    for t in "abc":
+        x, q4, sc, want = g[f"x_{t}"], g[f"q4_{t}"], g[f"s_{t}"], g[f"y_{t}"]
+        O, I = sc.shape[0], x.shape[1]
+        W = gpu.Mat.i4g(q4, sc, O, I)
+        prev = L.moty_cuda_set_i4g_float_path(1)
+        y = gpu.mat_apply(W, x)
+        L.moty_cuda_set_i4g_float_path(prev)
+        assert np.abs(y - want).max() <= 1e-6 * np.abs(want).max(), t
+        y0 = gpu.mat_apply(W, x)                                            # default setting
+        if I % 64 == 0:
+            assert y0.tobytes() == oracle.matmul_i4g_idot_s(x, q4, sc).tobytes()
+        else:
+            assert y0.tobytes() == y.tobytes()
+    rng = np.random.default_rng(5)
+    for (O, I, S) in ((1000, 4096, 1), (333, 2080, 9), (64, 16416, 2)):     # the last: longer than the integer path takes
+        q4 = rng.integers(0, 256, (O, I // 2), dtype=np.uint8); sc = rng.uniform(0.001, 0.02, (O, I // 32)).astype(np.float32)
+        x = rng.standard_normal((S, I)).astype(np.float32)
+        W = gpu.Mat.i4g(q4, sc, O, I)
+        prev = L.moty_cuda_set_i4g_float_path(1)
+        y = gpu.mat_apply(W, x)
+        L.moty_cuda_set_i4g_float_path(prev)
+        want = oracle.matmul_i4g_f32_s(x, q4, sc)
+        assert np.abs(y - want).max() <= 2e-6 * np.abs(want).max(), (O, I, S)

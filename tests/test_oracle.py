@@ -240,6 +240,20 @@ def test_int4_experts_are_the_int8_blocks_over_unpacked_codes(oracle):
     assert same_bits(oracle.moe_sigmoid(ex, g["x7"], g["logits7"], g["bias"])[0], g["out_sig7"])
 
 
+def test_i4g_float_path_golden(oracle):
+    """WF_I4G through the reference's default product (f32 x dequantized int4, nn/matmul.c:196-253; vectors generated in
+    a process with IDOT4=0): the restatement sums a group in element order, the reference in its SIMD tier's lane order,
+    so they agree to the f32 rounding of a 32-term sum (1e-6 of the output magnitude), not bit for bit -- and the vectors
+    are NOT the integer path's (which differs by several 1e-3)."""
+    g = golden("i4g_f32")
+    for t in "abc":
+        x, q4, sc, want = g[f"x_{t}"], g[f"q4_{t}"], g[f"s_{t}"], g[f"y_{t}"]
+        got = oracle.matmul_i4g_f32_s(x, q4, sc)
+        assert np.abs(got - want).max() <= 1e-6 * np.abs(want).max(), t
+        if x.shape[1] % 64 == 0:
+            assert np.abs(oracle.matmul_i4g_idot_s(x, q4, sc) - want).max() > 1e-4 * np.abs(want).max()
+
+
 def test_gelu_tanh_golden(oracle):
     """gemma's GeGLU element step: the restatement (with the multiply-add contraction the reference build applies to
     x + 0.044715 x^3) against vectors from the engine's own static gelu_tanh, bit for bit.  Both call the C library's tanhf."""
