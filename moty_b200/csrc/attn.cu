@@ -410,23 +410,30 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     }
 }
 
-// Prompts (head_dim <= 128).  A CTA takes 32 query rows that share every key and value row: consecutive tokens x the
+// Prompts.  A CTA takes 32 query rows that share every key and value row: consecutive tokens x the
 // query heads of one KV head (8 tokens x 4 heads, 16 x 2 or 32 x 1).  The positions are walked 64 at a time: the sub-chunk's key and value rows
 // are staged in shared memory once (int8 rows as their codes, scales aside), the 32 x 64 scores are register-tiled
 // dot products from shared memory (thread = one position x eight rows, no shuffles), one warp per token keeps the
 // running maximum and sum of its four rows, and the same warp accumulates its token's rows over the staged value
-// rows (lane = four dimensions).  Causal: a position past a token's own scores -1e30 and weighs 0.
-constexpr int AP_CH = 64, AP_HD = 128, AP_KP = AP_HD + 4, AP_PP = AP_CH + 4;
-constexpr size_t AP_SMEM = ((size_t)32 * AP_KP + (size_t)AP_CH * AP_KP + (size_t)AP_CH * AP_HD + (size_t)32 * AP_PP + 2 * AP_CH + 3 * 32) * 4;
+// rows (lane = four dimensions per 128).  Causal: a position past a token's own scores -1e30 and weighs 0; a sliding
+// layer starts at the first sub-chunk any of the CTA's tokens can see.  HD = 128 (two CTAs per SM) or 256 (one).
+constexpr int AP_CH = 64, AP_PP = AP_CH + 4;
+template <int HD> struct ApL {
+    static constexpr int KP = HD + 4;
+    static constexpr size_t SMEM = ((size_t)32 * KP + (size_t)AP_CH * KP + (size_t)AP_CH * HD + (size_t)32 * AP_PP + 2 * AP_CH + 3 * 32) * 4;
+};
 
-__global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
+template <int HD>
+__global__ void __launch_bounds__(256, HD == 128 ? 2 : 1) attn_prompt_kernel(AttnArgs a) {
+    constexpr int AP_KP = ApL<HD>::KP, NQ4 = HD / 4, NV = HD / 128;
     extern __shared__ float sm_attn[];
     float *Qs = sm_attn;                                  // [32][AP_KP]   row = token * 4 + head
     float *Kc = Qs + 32 * AP_KP;                          // [AP_CH][AP_KP]
-    float *Vc = Kc + AP_CH * AP_KP;                       // [AP_CH][AP_HD]
-    float *P = Vc + AP_CH * AP_HD;                        // [32][AP_PP]   scores, then weights
+    float *Vc = Kc + AP_CH * AP_KP;                       // [AP_CH][HD]
+    float *P = Vc + AP_CH * HD;                           // [32][AP_PP]   scores, then weights
     float *ksc = P + 32 * AP_PP, *vsc = ksc + AP_CH;      // row scales of an int8 cache
     float *m_s = vsc + AP_CH, *l_s = m_s + 32, *f_s = l_s + 32;
+    (void)f_s;
     const int hd = a.hd, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.H / a.KV, ngy = (G + AT_G - 1) / AT_G;
     const int kvh = blockIdx.y / ngy, g0 = (blockIdx.y - kvh * ngy) * AT_G;
@@ -440,28 +447,33 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
     const size_t base = (size_t)kvh * a.max_t;
     pdl_trigger();
     pdl_wait();
-    for (int i = tid; i < 32 * AP_HD; i += 256) {
-        const int row = i >> 7, dd = i & 127, tok = row >> lg, g = row & (ngp - 1);
+    for (int i = tid; i < 32 * HD; i += 256) {
+        const int row = i / HD, dd = i - row * HD, tok = row >> lg, g = row & (ngp - 1);
         Qs[row * AP_KP + dd] = tok < ntok && g < ng && dd < hd ? a.q[(size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + dd] : 0.f;
     }
     if (tid < 32) { m_s[tid] = -1e30f; l_s[tid] = 0.f; }
-    float4 acc[4];                                        // this warp's token, heads 0..3, dimensions 4 lane .. 4 lane + 3
+    float4 acc[4][NV];                                    // this warp's token, heads 0..3, dimensions 128 r + 4 lane .. + 3
 #pragma unroll
-    for (int j = 0; j < 4; j++) acc[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int j = 0; j < 4; j++)
+#pragma unroll
+        for (int r = 0; r < NV; r++) acc[j][r] = make_float4(0.f, 0.f, 0.f, 0.f);
     const int p_me = tid & 63, rg = tid >> 6;             // scores: my position in the sub-chunk, my eight rows rg * 8 ..
     const int hd4 = hd >> 2;
-    for (int c0 = 0; c0 < n_all; c0 += AP_CH) {
+    // a sliding layer: the CTA's first token sees positions from (pos_base + s0) - window + 1 on, the later ones from further on
+    int c_first = 0;
+    if (a.window > 0 && a.pos_base + s0 - a.window + 1 > 0) c_first = (a.pos_base + s0 - a.window + 1) / AP_CH * AP_CH;
+    for (int c0 = c_first; c0 < n_all; c0 += AP_CH) {
         const int nc = n_all - c0 < AP_CH ? n_all - c0 : AP_CH;
         __syncthreads();                                  // everyone is done with the previous sub-chunk (and Qs is written)
-        for (int i = tid; i < AP_CH * 32; i += 256) {     // stage: position i >> 5, dimensions 4 (i & 31) ..
-            const int pp = i >> 5, q4 = i & 31;
+        for (int i = tid; i < AP_CH * NQ4; i += 256) {    // stage: position i / NQ4, dimensions 4 (i % NQ4) ..
+            const int pp = i / NQ4, q4 = i - pp * NQ4;
             float4 kv = make_float4(0.f, 0.f, 0.f, 0.f), vv = kv;
             if (pp < nc && q4 < hd4) {
                 const size_t off = (base + c0 + pp) * hd + q4 * 4;
                 kv = attn_row4(a.K, a.K8, off); vv = attn_row4(a.V, a.V8, off);
             }
             *reinterpret_cast<float4 *>(Kc + pp * AP_KP + q4 * 4) = kv;
-            *reinterpret_cast<float4 *>(Vc + pp * AP_HD + q4 * 4) = vv;
+            *reinterpret_cast<float4 *>(Vc + pp * HD + q4 * 4) = vv;
         }
         if (tid < AP_CH) {
             ksc[tid] = a.K8 && tid < nc ? a.Ks[base + c0 + tid] : 1.f;
@@ -510,33 +522,43 @@ __global__ void __launch_bounds__(256, 2) attn_prompt_kernel(AttnArgs a) {
             row[lane + 32] = a.V8 ? __fmul_rn(e1, vsc[lane + 32]) : e1;
             __syncwarp();
             if (lane == 0) { m_s[warp * 4 + j] = m_new; l_s[warp * 4 + j] = fmaf(l_s[warp * 4 + j], f, sum); }
-            acc[j].x *= f; acc[j].y *= f; acc[j].z *= f; acc[j].w *= f;
+#pragma unroll
+            for (int r = 0; r < NV; r++) { acc[j][r].x *= f; acc[j][r].y *= f; acc[j][r].z *= f; acc[j][r].w *= f; }
         }
         __syncwarp();
-        // accumulation (hw/hw_ops.h:56-59): this warp's token over the staged value rows, lane = four dimensions
-        if (lane < hd4) {
+        // accumulation (hw/hw_ops.h:56-59): this warp's token over the staged value rows, lane = four dimensions per 128
+        {
             const float *pr = P + warp * 4 * AP_PP;
             for (int pp = 0; pp < nc; pp++) {
-                const float4 vv = *reinterpret_cast<const float4 *>(Vc + pp * AP_HD + lane * 4);
+                float w4[4];
 #pragma unroll
-                for (int j = 0; j < 4; j++) {
-                    const float w = pr[j * AP_PP + pp];
-                    acc[j].x = fmaf(w, vv.x, acc[j].x); acc[j].y = fmaf(w, vv.y, acc[j].y);
-                    acc[j].z = fmaf(w, vv.z, acc[j].z); acc[j].w = fmaf(w, vv.w, acc[j].w);
+                for (int j = 0; j < 4; j++) w4[j] = pr[j * AP_PP + pp];
+#pragma unroll
+                for (int r = 0; r < NV; r++) {
+                    if (r * 32 + lane < hd4) {
+                        const float4 vv = *reinterpret_cast<const float4 *>(Vc + pp * HD + (r * 32 + lane) * 4);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            acc[j][r].x = fmaf(w4[j], vv.x, acc[j][r].x); acc[j][r].y = fmaf(w4[j], vv.y, acc[j][r].y);
+                            acc[j][r].z = fmaf(w4[j], vv.z, acc[j][r].z); acc[j][r].w = fmaf(w4[j], vv.w, acc[j][r].w);
+                        }
+                    }
                 }
             }
         }
     }
     __syncwarp();
-    if (lane < hd4) {
+#pragma unroll
+    for (int r = 0; r < NV; r++) {
+        if (r * 32 + lane >= hd4) continue;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
             const int row = warp * 4 + j, tok = row >> lg, g = row & (ngp - 1);
             if (tok >= ntok || g >= ng) continue;
             const float l = l_s[row];
-            float4 o = acc[j];
+            float4 o = acc[j][r];
             o.x = __fdiv_rn(o.x, l); o.y = __fdiv_rn(o.y, l); o.z = __fdiv_rn(o.z, l); o.w = __fdiv_rn(o.w, l);
-            *reinterpret_cast<float4 *>(a.ctx + (size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + lane * 4) = o;
+            *reinterpret_cast<float4 *>(a.ctx + (size_t)(s0 + tok) * a.H * hd + (size_t)(head0 + g) * hd + (r * 32 + lane) * 4) = o;
         }
     }
 }
@@ -627,16 +649,19 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     // prompts: eight tokens per CTA share staged key and value rows, when that still gives every SM a CTA
     const int ng_cta = G < AT_G ? G : AT_G, tq = ng_cta > 2 ? 8 : (ng_cta == 2 ? 16 : 32);
     const long long tiles = (long long)((S + tq - 1) / tq) * KV * ngy;
-    if (S >= 8 && hd <= AP_HD && tiles >= sms && !pos_dev) {
+    if (S >= 8 && tiles >= sms && !pos_dev) {
         static bool attr_p[MOTY_MAX_DEV];
         int devp = 0;
         CK(cudaGetDevice(&devp));
         if (devp < 0 || devp >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "attn_core: device %d", devp);
         if (!attr_p[devp]) {
-            CK(cudaFuncSetAttribute(attn_prompt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)AP_SMEM));
+            CK(cudaFuncSetAttribute(attn_prompt_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ApL<128>::SMEM));
+            CK(cudaFuncSetAttribute(attn_prompt_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ApL<256>::SMEM));
             attr_p[devp] = true;
         }
-        CK(moty_launch_pdl(attn_prompt_kernel, dim3((S + tq - 1) / tq, KV * ngy), dim3(256), AP_SMEM, st, a));
+        const dim3 pgrid((S + tq - 1) / tq, KV * ngy);
+        if (hd <= 128) CK(moty_launch_pdl(attn_prompt_kernel<128>, pgrid, dim3(256), ApL<128>::SMEM, st, a));
+        else CK(moty_launch_pdl(attn_prompt_kernel<256>, pgrid, dim3(256), ApL<256>::SMEM, st, a));
         return 0;
     }
     // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
