@@ -86,6 +86,18 @@ int moty_cuda_selftest_expire_wait(int device, int which, void *stream);
  * the graph.  on = 0 lifts the freeze (graphs captured before must then be dropped).  No reference counterpart:
  * its drivers grow function-level static scratch with malloc (nn/matmul.c:55-58). */
 int moty_cuda_scratch_freeze(int device, int on);
+/* CUDA graphs for a caller that does not link the CUDA runtime itself (the reference is plain C): everything the *_dev
+ * entries enqueue on `stream` (NULL = the library's) between graph_begin and graph_end is captured instead of run;
+ * graph_launch replays it on that stream.  Rules: run the sequence once before capturing it (scratch, kernel
+ * attributes); between begin and end call only *_dev entries that enqueue work (no uploads from pageable memory, no
+ * downloads, no kernel_status); take positions from the device (moty_cuda_attn_core_posdev) and feed token ids and
+ * positions with moty_cuda_dev_upload before each launch.  graph_end freezes the scratch (as scratch_freeze does) until
+ * the graph is freed.  No reference counterpart. */
+typedef struct MotyCudaGraph MotyCudaGraph;
+int moty_cuda_graph_begin(int device, void *stream);
+int moty_cuda_graph_end(MotyCudaGraph **out, int device, void *stream);
+int moty_cuda_graph_launch(MotyCudaGraph *g);
+int moty_cuda_graph_free(MotyCudaGraph *g);
 
 /* Device memory for a C host that keeps its activations on the GPU between *_dev entries without the CUDA headers
  * (the reference is plain C): allocate, free, copy in (enqueued on `stream`, NULL = the library's; returns at once)

@@ -163,6 +163,64 @@ extern "C" int moty_cuda_scratch_freeze(int device, int on) {
     return 0;
 }
 
+// ---------------------------------------------------------------------------
+// CUDA graphs for callers that do not link the CUDA runtime (a plain-C engine): capture what the *_dev entries enqueue
+// on a stream between begin and end, replay it with launch.  The scratch is frozen from begin until the graph is freed
+// (it holds the scratch addresses), so the largest call of the captured sequence must have run once before.
+// ---------------------------------------------------------------------------
+static cudaStream_t pick_stream(DevCtx *c, void *stream) { return stream ? (cudaStream_t)stream : c->stream; }
+
+struct MotyCudaGraph { int device; cudaGraph_t graph; cudaGraphExec_t exec; cudaStream_t stream; bool froze; };
+
+extern "C" int moty_cuda_graph_begin(int device, void *stream) {
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    cudaStream_t st = pick_stream(c, stream);
+    CK(cudaStreamSynchronize(st));
+    CK(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+    return 0;
+}
+
+extern "C" int moty_cuda_graph_end(MotyCudaGraph **out, int device, void *stream) {
+    if (!out) return moty_set_error(MOTY_CUDA_EARG, "graph_end: null");
+    DevCtx *c = moty_ctx(device);
+    if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
+    MOTY_USE_DEVICE(device);
+    cudaStream_t st = pick_stream(c, stream);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(st, &g);
+    if (e != cudaSuccess || !g) { cudaGetLastError(); return moty_set_error(MOTY_CUDA_ECUDA, "graph_end: capture failed: %s", cudaGetErrorString(e)); }
+    cudaGraphExec_t ex = nullptr;
+    e = cudaGraphInstantiate(&ex, g, 0);
+    if (e != cudaSuccess) { cudaGraphDestroy(g); cudaGetLastError(); return moty_set_error(MOTY_CUDA_ECUDA, "graph_end: instantiate: %s", cudaGetErrorString(e)); }
+    MotyCudaGraph *h = new MotyCudaGraph{device, g, ex, st, !c->frozen};
+    c->frozen = true;
+    *out = h;
+    return 0;
+}
+
+extern "C" int moty_cuda_graph_launch(MotyCudaGraph *g) {
+    if (!g) return moty_set_error(MOTY_CUDA_EARG, "graph_launch: null");
+    MOTY_USE_DEVICE(g->device);
+    CK(cudaGraphLaunch(g->exec, g->stream));
+    return 0;
+}
+
+extern "C" int moty_cuda_graph_free(MotyCudaGraph *g) {
+    if (!g) return 0;
+    DevCtx *c = moty_ctx(g->device);
+    if (c) {
+        MOTY_USE_DEVICE(g->device);
+        cudaStreamSynchronize(g->stream);
+        if (g->froze) c->frozen = false;
+    }
+    cudaGraphExecDestroy(g->exec);
+    cudaGraphDestroy(g->graph);
+    delete g;
+    return 0;
+}
+
 extern "C" int moty_cuda_kernel_status(int device, void *stream) {
     DevCtx *c = moty_ctx(device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", device);
@@ -234,7 +292,6 @@ extern "C" int moty_cuda_host_free(void *p) {
     return 0;
 }
 
-static cudaStream_t pick_stream(DevCtx *c, void *stream) { return stream ? (cudaStream_t)stream : c->stream; }
 
 // ---------------------------------------------------------------------------
 // weights

@@ -53,9 +53,11 @@ static int shim_attach_model(Model *m, int dev) {
 typedef struct {
     int dev, cap_S, max_t;
     float *x, *nrm, *tmp, *q, *k, *v, *ctx, *logits, *final_norm;
-    int *ids;
+    int *ids, *pos;                   /* token ids of the step; the first position, for the captured decode step */
     float **in_ln, **post_ln;
     MotyCudaAttn **attn;
+    MotyCudaGraph *graph;             /* one decode token, captured after the first one has run (MOTY_SHIM_GRAPH=0: never) */
+    int decoded;
 } ShimDev;
 static ShimDev g_sd;
 
@@ -81,6 +83,8 @@ static void shim_dev_init(Model *m, int dev, int cap_S, int max_t) {
     d->logits = shim_dev_f32(NULL, c->vocab, dev);
     d->final_norm = shim_dev_f32(m->base.final_norm, D, dev);
     void *ids = NULL; SHIM_CK(moty_cuda_dev_alloc(&ids, (size_t)cap_S * 4, dev)); d->ids = ids;
+    void *pos = NULL; SHIM_CK(moty_cuda_dev_alloc(&pos, 4, dev)); d->pos = pos;
+    d->graph = NULL; d->decoded = 0;
     d->in_ln = calloc(c->n_layers, sizeof(float *)); d->post_ln = calloc(c->n_layers, sizeof(float *));
     d->attn = calloc(c->n_layers, sizeof(MotyCudaAttn *));
     for (int i = 0; i < c->n_layers; i++) {
@@ -105,16 +109,13 @@ static void shim_check(const char *what, const float *dev_buf, const float *host
     free(tmp);
 }
 
-/* returns the logits of the last token (malloc'd), like step() */
-static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
+/* the operations of one step on the device buffers; pos_dev != NULL: one token whose position is read from the device
+ * (the form a captured graph can replay).  A residual add and the norm after it are one launch, as in the reference's
+ * fused add+norm (hw/hw_ops.h:30-32 then :14-18; same bits). */
+static void shim_layers(Model *m, int S, int pos_base, const int *pos_dev, int check, const int *ids) {
     Cfg *c = &m->c; ShimDev *d = &g_sd;
     int D = c->hidden;
-    if (S > d->cap_S || pos_base + S > d->max_t) moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] step of %d tokens at %d exceeds the device buffers\n", S, pos_base);
-    static int checked;
-    const int check = !checked && getenv("MOTY_SHIM_CHECK") && atoi(getenv("MOTY_SHIM_CHECK"));
     float *hx = NULL, *hn = NULL, *ht = NULL;
-    checked = 1;
-    SHIM_CK(moty_cuda_dev_upload(d->ids, ids, (size_t)S * 4, d->dev, NULL));
     SHIM_CK(moty_cuda_embed_rows_dev((MotyCudaMat *)m->base.lm_head.sh, d->x, d->ids, S, 1.f, NULL));
     if (check) {
         kv_alloc(m, d->max_t);
@@ -122,9 +123,9 @@ static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
         for (int s = 0; s < S; s++) embed_row(m, ids[s], 1.f, hx + (int64_t)s * D);
         shim_check("embed", d->x, hx, (int64_t)S * D, d->dev);
     }
+    SHIM_CK(moty_cuda_rmsnorm_dev(d->nrm, d->x, d->in_ln[0], S, D, c->eps, NULL));
     for (int i = 0; i < c->n_layers; i++) {
         Layer *l = &m->L[i];
-        SHIM_CK(moty_cuda_rmsnorm_dev(d->nrm, d->x, d->in_ln[i], S, D, c->eps, NULL));
         if (check && i == 0) {
             for (int s = 0; s < S; s++) rmsnorm_row(hn + (int64_t)s * D, hx + (int64_t)s * D, l->in_ln, D, c->eps);
             shim_check("layer 0 input norm", d->nrm, hn, (int64_t)S * D, d->dev);
@@ -140,7 +141,8 @@ static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
             SHIM_CK(moty_cuda_mat_apply_dev((MotyCudaMat *)l->k.sh, d->k, d->nrm, S, NULL));
             SHIM_CK(moty_cuda_mat_apply_dev((MotyCudaMat *)l->v.sh, d->v, d->nrm, S, NULL));
         }
-        SHIM_CK(moty_cuda_attn_core_dev(d->attn[i], d->ctx, d->q, d->k, d->v, S, pos_base, NULL));
+        if (pos_dev) SHIM_CK(moty_cuda_attn_core_posdev(d->attn[i], d->ctx, d->q, d->k, d->v, S, pos_dev, d->max_t - 1, NULL));
+        else SHIM_CK(moty_cuda_attn_core_dev(d->attn[i], d->ctx, d->q, d->k, d->v, S, pos_base, NULL));
         SHIM_CK(moty_cuda_mat_apply_dev((MotyCudaMat *)l->o.sh, d->tmp, d->ctx, S, NULL));
         if (check && i == 0) shim_check("layer 0 attention + o", d->tmp, ht, (int64_t)S * D, d->dev);
         SHIM_CK(moty_cuda_add_rmsnorm_dev(d->x, d->tmp, d->nrm, d->post_ln[i], S, D, c->eps, NULL));      /* x += attn; nrm = norm(x) */
@@ -154,11 +156,41 @@ static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
         SHIM_CK(moty_cuda_ffn_dev((MotyCudaMat *)l->gate.sh, (MotyCudaMat *)l->up.sh, (MotyCudaMat *)l->down.sh, MOTY_ACT_SILU,
                                   d->tmp, d->nrm, S, NULL));
         if (check && i == 0) { shim_check("layer 0 FFN", d->tmp, ht, (int64_t)S * D, d->dev); free(hx); free(hn); free(ht); }
-        SHIM_CK(moty_cuda_add_dev(d->x, d->tmp, (long long)S * D, NULL));
+        if (i + 1 < c->n_layers)                        /* x += ffn; nrm = the next layer's input norm */
+            SHIM_CK(moty_cuda_add_rmsnorm_dev(d->x, d->tmp, d->nrm, d->in_ln[i + 1], S, D, c->eps, NULL));
+        else
+            SHIM_CK(moty_cuda_add_dev(d->x, d->tmp, (long long)S * D, NULL));
     }
-    m->base.kv_len = pos_base + S;
     SHIM_CK(moty_cuda_rmsnorm_dev(d->nrm, d->x + (int64_t)(S - 1) * D, d->final_norm, 1, D, c->eps, NULL));
     SHIM_CK(moty_cuda_mat_apply_dev((MotyCudaMat *)m->base.lm_head.sh, d->logits, d->nrm, 1, NULL));
+}
+
+/* returns the logits of the last token (malloc'd), like step().  Decode tokens after the first are replayed from a
+ * CUDA graph of one token (captured through the library, which holds the stream): the token id and the position are
+ * uploaded in front of each replay. */
+static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
+    Cfg *c = &m->c; ShimDev *d = &g_sd;
+    if (S > d->cap_S || pos_base + S > d->max_t) moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] step of %d tokens at %d exceeds the device buffers\n", S, pos_base);
+    static int checked;
+    const int check = !checked && getenv("MOTY_SHIM_CHECK") && atoi(getenv("MOTY_SHIM_CHECK"));
+    checked = 1;
+    static int use_graph = -1;
+    if (use_graph < 0) { const char *e = getenv("MOTY_SHIM_GRAPH"); use_graph = e ? atoi(e) : 1; }
+    SHIM_CK(moty_cuda_dev_upload(d->ids, ids, (size_t)S * 4, d->dev, NULL));
+    if (S == 1 && use_graph && !check) {
+        SHIM_CK(moty_cuda_dev_upload(d->pos, &pos_base, 4, d->dev, NULL));
+        if (!d->graph && d->decoded >= 1) {             /* the token before this one ran the same sequence uncaptured */
+            SHIM_CK(moty_cuda_graph_begin(d->dev, NULL));
+            shim_layers(m, 1, pos_base, d->pos, 0, ids);
+            SHIM_CK(moty_cuda_graph_end(&d->graph, d->dev, NULL));
+        }
+        if (d->graph) SHIM_CK(moty_cuda_graph_launch(d->graph));
+        else shim_layers(m, 1, pos_base, d->pos, 0, ids);
+        d->decoded++;
+    } else {
+        shim_layers(m, S, pos_base, NULL, check, ids);
+    }
+    m->base.kv_len = pos_base + S;
     float *logit = falloc(c->vocab);
     SHIM_CK(moty_cuda_dev_download(logit, d->logits, (size_t)c->vocab * 4, d->dev, NULL));
     SHIM_CK(moty_cuda_kernel_status(d->dev, NULL));
@@ -170,9 +202,13 @@ static float *shim_step_any(Model *m, const int *ids, int S, int pos_base) {
     return g_shim_resident ? shim_step_dev(m, ids, S, pos_base) : step(m, ids, S, pos_base);
 }
 
+/* FNV-1a over 64-bit words (the row is a multiple of 4 bytes; a last half word is taken alone): the trace hashes 600 KB
+ * per token, and byte by byte that cost more than the GPU's whole step */
 static uint64_t shim_fnv(const void *p, size_t n) {
     const unsigned char *b = p; uint64_t h = 1469598103934665603ULL;
-    for (size_t i = 0; i < n; i++) { h ^= b[i]; h *= 1099511628211ULL; }
+    size_t i = 0;
+    for (; i + 8 <= n; i += 8) { uint64_t w; memcpy(&w, b + i, 8); h ^= w; h *= 1099511628211ULL; }
+    for (; i < n; i++) { h ^= b[i]; h *= 1099511628211ULL; }
     return h;
 }
 
