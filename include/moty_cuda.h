@@ -149,8 +149,10 @@ int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *dev
  * Host pointers; returns with y written.  When x and y both lie in page-locked memory (moty_cuda_host_alloc,
  * cudaHostAlloc, cudaHostRegister; 16-byte aligned) and the product has no error word to report (MOTY_WF_I8 below 9
  * rows and the like), the bytes move by kernels chained to the product and the call waits on a flag word instead of
- * synchronising the stream; pageable buffers take copy-engine transfers.  Same results; MOTY_CUDA_HOST_KERNELS=0 in the
- * environment forces the copies. */
+ * synchronising the stream; a call that repeats with the same matrix and buffers (a decode loop) is replayed as one
+ * CUDA graph of those launches from its third occurrence on (dropped when the scratch moves or a matrix is freed).
+ * Pageable buffers take copy-engine transfers.  Same results; MOTY_CUDA_HOST_KERNELS=0 in the environment forces the
+ * copies. */
 int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
 /* MOTY_WF_I4G products: 0 (default) = the integer path the reference takes with IDOT4=1 (bit-exact), 1 = the product it
  * takes without that switch, f32 x int4 with one scale multiply per group of 32 (agrees with the reference to the f32

@@ -64,6 +64,7 @@ int moty_grow(DevCtx *c, Buf *b, size_t bytes) {
     size_t want = bytes + bytes / 4 + 256;
     CK(cudaMalloc(&b->p, want));
     b->cap = want;
+    c->gen++;
     return 0;
 }
 
@@ -124,7 +125,9 @@ extern "C" int moty_cuda_init(const int *devices, int ndev) {
     return 0;
 }
 
+static void host_calls_drop_all();
 extern "C" void moty_cuda_shutdown(void) {
+    host_calls_drop_all();
     for (int i = 0; i < g_nctx; i++) {
         DevCtx *c = &g_ctx[i];
         if (!c->ready) continue;
@@ -360,8 +363,10 @@ extern "C" int moty_cuda_upload_mat(MotyCudaMat **out, int fmt, const void *code
     return moty_cuda_upload_mat_rows(out, fmt, codes, scales, O, I, 0, O, device);
 }
 
+static unsigned long long g_mat_gen = 0;     // bumped when a matrix is freed: its address may come back with other contents
 extern "C" int moty_cuda_free_mat(MotyCudaMat *m) {
     if (!m) return 0;
+    g_mat_gen++;
     DevCtx *c = moty_ctx(m->device);
     if (c) { cudaSetDevice(m->device); cudaStreamSynchronize(c->stream); }
     if (m->codes) cudaFree(m->codes);
@@ -609,6 +614,19 @@ static bool host_kernels_on() {
     return on == 1;
 }
 
+// repeated host calls with pinned buffers, replayed as graphs (see mat_apply_host)
+struct HostCall { const MotyCudaMat *w; const void *x; void *y; int S, device; unsigned long long gen; cudaGraph_t graph; cudaGraphExec_t exec; };
+constexpr int HOST_CALLS = 32;
+static HostCall g_hostcalls[HOST_CALLS];
+static unsigned g_hostcall_next = 0;
+static void host_call_drop(HostCall *h) {
+    if (h->exec) cudaGraphExecDestroy(h->exec);
+    if (h->graph) cudaGraphDestroy(h->graph);
+    *h = HostCall{};
+}
+
+static void host_calls_drop_all() { for (int i = 0; i < HOST_CALLS; i++) host_call_drop(&g_hostcalls[i]); }
+
 // host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
 static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
     if (!w || !y || !x) return moty_set_error(MOTY_CUDA_EARG, "mat_apply: null argument");
@@ -631,20 +649,58 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
     if (!acc && !check && host_kernels_on() && (x_map = (const float *)mapped_alias(x, xb)) != nullptr &&
         (y_map = (float *)mapped_alias(y, yb)) != nullptr) {
         const unsigned seq = ++c->hseq;
-        CKR(launch_stage_in((float *)c->dx.p, x_map, (long long)S * w->I, c->stream));
-        CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, nullptr, c->stream));
-        CKR(launch_tail_out(y_map, (const float *)c->dy.p, (long long)S * w->O, reinterpret_cast<unsigned *>(c->ctr) + 8, c->hflag_dev, seq,
-                            c->sms, c->stream));
+        unsigned *ctr = reinterpret_cast<unsigned *>(c->ctr) + 8;
+        auto enqueue = [&]() -> int {
+            CKR(launch_stage_in((float *)c->dx.p, x_map, (long long)S * w->I, c->stream));
+            CKR(mat_apply_on(c, w, (float *)c->dy.p, (const float *)c->dx.p, S, nullptr, c->stream));
+            return launch_tail_out(y_map, (const float *)c->dy.p, (long long)S * w->O, ctr, c->hflag_dev, c->sms, c->stream);
+        };
+        // A call that repeats with the same matrix and buffers (a decode loop) is replayed as ONE graph of its three
+        // launches: first sight runs it launch by launch, second sight captures it, from then on one submission per call.
+        // A graph holds scratch and matrix addresses, so it is only used while neither has moved or been freed since.
+        HostCall *hit = nullptr, *slot = nullptr;
+        const unsigned long long gen = c->gen + g_mat_gen;
+        for (int i = 0; i < HOST_CALLS; i++) {
+            HostCall *h = &g_hostcalls[i];
+            if (h->w == w && h->x == x_map && h->y == y_map && h->S == S && h->device == w->device) { hit = h; break; }
+            if (!slot && !h->w) slot = h;
+        }
+        if (hit && hit->gen != gen) { host_call_drop(hit); hit = nullptr; }
+        if (hit && hit->exec) {
+            CK(cudaGraphLaunch(hit->exec, c->stream));
+        } else if (hit) {                                          // second sight: capture (the first run sized every buffer)
+            cudaGraph_t g = nullptr;
+            CK(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+            const int rc = enqueue();
+            const cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+            if (rc != 0 || e != cudaSuccess || !g || c->gen + g_mat_gen != gen || cudaGraphInstantiate(&hit->exec, g, 0) != cudaSuccess) {
+                cudaGetLastError();
+                if (g) cudaGraphDestroy(g);
+                hit->exec = nullptr; hit->w = nullptr;             // give up on this key for now
+                CKR(enqueue());
+            } else {
+                hit->graph = g;
+                CK(cudaGraphLaunch(hit->exec, c->stream));
+            }
+        } else {
+            if (!hit) {
+                if (!slot) { slot = &g_hostcalls[g_hostcall_next++ % HOST_CALLS]; host_call_drop(slot); }
+                slot->w = w; slot->x = x_map; slot->y = y_map; slot->S = S; slot->device = w->device; slot->gen = gen;
+                slot->exec = nullptr; slot->graph = nullptr;
+            }
+            CKR(enqueue());
+        }
         volatile unsigned *flag = c->hflag;
         for (long long spin = 0; *flag != seq; spin++) {
-            if (spin >= (1LL << 22)) {                             // a fraction of a second: let the driver wait (and report)
+            if (spin >= (1LL << 22) || ((spin & 1023) == 1023 && cudaStreamQuery(c->stream) != cudaErrorNotReady)) {
+                // a fraction of a second has passed, or the stream has drained (or failed): let the driver wait and report,
+                // then bring the host's count back in step with the device's
                 CK(cudaStreamSynchronize(c->stream));
-                if (*flag != seq) return moty_set_error(MOTY_CUDA_EKERNEL, "mat_apply: the result copy did not report completion");
-                break;
-            }
-            if ((spin & 1023) == 1023 && cudaStreamQuery(c->stream) != cudaErrorNotReady) {   // finished or failed: look once more
                 if (*flag == seq) break;
-                CK(cudaStreamSynchronize(c->stream));
+                unsigned dev_seq = 0;
+                CK(cudaMemcpy(&dev_seq, ctr + 1, 4, cudaMemcpyDeviceToHost));
+                c->hseq = dev_seq;
+                return moty_set_error(MOTY_CUDA_EKERNEL, "mat_apply: the result copy did not report completion");
             }
         }
         return 0;

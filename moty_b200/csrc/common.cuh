@@ -76,6 +76,8 @@ struct DevCtx {
     // host-pointer entries with pinned buffers (hostio.cu): a pinned flag word the last kernel of a call writes, its
     // device alias, and the sequence number of the latest call
     unsigned *hflag = nullptr, *hflag_dev = nullptr, hseq = 0;
+    // bumped whenever a scratch buffer of this device moves: cached graphs of host calls hold scratch addresses
+    unsigned long long gen = 0;
 };
 
 // Every entry point that makes a GPU current puts the caller's device back before it returns.

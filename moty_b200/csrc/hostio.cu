@@ -4,9 +4,10 @@
 // synchronisation after it a few more.  Page-locked host memory is mapped into the device's address space, so
 //   stage_in_kernel   reads x from the host buffer (coalesced 16-byte loads over PCIe) into the device scratch,
 //   tail_out_kernel   writes y from the device scratch to the host buffer (coalesced 16-byte stores), fences, and the
-//                     last CTA to finish stores the call's sequence number to a pinned flag word,
+//                     last CTA to finish stores the call's sequence number (counted on the device) to a pinned flag word,
 // and the host waits for that word (bounded; then it falls back to a stream synchronisation) instead of synchronising.
-// Both are chained to the product between them by programmatic dependent launch.  Pageable buffers (malloc) are not
+// Both are chained to the product between them by programmatic dependent launch, and a call that repeats (same matrix,
+// same buffers: a decode loop) is replayed as one CUDA graph of the three launches (api.cu), one submission instead of three.  Pageable buffers (malloc) are not
 // mapped: those calls keep the copy-engine path.
 #include "kernels.cuh"
 
@@ -20,8 +21,10 @@ __global__ void __launch_bounds__(256) stage_in_kernel(float *dst, const float *
     for (long long i = n4 * 4 + i0; i < n; i += step) dst[i] = src_host[i];
 }
 
+// ctr[0]: CTAs that have finished (zero between launches); ctr[1]: calls completed so far -- the value the flag word gets,
+// kept on the device so that a replayed CUDA graph of a call needs no new argument
 __global__ void __launch_bounds__(256) tail_out_kernel(float *dst_host, const float *src, long long n, unsigned *ctr,
-                                                       volatile unsigned *flag_host, unsigned seq) {
+                                                       volatile unsigned *flag_host) {
     __shared__ bool last;
     pdl_trigger();
     pdl_wait();                                            // the product's results
@@ -33,7 +36,9 @@ __global__ void __launch_bounds__(256) tail_out_kernel(float *dst_host, const fl
     if (threadIdx.x == 0) last = atomicAdd(ctr, 1u) == gridDim.x - 1;
     __syncthreads();
     if (last && threadIdx.x == 0) {
-        *ctr = 0;                                          // zero between launches
+        ctr[0] = 0;                                        // zero between launches
+        const unsigned seq = ctr[1] + 1;
+        ctr[1] = seq;
         __threadfence_system();
         *flag_host = seq;
     }
@@ -50,12 +55,11 @@ int launch_stage_in(float *dst, const float *src_host, long long n, cudaStream_t
     return 0;
 }
 
-int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, unsigned seq, int sms,
-                    cudaStream_t st) {
+int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, int sms, cudaStream_t st) {
     long long ctas = (n / 4 + 1023) / 1024;                // four 16-byte stores per thread
     if (ctas < 1) ctas = 1;
     if (ctas > sms) ctas = sms;
     CK(moty_launch_pdl(tail_out_kernel, dim3((unsigned)ctas), dim3(256), (size_t)0, st, dst_host, src, n, ctr,
-                       (volatile unsigned *)flag_host, seq));
+                       (volatile unsigned *)flag_host));
     return 0;
 }

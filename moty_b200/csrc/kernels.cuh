@@ -158,8 +158,7 @@ int launch_i4_rows_to_i8(const uint8_t *q4, int8_t *q8, long long rows, int n, c
 
 // ---- hostio.cu: activations in / results out between mapped (pinned) host buffers and the device, by kernels ----
 int launch_stage_in(float *dst, const float *src_host, long long n, cudaStream_t st);
-int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, unsigned seq, int sms,
-                    cudaStream_t st);
+int launch_tail_out(float *dst_host, const float *src, long long n, unsigned *ctr, unsigned *flag_host, int sms, cudaStream_t st);
 
 // ---- gemv_q8_gateup.cu: h = act(gate . x) * (up . x) for one token in one launch (rows of at most 4096 values) ----
 bool q8_gateup_supported(int I, int D);

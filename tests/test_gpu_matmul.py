@@ -281,7 +281,7 @@ def test_host_entry_with_pinned_buffers_equals_pageable(gpu, oracle):
         W = gpu.Mat.i8(Wq, sc)
         hx = gpu.pinned_empty((S, I), np.float32); hy = gpu.pinned_empty((S, O), np.float32)
         pad = gpu.pinned_empty((S * I + 1,), np.float32)                   # a pinned buffer 4 bytes off the 16-byte grid
-        for rep in range(3):
+        for rep in range(5):                                               # the third call on is a replayed graph of the call
             x = rng.standard_normal((S, I)).astype(np.float32)
             hx[...] = x; hy[...] = np.nan
             gpu.mat_apply(W, hx, hy)                                       # pinned -> kernels
@@ -292,6 +292,12 @@ def test_host_entry_with_pinned_buffers_equals_pageable(gpu, oracle):
             y2 = gpu.pinned_empty((S, O), np.float32)
             gpu.mat_apply(W, off, y2)                                      # misaligned pinned x -> copies
             assert y2.tobytes() == want.tobytes()
+        # a matrix freed and another one created (possibly at the same address) must not meet a stale graph
+        W.free()
+        Wq2 = rng.integers(-127, 128, (O, I), dtype=np.int8); W2 = gpu.Mat.i8(Wq2, sc)
+        for rep in range(3):
+            gpu.mat_apply(W2, hx, hy)
+            assert hy.tobytes() == oracle.matmul_q_s(np.asarray(hx), Wq2, sc).tobytes()
 
 
 def test_i4g_float_path(gpu, oracle):
