@@ -616,9 +616,18 @@ static bool host_kernels_on() {
 
 // repeated host calls with pinned buffers, replayed as graphs (see mat_apply_host)
 struct HostCall { const MotyCudaMat *w; const void *x; void *y; int S, device; unsigned long long gen; cudaGraph_t graph; cudaGraphExec_t exec; };
-constexpr int HOST_CALLS = 32;
+// an open hash table: a key lives in one of HOST_PROBE slots from its hash on (an engine that serves every matrix of a
+// model through one pair of staging buffers has hundreds of live keys)
+constexpr int HOST_CALLS = 2048, HOST_PROBE = 8;
 static HostCall g_hostcalls[HOST_CALLS];
 static unsigned g_hostcall_next = 0;
+static inline unsigned host_call_hash(const MotyCudaMat *w, const void *x, const void *y, int S) {
+    unsigned long long h = (reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull;
+    h ^= (reinterpret_cast<uintptr_t>(x) >> 4) * 0xC2B2AE3D27D4EB4Full;
+    h ^= (reinterpret_cast<uintptr_t>(y) >> 4) * 0x165667B19E3779F9ull;
+    h ^= (unsigned long long)S * 0x27D4EB2F165667C5ull;
+    return (unsigned)(h >> 40) & (HOST_CALLS - 1);
+}
 static void host_call_drop(HostCall *h) {
     if (h->exec) cudaGraphExecDestroy(h->exec);
     if (h->graph) cudaGraphDestroy(h->graph);
@@ -660,8 +669,9 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
         // A graph holds scratch and matrix addresses, so it is only used while neither has moved or been freed since.
         HostCall *hit = nullptr, *slot = nullptr;
         const unsigned long long gen = c->gen + g_mat_gen;
-        for (int i = 0; i < HOST_CALLS; i++) {
-            HostCall *h = &g_hostcalls[i];
+        const unsigned h0 = host_call_hash(w, x_map, y_map, S);
+        for (int i = 0; i < HOST_PROBE; i++) {
+            HostCall *h = &g_hostcalls[(h0 + i) & (HOST_CALLS - 1)];
             if (h->w == w && h->x == x_map && h->y == y_map && h->S == S && h->device == w->device) { hit = h; break; }
             if (!slot && !h->w) slot = h;
         }
@@ -684,7 +694,7 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
             }
         } else {
             if (!hit) {
-                if (!slot) { slot = &g_hostcalls[g_hostcall_next++ % HOST_CALLS]; host_call_drop(slot); }
+                if (!slot) { slot = &g_hostcalls[(h0 + g_hostcall_next++ % HOST_PROBE) & (HOST_CALLS - 1)]; host_call_drop(slot); }
                 slot->w = w; slot->x = x_map; slot->y = y_map; slot->S = S; slot->device = w->device; slot->gen = gen;
                 slot->exec = nullptr; slot->graph = nullptr;
             }

@@ -12,6 +12,7 @@
 #include "nn/nn_matmul.h"      /* NN_QROW_MAX */
 #include "moty_cuda.h"
 #include <stdlib.h>
+#include <string.h>
 
 /* The library reproduces the integer paths: IDOT=1 for int8 rows (the default, nn/matmul.c:52-53) and
  * IDOT4=1 for the two int4 row formats (opt-in, nn/matmul.c:77,171).  With the other setting of a knob
@@ -21,8 +22,36 @@ static int env_is(const char *k, int dflt) { const char *e = getenv(k); return e
 static int g_mats;
 static long long g_bytes, g_calls;
 
+/* The engine's activations live in malloc'd buffers that come and go (falloc / free around every block), which the
+ * library can only serve with copy-engine transfers from pageable memory.  Decode-sized calls (a few rows) go through
+ * one pair of page-locked staging buffers instead: with pinned buffers at both ends the library moves the bytes by
+ * kernels, waits on a flag word, and replays a repeated (matrix, buffers) call as one CUDA graph -- the two memcpys
+ * here cost less than what that saves (MOTY_SHIM_STAGE=0: hand the engine's own pointers through). */
+static float *g_xs, *g_ys;
+static size_t g_xs_cap, g_ys_cap;
+static int g_stage = -1;
+
+static int stage_grow(float **p, size_t *cap, size_t bytes) {
+    if (bytes <= *cap) return 0;
+    if (*p) moty_cuda_host_free(*p);
+    *p = NULL; *cap = 0;
+    void *q = NULL;
+    if (moty_cuda_host_alloc(&q, bytes + bytes / 2 + 4096) != 0) return -1;
+    *p = q; *cap = bytes + bytes / 2 + 4096;
+    return 0;
+}
+
 static void cuda_apply(float *y, const float *x, const struct Mat *w, int S) {
     g_calls++;
+    if (g_stage < 0) g_stage = env_is("MOTY_SHIM_STAGE", 1);
+    const size_t xb = (size_t)S * w->I * 4, yb = (size_t)S * w->O * 4;
+    if (g_stage && S <= 8 && stage_grow(&g_xs, &g_xs_cap, xb) == 0 && stage_grow(&g_ys, &g_ys_cap, yb) == 0) {
+        memcpy(g_xs, x, xb);
+        if (moty_cuda_mat_apply((MotyCudaMat *)w->sh, g_ys, g_xs, S) != 0)
+            moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] mat_apply %dx%d S=%d: %s\n", w->O, w->I, S, moty_cuda_last_error());
+        memcpy(y, g_ys, yb);
+        return;
+    }
     if (moty_cuda_mat_apply((MotyCudaMat *)w->sh, y, x, S) != 0)
         moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] mat_apply %dx%d S=%d: %s\n", w->O, w->I, S, moty_cuda_last_error());
 }
@@ -71,6 +100,9 @@ void moty_hw_cuda_detach(Mat *w) {
 
 void moty_hw_cuda_close(void) {
     moty_nn_set_stream_fn(NULL);
+    if (g_xs) moty_cuda_host_free(g_xs);
+    if (g_ys) moty_cuda_host_free(g_ys);
+    g_xs = g_ys = NULL; g_xs_cap = g_ys_cap = 0;
     moty_cuda_shutdown();
 }
 
