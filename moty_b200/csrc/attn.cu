@@ -184,8 +184,13 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
     float den0 = 1.f, den1 = 1.f;
     if (FUSE && warp > AT_G) {
         const int jj = tid - (AT_G + 1) * 32;
-        den0 = powf(a.theta, __fdiv_rn((float)(2 * jj), (float)a.rot));
-        den1 = powf(a.theta, __fdiv_rn((float)(2 * (jj + ROPE_T)), (float)a.rot));
+        if (a.gemma) {                                                  // engines/gemma.c:290: theta^(-2j/hd), a factor
+            den0 = powf(a.theta, __fdiv_rn(__fmul_rn(-2.0f, (float)jj), (float)hd));
+            den1 = powf(a.theta, __fdiv_rn(__fmul_rn(-2.0f, (float)(jj + ROPE_T)), (float)hd));
+        } else {                                                        // nn/rope.c:41: theta^(2j/rot), a divisor
+            den0 = powf(a.theta, __fdiv_rn((float)(2 * jj), (float)a.rot));
+            den1 = powf(a.theta, __fdiv_rn((float)(2 * (jj + ROPE_T)), (float)a.rot));
+        }
     }
     pdl_trigger();
     pdl_wait();                                                         // rotated q and the cache rows of this call come from attn_prep_kernel (without FUSE)
@@ -204,7 +209,9 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
         for (int i = ng * NV * 128 + tid; i < AT_G * NV * 128; i += AT_WARPS * 32) qs[i] = 0.f;
         constexpr int NJ = NV * 4;                                      // lane l holds dimensions l + 32 j
         const bool mine = warp < ng || (warp == AT_G && own), isq = warp < ng;
-        const int half = a.rot / 2;
+        // pairs (j, j + half), nang of them rotated: nn/rope.c:39-49 (half = nang = rot / 2) or engines/gemma.c:287-297
+        // (half = hd / 2, nang = rot)
+        const int half = a.gemma ? hd / 2 : a.rot / 2, nang = a.gemma ? a.rot : a.rot / 2;
         float *xs = ps + warp * (NV * 128);
         float x[NJ];
         if (mine) {
@@ -230,16 +237,19 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
             for (int j = 0; j < NJ; j++) xs[lane + 32 * j] = x[j];
         } else if (warp > AT_G) {                                       // the other warps: cos and sin of the rot / 2 angles, once
             const int jj = tid - (AT_G + 1) * 32;                       // nn/rope.c:39-44
-            if (jj < half) { const float an = __fdiv_rn((float)pos, den0); sc[jj] = cosf(an); sc[128 + jj] = sinf(an); }
-            if (jj + ROPE_T < half) { const float an = __fdiv_rn((float)pos, den1); sc[jj + ROPE_T] = cosf(an); sc[128 + jj + ROPE_T] = sinf(an); }
+            if (jj < nang) { const float an = a.gemma ? __fmul_rn((float)pos, den0) : __fdiv_rn((float)pos, den0); sc[jj] = cosf(an); sc[128 + jj] = sinf(an); }
+            if (jj + ROPE_T < nang) {
+                const float an = a.gemma ? __fmul_rn((float)pos, den1) : __fdiv_rn((float)pos, den1);
+                sc[jj + ROPE_T] = cosf(an); sc[128 + jj + ROPE_T] = sinf(an);
+            }
         }
         __syncthreads();
         if (mine) {
 #pragma unroll
             for (int j = 0; j < NJ; j++) {                              // nn/rope.c:45-49
                 const int d = lane + 32 * j;
-                if (d < a.rot) {
-                    const int jj = d < half ? d : d - half;
+                const int jj = d < half ? d : d - half;
+                if (d < 2 * half && jj < nang) {
                     const float c = sc[jj], sn = sc[128 + jj];
                     const float lo = xs[jj], hi = xs[jj + half];
                     x[j] = d < half ? __fsub_rn(__fmul_rn(lo, c), __fmul_rn(hi, sn)) : __fadd_rn(__fmul_rn(lo, sn), __fmul_rn(hi, c));
@@ -253,6 +263,18 @@ __global__ void __launch_bounds__(AT_WARPS * 32, NV == 1 ? 3 : 1) attn_flash_ker
                 float vv[NJ];
 #pragma unroll
                 for (int j = 0; j < NJ; j++) vv[j] = lane + 32 * j < hd ? a.v[(size_t)kvh * hd + lane + 32 * j] : 0.f;
+                if (a.vn) {                                             // gemma's value norm (engines/gemma.c:320-324)
+                    double sv2 = 0.0;
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) sv2 += (double)vv[j] * (double)vv[j];
+                    for (int off = 16; off > 0; off >>= 1) sv2 += __shfl_xor_sync(0xffffffffu, sv2, off);
+                    const float rv = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn((float)(sv2 / hd), a.eps)));
+#pragma unroll
+                    for (int j = 0; j < NJ; j++) {
+                        const int d = lane + 32 * j;
+                        if (d < hd) vv[j] = __fmul_rn(__fmul_rn(vv[j], rv), a.vn[d]);
+                    }
+                }
                 if (a.K8) {                                             // nn/mat.c:15-17: qrow_i8 per row
                     float ak = 0.f, av = 0.f;
 #pragma unroll
@@ -640,7 +662,7 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     const int nth_prep = (hd + 31) / 32 * 32;
     // one token at a position read from the device (a replayed decode step): norm, rotation and cache store ride in the
     // scores launch, and q and k are not written back
-    const bool fuse = pos_dev && S == 1 && !gemma && !vn;              // (the fused form carries the qwen-style rotation only)
+    const bool fuse = pos_dev && S == 1;
     if (!fuse) CK(moty_launch_pdl(attn_prep_kernel, dim3(S, H + KV), dim3(nth_prep), (size_t)0, st, a));
     const int NVr = hd > 128 ? 2 : 1;
     const size_t smem = ((size_t)AT_G * NVr * 128 + (size_t)AT_G * AT_CH + (size_t)AT_WARPS * AT_G * NVr * 128) * 4;

@@ -132,18 +132,21 @@ def test_attn_core_vs_oracle(gpu, oracle, H, KV, hd, rot, kv8):
                                     np.zeros((9, KV * hd), np.float32), 0)
 
 
-@pytest.mark.parametrize("H,KV,hd,rot,kv8,T0", [(16, 8, 128, 128, False, 700), (16, 8, 128, 128, True, 700), (8, 2, 64, 32, False, 40),
-                                                 (4, 4, 256, 256, False, 300), (12, 2, 96, 96, True, 1500), (16, 2, 128, 64, False, 5)])
-def test_attn_decode_one_launch_equals_two(gpu, H, KV, hd, rot, kv8, T0):
+@pytest.mark.parametrize("H,KV,hd,rot,kv8,T0,gemma", [(16, 8, 128, 128, False, 700, 0), (16, 8, 128, 128, True, 700, 0), (8, 2, 64, 32, False, 40, 0),
+                                                       (4, 4, 256, 256, False, 300, 0), (12, 2, 96, 96, True, 1500, 0), (16, 2, 128, 64, False, 5, 0),
+                                                       (16, 8, 256, 128, False, 1300, 1024), (16, 8, 256, 32, False, 900, -1), (4, 2, 64, 32, True, 50, 16)])
+def test_attn_decode_one_launch_equals_two(gpu, H, KV, hd, rot, kv8, T0, gemma):
     """One token at a position read from the device: norm, rotation and cache store inside the scores launch.  Same
     context rows and same cache rows as the prep + scores pair of attn_core_dev, step after step (the f64 sum of squares
-    is taken in another order, hence 1e-6 and not bit for bit), and q, k stay as they came."""
+    is taken in another order, hence 1e-6 and not bit for bit), and q, k stay as they came.  gemma != 0: the gemma
+    flavour (rot = rotated pairs, (1 + w) multipliers, value norm; > 0 = the sliding window, -1 = a global layer)."""
     import torch
     rng = np.random.default_rng(H * 1000 + hd + T0)
     max_t = T0 + 8
     qn = rng.uniform(0.5, 1.5, hd).astype(np.float32); kn = rng.uniform(0.5, 1.5, hd).astype(np.float32)
-    a = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8)
-    b = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8)
+    kw = dict(gemma=True, window=max(gemma, 0), vn=rng.uniform(0.5, 1.5, hd).astype(np.float32), theta=1e4) if gemma else {}
+    a = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8, **kw)
+    b = gpu.Attn(H, KV, hd, max_t, rot=rot, qn=qn, kn=kn, kv8=kv8, **kw)
     f = lambda *sh: rng.standard_normal(sh).astype(np.float32)
     q0, k0, v0 = f(T0, H * hd), f(T0, KV * hd), f(T0, KV * hd)
     a.core(q0.copy(), k0.copy(), v0, 0); b.core(q0.copy(), k0.copy(), v0, 0)        # the same prompt in both caches
