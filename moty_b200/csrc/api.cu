@@ -619,8 +619,8 @@ struct HostCall { const MotyCudaMat *w; const void *x; void *y; int S, device; u
 // an open hash table: a key lives in one of HOST_PROBE slots from its hash on (an engine that serves every matrix of a
 // model through one pair of staging buffers has hundreds of live keys)
 constexpr int HOST_CALLS = 2048, HOST_PROBE = 8;
-static HostCall g_hostcalls[HOST_CALLS];
-static unsigned g_hostcall_next = 0;
+static HostCall g_hostcalls_all[MOTY_MAX_DEV][HOST_CALLS];      // one table per device context: calls on different GPUs
+static unsigned g_hostcall_next_all[MOTY_MAX_DEV];               // may come from different host threads
 static inline unsigned host_call_hash(const MotyCudaMat *w, const void *x, const void *y, int S) {
     unsigned long long h = (reinterpret_cast<uintptr_t>(w) >> 4) * 0x9E3779B97F4A7C15ull;
     h ^= (reinterpret_cast<uintptr_t>(x) >> 4) * 0xC2B2AE3D27D4EB4Full;
@@ -634,7 +634,10 @@ static void host_call_drop(HostCall *h) {
     *h = HostCall{};
 }
 
-static void host_calls_drop_all() { for (int i = 0; i < HOST_CALLS; i++) host_call_drop(&g_hostcalls[i]); }
+static void host_calls_drop_all() {
+    for (int d = 0; d < MOTY_MAX_DEV; d++)
+        for (int i = 0; i < HOST_CALLS; i++) host_call_drop(&g_hostcalls_all[d][i]);
+}
 
 // host-pointer wrapper shared by the entries below: copy in, run, copy out, wait
 static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x, int S) {
@@ -668,6 +671,8 @@ static int mat_apply_host(MotyCudaMat *w, float *y, int32_t *acc, const float *x
         // launches: first sight runs it launch by launch, second sight captures it, from then on one submission per call.
         // A graph holds scratch and matrix addresses, so it is only used while neither has moved or been freed since.
         HostCall *hit = nullptr, *slot = nullptr;
+        HostCall *g_hostcalls = g_hostcalls_all[c - g_ctx];
+        unsigned &g_hostcall_next = g_hostcall_next_all[c - g_ctx];
         const unsigned long long gen = c->gen + g_mat_gen;
         const unsigned h0 = host_call_hash(w, x_map, y_map, S);
         for (int i = 0; i < HOST_PROBE; i++) {
