@@ -667,11 +667,12 @@ def run_gpu(args):
     sp = stream.cuda_stream
     total_bytes = sum(algo_bytes(*s) for s in SHAPES)
 
-    # Every launch of this pass carries about 5 us that is not streaming (launch, the per-CTA row quantizer, the tail):
-    # for the 1-3 MB matrices that is ten times their HBM time.  They go out as ONE launch
-    # (moty_cuda_mat_apply_multi_dev); --no-multi launches them one by one.  --multi-max-mb 64 also folds the
-    # 15360 x 3840 matrix in (measured: no gain -- the generic two-row units of that kernel stream a 59 MB matrix less
-    # well than its own launch does, which cancels the saved fixed cost: 66.3 against 66.2 us per pass).
+    # Every launch of this pass carries a few microseconds that are not streaming (launch, the per-CTA row quantizer,
+    # the tail): for the 1-3 MB matrices that is ten times their HBM time.  They go out as ONE launch together with the
+    # 15360 x 3840 matrix (moty_cuda_mat_apply_multi_dev takes rows of at most 4096 values; --multi-max-mb caps the
+    # size of a matrix that joins, --no-multi launches every matrix by itself).  Measured with the passes replayed as
+    # chained graphs: 53.5 us per pass with six launches, 52.4 with the three small ones in one, 51.0 with the 59 MB
+    # matrix in it as well.  The dominant matrix keeps its own launch: it is the kernel the roofline is reported for.
     multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 4096 and i != DOMINANT and
              SHAPES[i][0] * SHAPES[i][1] <= (args.multi_max_mb << 20)] if not args.no_multi else []
     singles = [i for i in range(len(SHAPES)) if i not in multi]
@@ -1116,7 +1117,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
-    ap.add_argument("--multi-max-mb", type=int, default=4, help="largest matrix (MB) that joins the several-products-in-one-launch call")
+    ap.add_argument("--multi-max-mb", type=int, default=64, help="largest matrix (MB) that joins the several-products-in-one-launch call")
     ap.add_argument("--no-multi", action="store_true", help="launch the small matrices one by one instead of in one launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
