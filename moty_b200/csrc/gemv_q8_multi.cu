@@ -3,8 +3,9 @@
 // A decode step is full of small matrices whose own GEMV launch costs more than their bytes: a 1-3 MB matrix is
 // 0.2-0.5 us of HBM time behind 4-5 us of launch, prologue and tail.  This kernel takes up to eight (matrix, row)
 // pairs -- moty_matmul_q_s with S = 1 for each (nn/matmul.c:51-66, IDOT=1), e.g. the q, k and v projections of a
-// layer, or independent products of a benchmark pass -- cuts ALL their rows into units of two rows and deals the
-// units round-robin to one persistent grid, so the fixed cost is paid once and the tail is one unit long.
+// layer, or independent products of a benchmark pass -- cuts ALL their rows into units of two, four or eight rows (16
+// 128-bit loads per lane in flight whatever the row length) and deals the units round-robin to one persistent grid, so
+// the fixed cost is paid once and the tail is one unit long.
 // Every CTA quantizes each activation row (moty_hw_qrow_i8, hw/hw_quant.h:9-16: exact amax, true division,
 // round-half-even) into shared memory behind its first weight loads.
 // Same dp4a arithmetic and the same (scale[o] * sx) * (float)dot epilogue as q8_stream_kernel: same bits.
@@ -14,14 +15,84 @@
 
 namespace {
 
-constexpr int MULTI_MAX = 8, MR = 2, MLPR = 8;
+constexpr int MULTI_MAX = 8;
 
+// N per-lane partial sums -> lane L holds the total of value (L >> (5 - log2 N))
+template <int N> struct LgM { static constexpr int v = 1 + LgM<N / 2>::v; };
+template <> struct LgM<1> { static constexpr int v = 0; };
+template <int N>
+__device__ __forceinline__ void reduce_multi_m(int (&v)[N], int lane) {
+    int off = 16;
+#pragma unroll
+    for (int n = N; n > 1; n >>= 1, off >>= 1) {
+#pragma unroll
+        for (int i = 0; i < n / 2; i++) {
+            const bool up = (lane & off) != 0;
+            const int send = up ? v[i] : v[i + n / 2];
+            const int keep = up ? v[i + n / 2] : v[i];
+            v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+    for (; off > 0; off >>= 1) v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+}
+
+// A unit is R rows of one matrix with LPR 128-bit loads per lane and row, R * LPR = 16 loads in flight per lane whatever
+// the row length: rows of up to 1024 values go eight to a unit (kind 2), up to 2048 four (kind 1), longer ones two (kind 0).
 struct MultiArgs {
     const int8_t *w[MULTI_MAX]; const float *scale[MULTI_MAX]; const float *x[MULTI_MAX]; float *y[MULTI_MAX];
     int O[MULTI_MAX], I16[MULTI_MAX], xoff[MULTI_MAX];     // xoff: where matrix m's codes start in shared memory (bytes)
-    int ustart[MULTI_MAX + 1];                             // prefix of units (row pairs) per matrix
+    int kind[MULTI_MAX];
+    int ustart[MULTI_MAX + 1];                             // prefix of units per matrix
     int n;
 };
+
+template <int R, int LPR>
+__device__ __forceinline__ void multi_issue(const MultiArgs &a, int m, int r0, int lane, int4 (&wv)[16], float &my_scale) {
+    const int I16 = a.I16[m], O = a.O[m];
+#pragma unroll
+    for (int r = 0; r < R; r++) {
+        const int o = r0 + r < O ? r0 + r : O - 1;
+        const int4 *p = reinterpret_cast<const int4 *>(a.w[m]) + (size_t)o * I16;
+#pragma unroll
+        for (int j = 0; j < LPR; j++) {
+            const int k = j * 32 + lane;
+            wv[r * LPR + j] = k < I16 ? ldg_stream16(p + k) : make_int4(0, 0, 0, 0);
+        }
+    }
+    constexpr int SH = 5 - LgM<R>::v;                       // after the reduction lane L reports row L >> SH
+    const int o = r0 + (lane >> SH);
+    my_scale = __ldg(a.scale[m] + (o < O ? o : O - 1));
+}
+
+template <int R, int LPR>
+__device__ __forceinline__ void multi_dots(const MultiArgs &a, int m, int lane, const int4 (&wv)[16], const int4 *xs, int (&dot)[8]) {
+    const int I16 = a.I16[m];
+#pragma unroll
+    for (int r = 0; r < 8; r++) dot[r] = 0;
+#pragma unroll
+    for (int j = 0; j < LPR; j++) {
+        if (j * 32 < I16) {                                // warp-uniform
+            int k = j * 32 + lane; k = k < I16 ? k : I16 - 1;          // weights past the row were loaded as zeros
+            const int4 xv = xs[k];
+#pragma unroll
+            for (int r = 0; r < R; r++) dot[r] = dp4a4(wv[r * LPR + j], xv, dot[r]);
+        }
+    }
+}
+
+template <int R>
+__device__ __forceinline__ void multi_write(const MultiArgs &a, int m, int r0, int lane, int (&dot)[8], float my_scale, float sx) {
+    int d[R];
+#pragma unroll
+    for (int r = 0; r < R; r++) d[r] = dot[r];
+    reduce_multi_m<R>(d, lane);
+    constexpr int SH = 5 - LgM<R>::v;
+    const int o = r0 + (lane >> SH);
+    // (scale[o] * sx) * (float)dot, left to right (nn/matmul.c:34)
+    if ((lane & ((1 << SH) - 1)) == 0 && o < a.O[m]) a.y[m][o] = __fmul_rn(__fmul_rn(my_scale, sx), (float)d[0]);
+}
+
+__device__ __forceinline__ int multi_rows(int kind) { return kind == 2 ? 8 : (kind == 1 ? 4 : 2); }
 
 __global__ void __launch_bounds__(256, 2) q8_multi_kernel(MultiArgs a) {
     extern __shared__ int4 smem4[];
@@ -31,25 +102,17 @@ __global__ void __launch_bounds__(256, 2) q8_multi_kernel(MultiArgs a) {
     const int nunits = a.ustart[a.n], nwarps = gridDim.x * 8;
     int8_t *xq_s = reinterpret_cast<int8_t *>(smem4);
 
-    int4 wv[MR][MLPR];
-    float sc[MR];
+    int4 wv[16];
+    float my_scale = 0.f;
     int um = 0, ur = 0;                                    // matrix and first row of the unit in flight
     auto issue = [&](int u) {
         int m = 0;
         while (m + 1 < a.n && u >= a.ustart[m + 1]) m++;
-        um = m; ur = (u - a.ustart[m]) * MR;
-        const int I16 = a.I16[m], O = a.O[m];
-#pragma unroll
-        for (int r = 0; r < MR; r++) {
-            const int o = ur + r < O ? ur + r : O - 1;
-            const int4 *p = reinterpret_cast<const int4 *>(a.w[m]) + (size_t)o * I16;
-#pragma unroll
-            for (int j = 0; j < MLPR; j++) {
-                const int k = j * 32 + lane;
-                wv[r][j] = k < I16 ? ldg_stream16(p + k) : make_int4(0, 0, 0, 0);
-            }
-            sc[r] = __ldg(a.scale[m] + o);
-        }
+        const int kind = a.kind[m];
+        um = m; ur = (u - a.ustart[m]) * multi_rows(kind);
+        if (kind == 2) multi_issue<8, 2>(a, m, ur, lane, wv, my_scale);
+        else if (kind == 1) multi_issue<4, 4>(a, m, ur, lane, wv, my_scale);
+        else multi_issue<2, 8>(a, m, ur, lane, wv, my_scale);
     };
     int u = blockIdx.x * 8 + warp;
     pdl_trigger();
@@ -85,30 +148,18 @@ __global__ void __launch_bounds__(256, 2) q8_multi_kernel(MultiArgs a) {
     __syncthreads();
 
     while (u < nunits) {
-        const int m = um, r0 = ur, I16 = a.I16[m], O = a.O[m];
+        const int m = um, r0 = ur, kind = a.kind[m];
         const int4 *xs = reinterpret_cast<const int4 *>(xq_s + a.xoff[m]);
-        int dot[MR];
-#pragma unroll
-        for (int r = 0; r < MR; r++) dot[r] = 0;
-#pragma unroll
-        for (int j = 0; j < MLPR; j++) {
-            if (j * 32 < I16) {                            // warp-uniform
-                int k = j * 32 + lane; k = k < I16 ? k : I16 - 1;      // weights past the row were loaded as zeros
-                const int4 xv = xs[k];
-#pragma unroll
-                for (int r = 0; r < MR; r++) dot[r] = dp4a4(wv[r][j], xv, dot[r]);
-            }
-        }
-        const float s0 = sc[0], s1 = sc[1], sx = sx_s[m];
+        const float sx = sx_s[m], sc = my_scale;
+        int dot[8];
+        if (kind == 2) multi_dots<8, 2>(a, m, lane, wv, xs, dot);
+        else if (kind == 1) multi_dots<4, 4>(a, m, lane, wv, xs, dot);
+        else multi_dots<2, 8>(a, m, lane, wv, xs, dot);
         u += nwarps;
         if (u < nunits) issue(u);                          // the next unit's loads go out before this result is written
-#pragma unroll
-        for (int r = 0; r < MR; r++) dot[r] = warp_sum_i32(dot[r]);
-        if (lane < MR && r0 + lane < O) {
-            // (scale[o] * sx) * (float)dot, left to right (nn/matmul.c:34)
-            const int d = lane == 0 ? dot[0] : dot[1];
-            a.y[m][r0 + lane] = __fmul_rn(__fmul_rn(lane == 0 ? s0 : s1, sx), (float)d);
-        }
+        if (kind == 2) multi_write<8>(a, m, r0, lane, dot, sc, sx);
+        else if (kind == 1) multi_write<4>(a, m, r0, lane, dot, sc, sx);
+        else multi_write<2>(a, m, r0, lane, dot, sc, sx);
     }
 }
 
@@ -128,7 +179,9 @@ int launch_q8_multi(int n, const int8_t *const *w, const float *const *scale, co
             return moty_set_error(MOTY_CUDA_EARG, "q8_multi: matrix %d is %dx%d (rows of 16..4096 bytes, x 16-byte aligned)", m, O[m], I[m]);
         a.w[m] = w[m]; a.scale[m] = scale[m]; a.x[m] = x[m]; a.y[m] = y[m]; a.O[m] = O[m]; a.I16[m] = I[m] / 16;
         a.xoff[m] = xoff; xoff += I[m];
-        a.ustart[m] = units; units += (O[m] + MR - 1) / MR;
+        a.kind[m] = I[m] <= 1024 ? 2 : (I[m] <= 2048 ? 1 : 0);
+        const int rows = a.kind[m] == 2 ? 8 : (a.kind[m] == 1 ? 4 : 2);
+        a.ustart[m] = units; units += (O[m] + rows - 1) / rows;
     }
     a.ustart[n] = units;
     const size_t smem = (size_t)xoff;
