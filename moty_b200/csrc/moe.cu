@@ -295,9 +295,12 @@ int launch_moe_peer_combine(float *out, const float *table, const float *w, cons
 // ---------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) f32_rows_kernel(const float *__restrict__ W, const float *__restrict__ x,
                                                        float *__restrict__ y, int S, int I, int O) {
+    // a warp takes one output row and four consecutive tokens (blockIdx.y); per (row, token) the same lane-strided
+    // fmaf chain and shuffle tree whatever the batch size, so a token's logits do not depend on how many come with it
     int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (o >= O) return;
-    for (int s = 0; s < S; s++) {
+    const int s0 = blockIdx.y * 4, s1 = s0 + 4 < S ? s0 + 4 : S;
+    for (int s = s0; s < s1; s++) {
         float acc = 0.f;
         for (int i = lane; i < I; i += 32) acc = fmaf(W[(size_t)o * I + i], x[(size_t)s * I + i], acc);
 #pragma unroll
@@ -311,7 +314,8 @@ int launch_f32_rows(const float *W, const float *x, float *y, int S, int I, int 
     // a plain launch on purpose: chained programmatically it measured slower over a whole OLMoE-shaped decode step, with
     // the cooperative layer kernel after it (1095 against 1116 tok/s replayed) and with the two chained layer launches
     // (1129 against 1217; same GPU, twice each)
-    f32_rows_kernel<<<(O + 7) / 8, 256, 0, st>>>(W, x, y, S, I, O);
+    if ((S + 3) / 4 > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "f32 matrix: S=%d in one call", S);
+    f32_rows_kernel<<<dim3((O + 7) / 8, (S + 3) / 4), 256, 0, st>>>(W, x, y, S, I, O);
     CK(cudaGetLastError());
     return 0;
 }
