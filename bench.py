@@ -668,12 +668,13 @@ def run_gpu(args):
     total_bytes = sum(algo_bytes(*s) for s in SHAPES)
 
     # Every launch of this pass carries a few microseconds that are not streaming (launch, the per-CTA row quantizer,
-    # the tail): for the 1-3 MB matrices that is ten times their HBM time.  They go out as ONE launch together with the
-    # 15360 x 3840 matrix (moty_cuda_mat_apply_multi_dev takes rows of at most 4096 values; --multi-max-mb caps the
-    # size of a matrix that joins, --no-multi launches every matrix by itself).  Measured with the passes replayed as
-    # chained graphs: 53.5 us per pass with six launches, 52.4 with the three small ones in one, 51.0 with the 59 MB
-    # matrix in it as well, 49.5 once that launch sized its units by row length.  The dominant matrix keeps its own launch: it is the kernel the roofline is reported for.
-    multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 4096 and i != DOMINANT and
+    # the tail): for the 1-3 MB matrices that is ten times their HBM time.  All matrices but the dominant one go out as
+    # ONE launch (moty_cuda_mat_apply_multi_dev; --multi-max-mb caps the size of a matrix that joins, --no-multi
+    # launches every matrix by itself).  Measured with the passes replayed as chained graphs: 53.5 us per pass with six
+    # launches, 52.4 with the three small matrices in one, 51.0 with the 15360 x 3840 matrix in it as well, 49.5 once that
+    # launch sized its units by row length, 47.95 with the 3840 x 15360 matrix (rows split in K) in it too.  The dominant
+    # matrix keeps its own launch: it is the kernel the roofline is reported for.
+    multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 16384 and i != DOMINANT and
              SHAPES[i][0] * SHAPES[i][1] <= (args.multi_max_mb << 20)] if not args.no_multi else []
     singles = [i for i in range(len(SHAPES)) if i not in multi]
 

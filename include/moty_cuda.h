@@ -160,8 +160,9 @@ int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
 int moty_cuda_set_i4g_float_path(int on);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
 /* n (1..8) independent one-row products in ONE launch: y_dev[m] = mat_apply(w[m], x_dev[m], S = 1) for MOTY_WF_I8
- * matrices on one GPU with I % 16 == 0 and I <= 4096 (x_dev[m] 16-byte aligned; the pointers may repeat: the q, k, v
- * projections of a layer share their row).  Small matrices cost a launch each otherwise (1-3 MB: 0.2-0.5 us of HBM
+ * matrices on one GPU with I % 16 == 0 and I <= 16384 (x_dev[m] 16-byte aligned; the pointers may repeat: the q, k, v
+ * projections of a layer share their row; rows longer than 4096 values are split in K and combined exactly, as in the
+ * single-matrix kernel).  Small matrices cost a launch each otherwise (1-3 MB: 0.2-0.5 us of HBM
  * time behind 4-5 us of fixed cost); here all rows of all matrices are dealt to one persistent grid.  Same bits as n
  * calls of mat_apply_dev.  w, y_dev, x_dev are HOST arrays of n pointers.  No reference counterpart (the reference
  * calls moty_mat_apply once per matrix, nn/mat.c:70). */

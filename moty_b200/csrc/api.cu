@@ -555,13 +555,22 @@ extern "C" int moty_cuda_mat_apply_multi_dev(int n, MotyCudaMat *const *w, float
     for (int m = 0; m < n; m++) {
         if (!w[m] || !y_dev[m] || !x_dev[m]) return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: null argument for matrix %d", m);
         if (w[m]->fmt != MOTY_WF_I8 || w[m]->device != w[0]->device || !q8_multi_supported(w[m]->I))
-            return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: matrix %d must be MOTY_WF_I8 on the same GPU with I %% 16 == 0, I <= 4096", m);
+            return moty_set_error(MOTY_CUDA_EARG, "mat_apply_multi_dev: matrix %d must be MOTY_WF_I8 on the same GPU with I %% 16 == 0, I <= 16384", m);
         codes[m] = (const int8_t *)w[m]->codes; scales[m] = (const float *)w[m]->scales; O[m] = w[m]->O; I[m] = w[m]->I;
     }
     DevCtx *c = moty_ctx(w[0]->device);
     if (!c) return moty_set_error(MOTY_CUDA_EINIT, "device %d not initialised", w[0]->device);
     MOTY_USE_DEVICE(w[0]->device);
-    return launch_q8_multi(n, codes, scales, x_dev, y_dev, O, I, c->sms, pick_stream(c, stream));
+    // rows longer than 4096 values are split in K and meet in 64-bit cells (zero between launches), one run per matrix
+    unsigned long long *cells[8] = {nullptr};
+    size_t ncell = 0;
+    for (int m = 0; m < n; m++) if (I[m] > 4096) ncell += (size_t)O[m];
+    if (ncell) {
+        CKR(moty_grow_zero(c, &c->kcell, ncell * 8));
+        size_t off = 0;
+        for (int m = 0; m < n; m++) if (I[m] > 4096) { cells[m] = (unsigned long long *)c->kcell.p + off; off += (size_t)O[m]; }
+    }
+    return launch_q8_multi(n, codes, scales, x_dev, y_dev, O, I, c->sms, pick_stream(c, stream), cells);
 }
 
 extern "C" int moty_cuda_mat_addnorm_supported(const MotyCudaMat *w) {

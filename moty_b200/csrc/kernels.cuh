@@ -170,4 +170,4 @@ int launch_q8_gateup(const int8_t *g, const float *gs, const int8_t *u, const fl
 // ---- gemv_q8_multi.cu: up to eight independent S = 1 Q8_0 products in one launch ----
 bool q8_multi_supported(int I);
 int launch_q8_multi(int n, const int8_t *const *w, const float *const *scale, const float *const *x, float *const *y,
-                    const int *O, const int *I, int sms, cudaStream_t st);
+                    const int *O, const int *I, int sms, cudaStream_t st, unsigned long long *const *cells = nullptr);

@@ -251,7 +251,7 @@ def test_q8_multi_launch_equals_single_launches(gpu, oracle):
     and ragged ones; twice in a row."""
     import torch
     rng = np.random.default_rng(5)
-    shapes = [(1024, 1024), (3072, 1024), (1024, 3072), (515, 3840), (9, 16), (2048, 1024), (1, 4096), (77, 2064)]
+    shapes = [(1024, 1024), (3072, 1024), (1024, 3072), (515, 3840), (9, 16), (2048, 1024), (1, 4096), (259, 15360)]
     mats = [(rng.integers(-127, 128, s, dtype=np.int8), rng.uniform(0.001, 0.02, s[0]).astype(np.float32)) for s in shapes]
     W = [gpu.Mat.i8(q, sc) for q, sc in mats]
     sh = gpu.stream_handle(torch.cuda.current_stream())
@@ -266,9 +266,19 @@ def test_q8_multi_launch_equals_single_launches(gpu, oracle):
         for (q, sc), w, x, y in zip(mats, W, xs, dy):
             got = y.cpu().numpy()
             assert same_bits(got, gpu.mat_apply(w, x)) and same_bits(got, oracle.matmul_q_s(x, q, sc))
-    with pytest.raises(gpu.MotyCudaError):                       # rows longer than 4096 need the K split of the single kernel
-        big = gpu.Mat.i8(rng.integers(-127, 128, (8, 8192), dtype=np.int8), np.ones(8, np.float32))
-        gpu.mat_apply_multi_dev([big], [dy[0].data_ptr()], [dx[0].data_ptr()], sh)
+    # rows longer than 4096 values are split in K: two such matrices in one launch (their cells sit side by side), twice
+    shapes2 = [(300, 8192), (77, 4112), (64, 16384), (1000, 1024)]
+    mats2 = [(rng.integers(-127, 128, s, dtype=np.int8), rng.uniform(0.001, 0.02, s[0]).astype(np.float32)) for s in shapes2]
+    W2 = [gpu.Mat.i8(q, sc) for q, sc in mats2]
+    for trial in range(2):
+        xs = [rng.standard_normal((1, s[1])).astype(np.float32) for s in shapes2]
+        dx = [torch.from_numpy(x).cuda() for x in xs]
+        dy = [torch.full((1, s[0]), float("nan"), device="cuda") for s in shapes2]
+        gpu.mat_apply_multi_dev(W2, [y.data_ptr() for y in dy], [x.data_ptr() for x in dx], sh)
+        torch.cuda.synchronize()
+        for (q, sc), w, x, y in zip(mats2, W2, xs, dy):
+            got = y.cpu().numpy()
+            assert same_bits(got, gpu.mat_apply(w, x)) and same_bits(got, oracle.matmul_q_s(x, q, sc))
 
 
 def test_host_entry_with_pinned_buffers_equals_pageable(gpu, oracle):
