@@ -14,9 +14,10 @@ value      algorithmic GB/s with activations and results resident on the GPU
            passes' launches between the two events on the launch stream, max over ranks
 e2e        the same passes through the host-pointer entry moty_cuda_mat_apply
            (pinned host buffers; H2D of x and D2H of y inside the timed region)
-roofline   the dominant kernel (the 151936x1024 GEMV): bytes / its own average
-           launch time, measured with events around its launch in K further passes of
-           the same sequence right after the timed region
+roofline   the dominant kernel -- the launch that holds the 151936x1024 matrix: by default the
+           one launch of the whole pass (q8_multi_kernel, six matrices), with --multi-max-mb 64
+           or --no-multi that matrix's own GEMV --: bytes / its own average launch time,
+           measured with events around its launch in K further passes right after the timed region
 cpu_baseline / --impl reference
            the reference's own OpenMP code (oracle/_ref, else the C restatement)
            on the host cores, same passes
@@ -78,9 +79,9 @@ def measured_peak():
     return 6650.0, "fallback"
 
 
-def profile_traffic():
+def profile_traffic(name="q8_stream_gemv_151936x1024.md"):
     """DRAM bytes per launch of the dominant kernel, from the committed ncu summary."""
-    p = os.path.join(ROOT, "profiles", "q8_stream_gemv_151936x1024.md")
+    p = os.path.join(ROOT, "profiles", name)
     if os.path.exists(p):
         m = re.search(r"dram_bytes_per_launch:\s*([0-9.eE+]+)", open(p).read())
         if m:
@@ -668,14 +669,18 @@ def run_gpu(args):
     total_bytes = sum(algo_bytes(*s) for s in SHAPES)
 
     # Every launch of this pass carries a few microseconds that are not streaming (launch, the per-CTA row quantizer,
-    # the tail): for the 1-3 MB matrices that is ten times their HBM time.  All matrices but the dominant one go out as
-    # ONE launch (moty_cuda_mat_apply_multi_dev; --multi-max-mb caps the size of a matrix that joins, --no-multi
-    # launches every matrix by itself).  Measured with the passes replayed as chained graphs: 53.5 us per pass with six
-    # launches, 52.4 with the three small matrices in one, 51.0 with the 15360 x 3840 matrix in it as well, 49.5 once that
-    # launch sized its units by row length, 47.95 with the 3840 x 15360 matrix (rows split in K) in it too.  The dominant
-    # matrix keeps its own launch: it is the kernel the roofline is reported for.
-    multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 16384 and i != DOMINANT and
+    # the tail): for the 1-3 MB matrices that is ten times their HBM time.  The six products of a pass are independent,
+    # so they go out as ONE launch (moty_cuda_mat_apply_multi_dev; --multi-max-mb caps the size of a matrix that joins,
+    # --no-multi launches every matrix by itself).  Measured with the passes replayed as chained graphs: 53.5 us per
+    # pass with six launches, 52.4 with the three small matrices in one, 51.0 with the 15360 x 3840 matrix in it as well,
+    # 49.5 once that launch sized its units by row length, 47.95 with the 3840 x 15360 matrix (rows split in K) in it
+    # too, and 46 with the dominant matrix as well.
+    multi = [i for i in range(len(SHAPES)) if SHAPES[i][1] <= 16384 and
              SHAPES[i][0] * SHAPES[i][1] <= (args.multi_max_mb << 20)] if not args.no_multi else []
+    if len(multi) < 2:
+        multi = []
+    # the launch the roofline is reported for: the one that holds the dominant matrix
+    roof = multi if DOMINANT in multi else [DOMINANT]
     singles = [i for i in range(len(SHAPES)) if i not in multi]
 
     def launch(idxs):
@@ -742,26 +747,28 @@ def run_gpu(args):
             barrier()
             round_ms.append(e0.elapsed_time(e1))
         ms = statistics.median(round_ms)
-        # The roofline's kernel: K further passes of the same sequence right after, now with the dominant GEMV launched
-        # directly between two events on its stream (the matrices before and after it replayed from two graphs), so that
-        # its own duration is measured in place, with the rest of the 280 MB pass between two of its launches.  These
-        # passes are not part of `value`: the events cost the overlap described above.
-        g_before = None if args.no_graph else capture(list(range(0, DOMINANT)))
-        g_after = None if args.no_graph else capture(list(range(DOMINANT + 1, len(SHAPES))))
+        # The roofline's kernel: K further passes of the same sequence right after, now with the launch that holds the
+        # dominant matrix issued directly between two events on its stream (what comes before and after it in the pass
+        # replayed from two graphs), so that its own duration is measured in place, every launch of it streaming the
+        # pass's 280 MB anew.  These passes are not part of `value`: the events cost the overlap described above.
+        before = [i for i in range(0, min(roof)) if i not in roof]
+        after = [i for i in range(len(SHAPES)) if i not in roof and i not in before]
+        g_before = None if args.no_graph else capture(before)
+        g_after = None if args.no_graph else capture(after)
         dom_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
         dom_all = []
         for rnd in range(3):
             barrier()
             for k in range(K):
                 if args.no_graph:
-                    launch(list(range(0, DOMINANT)))
+                    launch(before)
                 elif g_before is not None:
                     g_before.replay()
                 dom_ev[k][0].record(stream)
-                mb.mat_apply_dev(W[DOMINANT], ys[DOMINANT].data_ptr(), xs[DOMINANT].data_ptr(), 1, sp)
+                launch(roof)
                 dom_ev[k][1].record(stream)
                 if args.no_graph:
-                    launch(list(range(DOMINANT + 1, len(SHAPES))))
+                    launch(after)
                 elif g_after is not None:
                     g_after.replay()
             barrier()
@@ -820,8 +827,21 @@ def run_gpu(args):
     value = world * total_bytes * K / (ms * 1e-3) / 1e9
     e2e = world * total_bytes * Ke / e2e_s / 1e9
     peak, peak_kind = measured_peak()
-    O, I = SHAPES[DOMINANT]
-    achieved = algo_bytes(O, I) / (dom_ms * 1e-3) / 1e9
+    roof_bytes = sum(algo_bytes(*SHAPES[i]) for i in roof)
+    isolated_ms = dom_ms
+    whole_pass = len(roof) == len(SHAPES)
+    if whole_pass:
+        # the pass IS this kernel: its average launch duration over the timed region is the region's own events / K
+        dom_ms = ms / K
+    achieved = roof_bytes / (dom_ms * 1e-3) / 1e9
+    if len(roof) > 1:
+        roof_kernel = (f"q8_multi_kernel, {len(roof)} matrices of the pass in one launch (" +
+                       ", ".join(f"{SHAPES[i][0]}x{SHAPES[i][1]}" for i in roof) + "), S=1")
+        roof_profile = "q8_multi_sweep_pass.md"
+    else:
+        roof_kernel = "q8_stream_kernel<1,4,2,fused> 151936x1024 S=1"
+        roof_profile = "q8_stream_gemv_151936x1024.md"
+    roof_traffic = profile_traffic(roof_profile)
     cpu = None
     if world == 1 and not args.no_cpu:
         gbs, cores, kind, done, dt = cpu_arm(mats, 10 ** 9, 1, budget_s=12.0)
@@ -840,14 +860,20 @@ def run_gpu(args):
                       (f"; the {len(multi)} matrices of at most {args.multi_max_mb} MB in one launch" if len(multi) > 1 else ""),
             "timed_region": f"median of {ROUNDS} rounds of {K} steps",
             "pct_of_8TBs": round(100 * value / world / 8000.0, 2),
-            "roofline": {"bound": "hbm", "kernel": "q8_stream_kernel<1,4,2,fused> 151936x1024 S=1", "achieved": round(achieved, 1),
+            "roofline": {"bound": "hbm", "kernel": roof_kernel, "achieved": round(achieved, 1),
                          "peak": peak, "peak_kind": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                         "traffic": profile_traffic(),
-                         "traffic_source": "committed ncu summary profiles/q8_stream_gemv_151936x1024.md (dram read + write bytes of one launch of this kernel), not measured in this run",
-                         "algorithmic_bytes": algo_bytes(O, I),
+                         "traffic": roof_traffic,
+                         "traffic_source": (f"committed ncu summary profiles/{roof_profile} (dram read + write bytes of one launch of this kernel), "
+                                            "not measured in this run") if roof_traffic is not None else None,
+                         "algorithmic_bytes": roof_bytes,
                          "avg_launch_us": round(dom_ms * 1e3, 3),
-                         "timing": f"CUDA events around this kernel's launch in {K} further passes of the same sequence, right after the "
-                                   "timed region (events between launches end the launch overlap, so they stay out of `value`)"},
+                         "isolated_launch_us": round(isolated_ms * 1e3, 3),
+                         "timing": ((f"avg_launch_us: the timed region is {K} launches of this kernel and nothing else, CUDA events around "
+                                     "them on the launch stream / their number; ") if whole_pass else
+                                    (f"avg_launch_us: CUDA events around this kernel's launch in {K} further passes of the same sequence, "
+                                     "right after the timed region; ")) +
+                                   (f"isolated_launch_us: one launch between two events, in {K} further passes right after the timed region "
+                                    "(an event between two launches ends their overlap: launch latency, first loads and tail are then exposed)")},
             "cpu_baseline": cpu,
             "e2e": {"value": round(e2e, 2), "unit": "GB/s", "steps": Ke,
                     "h2d_bytes_per_step": sum(4 * I for (_, I) in SHAPES), "d2h_bytes_per_step": sum(4 * O for (O, _) in SHAPES)},
@@ -1118,7 +1144,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--shapes", default="", help="comma-separated indices into the sweep (profiling aid); default all six")
-    ap.add_argument("--multi-max-mb", type=int, default=64, help="largest matrix (MB) that joins the several-products-in-one-launch call")
+    ap.add_argument("--multi-max-mb", type=int, default=256, help="largest matrix (MB) that joins the several-products-in-one-launch call")
     ap.add_argument("--no-multi", action="store_true", help="launch the small matrices one by one instead of in one launch")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg (profiling aid)")
     ap.add_argument("--no-graph", action="store_true", help="launch every GEMV directly instead of replaying CUDA graphs")
