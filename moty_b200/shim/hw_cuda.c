@@ -16,7 +16,8 @@
 
 /* The library reproduces the integer paths: IDOT=1 for int8 rows (the default, nn/matmul.c:52-53) and
  * IDOT4=1 for the two int4 row formats (opt-in, nn/matmul.c:77,171).  With the other setting of a knob
- * the reference computes an f32 product instead; those matrices stay on the CPU. */
+ * the reference computes an f32 product instead; those matrices stay on the CPU -- except the grouped int4
+ * layout, whose f32 x int4 product the library has too (to f32 rounding, not bit for bit). */
 static int env_is(const char *k, int dflt) { const char *e = getenv(k); return e && *e ? atoi(e) : dflt; }
 
 static int g_mats;
@@ -59,6 +60,9 @@ static void cuda_apply(float *y, const float *x, const struct Mat *w, int S) {
 void moty_hw_cuda_open(const int *devs, int n) {
     if (moty_cuda_init(devs, n) != 0)
         moty_fail_code(MOTY_FAIL_GENERIC, "[cuda] init: %s\n", moty_cuda_last_error());
+    /* grouped int4: the integer product with IDOT4=1, the f32 x int4 product without (the reference's default); the
+     * library takes the f32 product by itself for the row lengths the integer one does not cover (nn/matmul.c:172) */
+    moty_cuda_set_i4g_float_path(env_is("IDOT4", 0) ? 0 : 1);
     moty_nn_set_stream_fn(cuda_apply);
 }
 
@@ -79,8 +83,8 @@ int moty_hw_cuda_attach(Mat *w, int device) {
     case WF_I4:
         if (!w->q4 || !w->qs || w->I > NN_QROW_MAX || !env_is("IDOT4", 0)) return 0;
         rc = moty_cuda_upload_mat(&h, MOTY_WF_I4, w->q4, w->qs, w->O, w->I, device); break;
-    case WF_I4G:
-        if (!w->q4 || !w->qs || w->gs != 32 || w->I % 64 || w->I > NN_QROW_MAX || !env_is("IDOT4", 0)) return 0;
+    case WF_I4G:                                                        /* either product of nn/matmul.c:164-253: see moty_hw_cuda_open */
+        if (!w->q4 || !w->qs || w->gs != 32 || w->I % 32) return 0;
         rc = moty_cuda_upload_mat(&h, MOTY_WF_I4G, w->q4, w->qs, w->O, w->I, device); break;
     default:
         return 0;                                                       /* stays on the CPU path */
