@@ -227,7 +227,10 @@ def run_extras(torch, mb, dev, stream, W8, local):
         s16 = np.full(nblk * nb * 4, 0x1A00, np.uint16)               # f16 0.00293
         W4.append(mb.Mat.q4r4(q4, s16, O, I, device=local))
     with torch.cuda.stream(stream):
-        for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4), ("q4r4", W4, 512, 2)):
+        for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4), ("q4r4", W4, 512, 2),
+                                       ("q4r4_relaxed", W4, 16, 4), ("q4r4_relaxed", W4, 512, 2)):
+            # (q4r4_relaxed: after moty_cuda_set_q4r4_batch_relaxed(1) -- one formula for a group's term, within 1e-5)
+            mb.lib().moty_cuda_set_q4r4_batch_relaxed(1 if fmt == "q4r4_relaxed" else 0)
             xs = [torch.randn((S, I), device=dev) for (_, I) in SHAPES]
             ys = [torch.empty((S, O), device=dev) for (O, _) in SHAPES]
             ev = [[] for _ in SHAPES]
@@ -246,6 +249,7 @@ def run_extras(torch, mb, dev, stream, W8, local):
                 out["rows"].append({"fmt": fmt, "S": S, "O": O, "I": I, "us": round(us, 2),
                                     "GBs": round(nbytes / us / 1e3, 1), "TOPS": round(2.0 * S * O * I / us / 1e6, 2)})
             del xs, ys
+    mb.lib().moty_cuda_set_q4r4_batch_relaxed(0)
     del W4
     out["moe"] = run_moe_extras(torch, mb, dev, stream, local)
     out["blocks"] = run_block_extras(torch, mb, dev, stream, local)
@@ -449,6 +453,10 @@ def run_moe_extras(torch, mb, dev, stream, local):
                     row["us_mma_sync_tiles"] = round(time_moe(torch, layers, name, S, dev, stream, reps=3, run=4), 1)
                     mb.lib().moty_cuda_set_moe_batch_path(prev)
                     row["path"] = "tcgen05 grouped (gate+up+SiLU one pass), 7 launches"
+                if f == "q4r4" and S >= 64:             # the grouped products with one formula per group term (opt-in, within 1e-5)
+                    prev = mb.lib().moty_cuda_set_q4r4_batch_relaxed(1)
+                    row["us_relaxed"] = round(time_moe(torch, layers, name, S, dev, stream, reps=3, run=4), 1)
+                    mb.lib().moty_cuda_set_q4r4_batch_relaxed(prev)
                 rows.append(row)
         for m in layers:
             m.free()
@@ -968,6 +976,8 @@ def run_case(args):
     rng = np.random.default_rng(3)
     if parts[0] == "moe":                                      # moe:NAME:S -- layer calls of a routed layer, two weight sets
         name, S = parts[1], int(parts[2])
+        if len(parts) > 3 and parts[3] == "relaxed":       # moe:NAME:S:relaxed -- Q4R4 grouped products with the opt-in switch
+            mb.lib().moty_cuda_set_q4r4_batch_relaxed(1)
         layers, per_expert = make_moe_layers(mb, name, 2, 0, rng)
         stream = torch.cuda.Stream(device=dev)
         with torch.cuda.stream(stream):
@@ -1107,6 +1117,9 @@ def run_case(args):
         return
     fmt, S, O, I = parts
     S, O, I = int(S), int(O), int(I)
+    if fmt in ("q4r4x", "q8r4x"):                       # the batch kernel with one formula for every token (opt-in switch)
+        mb.lib().moty_cuda_set_q4r4_batch_relaxed(1)
+        fmt = fmt[:-1]
     if fmt == "q8_0":
         w = mb.Mat.i8(rng.integers(-127, 128, (O, I), dtype=np.int8), rng.uniform(0.001, 0.02, O).astype(np.float32), device=0)
         nbytes = algo_bytes(O, I, S)

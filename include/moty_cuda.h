@@ -158,6 +158,13 @@ int moty_cuda_mat_apply(MotyCudaMat *w, float *y, const float *x, int S);
  * takes without that switch, f32 x int4 with one scale multiply per group of 32 (agrees with the reference to the f32
  * rounding of a 32-term sum: its own SIMD tiers order that sum differently too).  Returns the previous value. */
 int moty_cuda_set_i4g_float_path(int on);
+/* MOTY_WF_Q4R4 / MOTY_WF_Q8R4 batches of five rows and more, dense and grouped (MoE prompts): 0 (default) = bit for bit
+ * what moty_matmul_q4r4_s computes, which has two formulas for a group's term and picks one by the token's place in its
+ * 32-token tile (hw/hw_q4r4.h:58-59 token by token, :78-81 four tokens at a time); 1 = the token-by-token formula for
+ * every token: tokens the reference treats that way keep their bits, the others move by the rounding of one fused
+ * multiply-add per group (about 1e-7 of the row's largest term), and the kernel sheds a third of its instructions.
+ * Batches of up to four rows are not affected.  Returns the previous value. */
+int moty_cuda_set_q4r4_batch_relaxed(int on);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);
 /* n (1..8) independent one-row products in ONE launch: y_dev[m] = mat_apply(w[m], x_dev[m], S = 1) for MOTY_WF_I8
  * matrices on one GPU with I % 16 == 0 and I <= 16384 (x_dev[m] 16-byte aligned; the pointers may repeat: the q, k, v

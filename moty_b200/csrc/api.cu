@@ -30,6 +30,7 @@ bool moty_debug_sync() {
     return on == 1;
 }
 
+static int g_q4r4_relaxed = 0;  // Q4R4 / Q8R4 batches (S >= 5): 0 = the reference's two formulas bit for bit, 1 = one formula, faster
 static int g_i4g_float = 0;     // MOTY_WF_I4G products: 0 = integer path (the reference with IDOT4=1), 1 = f32 x int4 (its default)
 
 // Programmatic dependent launch is on unless the environment says MOTY_CUDA_PDL=0 (read once).
@@ -485,7 +486,7 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
                                (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
                                (uint8_t *)c->misc.p, y, O, S, I, O, 0,
-                               c->sms, st);
+                               c->sms, st, g_q4r4_relaxed);
     }
     if (w->fmt == MOTY_WF_Q8R4) {
         // the int8 sibling of Q4R4: same group quantizer, same chain, no offset term; one kernel for every S
@@ -504,7 +505,7 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
                                (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
-                               (uint8_t *)c->misc.p, y, O, S, I, O, 1, c->sms, st);
+                               (uint8_t *)c->misc.p, y, O, S, I, O, 1, c->sms, st, g_q4r4_relaxed);
     }
     if (w->fmt == MOTY_WF_I4) {
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
@@ -536,6 +537,14 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
 extern "C" int moty_cuda_set_i4g_float_path(int on) {
     const int prev = g_i4g_float;
     g_i4g_float = on ? 1 : 0;
+    if (prev != g_i4g_float) g_mat_gen++;       // cached graphs of host calls hold the kernels of the other path
+    return prev;
+}
+
+extern "C" int moty_cuda_set_q4r4_batch_relaxed(int on) {
+    const int prev = g_q4r4_relaxed;
+    g_q4r4_relaxed = on ? 1 : 0;
+    if (prev != g_q4r4_relaxed) g_mat_gen++;
     return prev;
 }
 
@@ -1676,15 +1685,15 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         CKR(moty_grow(c, &c->rec, P8 * (size_t)(nbD > nbI ? nbD : nbI) * 8));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_gate, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
-                                    m->pair_tok, m->form, (int2 *)c->rec.p, 1, (float *)c->g.p, I, (int)P, D, I, st));
+                                    m->pair_tok, m->form, (int2 *)c->rec.p, 1, (float *)c->g.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_up, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
-                                    m->pair_tok, m->form, (int2 *)c->rec.p, 0, (float *)c->u.p, I, (int)P, D, I, st));
+                                    m->pair_tok, m->form, (int2 *)c->rec.p, 0, (float *)c->u.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
         CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
         CKR(launch_quant_g32((const float *)c->g.p, (int)P, I, (int8_t *)c->hq.p, (float *)c->hxs.p, (int32_t *)c->hxsum.p, st));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_down, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->hq.p, (const float *)c->hxs.p, (const int32_t *)c->hxsum.p,
-                                    nullptr, m->form, (int2 *)c->rec.p, 1, (float *)c->h.p, D, (int)P, I, D, st));
+                                    nullptr, m->form, (int2 *)c->rec.p, 1, (float *)c->h.p, D, (int)P, I, D, st, g_q4r4_relaxed, c->sms));
     }
     CKR(launch_moe_combine(out, (const float *)c->h.p, wp, m->pos_of, m->ord, S, K, D, st));
     if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, P * 4, cudaMemcpyDeviceToDevice, st));

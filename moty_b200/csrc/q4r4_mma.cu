@@ -25,6 +25,12 @@
 // chain step needs in either of the reference's formulas (which one is a per-token flag):
 //   token-by-token (hw/hw_q4r4.h:58-59), v = 8*xsum:        acc = fma((float)(sum - v), d*xs, acc)
 //   4-token tile   (hw/hw_q4r4.h:78-81), v = (8*xsum)*xs:   acc = fma((float)sum, d*xs, acc); acc = fma(-d, v, acc)
+//
+// RELAX (opt-in, moty_cuda_set_q4r4_batch_relaxed): every token takes the token-by-token formula.  Tokens the
+// reference treats that way keep their bits; the others move by the rounding of one FFMA per group.  The record
+// then carries v = 0x4B400000 - 8*xsum and goes in as the MMA's accumulator input, so the instruction returns the bit
+// pattern of the float 1.5 * 2^23 + (sum - 8*xsum) and a chain step is FADD, FMUL, FFMA: no integer add, no
+// per-token select, no second FFMA.
 #include "kernels.cuh"
 #include <string.h>
 
@@ -55,6 +61,20 @@ __device__ __forceinline__ void mma_s8s8_16832_z(int (&c)[4], unsigned a0, unsig
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
+// the same with an accumulator input: the four registers of one 128-bit load, {c0, c1} for rows gid and gid + 8 alike
+__device__ __forceinline__ void mma_u8s8_16832_c4(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                                  unsigned b0, unsigned b1, const int4 &ci) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(ci.x), "r"(ci.y), "r"(ci.z), "r"(ci.w));
+}
+__device__ __forceinline__ void mma_s8s8_16832_c4(int (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                                  unsigned b0, unsigned b1, const int4 &ci) {
+    asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(ci.x), "r"(ci.y), "r"(ci.z), "r"(ci.w));
+}
+
 // int -> float for |i| < 2^22 without the conversion unit (a quarter-rate pipe that the chain would
 // saturate): 0x4B400000 is 1.5 * 2^23 as a float; adding i to its bit pattern gives the float
 // 1.5 * 2^23 + i exactly, and the subtraction is exact.  Group sums are below 2^17 in magnitude.
@@ -69,6 +89,25 @@ __device__ __forceinline__ float q4_chain_step(float acc, int sum, float d, int 
     if (tile_form) acc = fmaf(-d, __int_as_float(v), acc);
     return acc;
 }
+// RELAX: biased = 0x4B400000 + sum - 8*xsum comes straight from the MMA, and the step is
+//     acc = fmaf(small_int_to_float(biased), d * xs, acc)
+// done for two tokens at a time by the packed instructions below.
+
+// Two f32 lanes per instruction (add / mul / fma .f32x2): each lane rounds like the scalar instruction, so the packed chain
+// gives the bits of the scalar step at half the issue slots.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack2(float lo, float hi) {
+    f32x2_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi)); return r;
+}
+__device__ __forceinline__ f32x2_t pack2i(int lo, int hi) {
+    f32x2_t r; asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi)); return r;
+}
+__device__ __forceinline__ void unpack2(f32x2_t v, float &lo, float &hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v)); }
+__device__ __forceinline__ f32x2_t add2(f32x2_t a, f32x2_t b) { f32x2_t r; asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2_t mul2(f32x2_t a, f32x2_t b) { f32x2_t r; asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b)); return r; }
+__device__ __forceinline__ f32x2_t fma2(f32x2_t a, f32x2_t b, f32x2_t c) {
+    f32x2_t r; asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c)); return r;
+}
 
 // A CTA takes 8 M tiles (128 weight rows, one M tile per warp) x NT N tiles (8 NT tokens) and walks
 // the groups in stages of GCH = 8.  One stage in shared memory:
@@ -77,20 +116,28 @@ __device__ __forceinline__ float q4_chain_step(float acc, int sum, float d, int 
 //   D  per warp: 4 x 64 bytes of f16 scales
 //   B  the tokens' codes, 256 bytes per token, token stride 272 bytes (eight tokens -> eight bank groups)
 //   R  the records, [group][token pair] 16 bytes
-constexpr int GCH = 8, NSTG = 3;
+constexpr int GCH = 8;
+
 constexpr int STG_D1 = 4 * 64, BTOK = 272;
 // Q8 = the int8 sibling Q8R4 (hw/hw_q4r4.h:92-130): 128 bytes per (block, group) = 4 rows x 32 signed codes, no
 // offset term, the same chain.  Its blocks are padded by 16 bytes: a row's fragment words sit 32 bytes apart,
 // so the second block of a fragment load has to land 16 bytes off to miss the banks of the first.
-template <int NT, bool Q8> struct Q4Stage {
+// NSLOT = M tiles per CTA.  RELAX: the records sit as the fragment wants them: R [tile][group][token pair] = {c0, c1, c0, c1},
+// the MMA's accumulator input as one 128-bit load, and RX [tile][group][token pair] = {xs0, xs1}
+template <int NT, bool Q8, int NSLOT = 8, bool RELAX = false> struct Q4Stage {
     static constexpr int GB = Q8 ? 128 : 64;                   // bytes per (block, group)
     static constexpr int WBLK = Q8 ? GCH * 128 + 16 : GCH * 64 + 64, STG_W1 = 4 * WBLK;
-    static constexpr int W = 0, D = 8 * STG_W1, B = D + 8 * STG_D1, R = B + NT * 8 * BTOK, BYTES = R + NT * GCH * 64;
+    static constexpr int W = 0, D = NSLOT * STG_W1, B = D + NSLOT * STG_D1, R = B + NT * 8 * BTOK, RX = R + NT * GCH * 64;
+    static constexpr int BYTES = RX + (RELAX ? NT * GCH * 32 : 0);
 };
 
-template <int NT, bool Q8>
-__global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
-    using L = Q4Stage<NT, Q8>;
+// MW = M tiles per warp: the CTA still takes 128 rows, with 8 / MW warps.  With two M tiles a warp loads a token
+// tile's codes and records once for both, which halves the shared-memory wavefronts per MMA (the records are a
+// 128-bit load that four lanes share: four wavefronts however few bytes it moves).
+template <int NT, bool Q8, bool RELAX, int MW, int NS, int NW>
+__global__ void __launch_bounds__(32 * NW) q4r4_mma_kernel(Q4MmaArgs a) {
+    constexpr int NSLOT = NW * MW, NTHR = 32 * NW;
+    using L = Q4Stage<NT, Q8, NSLOT, RELAX>;
     constexpr int GB = L::GB, WBLK = L::WBLK, STG_W1 = L::STG_W1;
     extern __shared__ int4 smem_q4mma[];
     unsigned char *smem = reinterpret_cast<unsigned char *>(smem_q4mma);
@@ -106,103 +153,143 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
         Wp = t.w; Dp = t.d; n00 = t.row0; S = t.row0 + t.nrows;
     }
     const int nblk = (O + 3) / 4, nstage = (nb + GCH - 1) / GCH;
-    const int mt = blockIdx.x * 8 + warp;                      // this warp's M tile (may lie past the end: it still copies and syncs)
-    const int row_a = mt * 16 + gid, row_b = row_a + 8;
-    // where this thread's fragment words and scales sit inside a stage
+    // the warp's M tiles are slots vw0 .. vw0 + MW - 1 of the CTA's eight (a tile may lie past the end: it is still copied)
+    const int vw0 = warp * MW, mt0 = blockIdx.x * NSLOT + vw0;
+    // where this thread's fragment words and scales sit inside a stage, for M-tile slot 0
     const int ba_l = gid >> 2, bb_l = ba_l + 2, rr = gid & 3;
-    const int offA = L::W + warp * STG_W1 + ba_l * WBLK + rr * (GB / 4) + tid * 4, offB = L::W + warp * STG_W1 + bb_l * WBLK + rr * (GB / 4) + tid * 4;
-    const int offdA = L::D + warp * STG_D1 + ba_l * 64 + rr * 2, offdB = L::D + warp * STG_D1 + bb_l * 64 + rr * 2;
+    const int offA = L::W + ba_l * WBLK + rr * (GB / 4) + tid * 4, offB = L::W + bb_l * WBLK + rr * (GB / 4) + tid * 4;
+    const int offdA = L::D + ba_l * 64 + rr * 2, offdB = L::D + bb_l * 64 + rr * 2;
     // first group held by stage s: a partial last stage is shifted back so that it never runs past the row
     auto stage_g0 = [&](int s) { const int g0 = s * GCH; return g0 + GCH <= nb ? g0 : (nb >= GCH ? nb - GCH : 0); };
     auto fill_w = [&](int s) {                                 // weights: lane l copies int4 number l of each block, and 8 bytes of scales
         if (s >= nstage) return;
-        unsigned char *dst = smem + (size_t)(s % NSTG) * L::BYTES;
+        unsigned char *dst = smem + (size_t)(s % NS) * L::BYTES;
         const int gs = stage_g0(s);
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-            int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
+        for (int m = 0; m < MW; m++) {
+            const int vw = vw0 + m, mt = mt0 + m;
 #pragma unroll
-            for (int h = 0; h < GB / 64; h++) {                // 512 bytes per round of the warp
-                const int off = h * 512 + lane * 16;
-                if (nb >= GCH || off < nb * GB)
-                    cp_async16(dst + L::W + warp * STG_W1 + q * WBLK + off, Wp + ((size_t)blk * nb + gs) * GB + off);
+            for (int q = 0; q < 4; q++) {
+                int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
+#pragma unroll
+                for (int h = 0; h < GB / 64; h++) {            // 512 bytes per round of the warp
+                    const int off = h * 512 + lane * 16;
+                    if (nb >= GCH || off < nb * GB)
+                        cp_async16(dst + L::W + vw * STG_W1 + q * WBLK + off, Wp + ((size_t)blk * nb + gs) * GB + off);
+                }
             }
+            const int q = lane >> 3, part = lane & 7;
+            int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
+            if (nb >= GCH || part < nb)
+                cp_async8(dst + L::D + vw * STG_D1 + q * 64 + part * 8, Dp + ((size_t)blk * nb + gs) * 4 + part * 4);
         }
-        const int q = lane >> 3, part = lane & 7;
-        int blk = mt * 4 + q; blk = blk < nblk ? blk : nblk - 1;
-        if (nb >= GCH || part < nb)
-            cp_async8(dst + L::D + warp * STG_D1 + q * 64 + part * 8, Dp + ((size_t)blk * nb + gs) * 4 + part * 4);
     };
     auto fill_x = [&](int s) {                                 // activation side: codes and records of the CTA's tokens
         if (s >= nstage) return;
-        unsigned char *dst = smem + (size_t)(s % NSTG) * L::BYTES;
+        unsigned char *dst = smem + (size_t)(s % NS) * L::BYTES;
         const int gs = stage_g0(s);
-        for (int t = threadIdx.x; t < NT * 128; t += 256) {    // 16 chunks of 16 bytes per token
+        for (int t = threadIdx.x; t < NT * 128; t += NTHR) {   // 16 chunks of 16 bytes per token
             const int tok = t >> 4, ch = t & 15;
             int n = n00 + tok; n = n < S ? n : S - 1;
             if (a.xmap) n = a.xmap[n];
             if (nb >= GCH || ch * 16 < nb * 32)
                 cp_async16(dst + L::B + tok * BTOK + ch * 16, a.xq + (size_t)n * I + (size_t)gs * 32 + ch * 16);
         }
-        if (!a.tiles) {
-            for (int t = threadIdx.x; t < NT * GCH * 4; t += 256) {   // per N tile and group: four token pairs of 16 bytes
+        if (RELAX) {                                           // record {xs, c} of token k: xs -> RX, c -> both halves of its pair's R entry
+            for (int t = threadIdx.x; t < NT * GCH * 8; t += NTHR) {
+                const int j = t / (GCH * 8), u = (t >> 3) % GCH, k = t & 7;
+                if (gs + u < nb && n00 + j * 8 + k < (a.tiles ? S : a.S8)) {
+                    const int *src = reinterpret_cast<const int *>(a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + k);
+                    unsigned char *r = dst + L::R + j * GCH * 64 + u * 64 + (k >> 1) * 16 + (k & 1) * 4;
+                    cp_async4(dst + L::RX + j * GCH * 32 + u * 32 + k * 4, src);
+                    cp_async4(r, src + 1);
+                    cp_async4(r + 8, src + 1);
+                }
+            }
+        } else if (!a.tiles) {
+            for (int t = threadIdx.x; t < NT * GCH * 4; t += NTHR) {  // per N tile and group: four token pairs of 16 bytes
                 const int j = t / (GCH * 4), u = (t >> 2) % GCH, pr = t & 3;
                 if (gs + u < nb && n00 + j * 8 + pr * 2 < a.S8)        // token pairs past the padded batch: nothing to copy, nothing stored
                     cp_async16(dst + L::R + j * GCH * 64 + u * 64 + pr * 16, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + pr * 2);
             }
         } else {
-            for (int t = threadIdx.x; t < NT * GCH * 8; t += 256) {   // a tile may start at an odd row: single 8-byte records
+            for (int t = threadIdx.x; t < NT * GCH * 8; t += NTHR) {  // a tile may start at an odd row: single 8-byte records
                 const int j = t / (GCH * 8), u = (t >> 3) % GCH, k = t & 7;
                 if (gs + u < nb && n00 + j * 8 + k < S)
                     cp_async8(dst + L::R + j * GCH * 64 + u * 64 + k * 8, a.rec + (size_t)(gs + u) * a.S8 + n00 + j * 8 + k);
             }
         }
     };
-    fill_w(0); fill_w(1);                                      // weights only: may overlap the previous kernel
+#pragma unroll
+    for (int i = 0; i < NS - 1; i++) fill_w(i);                // weights only: may overlap the previous kernel
     pdl_wait();                                                // codes and records come from the kernels before this one
-    fill_x(0); cp_async_commit();
-    fill_x(1); cp_async_commit();
+#pragma unroll
+    for (int i = 0; i < NS - 1; i++) { fill_x(i); cp_async_commit(); }
 
     bool f0[NT], f1[NT];
-    float acc[NT][4];
+    float acc[MW][NT][4];
+    f32x2_t pacc[MW][NT][2];                                   // RELAX: {(row_a, t0), (row_a, t1)} and {(row_b, t0), (row_b, t1)}
+    const f32x2_t neg_magic = pack2(-12582912.0f, -12582912.0f);
 #pragma unroll
     for (int j = 0; j < NT; j++) {
         int t0 = n00 + j * 8 + tid * 2, t1 = t0 + 1;
-        f0[j] = t0 < S && a.form[t0] != 0; f1[j] = t1 < S && a.form[t1] != 0;
-        acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+        f0[j] = !RELAX && t0 < S && a.form[t0] != 0; f1[j] = !RELAX && t1 < S && a.form[t1] != 0;
+#pragma unroll
+        for (int m = 0; m < MW; m++) {
+            acc[m][j][0] = acc[m][j][1] = acc[m][j][2] = acc[m][j][3] = 0.f;
+            pacc[m][j][0] = pacc[m][j][1] = 0ull;
+        }
     }
     for (int s = 0; s < nstage; s++) {
-        cp_async_wait<1>();                                    // this thread's copies of stage s have landed
+        cp_async_wait<NS - 2>();                               // this thread's copies of stage s have landed
         __syncthreads();                                       // everyone's have, and everyone is done with stage s - 1
-        fill_w(s + 2); fill_x(s + 2); cp_async_commit();       // into the slot stage s - 1 used
-        const unsigned char *st = smem + (size_t)(s % NSTG) * L::BYTES;
+        fill_w(s + NS - 1); fill_x(s + NS - 1); cp_async_commit();   // into the slot stage s - 1 used
+        const unsigned char *st = smem + (size_t)(s % NS) * L::BYTES;
         const int g0 = s * GCH, gs = stage_g0(s);
         auto group_step = [&](int ul) {                        // ul: position of the group inside the stage
-            const float dA = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdA + ul * 8));
-            const float dB = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(st + offdB + ul * 8));
-            unsigned a0, a1, a2, a3;
-            if (Q8) {                                          // a row's codes k = 4 tid .. and k = 16 + 4 tid ..: two words
-                a0 = *reinterpret_cast<const unsigned *>(st + offA + ul * GB); a2 = *reinterpret_cast<const unsigned *>(st + offA + ul * GB + 16);
-                a1 = *reinterpret_cast<const unsigned *>(st + offB + ul * GB); a3 = *reinterpret_cast<const unsigned *>(st + offB + ul * GB + 16);
-            } else {                                           // one word: low nibbles -> a0/a1, high nibbles -> a2/a3
-                const unsigned wA = *reinterpret_cast<const unsigned *>(st + offA + ul * GB);
-                const unsigned wB = *reinterpret_cast<const unsigned *>(st + offB + ul * GB);
-                a0 = wA & 0x0f0f0f0fu; a2 = (wA >> 4) & 0x0f0f0f0fu;
-                a1 = wB & 0x0f0f0f0fu; a3 = (wB >> 4) & 0x0f0f0f0fu;
+            float dA[MW], dB[MW];
+            unsigned a0[MW], a1[MW], a2[MW], a3[MW];
+#pragma unroll
+            for (int m = 0; m < MW; m++) {
+                const unsigned char *sw = st + (vw0 + m) * STG_W1, *sd = st + (vw0 + m) * STG_D1;
+                dA[m] = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(sd + offdA + ul * 8));
+                dB[m] = f16bits_to_f32(*reinterpret_cast<const uint16_t *>(sd + offdB + ul * 8));
+                if (Q8) {                                      // a row's codes k = 4 tid .. and k = 16 + 4 tid ..: two words
+                    a0[m] = *reinterpret_cast<const unsigned *>(sw + offA + ul * GB); a2[m] = *reinterpret_cast<const unsigned *>(sw + offA + ul * GB + 16);
+                    a1[m] = *reinterpret_cast<const unsigned *>(sw + offB + ul * GB); a3[m] = *reinterpret_cast<const unsigned *>(sw + offB + ul * GB + 16);
+                } else {                                       // one word: low nibbles -> a0/a1, high nibbles -> a2/a3
+                    const unsigned wA = *reinterpret_cast<const unsigned *>(sw + offA + ul * GB);
+                    const unsigned wB = *reinterpret_cast<const unsigned *>(sw + offB + ul * GB);
+                    a0[m] = wA & 0x0f0f0f0fu; a2[m] = (wA >> 4) & 0x0f0f0f0fu;
+                    a1[m] = wB & 0x0f0f0f0fu; a3[m] = (wB >> 4) & 0x0f0f0f0fu;
+                }
             }
 #pragma unroll
             for (int j = 0; j < NT; j++) {
                 const unsigned char *bp = st + L::B + (j * 8 + gid) * BTOK + ul * 32 + tid * 4;
                 const unsigned b0 = *reinterpret_cast<const unsigned *>(bp), b1 = *reinterpret_cast<const unsigned *>(bp + 16);
-                int c[4];
-                if (Q8) mma_s8s8_16832_z(c, a0, a1, a2, a3, b0, b1);
-                else mma_u8s8_16832(c, a0, a1, a2, a3, b0, b1);
-                const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1
-                const int v0 = f0[j] ? 0 : q.y, v1 = f1[j] ? 0 : q.w;
-                acc[j][0] = q4_chain_step(acc[j][0], c[0], dA, q.x, v0, q.y, f0[j]);   // (row_a, t0)
-                acc[j][1] = q4_chain_step(acc[j][1], c[1], dA, q.z, v1, q.w, f1[j]);   // (row_a, t1)
-                acc[j][2] = q4_chain_step(acc[j][2], c[2], dB, q.x, v0, q.y, f0[j]);   // (row_b, t0)
-                acc[j][3] = q4_chain_step(acc[j][3], c[3], dB, q.z, v1, q.w, f1[j]);   // (row_b, t1)
+                const int4 q = *reinterpret_cast<const int4 *>(st + L::R + j * GCH * 64 + ul * 64 + tid * 16);   // {xs, v} of tokens t0, t1; RELAX: {c0, c1, c0, c1}
+                f32x2_t xs2 = 0ull;
+                if (RELAX) xs2 = *reinterpret_cast<const f32x2_t *>(st + L::RX + j * GCH * 32 + ul * 32 + tid * 8);
+#pragma unroll
+                for (int m = 0; m < MW; m++) {
+                    int c[4];
+                    if (RELAX) {                               // the relaxed step, two tokens per instruction
+                        if (Q8) mma_s8s8_16832_c4(c, a0[m], a1[m], a2[m], a3[m], b0, b1, q);
+                        else mma_u8s8_16832_c4(c, a0[m], a1[m], a2[m], a3[m], b0, b1, q);
+                        const f32x2_t fa = add2(pack2i(c[0], c[1]), neg_magic), fb = add2(pack2i(c[2], c[3]), neg_magic);
+                        pacc[m][j][0] = fma2(fa, mul2(pack2(dA[m], dA[m]), xs2), pacc[m][j][0]);
+                        pacc[m][j][1] = fma2(fb, mul2(pack2(dB[m], dB[m]), xs2), pacc[m][j][1]);
+                    } else {
+                        if (Q8) mma_s8s8_16832_z(c, a0[m], a1[m], a2[m], a3[m], b0, b1);
+                        else mma_u8s8_16832(c, a0[m], a1[m], a2[m], a3[m], b0, b1);
+                        const int v0 = f0[j] ? 0 : q.y, v1 = f1[j] ? 0 : q.w;
+                        acc[m][j][0] = q4_chain_step(acc[m][j][0], c[0], dA[m], q.x, v0, q.y, f0[j]);   // (row_a, t0)
+                        acc[m][j][1] = q4_chain_step(acc[m][j][1], c[1], dA[m], q.z, v1, q.w, f1[j]);   // (row_a, t1)
+                        acc[m][j][2] = q4_chain_step(acc[m][j][2], c[2], dB[m], q.x, v0, q.y, f0[j]);   // (row_b, t0)
+                        acc[m][j][3] = q4_chain_step(acc[m][j][3], c[3], dB[m], q.z, v1, q.w, f1[j]);   // (row_b, t1)
+                    }
+                }
             }
         };
         if (g0 + GCH <= nb) {
@@ -213,16 +300,29 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
         }
     }
     cp_async_wait<0>();
+    if (RELAX) {
 #pragma unroll
-    for (int j = 0; j < NT; j++) {
-        const int t0 = n00 + j * 8 + tid * 2, t1 = t0 + 1;
-        if (t0 < S) {
-            if (row_a < O) a.y[(size_t)t0 * a.ldy + row_a] = acc[j][0];
-            if (row_b < O) a.y[(size_t)t0 * a.ldy + row_b] = acc[j][2];
-        }
-        if (t1 < S) {
-            if (row_a < O) a.y[(size_t)t1 * a.ldy + row_a] = acc[j][1];
-            if (row_b < O) a.y[(size_t)t1 * a.ldy + row_b] = acc[j][3];
+        for (int m = 0; m < MW; m++)
+#pragma unroll
+            for (int j = 0; j < NT; j++) {
+                unpack2(pacc[m][j][0], acc[m][j][0], acc[m][j][1]);
+                unpack2(pacc[m][j][1], acc[m][j][2], acc[m][j][3]);
+            }
+    }
+#pragma unroll
+    for (int m = 0; m < MW; m++) {
+        const int row_a = (mt0 + m) * 16 + gid, row_b = row_a + 8;
+#pragma unroll
+        for (int j = 0; j < NT; j++) {
+            const int t0 = n00 + j * 8 + tid * 2, t1 = t0 + 1;
+            if (t0 < S) {
+                if (row_a < O) a.y[(size_t)t0 * a.ldy + row_a] = acc[m][j][0];
+                if (row_b < O) a.y[(size_t)t0 * a.ldy + row_b] = acc[m][j][2];
+            }
+            if (t1 < S) {
+                if (row_a < O) a.y[(size_t)t1 * a.ldy + row_a] = acc[m][j][1];
+                if (row_b < O) a.y[(size_t)t1 * a.ldy + row_b] = acc[m][j][3];
+            }
         }
     }
 }
@@ -233,7 +333,7 @@ __global__ void __launch_bounds__(256) q4r4_mma_kernel(Q4MmaArgs a) {
 // token-by-token kernel (nn/matmul.c:424-432)
 __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
                                                        int2 *__restrict__ rec, uint8_t *__restrict__ form, int S, int S8, int nb,
-                                                       int q8) {
+                                                       int q8, int relax) {
     pdl_wait();                                   // (no early trigger: the product after this one is not persistent, and its
                                                   // CTAs spread unevenly when they arrive while others are still resident)
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
@@ -246,54 +346,76 @@ __global__ void __launch_bounds__(256) q4r4_rec_kernel(const float *__restrict__
         const int f = (!q8 && (t - t0) < ns / 4 * 4) ? 1 : 0;            // Q8R4 has one formula and no offset term
         const float sc = xs[(size_t)t * nb + g]; const int sm = q8 ? 0 : xsum[(size_t)t * nb + g];
         r.x = __float_as_int(sc);
-        r.y = f ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm;
+        r.y = relax ? 0x4B400000 - 8 * sm : (f ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm);
         if (g == 0) form[t] = (uint8_t)f;
     }
     rec[i] = r;
 }
 
-template <int NT, bool Q8 = false>
-static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st, int ntiles_max = 0) {
-    constexpr int SMEM = NSTG * Q4Stage<NT, Q8>::BYTES;
+template <int NT, bool Q8, bool RELAX, int MW, int NS, int NW>
+static int launch_mma_tm(const Q4MmaArgs &a, cudaStream_t st, int ntiles_max) {
+    constexpr int NSLOT = NW * MW, SMEM = NS * Q4Stage<NT, Q8, NSLOT, RELAX>::BYTES;
     static bool attr_done[MOTY_MAX_DEV];
     int dev = 0;
     CK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= MOTY_MAX_DEV) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: device %d", dev);
     if (!attr_done[dev]) {
-        CK(cudaFuncSetAttribute(q4r4_mma_kernel<NT, Q8>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
+        CK(cudaFuncSetAttribute(q4r4_mma_kernel<NT, Q8, RELAX, MW, NS, NW>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM));
         attr_done[dev] = true;
     }
     const int nmt = (a.O + 15) / 16;
-    dim3 grid((nmt + 7) / 8, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT));
+    dim3 grid((nmt + NSLOT - 1) / NSLOT, a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT));
     if (grid.y > 65535) return moty_set_error(MOTY_CUDA_ELIMIT, "q4r4_mma: S=%d in one call", a.S);
-    CK(moty_launch_pdl(q4r4_mma_kernel<NT, Q8>, grid, dim3(256), (size_t)SMEM, st, a));
+    CK(moty_launch_pdl(q4r4_mma_kernel<NT, Q8, RELAX, MW, NS, NW>, grid, dim3(32 * NW), (size_t)SMEM, st, a));
     return 0;
+}
+// The exact kernel: 8 warps x one M tile, three stages.  The relaxed one: two M tiles per warp and two stages (more CTAs
+// per SM: it is bound by latency, not by bytes); 128 rows per CTA, or 256 when 128-row CTAs would come to between one
+// and three resident sets of 3 per SM (measured: 3840 x 15360 at S = 512 285 vs 320 us; no difference on larger grids).
+template <int NT, bool Q8 = false, bool RELAX = false>
+static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st, int sms, int ntiles_max = 0) {
+    if (!RELAX) return launch_mma_tm<NT, Q8, false, 1, 3, 8>(a, st, ntiles_max);
+    const long long rows = a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT);
+    const long long ctas4 = ((a.O + 15) / 16 + 7) / 8 * rows, slots = 3LL * sms;
+    if (ctas4 > slots && ctas4 < 3 * slots) return launch_mma_tm<NT, Q8, true, 2, 2, 8>(a, st, ntiles_max);
+    return launch_mma_tm<NT, Q8, true, 2, 2, 4>(a, st, ntiles_max);
 }
 
 // xq/xs/xsum: the group-quantized batch; rec: scratch for (I/32) * ceil8(S) records of 8 bytes;
 // form: scratch for S bytes
 // q8 != 0: w holds Q8R4 codes (128 bytes per block and group)
+// relax != 0: the token-by-token formula for every token (see the head of this file)
 int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
-                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int q8, int sms, cudaStream_t st) {
+                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int q8, int sms, cudaStream_t st, int relax) {
     if (I % 32 != 0 || I <= 0 || S <= 0) return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma: S=%d I=%d", S, I);
     if (O <= 0) return 0;
     const int nb = I / 32, S8 = (S + 7) / 8 * 8;
     const long long nrec = (long long)S8 * nb;
-    CK(moty_launch_pdl(q4r4_rec_kernel, dim3((unsigned)((nrec + 255) / 256)), dim3(256), (size_t)0, st, xs, xsum, rec, form, S, S8, nb, q8));
+    CK(moty_launch_pdl(q4r4_rec_kernel, dim3((unsigned)((nrec + 255) / 256)), dim3(256), (size_t)0, st, xs, xsum, rec, form, S, S8, nb, q8, relax));
     Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.w = w; a.d = d; a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = S; a.S8 = S8; a.I = I; a.O = O;
     // more N tiles per CTA amortise the weight traffic and unpack; fewer give more CTAs: keep ~2 CTAs per SM
     const long long mct = ((O + 15) / 16 + 7) / 8, want = (long long)sms * 2;
     // (never a tile wider than the batch: its empty token columns would cost the same chain work)
     const bool nt4 = S > 16 && mct * ((S + 31) / 32) >= want, nt2 = S > 8 && mct * ((S + 15) / 16) >= want;
-    if (q8) {
-        if (nt4) return launch_mma_t<4, true>(a, st);
-        if (nt2) return launch_mma_t<2, true>(a, st);
-        return launch_mma_t<1, true>(a, st);
+    if (relax) {
+        if (q8) {
+            if (nt4) return launch_mma_t<4, true, true>(a, st, sms);
+            if (nt2) return launch_mma_t<2, true, true>(a, st, sms);
+            return launch_mma_t<1, true, true>(a, st, sms);
+        }
+        if (nt4) return launch_mma_t<4, false, true>(a, st, sms);
+        if (nt2) return launch_mma_t<2, false, true>(a, st, sms);
+        return launch_mma_t<1, false, true>(a, st, sms);
     }
-    if (nt4) return launch_mma_t<4>(a, st);
-    if (nt2) return launch_mma_t<2>(a, st);
-    return launch_mma_t<1>(a, st);
+    if (q8) {
+        if (nt4) return launch_mma_t<4, true>(a, st, sms);
+        if (nt2) return launch_mma_t<2, true>(a, st, sms);
+        return launch_mma_t<1, true>(a, st, sms);
+    }
+    if (nt4) return launch_mma_t<4>(a, st, sms);
+    if (nt2) return launch_mma_t<2>(a, st, sms);
+    return launch_mma_t<1>(a, st, sms);
 }
 
 // records of a gathered batch: row p of the batch is row xmap[p] (null: p) of xs/xsum, its formula
@@ -301,7 +423,7 @@ int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const
 __global__ void __launch_bounds__(256) q4r4_rec_gather_kernel(const float *__restrict__ xs, const int32_t *__restrict__ xsum,
                                                               const int *__restrict__ xmap, const uint8_t *__restrict__ form,
                                                               const int *__restrict__ npairs_dev, int2 *__restrict__ rec,
-                                                              int P8, int nb) {
+                                                              int P8, int nb, int relax) {
     pdl_wait();
     const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
     if (i >= (long long)P8 * nb) return;
@@ -311,7 +433,7 @@ __global__ void __launch_bounds__(256) q4r4_rec_gather_kernel(const float *__res
         const int t = xmap ? xmap[p] : p;
         const float sc = xs[(size_t)t * nb + g]; const int sm = xsum[(size_t)t * nb + g];
         r.x = __float_as_int(sc);
-        r.y = form[p] ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm;
+        r.y = relax ? 0x4B400000 - 8 * sm : (form[p] ? __float_as_int(__fmul_rn(__fmul_rn(8.f, (float)sm), sc)) : 8 * sm);
     }
     rec[i] = r;
 }
@@ -322,7 +444,7 @@ __global__ void __launch_bounds__(256) q4r4_rec_gather_kernel(const float *__res
 int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
                             const int *npairs_dev, const int8_t *xq, const float *xs, const int32_t *xsum,
                             const int *xmap, const uint8_t *form, int2 *rec, int build_rec, float *y, int ldy, int P,
-                            int I, int O, cudaStream_t st) {
+                            int I, int O, cudaStream_t st, int relax, int sms) {
     if (I % 32 != 0 || I <= 0 || P <= 0 || (tile_rows != 8 && tile_rows != 16 && tile_rows != 32))
         return moty_set_error(MOTY_CUDA_EARG, "q4r4_mma_grouped: P=%d I=%d tile=%d", P, I, tile_rows);
     if (O <= 0 || ntiles_max <= 0) return 0;
@@ -331,12 +453,17 @@ int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntil
     const long long nrec = (long long)P8 * nb;
     if (build_rec) {                                           // gate and up share the records of the gathered input
         CK(moty_launch_pdl(q4r4_rec_gather_kernel, dim3((unsigned)((nrec + 255) / 256)), dim3(256), (size_t)0, st, xs, xsum, xmap, form,
-                           npairs_dev, rec, P8, nb));
+                           npairs_dev, rec, P8, nb, relax));
     }
     Q4MmaArgs a; memset(&a, 0, sizeof a);
     a.xq = xq; a.rec = rec; a.form = form; a.y = y; a.ldy = ldy; a.S = P; a.S8 = P8; a.I = I; a.O = O;
     a.tiles = tiles; a.ntiles_dev = ntiles_dev; a.xmap = xmap;
-    if (tile_rows == 32) return launch_mma_t<4>(a, st, ntiles_max);
-    if (tile_rows == 16) return launch_mma_t<2>(a, st, ntiles_max);
-    return launch_mma_t<1>(a, st, ntiles_max);
+    if (relax) {
+        if (tile_rows == 32) return launch_mma_t<4, false, true>(a, st, sms, ntiles_max);
+        if (tile_rows == 16) return launch_mma_t<2, false, true>(a, st, sms, ntiles_max);
+        return launch_mma_t<1, false, true>(a, st, sms, ntiles_max);
+    }
+    if (tile_rows == 32) return launch_mma_t<4>(a, st, sms, ntiles_max);
+    if (tile_rows == 16) return launch_mma_t<2>(a, st, sms, ntiles_max);
+    return launch_mma_t<1>(a, st, sms, ntiles_max);
 }

@@ -258,6 +258,37 @@ def test_moe_q4r4_vs_oracle(gpu, oracle, S):
     assert same_bits(got, want)
 
 
+@pytest.mark.parametrize("S", [21, 130])
+def test_moe_q4r4_batch_relaxed(gpu, oracle, S):
+    """A routed Q4R4 prompt with moty_cuda_set_q4r4_batch_relaxed(1): within 1e-5 of the oracle's magnitude per token
+    (the grouped products use one formula for a group's term instead of the reference's two); the default is bit-exact
+    before and after."""
+    from oracle import Experts
+    E, K, I, D = 16, 4, 96, 128
+    rng = np.random.default_rng(100 + S)
+    packs = {k: [oracle.pack_q4r4((rng.standard_normal(shape) * 0.05).astype(np.float32)) for _ in range(E)]
+             for k, shape in (("g", (I, D)), ("u", (I, D)), ("d", (D, I)))}
+    cat = lambda k, j: np.concatenate([p[j] for p in packs[k]])
+    ex = Experts(E, K, I, D, cat("g", 0), cat("u", 0), cat("d", 0), cat("g", 1), cat("u", 1), cat("d", 1))
+    m = gpu.Moe(E, K, I, D, efmt=gpu.WF_Q4R4)
+    for e in range(E):
+        m.upload_expert(e, packs["g"][e][0], packs["g"][e][1], packs["u"][e][0], packs["u"][e][1],
+                        packs["d"][e][0], packs["d"][e][1])
+    x = rng.standard_normal((S, D)).astype(np.float32)
+    logits = (rng.standard_normal((S, E)) * 0.5).astype(np.float32)
+    want = oracle.moe_q4r4(ex, x, logits)[0]
+    assert same_bits(m.batch(x, logits), want)
+    L = gpu.lib()
+    prev = L.moty_cuda_set_q4r4_batch_relaxed(1)
+    try:
+        got = m.batch(x, logits)
+    finally:
+        L.moty_cuda_set_q4r4_batch_relaxed(prev)
+    err = np.abs(got - want).max(axis=1) / np.abs(want).max(axis=1)
+    assert err.max() <= 1e-5, err.max()
+    assert same_bits(m.batch(x, logits), want)
+
+
 def test_expert_shards_sum_to_the_whole(gpu, oracle):
     """Two expert-parallel shards: their partial outputs add up to the unsharded
     block (f32 sums in another order: compared at 1e-5 of magnitude)."""

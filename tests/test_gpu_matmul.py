@@ -88,6 +88,38 @@ def test_q4r4_batches_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I,S", [(4096, 256, 320), (4100, 352, 157), (2052, 3840, 37), (1024, 1024, 5), (515, 3840, 512)])
+def test_q4r4_batch_relaxed(gpu, oracle, O, I, S):
+    """moty_cuda_set_q4r4_batch_relaxed(1): the token-by-token formula (hw/hw_q4r4.h:58-59) for every token of a batch.
+    Tokens that moty_matmul_q4r4_s sends through that formula -- the last S % 4 of the batch's final 32-token tile
+    (nn/matmul.c:424-432) -- keep their bits; the others stay within 1e-5 of the row's magnitude (measured: a few 1e-7).
+    Q8R4 has one formula, so its relaxed result is bit for bit the exact one.  The switch is put back and the exact path
+    checked again afterwards."""
+    rng = np.random.default_rng(O + 7 * I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, s16 = oracle.pack_q4r4(Wf)
+    q8, s16b = oracle.pack_q8r4(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    W4, W8 = gpu.Mat.q4r4(q4, s16, O, I), gpu.Mat.q8r4(q8, s16b, O, I)
+    yo = oracle.matmul_q4r4_s(x, q4, s16, O)
+    L = gpu.lib()
+    prev = L.moty_cuda_set_q4r4_batch_relaxed(1)
+    try:
+        y = gpu.mat_apply(W4, x)
+        y8 = gpu.mat_apply(W8, x)
+    finally:
+        assert L.moty_cuda_set_q4r4_batch_relaxed(prev) == 1
+    assert prev == 0
+    tile0 = (S - 1) // 32 * 32
+    first_single = tile0 + (S - tile0) // 4 * 4                             # tokens from here on take the token-by-token kernel
+    assert same_bits(y[first_single:], yo[first_single:])
+    err = np.abs(y - yo).max(axis=1) / np.abs(yo).max(axis=1)
+    assert err.max() <= 1e-5, err.max()
+    assert first_single == 0 or err[:first_single].max() > 0, "the relaxed kernel did not run"
+    assert same_bits(y8, oracle.matmul_q8r4_s(x, q8, s16b, O))
+    assert same_bits(gpu.mat_apply(W4, x), yo)                              # the default again
+
+
 @pytest.mark.parametrize("O,I", [(57000, 256), (56833, 512), (151936, 1024)])
 def test_q4r4_decode_many_rows_vs_oracle(gpu, oracle, O, I):
     """Matrices with enough rows for the lane-per-row decode kernel (one activation row), a row
