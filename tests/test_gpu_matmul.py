@@ -92,7 +92,7 @@ def test_q4r4_batches_vs_oracle(gpu, oracle, O, I, S):
 def test_q4r4_batch_relaxed(gpu, oracle, O, I, S):
     """moty_cuda_set_q4r4_batch_relaxed(1): the token-by-token formula (hw/hw_q4r4.h:58-59) for every token of a batch.
     Tokens that moty_matmul_q4r4_s sends through that formula -- the last S % 4 of the batch's final 32-token tile
-    (nn/matmul.c:424-432) -- keep their bits; the others stay within 1e-5 of the row's magnitude (measured: a few 1e-7).
+    (nn/matmul.c:424-432) -- keep their bits; the others stay within 1e-5 of the row's magnitude.
     Q8R4 has one formula, so its relaxed result is bit for bit the exact one.  The switch is put back and the exact path
     checked again afterwards."""
     rng = np.random.default_rng(O + 7 * I + S)
