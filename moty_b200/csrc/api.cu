@@ -481,12 +481,10 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
                                       (const uint8_t *)c->misc.p, y, S, I, O, c->sms, st);
         }
         // batches: integer MMA per group, sequential f32 chain in registers
-        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 8));
-        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 16));
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
-                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
-                               (uint8_t *)c->misc.p, y, O, S, I, O, 0,
-                               c->sms, st, g_q4r4_relaxed);
+                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int4 *)c->rec.p,
+                               y, O, S, I, O, 0, c->sms, st, g_q4r4_relaxed);
     }
     if (w->fmt == MOTY_WF_Q8R4) {
         // the int8 sibling of Q4R4: same group quantizer, same chain, no offset term; one kernel for every S
@@ -500,12 +498,11 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
         CKR(moty_grow(c, &c->xs, (size_t)S * nb * 4));
         CKR(moty_grow(c, &c->xsum, (size_t)S * nb * 4));
-        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 8));
-        CKR(moty_grow(c, &c->misc, (size_t)S + 16));
+        CKR(moty_grow(c, &c->rec, (size_t)((S + 7) / 8 * 8) * nb * 16));
         CKR(launch_quant_g32(x, S, I, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
-                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int2 *)c->rec.p,
-                               (uint8_t *)c->misc.p, y, O, S, I, O, 1, c->sms, st, g_q4r4_relaxed);
+                               (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int4 *)c->rec.p,
+                               y, O, S, I, O, 1, c->sms, st, g_q4r4_relaxed);
     }
     if (w->fmt == MOTY_WF_I4) {
         CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
@@ -1682,18 +1679,18 @@ static int moe_apply_on(DevCtx *c, MotyCudaMoe *m, float *out, const float *x, i
         CKR(moty_grow(c, &c->hxsum, P * nbI * 4));
         CKR(launch_quant_g32(x, S, D, (int8_t *)c->xi.p, (float *)c->xs.p, (int32_t *)c->xsum.p, st));
         const size_t P8 = (P + 7) / 8 * 8;
-        CKR(moty_grow(c, &c->rec, P8 * (size_t)(nbD > nbI ? nbD : nbI) * 8));
+        CKR(moty_grow(c, &c->rec, P8 * (size_t)(nbD > nbI ? nbD : nbI) * 16));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_gate, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
-                                    m->pair_tok, m->form, (int2 *)c->rec.p, 1, (float *)c->g.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
+                                    m->pair_tok, m->form, (int4 *)c->rec.p, 1, (float *)c->g.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_up, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->xi.p, (const float *)c->xs.p, (const int32_t *)c->xsum.p,
-                                    m->pair_tok, m->form, (int2 *)c->rec.p, 0, (float *)c->u.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
+                                    m->pair_tok, m->form, (int4 *)c->rec.p, 0, (float *)c->u.p, I, (int)P, D, I, st, g_q4r4_relaxed, c->sms));
         CKR(launch_act_mul((float *)c->g.p, (const float *)c->u.p, (int64_t)P * I, MOTY_ACT_SILU, st));
         CKR(launch_quant_g32((const float *)c->g.p, (int)P, I, (int8_t *)c->hq.p, (float *)c->hxs.p, (int32_t *)c->hxsum.p, st));
         CKR(launch_q4r4_mma_grouped((const Q4Tile *)m->t_down, m->counters, ntiles_max, T, m->counters + 1,
                                     (const int8_t *)c->hq.p, (const float *)c->hxs.p, (const int32_t *)c->hxsum.p,
-                                    nullptr, m->form, (int2 *)c->rec.p, 1, (float *)c->h.p, D, (int)P, I, D, st, g_q4r4_relaxed, c->sms));
+                                    nullptr, m->form, (int4 *)c->rec.p, 1, (float *)c->h.p, D, (int)P, I, D, st, g_q4r4_relaxed, c->sms));
     }
     CKR(launch_moe_combine(out, (const float *)c->h.p, wp, m->pos_of, m->ord, S, K, D, st));
     if (idx_out) CK(cudaMemcpyAsync(idx_out, m->idx, P * 4, cudaMemcpyDeviceToDevice, st));

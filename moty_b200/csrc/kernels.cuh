@@ -130,12 +130,11 @@ int launch_q8_mma_grouped(const Q8Tile *tiles, const int *ntiles_dev, int ntiles
 
 // ---- q4r4_mma.cu: Q4R4 x a batch of rows, integer MMA per group + the sequential f32 chain ----
 int launch_q4r4_mma(const uint8_t *w, const uint16_t *d, const int8_t *xq, const float *xs, const int32_t *xsum,
-                    int2 *rec, uint8_t *form, float *y, int ldy, int S, int I, int O, int q8, int sms, cudaStream_t st,
-                    int relax = 0);
+                    int4 *rec, float *y, int ldy, int S, int I, int O, int q8, int sms, cudaStream_t st, int relax = 0);
 
 int launch_q4r4_mma_grouped(const Q4Tile *tiles, const int *ntiles_dev, int ntiles_max, int tile_rows,
                             const int *npairs_dev, const int8_t *xq, const float *xs, const int32_t *xsum,
-                            const int *xmap, const uint8_t *form, int2 *rec, int build_rec, float *y, int ldy, int P,
+                            const int *xmap, const uint8_t *form, int4 *rec, int build_rec, float *y, int ldy, int P,
                             int I, int O, cudaStream_t st, int relax = 0, int sms = 148);
 
 // ---- router.cu ----------------------------------------------------------------------
