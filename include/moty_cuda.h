@@ -162,7 +162,8 @@ int moty_cuda_set_i4g_float_path(int on);
  * what moty_matmul_q4r4_s computes, which has two formulas for a group's term and picks one by the token's place in its
  * 32-token tile (hw/hw_q4r4.h:58-59 token by token, :78-81 four tokens at a time); 1 = the token-by-token formula for
  * every token: tokens the reference treats that way keep their bits, the others move by the rounding of one fused
- * multiply-add per group (about 1e-7 of the row's largest term), and the kernel sheds a third of its instructions.
+ * multiply-add per group (about 1e-7 of the row's largest term), and the kernel sheds the second of its two
+ * accumulate steps (1.2x on large batches).
  * Batches of up to four rows are not affected.  Returns the previous value. */
 int moty_cuda_set_q4r4_batch_relaxed(int on);
 int moty_cuda_mat_apply_dev(MotyCudaMat *w, float *y_dev, const float *x_dev, int S, void *stream);

@@ -352,6 +352,10 @@ template <int NT, bool Q8, bool RELAX>
 static int launch_mma_t(const Q4MmaArgs &a, cudaStream_t st, int sms, int ntiles_max = 0) {
     const long long rows = a.tiles ? ntiles_max : (a.S + 8 * NT - 1) / (8 * NT);
     const long long ctas4 = ((a.O + 15) / 16 + 7) / 8 * rows, slots = 3LL * sms;
+    // fewer CTAs than SMs (a few tokens x a matrix of few, long rows): the call streams the weights through a handful of
+    // CTAs, and what counts is bytes in flight per CTA: eight warps, one M tile each, three stages
+    // (3840 x 15360 at S = 16: 60 CTAs, 60 us against 71)
+    if (ctas4 < sms) return launch_mma_tm<NT, Q8, RELAX, 1, 3, 8>(a, st, ntiles_max);
     if (ctas4 > slots && ctas4 < 3 * slots) return launch_mma_tm<NT, Q8, RELAX, 2, 2, 8>(a, st, ntiles_max);
     return launch_mma_tm<NT, Q8, RELAX, 2, 2, 4>(a, st, ntiles_max);
 }
