@@ -525,8 +525,10 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
             return launch_i4g_gemv2((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
                                     (const float *)c->sx.p, y, (float *)c->rec.p, c->err_dev + 2, I, O, c->sms, st);
         }
-        return launch_i4g_rows((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
-                               (const float *)c->sx.p, y, S, I, O, st);
+        // two rows and more: integer MMA per group, the f32 chain in registers
+        CKR(moty_grow(c, &c->rec, i4g_mma_scratch_bytes(S, I)));
+        return launch_i4g_mma((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
+                              (const float *)c->sx.p, (int *)c->rec.p, y, S, I, O, c->sms, st);
     }
     return moty_set_error(MOTY_CUDA_EARG, "mat_apply: format %d", w->fmt);
 }

@@ -98,10 +98,6 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
 size_t attn_scratch_bytes(int S, int H, int KV, int hd, int sms);
 int launch_attn_gate(float *ctx, const float *gate, long long n, cudaStream_t st);
 
-// ---- i4g.cu: WF_I4G (grouped int4, group 32, f32 group scales) x row-quantized activations ----
-int launch_i4g_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx, float *y,
-                    int S, int I, int O, cudaStream_t st);
-
 // ---- q4r4_gemv2.cu: Q4R4 / Q8R4 decode GEMV in two phases (parallel integer sums, then the chain) ----
 bool q4r4_gemv2_supported(int I, int O, int q8, int sms);
 size_t q4r4_gemv2_scratch_bytes(int I, int O);
@@ -109,6 +105,11 @@ int launch_q4r4_gemv2(const uint8_t *w, const uint16_t *d, const float *x, float
                       int I, int O, int q8, int sms, cudaStream_t st);
 
 // the reference's default (IDOT4 unset) product for the same layout: f32 activations x dequantized int4
+// ---- i4g_mma.cu: WF_I4G (grouped int4, group 32, f32 group scales) x row-quantized activations, two rows and more:
+// one integer MMA per group, the f32 chain in registers; i4g.cu: the reference's default f32 x int4 product ----
+size_t i4g_mma_scratch_bytes(int S, int I);
+int launch_i4g_mma(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx, int *rec, float *y,
+                   int S, int I, int O, int sms, cudaStream_t st);
 int launch_i4g_f32_rows(const uint8_t *w4, const float *scale, const float *x, float *y, int S, int I, int O, cudaStream_t st);
 int launch_i4g_gemv2(const uint8_t *w4, const float *gscale, const int8_t *xi, const float *sx, float *y, float *ab,
                      int *err, int I, int O, int sms, cudaStream_t st);

@@ -228,6 +228,26 @@ def test_i4g_vs_oracle(gpu, oracle, O, I, S):
     assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
 
 
+@pytest.mark.parametrize("O,I,S", [(4096, 256, 320), (4100, 320, 157), (2052, 3840, 33), (1000, 64, 9), (515, 192, 70), (130, 16384, 12),
+                                   (3838, 15360, 19), (1024, 1024, 512)])
+def test_i4g_batches_vs_oracle(gpu, oracle, O, I, S):
+    """WF_I4G batches of nine rows and more (the tensor-core kernel, one integer MMA per group): ragged in every dimension
+    -- rows not a multiple of 128, tokens not a multiple of 8, group counts below and not a multiple of the 8-group
+    stage -- and codes at both extremes with saturating activations.  Bit-exact."""
+    rng = np.random.default_rng(O + 3 * I + S)
+    Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
+    q4, sc = oracle.pack_int4_grouped(Wf)
+    x = rng.standard_normal((S, I)).astype(np.float32)
+    y = gpu.mat_apply(gpu.Mat.i4g(q4, sc, O, I), x)
+    yo = oracle.matmul_i4g_idot_s(x, q4, sc)
+    assert same_bits(y, yo), f"max diff {np.abs(y - yo).max()} of {np.abs(yo).max()}"
+    if O <= 1100:
+        for fill in (0x00, 0xFF):
+            q4 = np.full((O, I // 2), fill, np.uint8); sc = rng.uniform(0.1, 0.5, (O, I // 32)).astype(np.float32)
+            x = np.zeros((S, I), np.float32); x[0] = 1000.0; x[1, ::2] = -3.0; x[1, 1::2] = 3.0; x[3:] = rng.standard_normal((S - 3, I))
+            assert same_bits(gpu.mat_apply(gpu.Mat.i4g(q4, sc, O, I), x), oracle.matmul_i4g_idot_s(x, q4, sc))
+
+
 def test_i4g_golden_and_extremes(gpu, oracle):
     g = golden("matmul_i4g")
     for tag in ("a", "b"):
