@@ -226,9 +226,13 @@ def run_extras(torch, mb, dev, stream, W8, local):
         q4 = rng.integers(0, 256, nblk * nb * 64, dtype=np.uint8)
         s16 = np.full(nblk * nb * 4, 0x1A00, np.uint16)               # f16 0.00293
         W4.append(mb.Mat.q4r4(q4, s16, O, I, device=local))
+    Wg = []                                                            # the legacy grouped int4 (row-major nibbles, f32 group scales)
+    for (O, I) in SHAPES:
+        Wg.append(mb.Mat.i4g(rng.integers(0, 256, (O, I // 2), dtype=np.uint8),
+                             np.full((O, I // 32), 0.003, np.float32), O, I, device=local))
     with torch.cuda.stream(stream):
         for fmt, mats, S, passes in (("q8_0", W8, 16, 6), ("q8_0", W8, 512, 3), ("q4r4", W4, 1, 10), ("q4r4", W4, 16, 4), ("q4r4", W4, 512, 2),
-                                       ("q4r4_relaxed", W4, 16, 4), ("q4r4_relaxed", W4, 512, 2)):
+                                       ("q4r4_relaxed", W4, 16, 4), ("q4r4_relaxed", W4, 512, 2), ("i4g", Wg, 16, 4), ("i4g", Wg, 512, 2)):
             # (q4r4_relaxed: after moty_cuda_set_q4r4_batch_relaxed(1) -- one formula for a group's term, within 1e-5)
             mb.lib().moty_cuda_set_q4r4_batch_relaxed(1 if fmt == "q4r4_relaxed" else 0)
             xs = [torch.randn((S, I), device=dev) for (_, I) in SHAPES]
@@ -245,12 +249,13 @@ def run_extras(torch, mb, dev, stream, W8, local):
             torch.cuda.synchronize()
             for i, (O, I) in enumerate(SHAPES):
                 us = statistics.mean(a.elapsed_time(b) for a, b in ev[i]) * 1e3
-                nbytes = algo_bytes(O, I, S) if fmt == "q8_0" else q4r4_bytes(O, I, S)
+                nbytes = (algo_bytes(O, I, S) if fmt == "q8_0" else
+                          O * I // 2 + 4 * O * (I // 32) + 4 * S * I + 4 * S * O if fmt == "i4g" else q4r4_bytes(O, I, S))
                 out["rows"].append({"fmt": fmt, "S": S, "O": O, "I": I, "us": round(us, 2),
                                     "GBs": round(nbytes / us / 1e3, 1), "TOPS": round(2.0 * S * O * I / us / 1e6, 2)})
             del xs, ys
     mb.lib().moty_cuda_set_q4r4_batch_relaxed(0)
-    del W4
+    del W4, Wg
     out["moe"] = run_moe_extras(torch, mb, dev, stream, local)
     out["blocks"] = run_block_extras(torch, mb, dev, stream, local)
     # the model-level view of the same kernels: a greedy decode of the configs[0] shape (wall clock, whole steps)
