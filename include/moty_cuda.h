@@ -120,7 +120,10 @@ int moty_cuda_host_free(void *p);
  *                                                                         (hw/hw_q4r4.h:3-11)
  *   MOTY_WF_Q8R4 codes int8 [ceil(O/4)][I/32][128] (4 rows x 32 codes), scales as Q4R4
  *                                                                         (hw/hw_q4r4.h:92-99)
- *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55)
+ *   MOTY_WF_I4   codes uint8 [O][(I+1)/2], scales f32 [O]               (nn/quant.c:35-55); kept on the device as
+ *                the int8 codes nibble - 8 (twice the bytes): the integer path of moty_matmul_i4_s (nn/matmul.c:75-101,
+ *                IDOT4=1) is the Q8_0 product over those codes, so every Q8_0 kernel serves it bit for bit;
+ *                moty_cuda_mat_shape still reports MOTY_WF_I4, moty_cuda_mat_bytes the bytes held
  *   MOTY_WF_I4G  codes uint8 [O][I/2] (even element in the low nibble), scales f32 [O][I/32]: grouped int4,
  *                group size 32 (nn/quant.c:57-83); applied through the integer path of
  *                moty_matmul_i4_grouped_s (nn/matmul.c:164-197, IDOT4=1) when I % 64 == 0 and I <= 16384,

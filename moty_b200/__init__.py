@@ -148,8 +148,9 @@ class Mat:
         return cls(WF_Q8R4, np.ascontiguousarray(q8, np.int8), np.ascontiguousarray(s16, np.uint16), O, I, device, rows)
 
     @classmethod
-    def i4(cls, q4, scale, O, I, device=0):
-        return cls(WF_I4, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device)
+    def i4(cls, q4, scale, O, I, device=0, rows=None):
+        """WF_I4: q4 [O][(I+1)/2] (even element in the low nibble), scale f32 [O]."""
+        return cls(WF_I4, np.ascontiguousarray(q4, np.uint8), _f32(scale), O, I, device, rows)
 
     @classmethod
     def i4g(cls, q4, scale, O, I, device=0):

@@ -340,6 +340,32 @@ extern "C" int moty_cuda_upload_mat_rows(MotyCudaMat **out, int fmt, const void 
     if (!m) return moty_set_error(MOTY_CUDA_ENOMEM, "upload_mat: host allocation");
     memset(m, 0, sizeof *m);
     m->fmt = fmt; m->O = rows; m->I = I; m->device = device; m->code_bytes = cb; m->scale_bytes = sb;
+    if (fmt == MOTY_WF_I4) {
+        // Per-row int4 rows are kept as the int8 codes nibble - 8: moty_matmul_i4_s with IDOT4=1 is
+        // scale[o] * sx[s] * (float)dot_i4i8(...) (nn/matmul.c:75-101), the integer dot over (nibble - 8) and the Q8_0
+        // epilogue, so every Q8_0 kernel -- streaming GEMV, mma.sync batches, tcgen05 GEMM -- serves them bit for bit.
+        // Twice the bytes in HBM; a packed-nibble stream for this legacy layout is not built.
+        void *packed = nullptr;
+        cudaError_t e4 = cudaMalloc(&packed, cb + 256);
+        if (e4 == cudaSuccess) e4 = cudaMalloc(&m->codes, (size_t)rows * I + 256);
+        if (e4 == cudaSuccess) e4 = cudaMalloc(&m->scales, sb + 256);
+        if (e4 == cudaSuccess) e4 = cudaMemcpyAsync(packed, (const char *)codes + cb0, cb, cudaMemcpyHostToDevice, c->stream);
+        if (e4 == cudaSuccess) e4 = cudaMemcpyAsync(m->scales, (const char *)scales + sb0, sb, cudaMemcpyHostToDevice, c->stream);
+        int rc4 = 0;
+        if (e4 == cudaSuccess) rc4 = launch_i4_rows_to_i8((const uint8_t *)packed, (int8_t *)m->codes, rows, I, c->stream);
+        if (e4 == cudaSuccess) e4 = cudaStreamSynchronize(c->stream);
+        if (packed) cudaFree(packed);
+        if (e4 != cudaSuccess || rc4 != 0) {
+            if (m->codes) cudaFree(m->codes);
+            if (m->scales) cudaFree(m->scales);
+            delete m;
+            return rc4 != 0 ? rc4 : moty_set_error(MOTY_CUDA_ENOMEM, "upload_mat (int4 rows): %s", cudaGetErrorString(e4));
+        }
+        m->fmt = MOTY_WF_I8; m->src_fmt = MOTY_WF_I4; m->code_bytes = (size_t)rows * I;
+        q8_tc_make_tmap(m);
+        *out = m;
+        return 0;
+    }
     cudaError_t e = cudaMalloc(&m->codes, cb + 256);
     if (e == cudaSuccess && sb) e = cudaMalloc(&m->scales, sb + 256);
     if (e != cudaSuccess) {
@@ -380,7 +406,7 @@ extern "C" int64_t moty_cuda_mat_bytes(const MotyCudaMat *m) { return m ? (int64
 
 extern "C" int moty_cuda_mat_shape(const MotyCudaMat *m, int *fmt, int *O, int *I, int *device) {
     if (!m) return moty_set_error(MOTY_CUDA_EARG, "mat_shape: null");
-    if (fmt) *fmt = m->fmt;
+    if (fmt) *fmt = m->src_fmt ? m->src_fmt : m->fmt;
     if (O) *O = m->O;
     if (I) *I = m->I;
     if (device) *device = m->device;
@@ -503,13 +529,6 @@ static int mat_apply_on(DevCtx *c, MotyCudaMat *w, float *y, const float *x, int
         return launch_q4r4_mma((const uint8_t *)w->codes, (const uint16_t *)w->scales, (const int8_t *)c->xi.p,
                                (const float *)c->xs.p, (const int32_t *)c->xsum.p, (int4 *)c->rec.p,
                                y, O, S, I, O, 1, c->sms, st, g_q4r4_relaxed);
-    }
-    if (w->fmt == MOTY_WF_I4) {
-        CKR(moty_grow(c, &c->xi, (size_t)S * I + 16));
-        CKR(moty_grow(c, &c->sx, (size_t)S * 4));
-        CKR(launch_qrow_i8(x, (int8_t *)c->xi.p, (float *)c->sx.p, S, I, st));
-        return launch_i4_rows((const uint8_t *)w->codes, (const float *)w->scales, (const int8_t *)c->xi.p,
-                              (const float *)c->sx.p, y, S, I, O, st);
     }
     if (w->fmt == MOTY_WF_I4G) {
         // moty_matmul_i4_grouped_s: the integer path (IDOT4=1) unless the caller asked for the reference's default, the

@@ -104,6 +104,7 @@ int moty_grow_zero(DevCtx *c, Buf *b, size_t bytes);   // device buffer, zero-fi
 
 struct MotyCudaMat {
     int fmt, O, I, device;
+    int src_fmt;        // the format it was uploaded in when that differs from fmt (WF_I4 rows are kept as WF_I8 codes), else 0
     void *codes;        // device
     void *scales;       // device
     size_t code_bytes, scale_bytes;

@@ -219,23 +219,3 @@ int launch_q8_any(const int8_t *W, const float *scale, const int8_t *xi, const f
     return 0;
 }
 
-// per-row int4 weights (WF_I4) with int8 activations: moty_matmul_i4_s, IDOT4=1
-// (nn/matmul.c:75-106)
-__global__ void __launch_bounds__(256) i4_rows_kernel(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx,
-                                                      float *y, int S, int I, int O) {
-    int o = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (o >= O) return;
-    const uint8_t *wr = w4 + (size_t)o * ((I + 1) / 2);
-    for (int s = 0; s < S; s++) {
-        int d = dot_i4_any(wr, xi + (size_t)s * I, I, lane);
-        if (lane == 0) y[(size_t)s * O + o] = __fmul_rn(__fmul_rn(scale[o], sx[s]), (float)d);
-    }
-}
-
-int launch_i4_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx,
-                   float *y, int S, int I, int O, cudaStream_t st) {
-    if (O <= 0 || S <= 0) return 0;
-    i4_rows_kernel<<<(O + 7) / 8, 256, 0, st>>>(w4, scale, xi, sx, y, S, I, O);
-    CK(cudaGetLastError());
-    return 0;
-}

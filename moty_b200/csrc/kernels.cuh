@@ -36,9 +36,6 @@ struct Q8Args {
 int launch_q8_small(const Q8Args &a, int sms, cudaStream_t st);
 int launch_dot_i8i8_rows(const int8_t *w, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
 int launch_dot_i4i8_rows(const uint8_t *w4, const int8_t *x, int nrows, int n, int32_t *out, cudaStream_t st);
-// per-row int4 weights (WF_I4) against int8 rows, same epilogue as Q8_0
-int launch_i4_rows(const uint8_t *w4, const float *scale, const int8_t *xi, const float *sx,
-                   float *y, int S, int I, int O, cudaStream_t st);
 
 int launch_q8_any(const int8_t *W, const float *scale, const int8_t *xi, const float *sx, float *y, int32_t *acc,
                   int S, int I, int O, cudaStream_t st);

@@ -201,13 +201,29 @@ def test_q4r4_long_rows_and_int16_worst_case(gpu, oracle):
 
 
 def test_i4_rows(gpu, oracle):
+    """Per-row int4 (WF_I4): held on the device as the int8 codes nibble - 8, so one row goes through the streaming
+    GEMV, small batches through the mma.sync kernel and large ones through the tcgen05 GEMM -- all bit for bit
+    moty_matmul_i4_s with IDOT4=1; odd row lengths, row shards, and the format the handle reports."""
     rng = np.random.default_rng(9)
-    for (O, I, S) in ((64, 128, 1), (33, 101, 3)):
+    for (O, I, S) in ((64, 128, 1), (33, 101, 3), (1024, 1024, 1), (1024, 1024, 5), (1000, 4096, 12), (1024, 1024, 64),
+                      (515, 3840, 512), (300, 15360, 9), (77, 16384, 2)):
         Wf = (rng.standard_normal((O, I)) * 0.02).astype(np.float32)
         q4, sc = oracle.pack_int4(Wf)
         x = rng.standard_normal((S, I)).astype(np.float32)
         W = gpu.Mat.i4(q4, sc, O, I)
-        assert same_bits(gpu.mat_apply(W, x), oracle.matmul_i4_idot_s(x, q4, sc, I))
+        assert same_bits(gpu.mat_apply(W, x), oracle.matmul_i4_idot_s(x, q4, sc, I)), (O, I, S)
+    O, I = 1000, 1024
+    q4 = rng.integers(0, 256, (O, I // 2), dtype=np.uint8); sc = rng.uniform(0.001, 0.02, O).astype(np.float32)
+    x = rng.standard_normal((3, I)).astype(np.float32)
+    W = gpu.Mat.i4(q4, sc, O, I)
+    whole = gpu.mat_apply(W, x)
+    assert same_bits(whole, oracle.matmul_i4_idot_s(x, q4, sc, I))
+    parts = [gpu.mat_apply(gpu.Mat.i4(q4, sc, O, I, rows=(a, b)), x) for a, b in ((0, 252), (252, 501), (501, 1000))]
+    assert same_bits(np.concatenate(parts, axis=1), whole)
+    import ctypes as C
+    fmt = C.c_int(-1)
+    assert gpu.lib().moty_cuda_mat_shape(W.h, C.byref(fmt), None, None, None) == 0 and fmt.value == gpu.WF_I4
+    assert W.nbytes() == O * I + 4 * O
 
 
 @pytest.mark.parametrize("O,I", [(1024, 1024), (3072, 1024), (1022, 3072), (515, 3840), (258, 15360), (77, 16384), (5, 32), (300, 96)])
