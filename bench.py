@@ -989,25 +989,45 @@ def run_case(args):
             us = time_moe(torch, layers, name, S, dev, stream, reps=max(1, args.steps // 16), run=16)
         print(json.dumps({"case": args.case, "us_per_layer": round(us, 2)}), flush=True)
         return
-    if parts[0] == "decode" and parts[1] == "olmoe":    # decode:olmoe[:NGEN] -- configs[2] shape: int8 attention matrices and experts
+    if parts[0] == "decode" and parts[1] in ("olmoe", "qwen3-30b-a3b"):
+        # decode:olmoe[:NGEN] -- configs[2] shape: int8 attention matrices and experts, 16 layers, 16 heads
+        # decode:qwen3-30b-a3b[:NGEN] -- configs[3] shape: Q4R4 attention matrices and experts, 48 layers, 32 query / 4 KV
+        #   heads, 128 experts top-8 of width 768, top-k weights renormalised; the tied head stays int8 as in the reference
+        #   (load_embed_q8).  Four weight sets are cycled over the layers in both.
         import time
         from moty_b200.decoder import DenseDecoder, DenseLayer
+        name = parts[1]
         ngen = int(parts[2]) if len(parts) > 2 else 256
-        NL, D, H, hd, V, PROMPT = 16, 2048, 16, 128, 50304, 512
-        E, K, I, _, _ = MOE_SHAPES["olmoe"]
-        moes, per_expert = make_moe_layers(mb, "olmoe", 4, 0, rng)          # four expert sets, cycled over the 16 layers
+        if name == "olmoe":
+            NL, D, H, KVH, hd, V, PROMPT, norm_topk = 16, 2048, 16, 16, 128, 50304, 512, 0
+        else:
+            NL, D, H, KVH, hd, V, PROMPT, norm_topk = 48, 2048, 32, 4, 128, 151936, 512, 1
+        E, K, I, _, efmt = MOE_SHAPES[name]
+        moes, per_expert = make_moe_layers(mb, name, 4, 0, rng)             # four expert sets, cycled over the layers
         for m in moes:
             m.set_router(mb.Mat.f32((rng.standard_normal((E, D)) * 0.02).astype(np.float32), device=0))
         one = lambda n: np.ones(n, np.float32)
         raw = lambda O, Kk: (rng.integers(-127, 128, (O, Kk), dtype=np.int8), rng.uniform(0.0002, 0.0006, O).astype(np.float32))
+        def q4mat(O, Kk):                               # random Q4R4 codes, f16 scale 0.00293 (outputs of the size of the inputs)
+            nblk, nb = (O + 3) // 4, Kk // 32
+            return mb.Mat.q4r4(rng.integers(0, 256, nblk * nb * 64, dtype=np.uint8), np.full(nblk * nb * 4, 0x1A00, np.uint16), O, Kk, device=0)
+        qw, kw = H * hd, KVH * hd
+        sets = []
+        for i in range(4):
+            if efmt == "i8":
+                q, k, v = raw(qw, D), raw(kw, D), raw(kw, D)
+                qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=0)
+                sets.append((mb.Mat.i8(*q, device=0), mb.Mat.i8(*k, device=0), mb.Mat.i8(*v, device=0), mb.Mat.i8(*raw(D, qw), device=0), qkv))
+                attn_bytes = 2 * D * qw + 2 * D * kw
+            else:
+                sets.append((q4mat(qw, D), q4mat(kw, D), q4mat(kw, D), q4mat(D, qw), q4mat(qw + 2 * kw, D)))
+                attn_bytes = (2 * D * qw + 2 * D * kw) * 72 // 128
         layers = []
         for i in range(NL):
-            q, k, v = raw(H * hd, D), raw(H * hd, D), raw(H * hd, D)
-            qkv = mb.Mat.i8(np.concatenate([q[0], k[0], v[0]]), np.concatenate([q[1], k[1], v[1]]), device=0)
-            layers.append(DenseLayer(mb.Mat.i8(*q, device=0), mb.Mat.i8(*k, device=0), mb.Mat.i8(*v, device=0), mb.Mat.i8(*raw(D, H * hd), device=0),
-                                     None, None, None, one(D), one(D), one(hd), one(hd), qkv=qkv, moe=moes[i % 4], norm_topk=0))
+            q, k, v, o, qkv = sets[i % 4]
+            layers.append(DenseLayer(q, k, v, o, None, None, None, one(D), one(D), one(hd), one(hd), qkv=qkv, moe=moes[i % 4], norm_topk=norm_topk))
         head = mb.Mat.i8(rng.integers(-127, 128, (V, D), dtype=np.int8), rng.uniform(0.005, 0.015, V).astype(np.float32), device=0)
-        dec = DenseDecoder(layers, head, one(D), H, H, hd, PROMPT + ngen + 8, max_S=PROMPT)
+        dec = DenseDecoder(layers, head, one(D), H, KVH, hd, PROMPT + ngen + 8, max_S=PROMPT)
         prompt = np.random.default_rng(1).integers(0, V, PROMPT).astype(np.int32)
         dec.step(prompt, 0); dec.step([1], PROMPT)
         torch.cuda.synchronize(); t0 = time.perf_counter()
@@ -1021,7 +1041,7 @@ def run_case(args):
         torch.cuda.synchronize(); t3 = time.perf_counter()
         tg = dec.greedy_graph(tok, PROMPT, ngen)
         torch.cuda.synchronize(); t4 = time.perf_counter()
-        wbytes = NL * (K * per_expert + 4 * D * H * hd + 4 * E * D) + head.nbytes()
+        wbytes = NL * (K * per_expert + attn_bytes + 4 * E * D) + head.nbytes()
         print(json.dumps({"case": args.case, "prefill_tok_s": round(PROMPT / (t1 - t0), 1), "decode_tok_s": round(ngen / (t2 - t1), 1),
                           "ms_per_token": round((t2 - t1) / ngen * 1e3, 3), "weight_MB_per_token": round(wbytes / 1e6, 1),
                           "graph_decode_tok_s": round(ngen / (t4 - t3), 1), "graph_ms_per_token": round((t4 - t3) / ngen * 1e3, 3),

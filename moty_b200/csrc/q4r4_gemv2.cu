@@ -340,7 +340,11 @@ bool q4r4_gemv2_supported(int I, int O, int q8, int sms) {
     if (I % 32 != 0 || I <= 0 || I > MOTY_QROW_MAX || O <= 0) return false;
     if (q8) return true;
     const int nbands = (O + 31) / 32;
-    return nbands < sms * 6 && (long long)((O + 3) / 4) * (I / 32) >= 400000;
+    // from 60 k cells up (2048 x 4096): measured inside a Qwen3-30B-A3B-shaped decode step, where the projections
+    // around the attention are 5120 x 2048 and 2048 x 4096 -- 2.71 -> 2.38 ms per token against the one-launch
+    // streaming kernel, although timed alone in a loop of its own the two launches are the slower ones at that size
+    // (9.2 against 5.7 us on 5120 x 2048): their first phase streams weights before its dependency wait
+    return nbands < sms * 6 && (long long)((O + 3) / 4) * (I / 32) >= 60000;
 }
 
 // WF_I4G through the two phases: xi/sx are the row quantized by qrow_i8 (same stream, just before)
