@@ -689,14 +689,19 @@ int launch_attn_core(float *ctx, float *q, float *k, const float *v, int S, int 
     // few (token, KV head) pairs: split the positions so that every SM gets a few CTAs
     int nsplit = 1;
     const long long units = (long long)S * KV * ngy;
+    // A split's positions come in multiples of one pass of the eight warps (64; with 128, the sub-chunk, a context of
+    // 500-1000 positions got too few CTAs: 32 query / 4 KV heads at 513 12.3 -> 9.9 us, 16 / 8 at 1000 11.2 -> 10.1 us;
+    // 32 measured worse).  Three resident sets of CTAs for heads of up to 128, two for wider ones (one CTA per SM there:
+    // 8192 positions 52 -> 44 us, 32768 129 -> 119 us; a single set is better around 2000-4000 and much worse beyond).
+    constexpr int gran = AT_PB * AT_WARPS;
     if (units < 2LL * sms && T > 2 * AT_CH) {                           // (a context of two sub-chunks is not worth a merge launch)
-        nsplit = (int)((3LL * sms + units - 1) / units);
-        const int most = (T + AT_CH - 1) / AT_CH;
+        nsplit = (int)(((NVr == 1 ? 3LL : 2LL) * sms + units - 1) / units);
+        const int most = (T + gran - 1) / gran;
         if (nsplit > most) nsplit = most;
         if (nsplit < 1) nsplit = 1;
     }
     int span = (T + nsplit - 1) / nsplit;
-    span = (span + AT_CH - 1) / AT_CH * AT_CH;
+    span = (span + gran - 1) / gran * gran;
     nsplit = (T + span - 1) / span;
     if (nsplit > 1 && !part) return moty_set_error(MOTY_CUDA_EARG, "attn_core: scratch for %d splits missing", nsplit);
     static bool attr_done[MOTY_MAX_DEV];
