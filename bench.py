@@ -274,7 +274,9 @@ def run_engine_qwen(ngen=128):
     """The reference's own `qwen` engine on the Qwen3-0.6B-shaped synthetic snapshot (64-token prompt, ngen greedy
     steps, QBITS=8): once as it is on the host cores, once with every matrix attached to the GPU through the
     reference-side shim (moty_b200/shim/hw_cuda.c: the per-matrix moty_mat_apply hook, host pointers, a copy in and
-    out per call).  Reports the engine's prefill / decode tok/s of both runs and whether ids and logit rows agree."""
+    out per call).  Reports the engine's prefill / decode tok/s of both runs and whether ids and logit rows agree.  The
+    decode figure is the time in step() + argmax per token, as in the engine's own loop (runtime/rt_gen_loop.h:46-84);
+    writing the trace rows (a hash of every 600 KB logit row) is the shim's instrument and is timed apart, in all three runs."""
     import re
     import shutil
     import tempfile

@@ -53,6 +53,7 @@ static int shim_attach_model(Model *m, int dev) {
 typedef struct {
     int dev, cap_S, max_t;
     float *x, *nrm, *tmp, *q, *k, *v, *ctx, *logits, *final_norm;
+    float *hlogits;                   /* page-locked: the logits row of the latest step (returned to the loop, never freed by it) */
     int *ids, *pos;                   /* token ids of the step; the first position, for the captured decode step */
     float **in_ln, **post_ln;
     MotyCudaAttn **attn;
@@ -82,8 +83,11 @@ static void shim_dev_init(Model *m, int dev, int cap_S, int max_t) {
     d->k = shim_dev_f32(NULL, (int64_t)cap_S * KV * hd, dev); d->v = shim_dev_f32(NULL, (int64_t)cap_S * KV * hd, dev);
     d->logits = shim_dev_f32(NULL, c->vocab, dev);
     d->final_norm = shim_dev_f32(m->base.final_norm, D, dev);
-    void *ids = NULL; SHIM_CK(moty_cuda_dev_alloc(&ids, (size_t)cap_S * 4, dev)); d->ids = ids;
-    void *pos = NULL; SHIM_CK(moty_cuda_dev_alloc(&pos, 4, dev)); d->pos = pos;
+    /* ids[0] and the position sit side by side: a decode token uploads both with one copy (a prompt needs no position
+     * on the device and may use the whole buffer) */
+    void *ids = NULL; SHIM_CK(moty_cuda_dev_alloc(&ids, ((size_t)cap_S + 1) * 4, dev)); d->ids = ids;
+    d->pos = d->ids + 1;
+    void *hl = NULL; SHIM_CK(moty_cuda_host_alloc(&hl, (size_t)c->vocab * 4)); d->hlogits = hl;
     d->graph = NULL; d->decoded = 0;
     d->in_ln = calloc(c->n_layers, sizeof(float *)); d->post_ln = calloc(c->n_layers, sizeof(float *));
     d->attn = calloc(c->n_layers, sizeof(MotyCudaAttn *));
@@ -176,9 +180,9 @@ static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
     checked = 1;
     static int use_graph = -1;
     if (use_graph < 0) { const char *e = getenv("MOTY_SHIM_GRAPH"); use_graph = e ? atoi(e) : 1; }
-    SHIM_CK(moty_cuda_dev_upload(d->ids, ids, (size_t)S * 4, d->dev, NULL));
     if (S == 1 && use_graph && !check) {
-        SHIM_CK(moty_cuda_dev_upload(d->pos, &pos_base, 4, d->dev, NULL));
+        const int idpos[2] = { ids[0], pos_base };
+        SHIM_CK(moty_cuda_dev_upload(d->ids, idpos, 8, d->dev, NULL));
         if (!d->graph && d->decoded >= 1) {             /* the token before this one ran the same sequence uncaptured */
             SHIM_CK(moty_cuda_graph_begin(d->dev, NULL));
             shim_layers(m, 1, pos_base, d->pos, 0, ids);
@@ -188,13 +192,13 @@ static float *shim_step_dev(Model *m, const int *ids, int S, int pos_base) {
         else shim_layers(m, 1, pos_base, d->pos, 0, ids);
         d->decoded++;
     } else {
+        SHIM_CK(moty_cuda_dev_upload(d->ids, ids, (size_t)S * 4, d->dev, NULL));
         shim_layers(m, S, pos_base, NULL, check, ids);
     }
     m->base.kv_len = pos_base + S;
-    float *logit = falloc(c->vocab);
-    SHIM_CK(moty_cuda_dev_download(logit, d->logits, (size_t)c->vocab * 4, d->dev, NULL));
+    SHIM_CK(moty_cuda_dev_download(d->hlogits, d->logits, (size_t)c->vocab * 4, d->dev, NULL));
     SHIM_CK(moty_cuda_kernel_status(d->dev, NULL));
-    return logit;
+    return d->hlogits;
 }
 
 static int g_shim_resident;
@@ -240,10 +244,13 @@ static int shim_run_trace(Model *m, const char *refpath, const char *tracepath) 
     double t1 = now_s();
     int len = np;
     const int force = getenv("MOTY_SHIM_FORCE") && atoi(getenv("MOTY_SHIM_FORCE"));
+    double t_trace = 0;                         /* the trace rows are this file's instrument, not part of run_ref's loop */
     for (int s = 0; s < n_new; s++) {
         int best = argmax_v(logit, m->c.vocab);
+        double ta = now_s();
         shim_trace_row(tf, s, logit, m->c.vocab, best);
-        free(logit);
+        t_trace += now_s() - ta;
+        if (!g_shim_resident) free(logit);      /* (the resident step hands out its own page-locked row) */
         out[len++] = force ? full[np + s] : best;
         if (s == n_new - 1) break;
         logit = shim_step_any(m, &out[len-1], 1, len-1);
@@ -251,8 +258,9 @@ static int shim_run_trace(Model *m, const char *refpath, const char *tracepath) 
     double t2 = now_s();
     fclose(tf);
     printf("C engine : "); for (int i = np; i < nfull; i++) printf("%d ", out[i]);
-    printf("\nprefill %d tok %.4f s %.2f tok/s | decode %d tok %.4f s %.2f tok/s\n",
-           np, t1 - t0, np / (t1 - t0), n_new - 1, t2 - t1, (n_new - 1) / (t2 - t1));
+    const double td = t2 - t1 - t_trace;        /* step + argmax per token, as in runtime/rt_gen_loop.h:46-84 */
+    printf("\nprefill %d tok %.4f s %.2f tok/s | decode %d tok %.4f s %.2f tok/s (writing the trace rows took another %.4f s)\n",
+           np, t1 - t0, np / (t1 - t0), n_new - 1, td, (n_new - 1) / td, t_trace);
     json_free(ref); free(buf); free(prompt); free(full); free(out);
     return 0;
 }
